@@ -1,0 +1,353 @@
+"""Pins the CPU oracle against the reference's own golden vectors and known-answer tests.
+
+Every expected number below is one of vyre's fixtures (file:line given per test); the oracle is only
+trusted by the GPU parity tests because these pass.
+"""
+import math
+
+import numpy as np
+
+import oracle
+
+
+def f32(*v):
+    return np.array(v, dtype=np.float32)
+
+
+def u32(*v):
+    return np.array(v, dtype=np.uint32)
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+# --- vyre-reference/src/float16.rs:90-131 ---------------------------------------------------------
+def test_bf16_f16_conversion_edges():
+    L = oracle.lib()
+    for b, v in [(0x0000, 0.0), (0x8000, -0.0), (0x3C00, 1.0), (0xC000, -2.0), (0x7C00, math.inf),
+                 (0xFC00, -math.inf), (0x0001, 5.9604645e-8), (0x03FF, 6.097555e-5)]:
+        assert bits(f32(L.vyo_f16_to_f32(b)))[0] == bits(f32(v))[0]
+        assert L.vyo_f32_to_f16(v) == b
+    assert math.isnan(L.vyo_f16_to_f32(0x7E01))
+    assert L.vyo_f32_to_f16(math.nan) == 0x7E00
+    assert L.vyo_f32_to_f16(1.00048828125) == 0x3C00
+    assert L.vyo_f32_to_f16(1.00146484375) == 0x3C02
+    for b, v in [(0x0000, 0.0), (0x8000, -0.0), (0x3F80, 1.0), (0xC000, -2.0), (0x7F80, math.inf),
+                 (0xFF80, -math.inf)]:
+        assert bits(f32(L.vyo_bf16_to_f32(b)))[0] == bits(f32(v))[0]
+        assert L.vyo_f32_to_bf16(v) == b
+    assert math.isnan(L.vyo_bf16_to_f32(0x7FC1))
+    assert L.vyo_f32_to_bf16(math.nan) == 0x7FC0
+    tie_even = np.array([0x3F808000], dtype=np.uint32).view(np.float32)[0]
+    tie_odd = np.array([0x3F818000], dtype=np.uint32).view(np.float32)[0]
+    assert L.vyo_f32_to_bf16(float(tie_even)) == 0x3F80
+    assert L.vyo_f32_to_bf16(float(tie_odd)) == 0x3F82
+
+
+def test_numpy_bf16_helper_matches_oracle_scalar():
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal(4096).astype(np.float32) * 3
+    a[:4] = [0.0, -0.0, 1e-40, np.inf]
+    got = oracle.f32_to_bf16_bits(a)
+    L = oracle.lib()
+    want = np.array([L.vyo_f32_to_bf16(float(v)) for v in a], dtype=np.uint16)
+    assert np.array_equal(got, want)
+
+
+# --- vyre-reference/src/execution/typed_ops/float_ops.rs:82-90; ieee754.rs:170-205 -------------------
+def test_canonicalisation_and_ulp_distance():
+    L = oracle.lib()
+    sub = np.array([0x00000001], dtype=np.uint32).view(np.float32)[0]
+    assert bits(f32(L.vyo_canonical_f32(float(sub))))[0] == 0
+    nsub = np.array([0x80000001], dtype=np.uint32).view(np.float32)[0]
+    assert bits(f32(L.vyo_canonical_f32(float(nsub))))[0] == 0x80000000
+    assert L.vyo_ulp_distance(0.0, -0.0) == 0
+    assert L.vyo_ulp_distance(1.0, float(np.nextafter(np.float32(1.0), np.float32(2.0)))) == 1
+    assert L.vyo_ulp_distance(float(sub), 0.0) == 0
+
+
+# --- vyre-primitives/src/math/quantized.rs:78-170 (registry fixtures) ---------------------------------
+def test_int4_primitive_registry_fixtures():
+    assert oracle.unpack_i4x8(u32(0x76210F98), 8).tolist() == [-8, -7, -1, 0, 1, 2, 6, 7]
+    assert oracle.pack_i4x8([-8, -7, -1, 0, 1, 2, 6, 7]).tolist() == [0x76210F98]
+    assert oracle.i4x8_dot_i32(u32(0x76210F98), u32(0x76210F98), 8) == 204
+    assert oracle.i4x8_dot_f32_scaled(u32(0x76210F98), u32(0x76210F98), 1.0, 1.0, 8) == 204.0
+    x = f32(-8, -7, -1, 0, 1, 2, 6, 7)
+    w4 = u32(*[0x76210F98] * 4)
+    assert oracle.i4x8_batched_matvec_f32_scaled(w4, x, f32(1, 1, 1, 1), 1, 4, 8).tolist() == [204.0] * 4
+    assert oracle.i4x8_batched_matvec_f32_scaled(w4, np.tile(x, 2), f32(1, 1, 1, 1), 2, 4, 8).tolist() == [204.0] * 8
+    act = u32(0x76210F98, 0x76210F98)
+    assert oracle.i4x8_batched_matmul_f32_scaled(w4, act, f32(1, 1, 1, 1), f32(1, 1), 2, 4, 8).tolist() == [204.0] * 8
+    assert oracle.i4x8_batched_matmul_top1_f32_scaled(w4, act, f32(1, 1, 1, 1), f32(1, 1), 2, 4, 8).tolist() == [
+        204.0, 204.0, 0.0, 0.0]
+
+
+# --- vyre-libs/src/nn/quant/int4.rs:203-243 -----------------------------------------------------------
+def test_int4_lib_registry_fixtures():
+    assert oracle.i4x8_dot_i32(u32(0xCDEF4321), u32(0xFEDC1234), 8) == 40
+    assert oracle.i4x8_dot_f32_scaled(u32(0xCDEF4321), u32(0xFEDC1234), 0.5, 0.25, 8) == 5.0
+
+
+# --- vyre-primitives/src/math/quantized/tests/layout_contracts.rs:1-108 -------------------------------
+def test_int4_layout_known_answers():
+    assert oracle.pack_i4x8(np.zeros(65, dtype=np.int32)).size == 9
+    rows = [[1, 2, 3, 4, -1, -2, -3, -4, 5], [4, 3, 2, 1, -4, -3, -2, -1, -5], [-8, -7, -6, -5, -4, -3, -2, -1, 0]]
+    packed = np.concatenate([oracle.pack_i4x8(r) for r in rows])
+    assert packed.size == 6  # 3 rows x ceil(9/8) words
+    # clamp contract (cpu.rs:35-61)
+    assert oracle.unpack_i4x8(oracle.pack_i4x8([100, -100]), 2).tolist() == [7, -8]
+    # vyre-libs/src/nn/quant/int4.rs:606-660: the matvec equals the plain sequential f32 loop bit for bit
+    x = f32(1.0, -0.5, 0.25, 2.0, -1.5, 0.75, 1.25, -2.0, 0.5)
+    scales = f32(0.5, 0.25, 0.125)
+    got = oracle.i4x8_batched_matvec_f32_scaled(packed, x, scales, 1, 3, 9)
+    want = []
+    for r, s in zip(rows, scales):
+        acc = np.float32(0)
+        for wv, xv in zip(r, x):
+            acc = np.float32(acc + np.float32(np.float32(wv) * xv))
+        want.append(np.float32(acc * s))
+    assert bits(got).tolist() == bits(np.array(want)).tolist()
+
+
+# --- vyre-libs/src/nn/linear/inner/linear_4bit.rs:1211-1255, 1723-1736 ----------------------------------
+def test_linear_4bit_fixtures():
+    x = np.arange(8, dtype=np.float32)
+    w = u32(0x76543210, 0xFEDCBA98, 0x11111111, 0x00000000)
+    assert oracle.linear_4bit(x, w, np.zeros(4), 8, 4).tolist() == [140.0, 364.0, 28.0, 0.0]
+    x = np.arange(1, 9, dtype=np.float32)
+    assert oracle.linear_4bit(x, u32(0x87654321, 0), np.zeros(2), 8, 2).tolist() == [204.0, 0.0]
+
+
+# --- linear_4bit.rs:1760-1776, 1317-1346, 1357-1395; tests/quantized_linear_affine_fma.rs:157-168 -------
+def test_affine_grouped_fixtures():
+    x = np.arange(1, 9, dtype=np.float32)
+    w = u32(0x87654321, 0)
+    scale, zp, b = f32(0.5, 1.0, 2.0, 1.0), u32(1, 0, 4, 0), f32(0.0, 3.0)
+    assert oracle.linear_4bit_affine_grouped(x, w, scale, zp, b, 8, 2, 4).tolist() == [150.0, 3.0]
+    xb = np.concatenate([x, np.zeros(8, dtype=np.float32)])
+    assert oracle.linear_4bit_affine_grouped(xb, w, scale, zp, b, 8, 2, 4, batch=2).tolist() == [150.0, 3.0, 0.0, 3.0]
+    # weight-reuse shape: K=256, N=8, g=64, B=8
+    act = np.repeat(np.arange(1, 9, dtype=np.float32), 256)
+    out = oracle.linear_4bit_affine_grouped(act, np.full(32 * 8, 0x11111111, dtype=np.uint32), np.ones(32),
+                                            np.zeros(32, dtype=np.uint32), np.arange(8, dtype=np.float32), 256, 8,
+                                            64, batch=8)
+    want = [256.0 * (bi + 1) + o for bi in range(8) for o in range(8)]
+    assert out.tolist() == want
+    # negative dequantised weights
+    out = oracle.linear_4bit_affine_grouped(np.ones(8), np.zeros(2, dtype=np.uint32), f32(2.0, 0.5), u32(15, 14),
+                                            f32(0.0, 1.0), 8, 2, 8)
+    assert out.tolist() == [-240.0, -55.0]
+
+
+# --- linear_4bit.rs:1611-1702: 8 out_dims x 6 group sizes x 48 seeds, assert_eq! exact -------------------
+def test_affine_grouped_generated_sweep_is_exact():
+    checked = 0
+    in_dim = 32
+    for out_dim in [1, 2, 3, 5, 8, 13, 21, 32]:
+        for group_size in [1, 2, 4, 8, 16, 32]:
+            for seed in range(48):
+                groups = -(-in_dim // group_size)
+                x = np.array([((k * 3 + seed) % 19) for k in range(in_dim)], dtype=np.float32)
+                packed = np.zeros((in_dim // 8) * out_dim, dtype=np.uint32)
+                for block in range(in_dim // 8):
+                    for o in range(out_dim):
+                        word = 0
+                        for lane in range(8):
+                            k = block * 8 + lane
+                            word |= ((k * 7 + o * 11 + seed) & 0xF) << (lane * 4)
+                        packed[block * out_dim + o] = word
+                scale = np.zeros(groups * out_dim, dtype=np.float32)
+                zp = np.zeros(groups * out_dim, dtype=np.uint32)
+                for g in range(groups):
+                    for o in range(out_dim):
+                        scale[g * out_dim + o] = [0.25, 0.5, 1.0, 2.0][(g + o + seed) & 3]
+                        zp[g * out_dim + o] = (g * 5 + o + seed) & 0xF
+                bias = np.array([(o + seed) & 7 for o in range(out_dim)], dtype=np.float32)
+                got = oracle.linear_4bit_affine_grouped(x, packed, scale, zp, bias, in_dim, out_dim, group_size)
+                want = oracle.linear_4bit_affine_grouped(x, packed, scale, zp, bias, in_dim, out_dim, group_size,
+                                                         simple=True)
+                assert bits(got).tolist() == bits(want).tolist(), (out_dim, group_size, seed)
+                checked += out_dim
+    assert checked >= 24000
+
+
+# --- tests/quantized_linear_affine_fma.rs:110-155: FMA order vs scalar mul_add oracle, drift <= 1e-4 ----
+def test_affine_grouped_fma_drift_cases():
+    def pack(weights, in_dim, out_dim):
+        p = np.zeros((in_dim // 8) * out_dim, dtype=np.uint32)
+        for block in range(in_dim // 8):
+            for o in range(out_dim):
+                word = 0
+                for lane in range(8):
+                    word |= (int(weights[(block * 8 + lane) * out_dim + o]) & 0xF) << (lane * 4)
+                p[block * out_dim + o] = word
+        return p
+
+    def scalar(x, weights, scales, zps, bias, g):
+        out_dim = len(bias)
+        res = []
+        for o in range(out_dim):
+            acc = np.float32(bias[o])
+            for gs in range(0, len(x), g):
+                grp = gs // g
+                s = np.float32(scales[grp * out_dim + o])
+                zo = np.float32(-1.0) * np.float32(np.float32(zps[grp * out_dim + o]) * s)
+                for k in range(gs, min(gs + g, len(x))):
+                    # dyadic fixture values: the f64 product-sum is exact, so one rounding to f32 == fma
+                    wv = np.float32(float(np.float32(weights[k * out_dim + o])) * float(s) + float(zo))
+                    acc = np.float32(float(x[k]) * float(wv) + float(acc))
+            res.append(acc)
+        return np.array(res, dtype=np.float32)
+
+    in_dim, out_dim = 64, 3
+    x = np.array([((k % 7) - 3.0) * 0.25 for k in range(in_dim)], dtype=np.float32)
+    weights = [((i * 5 + 3) & 0xF) for i in range(in_dim * out_dim)]
+    got = oracle.linear_4bit_affine_grouped(x, pack(weights, in_dim, out_dim), f32(0.25, 0.5, 1.0), u32(7, 8, 2),
+                                            f32(1.0, -2.0, 0.5), in_dim, out_dim, 64)
+    want = scalar(x, weights, [0.25, 0.5, 1.0], [7, 8, 2], [1.0, -2.0, 0.5], 64)
+    assert np.max(np.abs(got - want)) <= 1e-4
+
+    in_dim, out_dim = 32, 5
+    x = np.array([((k % 11) - 5.0) * 0.125 for k in range(in_dim)], dtype=np.float32)
+    weights = [((i * 11 + i // out_dim) & 0xF) for i in range(in_dim * out_dim)]
+    scales = [[0.125, 0.25, 0.5, 1.0][i & 3] for i in range((in_dim // 8) * out_dim)]
+    zps = [((i * 3 + 1) & 0xF) for i in range(len(scales))]
+    bias = [-3.0, -1.0, 0.0, 2.0, 4.0]
+    got = oracle.linear_4bit_affine_grouped(x, pack(weights, in_dim, out_dim), scales, zps, bias, in_dim, out_dim, 8)
+    want = scalar(x, weights, scales, zps, bias, 8)
+    assert np.max(np.abs(got - want)) <= 1e-4
+
+
+# --- vyre-libs/src/nn/quant/int8.rs:80-128 ----------------------------------------------------------------
+def test_int8_fixtures():
+    assert oracle.int8_unpack(u32(10, 20, 30, 40), f32(0.5, 2.0), 4, 2).tolist() == [5.0, 10.0, 60.0, 80.0]
+    assert oracle.int8_pack(u32(255, 256, 1, 0), 4).tolist() == [255, 0, 1, 0]
+
+
+# --- vyre-libs/src/nn/moe/gating.rs:157-180 (expected computed with expf; window 128 ULP) -----------------
+def test_moe_gate_fixture():
+    scores = f32(0.5, 1.0, 0.1, 2.0, 0.3, 3.0, 0.2, 0.4)
+    idx, w = oracle.moe_gate(scores, 2)
+    assert idx.tolist() == [5, 3]
+    mx = np.float32(3.0)
+    s = np.float32(0)
+    for v in scores:
+        s = np.float32(s + np.float32(math.exp(float(np.float32(v - mx)))))
+    want = [np.float32(np.float32(math.exp(float(np.float32(scores[i] - mx)))) / s) for i in (5, 3)]
+    L = oracle.lib()
+    for g, e in zip(w, want):
+        assert L.vyo_ulp_distance(float(g), float(e)) <= 128
+
+
+# --- vyre-libs/src/nn/moe/softmax_top_k.rs:111-136; top_k.rs:64-126 -----------------------------------------
+def test_softmax_top_k_and_top_k_fixtures():
+    scores = np.arange(1, 9, dtype=np.float32)
+    idx, w, bv, bi = oracle.softmax_top_k(scores, 2)
+    assert idx.tolist() == [7, 6] and bi.tolist() == [7, 6]
+    ev = np.exp((scores - np.float32(8.0)).astype(np.float32)).astype(np.float32)
+    s = np.float32(0)
+    for v in ev:
+        s = np.float32(s + v)
+    L = oracle.lib()
+    for g, e in zip(w, [ev[7] / s, ev[6] / s]):
+        assert L.vyo_ulp_distance(float(g), float(e)) <= 128
+    for g, e in zip(bv, [ev[7], ev[6]]):
+        assert L.vyo_ulp_distance(float(g), float(e)) <= 128
+    assert oracle.top_k(np.arange(1, 9, dtype=np.float32), 2).tolist() == [7, 6]
+    assert oracle.top_k(np.arange(8, 0, -1).astype(np.float32), 2).tolist() == [0, 1]
+    assert oracle.top_k(f32(3, 1, 4, 1, 5, 9, 2, 6), 3).tolist() == [5, 7, 4]
+
+
+# --- vyre-libs/src/nn/activation/swiglu.rs:51-79 ------------------------------------------------------------
+def test_swiglu_fixture():
+    gate, up = f32(0.0, 1.0, -1.0, 2.0), f32(1.0, 2.0, 3.0, 4.0)
+    got = oracle.swiglu(gate, up)
+    L = oracle.lib()
+    for g, u, o in zip(gate, up, got):
+        sig = np.float32(1.0) / np.float32(np.float32(1.0) + np.float32(math.exp(-float(g))))
+        want = np.float32(np.float32(g * u) * sig)
+        assert L.vyo_ulp_distance(float(o), float(want)) <= 128
+
+
+# --- vyre-libs/src/nn/moe/expert_mlp.rs:161-206 (tolerance 1e-5 in the reference test) ---------------------
+def test_expert_mlp_fixture():
+    x = f32(1.0, 2.0)
+    wg, bg = f32(0.5, -0.25, 1.0, 0.75), f32(0.1, -0.2)
+    wu, bu = f32(0.25, 0.5, -0.5, 1.25), f32(0.0, 0.3)
+    wd, bd = f32(1.0, -0.5, 0.25, 0.75), f32(0.2, -0.1)
+    got = oracle.expert_mlp(x, wg, bg, wu, bu, wd, bd, 2, 2, 2)
+    hidden = []
+    for h in range(2):
+        g, u = float(bg[h]), float(bu[h])
+        for k in range(2):
+            g += float(x[k]) * float(wg[k * 2 + h])
+            u += float(x[k]) * float(wu[k * 2 + h])
+        hidden.append(g * u / (1.0 + math.exp(-g)))
+    want = [float(bd[0]) + hidden[0] * float(wd[0]) + hidden[1] * float(wd[2]),
+            float(bd[1]) + hidden[0] * float(wd[1]) + hidden[1] * float(wd[3])]
+    assert np.max(np.abs(got - np.array(want, dtype=np.float32))) <= 1e-5
+
+
+# --- vyre-libs/src/nn/moe/moe_layer.rs:131-181 ---------------------------------------------------------------
+def test_moe_layer_accumulate_fixture():
+    out = oracle.moe_layer_accumulate(f32(0.6, 0.4), f32(1.0, 2.0, 3.0, 4.0), 2, 2)
+    assert abs(out[0] - 1.8) < 1e-5 and abs(out[1] - 2.8) < 1e-5
+
+
+# --- linear_rows: vyre-libs/src/nn/linear/inner/builder.rs:253-361 (f32 acc, cast on store) ----------------
+def test_linear_rows_layouts_and_bf16_cast():
+    x = f32(1, 2, 3, 4)  # rows=2, in=2
+    w_in_out = f32(1, 10, 100, 1000)  # [in=2,out=2]
+    assert oracle.linear_rows(x, w_in_out, None, 2, 2, 2).tolist() == [201.0, 2010.0, 403.0, 4030.0]
+    w_out_in = f32(1, 100, 10, 1000)  # [out,in]
+    assert oracle.linear_rows(x, w_out_in, None, 2, 2, 2, weight_out_in=True).tolist() == [201.0, 2010.0, 403.0, 4030.0]
+    assert oracle.linear_rows(x, w_in_out, f32(0.5, -0.5), 2, 2, 2).tolist() == [201.5, 2009.5, 403.5, 4029.5]
+    xb, wb = oracle.f32_to_bf16_bits(x), oracle.f32_to_bf16_bits(w_in_out)
+    out = oracle.linear_rows(xb, wb, None, 2, 2, 2, dtype=oracle.DT_BF16)
+    assert np.array_equal(out, oracle.f32_to_bf16_bits(f32(201.0, 2010.0, 403.0, 4030.0)))
+
+
+# --- vyre-libs/src/math/linalg/matmul.rs:17-60 (wrapping u32) -----------------------------------------------
+def test_matmul_u32_wraps():
+    a = u32(0xFFFFFFFF, 2)  # [1,2]
+    b = u32(2, 3)  # [2,1]
+    assert oracle.matmul_u32(a, b, None, 1, 2, 1).tolist() == [(0xFFFFFFFF * 2 + 6) & 0xFFFFFFFF]
+    # signed reading: (-1)*2 + 2*3 = 4
+    assert np.array(oracle.matmul_u32(a, b, None, 1, 2, 1), dtype=np.uint32).view(np.int32).tolist() == [4]
+
+
+# --- compositions (unpinned by reference fixtures; self-consistency with the pinned pieces) -----------------
+def test_int4_rowmajor_composition_matches_primitive_layout():
+    rng = np.random.default_rng(0)
+    n, k, m = 5, 256, 3
+    q = rng.integers(0, 16, size=(n, k), dtype=np.int32)
+    packed_words = np.concatenate([oracle.pack_i4x8(((row ^ 8) - 8 + 16) % 16 - 8) for row in q])  # unused shape check
+    assert packed_words.size == n * k // 8
+    w_bytes = (q[:, 0::2] | (q[:, 1::2] << 4)).astype(np.uint8)
+    # byte layout equals the primitive little-endian u32 word layout of the unsigned nibbles
+    words = w_bytes.reshape(-1).view(np.uint32)
+    for r in range(n):
+        for kk in (0, 1, 7, 8, 255):
+            assert (int(words[r * (k // 8) + kk // 8]) >> (4 * (kk % 8))) & 0xF == q[r, kk]
+    scale = oracle.f32_to_bf16_bits(rng.uniform(1e-3, 2e-2, size=(n, k // 128)).astype(np.float32))
+    x = oracle.f32_to_bf16_bits(rng.standard_normal((m, k)).astype(np.float32))
+    got = oracle.int4_rowmajor_linear(x, w_bytes, scale, m, n, k, out_dtype=oracle.DT_F32)
+    sf = oracle.bf16_bits_to_f32(scale).astype(np.float64)
+    wd = (q - 8).astype(np.float64) * np.repeat(sf, 128, axis=1)
+    want = oracle.bf16_bits_to_f32(x).astype(np.float64) @ wd.T
+    assert np.allclose(got, want.astype(np.float32), rtol=1e-6, atol=1e-6)
+
+
+def test_per_token_int8_quantisation_rule_and_int32_gemm():
+    rng = np.random.default_rng(1)
+    m, k, n = 4, 64, 6
+    x = oracle.f32_to_bf16_bits(rng.standard_normal((m, k)).astype(np.float32))
+    q, s = oracle.quantize_per_token_int8(x, m, k)
+    xf = oracle.bf16_bits_to_f32(x).reshape(m, k)
+    assert np.allclose(s, np.abs(xf).max(axis=1) / np.float32(127.0))
+    assert np.abs(q).max() == 127 and q.min() >= -127
+    assert np.array_equal(q, np.clip(np.rint(xf / s[:, None]), -127, 127).astype(np.int8))
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    got = oracle.int8_gemm_i32(q, w, m, n, k)
+    assert np.array_equal(got, q.astype(np.int32) @ w.astype(np.int32).T)
