@@ -1,0 +1,364 @@
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+
+Headline (N=1): the int4 group-quantized decode GEMV of the benchmark's second configuration
+(W u4 [14336, 4096], group 128, bf16 scales, x bf16 [M=1, 4096]), reported as achieved HBM GB/s =
+algorithmic bytes per launch / device time per launch. A step is one GEMV launch over one batch of
+activations; launches rotate over 8 resident copies of the weights (242 MB > the 126 MB L2) so every step
+streams its weights from HBM. Timing is CUDA events on the launching stream, max over ranks.
+
+For N > 1 the linear is sharded column-parallel: every rank owns a [14336, 4096] shard of a 14336*N-row
+linear (weak scaling) and each step ends with an NCCL all-gather of the bf16 outputs.
+
+`--impl reference` times the CPU restatement of the reference engine (oracle/) on the host cores over a bounded
+row sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+N_OUT, K_IN, GROUP = 14336, 4096, 128
+COPIES = 8
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(m: int, n: int = N_OUT, k: int = K_IN, group: int = GROUP) -> int:
+    """Packed weights + bf16 scales + bf16 x + bf16 y, each touched once."""
+    return n * k // 2 + n * (k // group) * 2 + m * k * 2 + m * n * 2
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(p) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def mark(self):
+        return len(self.rows)
+
+    def stop(self, lo: int = 0, hi: int | None = None) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        rows = self.rows[lo:hi] or self.rows[-3:]
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except Exception:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_rate(m: int, budget_s: float, steps: int | None = None, warmup: int = 0):
+    """Times the CPU restatement of the reference engine on a bounded row sample of the GEMV workload.
+    Returns (GB/s, seconds per step, sample description, threads)."""
+    import oracle
+    from vyre_b200 import synth
+
+    threads = oracle.num_threads()
+    x, w, s = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
+    probe_rows = 512
+    t0 = time.perf_counter()
+    oracle.int4_rowmajor_linear(x, w[:probe_rows], s[:probe_rows], m, probe_rows, K_IN)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    if steps is None:
+        rows, reps = N_OUT, max(3, int(budget_s / max(per_row * N_OUT, 1e-6)))
+        reps = min(reps, 200)
+    else:
+        rows = int(max(16, min(N_OUT, budget_s / max(1, steps + warmup) / max(per_row, 1e-9))))
+        reps = steps
+    for _ in range(warmup if steps is not None else 1):
+        oracle.int4_rowmajor_linear(x, w[:rows], s[:rows], m, rows, K_IN)
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        oracle.int4_rowmajor_linear(x, w[:rows], s[:rows], m, rows, K_IN)
+    dt = (time.perf_counter() - t0) / reps
+    gbs = algorithmic_bytes(m, n=rows) / dt / 1e9
+    sample = f"{reps} x int4 GEMV M={m} on rows [0,{rows}) of {N_OUT} x K={K_IN} (f64-accumulating oracle, OpenMP over rows)"
+    return gbs, dt, sample, threads
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    gbs, dt, sample, threads = cpu_reference_rate(1, budget_s=120.0, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": "int4_decode_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16xint4->f32", "data": "synthetic",
+        "config": {"workload": "int4 group-quantized decode GEMV M=1 N=14336 K=4096 g=128 (config 2), CPU row sample"},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_native(args) -> None:
+    import torch
+
+    import vyre_b200 as vb
+    from vyre_b200 import ffi, synth
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: PLW0642
+
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    L = ffi.lib()
+    m = args.m
+    steps = max(COPIES, (args.steps // COPIES) * COPIES)
+    warmup = max(3 * COPIES, ((args.warmup + COPIES - 1) // COPIES) * COPIES)
+
+    # ---- resident inputs: COPIES distinct weight sets so that consecutive steps never hit L2 -------------------
+    x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=rank)
+    x = torch.from_numpy(x_np.view(np.int16)).cuda()
+    ws, ss = [], []
+    for c in range(COPIES):
+        ws.append(torch.from_numpy(np.roll(w_np, c, axis=0)).cuda())
+        ss.append(torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda())
+    y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
+    y_all = torch.zeros((world, m, N_OUT), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.Stream()
+
+    def launch(c: int):
+        ffi.check(L.vyb_k_int4_gemv(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
+                                    GROUP, ffi.DT_BF16, C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+
+    with torch.cuda.stream(stream):
+        for c in range(COPIES):  # first launches configure the kernel; must precede graph capture
+            launch(c)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for c in range(COPIES):
+                launch(c)
+                if world > 1:
+                    dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
+    # parity guard inside the bench: the last copy's output must match the contract path bit for bit
+    with torch.cuda.stream(stream):
+        graph.replay()
+    stream.synchronize()
+    y_ref = y.clone()
+
+    for _ in range(warmup // COPIES):
+        with torch.cuda.stream(stream):
+            graph.replay()
+    stream.synchronize()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.15)
+    lo = sampler.mark()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        start.record(stream)
+        for _ in range(steps // COPIES):
+            graph.replay()
+        end.record(stream)
+    stream.synchronize()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    hi = sampler.mark()
+    elapsed_ms = start.elapsed_time(end)
+    if dist:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    clocks = sampler.stop(lo, hi) if rank == 0 else None
+    assert status.cpu().tolist() == [0, 0, 0, 0], "a bounded device-side wait ran out during the bench"
+    assert torch.equal(y, y_ref), "non-deterministic GEMV output during the bench"
+
+    ms_per_step = elapsed_ms / steps
+    bytes_per_step = algorithmic_bytes(m)
+    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    if rank != 0:
+        if dist:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- kernel-only time of the dominant kernel (no collective), for the roofline --------------------------------
+    kgraph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(kgraph, stream=stream):
+            for c in range(COPIES):
+                launch(c)
+    ksteps = min(steps, 40000)
+    ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.stream(stream):
+        for _ in range(4):
+            kgraph.replay()
+        ks.record(stream)
+        for _ in range(ksteps // COPIES):
+            kgraph.replay()
+        ke.record(stream)
+    stream.synchronize()
+    kernel_us = ks.elapsed_time(ke) * 1e3 / ksteps
+    peak, peak_kind = measured_peaks()
+    achieved = bytes_per_step / (kernel_us * 1e-6) / 1e9
+
+    extra = {}
+    for mm in (4, 8):
+        xm_np, _, _ = synth.int4_linear_inputs(mm, 16, K_IN, seed=3)
+        xm = torch.from_numpy(xm_np.view(np.int16)).cuda()
+        ym = torch.zeros((mm, N_OUT), dtype=torch.bfloat16, device="cuda")
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g2, stream=stream):
+                for c in range(COPIES):
+                    ffi.check(L.vyb_k_int4_gemv(xm.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), ym.data_ptr(), mm, N_OUT,
+                                                K_IN, GROUP, ffi.DT_BF16, C.c_void_p(stream.cuda_stream),
+                                                C.c_void_p(status.data_ptr())))
+            for _ in range(4):
+                g2.replay()
+            ks.record(stream)
+            for _ in range(2000 // COPIES):
+                g2.replay()
+            ke.record(stream)
+        stream.synchronize()
+        us = ks.elapsed_time(ke) * 1e3 / (2000 // COPIES * COPIES)
+        extra[f"m{mm}"] = {"us_per_launch": round(us, 3), "gbs": round(algorithmic_bytes(mm) / (us * 1e-6) / 1e9, 1),
+                           "frac_of_measured_peak": round(algorithmic_bytes(mm) / (us * 1e-6) / 1e9 / peak, 4)}
+
+    # ---- end to end through the contract path: host x -> submit -> wait -> host y, weights resident ---------------
+    dev = vb.Device.acquire(local_rank)
+    prog = vb.linear_int4_grouped_rowmajor("x", "w", "scale", "out", m, K_IN, N_OUT, GROUP, ffi.DT_BF16)
+    sess = vb.ArtifactSession.compile(prog, dev)
+    hw = [dev.resident_from(np.roll(w_np, c, axis=0).view(np.uint32)) for c in range(COPIES)]
+    hs = [dev.resident_from(np.roll(s_np, c, axis=0)) for c in range(COPIES)]
+    x_pinned = torch.from_numpy(x_np.view(np.int16).copy()).pin_memory().numpy().view(np.uint16)
+    depth = 4
+    e2e_steps = max(depth * COPIES, min(steps, 4000))
+
+    def submit(i: int):
+        bs = vb.BindingSet(sess.artifact.digest())
+        bs.insert_host(0, x_pinned)
+        bs.insert_resident(1, hw[i % COPIES])
+        bs.insert_resident(2, hs[i % COPIES])
+        return sess.submit(bs)
+
+    inflight, checksum, last = [], 0.0, None
+    for i in range(depth * COPIES):  # warm-up
+        submit(i).wait()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        inflight.append(submit(i))
+        if len(inflight) == depth:
+            last = inflight.pop(0).wait()
+            checksum += float(last.output_view(3, np.uint16)[0])
+    while inflight:
+        last = inflight.pop(0).wait()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    got_last = np.frombuffer(last.output(3), np.uint16).reshape(m, N_OUT)
+    want_last = y_ref.view(torch.int16).cpu().numpy().view(np.uint16)
+    assert np.array_equal(got_last, want_last), "contract path and kernel-level path disagree"
+    e2e = {"value": world * bytes_per_step / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(x_pinned.nbytes),
+           "d2h_bytes_per_step": int(m * N_OUT * 2), "us_per_step": round(e2e_s * 1e6, 2), "in_flight": depth,
+           "api": "ArtifactSession.submit/wait (vyb_submit, vyb_submission_wait), weights resident"}
+    for h in hw + hs:
+        dev.free_resident(h)
+    dev.release()
+
+    cpu_gbs, cpu_dt, cpu_sample, cpu_threads = cpu_reference_rate(m, budget_s=12.0)
+
+    line = {
+        "metric": "int4_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16xint4->f32", "data": "synthetic",
+        "config": {"workload": f"int4 group-quantized decode GEMV M={m} N={N_OUT} K={K_IN} g={GROUP} (config 2)",
+                   "per_gpu_shard": [N_OUT, K_IN], "parallelism": f"column-parallel x{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                   "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
+                   "launch": f"CUDA graph of {COPIES} launches"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "int4_gemv_kernel",
+                     "us_per_launch": round(kernel_us, 3), "algorithmic_bytes_per_launch": bytes_per_step,
+                     "frac_of_nominal_8tbs": achieved / 8000.0},
+        "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cpu_threads, "kind": "port", "sample": cpu_sample,
+                         "ms_per_gemv": round(cpu_dt * 1e3, 2)},
+        "e2e": e2e, "gpu_launches": steps, "clocks": clocks, "other_batches": extra,
+    }
+    print(json.dumps(line))
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100000)
+    ap.add_argument("--warmup", type=int, default=2000)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_native(args)
+
+
+if __name__ == "__main__":
+    main()

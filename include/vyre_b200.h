@@ -1,0 +1,409 @@
+/*
+ * vyre_b200.h - C ABI of libvyre_b200.so: a Blackwell (sm_100a) native backend for vyre's
+ * quantized-inference hot path (weight-only quantized linear + MoE expert dispatch).
+ *
+ * The reference boundary is a set of Rust traits plus an `inventory` registration; it has no C ABI.
+ * Every export below flattens exactly one reference item (cited as file:line within the vyre tree), so
+ * that a small Rust shim inside vyre-driver-cuda (`impl TargetCompiler`, `impl ArtifactMaterializer`,
+ * `impl ArtifactInstance`, `impl Submission`) forwards each trait method to one function here.
+ *
+ * Conventions
+ *  - every function returns an int32 status: 0 = ok, otherwise the reference's stable error id
+ *    (vyre-driver/src/backend/error.rs:47-59); the message of the last failure on the calling thread is
+ *    available from vyb_last_error_message() and always contains "Fix: ".
+ *  - nothing panics, traps or falls back to the CPU: a missing or non-sm_100 device is a structured
+ *    failure (vyre README.md:36-37).
+ *  - all pointers are plain host pointers unless a parameter is documented as a device pointer.
+ *  - handles are opaque and thread-safe; `*_free` accepts NULL.
+ */
+#ifndef VYRE_B200_H
+#define VYRE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define VYB_ABI_VERSION 1u
+
+/* ---- error ids: vyre-driver/src/backend/error.rs:47-59 (ErrorCode::stable_id) -------------------- */
+#define VYB_OK 0
+#define VYB_ERR_DEVICE_OUT_OF_MEMORY 1001
+#define VYB_ERR_UNSUPPORTED_FEATURE 1002
+#define VYB_ERR_POISONED_LOCK 1003
+#define VYB_ERR_KERNEL_COMPILE_FAILED 1004
+#define VYB_ERR_DISPATCH_FAILED 1005
+#define VYB_ERR_INVALID_PROGRAM 1006
+#define VYB_ERR_COOPERATIVE_RESIDENCY_EXCEEDED 1007
+#define VYB_ERR_DEVICE_LOST 1008
+#define VYB_ERR_UNKNOWN 1999
+
+/* ---- DataType tags: vyre-spec/src/data_type.rs:2-8,227-257 ---------------------------------------- */
+#define VYB_DT_U32 0x01u
+#define VYB_DT_I32 0x02u
+#define VYB_DT_F16 0x09u
+#define VYB_DT_BF16 0x0Au
+#define VYB_DT_F32 0x0Bu
+#define VYB_DT_U8 0x0Eu
+#define VYB_DT_I8 0x10u
+#define VYB_DT_I4 0x1Bu
+#define VYB_DT_QUANTIZED 0x1Fu
+
+/* BufferAccess: vyre-foundation/src/ir_inner/model/program/buffer_decl.rs */
+#define VYB_ACCESS_READ_ONLY 0u
+#define VYB_ACCESS_READ_WRITE 1u
+#define VYB_ACCESS_OUTPUT 2u    /* backend-allocated, zero-initialised output */
+#define VYB_ACCESS_WORKGROUP 3u /* workgroup scratch, never bound */
+
+typedef struct vyb_program vyb_program;       /* vyre_foundation::ir::Program */
+typedef struct vyb_artifact vyb_artifact;     /* vyre_megakernel::Artifact */
+typedef struct vyb_payload vyb_payload;       /* vyre_megakernel::TargetPayload */
+typedef struct vyb_device vyb_device;         /* vyre_driver Device + ArtifactMaterializer */
+typedef struct vyb_instance vyb_instance;     /* vyre_driver ArtifactInstance */
+typedef struct vyb_submission vyb_submission; /* vyre_driver Submission */
+typedef struct vyb_completion vyb_completion; /* vyre_driver Completion */
+
+/* vyre-driver/src/backend/resource.rs:22-84 (ResidentHandle = owner + id) */
+typedef struct vyb_resident_handle {
+    uint64_t owner;
+    uint64_t id;
+} vyb_resident_handle;
+
+/* vyre-megakernel TargetProfile as used by CudaTargetCompiler (vyre-driver-cuda/src/target_compiler.rs:35-71) */
+typedef struct vyb_target_profile {
+    char identity[64];
+    uint32_t generation; /* 100 = sm_100a */
+    uint32_t max_workgroup_size[3];
+    uint32_t max_invocations;
+    uint32_t max_dynamic_shared_bytes;
+    uint32_t subgroup_size;
+} vyb_target_profile;
+
+/* BackendRegistration: vyre-driver/src/backend/registry/inventory_streams.rs:38-69 */
+typedef struct vyb_registration_info {
+    const char* id;             /* "cuda-b200" */
+    const char* target_id;      /* "nvidia-sm100a" */
+    const char* payload_format; /* "b200-native" */
+    uint32_t format_version;    /* 1 */
+    uint32_t precedence;        /* rank among backends, CUDA's own is 5 (vyre-driver-cuda/src/lib.rs:1083-1088) */
+    vyb_target_profile profile;
+} vyb_registration_info;
+
+/* DeviceIdentity: vyre-driver/src/backend/artifact_lifecycle.rs:11-19 */
+typedef struct vyb_device_identity {
+    char backend[32];
+    char device[96];
+    uint64_t generation;
+} vyb_device_identity;
+
+/* CudaDeviceCaps subset: vyre-driver-cuda/src/device.rs:40-85 */
+typedef struct vyb_device_caps {
+    char name[128];
+    int32_t ordinal;
+    int32_t compute_major, compute_minor;
+    uint64_t total_memory;
+    int32_t max_threads_per_block;
+    int32_t shared_memory_per_block, shared_memory_per_sm, shared_memory_per_block_optin;
+    int32_t warp_size;
+    int32_t cooperative_launch;
+    int32_t multi_processor_count;
+    int32_t l2_cache_bytes;
+    int32_t memory_clock_rate_khz, core_clock_rate_khz, global_memory_bus_width_bits;
+} vyb_device_caps;
+
+/* BufferDecl view: vyre-foundation/src/ir_inner/model/program/buffer_decl.rs */
+typedef struct vyb_buffer_decl {
+    const char* name; /* owned by the program */
+    uint32_t binding;
+    uint32_t access;
+    uint32_t dtype;
+    uint32_t count;                 /* elements */
+    uint32_t has_output_byte_range; /* with_output_byte_range (linear_4bit.rs:743-771) */
+    uint64_t output_byte_begin, output_byte_end;
+} vyb_buffer_decl;
+
+/* QuantizedLinear4BitSpec: vyre-libs/src/nn/linear/inner/linear_4bit.rs:78-134 */
+typedef struct vyb_quantized_linear_4bit_spec {
+    uint32_t in_dim, out_dim;
+    uint32_t storage_dtype;        /* VYB_DT_I4 for a valid spec */
+    uint32_t scale_group_size;     /* QuantizationScale::PerGroup */
+    uint32_t zero_point_group_size; /* QuantizationZeroPoint::PerGroup */
+} vyb_quantized_linear_4bit_spec;
+
+/* QuantizedLinear4BitPlannerEvidence: linear_4bit.rs:30-69 */
+typedef struct vyb_planner_evidence {
+    uint32_t in_dim, out_dim, group_size, group_count;
+    uint64_t packed_weight_bytes, dequantized_weight_bytes, sidecar_bytes, bias_bytes, output_bytes;
+    uint64_t dequant_bytes_elided;
+    uint32_t matmul_m, matmul_k, matmul_n, matmul_tile;
+    const char* matmul_selected_path;
+    const char* matmul_candidate_path;  /* NULL when none */
+    const char* matmul_fallback_reason; /* NULL when none */
+    uint32_t tensor_core_eligible;
+    float output_drift_abs_tolerance; /* LINEAR_4BIT_AFFINE_GROUPED_OUTPUT_DRIFT_ABS_TOLERANCE = 1e-4 */
+} vyb_planner_evidence;
+
+/* BoundResource: vyre-driver/src/backend/artifact_lifecycle.rs:32-39 */
+#define VYB_BIND_HOST 0
+#define VYB_BIND_RESIDENT 1
+typedef struct vyb_binding {
+    uint32_t value_id; /* ArtifactValueId = BufferDecl binding slot */
+    int32_t kind;
+    const void* host_ptr; /* VYB_BIND_HOST: bytes are copied in during vyb_submit */
+    size_t len;
+    vyb_resident_handle resident; /* VYB_BIND_RESIDENT */
+} vyb_binding;
+
+/* DispatchConfig: vyre-driver/src/backend/dispatch_config.rs:26-110. Only grid, timeout_ns, label and
+ * leave_resident are honoured; a non-zero value in any other field is refused with UnsupportedFeature. */
+typedef struct vyb_dispatch_config {
+    uint32_t grid_override[3]; /* all zero = none; a zero axis next to non-zero ones is InvalidProgram */
+    uint32_t workgroup_override[3];
+    uint64_t timeout_ns;
+    const char* label;
+    uint32_t ulp_budget;
+    uint64_t max_output_bytes;
+    uint32_t cooperative;
+    uint32_t leave_resident; /* 1: outputs written into caller-bound resident buffers are not read back */
+} vyb_dispatch_config;
+
+/* ---- library ---------------------------------------------------------------------------------- */
+uint32_t vyb_abi_version(void);
+/* thread-local text of the last failure; BackendError Display (error.rs:83-191) */
+const char* vyb_last_error_message(void);
+/* BackendRegistration static (inventory_streams.rs:38-69; CUDA's instance vyre-driver-cuda/src/lib.rs:1068-1080) */
+int32_t vyb_registration(vyb_registration_info* out);
+/* BackendRegistration::supported_ops */
+uint32_t vyb_supported_op_count(void);
+const char* vyb_supported_op(uint32_t index);
+/* blake3 (the digest of Artifact/TargetPayload identities, vyre-megakernel/src/lib.rs:52-59) */
+void vyb_blake3(const void* data, size_t len, uint8_t out[32]);
+
+/* ---- operator surface: vyre-libs::nn::{linear,quant,moe,activation}; vyre-primitives::math::quantized -- */
+/* Same argument order as the Rust builders: buffer names, then dimensions. A builder that returns
+ * Result<Program,String> in the reference returns InvalidProgram with the same "Fix: ..." text here; a
+ * builder that returns a trap Program in the reference returns a program with vyb_program_is_trap() = 1. */
+
+/* linear_4bit.rs:255 */
+int32_t vyb_nn_linear_4bit(const char* x, const char* w_packed, const char* b, const char* out, uint32_t in_dim,
+                           uint32_t out_dim, vyb_program** program);
+/* linear_4bit.rs:357 */
+int32_t vyb_nn_linear_4bit_affine_grouped(const char* x, const char* w_packed, const char* scale,
+                                          const char* zero_point, const char* b, const char* out, uint32_t in_dim,
+                                          uint32_t out_dim, uint32_t group_size, vyb_program** program);
+/* linear_4bit.rs:382 */
+int32_t vyb_nn_linear_4bit_affine_grouped_batched(const char* x, const char* w_packed, const char* scale,
+                                                  const char* zero_point, const char* b, const char* out,
+                                                  uint32_t in_dim, uint32_t out_dim, uint32_t group_size,
+                                                  uint32_t batch_size, vyb_program** program);
+/* QuantizedLinear4BitSpec::affine_grouped, linear_4bit.rs:90 */
+void vyb_quantized_linear_4bit_spec_affine_grouped(uint32_t in_dim, uint32_t out_dim, uint32_t group_size,
+                                                   vyb_quantized_linear_4bit_spec* spec);
+/* linear_4bit.rs:1004 */
+int32_t vyb_nn_linear_4bit_affine_grouped_typed(const vyb_quantized_linear_4bit_spec* spec, const char* x,
+                                                const char* w_packed, const char* scale, const char* zero_point,
+                                                const char* b, const char* out, vyb_program** program);
+/* linear_4bit.rs:1033 */
+int32_t vyb_nn_linear_4bit_affine_grouped_batched_typed(const vyb_quantized_linear_4bit_spec* spec,
+                                                        uint32_t batch_size, const char* x, const char* w_packed,
+                                                        const char* scale, const char* zero_point, const char* b,
+                                                        const char* out, vyb_program** program);
+/* linear_4bit.rs:140 */
+int32_t vyb_nn_linear_4bit_affine_grouped_planner_evidence(const vyb_quantized_linear_4bit_spec* spec,
+                                                           vyb_planner_evidence* out);
+
+/* vyre-primitives/src/math/quantized/programs.rs:21,86,129,186,243,309,457. `lib_op_id` != 0 tags the
+ * program with the vyre-libs::quant::int4_* id of the library wrapper (vyre-libs/src/nn/quant/int4.rs:34-40,
+ * 110-195) instead of the primitive id. */
+int32_t vyb_math_unpack_i4x8(const char* packed_words, const char* out_lanes, uint32_t lane_count,
+                             vyb_program** program);
+int32_t vyb_math_i4x8_dot_i32(const char* lhs, const char* rhs, const char* out, uint32_t lane_count,
+                              uint32_t lib_op_id, vyb_program** program);
+int32_t vyb_math_i4x8_dot_f32_scaled(const char* lhs, const char* rhs, const char* lhs_scale, const char* rhs_scale,
+                                     const char* out, uint32_t lane_count, uint32_t lib_op_id,
+                                     vyb_program** program);
+int32_t vyb_math_i4x8_matvec_f32_scaled(const char* weights, const char* x, const char* row_scales, const char* out,
+                                        uint32_t rows, uint32_t cols, uint32_t lib_op_id, vyb_program** program);
+int32_t vyb_math_i4x8_batched_matvec_f32_scaled(const char* weights, const char* x, const char* row_scales,
+                                                const char* out, uint32_t batch, uint32_t rows, uint32_t cols,
+                                                uint32_t lib_op_id, vyb_program** program);
+int32_t vyb_math_i4x8_batched_matmul_f32_scaled(const char* weights, const char* activations,
+                                                const char* row_scales, const char* batch_scales, const char* out,
+                                                uint32_t batch, uint32_t rows, uint32_t cols, uint32_t lib_op_id,
+                                                vyb_program** program);
+int32_t vyb_math_i4x8_batched_matmul_top1_f32_scaled(const char* weights, const char* activations,
+                                                     const char* row_scales, const char* batch_scales,
+                                                     const char* out_scores, uint32_t batch, uint32_t rows,
+                                                     uint32_t cols, uint32_t lib_op_id, vyb_program** program);
+/* i4_packed_words, vyre-primitives/src/math/quantized.rs:58-60 */
+uint32_t vyb_i4_packed_words(uint32_t lane_count);
+
+/* vyre-libs/src/nn/quant/int8.rs:15,54 */
+int32_t vyb_quant_int8_unpack(const char* packed, const char* scales, const char* output, uint32_t n, uint32_t cols,
+                              vyb_program** program);
+int32_t vyb_quant_int8_pack(const char* input, const char* output, uint32_t n, vyb_program** program);
+
+/* vyre-libs/src/nn/linear/inner/builder.rs:172,202,220,241 (dtype: VYB_DT_F16 / BF16 / F32) */
+int32_t vyb_nn_linear_rows(const char* x, const char* w, const char* b, const char* out, uint32_t rows,
+                           uint32_t in_dim, uint32_t out_dim, vyb_program** program);
+int32_t vyb_nn_linear_rows_no_bias(const char* x, const char* w, const char* out, uint32_t rows, uint32_t in_dim,
+                                   uint32_t out_dim, vyb_program** program);
+int32_t vyb_nn_linear_rows_no_bias_typed(const char* x, const char* w, const char* out, uint32_t rows,
+                                         uint32_t in_dim, uint32_t out_dim, uint32_t dtype, vyb_program** program);
+int32_t vyb_nn_linear_rows_no_bias_out_in_typed(const char* x, const char* w, const char* out, uint32_t rows,
+                                                uint32_t in_dim, uint32_t out_dim, uint32_t dtype,
+                                                vyb_program** program);
+/* vyre-libs/src/math/linalg/matmul.rs:17-60 (wrapping u32) */
+int32_t vyb_math_matmul(const char* a, const char* b, const char* out, uint32_t m, uint32_t k, uint32_t n,
+                        vyb_program** program);
+
+/* vyre-libs/src/nn/moe/gating.rs:19; softmax_top_k.rs:25; top_k.rs:18 */
+int32_t vyb_nn_moe_gate(const char* input_scores, const char* output_indices, const char* output_weights,
+                        uint32_t num_experts, uint32_t k, vyb_program** program);
+int32_t vyb_nn_softmax_top_k(const char* scores, const char* out_indices, const char* out_weights, uint32_t n,
+                             uint32_t k, vyb_program** program);
+int32_t vyb_nn_top_k(const char* input, const char* output_indices, uint32_t n, uint32_t k, vyb_program** program);
+/* vyre-libs/src/nn/activation/swiglu.rs:17,26 */
+int32_t vyb_nn_swiglu(const char* gate, const char* up, const char* output, uint32_t n, vyb_program** program);
+int32_t vyb_nn_swiglu_typed(const char* gate, const char* up, const char* output, uint32_t n, uint32_t dtype,
+                            vyb_program** program);
+/* vyre-libs/src/nn/moe/expert_mlp.rs:18 */
+int32_t vyb_nn_expert_mlp(const char* x, const char* w_gate, const char* b_gate, const char* w_up, const char* b_up,
+                          const char* w_down, const char* b_down, const char* out, uint32_t in_dim,
+                          uint32_t hidden_dim, uint32_t out_dim, vyb_program** program);
+/* vyre-libs/src/nn/moe/moe_layer.rs:33 */
+int32_t vyb_nn_moe_layer_route_and_accumulate(const char* x, const char* w_router, const char* b_router,
+                                              const char* expert_indices, const char* expert_weights,
+                                              const char* expert_outputs, const char* out, uint32_t in_dim,
+                                              uint32_t num_experts, uint32_t out_dim, uint32_t k,
+                                              vyb_program** program);
+
+/* ---- serving-layout operators (no single reference builder; each composes the reference ops cited) --- */
+/* Group-quantized int4 linear in the checkpoint-native layout: W packed u4 [out_dim, in_dim/2] K-inner
+ * (the primitive word layout, programs.rs:181, read offset-binary with constant zero point 8), bf16 scale
+ * [out_dim, in_dim/group], x bf16 [batch, in_dim], f32 accumulate, out bf16 or f32 [batch, out_dim].
+ * Semantics = linear_4bit_affine_grouped (linear_4bit.rs:357) with zp == 8 and typed bf16 I/O
+ * (linear_rows_no_bias_out_in_typed, builder.rs:241). Slots: x=0, w=1, scale=2, out=3. The backend picks the
+ * decode GEMV for batch <= 8 and the tcgen05 prefill GEMM for large batches. op id
+ * "vyre-b200::nn::linear_int4_grouped_rowmajor". */
+int32_t vyb_nn_linear_int4_grouped_rowmajor(const char* x, const char* w_packed, const char* scale, const char* out,
+                                            uint32_t batch, uint32_t in_dim, uint32_t out_dim, uint32_t group_size,
+                                            uint32_t out_dtype, vyb_program** program);
+/* int8 weight-only linear: W int8 [out_dim, in_dim], per-output-channel f32 scale, x/out f32;
+ * = int8_unpack (int8.rs:15) with signed bytes + linear_rows_no_bias_out_in (builder.rs:241).
+ * Slots: x=0, w=1, scale=2, out=3. op id "vyre-b200::nn::linear_int8_weight_only". */
+int32_t vyb_nn_linear_int8_weight_only(const char* x, const char* w, const char* scale, const char* out,
+                                       uint32_t batch, uint32_t in_dim, uint32_t out_dim, vyb_program** program);
+/* Dynamic per-token int8 x int8 -> int32 linear: x bf16 [rows, in_dim] quantized per token
+ * (s_t = max|x|/127, q = clamp(rne(x/s_t), -127, 127)), W int8 [out_dim, in_dim]; out int32 [rows, out_dim]
+ * (= the wrapping-u32 Matmul, matmul.rs:17-60, on sign-extended bytes) and x_scale f32 [rows].
+ * Slots: x=0, w=1, x_scale=2 (RW), out=3. op id "vyre-b200::nn::linear_int8_dynamic". */
+int32_t vyb_nn_linear_int8_dynamic(const char* x, const char* w, const char* x_scale, const char* out, uint32_t rows,
+                                   uint32_t in_dim, uint32_t out_dim, vyb_program** program);
+/* Multi-token int4 MoE FFN layer: router linear (bf16 [experts, hidden]) -> moe_gate (gating.rs:19) per
+ * token -> per selected expert swiglu_typed(w1 x, w3 x) (swiglu.rs:26) -> w2 -> weighted accumulate
+ * (moe_layer.rs:33). Expert weights stacked: w13 u4 [E][2][inter][hidden/2], s13 bf16 [E][2][inter][hidden/g],
+ * w2 u4 [E][hidden][inter/2], s2 bf16 [E][hidden][inter/g].
+ * Slots: x=0, w_router=1, w13=2, s13=3, w2=4, s2=5, out=6 (bf16 [tokens, hidden]), routing_idx=7 (RW u32
+ * [tokens, topk]), routing_w=8 (RW f32 [tokens, topk]). op id "vyre-b200::nn::moe_ffn_int4". */
+int32_t vyb_nn_moe_ffn_int4(const char* x, const char* w_router, const char* w13, const char* s13, const char* w2,
+                            const char* s2, const char* out, const char* routing_idx, const char* routing_w,
+                            uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t topk,
+                            uint32_t group_size, vyb_program** program);
+
+/* ---- Program accessors (vyre_foundation::ir::Program) ---------------------------------------------- */
+const char* vyb_program_op_id(const vyb_program* p); /* outermost Region generator */
+uint32_t vyb_program_buffer_count(const vyb_program* p);
+int32_t vyb_program_buffer(const vyb_program* p, uint32_t index, vyb_buffer_decl* out);
+void vyb_program_workgroup_size(const vyb_program* p, uint32_t out[3]);
+/* 1 when the builder produced a trap program (vyre-primitives/src/lib.rs:83-98); such a program is
+ * refused by vyb_compile with InvalidProgram. vyb_program_trap_message gives the builder's "Fix: ..." text. */
+uint32_t vyb_program_is_trap(const vyb_program* p);
+const char* vyb_program_trap_message(const vyb_program* p);
+void vyb_program_fingerprint(const vyb_program* p, uint8_t out[32]); /* Program::fingerprint */
+void vyb_program_free(vyb_program* p);
+
+/* ---- compile: ProgramGraph::from_program + vyre_megakernel::compile (vyre-megakernel/src/lib.rs:832) -- */
+int32_t vyb_compile(const vyb_program* program, vyb_artifact** artifact);
+void vyb_artifact_digest(const vyb_artifact* a, uint8_t out[32]);
+void vyb_artifact_free(vyb_artifact* a);
+
+/* ---- TargetCompiler::compile (vyre-megakernel/src/target.rs:180-189; pure, needs no device) ----------- */
+int32_t vyb_target_compile(const vyb_artifact* artifact, vyb_payload** payload);
+void vyb_payload_digest(const vyb_payload* p, uint8_t out[32]);
+void vyb_payload_neutral_artifact(const vyb_payload* p, uint8_t out[32]);
+const char* vyb_payload_format(const vyb_payload* p);
+/* TargetPayload::to_bytes / from_bytes (vyre-megakernel/src/envelope.rs); from_bytes re-authenticates */
+int32_t vyb_payload_bytes(const vyb_payload* p, const uint8_t** bytes, size_t* len);
+int32_t vyb_payload_from_bytes(const uint8_t* bytes, size_t len, vyb_payload** payload);
+void vyb_payload_free(vyb_payload* p);
+
+/* ---- Device (artifact_lifecycle.rs:21-30) + ArtifactMaterializer (artifact_lifecycle.rs:132-186) ------- */
+int32_t vyb_device_acquire(int32_t ordinal, vyb_device** device);
+int32_t vyb_device_identity_of(const vyb_device* d, vyb_device_identity* out);
+int32_t vyb_device_caps_of(const vyb_device* d, vyb_device_caps* out);
+int32_t vyb_device_is_healthy(const vyb_device* d);
+/* Host-side loss injection for recovery tests: marks this generation lost exactly as a CUDA
+ * context-loss error would (vyre-runtime/src/recovery.rs:13-25); no device fault is provoked. */
+int32_t vyb_device_mark_lost(vyb_device* d, const char* reason);
+/* Re-acquire after loss: returns a new generation on the same ordinal (ArtifactSession::rematerialize,
+ * vyre-runtime/src/artifact_admission.rs:271-291, then re-admits the same payload bytes). */
+int32_t vyb_device_reacquire(vyb_device* d);
+void vyb_device_release(vyb_device* d);
+
+/* resident buffers: vyre-driver-cuda/src/backend/resident.rs:138-201,426-443 */
+int32_t vyb_alloc(vyb_device* d, size_t byte_len, vyb_resident_handle* out);
+int32_t vyb_upload(vyb_device* d, vyb_resident_handle h, const void* bytes, size_t len);
+int32_t vyb_upload_at(vyb_device* d, vyb_resident_handle h, size_t offset_bytes, const void* bytes, size_t len);
+/* VyreBackend::download_resident / download_resident_range (vyre-driver/src/backend/vyre_backend.rs:298-381) */
+int32_t vyb_download(vyb_device* d, vyb_resident_handle h, void* dst, size_t len);
+int32_t vyb_download_range(vyb_device* d, vyb_resident_handle h, size_t offset_bytes, void* dst, size_t len);
+int32_t vyb_free(vyb_device* d, vyb_resident_handle h);
+/* raw device pointer of a resident buffer, for hosts that share the CUDA context */
+int32_t vyb_resident_device_ptr(vyb_device* d, vyb_resident_handle h, void** device_ptr, size_t* len);
+
+/* ArtifactMaterializer::materialize with the fail-closed checks of materialize::admit
+ * (vyre-driver/src/materialize.rs:81-146) */
+int32_t vyb_materialize(vyb_device* d, const vyb_artifact* artifact, const vyb_payload* payload,
+                        vyb_instance** instance);
+void vyb_instance_artifact_digest(const vyb_instance* i, uint8_t out[32]);
+void vyb_instance_payload_digest(const vyb_instance* i, uint8_t out[32]);
+int32_t vyb_instance_device(const vyb_instance* i, vyb_device_identity* out);
+void vyb_instance_free(vyb_instance* i);
+
+/* ArtifactInstance::submit (artifact_lifecycle.rs:120-129; CUDA impl vyre-driver-cuda/src/materializer.rs:165-283).
+ * `artifact_digest` is BindingSet::artifact; a mismatch with the instance is InvalidProgram. Host and
+ * resident bindings may be mixed (the reference's CUDA instance refuses that, materializer.rs:186-190; here
+ * weights stay resident while activations arrive from the host). The launch is asynchronous on a
+ * library-owned non-default stream. `config` may be NULL. */
+int32_t vyb_submit(vyb_instance* instance, const uint8_t artifact_digest[32], const vyb_binding* bindings,
+                   size_t n_bindings, const vyb_dispatch_config* config, vyb_submission** submission);
+/* Submission::is_ready / wait (artifact_lifecycle.rs:112-117); wait consumes the submission */
+int32_t vyb_submission_is_ready(const vyb_submission* s);
+int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion);
+/* Completion (artifact_lifecycle.rs:100-109): host bytes per output value, device_ns when measured */
+int32_t vyb_completion_output(const vyb_completion* c, uint32_t value_id, const uint8_t** bytes, size_t* len);
+uint32_t vyb_completion_output_count(const vyb_completion* c);
+int32_t vyb_completion_device_ns(const vyb_completion* c, uint64_t* ns);
+void vyb_completion_free(vyb_completion* c);
+
+/* ---- kernel-level entry points ------------------------------------------------------------------------
+ * For a host that owns its buffers and stream (what the Rust shim's resident path calls after resolving
+ * handles; replaces launch_cuda_function -> cuLaunchKernel, vyre-driver-cuda/src/backend/launch.rs:65-125).
+ * All pointers are DEVICE pointers, `stream` is a cudaStream_t. `status` is an optional device pointer to
+ * 4 u32 words that a kernel with bounded waits sets non-zero when a wait ran out (never a trap). */
+
+/* y[m,n] = bf16|f32( sum_k x[m,k] * (q[n,k]-8) * s[n,k/group] ), m <= 8 per pass, HBM-bound decode path */
+int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                        uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
+                        uint32_t* status);
+/* C1: y f32 [m,n] = x f32 [m,k] . (int8 w[n,k] * s[n])^T */
+int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
+                                      uint32_t m, uint32_t n, uint32_t k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VYRE_B200_H */

@@ -1,0 +1,586 @@
+"""Host-side mirror of the reference's operator and submission interface over the C ABI.
+
+Names follow the Rust API so that tests read like the reference's own:
+  builders   vyre_libs::nn::{linear_4bit, linear_4bit_affine_grouped[_batched][_typed], ...},
+             vyre_primitives::math::quantized::{unpack_i4x8, i4x8_*}, vyre_libs::quant::{int8_*, int4_*}
+  lifecycle  ProgramGraph -> Artifact (compile) -> TargetPayload (TargetCompiler) -> ArtifactInstance
+             (ArtifactMaterializer) -> BindingSet -> Submission -> Completion, and ArtifactSession
+             (vyre-runtime/src/artifact_admission.rs:152-496) tying them together.
+Every call goes through libvyre_b200.so; nothing here computes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import ffi
+from .ffi import BackendError, check  # noqa: F401  (re-exported)
+
+
+def _b(s: str) -> bytes:
+    return s.encode()
+
+
+class Program:
+    """vyre_foundation::ir::Program as the native facet sees it (buffers, workgroup size, op region id)."""
+
+    def __init__(self, handle: int):
+        self._h = C.c_void_p(handle)
+
+    def __del__(self):
+        try:
+            if self._h:
+                ffi.lib().vyb_program_free(self._h)
+        except Exception:
+            pass
+
+    @property
+    def op_id(self) -> str:
+        return ffi.lib().vyb_program_op_id(self._h).decode()
+
+    def buffers(self) -> list[dict]:
+        L = ffi.lib()
+        out = []
+        for i in range(L.vyb_program_buffer_count(self._h)):
+            d = ffi.BufferDecl()
+            check(L.vyb_program_buffer(self._h, i, C.byref(d)))
+            out.append(dict(name=d.name.decode(), binding=d.binding, access=d.access, dtype=d.dtype, count=d.count,
+                            output_byte_range=(int(d.output_byte_begin), int(d.output_byte_end))
+                            if d.has_output_byte_range else None))
+        return out
+
+    def workgroup_size(self) -> list[int]:
+        arr = (C.c_uint32 * 3)()
+        ffi.lib().vyb_program_workgroup_size(self._h, C.byref(arr))
+        return list(arr)
+
+    @property
+    def is_trap(self) -> bool:
+        return bool(ffi.lib().vyb_program_is_trap(self._h))
+
+    @property
+    def trap_message(self) -> str:
+        return ffi.lib().vyb_program_trap_message(self._h).decode()
+
+    def fingerprint(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_program_fingerprint(self._h, buf)
+        return buf.raw
+
+
+def _build(fn_name: str, *args) -> Program:
+    out = C.c_void_p()
+    conv = [_b(a) if isinstance(a, str) else a for a in args]
+    check(getattr(ffi.lib(), fn_name)(*conv, C.byref(out)))
+    return Program(out.value)
+
+
+# ---- vyre_libs::nn / quant / vyre_primitives builders (argument order = the Rust builders') ---------------
+def linear_4bit(x, w_packed, b, out, in_dim, out_dim):
+    return _build("vyb_nn_linear_4bit", x, w_packed, b, out, in_dim, out_dim)
+
+
+def linear_4bit_affine_grouped(x, w_packed, scale, zero_point, b, out, in_dim, out_dim, group_size):
+    return _build("vyb_nn_linear_4bit_affine_grouped", x, w_packed, scale, zero_point, b, out, in_dim, out_dim,
+                  group_size)
+
+
+def linear_4bit_affine_grouped_batched(x, w_packed, scale, zero_point, b, out, in_dim, out_dim, group_size,
+                                       batch_size):
+    return _build("vyb_nn_linear_4bit_affine_grouped_batched", x, w_packed, scale, zero_point, b, out, in_dim,
+                  out_dim, group_size, batch_size)
+
+
+@dataclass
+class QuantizedLinear4BitSpec:
+    in_dim: int
+    out_dim: int
+    storage_dtype: int = ffi.DT_I4
+    scale_group_size: int = 0
+    zero_point_group_size: int = 0
+
+    @staticmethod
+    def affine_grouped(in_dim: int, out_dim: int, group_size: int) -> "QuantizedLinear4BitSpec":
+        s = ffi.QuantizedLinear4BitSpec()
+        ffi.lib().vyb_quantized_linear_4bit_spec_affine_grouped(in_dim, out_dim, group_size, C.byref(s))
+        return QuantizedLinear4BitSpec(s.in_dim, s.out_dim, s.storage_dtype, s.scale_group_size,
+                                       s.zero_point_group_size)
+
+    def _c(self):
+        return ffi.QuantizedLinear4BitSpec(self.in_dim, self.out_dim, self.storage_dtype, self.scale_group_size,
+                                           self.zero_point_group_size)
+
+
+def linear_4bit_affine_grouped_typed(spec, x, w_packed, scale, zero_point, b, out):
+    c = spec._c()
+    return _build("vyb_nn_linear_4bit_affine_grouped_typed", C.byref(c), x, w_packed, scale, zero_point, b, out)
+
+
+def linear_4bit_affine_grouped_batched_typed(spec, batch_size, x, w_packed, scale, zero_point, b, out):
+    c = spec._c()
+    return _build("vyb_nn_linear_4bit_affine_grouped_batched_typed", C.byref(c), batch_size, x, w_packed, scale,
+                  zero_point, b, out)
+
+
+def linear_4bit_affine_grouped_planner_evidence(spec) -> dict:
+    c = spec._c()
+    ev = ffi.PlannerEvidence()
+    check(ffi.lib().vyb_nn_linear_4bit_affine_grouped_planner_evidence(C.byref(c), C.byref(ev)))
+    d = {}
+    for name, _ in ffi.PlannerEvidence._fields_:
+        v = getattr(ev, name)
+        d[name] = v.decode() if isinstance(v, bytes) else v
+    return d
+
+
+def unpack_i4x8(packed_words, out_lanes, lane_count):
+    return _build("vyb_math_unpack_i4x8", packed_words, out_lanes, lane_count)
+
+
+def i4x8_dot_i32(lhs, rhs, out, lane_count, lib_op_id=False):
+    return _build("vyb_math_i4x8_dot_i32", lhs, rhs, out, lane_count, int(lib_op_id))
+
+
+def i4x8_dot_f32_scaled(lhs, rhs, lhs_scale, rhs_scale, out, lane_count, lib_op_id=False):
+    return _build("vyb_math_i4x8_dot_f32_scaled", lhs, rhs, lhs_scale, rhs_scale, out, lane_count, int(lib_op_id))
+
+
+def i4x8_matvec_f32_scaled(weights, x, row_scales, out, rows, cols, lib_op_id=False):
+    return _build("vyb_math_i4x8_matvec_f32_scaled", weights, x, row_scales, out, rows, cols, int(lib_op_id))
+
+
+def i4x8_batched_matvec_f32_scaled(weights, x, row_scales, out, batch, rows, cols, lib_op_id=False):
+    return _build("vyb_math_i4x8_batched_matvec_f32_scaled", weights, x, row_scales, out, batch, rows, cols,
+                  int(lib_op_id))
+
+
+def i4x8_batched_matmul_f32_scaled(weights, acts, row_scales, batch_scales, out, batch, rows, cols, lib_op_id=False):
+    return _build("vyb_math_i4x8_batched_matmul_f32_scaled", weights, acts, row_scales, batch_scales, out, batch,
+                  rows, cols, int(lib_op_id))
+
+
+def i4x8_batched_matmul_top1_f32_scaled(weights, acts, row_scales, batch_scales, out, batch, rows, cols,
+                                        lib_op_id=False):
+    return _build("vyb_math_i4x8_batched_matmul_top1_f32_scaled", weights, acts, row_scales, batch_scales, out,
+                  batch, rows, cols, int(lib_op_id))
+
+
+def int8_unpack(packed, scales, output, n, cols):
+    return _build("vyb_quant_int8_unpack", packed, scales, output, n, cols)
+
+
+def int8_pack(input_, output, n):
+    return _build("vyb_quant_int8_pack", input_, output, n)
+
+
+def linear_rows(x, w, b, out, rows, in_dim, out_dim):
+    return _build("vyb_nn_linear_rows", x, w, b, out, rows, in_dim, out_dim)
+
+
+def linear_rows_no_bias(x, w, out, rows, in_dim, out_dim):
+    return _build("vyb_nn_linear_rows_no_bias", x, w, out, rows, in_dim, out_dim)
+
+
+def linear_rows_no_bias_typed(x, w, out, rows, in_dim, out_dim, dtype):
+    return _build("vyb_nn_linear_rows_no_bias_typed", x, w, out, rows, in_dim, out_dim, dtype)
+
+
+def linear_rows_no_bias_out_in_typed(x, w, out, rows, in_dim, out_dim, dtype):
+    return _build("vyb_nn_linear_rows_no_bias_out_in_typed", x, w, out, rows, in_dim, out_dim, dtype)
+
+
+def matmul(a, b, out, m, k, n):
+    return _build("vyb_math_matmul", a, b, out, m, k, n)
+
+
+def moe_gate(input_scores, output_indices, output_weights, num_experts, k):
+    return _build("vyb_nn_moe_gate", input_scores, output_indices, output_weights, num_experts, k)
+
+
+def softmax_top_k(scores, out_indices, out_weights, n, k):
+    return _build("vyb_nn_softmax_top_k", scores, out_indices, out_weights, n, k)
+
+
+def top_k(input_, output_indices, n, k):
+    return _build("vyb_nn_top_k", input_, output_indices, n, k)
+
+
+def swiglu(gate, up, output, n):
+    return _build("vyb_nn_swiglu", gate, up, output, n)
+
+
+def swiglu_typed(gate, up, output, n, dtype):
+    return _build("vyb_nn_swiglu_typed", gate, up, output, n, dtype)
+
+
+def expert_mlp(x, w_gate, b_gate, w_up, b_up, w_down, b_down, out, in_dim, hidden_dim, out_dim):
+    return _build("vyb_nn_expert_mlp", x, w_gate, b_gate, w_up, b_up, w_down, b_down, out, in_dim, hidden_dim,
+                  out_dim)
+
+
+def moe_layer_route_and_accumulate(x, w_router, b_router, expert_indices, expert_weights, expert_outputs, out,
+                                   in_dim, num_experts, out_dim, k):
+    return _build("vyb_nn_moe_layer_route_and_accumulate", x, w_router, b_router, expert_indices, expert_weights,
+                  expert_outputs, out, in_dim, num_experts, out_dim, k)
+
+
+def linear_int4_grouped_rowmajor(x, w_packed, scale, out, batch, in_dim, out_dim, group_size, out_dtype=ffi.DT_BF16):
+    return _build("vyb_nn_linear_int4_grouped_rowmajor", x, w_packed, scale, out, batch, in_dim, out_dim, group_size,
+                  out_dtype)
+
+
+def linear_int8_weight_only(x, w, scale, out, batch, in_dim, out_dim):
+    return _build("vyb_nn_linear_int8_weight_only", x, w, scale, out, batch, in_dim, out_dim)
+
+
+def linear_int8_dynamic(x, w, x_scale, out, rows, in_dim, out_dim):
+    return _build("vyb_nn_linear_int8_dynamic", x, w, x_scale, out, rows, in_dim, out_dim)
+
+
+def moe_ffn_int4(x, w_router, w13, s13, w2, s2, out, routing_idx, routing_w, tokens, hidden, inter, experts, topk,
+                 group_size):
+    return _build("vyb_nn_moe_ffn_int4", x, w_router, w13, s13, w2, s2, out, routing_idx, routing_w, tokens, hidden,
+                  inter, experts, topk, group_size)
+
+
+def blake3(data: bytes) -> bytes:
+    buf = C.create_string_buffer(32)
+    ffi.lib().vyb_blake3(data, len(data), buf)
+    return buf.raw
+
+
+def registration() -> dict:
+    r = ffi.RegistrationInfo()
+    check(ffi.lib().vyb_registration(C.byref(r)))
+    return dict(id=r.id.decode(), target_id=r.target_id.decode(), payload_format=r.payload_format.decode(),
+                format_version=r.format_version, precedence=r.precedence,
+                profile=dict(identity=r.profile.identity.decode(), generation=r.profile.generation,
+                             max_workgroup_size=list(r.profile.max_workgroup_size),
+                             max_invocations=r.profile.max_invocations,
+                             max_dynamic_shared_bytes=r.profile.max_dynamic_shared_bytes,
+                             subgroup_size=r.profile.subgroup_size))
+
+
+def supported_ops() -> list[str]:
+    L = ffi.lib()
+    return [L.vyb_supported_op(i).decode() for i in range(L.vyb_supported_op_count())]
+
+
+# ---- lifecycle ---------------------------------------------------------------------------------------------
+class Artifact:
+    def __init__(self, handle):
+        self._h = C.c_void_p(handle)
+
+    def __del__(self):
+        try:
+            ffi.lib().vyb_artifact_free(self._h)
+        except Exception:
+            pass
+
+    def digest(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_artifact_digest(self._h, buf)
+        return buf.raw
+
+
+def compile(program: Program) -> Artifact:  # noqa: A001 - mirrors vyre_megakernel::compile
+    out = C.c_void_p()
+    check(ffi.lib().vyb_compile(program._h, C.byref(out)))
+    return Artifact(out.value)
+
+
+class TargetPayload:
+    def __init__(self, handle):
+        self._h = C.c_void_p(handle)
+
+    def __del__(self):
+        try:
+            ffi.lib().vyb_payload_free(self._h)
+        except Exception:
+            pass
+
+    def digest(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_payload_digest(self._h, buf)
+        return buf.raw
+
+    def neutral_artifact(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_payload_neutral_artifact(self._h, buf)
+        return buf.raw
+
+    def format(self) -> str:
+        return ffi.lib().vyb_payload_format(self._h).decode()
+
+    def to_bytes(self) -> bytes:
+        p = C.POINTER(C.c_uint8)()
+        n = C.c_size_t()
+        check(ffi.lib().vyb_payload_bytes(self._h, C.byref(p), C.byref(n)))
+        return C.string_at(p, n.value)
+
+    @staticmethod
+    def from_bytes(data: bytes) -> "TargetPayload":
+        out = C.c_void_p()
+        check(ffi.lib().vyb_payload_from_bytes(data, len(data), C.byref(out)))
+        return TargetPayload(out.value)
+
+
+def target_compile(artifact: Artifact) -> TargetPayload:
+    out = C.c_void_p()
+    check(ffi.lib().vyb_target_compile(artifact._h, C.byref(out)))
+    return TargetPayload(out.value)
+
+
+class Device:
+    """vyre_driver Device + ArtifactMaterializer for one acquired generation."""
+
+    def __init__(self, ordinal: int = 0):
+        out = C.c_void_p()
+        check(ffi.lib().vyb_device_acquire(ordinal, C.byref(out)))
+        self._h = out
+
+    @staticmethod
+    def acquire(ordinal: int = 0) -> "Device":
+        return Device(ordinal)
+
+    def release(self):
+        if self._h:
+            ffi.lib().vyb_device_release(self._h)
+            self._h = None
+
+    def identity(self) -> dict:
+        i = ffi.DeviceIdentity()
+        check(ffi.lib().vyb_device_identity_of(self._h, C.byref(i)))
+        return dict(backend=i.backend.decode(), device=i.device.decode(), generation=i.generation)
+
+    def caps(self) -> dict:
+        c = ffi.DeviceCaps()
+        check(ffi.lib().vyb_device_caps_of(self._h, C.byref(c)))
+        return {n: (getattr(c, n).decode() if n == "name" else getattr(c, n)) for n, _ in ffi.DeviceCaps._fields_}
+
+    def is_healthy(self) -> bool:
+        return bool(ffi.lib().vyb_device_is_healthy(self._h))
+
+    def mark_lost(self, reason: str = "injected by test"):
+        check(ffi.lib().vyb_device_mark_lost(self._h, _b(reason)))
+
+    def reacquire(self):
+        check(ffi.lib().vyb_device_reacquire(self._h))
+
+    # resident buffers
+    def allocate_resident(self, byte_len: int) -> ffi.ResidentHandle:
+        h = ffi.ResidentHandle()
+        check(ffi.lib().vyb_alloc(self._h, byte_len, C.byref(h)))
+        return h
+
+    def upload_resident(self, h, data) -> None:
+        a = np.ascontiguousarray(data)
+        check(ffi.lib().vyb_upload(self._h, h, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def upload_resident_at(self, h, offset: int, data) -> None:
+        a = np.ascontiguousarray(data)
+        check(ffi.lib().vyb_upload_at(self._h, h, offset, a.ctypes.data_as(C.c_void_p), a.nbytes))
+
+    def download_resident(self, h, nbytes: int, offset: int = 0) -> np.ndarray:
+        out = np.empty(nbytes, dtype=np.uint8)
+        check(ffi.lib().vyb_download_range(self._h, h, offset, out.ctypes.data_as(C.c_void_p), nbytes))
+        return out
+
+    def free_resident(self, h) -> None:
+        check(ffi.lib().vyb_free(self._h, h))
+
+    def resident_ptr(self, h) -> tuple[int, int]:
+        p = C.c_void_p()
+        n = C.c_size_t()
+        check(ffi.lib().vyb_resident_device_ptr(self._h, h, C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def resident_from(self, data) -> ffi.ResidentHandle:
+        a = np.ascontiguousarray(data)
+        h = self.allocate_resident(a.nbytes)
+        self.upload_resident(h, a)
+        return h
+
+    def materialize(self, artifact: Artifact, payload: TargetPayload) -> "ArtifactInstance":
+        out = C.c_void_p()
+        check(ffi.lib().vyb_materialize(self._h, artifact._h, payload._h, C.byref(out)))
+        return ArtifactInstance(out.value, self)
+
+
+class BindingSet:
+    """vyre_driver BindingSet: values keyed by ArtifactValueId (= buffer binding slot)."""
+
+    def __init__(self, artifact_digest: bytes):
+        self.artifact = artifact_digest
+        self.resources: dict[int, object] = {}
+        self.invocation_grid = None
+
+    def insert_host(self, value_id: int, data) -> None:
+        self.resources[value_id] = np.ascontiguousarray(data)
+
+    def insert_resident(self, value_id: int, handle) -> None:
+        self.resources[value_id] = handle
+
+    def set_invocation_grid(self, grid) -> None:
+        if any(g == 0 for g in grid):
+            axis = [g == 0 for g in grid].index(True)
+            raise BackendError(ffi.ERR_INVALID_PROGRAM,
+                               f"Fix: invocation grid axis {axis} must be positive, got {grid[axis]}.")
+        self.invocation_grid = list(grid)
+
+
+class Completion:
+    def __init__(self, handle):
+        self._h = C.c_void_p(handle)
+
+    def __del__(self):
+        try:
+            ffi.lib().vyb_completion_free(self._h)
+        except Exception:
+            pass
+
+    def output(self, value_id: int) -> bytes:
+        p = C.POINTER(C.c_uint8)()
+        n = C.c_size_t()
+        check(ffi.lib().vyb_completion_output(self._h, value_id, C.byref(p), C.byref(n)))
+        return C.string_at(p, n.value)
+
+    def output_view(self, value_id: int, dtype) -> np.ndarray:
+        """Zero-copy view of the pinned readback buffer; valid until this Completion is dropped."""
+        p = C.POINTER(C.c_uint8)()
+        n = C.c_size_t()
+        check(ffi.lib().vyb_completion_output(self._h, value_id, C.byref(p), C.byref(n)))
+        return np.ctypeslib.as_array(p, shape=(n.value,)).view(dtype)
+
+    @property
+    def device_ns(self):
+        ns = C.c_uint64()
+        rc = ffi.lib().vyb_completion_device_ns(self._h, C.byref(ns))
+        return ns.value if rc == 0 else None
+
+
+class Submission:
+    def __init__(self, handle, keepalive):
+        self._h = C.c_void_p(handle)
+        self._keep = keepalive
+
+    def is_ready(self) -> bool:
+        return bool(ffi.lib().vyb_submission_is_ready(self._h))
+
+    def wait(self) -> Completion:
+        out = C.c_void_p()
+        h, self._h = self._h, None
+        if h is None:
+            raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: completion may be consumed only once.")
+        check(ffi.lib().vyb_submission_wait(h, C.byref(out)))
+        self._keep = None
+        return Completion(out.value)
+
+
+class ArtifactInstance:
+    def __init__(self, handle, device: Device):
+        self._h = C.c_void_p(handle)
+        self._dev = device
+
+    def __del__(self):
+        try:
+            ffi.lib().vyb_instance_free(self._h)
+        except Exception:
+            pass
+
+    def artifact(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_instance_artifact_digest(self._h, buf)
+        return buf.raw
+
+    def payload(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_instance_payload_digest(self._h, buf)
+        return buf.raw
+
+    def device(self) -> dict:
+        i = ffi.DeviceIdentity()
+        check(ffi.lib().vyb_instance_device(self._h, C.byref(i)))
+        return dict(backend=i.backend.decode(), device=i.device.decode(), generation=i.generation)
+
+    def submit(self, bindings: BindingSet, leave_resident: bool = False, config: ffi.DispatchConfig | None = None):
+        arr = (ffi.Binding * max(1, len(bindings.resources)))()
+        keep = []
+        for i, (vid, res) in enumerate(sorted(bindings.resources.items())):
+            arr[i].value_id = vid
+            if isinstance(res, ffi.ResidentHandle):
+                arr[i].kind = ffi.BIND_RESIDENT
+                arr[i].resident = res
+            else:
+                arr[i].kind = ffi.BIND_HOST
+                arr[i].host_ptr = res.ctypes.data
+                arr[i].len = res.nbytes
+                keep.append(res)
+        cfg = config or ffi.DispatchConfig()
+        if bindings.invocation_grid:
+            for a in range(3):
+                cfg.grid_override[a] = bindings.invocation_grid[a]
+        if leave_resident:
+            cfg.leave_resident = 1
+        out = C.c_void_p()
+        check(ffi.lib().vyb_submit(self._h, bindings.artifact, arr, len(bindings.resources), C.byref(cfg),
+                                   C.byref(out)))
+        return Submission(out.value, keep)
+
+
+class ArtifactSession:
+    """vyre_runtime::ArtifactSession: compile -> attach target -> materialize -> submit
+    (vyre-runtime/src/artifact_admission.rs:152-496)."""
+
+    def __init__(self, program: Program, device: Device, envelope: bytes | None = None):
+        self.program = program
+        self.device = device
+        self.artifact = compile(program)
+        self.payload = TargetPayload.from_bytes(envelope) if envelope is not None else target_compile(self.artifact)
+        self.instance = device.materialize(self.artifact, self.payload)
+        self._buffers = program.buffers()
+
+    @staticmethod
+    def compile(program: Program, device: Device) -> "ArtifactSession":
+        return ArtifactSession(program, device)
+
+    def envelope_bytes(self) -> bytes:
+        return self.payload.to_bytes()
+
+    def rematerialize(self) -> None:
+        """Re-admit the same authenticated payload bytes on the device's current generation; never recompiles
+        (artifact_admission.rs:271-291)."""
+        self.instance = self.device.materialize(self.artifact, TargetPayload.from_bytes(self.payload.to_bytes()))
+
+    def input_slots(self) -> list[dict]:
+        return [b for b in self._buffers if b["access"] in (ffi.ACCESS_READ_ONLY, ffi.ACCESS_READ_WRITE)]
+
+    def output_slots(self) -> list[dict]:
+        return [b for b in self._buffers if b["access"] in (ffi.ACCESS_OUTPUT, ffi.ACCESS_READ_WRITE)]
+
+    def host_bindings(self, inputs: list) -> BindingSet:
+        """Inputs in ABI slot order of the ReadOnly / ReadWrite values (artifact_admission.rs:398-434)."""
+        slots = self.input_slots()
+        if len(inputs) != len(slots):
+            raise BackendError(ffi.ERR_INVALID_PROGRAM,
+                               f"Fix: expected {len(slots)} host input(s) in slot order, got {len(inputs)}.")
+        bs = BindingSet(self.artifact.digest())
+        for slot, data in zip(slots, inputs):
+            bs.insert_host(slot["binding"], data)
+        return bs
+
+    def submit(self, bindings: BindingSet, **kw) -> Submission:
+        return self.instance.submit(bindings, **kw)
+
+    def submit_and_wait(self, bindings: BindingSet, **kw) -> Completion:
+        return self.instance.submit(bindings, **kw).wait()
+
+    def ordered_outputs(self, completion: Completion) -> list[bytes]:
+        """Writable values in slot order (artifact_admission.rs:442-480)."""
+        return [completion.output(b["binding"]) for b in self.output_slots()]
+
+    def run_host(self, inputs: list) -> list[bytes]:
+        c = self.submit_and_wait(self.host_bindings(inputs))
+        return self.ordered_outputs(c)

@@ -1,0 +1,860 @@
+// Device, resident buffers, materialisation and submission: the ArtifactMaterializer / ArtifactInstance /
+// Submission side of the contract (vyre-driver/src/backend/artifact_lifecycle.rs:100-186), implemented on the
+// CUDA runtime. One library-owned non-blocking stream per instance (the reference forbids the legacy default
+// stream, vyre-driver-cuda/src/backend/launch.rs:81-87). No CPU fallback anywhere: a missing device, a foreign
+// handle or a wrong byte length is a structured error with "Fix:" text.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <atomic>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <unordered_map>
+
+#include "../kernels/kernels.h"
+#include "blake3.hpp"
+#include "model.hpp"
+
+using namespace vyb;
+
+namespace {
+
+std::atomic<uint64_t> g_next_owner{1};  // vyre-driver/src/backend/resource.rs:13 (starts at 1, never reused)
+
+struct Resident {
+    void* ptr = nullptr;
+    size_t len = 0;
+    uint32_t inflight = 0;
+};
+
+std::string cuda_msg(cudaError_t e) { return std::string(cudaGetErrorName(e)) + ": " + cudaGetErrorString(e); }
+
+}  // namespace
+
+struct vyb_device {
+    int ordinal = 0;
+    cudaDeviceProp prop{};
+    uint64_t owner = 0;
+    std::atomic<uint64_t> generation{1};
+    std::atomic<bool> lost{false};
+    std::string lost_reason;
+    std::string device_name;
+    std::mutex mu;
+    std::unordered_map<uint64_t, Resident> residents;
+    uint64_t next_id = 1;
+    uint64_t resident_bytes = 0;
+
+    int32_t check_alive(const char* what) {
+        if (lost.load())
+            return fail_device_lost(device_name, generation.load(), std::string(what) + " refused: " + lost_reason);
+        return VYB_OK;
+    }
+    // vyre-driver/src/backend/resource.rs:61-84 (ResidentOwner::resolve) + resident.rs:196-201,426-434
+    int32_t resolve(vyb_resident_handle h, const char* context, Resident** out) {
+        if (h.owner != owner)
+            return fail_invalid_program(
+                std::string("Fix: ") + context + " received resident handle " + std::to_string(h.id) +
+                " owned by backend instance " + std::to_string(h.owner) + ", but this instance is " +
+                std::to_string(owner) +
+                ". A resident handle is only valid on the backend instance that allocated it; reallocate and "
+                "re-upload the buffer on this instance, or keep the original instance alive for as long as the "
+                "handle is held.");
+        auto it = residents.find(h.id);
+        if (it == residents.end())
+            return fail_invalid_program(std::string("Fix: ") + context + " received unknown or already freed resident handle " +
+                                        std::to_string(h.id) + "; allocate it with vyb_alloc on this device first.");
+        *out = &it->second;
+        return VYB_OK;
+    }
+};
+
+namespace {
+
+struct PinnedBuf {
+    void* ptr = nullptr;
+    size_t cap = 0;
+    bool in_use = false;
+};
+struct DeviceBuf {
+    void* ptr = nullptr;
+    size_t cap = 0;
+    bool in_use = false;
+};
+
+}  // namespace
+
+struct vyb_instance {
+    vyb_device* dev = nullptr;
+    Program program;
+    uint32_t variant = 0;
+    Digest artifact{}, payload{};
+    vyb_device_identity identity{};
+    uint64_t generation = 0;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;
+    std::vector<PinnedBuf> pinned;
+    std::vector<DeviceBuf> temps;
+    void* scratch = nullptr;  // op-specific device scratch, sized at materialisation
+    size_t scratch_len = 0;
+    uint32_t* status_dev = nullptr;   // 4 words, raised by kernels whose bounded waits ran out
+    uint32_t* status_host = nullptr;  // pinned mirror
+
+    void* acquire_pinned(size_t len) {
+        for (auto& b : pinned)
+            if (!b.in_use && b.cap >= len) {
+                b.in_use = true;
+                return b.ptr;
+            }
+        PinnedBuf b;
+        if (cudaHostAlloc(&b.ptr, std::max<size_t>(len, 256), cudaHostAllocDefault) != cudaSuccess) return nullptr;
+        b.cap = std::max<size_t>(len, 256);
+        b.in_use = true;
+        pinned.push_back(b);
+        return b.ptr;
+    }
+    void release_pinned(void* p) {
+        for (auto& b : pinned)
+            if (b.ptr == p) b.in_use = false;
+    }
+    void* acquire_temp(size_t len) {
+        for (auto& b : temps)
+            if (!b.in_use && b.cap >= len) {
+                b.in_use = true;
+                return b.ptr;
+            }
+        DeviceBuf b;
+        if (cudaMalloc(&b.ptr, std::max<size_t>(len, 256)) != cudaSuccess) return nullptr;
+        b.cap = std::max<size_t>(len, 256);
+        b.in_use = true;
+        temps.push_back(b);
+        return b.ptr;
+    }
+    void release_temp(void* p) {
+        for (auto& b : temps)
+            if (b.ptr == p) b.in_use = false;
+    }
+};
+
+namespace {
+struct OutputSlot {
+    uint32_t value_id = 0;
+    void* dev_ptr = nullptr;
+    size_t len = 0;
+    void* host = nullptr;  // pinned readback target, nullptr when left resident
+};
+}  // namespace
+
+struct vyb_submission {
+    vyb_instance* inst = nullptr;
+    cudaEvent_t start = nullptr, end = nullptr, done = nullptr;
+    std::vector<void*> temps;
+    std::vector<OutputSlot> outputs;
+    std::vector<uint64_t> resident_ids;
+    bool consumed = false;
+};
+
+struct vyb_completion {
+    vyb_instance* inst = nullptr;
+    Digest artifact{};
+    std::vector<OutputSlot> outputs;
+    uint64_t device_ns = 0;
+    bool has_device_ns = false;
+};
+
+namespace {
+
+uint32_t rt_dtype(uint32_t tag) { return tag == VYB_DT_BF16 ? 1u : tag == VYB_DT_F16 ? 2u : 0u; }
+
+// Launch the kernels of one program. `b[slot]` is the device pointer bound to the BufferDecl binding slot.
+cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
+    const Program& p = inst->program;
+    const uint32_t* u = p.params.u;
+    using namespace vybk;
+    switch (p.kind) {
+        case OpKind::Linear4Bit:
+            return launch_linear_4bit((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2], (float*)b[3], u[0], u[1], s);
+        case OpKind::Linear4BitAffineGrouped:
+            return launch_linear_4bit_affine_grouped((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2],
+                                                     (const uint32_t*)b[3], (const float*)b[4], (float*)b[5], u[0], u[1],
+                                                     u[2], u[3], s);
+        case OpKind::I4Unpack: return launch_i4_unpack((const uint32_t*)b[0], (int32_t*)b[1], u[0], s);
+        case OpKind::I4DotI32: return launch_i4_dot_i32((const uint32_t*)b[0], (const uint32_t*)b[1], (int32_t*)b[2], u[0], s);
+        case OpKind::I4DotF32Scaled:
+            return launch_i4_dot_f32_scaled((const uint32_t*)b[0], (const uint32_t*)b[1], (const float*)b[2],
+                                            (const float*)b[3], (float*)b[4], u[0], s);
+        case OpKind::I4BatchedMatvec:
+            return launch_i4_batched_matvec((const uint32_t*)b[0], (const float*)b[1], (const float*)b[2], (float*)b[3],
+                                            u[0], u[1], u[2], s);
+        case OpKind::I4BatchedMatmul:
+            return launch_i4_batched_matmul((const uint32_t*)b[0], (const uint32_t*)b[1], (const float*)b[2],
+                                            (const float*)b[3], (float*)b[4], u[0], u[1], u[2], s);
+        case OpKind::I4BatchedMatmulTop1:
+            return launch_i4_batched_matmul_top1((const uint32_t*)b[0], (const uint32_t*)b[1], (const float*)b[2],
+                                                 (const float*)b[3], (float*)b[4], u[0], u[1], u[2], s);
+        case OpKind::Int8Unpack:
+            return launch_int8_unpack((const uint32_t*)b[0], (const float*)b[1], (float*)b[2], u[0], u[1], s);
+        case OpKind::Int8Pack: return launch_int8_pack((const uint32_t*)b[0], (uint32_t*)b[1], u[0], s);
+        case OpKind::LinearRows: {
+            const bool has_bias = u[5] != 0;
+            return launch_linear_rows(b[0], b[1], has_bias ? b[2] : nullptr, has_bias ? b[3] : b[2], u[0], u[1], u[2],
+                                      rt_dtype(u[3]), u[4], s);
+        }
+        case OpKind::MatmulU32:
+            return launch_matmul_u32((const uint32_t*)b[0], (const uint32_t*)b[1], (uint32_t*)b[2], u[0], u[1], u[2], s);
+        case OpKind::MoeGate: return launch_moe_gate((const float*)b[0], (uint32_t*)b[1], (float*)b[2], u[2], u[0], u[1], s);
+        case OpKind::SoftmaxTopK:
+            return launch_softmax_top_k((const float*)b[0], (uint32_t*)b[1], (float*)b[2], (float*)b[3], (uint32_t*)b[4],
+                                        u[0], u[1], s);
+        case OpKind::TopK:
+            return launch_top_k((const float*)b[0], (uint32_t*)b[1], (float*)b[2], (uint32_t*)b[3], u[0], u[1], s);
+        case OpKind::Swiglu: return launch_swiglu(b[0], b[1], b[2], u[0], rt_dtype(u[1]), s);
+        case OpKind::ExpertMlp:
+            return launch_expert_mlp((const float*)b[0], (const float*)b[1], (const float*)b[2], (const float*)b[3],
+                                     (const float*)b[4], (const float*)b[5], (const float*)b[6], (float*)b[7],
+                                     (float*)inst->scratch, u[0], u[1], u[2], s);
+        case OpKind::MoeLayerAccumulate:
+            return launch_moe_layer_accumulate((const float*)b[4], (const float*)b[5], (float*)b[6], u[3], u[2], s);
+        case OpKind::LinearInt4GroupedRowmajor: {
+            const uint32_t batch = u[0], k = u[1], n = u[2], group = u[3];
+            const uint32_t out_f32 = u[4] == VYB_DT_F32 ? 1u : 0u;
+            const size_t out_elem = out_f32 ? 4 : 2;
+            if (inst->variant == KV_INT4_GEMV_TMA || inst->variant == KV_INT4_PREFILL_TCGEN05) {
+                if (int4_gemv_supported(std::min(batch, 8u), n, k, group)) {
+                    for (uint32_t b0 = 0; b0 < batch; b0 += 8) {
+                        const uint32_t mb = std::min(8u, batch - b0);
+                        cudaError_t e = launch_int4_gemv((const uint16_t*)b[0] + size_t(b0) * k, b[1], b[2],
+                                                         (uint8_t*)b[3] + size_t(b0) * n * out_elem, mb, n, k, out_f32,
+                                                         inst->dev->prop.multiProcessorCount, s, inst->status_dev);
+                        if (e != cudaSuccess) return e;
+                    }
+                    return cudaSuccess;
+                }
+            }
+            return launch_int4_linear_generic(b[0], b[1], b[2], b[3], batch, n, k, group, out_f32, s);
+        }
+        case OpKind::LinearInt8WeightOnly:
+            return launch_int8_weight_only_linear((const float*)b[0], (const int8_t*)b[1], (const float*)b[2],
+                                                  (float*)b[3], u[0], u[2], u[1], s);
+        default: return cudaErrorNotSupported;
+    }
+}
+
+size_t scratch_bytes_for(const Program& p) {
+    switch (p.kind) {
+        case OpKind::ExpertMlp: return size_t(p.params.u[1]) * 4;
+        default: return 0;
+    }
+}
+
+bool kind_supported(OpKind k) {
+    switch (k) {
+        case OpKind::LinearInt8Dynamic:
+        case OpKind::MoeFfnInt4: return false;
+        default: return true;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+// ---- Device --------------------------------------------------------------------------------------------------
+int32_t vyb_device_acquire(int32_t ordinal, vyb_device** device) {
+    if (!device) return fail_invalid_program("Fix: pass a non-null device out-pointer.");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no CUDA device is visible to this process (" + cuda_msg(e) +
+                                         "); the native backend has no CPU path");
+    }
+    if (ordinal < 0 || ordinal >= count)
+        return fail_dispatch(int(cudaErrorInvalidDevice), "device ordinal " + std::to_string(ordinal) +
+                                                              " is out of range for " + std::to_string(count) +
+                                                              " visible device(s)");
+    auto d = std::make_unique<vyb_device>();
+    d->ordinal = ordinal;
+    e = cudaGetDeviceProperties(&d->prop, ordinal);
+    if (e != cudaSuccess) return fail_dispatch(int(e), "cudaGetDeviceProperties failed: " + cuda_msg(e));
+    if (d->prop.major != 10)
+        return fail_unsupported("sm_" + std::to_string(d->prop.major) + std::to_string(d->prop.minor) +
+                                " device (the native kernels are built for sm_100a only)");
+    e = cudaSetDevice(ordinal);
+    if (e != cudaSuccess) return fail_dispatch(int(e), "cudaSetDevice failed: " + cuda_msg(e));
+    d->owner = g_next_owner.fetch_add(1);
+    d->device_name = "cuda:" + std::to_string(ordinal) + ":" + d->prop.name;
+    *device = d.release();
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_device_identity_of(const vyb_device* d, vyb_device_identity* out) {
+    if (!d || !out) return fail_invalid_program("Fix: pass a non-null device and identity out-pointer.");
+    std::snprintf(out->backend, sizeof(out->backend), "%s", BACKEND_ID);
+    std::snprintf(out->device, sizeof(out->device), "%s", d->device_name.c_str());
+    out->generation = d->generation.load();
+    return VYB_OK;
+}
+
+int32_t vyb_device_caps_of(const vyb_device* d, vyb_device_caps* out) {
+    if (!d || !out) return fail_invalid_program("Fix: pass a non-null device and caps out-pointer.");
+    *out = vyb_device_caps{};
+    std::snprintf(out->name, sizeof(out->name), "%s", d->prop.name);
+    out->ordinal = d->ordinal;
+    out->compute_major = d->prop.major;
+    out->compute_minor = d->prop.minor;
+    out->total_memory = d->prop.totalGlobalMem;
+    out->max_threads_per_block = d->prop.maxThreadsPerBlock;
+    out->shared_memory_per_block = int32_t(d->prop.sharedMemPerBlock);
+    out->shared_memory_per_sm = int32_t(d->prop.sharedMemPerMultiprocessor);
+    out->shared_memory_per_block_optin = int32_t(d->prop.sharedMemPerBlockOptin);
+    out->warp_size = d->prop.warpSize;
+    out->cooperative_launch = d->prop.cooperativeLaunch;
+    out->multi_processor_count = d->prop.multiProcessorCount;
+    out->l2_cache_bytes = d->prop.l2CacheSize;
+    int v = 0;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMemoryClockRate, d->ordinal) == cudaSuccess) out->memory_clock_rate_khz = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrClockRate, d->ordinal) == cudaSuccess) out->core_clock_rate_khz = v;
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrGlobalMemoryBusWidth, d->ordinal) == cudaSuccess)
+        out->global_memory_bus_width_bits = v;
+    return VYB_OK;
+}
+
+int32_t vyb_device_is_healthy(const vyb_device* d) { return d && !d->lost.load() ? 1 : 0; }
+
+int32_t vyb_device_mark_lost(vyb_device* d, const char* reason) {
+    if (!d) return fail_invalid_program("Fix: pass a non-null device.");
+    std::lock_guard<std::mutex> lk(d->mu);
+    d->lost_reason = reason ? reason : "device marked lost by the host";
+    d->lost.store(true);
+    return VYB_OK;
+}
+
+int32_t vyb_device_reacquire(vyb_device* d) {
+    if (!d) return fail_invalid_program("Fix: pass a non-null device.");
+    std::lock_guard<std::mutex> lk(d->mu);
+    // handles of the lost generation are stale: drop the table (memory of a really lost context is gone;
+    // for the host-injected case the buffers are released here)
+    for (auto& kv : d->residents) cudaFree(kv.second.ptr);
+    d->residents.clear();
+    d->resident_bytes = 0;
+    d->owner = g_next_owner.fetch_add(1);
+    d->generation.fetch_add(1);
+    d->lost.store(false);
+    d->lost_reason.clear();
+    return VYB_OK;
+}
+
+void vyb_device_release(vyb_device* d) {
+    if (!d) return;
+    for (auto& kv : d->residents) cudaFree(kv.second.ptr);
+    delete d;
+}
+
+// ---- resident buffers (vyre-driver-cuda/src/backend/resident.rs) -------------------------------------------------
+int32_t vyb_alloc(vyb_device* d, size_t byte_len, vyb_resident_handle* out) {
+    if (!d || !out) return fail_invalid_program("Fix: pass a non-null device and handle out-pointer.");
+    if (int32_t rc = d->check_alive("resident allocation")) return rc;
+    if (byte_len == 0)
+        return fail_invalid_program(
+            "Fix: resident allocation of 0 bytes is refused; allocate at least one byte or skip the buffer.");
+    cudaSetDevice(d->ordinal);
+    size_t free_b = 0, total_b = 0;
+    cudaMemGetInfo(&free_b, &total_b);
+    if (byte_len > free_b) return fail_oom(byte_len, free_b);
+    void* ptr = nullptr;
+    cudaError_t e = cudaMalloc(&ptr, byte_len);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_oom(byte_len, free_b);
+    }
+    std::lock_guard<std::mutex> lk(d->mu);
+    uint64_t id = d->next_id++;
+    d->residents[id] = Resident{ptr, byte_len, 0};
+    d->resident_bytes += byte_len;
+    out->owner = d->owner;
+    out->id = id;
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_upload_at(vyb_device* d, vyb_resident_handle h, size_t offset_bytes, const void* bytes, size_t len) {
+    if (!d || (!bytes && len)) return fail_invalid_program("Fix: pass a non-null device and source bytes.");
+    if (int32_t rc = d->check_alive("resident upload")) return rc;
+    void* dst;
+    {
+        std::lock_guard<std::mutex> lk(d->mu);
+        Resident* r = nullptr;
+        if (int32_t rc = d->resolve(h, "CUDA resident upload", &r)) return rc;
+        if (offset_bytes > r->len || len > r->len - offset_bytes)
+            return fail_invalid_program("Fix: resident upload of " + std::to_string(len) + " bytes at offset " +
+                                        std::to_string(offset_bytes) + " exceeds the " + std::to_string(r->len) +
+                                        "-byte allocation; allocate a larger buffer or split the upload.");
+        dst = static_cast<uint8_t*>(r->ptr) + offset_bytes;
+    }
+    cudaSetDevice(d->ordinal);
+    cudaError_t e = cudaMemcpy(dst, bytes, len, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail_dispatch(int(e), "resident upload failed: " + cuda_msg(e));
+    clear_error();
+    return VYB_OK;
+}
+int32_t vyb_upload(vyb_device* d, vyb_resident_handle h, const void* bytes, size_t len) {
+    return vyb_upload_at(d, h, 0, bytes, len);
+}
+
+int32_t vyb_download_range(vyb_device* d, vyb_resident_handle h, size_t offset_bytes, void* dst, size_t len) {
+    if (!d || (!dst && len)) return fail_invalid_program("Fix: pass a non-null device and destination.");
+    if (int32_t rc = d->check_alive("resident download")) return rc;
+    const void* src;
+    {
+        std::lock_guard<std::mutex> lk(d->mu);
+        Resident* r = nullptr;
+        if (int32_t rc = d->resolve(h, "CUDA resident download", &r)) return rc;
+        if (offset_bytes > r->len || len > r->len - offset_bytes)
+            return fail_invalid_program("Fix: resident download of " + std::to_string(len) + " bytes at offset " +
+                                        std::to_string(offset_bytes) + " exceeds the " + std::to_string(r->len) +
+                                        "-byte allocation.");
+        src = static_cast<const uint8_t*>(r->ptr) + offset_bytes;
+    }
+    cudaSetDevice(d->ordinal);
+    cudaError_t e = cudaMemcpy(dst, src, len, cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_dispatch(int(e), "resident download failed: " + cuda_msg(e));
+    clear_error();
+    return VYB_OK;
+}
+int32_t vyb_download(vyb_device* d, vyb_resident_handle h, void* dst, size_t len) {
+    return vyb_download_range(d, h, 0, dst, len);
+}
+
+int32_t vyb_free(vyb_device* d, vyb_resident_handle h) {
+    if (!d) return fail_invalid_program("Fix: pass a non-null device.");
+    std::lock_guard<std::mutex> lk(d->mu);
+    Resident* r = nullptr;
+    if (int32_t rc = d->resolve(h, "CUDA resident free", &r)) return rc;
+    if (r->inflight != 0)
+        return fail_invalid_program("Fix: resident handle " + std::to_string(h.id) +
+                                    " is still bound to an in-flight dispatch; wait for the submission before freeing it.");
+    cudaFree(r->ptr);
+    d->resident_bytes -= r->len;
+    d->residents.erase(h.id);
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_resident_device_ptr(vyb_device* d, vyb_resident_handle h, void** device_ptr, size_t* len) {
+    if (!d || !device_ptr) return fail_invalid_program("Fix: pass a non-null device and pointer out-pointer.");
+    std::lock_guard<std::mutex> lk(d->mu);
+    Resident* r = nullptr;
+    if (int32_t rc = d->resolve(h, "CUDA resident pointer query", &r)) return rc;
+    *device_ptr = r->ptr;
+    if (len) *len = r->len;
+    return VYB_OK;
+}
+
+// ---- materialise: vyre-driver/src/materialize.rs:81-146 (admit), fail closed ------------------------------------------
+int32_t vyb_materialize(vyb_device* d, const vyb_artifact* artifact, const vyb_payload* payload,
+                        vyb_instance** instance) {
+    if (!d || !artifact || !payload || !instance)
+        return fail_invalid_program("Fix: pass non-null device, artifact, payload and instance out-pointer.");
+    if (int32_t rc = d->check_alive("materialisation")) return rc;
+    const Payload& pl = payload->p;
+    auto invalid_module = [](const std::string& m) {
+        return fail_invalid_program("Fix: " + m + "; recompile the artifact with this backend's target compiler.");
+    };
+    if (pl.neutral_artifact != artifact->a.digest)
+        return invalid_module("target payload is not authenticated for the supplied neutral artifact");
+    if (pl.format != PAYLOAD_FORMAT || pl.format_version != PAYLOAD_FORMAT_VERSION)
+        return fail_unsupported("target payload format `" + pl.format + "`");
+    if (!profile_equal(pl.profile, native_profile()))
+        return invalid_module("target payload profile does not match the acquired materializer profile");
+    {
+        // re-authenticate the bytes: a payload edited after sealing must not materialise
+        Payload check;
+        std::string err;
+        if (!Payload::from_bytes(pl.bytes.data(), pl.bytes.size(), &check, &err) || check.digest != pl.digest)
+            return invalid_module("target payload bytes fail authentication (" + err + ")");
+    }
+    if (pl.modules.size() != 1)
+        return invalid_module("target module count must equal the compiler-selected fusion-group count");
+    const TargetModule& m = pl.modules[0];
+    if (m.entry_point != "main") return invalid_module("target module entry point must be `main`");
+    Program prog;
+    std::string err;
+    if (!Program::from_wire(m.program_wire.data(), m.program_wire.size(), &prog, &err))
+        return invalid_module("selected Program is malformed: " + err);
+    if (prog.fingerprint() != artifact->a.program.fingerprint())
+        return invalid_module("target module group/stage/node identity must match the neutral selected plan");
+    if (prog.trap) return fail_invalid_program(prog.trap_message);
+    if (m.kernel_variant != select_kernel_variant(prog))
+        return invalid_module("target module kernel variant disagrees with the op spec");
+    if (!kind_supported(prog.kind)) return fail_unsupported("operator `" + prog.op_id + "`");
+
+    cudaSetDevice(d->ordinal);
+    auto inst = std::make_unique<vyb_instance>();
+    inst->dev = d;
+    inst->program = std::move(prog);
+    inst->variant = m.kernel_variant;
+    inst->artifact = artifact->a.digest;
+    inst->payload = pl.digest;
+    vyb_device_identity_of(d, &inst->identity);
+    inst->generation = d->generation.load();
+    cudaError_t e = cudaStreamCreateWithFlags(&inst->stream, cudaStreamNonBlocking);
+    if (e != cudaSuccess) return fail_dispatch(int(e), "stream creation failed: " + cuda_msg(e));
+    inst->scratch_len = scratch_bytes_for(inst->program);
+    if (inst->scratch_len) {
+        e = cudaMalloc(&inst->scratch, inst->scratch_len);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            cudaStreamDestroy(inst->stream);
+            return fail_oom(inst->scratch_len, 0);
+        }
+    }
+    e = cudaMalloc(reinterpret_cast<void**>(&inst->status_dev), 16);
+    if (e == cudaSuccess) e = cudaMemset(inst->status_dev, 0, 16);
+    if (e == cudaSuccess) e = cudaHostAlloc(reinterpret_cast<void**>(&inst->status_host), 16, cudaHostAllocDefault);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "status buffer allocation failed: " + cuda_msg(e));
+    }
+    std::memset(inst->status_host, 0, 16);
+    *instance = inst.release();
+    clear_error();
+    return VYB_OK;
+}
+
+void vyb_instance_artifact_digest(const vyb_instance* i, uint8_t out[32]) { std::memcpy(out, i->artifact.data(), 32); }
+void vyb_instance_payload_digest(const vyb_instance* i, uint8_t out[32]) { std::memcpy(out, i->payload.data(), 32); }
+int32_t vyb_instance_device(const vyb_instance* i, vyb_device_identity* out) {
+    if (!i || !out) return fail_invalid_program("Fix: pass a non-null instance and identity out-pointer.");
+    *out = i->identity;
+    return VYB_OK;
+}
+void vyb_instance_free(vyb_instance* i) {
+    if (!i) return;
+    cudaSetDevice(i->dev->ordinal);
+    if (i->stream) {
+        cudaStreamSynchronize(i->stream);
+        cudaStreamDestroy(i->stream);
+    }
+    for (auto& b : i->pinned) cudaFreeHost(b.ptr);
+    for (auto& b : i->temps) cudaFree(b.ptr);
+    if (i->scratch) cudaFree(i->scratch);
+    if (i->status_dev) cudaFree(i->status_dev);
+    if (i->status_host) cudaFreeHost(i->status_host);
+    delete i;
+}
+
+// ---- submit (vyre-driver-cuda/src/materializer.rs:165-283) -------------------------------------------------------------
+int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const vyb_binding* bindings,
+                   size_t n_bindings, const vyb_dispatch_config* config, vyb_submission** submission) {
+    if (!inst || !artifact_digest || !submission || (!bindings && n_bindings))
+        return fail_invalid_program("Fix: pass non-null instance, artifact digest, bindings and submission out-pointer.");
+    vyb_device* d = inst->dev;
+    if (int32_t rc = d->check_alive("submission")) return rc;
+    if (inst->generation != d->generation.load())
+        return fail_device_lost(d->device_name, inst->generation,
+                                "the instance belongs to a previous device generation");
+    if (std::memcmp(artifact_digest, inst->artifact.data(), 32) != 0)
+        return fail_invalid_program(
+            "Fix: the binding set was built for a different artifact than this instance; rebuild the bindings from the "
+            "session that owns the instance.");
+    bool leave_resident = false;
+    if (config) {
+        const bool any_grid = config->grid_override[0] || config->grid_override[1] || config->grid_override[2];
+        if (any_grid)
+            for (int a = 0; a < 3; ++a)
+                if (config->grid_override[a] == 0)
+                    return fail_invalid_program("Fix: invocation grid axis " + std::to_string(a) +
+                                                " must be positive, got 0.");
+        if (config->workgroup_override[0] || config->workgroup_override[1] || config->workgroup_override[2])
+            return fail_unsupported("DispatchConfig.workgroup_override (hand-written kernels fix their launch shape)");
+        if (config->ulp_budget) return fail_unsupported("DispatchConfig.ulp_budget");
+        if (config->max_output_bytes) return fail_unsupported("DispatchConfig.max_output_bytes");
+        if (config->cooperative) return fail_unsupported("DispatchConfig.cooperative");
+        leave_resident = config->leave_resident != 0;
+    }
+    const Program& p = inst->program;
+    std::lock_guard<std::mutex> ilk(inst->mu);
+    cudaSetDevice(d->ordinal);
+
+    auto sub = std::make_unique<vyb_submission>();
+    sub->inst = inst;
+    void* slot_ptr[16] = {nullptr};
+    auto cleanup = [&]() {
+        for (void* t : sub->temps) inst->release_temp(t);
+        for (auto& o : sub->outputs)
+            if (o.host) inst->release_pinned(o.host);
+        std::lock_guard<std::mutex> lk(d->mu);
+        for (uint64_t id : sub->resident_ids) {
+            auto it = d->residents.find(id);
+            if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
+        }
+    };
+    for (size_t i = 0; i < n_bindings; ++i) {
+        if (!p.buffer_by_binding(bindings[i].value_id)) {
+            cleanup();
+            return fail_invalid_program("Fix: binding names value id " + std::to_string(bindings[i].value_id) +
+                                        ", which this artifact does not declare; bind only the program's buffer slots.");
+        }
+    }
+    for (const BufferDecl& bd : p.buffers) {
+        if (bd.access == VYB_ACCESS_WORKGROUP) continue;
+        if (bd.binding >= 16) {
+            cleanup();
+            return fail_invalid_program("Fix: binding slot exceeds the 16 slots this backend supports.");
+        }
+        const size_t need = size_t(bd.count) * dtype_size_bytes(bd.dtype);
+        const size_t logical = bd.has_output_byte_range ? size_t(bd.output_byte_end - bd.output_byte_begin) : need;
+        const vyb_binding* b = nullptr;
+        for (size_t i = 0; i < n_bindings; ++i)
+            if (bindings[i].value_id == bd.binding) b = &bindings[i];
+        const bool is_input = bd.access == VYB_ACCESS_READ_ONLY || bd.access == VYB_ACCESS_READ_WRITE;
+        const bool is_output = bd.access == VYB_ACCESS_OUTPUT || bd.access == VYB_ACCESS_READ_WRITE;
+        void* dev_ptr = nullptr;
+        bool resident = false;
+        if (b && b->kind == VYB_BIND_RESIDENT) {
+            std::lock_guard<std::mutex> lk(d->mu);
+            Resident* r = nullptr;
+            if (int32_t rc = d->resolve(b->resident, "CUDA resident dispatch", &r)) {
+                cleanup();
+                return rc;
+            }
+            // an output may be bound with its logical (trimmed) size; inputs need the declared size
+            const size_t min_len = bd.access == VYB_ACCESS_OUTPUT ? logical : need;
+            if (r->len < min_len) {
+                cleanup();
+                return fail_invalid_program("Fix: resident buffer bound to `" + bd.name + "` holds " +
+                                            std::to_string(r->len) + " bytes but the program needs " +
+                                            std::to_string(min_len) + "; allocate the declared size.");
+            }
+            r->inflight++;
+            sub->resident_ids.push_back(b->resident.id);
+            dev_ptr = r->ptr;
+            resident = true;
+        } else if (b && b->kind == VYB_BIND_HOST) {
+            const bool placeholder_ok = bd.access == VYB_ACCESS_OUTPUT && (b->len == logical || b->len == need);
+            if (b->len != need && !placeholder_ok) {
+                cleanup();
+                return fail_invalid_program("Fix: host bytes bound to `" + bd.name + "` are " + std::to_string(b->len) +
+                                            " bytes but the program declares " + std::to_string(need) +
+                                            "; bind exactly count * element size bytes.");
+            }
+            if (!b->host_ptr && b->len) {
+                cleanup();
+                return fail_invalid_program("Fix: host binding for `" + bd.name + "` has a null pointer.");
+            }
+        } else if (b) {
+            cleanup();
+            return fail_invalid_program("Fix: binding kind must be VYB_BIND_HOST or VYB_BIND_RESIDENT.");
+        } else if (bd.access != VYB_ACCESS_OUTPUT) {
+            cleanup();
+            return fail_invalid_program("Fix: missing input for buffer `" + bd.name + "` (slot " +
+                                        std::to_string(bd.binding) + "); bind every ReadOnly and ReadWrite buffer.");
+        }
+        if (!resident) {
+            dev_ptr = inst->acquire_temp(need);
+            if (!dev_ptr) {
+                cleanup();
+                return fail_oom(need, 0);
+            }
+            sub->temps.push_back(dev_ptr);
+            cudaError_t e = cudaSuccess;
+            if (is_input)
+                e = cudaMemcpyAsync(dev_ptr, b->host_ptr, need, cudaMemcpyHostToDevice, inst->stream);
+            else
+                e = cudaMemsetAsync(dev_ptr, 0, need, inst->stream);  // backend-allocated outputs start zeroed
+            if (e != cudaSuccess) {
+                cleanup();
+                return fail_dispatch(int(e), "input staging failed: " + cuda_msg(e));
+            }
+        }
+        slot_ptr[bd.binding] = dev_ptr;
+        if (is_output) {
+            OutputSlot o;
+            o.value_id = bd.binding;
+            o.dev_ptr = static_cast<uint8_t*>(dev_ptr) + (bd.has_output_byte_range ? bd.output_byte_begin : 0);
+            o.len = logical;
+            if (!(resident && leave_resident)) {
+                o.host = inst->acquire_pinned(logical);
+                if (!o.host) {
+                    cleanup();
+                    return fail_oom(logical, 0);
+                }
+            }
+            sub->outputs.push_back(o);
+        }
+    }
+    cudaEventCreate(&sub->start);
+    cudaEventCreate(&sub->end);
+    cudaEventCreateWithFlags(&sub->done, cudaEventDisableTiming);
+    cudaEventRecord(sub->start, inst->stream);
+    cudaError_t e = dispatch(inst, slot_ptr, inst->stream);
+    cudaEventRecord(sub->end, inst->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaStreamSynchronize(inst->stream);
+        cleanup();
+        cudaEventDestroy(sub->start);
+        cudaEventDestroy(sub->end);
+        cudaEventDestroy(sub->done);
+        if (e == cudaErrorNotSupported) return fail_unsupported("operator `" + p.op_id + "`");
+        return fail_dispatch(int(e), "kernel launch failed: " + cuda_msg(e));
+    }
+    for (auto& o : sub->outputs)
+        if (o.host) cudaMemcpyAsync(o.host, o.dev_ptr, o.len, cudaMemcpyDeviceToHost, inst->stream);
+    cudaMemcpyAsync(inst->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
+    cudaEventRecord(sub->done, inst->stream);
+    *submission = sub.release();
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_submission_is_ready(const vyb_submission* s) {
+    if (!s || s->consumed) return 0;
+    return cudaEventQuery(s->done) == cudaSuccess ? 1 : 0;
+}
+
+int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion) {
+    if (!s || !completion) return fail_invalid_program("Fix: pass a non-null submission and completion out-pointer.");
+    if (s->consumed) return fail_invalid_program("Fix: completion may be consumed only once.");
+    vyb_instance* inst = s->inst;
+    vyb_device* d = inst->dev;
+    cudaSetDevice(d->ordinal);
+    cudaError_t e = cudaEventSynchronize(s->done);
+    float ms = 0.0f;
+    const bool timed = e == cudaSuccess && cudaEventElapsedTime(&ms, s->start, s->end) == cudaSuccess;
+    uint32_t status = 0;
+    {
+        std::lock_guard<std::mutex> ilk(inst->mu);
+        for (void* t : s->temps) inst->release_temp(t);
+        if (e == cudaSuccess) {
+            status = inst->status_host[0];
+            if (status) {
+                cudaMemsetAsync(inst->status_dev, 0, 16, inst->stream);
+                inst->status_host[0] = 0;
+            }
+        }
+    }
+    {
+        std::lock_guard<std::mutex> lk(d->mu);
+        for (uint64_t id : s->resident_ids) {
+            auto it = d->residents.find(id);
+            if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
+        }
+    }
+    cudaEventDestroy(s->start);
+    cudaEventDestroy(s->end);
+    cudaEventDestroy(s->done);
+    s->consumed = true;
+    auto release_outputs = [&]() {
+        std::lock_guard<std::mutex> ilk(inst->mu);
+        for (auto& o : s->outputs)
+            if (o.host) inst->release_pinned(o.host);
+    };
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        release_outputs();
+        delete s;
+        const bool lost = e == cudaErrorIllegalAddress || e == cudaErrorLaunchFailure || e == cudaErrorHardwareStackError ||
+                          e == cudaErrorIllegalInstruction || e == cudaErrorECCUncorrectable || e == cudaErrorDevicesUnavailable;
+        if (lost) {
+            vyb_device_mark_lost(d, cuda_msg(e).c_str());
+            return fail_device_lost(d->device_name, d->generation.load(), cuda_msg(e));
+        }
+        return fail_dispatch(int(e), "submission failed: " + cuda_msg(e));
+    }
+    if (status) {
+        release_outputs();
+        delete s;
+        return fail_dispatch(int(status), "a bounded device-side wait ran out (kernel status word " +
+                                              std::to_string(status) + "); the kernel drained without completing");
+    }
+    auto c = std::make_unique<vyb_completion>();
+    c->inst = inst;
+    c->artifact = inst->artifact;
+    c->outputs = std::move(s->outputs);
+    c->has_device_ns = timed;
+    c->device_ns = timed ? uint64_t(double(ms) * 1.0e6) : 0;
+    delete s;
+    *completion = c.release();
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_completion_output(const vyb_completion* c, uint32_t value_id, const uint8_t** bytes, size_t* len) {
+    if (!c || !bytes || !len) return fail_invalid_program("Fix: pass non-null completion, bytes and len pointers.");
+    for (const auto& o : c->outputs)
+        if (o.value_id == value_id) {
+            if (!o.host)
+                return fail_invalid_program("Fix: output value " + std::to_string(value_id) +
+                                            " was left resident (leave_resident=1); download it from its resident handle.");
+            *bytes = static_cast<const uint8_t*>(o.host);
+            *len = o.len;
+            return VYB_OK;
+        }
+    return fail_invalid_program("Fix: value id " + std::to_string(value_id) + " is not an output of this artifact.");
+}
+uint32_t vyb_completion_output_count(const vyb_completion* c) { return c ? uint32_t(c->outputs.size()) : 0; }
+int32_t vyb_completion_device_ns(const vyb_completion* c, uint64_t* ns) {
+    if (!c || !ns) return fail_invalid_program("Fix: pass non-null completion and ns pointers.");
+    if (!c->has_device_ns) return fail_unsupported("device timestamps for this submission");
+    *ns = c->device_ns;
+    return VYB_OK;
+}
+void vyb_completion_free(vyb_completion* c) {
+    if (!c) return;
+    {
+        std::lock_guard<std::mutex> ilk(c->inst->mu);
+        for (auto& o : c->outputs)
+            if (o.host) c->inst->release_pinned(o.host);
+    }
+    delete c;
+}
+
+// ---- kernel-level entry points ----------------------------------------------------------------------------------------------
+int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                        uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
+                        uint32_t* status) {
+    if (!x_bf16 || !w_packed || !scale_bf16 || !y) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (out_dtype != VYB_DT_BF16 && out_dtype != VYB_DT_F32)
+        return fail_invalid_program("Fix: int4 gemv output dtype must be BF16 or F32.");
+    if (!vybk::int4_gemv_supported(m, n, k, group_size))
+        return fail_unsupported("int4 gemv shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
+                                std::to_string(k) + " group=" + std::to_string(group_size) +
+                                " (needs 1 <= m <= 8, group 128, k a multiple of 1024)");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) |
+         reinterpret_cast<uintptr_t>(scale_bf16)) & 15)
+        return fail_invalid_program("Fix: int4 gemv operands must be 16-byte aligned (bulk copies start on 16-byte boundaries).");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    e = vybk::launch_int4_gemv(x_bf16, w_packed, scale_bf16, y, m, n, k, out_dtype == VYB_DT_F32 ? 1u : 0u, sms,
+                               static_cast<cudaStream_t>(stream), status);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "int4 gemv launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
+}
+
+int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
+                                      uint32_t m, uint32_t n, uint32_t k, void* stream) {
+    if (!x_f32 || !w_i8 || !scale_f32 || !y_f32) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (m == 0 || n == 0 || k == 0)
+        return fail_invalid_program("Fix: int8 weight-only linear requires nonzero m, n and k.");
+    cudaError_t e = vybk::launch_int8_weight_only_linear(static_cast<const float*>(x_f32), static_cast<const int8_t*>(w_i8),
+                                                         static_cast<const float*>(scale_f32), static_cast<float*>(y_f32),
+                                                         m, n, k, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "int8 weight-only launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Launch prototypes of the hand-written sm_100a kernels. All pointers are device pointers; every launcher
+// returns the cudaError_t of the launch (0 = ok) and never synchronises.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace vybk {
+
+// ---- decode GEMV / skinny GEMM (int4_gemv.cu) ---------------------------------------------------------------
+// y[m,n] = cast( sum_k x[m,k] * (q[n,k]-8) * s[n,k/128] ), m <= 8, group 128, k % 1024 == 0.
+// out_dtype: 0 = bf16, 1 = f32. status: optional 4-word device buffer set non-zero when a bounded wait ran out.
+bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
+cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                             uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
+                             uint32_t* status);
+// any group size dividing k, k % 8 == 0, any m; plain loads, no TMA
+cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,
+                                       uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32,
+                                       cudaStream_t stream);
+
+// ---- int8 weight-only linear (int8_linear.cu) ------------------------------------------------------------------
+cudaError_t launch_int8_weight_only_linear(const float* x, const int8_t* w, const float* scale, float* y, uint32_t m,
+                                           uint32_t n, uint32_t k, cudaStream_t stream);
+
+// ---- reference-shaped small ops (ref_ops.cu); each keeps the reference's evaluation order -----------------------
+cudaError_t launch_linear_4bit(const float* x, const uint32_t* w, const float* b, float* out, uint32_t in_dim,
+                               uint32_t out_dim, cudaStream_t s);
+cudaError_t launch_linear_4bit_affine_grouped(const float* x, const uint32_t* w, const float* scale,
+                                              const uint32_t* zp, const float* b, float* out, uint32_t in_dim,
+                                              uint32_t out_dim, uint32_t group, uint32_t batch, cudaStream_t s);
+cudaError_t launch_i4_unpack(const uint32_t* packed, int32_t* out, uint32_t lanes, cudaStream_t s);
+cudaError_t launch_i4_dot_i32(const uint32_t* lhs, const uint32_t* rhs, int32_t* out, uint32_t lanes, cudaStream_t s);
+cudaError_t launch_i4_dot_f32_scaled(const uint32_t* lhs, const uint32_t* rhs, const float* ls, const float* rs,
+                                     float* out, uint32_t lanes, cudaStream_t s);
+cudaError_t launch_i4_batched_matvec(const uint32_t* w, const float* x, const float* scales, float* out,
+                                     uint32_t batch, uint32_t rows, uint32_t cols, cudaStream_t s);
+cudaError_t launch_i4_batched_matmul(const uint32_t* w, const uint32_t* act, const float* rs, const float* bs,
+                                     float* out, uint32_t batch, uint32_t rows, uint32_t cols, cudaStream_t s);
+cudaError_t launch_i4_batched_matmul_top1(const uint32_t* w, const uint32_t* act, const float* rs, const float* bs,
+                                          float* out, uint32_t batch, uint32_t rows, uint32_t cols, cudaStream_t s);
+cudaError_t launch_int8_unpack(const uint32_t* packed, const float* scales, float* out, uint32_t n, uint32_t cols,
+                               cudaStream_t s);
+cudaError_t launch_int8_pack(const uint32_t* in, uint32_t* out, uint32_t n, cudaStream_t s);
+// dtype: 0 = f32, 1 = bf16, 2 = f16
+cudaError_t launch_linear_rows(const void* x, const void* w, const void* bias, void* out, uint32_t rows,
+                               uint32_t in_dim, uint32_t out_dim, uint32_t dtype, uint32_t out_in, cudaStream_t s);
+cudaError_t launch_matmul_u32(const uint32_t* a, const uint32_t* b, uint32_t* out, uint32_t m, uint32_t k, uint32_t n,
+                              cudaStream_t s);
+cudaError_t launch_moe_gate(const float* scores, uint32_t* idx, float* weights, uint32_t tokens, uint32_t experts,
+                            uint32_t k, cudaStream_t s);
+cudaError_t launch_softmax_top_k(const float* scores, uint32_t* out_idx, float* out_w, float* best_vals,
+                                 uint32_t* best_idxs, uint32_t n, uint32_t k, cudaStream_t s);
+cudaError_t launch_top_k(const float* in, uint32_t* out_idx, float* best_vals, uint32_t* best_idxs, uint32_t n,
+                         uint32_t k, cudaStream_t s);
+cudaError_t launch_swiglu(const void* gate, const void* up, void* out, uint32_t n, uint32_t dtype, cudaStream_t s);
+// hidden_scratch: f32 [hidden]
+cudaError_t launch_expert_mlp(const float* x, const float* wg, const float* bg, const float* wu, const float* bu,
+                              const float* wd, const float* bd, float* out, float* hidden_scratch, uint32_t in_dim,
+                              uint32_t hidden, uint32_t out_dim, cudaStream_t s);
+cudaError_t launch_moe_layer_accumulate(const float* weights, const float* expert_out, float* out, uint32_t k,
+                                        uint32_t out_dim, cudaStream_t s);
+
+}  // namespace vybk

@@ -1,0 +1,221 @@
+"""ctypes binding of libvyre_b200.so (the C ABI declared in include/vyre_b200.h).
+
+The library is the product; this module only loads it and gives every export its signature. Loading fails
+loudly when the library has not been built: there is no Python or CPU fallback for any operator.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libvyre_b200.so")
+
+# DataType tags (vyre-spec/src/data_type.rs:227-257)
+DT_U32, DT_I32, DT_F16, DT_BF16, DT_F32, DT_U8, DT_I8, DT_I4 = 0x01, 0x02, 0x09, 0x0A, 0x0B, 0x0E, 0x10, 0x1B
+ACCESS_READ_ONLY, ACCESS_READ_WRITE, ACCESS_OUTPUT, ACCESS_WORKGROUP = 0, 1, 2, 3
+BIND_HOST, BIND_RESIDENT = 0, 1
+
+ERR_DEVICE_OUT_OF_MEMORY = 1001
+ERR_UNSUPPORTED_FEATURE = 1002
+ERR_DISPATCH_FAILED = 1005
+ERR_INVALID_PROGRAM = 1006
+ERR_DEVICE_LOST = 1008
+
+
+class BackendError(RuntimeError):
+    """vyre_driver::BackendError: `code` is ErrorCode::stable_id, the message always carries 'Fix:'."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+class ResidentHandle(C.Structure):
+    _fields_ = [("owner", C.c_uint64), ("id", C.c_uint64)]
+
+
+class TargetProfile(C.Structure):
+    _fields_ = [("identity", C.c_char * 64), ("generation", C.c_uint32), ("max_workgroup_size", C.c_uint32 * 3),
+                ("max_invocations", C.c_uint32), ("max_dynamic_shared_bytes", C.c_uint32),
+                ("subgroup_size", C.c_uint32)]
+
+
+class RegistrationInfo(C.Structure):
+    _fields_ = [("id", C.c_char_p), ("target_id", C.c_char_p), ("payload_format", C.c_char_p),
+                ("format_version", C.c_uint32), ("precedence", C.c_uint32), ("profile", TargetProfile)]
+
+
+class DeviceIdentity(C.Structure):
+    _fields_ = [("backend", C.c_char * 32), ("device", C.c_char * 96), ("generation", C.c_uint64)]
+
+
+class DeviceCaps(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("ordinal", C.c_int32), ("compute_major", C.c_int32),
+                ("compute_minor", C.c_int32), ("total_memory", C.c_uint64), ("max_threads_per_block", C.c_int32),
+                ("shared_memory_per_block", C.c_int32), ("shared_memory_per_sm", C.c_int32),
+                ("shared_memory_per_block_optin", C.c_int32), ("warp_size", C.c_int32),
+                ("cooperative_launch", C.c_int32), ("multi_processor_count", C.c_int32), ("l2_cache_bytes", C.c_int32),
+                ("memory_clock_rate_khz", C.c_int32), ("core_clock_rate_khz", C.c_int32),
+                ("global_memory_bus_width_bits", C.c_int32)]
+
+
+class BufferDecl(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("binding", C.c_uint32), ("access", C.c_uint32), ("dtype", C.c_uint32),
+                ("count", C.c_uint32), ("has_output_byte_range", C.c_uint32), ("output_byte_begin", C.c_uint64),
+                ("output_byte_end", C.c_uint64)]
+
+
+class QuantizedLinear4BitSpec(C.Structure):
+    _fields_ = [("in_dim", C.c_uint32), ("out_dim", C.c_uint32), ("storage_dtype", C.c_uint32),
+                ("scale_group_size", C.c_uint32), ("zero_point_group_size", C.c_uint32)]
+
+
+class PlannerEvidence(C.Structure):
+    _fields_ = [("in_dim", C.c_uint32), ("out_dim", C.c_uint32), ("group_size", C.c_uint32),
+                ("group_count", C.c_uint32), ("packed_weight_bytes", C.c_uint64),
+                ("dequantized_weight_bytes", C.c_uint64), ("sidecar_bytes", C.c_uint64), ("bias_bytes", C.c_uint64),
+                ("output_bytes", C.c_uint64), ("dequant_bytes_elided", C.c_uint64), ("matmul_m", C.c_uint32),
+                ("matmul_k", C.c_uint32), ("matmul_n", C.c_uint32), ("matmul_tile", C.c_uint32),
+                ("matmul_selected_path", C.c_char_p), ("matmul_candidate_path", C.c_char_p),
+                ("matmul_fallback_reason", C.c_char_p), ("tensor_core_eligible", C.c_uint32),
+                ("output_drift_abs_tolerance", C.c_float)]
+
+
+class Binding(C.Structure):
+    _fields_ = [("value_id", C.c_uint32), ("kind", C.c_int32), ("host_ptr", C.c_void_p), ("len", C.c_size_t),
+                ("resident", ResidentHandle)]
+
+
+class DispatchConfig(C.Structure):
+    _fields_ = [("grid_override", C.c_uint32 * 3), ("workgroup_override", C.c_uint32 * 3), ("timeout_ns", C.c_uint64),
+                ("label", C.c_char_p), ("ulp_budget", C.c_uint32), ("max_output_bytes", C.c_uint64),
+                ("cooperative", C.c_uint32), ("leave_resident", C.c_uint32)]
+
+
+_lib = None
+_S, _U, _P, _PP = C.c_char_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_void_p)
+
+# name -> argtypes for every status-returning export (restype int32)
+_STATUS_FUNCS = {
+    "vyb_registration": [C.POINTER(RegistrationInfo)],
+    "vyb_nn_linear_4bit": [_S, _S, _S, _S, _U, _U, _PP],
+    "vyb_nn_linear_4bit_affine_grouped": [_S] * 6 + [_U] * 3 + [_PP],
+    "vyb_nn_linear_4bit_affine_grouped_batched": [_S] * 6 + [_U] * 4 + [_PP],
+    "vyb_nn_linear_4bit_affine_grouped_typed": [C.POINTER(QuantizedLinear4BitSpec)] + [_S] * 6 + [_PP],
+    "vyb_nn_linear_4bit_affine_grouped_batched_typed": [C.POINTER(QuantizedLinear4BitSpec), _U] + [_S] * 6 + [_PP],
+    "vyb_nn_linear_4bit_affine_grouped_planner_evidence": [C.POINTER(QuantizedLinear4BitSpec),
+                                                            C.POINTER(PlannerEvidence)],
+    "vyb_math_unpack_i4x8": [_S, _S, _U, _PP],
+    "vyb_math_i4x8_dot_i32": [_S, _S, _S, _U, _U, _PP],
+    "vyb_math_i4x8_dot_f32_scaled": [_S] * 5 + [_U, _U, _PP],
+    "vyb_math_i4x8_matvec_f32_scaled": [_S] * 4 + [_U, _U, _U, _PP],
+    "vyb_math_i4x8_batched_matvec_f32_scaled": [_S] * 4 + [_U] * 4 + [_PP],
+    "vyb_math_i4x8_batched_matmul_f32_scaled": [_S] * 5 + [_U] * 4 + [_PP],
+    "vyb_math_i4x8_batched_matmul_top1_f32_scaled": [_S] * 5 + [_U] * 4 + [_PP],
+    "vyb_quant_int8_unpack": [_S, _S, _S, _U, _U, _PP],
+    "vyb_quant_int8_pack": [_S, _S, _U, _PP],
+    "vyb_nn_linear_rows": [_S] * 4 + [_U] * 3 + [_PP],
+    "vyb_nn_linear_rows_no_bias": [_S] * 3 + [_U] * 3 + [_PP],
+    "vyb_nn_linear_rows_no_bias_typed": [_S] * 3 + [_U] * 4 + [_PP],
+    "vyb_nn_linear_rows_no_bias_out_in_typed": [_S] * 3 + [_U] * 4 + [_PP],
+    "vyb_math_matmul": [_S] * 3 + [_U] * 3 + [_PP],
+    "vyb_nn_moe_gate": [_S] * 3 + [_U, _U, _PP],
+    "vyb_nn_softmax_top_k": [_S] * 3 + [_U, _U, _PP],
+    "vyb_nn_top_k": [_S, _S, _U, _U, _PP],
+    "vyb_nn_swiglu": [_S] * 3 + [_U, _PP],
+    "vyb_nn_swiglu_typed": [_S] * 3 + [_U, _U, _PP],
+    "vyb_nn_expert_mlp": [_S] * 8 + [_U] * 3 + [_PP],
+    "vyb_nn_moe_layer_route_and_accumulate": [_S] * 7 + [_U] * 4 + [_PP],
+    "vyb_nn_linear_int4_grouped_rowmajor": [_S] * 4 + [_U] * 5 + [_PP],
+    "vyb_nn_linear_int8_weight_only": [_S] * 4 + [_U] * 3 + [_PP],
+    "vyb_nn_linear_int8_dynamic": [_S] * 4 + [_U] * 3 + [_PP],
+    "vyb_nn_moe_ffn_int4": [_S] * 9 + [_U] * 6 + [_PP],
+    "vyb_program_buffer": [_P, _U, C.POINTER(BufferDecl)],
+    "vyb_compile": [_P, _PP],
+    "vyb_target_compile": [_P, _PP],
+    "vyb_payload_bytes": [_P, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
+    "vyb_payload_from_bytes": [C.c_char_p, C.c_size_t, _PP],
+    "vyb_device_acquire": [C.c_int32, _PP],
+    "vyb_device_identity_of": [_P, C.POINTER(DeviceIdentity)],
+    "vyb_device_caps_of": [_P, C.POINTER(DeviceCaps)],
+    "vyb_device_is_healthy": [_P],
+    "vyb_device_mark_lost": [_P, _S],
+    "vyb_device_reacquire": [_P],
+    "vyb_alloc": [_P, C.c_size_t, C.POINTER(ResidentHandle)],
+    "vyb_upload": [_P, ResidentHandle, _P, C.c_size_t],
+    "vyb_upload_at": [_P, ResidentHandle, C.c_size_t, _P, C.c_size_t],
+    "vyb_download": [_P, ResidentHandle, _P, C.c_size_t],
+    "vyb_download_range": [_P, ResidentHandle, C.c_size_t, _P, C.c_size_t],
+    "vyb_free": [_P, ResidentHandle],
+    "vyb_resident_device_ptr": [_P, ResidentHandle, _PP, C.POINTER(C.c_size_t)],
+    "vyb_materialize": [_P, _P, _P, _PP],
+    "vyb_instance_device": [_P, C.POINTER(DeviceIdentity)],
+    "vyb_submit": [_P, C.c_char_p, C.POINTER(Binding), C.c_size_t, C.POINTER(DispatchConfig), _PP],
+    "vyb_submission_is_ready": [_P],
+    "vyb_submission_wait": [_P, _PP],
+    "vyb_completion_output": [_P, _U, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
+    "vyb_completion_device_ns": [_P, C.POINTER(C.c_uint64)],
+    "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_int8_weight_only_linear": [_P, _P, _P, _P, _U, _U, _U, _P],
+}
+
+_OTHER_FUNCS = {
+    "vyb_abi_version": (C.c_uint32, []),
+    "vyb_last_error_message": (C.c_char_p, []),
+    "vyb_supported_op_count": (C.c_uint32, []),
+    "vyb_supported_op": (C.c_char_p, [_U]),
+    "vyb_blake3": (None, [_P, C.c_size_t, C.c_char_p]),
+    "vyb_i4_packed_words": (C.c_uint32, [_U]),
+    "vyb_quantized_linear_4bit_spec_affine_grouped": (None, [_U, _U, _U, C.POINTER(QuantizedLinear4BitSpec)]),
+    "vyb_program_op_id": (C.c_char_p, [_P]),
+    "vyb_program_buffer_count": (C.c_uint32, [_P]),
+    "vyb_program_workgroup_size": (None, [_P, C.POINTER(C.c_uint32 * 3)]),
+    "vyb_program_is_trap": (C.c_uint32, [_P]),
+    "vyb_program_trap_message": (C.c_char_p, [_P]),
+    "vyb_program_fingerprint": (None, [_P, C.c_char_p]),
+    "vyb_program_free": (None, [_P]),
+    "vyb_artifact_digest": (None, [_P, C.c_char_p]),
+    "vyb_artifact_free": (None, [_P]),
+    "vyb_payload_digest": (None, [_P, C.c_char_p]),
+    "vyb_payload_neutral_artifact": (None, [_P, C.c_char_p]),
+    "vyb_payload_format": (C.c_char_p, [_P]),
+    "vyb_payload_free": (None, [_P]),
+    "vyb_device_release": (None, [_P]),
+    "vyb_instance_artifact_digest": (None, [_P, C.c_char_p]),
+    "vyb_instance_payload_digest": (None, [_P, C.c_char_p]),
+    "vyb_instance_free": (None, [_P]),
+    "vyb_completion_output_count": (C.c_uint32, [_P]),
+    "vyb_completion_free": (None, [_P]),
+}
+
+
+def exported_names() -> list[str]:
+    return sorted(list(_STATUS_FUNCS) + list(_OTHER_FUNCS))
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m vyre_b200.build` (nvcc, sm_100a). "
+                "The native library is the only implementation; there is no fallback.")
+        L = C.CDLL(LIB_PATH)
+        for name, args in _STATUS_FUNCS.items():
+            fn = getattr(L, name)
+            fn.restype = C.c_int32
+            fn.argtypes = args
+        for name, (res, args) in _OTHER_FUNCS.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        msg = lib().vyb_last_error_message()
+        raise BackendError(rc, msg.decode("utf-8", "replace") if msg else "")
