@@ -145,6 +145,42 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def run_quick(args) -> None:
+    """A few plain launches of the decode GEMV over rotating weight copies; prints one short JSON line."""
+    import torch
+
+    from vyre_b200 import ffi, synth
+
+    L = ffi.lib()
+    m = args.m
+    x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
+    x = torch.from_numpy(x_np.view(np.int16)).cuda()
+    ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(COPIES)]
+    ss = [torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda() for c in range(COPIES)]
+    y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def launch(i: int):
+        c = i % COPIES
+        ffi.check(L.vyb_k_int4_gemv(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
+                                    GROUP, ffi.DT_BF16, C.c_void_p(stream), C.c_void_p(status.data_ptr())))
+
+    for i in range(args.warmup):
+        launch(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(args.steps):
+        launch(i)
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / max(1, args.steps)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    print(json.dumps({"quick": True, "m": m, "steps": args.steps, "us_per_launch": us,
+                      "gbs": algorithmic_bytes(m) / (us * 1e-6) / 1e9}))
+
+
 def run_native(args) -> None:
     import torch
 
@@ -353,9 +389,13 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2000)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
+    ap.add_argument("--quick", action="store_true",
+                    help="kernel-only run without graphs, end-to-end leg or CPU baseline (the case profiled under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.quick:
+        run_quick(args)
     else:
         run_native(args)
 

@@ -49,8 +49,11 @@ def test_decode_gemv_config2_full_size(dev, m):
     err = rel_err(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want))
     assert err <= TOL_BF16_OUT, err
     # same rounding as the oracle except where f32 accumulation order moves a value across a rounding boundary
+    # (outputs far below the typical magnitude are excluded: a bf16 ulp there is far below the f32 sum's error)
+    wf = synth.bf16_bits_to_f32(want)
+    big = np.abs(wf) >= 1e-2 * np.sqrt(np.mean(wf.astype(np.float64) ** 2))
     ulp = np.abs(got.astype(np.int32) - want.astype(np.int32))
-    assert ulp.max() <= 1 and np.mean(ulp != 0) < 0.02
+    assert ulp[big].max() <= 1 and np.mean(ulp != 0) < 0.02
     got32 = run_int4(dev, x, w, s, m, n, k, out_dtype=ffi.DT_F32)
     want32 = oracle.int4_rowmajor_linear(x, w, s, m, n, k, out_dtype=oracle.DT_F32)
     assert rel_err(got32, want32) <= TOL_F32_ACC
@@ -125,7 +128,8 @@ def test_int8_weight_only_config1(dev):
     want = oracle.int8_weight_only_linear(x, w, s, m, n, k, mode=0)
     assert rel_err(got, want) <= TOL_F32_ACC
     # and against the reference's own sequential f32 order (int8_unpack then linear_rows_out_in)
-    assert rel_err(got, oracle.int8_weight_only_linear(x, w, s, m, n, k, mode=1)) <= TOL_F32_ACC
+    # (that order carries its own f32 rounding of about the same size, hence twice the window)
+    assert rel_err(got, oracle.int8_weight_only_linear(x, w, s, m, n, k, mode=1)) <= 2 * TOL_F32_ACC
     for (mm, nn, kk) in [(1, 1, 1), (3, 7, 17), (17, 9, 48), (33, 65, 1040)]:
         x, w, s = synth.int8_weight_only_inputs(mm, nn, kk, seed=kk)
         prog = vb.linear_int8_weight_only("x", "w", "scale", "out", mm, kk, nn)

@@ -12,12 +12,11 @@
 //    Row pitch in shared memory is 2048+64 B so that the 128-bit fragment loads below are bank-conflict free.
 //  * 16 consumer warps each own a fixed 256-k slice of the stage. The activation fragments for that slice
 //    live in registers for the whole kernel (32 regs), so shared memory is read exactly once per weight byte.
-//  * Dequantisation is one LOP3 per two weights: (w >> 4i) & 0x000F000F | 0x43004300 is the bf16 pair
-//    (128+q_lo, 128+q_hi), fed straight into mma.sync.m16n8k16 (A = 16 weight rows, B = 8 batch columns,
-//    f32 accumulate). k is permuted identically on the A and B side, which a contraction allows.
-//    The constant 128+8 is removed per 128-k group with the activation group sum:
-//    sum_k (q-8) x = sum_k (128+q) x - 136 sum_k x, and the group scale multiplies the f32 group result,
-//    so products are exact and only f32 accumulation rounds.
+//  * Dequantisation is two instructions per two weights: (w >> 4i) & 0x000F000F | 0x43004300 is the bf16 pair
+//    (128+q_lo, 128+q_hi), a packed bf16 subtract of 136 makes it (q_lo-8, q_hi-8) exactly, and the pair is
+//    fed straight into mma.sync.m16n8k16 (A = 16 weight rows, B = 8 batch columns, f32 accumulate). k is
+//    permuted identically on the A and B side, which a contraction allows. The group scale multiplies the
+//    f32 group result, so products are exact and only f32 accumulation rounds.
 //  * Each warp leaves a 16x8 partial per tile in a shared slot; the last warp to arrive reduces the 16
 //    partials in fixed order (deterministic) and stores the outputs.
 //
@@ -108,13 +107,19 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
 }
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// bf16 pair (128 + nibble i, 128 + nibble i+4) of a packed word, exact
-__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int i) { return ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u; }
+// bf16 pair (nibble i - 8, nibble i+4 - 8) of a packed word: the LOP3 builds (128+q) in both halves, the packed
+// subtract of 136 (0x4308) is exact
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int i) {
+    const uint32_t v = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+    uint32_t r;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(0x43084308u));
+    return r;
+}
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 
@@ -126,6 +131,7 @@ struct Params {
     uint32_t m, n, k, groups;  // groups = k / 128
     uint32_t out_f32;
     uint32_t* status;
+    unsigned long long* trace;  // optional: per-CTA timeline (64 slots each), for tuning only
 };
 
 __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
@@ -137,12 +143,26 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    auto stamp = [&](int slot) {
+        if (p.trace && lane == 0 && (warp == 0 || warp == CONSUMER_WARPS)) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            p.trace[size_t(blockIdx.x) * 64 + (warp == 0 ? 0 : 32) + slot] = t;
+        }
+    };
+    stamp(0);
     const uint32_t r0 = uint32_t((uint64_t(blockIdx.x) * p.n) / gridDim.x);
     const uint32_t r1 = uint32_t((uint64_t(blockIdx.x + 1) * p.n) / gridDim.x);
     const uint32_t ntiles = (r1 - r0 + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t nkb = (p.k + KBLOCK - 1) / KBLOCK;
     const uint32_t units = ntiles * nkb;
     const uint32_t row_bytes = p.k / 2;
+    // When one k-block covers the whole row (k <= 4096) the rows of a tile are contiguous in global memory:
+    // the whole tile is ONE bulk copy (and its scales one more), laid out in shared memory with the global
+    // pitch. Otherwise each row needs its own copy and gets a padded, bank-conflict-free pitch.
+    const bool contiguous = nkb == 1;
+    const uint32_t row_pitch = contiguous ? row_bytes : uint32_t(ROW_PITCH);
+    const uint32_t scale_pitch = contiguous ? p.groups * 2 : uint32_t(SCALE_PITCH);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -155,6 +175,7 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncthreads();
+    stamp(1);
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------ producer warp ------------------------------
@@ -170,19 +191,31 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
             const uint32_t kbytes = min(uint32_t(KBLOCK), p.k - kb * KBLOCK) / 2;
             const uint32_t sbytes = min(uint32_t(KBLOCK / 128), p.groups - kb * (KBLOCK / 128)) * 2;
             const uint32_t bar = smem_u32(&ctrl->full[s]);
-            if (lane == 0) mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
-            __syncwarp();
+            if (u < 12) stamp(2 + u);
             uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
-            if (lane < TILE_ROWS) {
-                if (uint32_t(lane) < rows_valid)
-                    bulk_g2s(smem_u32(stage + lane * ROW_PITCH),
-                             p.w + size_t(row_base + lane) * row_bytes + size_t(kb) * ROW_BYTES, kbytes, bar);
+            if (contiguous) {
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
+                    bulk_g2s(smem_u32(stage), p.w + size_t(row_base) * row_bytes, rows_valid * kbytes, bar);
+                    bulk_g2s(smem_u32(stage + STAGE_W_BYTES), p.scales + size_t(row_base) * p.groups,
+                             rows_valid * sbytes, bar);
+                }
             } else {
-                const uint32_t r = lane - TILE_ROWS;
-                if (r < rows_valid)
-                    bulk_g2s(smem_u32(stage + STAGE_W_BYTES + r * SCALE_PITCH),
-                             p.scales + size_t(row_base + r) * p.groups + size_t(kb) * (KBLOCK / 128), sbytes, bar);
+                if (lane == 0) mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
+                __syncwarp();
+                if (lane < TILE_ROWS) {
+                    if (uint32_t(lane) < rows_valid)
+                        bulk_g2s(smem_u32(stage + lane * ROW_PITCH),
+                                 p.w + size_t(row_base + lane) * row_bytes + size_t(kb) * ROW_BYTES, kbytes, bar);
+                } else {
+                    const uint32_t r = lane - TILE_ROWS;
+                    if (r < rows_valid)
+                        bulk_g2s(smem_u32(stage + STAGE_W_BYTES + r * SCALE_PITCH),
+                                 p.scales + size_t(row_base + r) * p.groups + size_t(kb) * (KBLOCK / 128), sbytes,
+                                 bar);
+                }
             }
+            __syncwarp();
         }
         if (!alive && lane == 0 && p.status) atomicOr(p.status, 1u);
         return;
@@ -192,12 +225,10 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     const int g = lane >> 2;  // mma row group / batch column of the B fragment
     const int t = lane & 3;
     uint32_t xb[2][4][4];
-    float xs[2][2];
 
     auto load_x = [&](uint32_t kb) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-            float part = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 const uint32_t k0 = kb * KBLOCK + warp * WARP_K + c * 128 + t * 32 + wi * 8;
@@ -207,65 +238,85 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
                 xb[c][wi][1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
                 xb[c][wi][2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
                 xb[c][wi][3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
-                part += (bf16_lo(v.x) + bf16_hi(v.x)) + (bf16_lo(v.y) + bf16_hi(v.y)) +
-                        (bf16_lo(v.z) + bf16_hi(v.z)) + (bf16_lo(v.w) + bf16_hi(v.w));
             }
-            part += __shfl_xor_sync(0xffffffffu, part, 1);
-            part += __shfl_xor_sync(0xffffffffu, part, 2);
-            // the D fragment of this lane holds batch columns 2t and 2t+1
-            xs[c][0] = 136.0f * __shfl_sync(0xffffffffu, part, 4 * (2 * t));
-            xs[c][1] = 136.0f * __shfl_sync(0xffffffffu, part, 4 * (2 * t + 1));
         }
     };
     if (nkb == 1) load_x(0);
+    stamp(2);
 
-    bool alive = true;
+    // per-unit register image of this warp's slice of the stage: 2 x 16 B of each of the two fragment rows
+    // plus the two group scales of each row
+    struct Frag {
+        uint4 wl[2], wh[2];
+        uint32_t sc_lo, sc_hi;
+    };
+    auto fetch = [&](uint32_t u, Frag& f) -> bool {
+        const uint32_t s = u % STAGES;
+        bool ok = mbar_wait(smem_u32(&ctrl->full[s]), (u / STAGES) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) return false;
+        const uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
+        const uint8_t* wrow_lo = stage + g * row_pitch + warp * (WARP_K / 2) + t * 16;
+        const uint8_t* wrow_hi = wrow_lo + 8 * row_pitch;
+        f.wl[0] = *reinterpret_cast<const uint4*>(wrow_lo);
+        f.wh[0] = *reinterpret_cast<const uint4*>(wrow_hi);
+        f.wl[1] = *reinterpret_cast<const uint4*>(wrow_lo + 64);
+        f.wh[1] = *reinterpret_cast<const uint4*>(wrow_hi + 64);
+        f.sc_lo = *reinterpret_cast<const uint32_t*>(stage + STAGE_W_BYTES + g * scale_pitch + warp * 4);
+        f.sc_hi = *reinterpret_cast<const uint32_t*>(stage + STAGE_W_BYTES + (g + 8) * scale_pitch + warp * 4);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->empty[s]));
+        return true;
+    };
+
+    Frag cur, nxt;
+    bool alive = units > 0 ? fetch(0, cur) : true;
     for (uint32_t tile = 0; tile < ntiles && alive; ++tile) {
         float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (uint32_t kb = 0; kb < nkb; ++kb) {
             const uint32_t u = tile * nkb + kb;
-            const uint32_t s = u % STAGES;
             if (nkb != 1) load_x(kb);
-            alive = mbar_wait(smem_u32(&ctrl->full[s]), (u / STAGES) & 1, abort_flag);
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
-            const uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
-            const uint8_t* wrow_lo = stage + g * ROW_PITCH + warp * (WARP_K / 2) + t * 16;
-            const uint8_t* wrow_hi = wrow_lo + 8 * ROW_PITCH;
-            uint4 wl[2], wh[2];
-            wl[0] = *reinterpret_cast<const uint4*>(wrow_lo);
-            wh[0] = *reinterpret_cast<const uint4*>(wrow_hi);
-            wl[1] = *reinterpret_cast<const uint4*>(wrow_lo + 64);
-            wh[1] = *reinterpret_cast<const uint4*>(wrow_hi + 64);
-            const uint32_t sc_lo = *reinterpret_cast<const uint32_t*>(stage + STAGE_W_BYTES + g * SCALE_PITCH + warp * 4);
-            const uint32_t sc_hi =
-                *reinterpret_cast<const uint32_t*>(stage + STAGE_W_BYTES + (g + 8) * SCALE_PITCH + warp * 4);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->empty[s]));
-
+            if (u < 12) stamp(3 + 2 * u);
+            // software pipeline: pull the next unit's fragments into registers before the math of this one
+            const bool have_next = u + 1 < units;
+            if (have_next && nkb == 1) {
+                alive = fetch(u + 1, nxt);
+                if (!alive) break;
+            }
             if (kb * KBLOCK + warp * WARP_K < p.k) {
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
-                    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    const uint32_t lo[4] = {wl[c].x, wl[c].y, wl[c].z, wl[c].w};
-                    const uint32_t hi[4] = {wh[c].x, wh[c].y, wh[c].z, wh[c].w};
+                    // two independent accumulator chains per group keep the tensor pipe from waiting on itself
+                    float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    float acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    const uint32_t lo[4] = {cur.wl[c].x, cur.wl[c].y, cur.wl[c].z, cur.wl[c].w};
+                    const uint32_t hi[4] = {cur.wh[c].x, cur.wh[c].y, cur.wh[c].z, cur.wh[c].w};
 #pragma unroll
                     for (int wi = 0; wi < 4; ++wi) {
-                        mma_bf16(acc, nib_pair(lo[wi], 0), nib_pair(hi[wi], 0), nib_pair(lo[wi], 1), nib_pair(hi[wi], 1),
+                        mma_bf16(acc0, nib_pair(lo[wi], 0), nib_pair(hi[wi], 0), nib_pair(lo[wi], 1), nib_pair(hi[wi], 1),
                                  xb[c][wi][0], xb[c][wi][1]);
-                        mma_bf16(acc, nib_pair(lo[wi], 2), nib_pair(hi[wi], 2), nib_pair(lo[wi], 3), nib_pair(hi[wi], 3),
+                        mma_bf16(acc1, nib_pair(lo[wi], 2), nib_pair(hi[wi], 2), nib_pair(lo[wi], 3), nib_pair(hi[wi], 3),
                                  xb[c][wi][2], xb[c][wi][3]);
                     }
-                    const float s_lo = c == 0 ? bf16_lo(sc_lo) : bf16_hi(sc_lo);
-                    const float s_hi = c == 0 ? bf16_lo(sc_hi) : bf16_hi(sc_hi);
-                    out[0] = fmaf(s_lo, acc[0] - xs[c][0], out[0]);
-                    out[1] = fmaf(s_lo, acc[1] - xs[c][1], out[1]);
-                    out[2] = fmaf(s_hi, acc[2] - xs[c][0], out[2]);
-                    out[3] = fmaf(s_hi, acc[3] - xs[c][1], out[3]);
+                    const float s_lo = c == 0 ? bf16_lo(cur.sc_lo) : bf16_hi(cur.sc_lo);
+                    const float s_hi = c == 0 ? bf16_lo(cur.sc_hi) : bf16_hi(cur.sc_hi);
+                    out[0] = fmaf(s_lo, acc0[0] + acc1[0], out[0]);
+                    out[1] = fmaf(s_lo, acc0[1] + acc1[1], out[1]);
+                    out[2] = fmaf(s_hi, acc0[2] + acc1[2], out[2]);
+                    out[3] = fmaf(s_hi, acc0[3] + acc1[3], out[3]);
+                }
+            }
+            if (have_next) {
+                if (nkb == 1) {
+                    cur = nxt;
+                } else {
+                    alive = fetch(u + 1, cur);
+                    if (!alive) break;
                 }
             }
         }
         if (!alive) break;
+        if (tile < 12) stamp(4 + 2 * tile);
 
         // cross-warp reduction of the tile: last arriving warp sums the 16 partials in warp order
         const uint32_t slot = tile % RED_SLOTS;
@@ -315,6 +366,7 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
             }
         }
     }
+    stamp(31);
     if (!alive && lane == 0 && p.status) atomicOr(p.status, 2u);
 }
 
@@ -358,6 +410,9 @@ __global__ void __launch_bounds__(256) int4_linear_generic_kernel(const uint16_t
 
 }  // namespace
 
+unsigned long long* g_gemv_trace = nullptr;
+void set_int4_gemv_trace(unsigned long long* t) { g_gemv_trace = t; }
+
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
     return m >= 1 && m <= 8 && n >= 1 && group == 128 && k >= 1024 && k % 1024 == 0;
 }
@@ -387,6 +442,7 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     p.groups = k / 128;
     p.out_f32 = out_f32;
     p.status = status;
+    p.trace = g_gemv_trace;
     const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
     int4_gemv_kernel<<<grid, THREADS, SMEM_TOTAL, stream>>>(p);

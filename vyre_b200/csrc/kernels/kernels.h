@@ -10,6 +10,7 @@ namespace vybk {
 // ---- decode GEMV / skinny GEMM (int4_gemv.cu) ---------------------------------------------------------------
 // y[m,n] = cast( sum_k x[m,k] * (q[n,k]-8) * s[n,k/128] ), m <= 8, group 128, k % 1024 == 0.
 // out_dtype: 0 = bf16, 1 = f32. status: optional 4-word device buffer set non-zero when a bounded wait ran out.
+void set_int4_gemv_trace(unsigned long long* device_buffer);  // tuning aid: per-CTA timeline, nullptr = off
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
