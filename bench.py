@@ -155,16 +155,18 @@ def run_quick(args) -> None:
     m = args.m
     x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
     x = torch.from_numpy(x_np.view(np.int16)).cuda()
-    ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(COPIES)]
-    ss = [torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda() for c in range(COPIES)]
+    copies = max(1, args.copies)
+    ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(copies)]
+    ss = [torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda() for c in range(copies)]
     y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     stream = torch.cuda.current_stream().cuda_stream
 
     def launch(i: int):
-        c = i % COPIES
-        ffi.check(L.vyb_k_int4_gemv(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
-                                    GROUP, ffi.DT_BF16, C.c_void_p(stream), C.c_void_p(status.data_ptr())))
+        c = i % copies
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
+                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS, C.c_void_p(stream),
+                                       C.c_void_p(status.data_ptr())))
 
     for i in range(args.warmup):
         launch(i)
@@ -177,7 +179,7 @@ def run_quick(args) -> None:
     torch.cuda.synchronize()
     us = start.elapsed_time(end) * 1e3 / max(1, args.steps)
     assert status.cpu().tolist() == [0, 0, 0, 0]
-    print(json.dumps({"quick": True, "m": m, "steps": args.steps, "us_per_launch": us,
+    print(json.dumps({"quick": True, "m": m, "steps": args.steps, "copies": copies, "us_per_launch": us,
                       "gbs": algorithmic_bytes(m) / (us * 1e-6) / 1e9}))
 
 
@@ -214,8 +216,10 @@ def run_native(args) -> None:
     stream = torch.cuda.Stream()
 
     def launch(c: int):
-        ffi.check(L.vyb_k_int4_gemv(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
-                                    GROUP, ffi.DT_BF16, C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+        # weights are graph constants: the launch may overlap the tail of the previous one (see the header)
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
+                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
+                                       C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
 
     with torch.cuda.stream(stream):
         for c in range(COPIES):  # first launches configure the kernel; must precede graph capture
@@ -305,9 +309,9 @@ def run_native(args) -> None:
         with torch.cuda.stream(stream):
             with torch.cuda.graph(g2, stream=stream):
                 for c in range(COPIES):
-                    ffi.check(L.vyb_k_int4_gemv(xm.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), ym.data_ptr(), mm, N_OUT,
-                                                K_IN, GROUP, ffi.DT_BF16, C.c_void_p(stream.cuda_stream),
-                                                C.c_void_p(status.data_ptr())))
+                    ffi.check(L.vyb_k_int4_gemv_ex(xm.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), ym.data_ptr(), mm,
+                                                   N_OUT, K_IN, GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
+                                                   C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
             for _ in range(4):
                 g2.replay()
             ks.record(stream)
@@ -367,7 +371,7 @@ def run_native(args) -> None:
         "config": {"workload": f"int4 group-quantized decode GEMV M={m} N={N_OUT} K={K_IN} g={GROUP} (config 2)",
                    "per_gpu_shard": [N_OUT, K_IN], "parallelism": f"column-parallel x{world}" + (" + NCCL all-gather" if world > 1 else ""),
                    "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
-                   "launch": f"CUDA graph of {COPIES} launches"},
+                   "launch": f"CUDA graph of {COPIES} launches, programmatic dependent launch (constant weights)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "int4_gemv_kernel",
                      "us_per_launch": round(kernel_us, 3), "algorithmic_bytes_per_launch": bytes_per_step,
@@ -389,6 +393,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2000)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
+    ap.add_argument("--copies", type=int, default=COPIES,
+                    help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
     ap.add_argument("--quick", action="store_true",
                     help="kernel-only run without graphs, end-to-end leg or CPU baseline (the case profiled under ncu)")
     args = ap.parse_args()

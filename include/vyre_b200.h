@@ -399,6 +399,14 @@ void vyb_completion_free(vyb_completion* c);
 int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
                         uint32_t* status);
+/* Same with launch flags. VYB_LAUNCH_CONSTANT_WEIGHTS: w_packed and scale_bf16 are constants of the graph
+ * (ValueLifetime::Constant, vyre-libs/src/nn/model/dense_gated_mlp.rs:59-370), never written by a kernel that
+ * precedes this launch in the stream; the kernel is then launched with programmatic stream serialization and
+ * starts streaming them while the preceding kernel drains. Activations and outputs still wait for it. */
+#define VYB_LAUNCH_CONSTANT_WEIGHTS 1u
+int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                           uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,
+                           void* stream, uint32_t* status);
 /* C1: y f32 [m,n] = x f32 [m,k] . (int8 w[n,k] * s[n])^T */
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
                                       uint32_t m, uint32_t n, uint32_t k, void* stream);

@@ -817,10 +817,12 @@ void vyb_debug_set_int4_gemv_trace(void* device_buffer) {
     vybk::set_int4_gemv_trace(static_cast<unsigned long long*>(device_buffer));
 }
 
+void vyb_debug_set_int4_gemv_flags(uint32_t flags) { vybk::set_int4_gemv_debug(flags); }
+
 // ---- kernel-level entry points ----------------------------------------------------------------------------------------------
-int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
-                        uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
-                        uint32_t* status) {
+int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                           uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,
+                           void* stream, uint32_t* status) {
     if (!x_bf16 || !w_packed || !scale_bf16 || !y) return fail_invalid_program("Fix: pass non-null device pointers.");
     if (out_dtype != VYB_DT_BF16 && out_dtype != VYB_DT_F32)
         return fail_invalid_program("Fix: int4 gemv output dtype must be BF16 or F32.");
@@ -839,12 +841,18 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
         return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
     }
     e = vybk::launch_int4_gemv(x_bf16, w_packed, scale_bf16, y, m, n, k, out_dtype == VYB_DT_F32 ? 1u : 0u, sms,
-                               static_cast<cudaStream_t>(stream), status);
+                               static_cast<cudaStream_t>(stream), status, (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail_dispatch(int(e), "int4 gemv launch failed: " + cuda_msg(e));
     }
     return VYB_OK;
+}
+
+int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                        uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
+                        uint32_t* status) {
+    return vyb_k_int4_gemv_ex(x_bf16, w_packed, scale_bf16, y, m, n, k, group_size, out_dtype, 0, stream, status);
 }
 
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,

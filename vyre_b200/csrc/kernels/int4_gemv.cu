@@ -1,22 +1,32 @@
 // Decode GEMV / skinny GEMM for group-quantized int4 weights (batch <= 8 per pass), sm_100a.
 //
-//   y[m, n] = cast( sum_k x[m, k] * (q[n, k] - 8) * s[n, k / 128] )      f32 accumulate
+//   y[m, n] = cast( sum_k x[m, k] * (q[n, k] - 8) * s[n, k / 128] )
 //
-// The op is HBM-bound: 0.5 byte of weight per MAC and nothing is reused, so the design goal is to keep
-// ~35 KB of loads in flight per SM and to spend as few issue slots per weight as possible.
+// The op is HBM-bound (0.5 byte of weight per MAC, nothing reused), so the kernel is built around two
+// budgets: keep tens of KB of loads in flight per SM, and spend as few issue slots per weight as possible.
+// Integer/logic instructions run at half rate, and a bf16 dequantisation (shift, mask, or-magic, subtract
+// per nibble pair) costs more issue time per byte than HBM needs to deliver it, so the weights never become
+// floating point here.
 //
-//  * One persistent CTA per SM owns a contiguous row range of W (balanced to within one row).
-//  * A producer warp streams the range in 16-row x 4096-k stages with 1-D bulk TMA copies
-//    (cp.async.bulk, one 2 KB copy per row, one 64 B copy per row of scales) into a 4-stage shared-memory
-//    ring guarded by full/empty mbarriers: 4 x 35 KB in flight per SM, DRAM sees purely sequential streams.
-//    Row pitch in shared memory is 2048+64 B so that the 128-bit fragment loads below are bank-conflict free.
-//  * 16 consumer warps each own a fixed 256-k slice of the stage. The activation fragments for that slice
-//    live in registers for the whole kernel (32 regs), so shared memory is read exactly once per weight byte.
-//  * Dequantisation is two instructions per two weights: (w >> 4i) & 0x000F000F | 0x43004300 is the bf16 pair
-//    (128+q_lo, 128+q_hi), a packed bf16 subtract of 136 makes it (q_lo-8, q_hi-8) exactly, and the pair is
-//    fed straight into mma.sync.m16n8k16 (A = 16 weight rows, B = 8 batch columns, f32 accumulate). k is
-//    permuted identically on the A and B side, which a contraction allows. The group scale multiplies the
-//    f32 group result, so products are exact and only f32 accumulation rounds.
+//  * One persistent CTA per SM owns a contiguous row range of W (balanced to within one row) and streams it
+//    in 16-row x 4096-k stages through a 4-stage shared-memory ring guarded by full/empty mbarriers. When a
+//    k-block covers the whole row (k <= 4096) the 16 rows of a stage are contiguous in global memory and the
+//    stage is ONE 32 KB bulk TMA copy plus one for its scales (cp.async.bulk); per-copy issue cost is what
+//    limits a TMA producer, so few large copies matter. Longer rows fall back to one copy per row.
+//  * 16 warps each own a fixed 256-k slice of the stage. The activation fragments of that slice live in
+//    registers for the whole kernel, so shared memory is read exactly once per weight byte.
+//  * A packed word holds 8 nibbles. `(w & 0xF0F0F0F0) ^ 0x80808080` turns the four odd nibbles into the signed
+//    bytes 16*(q-8) (a nibble in the high half of a byte with its top bit flipped IS the two's-complement
+//    value scaled by 16); `((w << 4) & 0xF0F0F0F0) ^ 0x80808080` does the same for the even ones: 3 logic
+//    instructions per 8 weights, zero point included. Those bytes are the A operand of
+//    mma.sync.m16n8k32 (s8 x u8/s8, s32 accumulate). k is permuted identically on both operands.
+//  * The bf16 activations are converted once per kernel to block-floating integers: per (batch row, 128-k
+//    group) a power-of-two step delta = 2^(e_max - 8*LIMBS + 2) and X = rint(x / delta), split into LIMBS
+//    byte limbs (low limbs unsigned, top limb signed), each limb its own B operand. bf16 carries 8
+//    significant bits, so with LIMBS = 3 every element within 2^-16 of its group's maximum is represented
+//    exactly (f32 outputs); LIMBS = 2 keeps 16 bits per group (error <= 2^-16 of the group maximum per
+//    element, far inside the 1e-2 window of bf16 outputs). Integer accumulation is exact; per group the limb
+//    sums are recombined in f32 and scaled by s * delta / 16, the only place rounding happens.
 //  * Each warp leaves a 16x8 partial per tile in a shared slot; the last warp to arrive reduces the 16
 //    partials in fixed order (deterministic) and stores the outputs.
 //
@@ -37,21 +47,21 @@ namespace {
 
 constexpr int TILE_ROWS = 16;
 constexpr int KBLOCK = 4096;
-constexpr int CONSUMER_WARPS = 16;
-constexpr int WARP_K = KBLOCK / CONSUMER_WARPS;  // 256 = two 128-k groups
+constexpr int WARPS = 16;
+constexpr int WARP_K = KBLOCK / WARPS;  // 256 = two 128-k groups
 constexpr int STAGES = 4;
 constexpr int ROW_BYTES = KBLOCK / 2;
-constexpr int ROW_PITCH = ROW_BYTES + 64;
-constexpr int SCALE_ROW_BYTES = (KBLOCK / 128) * 2;
+constexpr int ROW_PITCH = ROW_BYTES + 64;  // padded pitch of the per-row copy path (conflict-free fragment loads)
 constexpr int SCALE_PITCH = 80;
 constexpr int STAGE_W_BYTES = TILE_ROWS * ROW_PITCH;
 constexpr int STAGE_S_BYTES = TILE_ROWS * SCALE_PITCH;
 constexpr int STAGE_BYTES = STAGE_W_BYTES + STAGE_S_BYTES;
 constexpr int RED_SLOTS = 2 * STAGES;
-constexpr int RED_SLOT_FLOATS = CONSUMER_WARPS * 128;
-constexpr int THREADS = (CONSUMER_WARPS + 1) * 32;
+constexpr int RED_SLOT_FLOATS = WARPS * 128;
+constexpr int THREADS = (WARPS + 1) * 32;  // 16 consumer warps + 1 producer warp
 constexpr int SMEM_RING = STAGES * STAGE_BYTES;
-constexpr int SMEM_RED = RED_SLOTS * RED_SLOT_FLOATS * 4;
+constexpr int X_PITCH = KBLOCK + 16;  // byte pitch of one staged activation row (keeps fragment reads conflict-free)
+constexpr int SMEM_RED = RED_SLOTS * RED_SLOT_FLOATS * 4 + 2048;  // reduction slots; doubles as X staging in the prologue
 constexpr int SMEM_CTRL = 256;
 constexpr int SMEM_TOTAL = SMEM_RING + SMEM_RED + SMEM_CTRL;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
@@ -63,7 +73,7 @@ static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
 struct Ctrl {
     unsigned long long full[STAGES];
     unsigned long long empty[STAGES];
-    unsigned int count[RED_SLOTS];
+    unsigned long long red_full[RED_SLOTS];  // 16 arrivals: every warp left its partial of the tile in the slot
     unsigned int abort_flag;
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL, "control block");
@@ -92,6 +102,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: false when the limit ran out or another warp already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile unsigned int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -105,21 +116,23 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
 }
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+// D(16x8, s32) += A(16x32, s8, row) * B(32x8, u8 or s8, col)
+template <bool B_SIGNED>
+__device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    if constexpr (B_SIGNED) {
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    } else {
+        asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+            : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+            : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
 }
-// bf16 pair (nibble i - 8, nibble i+4 - 8) of a packed word: the LOP3 builds (128+q) in both halves, the packed
-// subtract of 136 (0x4308) is exact
-__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int i) {
-    const uint32_t v = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
-    uint32_t r;
-    asm("sub.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(0x43084308u));
-    return r;
-}
+// signed bytes 16*(q-8) of the four even / odd nibbles of a packed word
+__device__ __forceinline__ uint32_t even_nibbles(uint32_t w) { return ((w << 4) & 0xF0F0F0F0u) ^ 0x80808080u; }
+__device__ __forceinline__ uint32_t odd_nibbles(uint32_t w) { return (w & 0xF0F0F0F0u) ^ 0x80808080u; }
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
 
@@ -129,11 +142,12 @@ struct Params {
     const uint16_t* scales;
     void* y;
     uint32_t m, n, k, groups;  // groups = k / 128
-    uint32_t out_f32;
     uint32_t* status;
-    unsigned long long* trace;  // optional: per-CTA timeline (64 slots each), for tuning only
+    unsigned long long* trace;  // optional: per-CTA timeline (64 slots each), tuning aid only
+    uint32_t debug;             // tuning aid: bit0 = skip the math, bit1 = split the tile copy in 4
 };
 
+template <int LIMBS, bool OUT_F32>
 __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* ring = smem;
@@ -144,231 +158,365 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     auto stamp = [&](int slot) {
-        if (p.trace && lane == 0 && (warp == 0 || warp == CONSUMER_WARPS)) {
+        if (p.trace && lane == 0 && (warp == 0 || warp == WARPS)) {
             unsigned long long t;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[size_t(blockIdx.x) * 64 + (warp == 0 ? 0 : 32) + slot] = t;
+            p.trace[size_t(blockIdx.x) * 64 + slot] = t;
         }
     };
     stamp(0);
-    const uint32_t r0 = uint32_t((uint64_t(blockIdx.x) * p.n) / gridDim.x);
-    const uint32_t r1 = uint32_t((uint64_t(blockIdx.x + 1) * p.n) / gridDim.x);
+    // Programmatic dependent launch: let the next kernel in the stream begin its own launch and weight prefetch
+    // now; it still waits (griddepcontrol.wait) before touching activations or outputs. No-ops for plain launches.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t rows_base = p.n / gridDim.x, rows_rem = p.n % gridDim.x;
+    const uint32_t r0 = blockIdx.x * rows_base + min(blockIdx.x, rows_rem);
+    const uint32_t r1 = r0 + rows_base + (blockIdx.x < rows_rem ? 1u : 0u);
     const uint32_t ntiles = (r1 - r0 + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t nkb = (p.k + KBLOCK - 1) / KBLOCK;
     const uint32_t units = ntiles * nkb;
     const uint32_t row_bytes = p.k / 2;
-    // When one k-block covers the whole row (k <= 4096) the rows of a tile are contiguous in global memory:
-    // the whole tile is ONE bulk copy (and its scales one more), laid out in shared memory with the global
-    // pitch. Otherwise each row needs its own copy and gets a padded, bank-conflict-free pitch.
+    // One k-block per row (k <= 4096): the rows of a tile are contiguous in global memory, the whole tile is
+    // one bulk copy laid out with the global pitch. Otherwise one copy per row into a padded pitch.
     const bool contiguous = nkb == 1;
     const uint32_t row_pitch = contiguous ? row_bytes : uint32_t(ROW_PITCH);
     const uint32_t scale_pitch = contiguous ? p.groups * 2 : uint32_t(SCALE_PITCH);
 
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&ctrl->full[s]), 1);
-            mbar_init(smem_u32(&ctrl->empty[s]), CONSUMER_WARPS);
-        }
-        for (int s = 0; s < RED_SLOTS; ++s) ctrl->count[s] = 0;
-        ctrl->abort_flag = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
-    stamp(1);
-
-    if (warp == CONSUMER_WARPS) {
-        // ------------------------------ producer warp ------------------------------
-        bool alive = true;
-        for (uint32_t u = 0; u < units && alive; ++u) {
-            const uint32_t s = u % STAGES;
-            if (u >= STAGES) alive = mbar_wait(smem_u32(&ctrl->empty[s]), ((u / STAGES) - 1) & 1, abort_flag);
-            alive = __all_sync(0xffffffffu, alive);
-            if (!alive) break;
-            const uint32_t tile = u / nkb, kb = u % nkb;
-            const uint32_t row_base = r0 + tile * TILE_ROWS;
-            const uint32_t rows_valid = min(uint32_t(TILE_ROWS), r1 - row_base);
-            const uint32_t kbytes = min(uint32_t(KBLOCK), p.k - kb * KBLOCK) / 2;
-            const uint32_t sbytes = min(uint32_t(KBLOCK / 128), p.groups - kb * (KBLOCK / 128)) * 2;
-            const uint32_t bar = smem_u32(&ctrl->full[s]);
-            if (u < 12) stamp(2 + u);
-            uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
-            if (contiguous) {
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
-                    bulk_g2s(smem_u32(stage), p.w + size_t(row_base) * row_bytes, rows_valid * kbytes, bar);
-                    bulk_g2s(smem_u32(stage + STAGE_W_BYTES), p.scales + size_t(row_base) * p.groups,
-                             rows_valid * sbytes, bar);
-                }
-            } else {
+    // Producer warp: fill the stage of unit u. Contiguous mode needs lane 0 only.
+    auto produce = [&](uint32_t u) {
+        const uint32_t s = u % STAGES;
+        const uint32_t tile = u / nkb, kb = u % nkb;
+        const uint32_t row_base = r0 + tile * TILE_ROWS;
+        const uint32_t rows_valid = min(uint32_t(TILE_ROWS), r1 - row_base);
+        const uint32_t kbytes = min(uint32_t(KBLOCK), p.k - kb * KBLOCK) / 2;
+        const uint32_t sbytes = min(uint32_t(KBLOCK / 128), p.groups - kb * (KBLOCK / 128)) * 2;
+        const uint32_t bar = smem_u32(&ctrl->full[s]);
+        uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
+        if (contiguous) {
+            if ((p.debug & 2u) && rows_valid == TILE_ROWS) {
                 if (lane == 0) mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
                 __syncwarp();
-                if (lane < TILE_ROWS) {
-                    if (uint32_t(lane) < rows_valid)
-                        bulk_g2s(smem_u32(stage + lane * ROW_PITCH),
-                                 p.w + size_t(row_base + lane) * row_bytes + size_t(kb) * ROW_BYTES, kbytes, bar);
-                } else {
-                    const uint32_t r = lane - TILE_ROWS;
-                    if (r < rows_valid)
-                        bulk_g2s(smem_u32(stage + STAGE_W_BYTES + r * SCALE_PITCH),
-                                 p.scales + size_t(row_base + r) * p.groups + size_t(kb) * (KBLOCK / 128), sbytes,
-                                 bar);
-                }
+                if (lane < 4)
+                    bulk_g2s(smem_u32(stage + lane * 4 * kbytes), p.w + size_t(row_base + lane * 4) * row_bytes, 4 * kbytes, bar);
+                if (lane == 4)
+                    bulk_g2s(smem_u32(stage + STAGE_W_BYTES), p.scales + size_t(row_base) * p.groups, rows_valid * sbytes, bar);
+                __syncwarp();
+            } else if (lane == 0) {
+                mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
+                bulk_g2s(smem_u32(stage), p.w + size_t(row_base) * row_bytes, rows_valid * kbytes, bar);
+                bulk_g2s(smem_u32(stage + STAGE_W_BYTES), p.scales + size_t(row_base) * p.groups, rows_valid * sbytes,
+                         bar);
+            }
+        } else {
+            if (lane == 0) mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
+            __syncwarp();
+            if (lane < TILE_ROWS) {
+                if (uint32_t(lane) < rows_valid)
+                    bulk_g2s(smem_u32(stage + lane * ROW_PITCH),
+                             p.w + size_t(row_base + lane) * row_bytes + size_t(kb) * ROW_BYTES, kbytes, bar);
+            } else {
+                const uint32_t r = lane - TILE_ROWS;
+                if (r < rows_valid)
+                    bulk_g2s(smem_u32(stage + STAGE_W_BYTES + r * SCALE_PITCH),
+                             p.scales + size_t(row_base + r) * p.groups + size_t(kb) * (KBLOCK / 128), sbytes, bar);
             }
             __syncwarp();
         }
-        if (!alive && lane == 0 && p.status) atomicOr(p.status, 1u);
-        return;
+    };
+
+    // Whole-row case: the activations are quantised ONCE per CTA, spread over all 512 threads (8 elements per
+    // thread per batch row), through a staging area that later becomes the reduction slots. Their loads are
+    // issued first of all: behind 140 KB of bulk weight traffic per SM they would wait microseconds.
+    const uint32_t stage_bytes_x = uint32_t(LIMBS) * p.m * X_PITCH;
+    const bool coop = nkb == 1 && stage_bytes_x + p.m * 32 * 4 <= uint32_t(SMEM_RED);
+    uint4 xv[8];
+    // activations may come from the preceding kernel: everything that reads x or writes y runs after this point,
+    // only the (constant) weight stream of the producer warp starts before it
+    if (warp != WARPS) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (coop) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            xv[j] = make_uint4(0, 0, 0, 0);
+            if (uint32_t(j) < p.m && threadIdx.x * 8 < p.k)
+                xv[j] = *reinterpret_cast<const uint4*>(p.x + size_t(j) * p.k + threadIdx.x * 8);
+        }
     }
 
-    // -------------------------------- consumer warps --------------------------------
-    const int g = lane >> 2;  // mma row group / batch column of the B fragment
+    if (warp == WARPS) {
+        // ------------------------------ producer warp ------------------------------
+        if (lane == 0) {
+            for (int s = 0; s < STAGES; ++s) {
+                mbar_init(smem_u32(&ctrl->full[s]), 1);
+                mbar_init(smem_u32(&ctrl->empty[s]), WARPS);
+            }
+            for (int s = 0; s < RED_SLOTS; ++s) mbar_init(smem_u32(&ctrl->red_full[s]), WARPS);
+            ctrl->abort_flag = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+        __syncwarp();
+        // tell the consumers the barriers exist (they wait on named barrier 2) and start streaming at once
+        asm volatile("bar.arrive 2, %0;" ::"n"(THREADS) : "memory");
+        bool ok = true;
+        for (uint32_t u = 0; u < units; ++u) {
+            if (u >= STAGES) ok = mbar_wait(smem_u32(&ctrl->empty[u % STAGES]), ((u / STAGES) - 1) & 1, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (u < 16) stamp(32 + u);
+            produce(u);
+            if (u < 16) stamp(48 + u);
+        }
+        if (!ok && lane == 0 && p.status) atomicOr(p.status, 2u);
+        return;
+    }
+    asm volatile("bar.sync 2, %0;" ::"n"(THREADS) : "memory");
+    stamp(1);
+
+    const int g = lane >> 2;  // mma row group; batch row of the B fragment
     const int t = lane & 3;
-    uint32_t xb[2][4][4];
+    // B fragments of this warp's 256-k slice: [group][limb][word][even|odd], and the per-(batch, group) step
+    uint32_t xb[2][LIMBS][4][2];
+    float dq[2][2];  // delta / 16 for the two batch columns (2t, 2t+1) of this lane's D fragment
 
     auto load_x = [&](uint32_t kb) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
+            uint4 v[4];
+            float amax = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < 4; ++wi) {
                 const uint32_t k0 = kb * KBLOCK + warp * WARP_K + c * 128 + t * 32 + wi * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (uint32_t(g) < p.m && k0 < p.k) v = *reinterpret_cast<const uint4*>(p.x + size_t(g) * p.k + k0);
-                xb[c][wi][0] = __byte_perm(v.x, v.z, 0x5410);  // (x0, x4)
-                xb[c][wi][1] = __byte_perm(v.x, v.z, 0x7632);  // (x1, x5)
-                xb[c][wi][2] = __byte_perm(v.y, v.w, 0x5410);  // (x2, x6)
-                xb[c][wi][3] = __byte_perm(v.y, v.w, 0x7632);  // (x3, x7)
+                v[wi] = make_uint4(0, 0, 0, 0);
+                if (uint32_t(g) < p.m && k0 < p.k) v[wi] = *reinterpret_cast<const uint4*>(p.x + size_t(g) * p.k + k0);
+                const uint32_t r[4] = {v[wi].x, v[wi].y, v[wi].z, v[wi].w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(r[j])), fabsf(bf16_hi(r[j]))));
             }
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            // power-of-two step: |x| / delta < 2^(8*LIMBS - 1); exponent clamped so that 1/delta stays finite
+            int e = int((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
+            e = max(e, -100);
+            const int de = e - (8 * LIMBS - 2);                                   // delta = 2^de
+            const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);    // 2^-de
+            float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);        // delta / 16
+            if (e > 127) delta16 = __uint_as_float(0x7FC00000u);  // Inf/NaN activations poison their batch row
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {
+                const uint32_t r[4] = {v[wi].x, v[wi].y, v[wi].z, v[wi].w};
+                int X[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    X[2 * j] = __float2int_rn(bf16_lo(r[j]) * inv_delta);
+                    X[2 * j + 1] = __float2int_rn(bf16_hi(r[j]) * inv_delta);
+                }
+#pragma unroll
+                for (int l = 0; l < LIMBS; ++l) {
+                    // byte limb l of each element; the top limb keeps the sign through the arithmetic shift
+                    auto limb = [&](int val) { return uint32_t(val >> (8 * l)) & 0xFFu; };
+                    xb[c][l][wi][0] = limb(X[0]) | (limb(X[2]) << 8) | (limb(X[4]) << 16) | (limb(X[6]) << 24);
+                    xb[c][l][wi][1] = limb(X[1]) | (limb(X[3]) << 8) | (limb(X[5]) << 16) | (limb(X[7]) << 24);
+                }
+            }
+            // this lane's D fragment holds batch columns 2t and 2t+1: fetch their steps from lanes 4*(2t), 4*(2t+1)
+            dq[c][0] = __shfl_sync(0xffffffffu, delta16, 4 * (2 * t));
+            dq[c][1] = __shfl_sync(0xffffffffu, delta16, 4 * (2 * t + 1));
         }
     };
-    if (nkb == 1) load_x(0);
+    // barrier over the 16 consumer warps only (the producer warp is busy feeding the ring)
+    auto consumer_sync = [] { asm volatile("bar.sync 1, %0;" ::"n"(WARPS * 32) : "memory"); };
+    if (coop) {
+        uint8_t* xs = reinterpret_cast<uint8_t*>(red);                    // [LIMBS][m][X_PITCH] limb bytes
+        float* dqs = reinterpret_cast<float*>(xs + stage_bytes_x);        // [m][32] delta / 16
+        const uint32_t k0 = threadIdx.x * 8;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (uint32_t(j) >= p.m) break;
+            const uint32_t r[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+            float amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fmaxf(fabsf(bf16_lo(r[i])), fabsf(bf16_hi(r[i]))));
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 lanes = 1 group
+            int e = int((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
+            e = max(e, -100);
+            const int de = e - (8 * LIMBS - 2);
+            const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);
+            float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);
+            if (e > 127) delta16 = __uint_as_float(0x7FC00000u);
+            int X[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                if constexpr (LIMBS == 2) {
+                    // |X| < 2^15: adding 1.5 * 2^23 leaves the rounded integer in the low mantissa bits
+                    X[2 * i] = __float_as_int(fmaf(bf16_lo(r[i]), inv_delta, 12582912.0f)) - 0x4B400000;
+                    X[2 * i + 1] = __float_as_int(fmaf(bf16_hi(r[i]), inv_delta, 12582912.0f)) - 0x4B400000;
+                } else {
+                    X[2 * i] = __float2int_rn(bf16_lo(r[i]) * inv_delta);
+                    X[2 * i + 1] = __float2int_rn(bf16_hi(r[i]) * inv_delta);
+                }
+            }
+#pragma unroll
+            for (int l = 0; l < LIMBS; ++l) {
+                auto limb = [&](int val) { return uint32_t(val >> (8 * l)) & 0xFFu; };
+                uint2 pk;
+                pk.x = limb(X[0]) | (limb(X[2]) << 8) | (limb(X[4]) << 16) | (limb(X[6]) << 24);
+                pk.y = limb(X[1]) | (limb(X[3]) << 8) | (limb(X[5]) << 16) | (limb(X[7]) << 24);
+                *reinterpret_cast<uint2*>(xs + (size_t(l) * p.m + j) * X_PITCH + k0) = pk;
+            }
+            if ((threadIdx.x & 15u) == 0) dqs[j * 32 + (threadIdx.x >> 4)] = delta16;
+        }
+        consumer_sync();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+            for (int l = 0; l < LIMBS; ++l) {
+                uint4 a = make_uint4(0, 0, 0, 0), b = make_uint4(0, 0, 0, 0);
+                if (uint32_t(g) < p.m) {
+                    const uint8_t* src = xs + (size_t(l) * p.m + g) * X_PITCH + warp * WARP_K + c * 128 + t * 32;
+                    a = *reinterpret_cast<const uint4*>(src);
+                    b = *reinterpret_cast<const uint4*>(src + 16);
+                }
+                xb[c][l][0][0] = a.x; xb[c][l][0][1] = a.y; xb[c][l][1][0] = a.z; xb[c][l][1][1] = a.w;
+                xb[c][l][2][0] = b.x; xb[c][l][2][1] = b.y; xb[c][l][3][0] = b.z; xb[c][l][3][1] = b.w;
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t col = 2 * t + j;
+                dq[c][j] = col < p.m ? dqs[col * 32 + warp * 2 + c] : 0.0f;
+            }
+        }
+        consumer_sync();  // the staging area is free again: it is the reduction slots from here on
+    } else if (nkb == 1) {
+        load_x(0);
+    }
     stamp(2);
 
-    // per-unit register image of this warp's slice of the stage: 2 x 16 B of each of the two fragment rows
-    // plus the two group scales of each row
-    struct Frag {
-        uint4 wl[2], wh[2];
-        uint32_t sc_lo, sc_hi;
+    // Register image of one 128-k group of this warp's slice: 16 B of each of the two fragment rows + 2 scales.
+    // The loop below keeps one half in flight from shared memory while it does the math of the other.
+    struct Half {
+        uint4 wl, wh;
+        uint32_t sc;  // bf16 scale of row g in the low half, of row g+8 in the high half
     };
-    auto fetch = [&](uint32_t u, Frag& f) -> bool {
-        const uint32_t s = u % STAGES;
-        bool ok = mbar_wait(smem_u32(&ctrl->full[s]), (u / STAGES) & 1, abort_flag);
+    auto wait_full = [&](uint32_t u) -> bool {
+        return mbar_wait(smem_u32(&ctrl->full[u % STAGES]), (u / STAGES) & 1, abort_flag);
+    };
+    auto load_half = [&](uint32_t u, int c, Half& h) {
+        const uint8_t* stage = ring + size_t(u % STAGES) * STAGE_BYTES;
+        const uint8_t* wrow = stage + g * row_pitch + warp * (WARP_K / 2) + c * 64 + t * 16;
+        h.wl = *reinterpret_cast<const uint4*>(wrow);
+        h.wh = *reinterpret_cast<const uint4*>(wrow + 8 * row_pitch);
+        const uint8_t* srow = stage + STAGE_W_BYTES + g * scale_pitch + (warp * 2 + c) * 2;
+        h.sc = uint32_t(*reinterpret_cast<const uint16_t*>(srow)) |
+               (uint32_t(*reinterpret_cast<const uint16_t*>(srow + 8 * scale_pitch)) << 16);
+    };
+    auto release = [&](uint32_t u) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->empty[u % STAGES]));
+    };
+    // one 128-k group: 4 words per row, two independent accumulator sets per limb (words 0-1 and 2-3)
+    auto math_half = [&](const Half& h, const uint32_t (&xg)[LIMBS][4][2], const float (&dqg)[2], float (&out)[4]) {
+        int acc[LIMBS][2][4];
+#pragma unroll
+        for (int l = 0; l < LIMBS; ++l)
+#pragma unroll
+            for (int q = 0; q < 2; ++q)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) acc[l][q][i] = 0;
+        const uint32_t lo[4] = {h.wl.x, h.wl.y, h.wl.z, h.wl.w};
+        const uint32_t hi[4] = {h.wh.x, h.wh.y, h.wh.z, h.wh.w};
+#pragma unroll
+        for (int wi = 0; wi < 4; ++wi) {
+            const uint32_t a0 = even_nibbles(lo[wi]), a1 = even_nibbles(hi[wi]);
+            const uint32_t a2 = odd_nibbles(lo[wi]), a3 = odd_nibbles(hi[wi]);
+#pragma unroll
+            for (int l = 0; l < LIMBS; ++l) {
+                if (l == LIMBS - 1)
+                    mma_s8<true>(acc[l][wi >> 1], a0, a1, a2, a3, xg[l][wi][0], xg[l][wi][1]);
+                else
+                    mma_s8<false>(acc[l][wi >> 1], a0, a1, a2, a3, xg[l][wi][0], xg[l][wi][1]);
+            }
+        }
+        const float s_lo = bf16_lo(h.sc), s_hi = bf16_hi(h.sc);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            // every limb sum is below 2^24 in magnitude, so the int -> float conversions are exact
+            float v = float(acc[LIMBS - 1][0][i] + acc[LIMBS - 1][1][i]);
+#pragma unroll
+            for (int l = LIMBS - 2; l >= 0; --l) v = fmaf(v, 256.0f, float(acc[l][0][i] + acc[l][1][i]));
+            out[i] = fmaf((i < 2 ? s_lo : s_hi) * dqg[i & 1], v, out[i]);
+        }
+    };
+
+    // sum the 16 partials of a finished tile and store its outputs (called by one designated warp per tile)
+    auto reduce_tile = [&](uint32_t tile) -> bool {
+        const uint32_t slot = tile % RED_SLOTS;
+        bool ok = mbar_wait(smem_u32(&ctrl->red_full[slot]), (tile / RED_SLOTS) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) return false;
-        const uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
-        const uint8_t* wrow_lo = stage + g * row_pitch + warp * (WARP_K / 2) + t * 16;
-        const uint8_t* wrow_hi = wrow_lo + 8 * row_pitch;
-        f.wl[0] = *reinterpret_cast<const uint4*>(wrow_lo);
-        f.wh[0] = *reinterpret_cast<const uint4*>(wrow_hi);
-        f.wl[1] = *reinterpret_cast<const uint4*>(wrow_lo + 64);
-        f.wh[1] = *reinterpret_cast<const uint4*>(wrow_hi + 64);
-        f.sc_lo = *reinterpret_cast<const uint32_t*>(stage + STAGE_W_BYTES + g * scale_pitch + warp * 4);
-        f.sc_hi = *reinterpret_cast<const uint32_t*>(stage + STAGE_W_BYTES + (g + 8) * scale_pitch + warp * 4);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctrl->empty[s]));
+        const float* slot_base = red + size_t(slot) * RED_SLOT_FLOATS;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float4 v = *reinterpret_cast<const float4*>(slot_base + w * 128 + lane * 4);
+            sum.x += v.x;
+            sum.y += v.y;
+            sum.z += v.z;
+            sum.w += v.w;
+        }
+        const uint32_t row_lo = r0 + tile * TILE_ROWS + g;
+        const float vals[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t row = i < 2 ? row_lo : row_lo + 8;
+            const uint32_t col = 2 * t + (i & 1);
+            if (row < r1 && col < p.m) {
+                if constexpr (OUT_F32)
+                    static_cast<float*>(p.y)[size_t(col) * p.n + row] = vals[i];
+                else
+                    static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(vals[i]);
+            }
+        }
         return true;
     };
 
-    Frag cur, nxt;
-    bool alive = units > 0 ? fetch(0, cur) : true;
-    for (uint32_t tile = 0; tile < ntiles && alive; ++tile) {
-        float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (uint32_t kb = 0; kb < nkb; ++kb) {
-            const uint32_t u = tile * nkb + kb;
-            if (nkb != 1) load_x(kb);
-            if (u < 12) stamp(3 + 2 * u);
-            // software pipeline: pull the next unit's fragments into registers before the math of this one
-            const bool have_next = u + 1 < units;
-            if (have_next && nkb == 1) {
-                alive = fetch(u + 1, nxt);
-                if (!alive) break;
-            }
-            if (kb * KBLOCK + warp * WARP_K < p.k) {
-#pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    // two independent accumulator chains per group keep the tensor pipe from waiting on itself
-                    float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    float acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    const uint32_t lo[4] = {cur.wl[c].x, cur.wl[c].y, cur.wl[c].z, cur.wl[c].w};
-                    const uint32_t hi[4] = {cur.wh[c].x, cur.wh[c].y, cur.wh[c].z, cur.wh[c].w};
-#pragma unroll
-                    for (int wi = 0; wi < 4; ++wi) {
-                        mma_bf16(acc0, nib_pair(lo[wi], 0), nib_pair(hi[wi], 0), nib_pair(lo[wi], 1), nib_pair(hi[wi], 1),
-                                 xb[c][wi][0], xb[c][wi][1]);
-                        mma_bf16(acc1, nib_pair(lo[wi], 2), nib_pair(hi[wi], 2), nib_pair(lo[wi], 3), nib_pair(hi[wi], 3),
-                                 xb[c][wi][2], xb[c][wi][3]);
-                    }
-                    const float s_lo = c == 0 ? bf16_lo(cur.sc_lo) : bf16_hi(cur.sc_lo);
-                    const float s_hi = c == 0 ? bf16_lo(cur.sc_hi) : bf16_hi(cur.sc_hi);
-                    out[0] = fmaf(s_lo, acc0[0] + acc1[0], out[0]);
-                    out[1] = fmaf(s_lo, acc0[1] + acc1[1], out[1]);
-                    out[2] = fmaf(s_hi, acc0[2] + acc1[2], out[2]);
-                    out[3] = fmaf(s_hi, acc0[3] + acc1[3], out[3]);
-                }
-            }
-            if (have_next) {
-                if (nkb == 1) {
-                    cur = nxt;
-                } else {
-                    alive = fetch(u + 1, cur);
-                    if (!alive) break;
-                }
-            }
+    Half ha, hb;
+    float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    bool alive = units == 0 || wait_full(0);
+    if (alive && units > 0) load_half(0, 0, ha);
+    for (uint32_t u = 0; u < units && alive; ++u) {
+        const uint32_t tile = u / nkb, kb = u - tile * nkb;
+        if (nkb != 1) load_x(kb);
+        if (u < 9) stamp(3 + 3 * u);
+        const bool active = kb * KBLOCK + warp * WARP_K < p.k;
+        load_half(u, 1, hb);
+        release(u);  // both halves of the unit have been read: the stage may be refilled while the math runs
+        if (active && !(p.debug & 1u)) math_half(ha, xb[0], dq[0], out);
+        if (u + 1 < units) {  // next unit's first half goes to registers behind the math of this unit's second
+            alive = wait_full(u + 1);
+            if (!alive) break;
+            load_half(u + 1, 0, ha);
         }
-        if (!alive) break;
-        if (tile < 12) stamp(4 + 2 * tile);
-
-        // cross-warp reduction of the tile: last arriving warp sums the 16 partials in warp order
-        const uint32_t slot = tile % RED_SLOTS;
-        float* slot_base = red + size_t(slot) * RED_SLOT_FLOATS;
-        *reinterpret_cast<float4*>(slot_base + warp * 128 + lane * 4) = make_float4(out[0], out[1], out[2], out[3]);
-        __threadfence_block();
-        __syncwarp();
-        unsigned int old = 0;
-        if (lane == 0) old = atomicAdd(&ctrl->count[slot], 1u);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        if (old == CONSUMER_WARPS - 1) {
-            __threadfence_block();
-            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int w = 0; w < CONSUMER_WARPS; ++w) {
-                const float4 v = *reinterpret_cast<const float4*>(slot_base + w * 128 + lane * 4);
-                sum.x += v.x;
-                sum.y += v.y;
-                sum.z += v.z;
-                sum.w += v.w;
-            }
+        if (u < 9) stamp(4 + 3 * u);
+        if (active && !(p.debug & 1u)) math_half(hb, xb[1], dq[1], out);
+        if (u < 9) stamp(5 + 3 * u);
+        if (kb + 1 == nkb) {
+            // cross-warp reduction of the tile: every warp leaves its 16x8 partial in the tile's slot and arrives
+            // on the slot barrier; warp (tile % 16) sums the slot one tile LATER, when the barrier has long
+            // completed, so nobody waits. Partials are added in warp order: deterministic.
+            const uint32_t slot = tile % RED_SLOTS;
+            *reinterpret_cast<float4*>(red + size_t(slot) * RED_SLOT_FLOATS + warp * 128 + lane * 4) =
+                make_float4(out[0], out[1], out[2], out[3]);
+            out[0] = out[1] = out[2] = out[3] = 0.0f;
             __syncwarp();
-            if (lane == 0) ctrl->count[slot] = 0;
-            const uint32_t row_lo = r0 + tile * TILE_ROWS + g;
-            const uint32_t row_hi = row_lo + 8;
-            const uint32_t n0 = 2 * t, n1 = 2 * t + 1;
-            if (p.out_f32) {
-                float* y = static_cast<float*>(p.y);
-                if (row_lo < r1) {
-                    if (n0 < p.m) y[size_t(n0) * p.n + row_lo] = sum.x;
-                    if (n1 < p.m) y[size_t(n1) * p.n + row_lo] = sum.y;
-                }
-                if (row_hi < r1) {
-                    if (n0 < p.m) y[size_t(n0) * p.n + row_hi] = sum.z;
-                    if (n1 < p.m) y[size_t(n1) * p.n + row_hi] = sum.w;
-                }
-            } else {
-                __nv_bfloat16* y = static_cast<__nv_bfloat16*>(p.y);
-                if (row_lo < r1) {
-                    if (n0 < p.m) y[size_t(n0) * p.n + row_lo] = __float2bfloat16_rn(sum.x);
-                    if (n1 < p.m) y[size_t(n1) * p.n + row_lo] = __float2bfloat16_rn(sum.y);
-                }
-                if (row_hi < r1) {
-                    if (n0 < p.m) y[size_t(n0) * p.n + row_hi] = __float2bfloat16_rn(sum.z);
-                    if (n1 < p.m) y[size_t(n1) * p.n + row_hi] = __float2bfloat16_rn(sum.w);
-                }
-            }
+            if (lane == 0) mbar_arrive(smem_u32(&ctrl->red_full[slot]));
+            if (tile > 0 && uint32_t(warp) == (tile - 1) % WARPS) alive = reduce_tile(tile - 1);
         }
     }
+    if (alive && ntiles > 0 && uint32_t(warp) == (ntiles - 1) % WARPS) alive = reduce_tile(ntiles - 1);
     stamp(31);
-    if (!alive && lane == 0 && p.status) atomicOr(p.status, 2u);
+    if (!alive && lane == 0 && p.status) atomicOr(p.status, 1u);
 }
+
 
 // ---- fallback: any group size dividing k, any batch; warp per output row, plain 32-bit loads -------------------
 __global__ void __launch_bounds__(256) int4_linear_generic_kernel(const uint16_t* __restrict__ x,
@@ -408,10 +556,13 @@ __global__ void __launch_bounds__(256) int4_linear_generic_kernel(const uint16_t
     }
 }
 
+unsigned long long* g_gemv_trace = nullptr;
+uint32_t g_gemv_debug = 0;
+
 }  // namespace
 
-unsigned long long* g_gemv_trace = nullptr;
 void set_int4_gemv_trace(unsigned long long* t) { g_gemv_trace = t; }
+void set_int4_gemv_debug(uint32_t flags) { g_gemv_debug = flags; }
 
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
     return m >= 1 && m <= 8 && n >= 1 && group == 128 && k >= 1024 && k % 1024 == 0;
@@ -419,7 +570,7 @@ bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
 
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                             uint32_t* status) {
+                             uint32_t* status, bool constant_weights) {
     // opt in to the large dynamic shared-memory carve-out once per device
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -427,7 +578,10 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     if (de != cudaSuccess) return de;
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        cudaError_t e = cudaFuncSetAttribute(int4_gemv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+        cudaError_t e = cudaFuncSetAttribute(int4_gemv_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_TOTAL);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(int4_gemv_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_release);
     }
@@ -440,13 +594,24 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     p.n = n;
     p.k = k;
     p.groups = k / 128;
-    p.out_f32 = out_f32;
     p.status = status;
     p.trace = g_gemv_trace;
+    p.debug = g_gemv_debug;
     const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
-    int4_gemv_kernel<<<grid, THREADS, SMEM_TOTAL, stream>>>(p);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    // with constant weights the launch may overlap the tail of the preceding kernel of the stream
+    cfg.attrs = &attr;
+    cfg.numAttrs = constant_weights ? 1 : 0;
+    if (out_f32) return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<3, true>, p);
+    return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<2, false>, p);
 }
 
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,
@@ -459,3 +624,4 @@ cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed,
 }
 
 }  // namespace vybk
+

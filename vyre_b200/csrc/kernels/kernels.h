@@ -11,10 +11,11 @@ namespace vybk {
 // y[m,n] = cast( sum_k x[m,k] * (q[n,k]-8) * s[n,k/128] ), m <= 8, group 128, k % 1024 == 0.
 // out_dtype: 0 = bf16, 1 = f32. status: optional 4-word device buffer set non-zero when a bounded wait ran out.
 void set_int4_gemv_trace(unsigned long long* device_buffer);  // tuning aid: per-CTA timeline, nullptr = off
+void set_int4_gemv_debug(uint32_t flags);                     // tuning aid: see int4_gemv.cu
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                             uint32_t* status);
+                             uint32_t* status, bool constant_weights = false);
 // any group size dividing k, k % 8 == 0, any m; plain loads, no TMA
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,
                                        uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32,

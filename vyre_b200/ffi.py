@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "_lib", "libvyre_b200.so")
 DT_U32, DT_I32, DT_F16, DT_BF16, DT_F32, DT_U8, DT_I8, DT_I4 = 0x01, 0x02, 0x09, 0x0A, 0x0B, 0x0E, 0x10, 0x1B
 ACCESS_READ_ONLY, ACCESS_READ_WRITE, ACCESS_OUTPUT, ACCESS_WORKGROUP = 0, 1, 2, 3
 BIND_HOST, BIND_RESIDENT = 0, 1
+LAUNCH_CONSTANT_WEIGHTS = 1
 
 ERR_DEVICE_OUT_OF_MEMORY = 1001
 ERR_UNSUPPORTED_FEATURE = 1002
@@ -158,6 +159,7 @@ _STATUS_FUNCS = {
     "vyb_completion_output": [_P, _U, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
     "vyb_completion_device_ns": [_P, C.POINTER(C.c_uint64)],
     "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_int4_gemv_ex": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int8_weight_only_linear": [_P, _P, _P, _P, _U, _U, _U, _P],
 }
 
