@@ -33,6 +33,9 @@ std::string cuda_msg(cudaError_t e) { return std::string(cudaGetErrorName(e)) + 
 }  // namespace
 
 struct vyb_device {
+    // The handle given to the caller owns one reference; every instance materialised on the device owns
+    // another, so an instance (or a completion) released after vyb_device_release never touches freed state.
+    std::atomic<int> refs{1};
     int ordinal = 0;
     cudaDeviceProp prop{};
     uint64_t owner = 0;
@@ -85,6 +88,7 @@ struct DeviceBuf {
 }  // namespace
 
 struct vyb_instance {
+    std::atomic<int> refs{1};  // the caller's handle + one per live submission / completion
     vyb_device* dev = nullptr;
     Program program;
     uint32_t variant = 0;
@@ -137,6 +141,29 @@ struct vyb_instance {
 };
 
 namespace {
+void device_unref(vyb_device* d) {
+    if (d && d->refs.fetch_sub(1) == 1) {
+        cudaSetDevice(d->ordinal);
+        for (auto& kv : d->residents) cudaFree(kv.second.ptr);
+        delete d;
+    }
+}
+void instance_unref(vyb_instance* i) {
+    if (!i || i->refs.fetch_sub(1) != 1) return;
+    cudaSetDevice(i->dev->ordinal);
+    if (i->stream) {
+        cudaStreamSynchronize(i->stream);
+        cudaStreamDestroy(i->stream);
+    }
+    for (auto& b : i->pinned) cudaFreeHost(b.ptr);
+    for (auto& b : i->temps) cudaFree(b.ptr);
+    if (i->scratch) cudaFree(i->scratch);
+    if (i->status_dev) cudaFree(i->status_dev);
+    if (i->status_host) cudaFreeHost(i->status_host);
+    device_unref(i->dev);
+    delete i;
+}
+
 struct OutputSlot {
     uint32_t value_id = 0;
     void* dev_ptr = nullptr;
@@ -346,11 +373,7 @@ int32_t vyb_device_reacquire(vyb_device* d) {
     return VYB_OK;
 }
 
-void vyb_device_release(vyb_device* d) {
-    if (!d) return;
-    for (auto& kv : d->residents) cudaFree(kv.second.ptr);
-    delete d;
-}
+void vyb_device_release(vyb_device* d) { device_unref(d); }
 
 // ---- resident buffers (vyre-driver-cuda/src/backend/resident.rs) -------------------------------------------------
 int32_t vyb_alloc(vyb_device* d, size_t byte_len, vyb_resident_handle* out) {
@@ -518,6 +541,7 @@ int32_t vyb_materialize(vyb_device* d, const vyb_artifact* artifact, const vyb_p
         return fail_dispatch(int(e), "status buffer allocation failed: " + cuda_msg(e));
     }
     std::memset(inst->status_host, 0, 16);
+    d->refs.fetch_add(1);
     *instance = inst.release();
     clear_error();
     return VYB_OK;
@@ -530,20 +554,7 @@ int32_t vyb_instance_device(const vyb_instance* i, vyb_device_identity* out) {
     *out = i->identity;
     return VYB_OK;
 }
-void vyb_instance_free(vyb_instance* i) {
-    if (!i) return;
-    cudaSetDevice(i->dev->ordinal);
-    if (i->stream) {
-        cudaStreamSynchronize(i->stream);
-        cudaStreamDestroy(i->stream);
-    }
-    for (auto& b : i->pinned) cudaFreeHost(b.ptr);
-    for (auto& b : i->temps) cudaFree(b.ptr);
-    if (i->scratch) cudaFree(i->scratch);
-    if (i->status_dev) cudaFree(i->status_dev);
-    if (i->status_host) cudaFreeHost(i->status_host);
-    delete i;
-}
+void vyb_instance_free(vyb_instance* i) { instance_unref(i); }
 
 // ---- submit (vyre-driver-cuda/src/materializer.rs:165-283) -------------------------------------------------------------
 int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const vyb_binding* bindings,
@@ -689,6 +700,7 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
     cudaEventCreate(&sub->end);
     cudaEventCreateWithFlags(&sub->done, cudaEventDisableTiming);
     cudaEventRecord(sub->start, inst->stream);
+    cudaGetLastError();  // a non-sticky error left by an unrelated earlier call must not be blamed on this launch
     cudaError_t e = dispatch(inst, slot_ptr, inst->stream);
     cudaEventRecord(sub->end, inst->stream);
     if (e != cudaSuccess) {
@@ -705,6 +717,7 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
         if (o.host) cudaMemcpyAsync(o.host, o.dev_ptr, o.len, cudaMemcpyDeviceToHost, inst->stream);
     cudaMemcpyAsync(inst->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
     cudaEventRecord(sub->done, inst->stream);
+    inst->refs.fetch_add(1);  // released by the completion (or by a failed wait)
     *submission = sub.release();
     clear_error();
     return VYB_OK;
@@ -756,6 +769,7 @@ int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion) {
         cudaGetLastError();
         release_outputs();
         delete s;
+        instance_unref(inst);
         const bool lost = e == cudaErrorIllegalAddress || e == cudaErrorLaunchFailure || e == cudaErrorHardwareStackError ||
                           e == cudaErrorIllegalInstruction || e == cudaErrorECCUncorrectable || e == cudaErrorDevicesUnavailable;
         if (lost) {
@@ -767,6 +781,7 @@ int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion) {
     if (status) {
         release_outputs();
         delete s;
+        instance_unref(inst);
         return fail_dispatch(int(status), "a bounded device-side wait ran out (kernel status word " +
                                               std::to_string(status) + "); the kernel drained without completing");
     }
@@ -809,6 +824,7 @@ void vyb_completion_free(vyb_completion* c) {
         for (auto& o : c->outputs)
             if (o.host) c->inst->release_pinned(o.host);
     }
+    instance_unref(c->inst);
     delete c;
 }
 
