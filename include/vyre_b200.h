@@ -411,6 +411,15 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
                                       uint32_t m, uint32_t n, uint32_t k, void* stream);
 
+/* Per-token symmetric int8 quantisation of bf16 rows: s_t = max|x_t| / 127, q = clamp(rint(x / s_t), -127, 127).
+ * No reference builder quantises activations; the rule is this backend's (see vyb_nn_linear_int8_dynamic). */
+int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scales_f32, uint32_t m, uint32_t k,
+                                      void* stream);
+/* out int32 [m,n] = a int8 [m,k] . w int8 [n,k]^T on tcgen05 (kind::i8, s32 accumulate in TMEM); the signed
+ * reading of the reference's wrapping-u32 Matmul (vyre-libs/src/math/linalg/matmul.rs:17-60). k % 16 == 0. */
+int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
+                            void* stream, uint32_t* status);
+
 #ifdef __cplusplus
 }
 #endif

@@ -33,6 +33,7 @@ SOURCES = {
     "kernels/ref_ops.cu": ["-ftz=true", "-prec-div=true", "-prec-sqrt=true", "-fmad=false"],
     "kernels/int4_gemv.cu": [],
     "kernels/int8_linear.cu": [],
+    "kernels/int8_gemm_tcgen05.cu": [],
 }
 
 

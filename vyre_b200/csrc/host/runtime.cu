@@ -260,6 +260,15 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             }
             return launch_int4_linear_generic(b[0], b[1], b[2], b[3], batch, n, k, group, out_f32, s);
         }
+        case OpKind::LinearInt8Dynamic: {
+            const uint32_t rows = u[0], k = u[1], n = u[2];
+            if (!int8_gemm_supported(rows, n, k)) return cudaErrorNotSupported;
+            int8_t* xq = static_cast<int8_t*>(inst->scratch);  // [rows, k] quantised activations
+            cudaError_t e = launch_quantize_per_token_int8(b[0], xq, (float*)b[2], rows, k, s);
+            if (e != cudaSuccess) return e;
+            return launch_int8_gemm(xq, (const int8_t*)b[1], (int32_t*)b[3], rows, n, k,
+                                    inst->dev->prop.multiProcessorCount, s, inst->status_dev);
+        }
         case OpKind::LinearInt8WeightOnly:
             return launch_int8_weight_only_linear((const float*)b[0], (const int8_t*)b[1], (const float*)b[2],
                                                   (float*)b[3], u[0], u[2], u[1], s);
@@ -270,13 +279,13 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
 size_t scratch_bytes_for(const Program& p) {
     switch (p.kind) {
         case OpKind::ExpertMlp: return size_t(p.params.u[1]) * 4;
+        case OpKind::LinearInt8Dynamic: return size_t(p.params.u[0]) * p.params.u[1];
         default: return 0;
     }
 }
 
 bool kind_supported(OpKind k) {
     switch (k) {
-        case OpKind::LinearInt8Dynamic:
         case OpKind::MoeFfnInt4: return false;
         default: return true;
     }
@@ -869,6 +878,43 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
                         uint32_t* status) {
     return vyb_k_int4_gemv_ex(x_bf16, w_packed, scale_bf16, y, m, n, k, group_size, out_dtype, 0, stream, status);
+}
+
+int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scales_f32, uint32_t m, uint32_t k,
+                                      void* stream) {
+    if (!x_bf16 || !q_i8 || !scales_f32) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (m == 0 || k == 0) return fail_invalid_program("Fix: per-token quantisation requires nonzero m and k.");
+    cudaError_t e = vybk::launch_quantize_per_token_int8(x_bf16, static_cast<int8_t*>(q_i8), static_cast<float*>(scales_f32),
+                                                         m, k, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "per-token quantisation launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
+}
+
+int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
+                            void* stream, uint32_t* status) {
+    if (!a_i8 || !w_i8 || !out_i32) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (!vybk::int8_gemm_supported(m, n, k))
+        return fail_unsupported("int8 gemm shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
+                                std::to_string(k) + " (needs k a multiple of 16 and at most 133000)");
+    if ((reinterpret_cast<uintptr_t>(a_i8) | reinterpret_cast<uintptr_t>(w_i8) | reinterpret_cast<uintptr_t>(out_i32)) & 15)
+        return fail_invalid_program("Fix: int8 gemm operands must be 16-byte aligned (TMA tensor maps need it).");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    e = vybk::launch_int8_gemm(static_cast<const int8_t*>(a_i8), static_cast<const int8_t*>(w_i8),
+                               static_cast<int32_t*>(out_i32), m, n, k, sms, static_cast<cudaStream_t>(stream), status);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "int8 gemm launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
 }
 
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,

@@ -25,6 +25,13 @@ cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed,
 cudaError_t launch_int8_weight_only_linear(const float* x, const int8_t* w, const float* scale, float* y, uint32_t m,
                                            uint32_t n, uint32_t k, cudaStream_t stream);
 
+// ---- int8 x int8 -> int32 GEMM on tcgen05 + per-token activation quantiser (int8_gemm_tcgen05.cu) --------------
+bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
+cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
+                             int sm_count, cudaStream_t stream, uint32_t* status);
+cudaError_t launch_quantize_per_token_int8(const void* x_bf16, int8_t* q, float* scales, uint32_t m, uint32_t k,
+                                           cudaStream_t stream);
+
 // ---- reference-shaped small ops (ref_ops.cu); each keeps the reference's evaluation order -----------------------
 cudaError_t launch_linear_4bit(const float* x, const uint32_t* w, const float* b, float* out, uint32_t in_dim,
                                uint32_t out_dim, cudaStream_t s);
