@@ -411,6 +411,12 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
                                       uint32_t m, uint32_t n, uint32_t k, void* stream);
 
+/* Prefill GEMM: y[m,n] = bf16|f32( sum_k x[m,k] * bf16((q[n,k]-8) * s[n,k/group]) ), weights dequantised to bf16
+ * tiles inside the kernel and contracted on tcgen05 (f32 accumulate in TMEM). Same operands and layout as
+ * vyb_k_int4_gemv, any m; k and group multiples of 64. */
+int32_t vyb_k_int4_prefill_gemm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
+                                uint32_t* status);
 /* Per-token symmetric int8 quantisation of bf16 rows: s_t = max|x_t| / 127, q = clamp(rint(x / s_t), -127, 127).
  * No reference builder quantises activations; the rule is this backend's (see vyb_nn_linear_int8_dynamic). */
 int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scales_f32, uint32_t m, uint32_t k,

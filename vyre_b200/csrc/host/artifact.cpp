@@ -80,9 +80,12 @@ uint32_t select_kernel_variant(const Program& p) {
     switch (p.kind) {
         case OpKind::LinearInt4GroupedRowmajor: {
             const uint32_t batch = p.params.u[0], in_dim = p.params.u[1], group = p.params.u[3];
-            const bool tma_ok = group == 128 && in_dim % 1024 == 0;
-            if (tma_ok && batch <= 64) return KV_INT4_GEMV_TMA;
-            if (tma_ok && in_dim % 64 == 0 && p.params.u[2] % 8 == 0) return KV_INT4_PREFILL_TCGEN05;
+            // decode batches stream the weights once per 8 rows; from 65 rows on the contraction is dense enough
+            // for the tensor-core path with in-kernel dequantisation
+            const bool gemv_ok = group == 128 && in_dim % 1024 == 0;
+            const bool prefill_ok = in_dim % 64 == 0 && group % 64 == 0 && in_dim % group == 0;
+            if (gemv_ok && (batch <= 64 || !prefill_ok)) return KV_INT4_GEMV_TMA;
+            if (prefill_ok && batch > 8) return KV_INT4_PREFILL_TCGEN05;
             return KV_GENERIC;
         }
         case OpKind::LinearInt8Dynamic: return KV_INT8_GEMM_TCGEN05;

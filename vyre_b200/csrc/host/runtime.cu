@@ -246,17 +246,18 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             const uint32_t batch = u[0], k = u[1], n = u[2], group = u[3];
             const uint32_t out_f32 = u[4] == VYB_DT_F32 ? 1u : 0u;
             const size_t out_elem = out_f32 ? 4 : 2;
-            if (inst->variant == KV_INT4_GEMV_TMA || inst->variant == KV_INT4_PREFILL_TCGEN05) {
-                if (int4_gemv_supported(std::min(batch, 8u), n, k, group)) {
-                    for (uint32_t b0 = 0; b0 < batch; b0 += 8) {
-                        const uint32_t mb = std::min(8u, batch - b0);
-                        cudaError_t e = launch_int4_gemv((const uint16_t*)b[0] + size_t(b0) * k, b[1], b[2],
-                                                         (uint8_t*)b[3] + size_t(b0) * n * out_elem, mb, n, k, out_f32,
-                                                         inst->dev->prop.multiProcessorCount, s, inst->status_dev);
-                        if (e != cudaSuccess) return e;
-                    }
-                    return cudaSuccess;
+            if (inst->variant == KV_INT4_PREFILL_TCGEN05 && int4_prefill_supported(batch, n, k, group))
+                return launch_int4_prefill(b[0], b[1], b[2], b[3], batch, n, k, group, out_f32,
+                                           inst->dev->prop.multiProcessorCount, s, inst->status_dev);
+            if (inst->variant == KV_INT4_GEMV_TMA && int4_gemv_supported(std::min(batch, 8u), n, k, group)) {
+                for (uint32_t b0 = 0; b0 < batch; b0 += 8) {
+                    const uint32_t mb = std::min(8u, batch - b0);
+                    cudaError_t e = launch_int4_gemv((const uint16_t*)b[0] + size_t(b0) * k, b[1], b[2],
+                                                     (uint8_t*)b[3] + size_t(b0) * n * out_elem, mb, n, k, out_f32,
+                                                     inst->dev->prop.multiProcessorCount, s, inst->status_dev);
+                    if (e != cudaSuccess) return e;
                 }
+                return cudaSuccess;
             }
             return launch_int4_linear_generic(b[0], b[1], b[2], b[3], batch, n, k, group, out_f32, s);
         }
@@ -878,6 +879,34 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
                         uint32_t* status) {
     return vyb_k_int4_gemv_ex(x_bf16, w_packed, scale_bf16, y, m, n, k, group_size, out_dtype, 0, stream, status);
+}
+
+int32_t vyb_k_int4_prefill_gemm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
+                                uint32_t* status) {
+    if (!x_bf16 || !w_packed || !scale_bf16 || !y) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (out_dtype != VYB_DT_BF16 && out_dtype != VYB_DT_F32)
+        return fail_invalid_program("Fix: int4 prefill output dtype must be BF16 or F32.");
+    if (!vybk::int4_prefill_supported(m, n, k, group_size))
+        return fail_unsupported("int4 prefill shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
+                                std::to_string(k) + " group=" + std::to_string(group_size) +
+                                " (needs k and group multiples of 64, group dividing k)");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(y)) & 15)
+        return fail_invalid_program("Fix: int4 prefill operands must be 16-byte aligned (TMA tensor maps need it).");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    e = vybk::launch_int4_prefill(x_bf16, w_packed, scale_bf16, y, m, n, k, group_size, out_dtype == VYB_DT_F32 ? 1u : 0u,
+                                  sms, static_cast<cudaStream_t>(stream), status);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "int4 prefill launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
 }
 
 int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scales_f32, uint32_t m, uint32_t k,

@@ -25,6 +25,12 @@ cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed,
 cudaError_t launch_int8_weight_only_linear(const float* x, const int8_t* w, const float* scale, float* y, uint32_t m,
                                            uint32_t n, uint32_t k, cudaStream_t stream);
 
+// ---- int4 prefill GEMM on tcgen05 with in-kernel dequantisation (int4_prefill_tcgen05.cu) -------------------------
+bool int4_prefill_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
+cudaError_t launch_int4_prefill(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32, int sm_count,
+                                cudaStream_t stream, uint32_t* status);
+
 // ---- int8 x int8 -> int32 GEMM on tcgen05 + per-token activation quantiser (int8_gemm_tcgen05.cu) --------------
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,

@@ -161,6 +161,7 @@ _STATUS_FUNCS = {
     "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int4_gemv_ex": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int8_weight_only_linear": [_P, _P, _P, _P, _U, _U, _U, _P],
+    "vyb_k_int4_prefill_gemm": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_quantize_per_token_int8": [_P, _P, _P, _U, _U, _P],
     "vyb_k_int8_gemm_i32": [_P, _P, _P, _U, _U, _U, _P, _P],
 }
