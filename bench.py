@@ -145,12 +145,58 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+def run_quick_gemm(args) -> None:
+    """A few plain launches of one of the tensor-core GEMMs (the cases profiled under ncu); one JSON line."""
+    import torch
+
+    from vyre_b200 import ffi
+
+    L = ffi.lib()
+    m, n, k = args.shape
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    if args.case == "prefill":
+        x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+        w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+        s = (torch.rand((n, k // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
+        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+
+        def launch():
+            ffi.check(L.vyb_k_int4_prefill_gemm(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), m, n, k, GROUP,
+                                                ffi.DT_BF16, stream, C.c_void_p(status.data_ptr())))
+        unit, scale = "TFLOP/s", 1e12
+    else:
+        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
+        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
+        y = torch.empty((m, n), dtype=torch.int32, device="cuda")
+
+        def launch():
+            ffi.check(L.vyb_k_int8_gemm_i32(a.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k, stream,
+                                            C.c_void_p(status.data_ptr())))
+        unit, scale = "TOP/s", 1e12
+    for _ in range(args.warmup):
+        launch()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(args.steps):
+        launch()
+    end.record()
+    torch.cuda.synchronize()
+    us = start.elapsed_time(end) * 1e3 / max(1, args.steps)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    print(json.dumps({"quick": True, "case": args.case, "shape": [m, n, k], "steps": args.steps, "us_per_launch": us,
+                      "rate": 2.0 * m * n * k / (us * 1e-6) / scale, "unit": unit}))
+
+
 def run_quick(args) -> None:
     """A few plain launches of the decode GEMV over rotating weight copies; prints one short JSON line."""
     import torch
 
     from vyre_b200 import ffi, synth
 
+    if args.case != "gemv":
+        return run_quick_gemm(args)
     L = ffi.lib()
     m = args.m
     x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
@@ -393,6 +439,10 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2000)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
+    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm"],
+                    help="kernel exercised by --quick")
+    ap.add_argument("--shape", type=int, nargs=3, default=[2048, 14336, 4096], metavar=("M", "N", "K"),
+                    help="GEMM shape for --quick --case prefill|int8gemm")
     ap.add_argument("--copies", type=int, default=COPIES,
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
     ap.add_argument("--quick", action="store_true",

@@ -225,14 +225,17 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             const uint32_t n0 = (tile / m_tiles) * BN;
             const bool row_valid = n0 + r < N;
             const uint16_t* srow = scales + size_t(row_valid ? n0 + r : 0) * groups;
+            // scales are read one group ahead: the load issued at a group change is consumed at the next one,
+            // so its latency hides behind a whole group of dequantisation instead of stalling every other stage
             uint32_t cur_group = 0xFFFFFFFFu, s2 = 0;
+            uint32_t s_next = row_valid ? uint32_t(srow[0]) : 0u;
             for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
                 const uint32_t s = it % STAGES;
                 const uint32_t g = (kb * BK) / group;
-                if (g != cur_group) {  // scale of this row's current group, broadcast to both bf16 halves
+                if (g != cur_group) {
                     cur_group = g;
-                    const uint32_t sv = (row_valid && g < groups) ? uint32_t(srow[g]) : 0u;
-                    s2 = sv | (sv << 16);
+                    s2 = s_next | (s_next << 16);  // this group's scale in both bf16 halves
+                    s_next = (row_valid && g + 1 < groups) ? uint32_t(srow[g + 1]) : 0u;
                 }
                 // the B tile of this stage must have been consumed by the MMAs of its previous use
                 if (it >= STAGES) ok = mbar_wait(smem_u32(&bars->empty[s]), ((it / STAGES) - 1) & 1, abort_flag);
