@@ -37,18 +37,23 @@ using namespace tc;
 
 constexpr int BM = 128, BN = 256, BK = 64;  // BK in bf16 elements (128 bytes per row)
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 3;
+// Three independent rings: the packed weights are prefetched deepest (they are small and come from HBM/L2), the
+// activation boxes next, and the dequantised tiles (the large ones) only need to cover dequant + MMA latency.
+constexpr int A_STAGES = 4, RAW_STAGES = 8, B_STAGES = 3;
+constexpr int RAW_AHEAD = 4;              // raw loads run this many stages ahead of the activation loads
 constexpr int A_BYTES = BM * BK * 2;      // 16 KB activations
 constexpr int B_BYTES = BN * BK * 2;      // 32 KB dequantised weights
 constexpr int RAW_BYTES = BN * (BK / 2);  // 8 KB packed weights
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES + RAW_BYTES;
+constexpr int B_RING = 0, A_RING = B_STAGES * B_BYTES, RAW_RING = A_RING + A_STAGES * A_BYTES;
+constexpr int RING_BYTES = RAW_RING + RAW_STAGES * RAW_BYTES;
 constexpr int DEQ_WARPS = 16;                 // two threads per weight row (32 k each)
 constexpr int THREADS = (6 + DEQ_WARPS) * 32;  // TMA, MMA, 4 epilogue, 16 dequant
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
 
 struct Bars {
-    unsigned long long tma_full[STAGES], b_full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+    unsigned long long a_full[A_STAGES], a_empty[A_STAGES], raw_full[RAW_STAGES], raw_empty[RAW_STAGES];
+    unsigned long long b_full[B_STAGES], b_empty[B_STAGES], acc_full[2], acc_empty[2];
     uint32_t tmem_base;
     unsigned int abort_flag;
 };
@@ -71,7 +76,7 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     uint32_t group, uint32_t* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    Bars* bars = reinterpret_cast<Bars*>(tiles + STAGES * STAGE_BYTES);
+    Bars* bars = reinterpret_cast<Bars*>(tiles + RING_BYTES);
     volatile unsigned int* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
@@ -79,10 +84,17 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     const uint32_t groups = K / group;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(smem_u32(&bars->tma_full[s]), 1);
+        for (int s = 0; s < A_STAGES; ++s) {
+            mbar_init(smem_u32(&bars->a_full[s]), 1);
+            mbar_init(smem_u32(&bars->a_empty[s]), 1);
+        }
+        for (int s = 0; s < RAW_STAGES; ++s) {
+            mbar_init(smem_u32(&bars->raw_full[s]), 1);
+            mbar_init(smem_u32(&bars->raw_empty[s]), DEQ_WARPS);
+        }
+        for (int s = 0; s < B_STAGES; ++s) {
             mbar_init(smem_u32(&bars->b_full[s]), DEQ_WARPS);
-            mbar_init(smem_u32(&bars->empty[s]), 1);
+            mbar_init(smem_u32(&bars->b_empty[s]), 1);
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bars->acc_full[a]), 1);
@@ -104,21 +116,40 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 
     if (warp == 0) {
         // ------------------------------------ TMA producer ------------------------------------
-        uint32_t it = 0;
+        // two cursors over the same (tile, k-block) sequence: the raw-weight cursor leads the activation cursor
+        uint32_t a_it = 0, r_it = 0, r_tile = blockIdx.x, r_kb = 0;
         bool ok = true;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m0 = int(tile % m_tiles) * BM, n0 = int(tile / m_tiles) * BN;
-            for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
-                const uint32_t s = it % STAGES;
-                if (it >= STAGES) ok = mbar_wait(smem_u32(&bars->empty[s]), ((it / STAGES) - 1) & 1, abort_flag);
+            const int m0 = int(tile % m_tiles) * BM;
+            for (uint32_t kb = 0; kb < k_blocks && ok; ++kb, ++a_it) {
+                while (ok && r_tile < total_tiles && r_it <= a_it + RAW_AHEAD) {
+                    const uint32_t rs = r_it % RAW_STAGES;
+                    if (r_it >= RAW_STAGES)
+                        ok = mbar_wait(smem_u32(&bars->raw_empty[rs]), ((r_it / RAW_STAGES) - 1) & 1, abort_flag);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    if (lane == 0) {
+                        const uint32_t bar = smem_u32(&bars->raw_full[rs]);
+                        mbar_arrive_expect_tx(bar, RAW_BYTES);
+                        tma_load_2d(smem_u32(tiles + RAW_RING + rs * RAW_BYTES), &map_w, int(r_kb * (BK / 2)),
+                                    int(r_tile / m_tiles) * BN, bar);
+                    }
+                    __syncwarp();
+                    ++r_it;
+                    if (++r_kb == k_blocks) {
+                        r_kb = 0;
+                        r_tile += gridDim.x;
+                    }
+                }
+                if (!ok) break;
+                const uint32_t as = a_it % A_STAGES;
+                if (a_it >= A_STAGES) ok = mbar_wait(smem_u32(&bars->a_empty[as]), ((a_it / A_STAGES) - 1) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (lane == 0) {
-                    const uint32_t bar = smem_u32(&bars->tma_full[s]);
-                    uint8_t* st = tiles + size_t(s) * STAGE_BYTES;
-                    mbar_arrive_expect_tx(bar, A_BYTES + RAW_BYTES);
-                    tma_load_2d(smem_u32(st), &map_x, int(kb * BK), m0, bar);
-                    tma_load_2d(smem_u32(st + A_BYTES + B_BYTES), &map_w, int(kb * (BK / 2)), n0, bar);
+                    const uint32_t bar = smem_u32(&bars->a_full[as]);
+                    mbar_arrive_expect_tx(bar, A_BYTES);
+                    tma_load_2d(smem_u32(tiles + A_RING + as * A_BYTES), &map_x, int(kb * BK), m0, bar);
                 }
                 __syncwarp();
             }
@@ -136,22 +167,21 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
             for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
-                const uint32_t s = it % STAGES;
-                const uint32_t par = (it / STAGES) & 1;
-                ok = mbar_wait(smem_u32(&bars->tma_full[s]), par, abort_flag) &&
-                     mbar_wait(smem_u32(&bars->b_full[s]), par, abort_flag);
+                const uint32_t as = it % A_STAGES, bs = it % B_STAGES;
+                ok = mbar_wait(smem_u32(&bars->a_full[as]), (it / A_STAGES) & 1, abort_flag) &&
+                     mbar_wait(smem_u32(&bars->b_full[bs]), (it / B_STAGES) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 tc_fence_after();
                 if (lane == 0) {
-                    const uint8_t* st = tiles + size_t(s) * STAGE_BYTES;
-                    const uint64_t da = smem_desc_sw128(smem_u32(st));
-                    const uint64_t db = smem_desc_sw128(smem_u32(st + A_BYTES));
+                    const uint64_t da = smem_desc_sw128(smem_u32(tiles + A_RING + as * A_BYTES));
+                    const uint64_t db = smem_desc_sw128(smem_u32(tiles + B_RING + bs * B_BYTES));
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
                         mma_f16(d_tmem, smem_desc_advance(da, k * UMMA_K * 2), smem_desc_advance(db, k * UMMA_K * 2), idesc,
                                 (kb | uint32_t(k)) != 0);
-                    tc_commit(smem_u32(&bars->empty[s]));
+                    tc_commit(smem_u32(&bars->a_empty[as]));
+                    tc_commit(smem_u32(&bars->b_empty[bs]));
                 }
                 __syncwarp();
             }
@@ -230,22 +260,21 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             uint32_t cur_group = 0xFFFFFFFFu, s2 = 0;
             uint32_t s_next = row_valid ? uint32_t(srow[0]) : 0u;
             for (uint32_t kb = 0; kb < k_blocks; ++kb, ++it) {
-                const uint32_t s = it % STAGES;
+                const uint32_t rs = it % RAW_STAGES, bs = it % B_STAGES;
                 const uint32_t g = (kb * BK) / group;
                 if (g != cur_group) {
                     cur_group = g;
                     s2 = s_next | (s_next << 16);  // this group's scale in both bf16 halves
                     s_next = (row_valid && g + 1 < groups) ? uint32_t(srow[g + 1]) : 0u;
                 }
-                // the B tile of this stage must have been consumed by the MMAs of its previous use
-                if (it >= STAGES) ok = mbar_wait(smem_u32(&bars->empty[s]), ((it / STAGES) - 1) & 1, abort_flag);
-                if (ok) ok = mbar_wait(smem_u32(&bars->tma_full[s]), (it / STAGES) & 1, abort_flag);
+                ok = mbar_wait(smem_u32(&bars->raw_full[rs]), (it / RAW_STAGES) & 1, abort_flag);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                uint8_t* st = tiles + size_t(s) * STAGE_BYTES;
-                const uint4 w0 = *reinterpret_cast<const uint4*>(st + A_BYTES + B_BYTES + r * (BK / 2) + half * 16);
+                const uint4 w0 = *reinterpret_cast<const uint4*>(tiles + RAW_RING + rs * RAW_BYTES + r * (BK / 2) + half * 16);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&bars->raw_empty[rs]));  // the packed bytes now live in registers
                 const uint32_t words[4] = {w0.x, w0.y, w0.z, w0.w};
-                uint8_t* brow = st + A_BYTES + r * 128;
+                uint4 o[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t w = words[j];
@@ -257,17 +286,24 @@ int4_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
                     t1 = bf16x2_mul(bf16x2_sub(t1, 0x43084308u), s2);
                     t2 = bf16x2_mul(bf16x2_sub(t2, 0x43084308u), s2);
                     t3 = bf16x2_mul(bf16x2_sub(t3, 0x43084308u), s2);
-                    uint4 o;
-                    o.x = __byte_perm(t0, t1, 0x5410);  // (k0, k1)
-                    o.y = __byte_perm(t2, t3, 0x5410);  // (k2, k3)
-                    o.z = __byte_perm(t0, t1, 0x7632);  // (k4, k5)
-                    o.w = __byte_perm(t2, t3, 0x7632);  // (k6, k7)
+                    o[j].x = __byte_perm(t0, t1, 0x5410);  // (k0, k1)
+                    o[j].y = __byte_perm(t2, t3, 0x5410);  // (k2, k3)
+                    o[j].z = __byte_perm(t0, t1, 0x7632);  // (k4, k5)
+                    o[j].w = __byte_perm(t2, t3, 0x7632);  // (k6, k7)
+                }
+                // the dequantised tile slot must have been consumed by the MMAs of its previous use
+                if (it >= B_STAGES) ok = mbar_wait(smem_u32(&bars->b_empty[bs]), ((it / B_STAGES) - 1) & 1, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                uint8_t* brow = tiles + B_RING + bs * B_BYTES + r * 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
                     const uint32_t chunk = half * 4 + uint32_t(j);
-                    *reinterpret_cast<uint4*>(brow + ((chunk ^ (r & 7u)) << 4)) = o;
+                    *reinterpret_cast<uint4*>(brow + ((chunk ^ (r & 7u)) << 4)) = o[j];
                 }
                 fence_proxy_async();  // make the generic-proxy stores visible to the tensor core's operand reads
                 __syncwarp();
-                if (lane == 0) mbar_arrive(smem_u32(&bars->b_full[s]));
+                if (lane == 0) mbar_arrive(smem_u32(&bars->b_full[bs]));
             }
         }
     }
