@@ -425,6 +425,15 @@ int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scal
  * reading of the reference's wrapping-u32 Matmul (vyre-libs/src/math/linalg/matmul.rs:17-60). k % 16 == 0. */
 int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
                             void* stream, uint32_t* status);
+/* No counterpart in the reference. vyb_k_quantize_per_token_int8 followed by vyb_k_int8_gemm_i32 (x_scale_f32 [m],
+ * y_i32 [m,n]) for callers that must not allocate device memory: the quantised activations go to a fixed 8 MiB
+ * device array that belongs to the loaded library, so m * k <= 8388608 (larger shapes are InvalidProgram). All
+ * calls on a device share that array: overlapping calls (two streams, two threads) race, so serialise them on
+ * one stream. The first call on each device looks the array's address up; make it during set-up, before any
+ * stream capture. */
+int32_t vyb_k_linear_int8_dynamic_static_scratch(const void* x_bf16, const void* w_i8, void* x_scale_f32, void* y_i32,
+                                                 uint32_t m, uint32_t n, uint32_t k, void* stream, uint32_t* status);
+#define VYB_STATIC_SCRATCH_BYTES 8388608u
 
 #ifdef __cplusplus
 }

@@ -38,6 +38,12 @@ cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uin
 cudaError_t launch_quantize_per_token_int8(const void* x_bf16, int8_t* q, float* scales, uint32_t m, uint32_t k,
                                            cudaStream_t stream);
 
+// ---- the same two kernels with the quantised activations in a fixed device array (int8_dynamic_static_scratch.cu)
+size_t int8_dynamic_static_scratch_limit();
+cudaError_t launch_int8_dynamic_static_scratch(const void* x_bf16, const int8_t* w, float* x_scale, int32_t* y,
+                                               uint32_t m, uint32_t n, uint32_t k, int sm_count, cudaStream_t stream,
+                                               uint32_t* status);
+
 // ---- reference-shaped small ops (ref_ops.cu); each keeps the reference's evaluation order -----------------------
 cudaError_t launch_linear_4bit(const float* x, const uint32_t* w, const float* b, float* out, uint32_t in_dim,
                                uint32_t out_dim, cudaStream_t s);
