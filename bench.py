@@ -145,6 +145,11 @@ def run_reference(args) -> None:
     print(json.dumps(line))
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of int4_gemv_kernel, from one ncu capture of the M=1
+# case over 8 rotating weight copies (summary kept under profiles/); other batches were not captured.
+NCU_DRAM_BYTES_PER_LAUNCH = {1: 30346368}
+
+
 def run_quick_gemm(args) -> None:
     """A few plain launches of one of the tensor-core GEMMs (the cases profiled under ncu); one JSON line."""
     import torch
@@ -419,7 +424,7 @@ def run_native(args) -> None:
                    "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
                    "launch": f"CUDA graph of {COPIES} launches, programmatic dependent launch (constant weights)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "int4_gemv_kernel",
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(m), "peak_kind": f"of {peak_kind}", "kernel": "int4_gemv_kernel",
                      "us_per_launch": round(kernel_us, 3), "algorithmic_bytes_per_launch": bytes_per_step,
                      "frac_of_nominal_8tbs": achieved / 8000.0},
         "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cpu_threads, "kind": "port", "sample": cpu_sample,
