@@ -327,6 +327,10 @@ bool int4_prefill_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) 
 cudaError_t launch_int4_prefill(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                 uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32, int sm_count,
                                 cudaStream_t stream, uint32_t* status) {
+    // above 128 rows the CTA-pair kernel (256-row tiles, half the dequantisation per SM) takes over
+    if (int4_gemm_pair_supported(m, n, k, group) && sm_count >= 2)
+        return launch_int4_gemm_pair(x_bf16, w_packed, scale_bf16, y, m, n, k, group, out_f32, 0, 1, nullptr, nullptr, n,
+                                     sm_count, stream, status);
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

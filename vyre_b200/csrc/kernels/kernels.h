@@ -31,6 +31,16 @@ cudaError_t launch_int4_prefill(const void* x_bf16, const void* w_packed, const 
                                 uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32, int sm_count,
                                 cudaStream_t stream, uint32_t* status);
 
+// ---- int4 GEMM on CTA pairs (int4_gemm_pair_tcgen05.cu): dense, grouped per expert, grouped + SwiGLU ---------------
+// plain: y[m, n] over weights [experts][n][k/2]; glu: h[m, n] = swiglu over weights [experts][2][n][k/2] (W1 then W3).
+// tile_expert / m_tiles_dev (device pointers, optional) describe 256-row tiles of an expert-sorted, 256-padded
+// activation buffer; without them every row uses expert 0.
+bool int4_gemm_pair_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
+cudaError_t launch_int4_gemm_pair(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                  uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32, uint32_t glu, uint32_t experts,
+                                  const uint32_t* tile_expert, const uint32_t* m_tiles_dev, uint32_t ldy, int sm_count,
+                                  cudaStream_t stream, uint32_t* status);
+
 // ---- int8 x int8 -> int32 GEMM on tcgen05 + per-token activation quantiser (int8_gemm_tcgen05.cu) --------------
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
