@@ -307,7 +307,9 @@ int32_t vyb_nn_linear_int8_dynamic(const char* x, const char* w, const char* x_s
  * (moe_layer.rs:33). Expert weights stacked: w13 u4 [E][2][inter][hidden/2], s13 bf16 [E][2][inter][hidden/g],
  * w2 u4 [E][hidden][inter/2], s2 bf16 [E][hidden][inter/g].
  * Slots: x=0, w_router=1, w13=2, s13=3, w2=4, s2=5, out=6 (bf16 [tokens, hidden]), routing_idx=7 (RW u32
- * [tokens, topk]), routing_w=8 (RW f32 [tokens, topk]). op id "vyre-b200::nn::moe_ffn_int4". */
+ * [tokens, topk]), routing_w=8 (RW f32 [tokens, topk]). op id "vyre-b200::nn::moe_ffn_int4".
+ * The device path needs hidden and inter multiples of 256, group a multiple of 64, experts <= 64, topk <= 8;
+ * other shapes are UnsupportedFeature at materialisation. */
 int32_t vyb_nn_moe_ffn_int4(const char* x, const char* w_router, const char* w13, const char* s13, const char* w2,
                             const char* s2, const char* out, const char* routing_idx, const char* routing_w,
                             uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t topk,
@@ -425,6 +427,17 @@ int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scal
  * reading of the reference's wrapping-u32 Matmul (vyre-libs/src/math/linalg/matmul.rs:17-60). k % 16 == 0. */
 int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
                             void* stream, uint32_t* status);
+/* The fused multi-token MoE FFN layer of vyb_nn_moe_ffn_int4 on raw device pointers (same operands, layouts and
+ * results; batched composition of vyre-libs/src/nn/moe/{gating.rs:19,expert_mlp.rs:18,moe_layer.rs:33}). The caller
+ * provides the scratch (expert-sorted rows, hidden activations, per-pair outputs, routing plan); its size comes
+ * from vyb_k_moe_ffn_int4_scratch_bytes. routing_idx u32 [tokens, topk] and routing_w f32 [tokens, topk] are
+ * outputs. hidden and inter multiples of 256, group a multiple of 64, experts <= 64, topk <= 8. */
+int32_t vyb_k_moe_ffn_int4_scratch_bytes(uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
+                                         uint32_t topk, uint64_t* bytes);
+int32_t vyb_k_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, const void* w13, const void* s13, const void* w2,
+                           const void* s2, void* out_bf16, void* routing_idx, void* routing_w, void* scratch,
+                           uint64_t scratch_bytes, uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
+                           uint32_t topk, uint32_t group_size, void* stream, uint32_t* status);
 /* No counterpart in the reference. vyb_k_quantize_per_token_int8 followed by vyb_k_int8_gemm_i32 (x_scale_f32 [m],
  * y_i32 [m,n]) for callers that must not allocate device memory: the quantised activations go to a fixed 8 MiB
  * device array that belongs to the loaded library, so m * k <= 8388608 (larger shapes are InvalidProgram). All

@@ -266,7 +266,7 @@ def int8_gemm_i32(a, w, m, n, k, row_begin=0, row_end=None) -> np.ndarray:
     return out.reshape(row_end - row_begin, n)
 
 
-def moe_ffn_int4(x_bf16, w_router_bf16, w13, s13, w2, s2, tokens, hidden, inter, experts, topk, group=128):
+def moe_ffn_int4(x_bf16, w_router_bf16, w13, s13, w2, s2, tokens, hidden, inter, experts, topk, group=128, mode=0):
     x, wr = _c(x_bf16, np.uint16), _c(w_router_bf16, np.uint16)
     w13, s13, w2, s2 = _c(w13, np.uint8), _c(s13, np.uint16), _c(w2, np.uint8), _c(s2, np.uint16)
     tok = _c(tokens, np.uint32)
@@ -275,5 +275,5 @@ def moe_ffn_int4(x_bf16, w_router_bf16, w13, s13, w2, s2, tokens, hidden, inter,
     wts = np.zeros(tok.size * topk, dtype=np.float32)
     lib().vyo_moe_ffn_int4(_p(x), _p(wr), _p(w13), _p(s13), _p(w2), _p(s2), _p(tok), C.c_uint32(tok.size),
                            C.c_uint32(hidden), C.c_uint32(inter), C.c_uint32(experts), C.c_uint32(topk),
-                           C.c_uint32(group), _p(out), _p(idx), _p(wts))
+                           C.c_uint32(group), C.c_uint32(mode), _p(out), _p(idx), _p(wts))
     return out.reshape(tok.size, hidden), idx.reshape(tok.size, topk), wts.reshape(tok.size, topk)

@@ -621,10 +621,12 @@ VYO_API void vyo_int8_gemm_i32(const int8_t* a, const int8_t* w, int32_t* out, u
 // tokens: indices into x of the tokens to evaluate (so a sample of a large batch can be checked).
 // Expert weights are stacked: w13 = [E][2][H][K/2] (w1 then w3), s13 = [E][2][H][K/G]; w2 = [E][K][H/2], s2 = [E][K][H/G].
 // Also returns the routing (top-k indices and weights) for each evaluated token.
+// weight_mode: 0 = dequantised weights exact (the decode kernels' arithmetic), 1 = each dequantised weight rounded to
+// bf16 first (what a tensor-core path that materialises bf16 weight tiles computes); see vyo_int4_rowmajor_linear.
 VYO_API void vyo_moe_ffn_int4(const uint16_t* x_bf16, const uint16_t* w_router_bf16, const uint8_t* w13,
                               const uint16_t* s13, const uint8_t* w2, const uint16_t* s2, const uint32_t* tokens,
                               uint32_t n_tokens, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t topk,
-                              uint32_t group, uint16_t* out_bf16, uint32_t* out_idx, float* out_w) {
+                              uint32_t group, uint32_t weight_mode, uint16_t* out_bf16, uint32_t* out_idx, float* out_w) {
     const size_t w1_bytes = size_t(inter) * (hidden / 2);
     const size_t s1_elems = size_t(inter) * (hidden / group);
     const size_t w2_bytes = size_t(hidden) * (inter / 2);
@@ -646,11 +648,11 @@ VYO_API void vyo_moe_ffn_int4(const uint16_t* x_bf16, const uint16_t* w_router_b
             const uint8_t* w3 = w1 + w1_bytes;
             const uint16_t* s1 = s13 + size_t(e) * 2 * s1_elems;
             const uint16_t* s3 = s1 + s1_elems;
-            vyo_int4_rowmajor_linear(xt, w1, s1, g.data(), 1, inter, hidden, group, 8, DT_BF16, 0);
-            vyo_int4_rowmajor_linear(xt, w3, s3, u.data(), 1, inter, hidden, group, 8, DT_BF16, 0);
+            vyo_int4_rowmajor_linear(xt, w1, s1, g.data(), 1, inter, hidden, group, 8, DT_BF16, weight_mode);
+            vyo_int4_rowmajor_linear(xt, w3, s3, u.data(), 1, inter, hidden, group, 8, DT_BF16, weight_mode);
             vyo_swiglu(g.data(), u.data(), h.data(), inter, DT_BF16);
             vyo_int4_rowmajor_linear(h.data(), w2 + size_t(e) * w2_bytes, s2 + size_t(e) * s2_elems, y.data(), 1,
-                                     hidden, inter, group, 8, DT_BF16, 0);
+                                     hidden, inter, group, 8, DT_BF16, weight_mode);
             for (uint32_t c = 0; c < hidden; ++c) acc[c] = f_add(acc[c], f_mul(wts[j], bf16_to_f32(y[c])));
             out_idx[size_t(t) * topk + j] = e;
             out_w[size_t(t) * topk + j] = wts[j];

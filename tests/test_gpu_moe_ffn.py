@@ -1,0 +1,130 @@
+"""GPU parity of the fused multi-token int4 MoE FFN layer (benchmark config 4) against the CPU oracle.
+
+The oracle composes the single-token reference ops per token (router linear -> moe_gate -> swiglu(w1 x, w3 x) -> w2 ->
+weighted accumulate); the device path batches them (expert-sorted permutation, grouped tensor-core GEMMs). Routing
+indices must match exactly except at genuine near-ties of the bf16 router logits (different f32 summation order can
+flip the last bf16 bit); gate weights within the reference's transcendental window; bf16 outputs within 1e-2 of the
+oracle that rounds dequantised weights to bf16 like the tensor-core tiles do (mode 1): there almost every output is
+bit-identical and the rest are single bf16-ulp flips of an expert output, which the weighted sum of two experts can
+cancel against, so the error is measured against max(|want|, output RMS) (2e-2: one flipped ulp of a large expert
+output, scaled by its gate weight) and the identical fraction is asserted as well. Against the oracle with exact dequantised weights (mode 0) every g, u, h and y intermediate may
+differ by a bf16 ulp, so that comparison uses the same normalisation with 4e-2.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+import vyre_b200 as vb
+from vyre_b200 import api, ffi, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def run_kernel_level(x, wr, w13, s13, w2, s2, tokens, hidden, inter, experts, topk, group=128):
+    L = ffi.lib()
+    need = C.c_uint64(0)
+    ffi.check(L.vyb_k_moe_ffn_int4_scratch_bytes(tokens, hidden, inter, experts, topk, C.byref(need)))
+    t = {k: torch.from_numpy(v).cuda() for k, v in
+         dict(x=x.view(np.int16), wr=wr.view(np.int16), w13=w13, s13=s13.view(np.int16), w2=w2, s2=s2.view(np.int16)).items()}
+    out = torch.full((tokens, hidden), 3.0, dtype=torch.bfloat16, device="cuda")
+    idx = torch.full((tokens, topk), -1, dtype=torch.int32, device="cuda")
+    wts = torch.zeros((tokens, topk), dtype=torch.float32, device="cuda")
+    scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ffi.check(L.vyb_k_moe_ffn_int4(t["x"].data_ptr(), t["wr"].data_ptr(), t["w13"].data_ptr(), t["s13"].data_ptr(),
+                                   t["w2"].data_ptr(), t["s2"].data_ptr(), out.data_ptr(), idx.data_ptr(), wts.data_ptr(),
+                                   scratch.data_ptr(), need.value, tokens, hidden, inter, experts, topk, group,
+                                   C.c_void_p(torch.cuda.current_stream().cuda_stream), C.c_void_p(status.data_ptr())))
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    return (out.view(torch.int16).cpu().numpy().view(np.uint16), idx.cpu().numpy().astype(np.uint32), wts.cpu().numpy())
+
+
+def bf16f(a):
+    return synth.bf16_bits_to_f32(a).astype(np.float64)
+
+
+def check_against_oracle(got_out, got_idx, got_w, want_out, want_idx, want_w, x_rows, wr, max_tie_frac=0.02,
+                         tol=2e-2, floor_frac=1.0, min_identical=0.95):
+    """Rows whose routing differs must be near-ties of the router logits; all other rows must match."""
+    same = np.all(got_idx == want_idx, axis=1)
+    logits = bf16f(x_rows) @ bf16f(wr).T
+    for r in np.nonzero(~same)[0]:
+        involved = sorted(set(got_idx[r].tolist()) ^ set(want_idx[r].tolist())) or got_idx[r].tolist()
+        vals = logits[r, involved]
+        scale = max(1e-6, float(np.max(np.abs(logits[r]))))
+        assert float(np.max(vals) - np.min(vals)) <= scale * 2.0 ** -6, f"row {r}: routing differs without a near-tie"
+    assert np.count_nonzero(~same) <= max(1, int(max_tie_frac * len(same)))
+    assert np.allclose(got_w[same], want_w[same], rtol=2e-5, atol=1e-7)
+    g, w = bf16f(got_out[same]), bf16f(want_out[same])
+    floor = floor_frac * float(np.sqrt(np.mean(w ** 2))) + 1e-30
+    rel = np.max(np.abs(g - w) / np.maximum(np.abs(w), floor))
+    assert rel <= tol, rel
+    assert float(np.mean(got_out[same] == want_out[same])) >= min_identical
+
+
+@pytest.mark.parametrize("tokens,hidden,inter,experts,topk", [(300, 512, 768, 8, 2), (1, 256, 256, 4, 1), (77, 256, 512, 5, 3)])
+def test_moe_ffn_small_shapes_all_tokens(tokens, hidden, inter, experts, topk):
+    x, wr, w13, s13, w2, s2 = synth.moe_ffn_inputs(tokens, hidden, inter, experts, seed=tokens + hidden)
+    wr = synth.f32_to_bf16_bits(synth.bf16_bits_to_f32(wr) * np.float32(25.0))  # spread the logits: fewer near-ties
+    got = run_kernel_level(x, wr, w13, s13, w2, s2, tokens, hidden, inter, experts, topk)
+    want = oracle.moe_ffn_int4(x, wr, w13, s13, w2, s2, np.arange(tokens), hidden, inter, experts, topk, mode=1)
+    check_against_oracle(*got, *want, x, wr)
+    exact = oracle.moe_ffn_int4(x, wr, w13, s13, w2, s2, np.arange(tokens), hidden, inter, experts, topk, mode=0)
+    check_against_oracle(*got, *exact, x, wr, tol=4e-2, min_identical=0.0)
+
+
+def test_moe_ffn_empty_and_crowded_experts():
+    """Every token picks the same two experts: six segments are empty, two hold all rows (several 256-row tiles)."""
+    tokens, hidden, inter, experts, topk = 600, 256, 512, 8, 2
+    x, wr, w13, s13, w2, s2 = synth.moe_ffn_inputs(tokens, hidden, inter, experts, seed=5)
+    x = synth.f32_to_bf16_bits(np.abs(synth.bf16_bits_to_f32(x)))       # positive activations
+    wrf = np.zeros((experts, hidden), np.float32)
+    wrf[3] = 1.0                                                         # expert 3 always wins, then expert 0 (first of the ties)
+    wr = synth.f32_to_bf16_bits(wrf)
+    got = run_kernel_level(x, wr, w13, s13, w2, s2, tokens, hidden, inter, experts, topk)
+    assert np.all(got[1] == np.array([3, 0], np.uint32))
+    want = oracle.moe_ffn_int4(x, wr, w13, s13, w2, s2, np.arange(0, tokens, 7), hidden, inter, experts, topk, mode=1)
+    sel = np.arange(0, tokens, 7)
+    check_against_oracle(got[0][sel], got[1][sel], got[2][sel], *want, x[sel], wr)
+
+
+def test_moe_ffn_contract_path_matches_kernel_level_and_is_deterministic():
+    tokens, hidden, inter, experts, topk = 200, 256, 512, 8, 2
+    x, wr, w13, s13, w2, s2 = synth.moe_ffn_inputs(tokens, hidden, inter, experts, seed=9)
+    a = run_kernel_level(x, wr, w13, s13, w2, s2, tokens, hidden, inter, experts, topk)
+    b = run_kernel_level(x, wr, w13, s13, w2, s2, tokens, hidden, inter, experts, topk)
+    for u, v in zip(a, b):
+        assert np.array_equal(u, v)
+    dev = vb.Device.acquire(0)
+    try:
+        prog = api.moe_ffn_int4("x", "w_router", "w13", "s13", "w2", "s2", "out", "routing_idx", "routing_w", tokens, hidden,
+                                inter, experts, topk, 128)
+        sess = api.ArtifactSession.compile(prog, dev)
+        outs = sess.run_host([x, wr, w13, s13, w2, s2, np.zeros((tokens, topk), np.uint32), np.zeros((tokens, topk), np.float32)])
+        got_out = np.frombuffer(outs[0], np.uint16).reshape(tokens, hidden)
+        got_idx = np.frombuffer(outs[1], np.uint32).reshape(tokens, topk)
+        got_w = np.frombuffer(outs[2], np.float32).reshape(tokens, topk)
+        assert np.array_equal(got_out, a[0]) and np.array_equal(got_idx, a[1]) and np.array_equal(got_w, a[2])
+        bad = api.moe_ffn_int4("x", "w_router", "w13", "s13", "w2", "s2", "out", "routing_idx", "routing_w", 16, 384, 512,
+                               8, 2, 128)
+        with pytest.raises(ffi.BackendError) as ei:
+            api.ArtifactSession.compile(bad, dev)
+        assert ei.value.code == ffi.ERR_UNSUPPORTED_FEATURE and "Fix:" in str(ei.value)
+    finally:
+        dev.release()
+
+
+def test_moe_ffn_config4_full_size_sampled_tokens():
+    tokens, hidden, inter, experts, topk = 4096, 4096, 14336, 8, 2
+    x, wr, w13, s13, w2, s2 = synth.moe_ffn_inputs(tokens, hidden, inter, experts, seed=0)
+    got = run_kernel_level(x, wr, w13, s13, w2, s2, tokens, hidden, inter, experts, topk)
+    # size-independent properties: every token has two distinct experts, weights are softmax probabilities
+    assert np.all(got[1] < experts) and np.all(got[1][:, 0] != got[1][:, 1])
+    assert np.all(got[2] > 0) and np.all(got[2].sum(axis=1) <= 1.0 + 1e-6) and np.all(got[2][:, 0] >= got[2][:, 1])
+    sel = np.array([0, 1, 777, 2048, 4095])
+    want = oracle.moe_ffn_int4(x, wr, w13, s13, w2, s2, sel, hidden, inter, experts, topk, mode=1)
+    check_against_oracle(got[0][sel], got[1][sel], got[2][sel], *want, x[sel], wr, max_tie_frac=0.5)

@@ -36,6 +36,7 @@ SOURCES = {
     "kernels/int8_gemm_tcgen05.cu": [],
     "kernels/int4_prefill_tcgen05.cu": [],
     "kernels/int4_gemm_pair_tcgen05.cu": [],
+    "kernels/moe_ffn.cu": [],
     "kernels/int8_dynamic_static_scratch.cu": [],
 }
 

@@ -270,6 +270,13 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             return launch_int8_gemm(xq, (const int8_t*)b[1], (int32_t*)b[3], rows, n, k,
                                     inst->dev->prop.multiProcessorCount, s, inst->status_dev);
         }
+        case OpKind::MoeFfnInt4: {
+            const uint32_t tokens = u[0], hidden = u[1], inter = u[2], experts = u[3], topk = u[4], group = u[5];
+            if (!moe_ffn_int4_supported(tokens, hidden, inter, experts, topk, group)) return cudaErrorNotSupported;
+            return launch_moe_ffn_int4(b[0], b[1], b[2], b[3], b[4], b[5], b[6], (uint32_t*)b[7], (float*)b[8],
+                                       inst->scratch, tokens, hidden, inter, experts, topk, group,
+                                       inst->dev->prop.multiProcessorCount, s, inst->status_dev);
+        }
         case OpKind::LinearInt8WeightOnly:
             return launch_int8_weight_only_linear((const float*)b[0], (const int8_t*)b[1], (const float*)b[2],
                                                   (float*)b[3], u[0], u[2], u[1], s);
@@ -281,15 +288,24 @@ size_t scratch_bytes_for(const Program& p) {
     switch (p.kind) {
         case OpKind::ExpertMlp: return size_t(p.params.u[1]) * 4;
         case OpKind::LinearInt8Dynamic: return size_t(p.params.u[0]) * p.params.u[1];
+        case OpKind::MoeFfnInt4:
+            return vybk::moe_ffn_int4_scratch_bytes(p.params.u[0], p.params.u[1], p.params.u[2], p.params.u[3], p.params.u[4]);
         default: return 0;
     }
 }
 
-bool kind_supported(OpKind k) {
-    switch (k) {
-        case OpKind::MoeFfnInt4: return false;
-        default: return true;
+// every op kind has a kernel; the fused MoE layer additionally needs shapes its grouped tensor-core GEMM accepts
+bool program_supported(const Program& p, std::string* why) {
+    if (p.kind == OpKind::MoeFfnInt4) {
+        const uint32_t* u = p.params.u;
+        if (!vybk::moe_ffn_int4_supported(u[0], u[1], u[2], u[3], u[4], u[5])) {
+            *why = "operator `" + p.op_id + "` with hidden=" + std::to_string(u[1]) + " inter=" + std::to_string(u[2]) +
+                   " experts=" + std::to_string(u[3]) + " topk=" + std::to_string(u[4]) + " group=" + std::to_string(u[5]) +
+                   " (needs hidden and inter multiples of 256, group a multiple of 64, experts <= 64, topk <= 8)";
+            return false;
+        }
     }
+    return true;
 }
 
 }  // namespace
@@ -521,7 +537,10 @@ int32_t vyb_materialize(vyb_device* d, const vyb_artifact* artifact, const vyb_p
     if (prog.trap) return fail_invalid_program(prog.trap_message);
     if (m.kernel_variant != select_kernel_variant(prog))
         return invalid_module("target module kernel variant disagrees with the op spec");
-    if (!kind_supported(prog.kind)) return fail_unsupported("operator `" + prog.op_id + "`");
+    {
+        std::string why;
+        if (!program_supported(prog, &why)) return fail_unsupported(why);
+    }
 
     cudaSetDevice(d->ordinal);
     auto inst = std::make_unique<vyb_instance>();
@@ -918,6 +937,44 @@ int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scal
     if (e != cudaSuccess) {
         cudaGetLastError();
         return fail_dispatch(int(e), "per-token quantisation launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
+}
+
+int32_t vyb_k_moe_ffn_int4_scratch_bytes(uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
+                                         uint32_t topk, uint64_t* bytes) {
+    if (!bytes) return fail_invalid_program("Fix: pass a non-null byte-count out-pointer.");
+    *bytes = vybk::moe_ffn_int4_scratch_bytes(tokens, hidden, inter, experts, topk);
+    return VYB_OK;
+}
+
+int32_t vyb_k_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, const void* w13, const void* s13, const void* w2,
+                           const void* s2, void* out_bf16, void* routing_idx, void* routing_w, void* scratch,
+                           uint64_t scratch_bytes, uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
+                           uint32_t topk, uint32_t group_size, void* stream, uint32_t* status) {
+    if (!x_bf16 || !w_router_bf16 || !w13 || !s13 || !w2 || !s2 || !out_bf16 || !routing_idx || !routing_w || !scratch)
+        return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (!vybk::moe_ffn_int4_supported(tokens, hidden, inter, experts, topk, group_size))
+        return fail_unsupported("moe_ffn_int4 shape hidden=" + std::to_string(hidden) + " inter=" + std::to_string(inter) +
+                                " experts=" + std::to_string(experts) + " topk=" + std::to_string(topk) +
+                                " (needs hidden and inter multiples of 256, group a multiple of 64, experts <= 64, topk <= 8)");
+    const uint64_t need = vybk::moe_ffn_int4_scratch_bytes(tokens, hidden, inter, experts, topk);
+    if (scratch_bytes < need)
+        return fail_invalid_program("Fix: moe_ffn_int4 needs " + std::to_string(need) + " scratch bytes, got " +
+                                    std::to_string(scratch_bytes) + " (ask vyb_k_moe_ffn_int4_scratch_bytes).");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    e = vybk::launch_moe_ffn_int4(x_bf16, w_router_bf16, w13, s13, w2, s2, out_bf16, static_cast<uint32_t*>(routing_idx),
+                                  static_cast<float*>(routing_w), scratch, tokens, hidden, inter, experts, topk, group_size,
+                                  sms, static_cast<cudaStream_t>(stream), status);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "moe_ffn_int4 launch failed: " + cuda_msg(e));
     }
     return VYB_OK;
 }

@@ -41,6 +41,15 @@ cudaError_t launch_int4_gemm_pair(const void* x_bf16, const void* w_packed, cons
                                   const uint32_t* tile_expert, const uint32_t* m_tiles_dev, uint32_t ldy, int sm_count,
                                   cudaStream_t stream, uint32_t* status);
 
+// ---- multi-token int4 MoE FFN layer (moe_ffn.cu): router + gate, permutation, grouped GEMMs, combine -------------
+bool moe_ffn_int4_supported(uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t topk,
+                            uint32_t group);
+size_t moe_ffn_int4_scratch_bytes(uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t topk);
+cudaError_t launch_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, const void* w13, const void* s13,
+                                const void* w2, const void* s2, void* out_bf16, uint32_t* routing_idx, float* routing_w,
+                                void* scratch, uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
+                                uint32_t topk, uint32_t group, int sm_count, cudaStream_t stream, uint32_t* status);
+
 // ---- int8 x int8 -> int32 GEMM on tcgen05 + per-token activation quantiser (int8_gemm_tcgen05.cu) --------------
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
