@@ -170,6 +170,29 @@ def run_quick_gemm(args) -> None:
             ffi.check(L.vyb_k_int4_prefill_gemm(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), m, n, k, GROUP,
                                                 ffi.DT_BF16, stream, C.c_void_p(status.data_ptr())))
         unit, scale = "TFLOP/s", 1e12
+    elif args.case == "moe":
+        # --shape TOKENS INTER HIDDEN; 8 experts, top-2 (config 4 is --shape 4096 14336 4096)
+        experts, topk = 8, 2
+        tokens, inter, hidden = m, n, k
+        x = torch.randn((tokens, hidden), device="cuda").to(torch.bfloat16)
+        wr = (torch.randn((experts, hidden), device="cuda") * 0.02).to(torch.bfloat16)
+        w13 = torch.randint(0, 256, (experts, 2, inter, hidden // 2), dtype=torch.uint8, device="cuda")
+        s13 = (torch.rand((experts, 2, inter, hidden // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
+        w2 = torch.randint(0, 256, (experts, hidden, inter // 2), dtype=torch.uint8, device="cuda")
+        s2 = (torch.rand((experts, hidden, inter // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
+        out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+        ridx = torch.empty((tokens, topk), dtype=torch.int32, device="cuda")
+        rw = torch.empty((tokens, topk), dtype=torch.float32, device="cuda")
+        need = C.c_uint64(0)
+        ffi.check(L.vyb_k_moe_ffn_int4_scratch_bytes(tokens, hidden, inter, experts, topk, C.byref(need)))
+        scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+
+        def launch():
+            ffi.check(L.vyb_k_moe_ffn_int4(x.data_ptr(), wr.data_ptr(), w13.data_ptr(), s13.data_ptr(), w2.data_ptr(),
+                                           s2.data_ptr(), out.data_ptr(), ridx.data_ptr(), rw.data_ptr(),
+                                           scratch.data_ptr(), need.value, tokens, hidden, inter, experts, topk, GROUP,
+                                           stream, C.c_void_p(status.data_ptr())))
+        unit, scale = "TFLOP/s", 1e12 / (3 * topk)  # 3 projections per (token, expert) pair: rate counts expert flops
     else:
         a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
         w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
@@ -190,8 +213,11 @@ def run_quick_gemm(args) -> None:
     torch.cuda.synchronize()
     us = start.elapsed_time(end) * 1e3 / max(1, args.steps)
     assert status.cpu().tolist() == [0, 0, 0, 0]
-    print(json.dumps({"quick": True, "case": args.case, "shape": [m, n, k], "steps": args.steps, "us_per_launch": us,
-                      "rate": 2.0 * m * n * k / (us * 1e-6) / scale, "unit": unit}))
+    line = {"quick": True, "case": args.case, "shape": [m, n, k], "steps": args.steps, "us_per_launch": us,
+            "rate": 2.0 * m * n * k / (us * 1e-6) / scale, "unit": unit}
+    if args.case == "moe":
+        line["tokens_per_s"] = m / (us * 1e-6)
+    print(json.dumps(line))
 
 
 def run_quick(args) -> None:
@@ -444,7 +470,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=2000)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
-    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm"],
+    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm", "moe"],
                     help="kernel exercised by --quick")
     ap.add_argument("--shape", type=int, nargs=3, default=[2048, 14336, 4096], metavar=("M", "N", "K"),
                     help="GEMM shape for --quick --case prefill|int8gemm")
