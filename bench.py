@@ -274,6 +274,9 @@ def run_native(args) -> None:
     if world > 1:
         import torch.distributed as dist  # noqa: PLW0642
 
+        # the collectives here move a few KB: in-switch reduction buys nothing, and without it no rank's memory is
+        # bound to an NVLink multicast object while the ranks leave one after the other
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     L = ffi.lib()
     m = args.m
@@ -351,10 +354,15 @@ def run_native(args) -> None:
     bytes_per_step = algorithmic_bytes(m)
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
 
+    # All ranks leave the process group together, right after the timed region: the captured graph holds NCCL work
+    # and must be gone before the communicator is; what follows on rank 0 is single-GPU work without collectives.
+    if dist:
+        del graph
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+        dist = None
     if rank != 0:
-        if dist:
-            dist.barrier()
-            dist.destroy_process_group()
         return
 
     # ---- kernel-only time of the dominant kernel (no collective), for the roofline --------------------------------
@@ -458,9 +466,6 @@ def run_native(args) -> None:
         "e2e": e2e, "gpu_launches": steps, "clocks": clocks, "other_batches": extra,
     }
     print(json.dumps(line))
-    if dist:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 def main() -> None:
