@@ -438,6 +438,23 @@ int32_t vyb_k_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, const 
                            const void* s2, void* out_bf16, void* routing_idx, void* routing_w, void* scratch,
                            uint64_t scratch_bytes, uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
                            uint32_t topk, uint32_t group_size, void* stream, uint32_t* status);
+/* The stages of that layer on their own, for expert-parallel runs that exchange rows between them (all-to-all):
+ *   vyb_k_moe_route         router linear + moe_gate per token (gating.rs:19): routing_idx u32 / routing_w f32 [tokens, topk]
+ *   vyb_k_rows_gather_bf16  dst[i,:] = src[index[i],:] for bf16 rows (row_elems % 8 == 0); index 0xFFFFFFFF gives a zero row
+ *   vyb_k_moe_experts_int4  swiglu(W1 x, W3 x) then W2 (expert_mlp.rs:18) for expert-sorted rows whose per-expert
+ *                           segments are padded to 256 rows: tile_expert[i] = expert of rows [256 i, 256 i + 256),
+ *                           *m_tiles = number of such tiles (both in device memory), h_scratch bf16 [max_rows, inter]
+ *   vyb_k_moe_combine       out[t,:] = bf16(sum_j routing_w[t,j] * y_rows[pos[t,j],:]) (moe_layer.rs:33) */
+int32_t vyb_k_moe_route(const void* x_bf16, const void* w_router_bf16, void* routing_idx, void* routing_w, uint32_t tokens,
+                        uint32_t hidden, uint32_t experts, uint32_t topk, void* stream);
+int32_t vyb_k_rows_gather_bf16(const void* src, const void* index_u32, void* dst, uint32_t rows, uint32_t row_elems,
+                               void* stream);
+int32_t vyb_k_moe_experts_int4(const void* x_sorted, const void* w13, const void* s13, const void* w2, const void* s2,
+                               void* y_rows, void* h_scratch, const void* tile_expert_u32, const void* m_tiles_u32,
+                               uint32_t max_rows, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t group_size,
+                               void* stream, uint32_t* status);
+int32_t vyb_k_moe_combine(const void* y_rows, const void* pos_u32, const void* routing_w, void* out_bf16, uint32_t tokens,
+                          uint32_t hidden, uint32_t topk, void* stream);
 /* No counterpart in the reference. vyb_k_quantize_per_token_int8 followed by vyb_k_int8_gemm_i32 (x_scale_f32 [m],
  * y_i32 [m,n]) for callers that must not allocate device memory: the quantised activations go to a fixed 8 MiB
  * device array that belongs to the loaded library, so m * k <= 8388608 (larger shapes are InvalidProgram). All

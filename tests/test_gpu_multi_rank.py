@@ -1,0 +1,111 @@
+"""Two ranks on two GPUs (NCCL): expert-parallel MoE FFN and column-parallel int8 linear against the single-GPU kernels.
+
+Skipped on a box with fewer than two GPUs. Each rank is a child process; results must be bit-identical to the
+single-GPU path because every output row is computed by the same kernel arithmetic wherever it is placed.
+"""
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, q):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch.distributed as dist
+
+    from vyre_b200 import ffi, sharding, synth
+
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    try:
+        L = ffi.lib()
+        stream = lambda: C.c_void_p(torch.cuda.current_stream().cuda_stream)  # noqa: E731
+        # ---- expert-parallel MoE FFN -------------------------------------------------------------------------
+        tokens, hidden, inter, experts, topk = 640, 512, 768, 8, 2
+        x, wr, w13, s13, w2, s2 = synth.moe_ffn_inputs(tokens, hidden, inter, experts, seed=11)
+        dev = lambda a: torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda()  # noqa: E731
+        tx, twr, tw13, ts13, tw2, ts2 = (dev(a) for a in (x, wr, w13, s13, w2, s2))
+        # single-GPU reference: the fused layer over all tokens
+        need = C.c_uint64(0)
+        ffi.check(L.vyb_k_moe_ffn_int4_scratch_bytes(tokens, hidden, inter, experts, topk, C.byref(need)))
+        ref_out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+        ref_idx = torch.empty((tokens, topk), dtype=torch.int32, device="cuda")
+        ref_w = torch.empty((tokens, topk), dtype=torch.float32, device="cuda")
+        scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        ffi.check(L.vyb_k_moe_ffn_int4(tx.data_ptr(), twr.data_ptr(), tw13.data_ptr(), ts13.data_ptr(), tw2.data_ptr(),
+                                       ts2.data_ptr(), ref_out.data_ptr(), ref_idx.data_ptr(), ref_w.data_ptr(),
+                                       scratch.data_ptr(), need.value, tokens, hidden, inter, experts, topk, 128, stream(),
+                                       C.c_void_p(status.data_ptr())))
+        torch.cuda.synchronize()
+        assert status.cpu().tolist() == [0, 0, 0, 0]
+        # expert-parallel: this rank's tokens and experts
+        local = experts // world
+        t0, t1 = rank * tokens // world, (rank + 1) * tokens // world
+        ops = sharding.KernelOps(tw13[rank * local:(rank + 1) * local].contiguous(), ts13[rank * local:(rank + 1) * local].contiguous(),
+                                 tw2[rank * local:(rank + 1) * local].contiguous(), ts2[rank * local:(rank + 1) * local].contiguous(),
+                                 hidden, inter, local)
+        out, idx, wts = sharding.expert_parallel_moe_ffn(tx[t0:t1].contiguous(), twr, ops, experts, topk)
+        torch.cuda.synchronize()
+        assert ops.status.cpu().tolist() == [0, 0, 0, 0]
+        assert torch.equal(idx, ref_idx[t0:t1]) and torch.equal(wts, ref_w[t0:t1])
+        assert torch.equal(out.view(torch.int16), ref_out[t0:t1].view(torch.int16))
+
+        # ---- column-parallel dynamic int8 linear + all-gather ----------------------------------------------------
+        m, n, k = 256, 1000, 512
+        g = torch.Generator().manual_seed(5)
+        xa = (torch.randn(m, k, generator=g) * 2).to(torch.bfloat16).cuda()
+        wa = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).cuda()
+
+        def int8_linear(w_rows):
+            xq = torch.empty((m, k), dtype=torch.int8, device="cuda")
+            sc = torch.empty(m, dtype=torch.float32, device="cuda")
+            y = torch.empty((m, w_rows.shape[0]), dtype=torch.int32, device="cuda")
+            ffi.check(L.vyb_k_quantize_per_token_int8(xa.data_ptr(), xq.data_ptr(), sc.data_ptr(), m, k, stream()))
+            ffi.check(L.vyb_k_int8_gemm_i32(xq.data_ptr(), w_rows.data_ptr(), y.data_ptr(), m, w_rows.shape[0], k, stream(),
+                                            C.c_void_p(status.data_ptr())))
+            return y
+
+        full = int8_linear(wa)
+        b, e = sharding.column_shard(n, world, rank, multiple=8)
+        gathered = sharding.all_gather_columns(int8_linear(wa[b:e].contiguous()), n)
+        torch.cuda.synchronize()
+        assert status.cpu().tolist() == [0, 0, 0, 0]
+        assert torch.equal(gathered, full)
+        q.put((rank, "ok"))
+    except Exception as exc:  # noqa: BLE001 - reported to the parent
+        import traceback
+
+        q.put((rank, f"{type(exc).__name__}: {exc}\n{traceback.format_exc()}"))
+    finally:
+        torch.cuda.synchronize()
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_and_column_parallel_match_single_gpu():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+    assert sorted(results) == [(0, "ok"), (1, "ok")], results

@@ -941,6 +941,75 @@ int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scal
     return VYB_OK;
 }
 
+namespace {
+int32_t current_sm_count(int* sms) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    return VYB_OK;
+}
+int32_t launch_result(cudaError_t e, const char* what) {
+    if (e == cudaErrorNotSupported) {
+        cudaGetLastError();
+        return fail_unsupported(std::string(what) + " with these dimensions");
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), std::string(what) + " launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
+}
+}  // namespace
+
+int32_t vyb_k_moe_route(const void* x_bf16, const void* w_router_bf16, void* routing_idx, void* routing_w, uint32_t tokens,
+                        uint32_t hidden, uint32_t experts, uint32_t topk, void* stream) {
+    if (!x_bf16 || !w_router_bf16 || !routing_idx || !routing_w) return fail_invalid_program("Fix: pass non-null device pointers.");
+    return launch_result(vybk::launch_moe_route(x_bf16, w_router_bf16, static_cast<uint32_t*>(routing_idx),
+                                                static_cast<float*>(routing_w), tokens, hidden, experts, topk,
+                                                static_cast<cudaStream_t>(stream)),
+                         "moe_route");
+}
+
+int32_t vyb_k_rows_gather_bf16(const void* src, const void* index_u32, void* dst, uint32_t rows, uint32_t row_elems,
+                               void* stream) {
+    if (rows && (!src || !index_u32 || !dst)) return fail_invalid_program("Fix: pass non-null device pointers.");
+    int sms = 0;
+    if (int32_t rc = current_sm_count(&sms)) return rc;
+    return launch_result(vybk::launch_rows_gather_bf16(src, static_cast<const uint32_t*>(index_u32), dst, rows, row_elems, sms,
+                                                       static_cast<cudaStream_t>(stream)),
+                         "rows_gather_bf16");
+}
+
+int32_t vyb_k_moe_experts_int4(const void* x_sorted, const void* w13, const void* s13, const void* w2, const void* s2,
+                               void* y_rows, void* h_scratch, const void* tile_expert_u32, const void* m_tiles_u32,
+                               uint32_t max_rows, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t group_size,
+                               void* stream, uint32_t* status) {
+    if (!x_sorted || !w13 || !s13 || !w2 || !s2 || !y_rows || !h_scratch || !tile_expert_u32 || !m_tiles_u32)
+        return fail_invalid_program("Fix: pass non-null device pointers.");
+    int sms = 0;
+    if (int32_t rc = current_sm_count(&sms)) return rc;
+    return launch_result(
+        vybk::launch_moe_experts_int4(x_sorted, w13, s13, w2, s2, y_rows, h_scratch, static_cast<const uint32_t*>(tile_expert_u32),
+                                      static_cast<const uint32_t*>(m_tiles_u32), max_rows, hidden, inter, experts, group_size,
+                                      sms, static_cast<cudaStream_t>(stream), status),
+        "moe_experts_int4");
+}
+
+int32_t vyb_k_moe_combine(const void* y_rows, const void* pos_u32, const void* routing_w, void* out_bf16, uint32_t tokens,
+                          uint32_t hidden, uint32_t topk, void* stream) {
+    if (tokens && (!y_rows || !pos_u32 || !routing_w || !out_bf16)) return fail_invalid_program("Fix: pass non-null device pointers.");
+    int sms = 0;
+    if (int32_t rc = current_sm_count(&sms)) return rc;
+    return launch_result(vybk::launch_moe_combine(y_rows, static_cast<const uint32_t*>(pos_u32),
+                                                  static_cast<const float*>(routing_w), out_bf16, tokens, hidden, topk, sms,
+                                                  static_cast<cudaStream_t>(stream)),
+                         "moe_combine");
+}
+
 int32_t vyb_k_moe_ffn_int4_scratch_bytes(uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
                                          uint32_t topk, uint64_t* bytes) {
     if (!bytes) return fail_invalid_program("Fix: pass a non-null byte-count out-pointer.");

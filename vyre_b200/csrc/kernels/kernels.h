@@ -50,6 +50,18 @@ cudaError_t launch_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, c
                                 void* scratch, uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
                                 uint32_t topk, uint32_t group, int sm_count, cudaStream_t stream, uint32_t* status);
 
+// the stages of the layer on their own (expert-parallel runs put an exchange between them)
+cudaError_t launch_moe_route(const void* x_bf16, const void* w_router_bf16, uint32_t* routing_idx, float* routing_w,
+                             uint32_t tokens, uint32_t hidden, uint32_t experts, uint32_t topk, cudaStream_t stream);
+cudaError_t launch_rows_gather_bf16(const void* src, const uint32_t* index, void* dst, uint32_t rows, uint32_t row_elems,
+                                    int sm_count, cudaStream_t stream);
+cudaError_t launch_moe_experts_int4(const void* x_sorted, const void* w13, const void* s13, const void* w2, const void* s2,
+                                    void* y_rows, void* h_scratch, const uint32_t* tile_expert, const uint32_t* m_tiles_dev,
+                                    uint32_t max_rows, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t group,
+                                    int sm_count, cudaStream_t stream, uint32_t* status);
+cudaError_t launch_moe_combine(const void* y_rows, const uint32_t* pos, const float* routing_w, void* out_bf16,
+                               uint32_t tokens, uint32_t hidden, uint32_t topk, int sm_count, cudaStream_t stream);
+
 // ---- int8 x int8 -> int32 GEMM on tcgen05 + per-token activation quantiser (int8_gemm_tcgen05.cu) --------------
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,

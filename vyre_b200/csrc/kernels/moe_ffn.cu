@@ -210,6 +210,23 @@ moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_t* __restrict__ 
     }
 }
 
+// ---- generic row gather: dst[i, :] = src[index[i], :], zeros where index[i] is the padding marker --------------------
+__global__ void __launch_bounds__(256)
+rows_gather_kernel(const uint16_t* __restrict__ src, const uint32_t* __restrict__ index, uint16_t* __restrict__ dst,
+                   uint32_t rows, uint32_t row_elems) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (uint32_t p = blockIdx.x * 8 + warp; p < rows; p += gridDim.x * 8) {
+        const uint32_t t = index[p];
+        uint4* d = reinterpret_cast<uint4*>(dst + size_t(p) * row_elems);
+        if (t == PAD_TOKEN) {
+            for (uint32_t c = lane; c < row_elems / 8; c += 32) d[c] = make_uint4(0, 0, 0, 0);
+        } else {
+            const uint4* sp = reinterpret_cast<const uint4*>(src + size_t(t) * row_elems);
+            for (uint32_t c = lane; c < row_elems / 8; c += 32) d[c] = sp[c];
+        }
+    }
+}
+
 size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
 
 struct Layout {
@@ -285,6 +302,50 @@ cudaError_t launch_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, c
     if (e != cudaSuccess) return e;
     moe_combine_kernel<<<sm_count * 4, 256, 0, stream>>>(y, pos, routing_w, static_cast<uint16_t*>(out_bf16), tokens,
                                                          hidden, topk);
+    return cudaGetLastError();
+}
+
+// ---- the stages on their own, for expert-parallel runs where an exchange sits between them ---------------------------
+cudaError_t launch_moe_route(const void* x_bf16, const void* w_router_bf16, uint32_t* routing_idx, float* routing_w,
+                             uint32_t tokens, uint32_t hidden, uint32_t experts, uint32_t topk, cudaStream_t stream) {
+    if (tokens == 0 || experts == 0 || experts > MAX_EXPERTS || topk == 0 || topk > MAX_TOPK || topk > experts || hidden % 8)
+        return cudaErrorNotSupported;
+    moe_router_gate_kernel<<<(tokens + 7) / 8, 256, 0, stream>>>(static_cast<const uint16_t*>(x_bf16),
+                                                                 static_cast<const uint16_t*>(w_router_bf16), routing_idx,
+                                                                 routing_w, tokens, hidden, experts, topk);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rows_gather_bf16(const void* src, const uint32_t* index, void* dst, uint32_t rows, uint32_t row_elems,
+                                    int sm_count, cudaStream_t stream) {
+    if (row_elems % 8) return cudaErrorNotSupported;
+    if (rows == 0) return cudaSuccess;
+    rows_gather_kernel<<<sm_count * 4, 256, 0, stream>>>(static_cast<const uint16_t*>(src), index,
+                                                         static_cast<uint16_t*>(dst), rows, row_elems);
+    return cudaGetLastError();
+}
+
+// rows: expert-sorted, every expert's segment padded to 256 rows; plan[0] = number of 256-row tiles (device word),
+// tile_expert[i] = local expert of tile i. h_scratch holds [max_rows, inter] bf16.
+cudaError_t launch_moe_experts_int4(const void* x_sorted, const void* w13, const void* s13, const void* w2, const void* s2,
+                                    void* y_rows, void* h_scratch, const uint32_t* tile_expert, const uint32_t* m_tiles_dev,
+                                    uint32_t max_rows, uint32_t hidden, uint32_t inter, uint32_t experts, uint32_t group,
+                                    int sm_count, cudaStream_t stream, uint32_t* status) {
+    if (max_rows == 0 || max_rows % ROW_TILE || !moe_ffn_int4_supported(1, hidden, inter, experts, 1, group))
+        return cudaErrorNotSupported;
+    cudaError_t e = launch_int4_gemm_pair(x_sorted, w13, s13, h_scratch, max_rows, inter, hidden, group, 0, 1, experts,
+                                          tile_expert, m_tiles_dev, inter, sm_count, stream, status);
+    if (e != cudaSuccess) return e;
+    return launch_int4_gemm_pair(h_scratch, w2, s2, y_rows, max_rows, hidden, inter, group, 0, 0, experts, tile_expert,
+                                 m_tiles_dev, hidden, sm_count, stream, status);
+}
+
+cudaError_t launch_moe_combine(const void* y_rows, const uint32_t* pos, const float* routing_w, void* out_bf16,
+                               uint32_t tokens, uint32_t hidden, uint32_t topk, int sm_count, cudaStream_t stream) {
+    if (hidden % 8 || topk == 0 || topk > MAX_TOPK) return cudaErrorNotSupported;
+    if (tokens == 0) return cudaSuccess;
+    moe_combine_kernel<<<sm_count * 4, 256, 0, stream>>>(static_cast<const uint16_t*>(y_rows), pos, routing_w,
+                                                         static_cast<uint16_t*>(out_bf16), tokens, hidden, topk);
     return cudaGetLastError();
 }
 

@@ -164,6 +164,10 @@ _STATUS_FUNCS = {
     "vyb_k_int4_prefill_gemm": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_quantize_per_token_int8": [_P, _P, _P, _U, _U, _P],
     "vyb_k_int8_gemm_i32": [_P, _P, _P, _U, _U, _U, _P, _P],
+    "vyb_k_moe_route": [_P, _P, _P, _P, _U, _U, _U, _U, _P],
+    "vyb_k_rows_gather_bf16": [_P, _P, _P, _U, _U, _P],
+    "vyb_k_moe_experts_int4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_moe_combine": [_P, _P, _P, _P, _U, _U, _U, _P],
     "vyb_k_moe_ffn_int4_scratch_bytes": [_U, _U, _U, _U, _U, _P],
     "vyb_k_moe_ffn_int4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.c_uint64, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_linear_int8_dynamic_static_scratch": [_P, _P, _P, _P, _U, _U, _U, _P, _P],

@@ -1,0 +1,250 @@
+"""Sharding of the quantized-linear / MoE path over the GPUs of one box (one process per GPU, torch.distributed).
+
+Two partitionings, both without any exchange inside a contraction:
+
+* column-parallel linear: every reference kernel computes one output element independently of the others
+  (vyre-libs/src/nn/linear/inner/linear_4bit.rs:710-742), so rank r owns rows [begin, end) of W and its scales,
+  x is replicated, and one all-gather assembles [m, n];
+* expert-parallel MoE: experts are independent programs with disjoint weights
+  (vyre-libs/src/nn/moe/expert_mlp.rs:18-150), routing is per token (vyre-libs/src/nn/moe/gating.rs:19-69) and the
+  combine is a per-token weighted sum (vyre-libs/src/nn/moe/moe_layer.rs:57-101): tokens are split over the ranks,
+  rows travel to the rank that owns their expert (all-to-all), come back (all-to-all) and are combined at home.
+
+The planning functions are pure numpy and the exchanges are plain torch.distributed calls, so they run under gloo
+on CPU as well as under NCCL; the compute stages are the library's CUDA kernels (`KernelOps`) and exist only there.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+
+PAD = 0xFFFFFFFF
+ROW_TILE = 256  # rows per CTA-pair tile of the grouped expert GEMM
+
+
+# ---- column-parallel linear ---------------------------------------------------------------------------------------
+def column_shard(n: int, world: int, rank: int, multiple: int = 1) -> tuple[int, int]:
+    """Rows [begin, end) of an n-row weight owned by `rank`; shard sizes are multiples of `multiple` except the last."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"rank {rank} is outside a world of {world}")
+    units = (n + multiple - 1) // multiple
+    per, extra = divmod(units, world)
+    begin_u = rank * per + min(rank, extra)
+    end_u = begin_u + per + (1 if rank < extra else 0)
+    return min(n, begin_u * multiple), min(n, end_u * multiple)
+
+
+def all_gather_columns(y_local, n_total: int, group=None):
+    """[m, n_local] per rank -> [m, n_total] on every rank (equal shards: one all_gather_into_tensor, then a column
+    interleave; ragged shards: all_gather of padded shards)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    m = y_local.shape[0]
+    bounds = [column_shard(n_total, world, r) for r in range(world)]
+    widest = max(e - b for b, e in bounds)
+    padded = y_local
+    if y_local.shape[1] != widest:
+        padded = torch.zeros((m, widest), dtype=y_local.dtype, device=y_local.device)
+        padded[:, : y_local.shape[1]] = y_local
+    staged = torch.empty((world, m, widest), dtype=y_local.dtype, device=y_local.device)
+    dist.all_gather_into_tensor(staged.view(-1), padded.contiguous().view(-1), group=group)
+    out = torch.empty((m, n_total), dtype=y_local.dtype, device=y_local.device)
+    for r, (b, e) in enumerate(bounds):
+        out[:, b:e] = staged[r, :, : e - b]
+    return out
+
+
+# ---- expert-parallel MoE: planning (numpy) ------------------------------------------------------------------------
+@dataclass
+class DispatchPlan:
+    send_order: np.ndarray     # [pairs] u32: token of each sent row; rows are sorted by global expert, token order kept
+    pos: np.ndarray            # [tokens, topk] u32: row of each (token, slot) pair in the send buffer
+    expert_counts: np.ndarray  # [experts] i64: rows per global expert
+    send_splits: list          # rows sent to each rank
+
+
+def plan_dispatch(idx: np.ndarray, experts: int, world: int) -> DispatchPlan:
+    if experts % world:
+        raise ValueError(f"{experts} experts do not divide over {world} ranks")
+    idx = np.ascontiguousarray(idx, dtype=np.int64)
+    tokens, topk = idx.shape
+    if idx.size and (idx.min() < 0 or idx.max() >= experts):
+        raise ValueError("routing index out of range")
+    flat = idx.reshape(-1)
+    order = np.argsort(flat, kind="stable")  # by expert, then by (token, slot)
+    pos = np.empty(flat.size, dtype=np.uint32)
+    pos[order] = np.arange(flat.size, dtype=np.uint32)
+    counts = np.bincount(flat, minlength=experts).astype(np.int64)
+    local = experts // world
+    splits = counts.reshape(world, local).sum(axis=1).tolist()
+    return DispatchPlan((order // topk).astype(np.uint32), pos.reshape(tokens, topk), counts, [int(v) for v in splits])
+
+
+@dataclass
+class RegroupPlan:
+    src_index: np.ndarray    # [max_rows] u32: received row feeding each padded expert-sorted row, PAD for padding rows
+    ret_index: np.ndarray    # [n_recv] u32: padded row that holds the result of each received row
+    tile_expert: np.ndarray  # [max_tiles] u32: local expert of each 256-row tile (first m_tiles entries are valid)
+    m_tiles: int
+    max_rows: int
+
+
+def plan_regroup(recv_counts: np.ndarray, max_rows: int | None = None, row_tile: int = ROW_TILE) -> RegroupPlan:
+    """recv_counts[r, e] = rows received from rank r for local expert e; received rows are ordered by (r, e)."""
+    rc = np.ascontiguousarray(recv_counts, dtype=np.int64)
+    world, local = rc.shape
+    n_recv = int(rc.sum())
+    per_expert = rc.sum(axis=0)
+    padded = (per_expert + row_tile - 1) // row_tile * row_tile
+    seg_start = np.concatenate([[0], np.cumsum(padded)])
+    need = int(seg_start[-1])
+    if max_rows is None:
+        max_rows = max(row_tile, need)
+    if need > max_rows:
+        raise ValueError(f"expert segments need {need} rows but the buffers hold {max_rows}")
+    src = np.full(max_rows, PAD, dtype=np.uint32)
+    ret = np.empty(n_recv, dtype=np.uint32)
+    recv_off = np.concatenate([[0], np.cumsum(rc.reshape(-1))])  # start of block (r, e) in the received order
+    fill = np.zeros(local, dtype=np.int64)
+    for r in range(world):
+        for e in range(local):
+            c = int(rc[r, e])
+            if c == 0:
+                continue
+            a = int(recv_off[r * local + e])
+            d = int(seg_start[e] + fill[e])
+            src[d:d + c] = np.arange(a, a + c, dtype=np.uint32)
+            ret[a:a + c] = np.arange(d, d + c, dtype=np.uint32)
+            fill[e] += c
+    tiles = np.zeros(max_rows // row_tile, dtype=np.uint32)
+    m_tiles = need // row_tile
+    t = 0
+    for e in range(local):
+        k = int(padded[e] // row_tile)
+        tiles[t:t + k] = e
+        t += k
+    return RegroupPlan(src, ret, tiles, m_tiles, max_rows)
+
+
+# ---- exchanges (torch.distributed; gloo on CPU, NCCL on GPU) -------------------------------------------------------
+def exchange_counts(expert_counts: np.ndarray, world: int, device, group=None) -> np.ndarray:
+    """Every rank tells every other how many rows it sends for each of that rank's local experts.
+    Returns recv_counts [world, local_experts] on the host (the row exchange needs the split sizes there)."""
+    import torch
+    import torch.distributed as dist
+
+    send = torch.as_tensor(np.ascontiguousarray(expert_counts, dtype=np.int64), device=device)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.cpu().numpy().reshape(world, -1)
+
+
+def exchange_rows(rows, send_splits, recv_splits, group=None):
+    import torch
+    import torch.distributed as dist
+
+    out = torch.empty((int(sum(recv_splits)),) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=[int(v) for v in recv_splits],
+                           input_split_sizes=[int(v) for v in send_splits], group=group)
+    return out
+
+
+def expert_parallel_layer(x, idx_host: np.ndarray, wts, experts: int, ops, group=None, max_rows: int | None = None):
+    """One MoE FFN layer over the ranks of `group`, given this rank's tokens x [tokens, hidden] and their routing.
+
+    ops supplies the compute stages: gather(src, index_u32_numpy) -> rows, experts(rows_sorted, RegroupPlan) -> rows,
+    combine(y_rows, pos_numpy, wts) -> out. Returns out [tokens, hidden].
+    """
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    plan = plan_dispatch(idx_host, experts, world)
+    recv_counts = exchange_counts(plan.expert_counts, world, x.device, group)
+    recv_splits = recv_counts.sum(axis=1).tolist()
+    sent = ops.gather(x, plan.send_order)
+    received = exchange_rows(sent, plan.send_splits, recv_splits, group)
+    regroup = plan_regroup(recv_counts, max_rows)
+    sorted_rows = ops.gather(received, regroup.src_index)
+    y_sorted = ops.experts(sorted_rows, regroup)
+    y_received = ops.gather(y_sorted, regroup.ret_index)
+    y_home = exchange_rows(y_received, recv_splits, plan.send_splits, group)
+    return ops.combine(y_home, plan.pos, wts)
+
+
+# ---- compute stages on the device (C-ABI kernels; there is no CPU implementation) ---------------------------------
+class KernelOps:
+    """gather / experts / combine through the library's kernel-level entry points, for bf16 rows on the current device."""
+
+    def __init__(self, w13, s13, w2, s2, hidden: int, inter: int, local_experts: int, group_size: int = 128):
+        import torch
+
+        from . import ffi
+
+        self.ffi, self.lib, self.torch = ffi, ffi.lib(), torch
+        self.w13, self.s13, self.w2, self.s2 = w13, s13, w2, s2
+        self.hidden, self.inter, self.local_experts, self.group_size = hidden, inter, local_experts, group_size
+        self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self._h = None
+
+    def _stream(self):
+        return C.c_void_p(self.torch.cuda.current_stream().cuda_stream)
+
+    def _u32(self, a: np.ndarray):
+        return self.torch.from_numpy(np.ascontiguousarray(a, dtype=np.uint32).view(np.int32)).cuda()
+
+    def gather(self, src, index: np.ndarray):
+        torch = self.torch
+        rows = int(index.size)
+        dst = torch.empty((rows, src.shape[1]), dtype=src.dtype, device="cuda")
+        if rows:
+            ix = self._u32(index)
+            self.ffi.check(self.lib.vyb_k_rows_gather_bf16(src.data_ptr(), ix.data_ptr(), dst.data_ptr(), rows, src.shape[1],
+                                                           self._stream()))
+        return dst
+
+    def experts(self, rows_sorted, plan: RegroupPlan):
+        torch = self.torch
+        y = torch.empty((plan.max_rows, self.hidden), dtype=torch.bfloat16, device="cuda")
+        if self._h is None or self._h.shape[0] < plan.max_rows:
+            self._h = torch.empty((plan.max_rows, self.inter), dtype=torch.bfloat16, device="cuda")
+        tiles = self._u32(plan.tile_expert)
+        m_tiles = self._u32(np.array([plan.m_tiles], dtype=np.uint32))
+        self.ffi.check(self.lib.vyb_k_moe_experts_int4(
+            rows_sorted.data_ptr(), self.w13.data_ptr(), self.s13.data_ptr(), self.w2.data_ptr(), self.s2.data_ptr(),
+            y.data_ptr(), self._h.data_ptr(), tiles.data_ptr(), m_tiles.data_ptr(), plan.max_rows, self.hidden, self.inter,
+            self.local_experts, self.group_size, self._stream(), C.c_void_p(self.status.data_ptr())))
+        return y
+
+    def combine(self, y_rows, pos: np.ndarray, wts):
+        torch = self.torch
+        tokens, topk = pos.shape
+        out = torch.empty((tokens, self.hidden), dtype=torch.bfloat16, device="cuda")
+        p = self._u32(pos)
+        self.ffi.check(self.lib.vyb_k_moe_combine(y_rows.data_ptr(), p.data_ptr(), wts.data_ptr(), out.data_ptr(), tokens,
+                                                  self.hidden, topk, self._stream()))
+        return out
+
+
+def route(x, w_router, experts: int, topk: int):
+    """Router linear + gate on the device: (idx int32 [tokens, topk], wts f32 [tokens, topk])."""
+    import torch
+
+    from . import ffi
+
+    tokens, hidden = x.shape
+    idx = torch.empty((tokens, topk), dtype=torch.int32, device="cuda")
+    wts = torch.empty((tokens, topk), dtype=torch.float32, device="cuda")
+    ffi.check(ffi.lib().vyb_k_moe_route(x.data_ptr(), w_router.data_ptr(), idx.data_ptr(), wts.data_ptr(), tokens, hidden,
+                                        experts, topk, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    return idx, wts
+
+
+def expert_parallel_moe_ffn(x, w_router, ops: KernelOps, experts: int, topk: int, group=None, max_rows: int | None = None):
+    """Full expert-parallel layer for this rank's tokens: route on the device, plan on the host, exchange, compute."""
+    idx, wts = route(x, w_router, experts, topk)
+    out = expert_parallel_layer(x, idx.cpu().numpy(), wts, experts, ops, group, max_rows)
+    return out, idx, wts
