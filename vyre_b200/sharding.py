@@ -36,15 +36,18 @@ def column_shard(n: int, world: int, rank: int, multiple: int = 1) -> tuple[int,
     return min(n, begin_u * multiple), min(n, end_u * multiple)
 
 
-def all_gather_columns(y_local, n_total: int, group=None):
-    """[m, n_local] per rank -> [m, n_total] on every rank (equal shards: one all_gather_into_tensor, then a column
-    interleave; ragged shards: all_gather of padded shards)."""
+def all_gather_columns(y_local, n_total: int, group=None, multiple: int = 1):
+    """[m, n_local] per rank -> [m, n_total] on every rank, for shards cut by column_shard(n_total, world, r, multiple):
+    one all_gather_into_tensor of shards padded to the widest, then a column interleave."""
     import torch
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     m = y_local.shape[0]
-    bounds = [column_shard(n_total, world, r) for r in range(world)]
+    bounds = [column_shard(n_total, world, r, multiple) for r in range(world)]
+    rank = dist.get_rank(group)
+    if y_local.shape[1] != bounds[rank][1] - bounds[rank][0]:
+        raise ValueError(f"rank {rank} holds {y_local.shape[1]} columns but its shard of {n_total} is {bounds[rank]}")
     widest = max(e - b for b, e in bounds)
     padded = y_local
     if y_local.shape[1] != widest:
