@@ -468,6 +468,75 @@ def run_native(args) -> None:
     print(json.dumps(line))
 
 
+def run_moe_ep(args) -> None:
+    """Config 4 across the ranks: 4096 tokens in total (strong scaling), 8 experts top-2 split expert-parallel, two
+    all-to-all exchanges per layer. A step is one layer over every rank's tokens; value = tokens / s over all ranks.
+    The timed region holds everything a caller of the layer pays: routing, the host-side exchange plan (one
+    device-to-host read of the routing indices), both exchanges, grouped GEMMs and the combine."""
+    import torch
+
+    from vyre_b200 import sharding
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    import torch.distributed as dist
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    tokens_total, inter, hidden = args.shape
+    experts, topk = 8, 2
+    local = experts // world
+    tokens = tokens_total // world
+    torch.manual_seed(1234 + rank)
+    x = torch.randn((tokens, hidden), device="cuda").to(torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(7)  # the router is replicated: same values on every rank
+    wr = (torch.randn((experts, hidden), device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    w13 = torch.randint(0, 256, (local, 2, inter, hidden // 2), dtype=torch.uint8, device="cuda")
+    s13 = (torch.rand((local, 2, inter, hidden // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
+    w2 = torch.randint(0, 256, (local, hidden, inter // 2), dtype=torch.uint8, device="cuda")
+    s2 = (torch.rand((local, hidden, inter // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
+    ops = sharding.KernelOps(w13, s13, w2, s2, hidden, inter, local, GROUP)
+    max_rows = ((tokens_total * topk + 255) // 256) * 256 + local * 256  # worst case: every pair lands on this rank
+
+    def step():
+        return sharding.expert_parallel_moe_ffn(x, wr, ops, experts, topk, max_rows=max_rows)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    steps = max(1, args.steps)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    assert ops.status.cpu().tolist() == [0, 0, 0, 0]
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        flops = 2.0 * tokens_total * topk * 3 * inter * hidden
+        print(json.dumps({
+            "metric": "moe_ffn_tokens_per_s", "value": tokens_total / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16xint4->f32", "data": "synthetic",
+            "config": {"workload": f"int4 MoE FFN layer, {tokens_total} tokens, hidden {hidden}, inter {inter}, {experts} experts "
+                                   f"top-{topk} (config 4)", "parallelism": f"expert-parallel x{world}, NCCL all-to-all (dispatch + combine)",
+                       "tokens_per_rank": tokens, "experts_per_rank": local},
+            "expert_tflops": flops / (ms * 1e-3) / 1e12}))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -481,6 +550,8 @@ def main() -> None:
                     help="GEMM shape for --quick --case prefill|int8gemm")
     ap.add_argument("--copies", type=int, default=COPIES,
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
+    ap.add_argument("--workload", default="gemv", choices=["gemv", "moe"],
+                    help="gemv: the headline decode GEMV; moe: the expert-parallel MoE FFN layer (--shape TOKENS INTER HIDDEN)")
     ap.add_argument("--quick", action="store_true",
                     help="kernel-only run without graphs, end-to-end leg or CPU baseline (the case profiled under ncu)")
     args = ap.parse_args()
@@ -488,6 +559,12 @@ def main() -> None:
         run_reference(args)
     elif args.quick:
         run_quick(args)
+    elif args.workload == "moe":
+        if args.shape == [2048, 14336, 4096]:
+            args.shape = [4096, 14336, 4096]
+        if args.steps == 100000:
+            args.steps, args.warmup = 20, 3
+        run_moe_ep(args)
     else:
         run_native(args)
 
