@@ -29,14 +29,23 @@ constexpr uint32_t PAD_TOKEN = 0xFFFFFFFFu;
 
 __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_as_float(b << 16); }
 
-// ---- router + gate: one warp per token ------------------------------------------------------------------------------
+// ---- router + gate: one warp per token; a CTA keeps the router weights in shared memory and walks many tokens -------
+template <bool WR_IN_SMEM>
 __global__ void __launch_bounds__(256)
 moe_router_gate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w_router, uint32_t* __restrict__ idx,
                        float* __restrict__ wts, uint32_t tokens, uint32_t hidden, uint32_t experts, uint32_t topk) {
+    extern __shared__ __align__(16) uint8_t s_dyn[];
     __shared__ float s_logits[8][MAX_EXPERTS];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t t = blockIdx.x * 8 + warp;
-    if (t >= tokens) return;
+    const uint16_t* wr = w_router;
+    if constexpr (WR_IN_SMEM) {
+        uint4* dst = reinterpret_cast<uint4*>(s_dyn);
+        const uint4* src = reinterpret_cast<const uint4*>(w_router);
+        for (uint32_t i = threadIdx.x; i < experts * hidden / 8; i += blockDim.x) dst[i] = src[i];
+        __syncthreads();
+        wr = reinterpret_cast<const uint16_t*>(s_dyn);
+    }
+    for (uint32_t t = blockIdx.x * 8 + warp; t < tokens; t += gridDim.x * 8) {
     const uint16_t* xr = x + size_t(t) * hidden;
     for (uint32_t e0 = 0; e0 < experts; e0 += 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -47,7 +56,7 @@ moe_router_gate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restric
 #pragma unroll
             for (uint32_t e = 0; e < 8; ++e) {
                 if (e < ne) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(w_router + size_t(e0 + e) * hidden + k);
+                    const uint4 wv = *reinterpret_cast<const uint4*>(wr + size_t(e0 + e) * hidden + k);
                     const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
@@ -92,6 +101,33 @@ moe_router_gate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restric
             wts[size_t(t) * topk + j] = __fdiv_rn(expf(__fsub_rn(best_val[j], mx)), sum);
         }
     }
+    __syncwarp();
+    }  // token loop
+}
+
+// the router weights stay in shared memory when they fit beside the other kernels' carve-out
+constexpr size_t ROUTER_SMEM_LIMIT = 160 * 1024;
+cudaError_t launch_router_gate(const uint16_t* x, const uint16_t* w_router, uint32_t* idx, float* wts, uint32_t tokens,
+                               uint32_t hidden, uint32_t experts, uint32_t topk, int sm_count, cudaStream_t stream) {
+    const size_t wr_bytes = size_t(experts) * hidden * 2;
+    const uint32_t want_blocks = (tokens + 7) / 8;
+    if (wr_bytes <= ROUTER_SMEM_LIMIT) {
+        static bool configured[64] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (!configured[dev & 63]) {
+            e = cudaFuncSetAttribute(moe_router_gate_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     int(ROUTER_SMEM_LIMIT));
+            if (e != cudaSuccess) return e;
+            configured[dev & 63] = true;
+        }
+        const uint32_t grid = min(want_blocks, uint32_t(sm_count));
+        moe_router_gate_kernel<true><<<grid, 256, wr_bytes, stream>>>(x, w_router, idx, wts, tokens, hidden, experts, topk);
+    } else {
+        moe_router_gate_kernel<false><<<want_blocks, 256, 0, stream>>>(x, w_router, idx, wts, tokens, hidden, experts, topk);
+    }
+    return cudaGetLastError();
 }
 
 // ---- plan: expert segments, tile table, deterministic row positions (single CTA) -------------------------------------
@@ -284,13 +320,13 @@ cudaError_t launch_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, c
     uint16_t* y = reinterpret_cast<uint16_t*>(base + L.y);
     const uint32_t* tile_expert = plan + 2 + experts;
 
-    moe_router_gate_kernel<<<(tokens + 7) / 8, 256, 0, stream>>>(static_cast<const uint16_t*>(x_bf16),
-                                                                 static_cast<const uint16_t*>(w_router_bf16), routing_idx,
-                                                                 routing_w, tokens, hidden, experts, topk);
+    cudaError_t e = launch_router_gate(static_cast<const uint16_t*>(x_bf16), static_cast<const uint16_t*>(w_router_bf16),
+                                       routing_idx, routing_w, tokens, hidden, experts, topk, sm_count, stream);
+    if (e != cudaSuccess) return e;
     moe_plan_kernel<<<1, 1024, 0, stream>>>(routing_idx, plan, pos, row_token, tokens, experts, topk, L.max_rows);
     moe_gather_kernel<<<sm_count * 4, 256, 0, stream>>>(static_cast<const uint16_t*>(x_bf16), row_token, plan, xg, hidden,
                                                         experts);
-    cudaError_t e = cudaGetLastError();
+    e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     // h = swiglu(xg . W1^T, xg . W3^T) per expert
     e = launch_int4_gemm_pair(xg, w13, s13, h, L.max_rows, inter, hidden, group, 0, 1, experts, tile_expert, plan, inter,
@@ -310,10 +346,12 @@ cudaError_t launch_moe_route(const void* x_bf16, const void* w_router_bf16, uint
                              uint32_t tokens, uint32_t hidden, uint32_t experts, uint32_t topk, cudaStream_t stream) {
     if (tokens == 0 || experts == 0 || experts > MAX_EXPERTS || topk == 0 || topk > MAX_TOPK || topk > experts || hidden % 8)
         return cudaErrorNotSupported;
-    moe_router_gate_kernel<<<(tokens + 7) / 8, 256, 0, stream>>>(static_cast<const uint16_t*>(x_bf16),
-                                                                 static_cast<const uint16_t*>(w_router_bf16), routing_idx,
-                                                                 routing_w, tokens, hidden, experts, topk);
-    return cudaGetLastError();
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+    return launch_router_gate(static_cast<const uint16_t*>(x_bf16), static_cast<const uint16_t*>(w_router_bf16), routing_idx,
+                              routing_w, tokens, hidden, experts, topk, sms, stream);
 }
 
 cudaError_t launch_rows_gather_bf16(const void* src, const uint32_t* index, void* dst, uint32_t rows, uint32_t row_elems,
