@@ -409,6 +409,27 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
 int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                            uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,
                            void* stream, uint32_t* status);
+/* Column-parallel decode GEMV with the all-gather fused into its epilogue (no counterpart in the reference, whose
+ * backends are single-device; the sharding follows from its one-output-per-invocation kernels,
+ * vyre-libs/src/nn/linear/inner/linear_4bit.rs:710-742). One process per GPU; rank r owns n rows of the weight
+ * and stores its bf16 outputs into slice r of EVERY rank's gather buffer [2][world][m][n] over peer memory
+ * (NVLink), then bumps each peer's arrival counter. Step s uses buffer half s % 2. After each launch the same
+ * stream must run vyb_k_allgather_wait, which waits (bounded, ~2 s, status bit 128) for all peers of that step and
+ * advances the local step counter; whatever consumes the gathered [world][m][n] runs after it.
+ * peer_out / peer_flag: device addresses valid on THIS rank for every rank's buffer / 32-bit arrival counter
+ * (own rank included); epoch, ticket: local 32-bit words. All counters zero before the first step. */
+typedef struct vyb_allgather_ctx {
+    uint32_t world, rank;
+    uint64_t peer_out[8];
+    uint64_t peer_flag[8];
+    uint64_t epoch;
+    uint64_t ticket;
+} vyb_allgather_ctx;
+int32_t vyb_k_int4_gemv_allgather(const void* x_bf16, const void* w_packed, const void* scale_bf16,
+                                  const vyb_allgather_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                                  uint32_t flags, void* stream, uint32_t* status);
+int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status);
+
 /* C1: y f32 [m,n] = x f32 [m,k] . (int8 w[n,k] * s[n])^T */
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
                                       uint32_t m, uint32_t n, uint32_t k, void* stream);

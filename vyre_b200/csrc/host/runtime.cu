@@ -894,6 +894,80 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
     return VYB_OK;
 }
 
+namespace {
+int32_t current_sm_count(int* sms) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    return VYB_OK;
+}
+int32_t launch_result(cudaError_t e, const char* what) {
+    if (e == cudaErrorNotSupported) {
+        cudaGetLastError();
+        return fail_unsupported(std::string(what) + " with these dimensions");
+    }
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), std::string(what) + " launch failed: " + cuda_msg(e));
+    }
+    return VYB_OK;
+}
+}  // namespace
+
+namespace {
+int32_t to_gather(const vyb_allgather_ctx* ctx, vybk::GemvAllGather* ag) {
+    if (!ctx) return fail_invalid_program("Fix: pass a non-null all-gather context.");
+    if (ctx->world < 1 || ctx->world > 8 || ctx->rank >= ctx->world)
+        return fail_invalid_program("Fix: the all-gather context needs 1 <= world <= 8 and rank < world, got world=" +
+                                    std::to_string(ctx->world) + " rank=" + std::to_string(ctx->rank) + ".");
+    if (!ctx->epoch || !ctx->ticket) return fail_invalid_program("Fix: the all-gather context needs local epoch and ticket words.");
+    for (uint32_t r = 0; r < ctx->world; ++r)
+        if (!ctx->peer_out[r] || !ctx->peer_flag[r])
+            return fail_invalid_program("Fix: the all-gather context needs a gather buffer and an arrival counter for every rank.");
+    ag->world = ctx->world;
+    ag->rank = ctx->rank;
+    for (int r = 0; r < 8; ++r) {
+        ag->peer_out[r] = ctx->peer_out[r];
+        ag->peer_flag[r] = ctx->peer_flag[r];
+    }
+    ag->epoch = ctx->epoch;
+    ag->ticket = ctx->ticket;
+    return VYB_OK;
+}
+}  // namespace
+
+int32_t vyb_k_int4_gemv_allgather(const void* x_bf16, const void* w_packed, const void* scale_bf16,
+                                  const vyb_allgather_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                                  uint32_t flags, void* stream, uint32_t* status) {
+    if (!x_bf16 || !w_packed || !scale_bf16) return fail_invalid_program("Fix: pass non-null device pointers.");
+    vybk::GemvAllGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    if (!vybk::int4_gemv_supported(m, n, k, group_size))
+        return fail_unsupported("int4 gemv shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
+                                std::to_string(k) + " group=" + std::to_string(group_size) +
+                                " (needs 1 <= m <= 8, group 128, k a multiple of 1024)");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) |
+         reinterpret_cast<uintptr_t>(scale_bf16)) & 15)
+        return fail_invalid_program("Fix: int4 gemv operands must be 16-byte aligned (bulk copies start on 16-byte boundaries).");
+    int sms = 0;
+    if (int32_t rc = current_sm_count(&sms)) return rc;
+    void* y_local = reinterpret_cast<void*>(ag.peer_out[ag.rank]);
+    return launch_result(vybk::launch_int4_gemv(x_bf16, w_packed, scale_bf16, y_local, m, n, k, 0, sms,
+                                                static_cast<cudaStream_t>(stream), status,
+                                                (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0, &ag),
+                         "int4 gemv with all-gather epilogue");
+}
+
+int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status) {
+    vybk::GemvAllGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    return launch_result(vybk::launch_allgather_wait(ag, static_cast<cudaStream_t>(stream), status), "all-gather wait");
+}
+
 int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
                         uint32_t* status) {
@@ -941,29 +1015,6 @@ int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scal
     return VYB_OK;
 }
 
-namespace {
-int32_t current_sm_count(int* sms) {
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e == cudaSuccess) e = cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
-    }
-    return VYB_OK;
-}
-int32_t launch_result(cudaError_t e, const char* what) {
-    if (e == cudaErrorNotSupported) {
-        cudaGetLastError();
-        return fail_unsupported(std::string(what) + " with these dimensions");
-    }
-    if (e != cudaSuccess) {
-        cudaGetLastError();
-        return fail_dispatch(int(e), std::string(what) + " launch failed: " + cuda_msg(e));
-    }
-    return VYB_OK;
-}
-}  // namespace
 
 int32_t vyb_k_moe_route(const void* x_bf16, const void* w_router_bf16, void* routing_idx, void* routing_w, uint32_t tokens,
                         uint32_t hidden, uint32_t experts, uint32_t topk, void* stream) {

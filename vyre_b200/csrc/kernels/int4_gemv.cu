@@ -74,6 +74,7 @@ struct Ctrl {
     unsigned long long full[STAGES];
     unsigned long long empty[STAGES];
     unsigned long long red_full[RED_SLOTS];  // 16 arrivals: every warp left its partial of the tile in the slot
+    unsigned long long ag_done;              // 16 arrivals: every warp's peer stores are fenced (all-gather epilogue)
     unsigned int abort_flag;
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL, "control block");
@@ -145,6 +146,9 @@ struct Params {
     uint32_t* status;
     unsigned long long* trace;  // optional: per-CTA timeline (64 slots each), tuning aid only
     uint32_t debug;             // tuning aid: bit0 = skip the math, bit1 = split the tile copy in 4
+    // all-gather epilogue (world > 1): every rank stores its outputs straight into every peer's gather buffer
+    // [2][world][m][n] (double-buffered by step parity) over NVLink and then bumps the peer's arrival counter
+    GemvAllGather ag;
 };
 
 template <int LIMBS, bool OUT_F32>
@@ -232,6 +236,9 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     // activations may come from the preceding kernel: everything that reads x or writes y runs after this point,
     // only the (constant) weight stream of the producer warp starts before it
     if (warp != WARPS) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // steps completed so far (advanced by the wait kernel that follows every all-gather launch) select the buffer half
+    uint32_t ag_parity = 0;
+    if (p.ag.world != 0 && warp != WARPS) ag_parity = *reinterpret_cast<const volatile uint32_t*>(p.ag.epoch) & 1u;
     if (coop) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -249,6 +256,7 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
                 mbar_init(smem_u32(&ctrl->empty[s]), WARPS);
             }
             for (int s = 0; s < RED_SLOTS; ++s) mbar_init(smem_u32(&ctrl->red_full[s]), WARPS);
+            mbar_init(smem_u32(&ctrl->ag_done), WARPS);
             ctrl->abort_flag = 0;
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -470,10 +478,19 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
             const uint32_t row = i < 2 ? row_lo : row_lo + 8;
             const uint32_t col = 2 * t + (i & 1);
             if (row < r1 && col < p.m) {
-                if constexpr (OUT_F32)
+                if constexpr (OUT_F32) {
                     static_cast<float*>(p.y)[size_t(col) * p.n + row] = vals[i];
-                else
-                    static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(vals[i]);
+                } else {
+                    const __nv_bfloat16 v = __float2bfloat16_rn(vals[i]);
+                    if (p.ag.world != 0) {
+                        // this rank's slice of the gather buffer of the current step parity, on every rank
+                        const size_t off = ((size_t(ag_parity) * p.ag.world + p.ag.rank) * p.m + col) * p.n + row;
+                        for (uint32_t r = 0; r < p.ag.world; ++r)
+                            reinterpret_cast<__nv_bfloat16*>(p.ag.peer_out[r])[off] = v;
+                    } else {
+                        static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = v;
+                    }
+                }
             }
         }
         return true;
@@ -515,6 +532,51 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     if (alive && ntiles > 0 && uint32_t(warp) == (ntiles - 1) % WARPS) alive = reduce_tile(ntiles - 1);
     stamp(31);
     if (!alive && lane == 0 && p.status) atomicOr(p.status, 1u);
+    if (p.ag.world > 1) {
+        // All-gather completion. Every warp fences its peer stores at system scope and arrives; one thread waits
+        // (bounded) for the 16 warps and takes a ticket; the CTA that takes the last ticket of the launch bumps the
+        // arrival counter of every peer - by then all stores of all CTAs are visible there.
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&ctrl->ag_done));
+        if (warp == 0 && lane == 0) {
+            if (mbar_wait(smem_u32(&ctrl->ag_done), 0, abort_flag)) {
+                __threadfence();
+                const unsigned int ticket = atomicAdd(reinterpret_cast<unsigned int*>(p.ag.ticket), 1u);
+                if (ticket == gridDim.x - 1) {
+                    *reinterpret_cast<volatile unsigned int*>(p.ag.ticket) = 0;  // next launch starts from zero
+                    __threadfence_system();
+                    for (uint32_t r = 0; r < p.ag.world; ++r)
+                        if (r != p.ag.rank) atomicAdd_system(reinterpret_cast<unsigned int*>(p.ag.peer_flag[r]), 1u);
+                }
+            } else if (p.status) {
+                atomicOr(p.status, 64u);
+            }
+        }
+    }
+}
+
+// Completes one all-gather step on this rank: waits (bounded) until every peer's launch has bumped the local arrival
+// counter, then advances the local step counter. The next GEMV of the stream may start its weight stream meanwhile.
+__global__ void __launch_bounds__(32) allgather_wait_kernel(const GemvAllGather ag, uint32_t* status) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (threadIdx.x != 0) return;
+    volatile uint32_t* epoch = reinterpret_cast<volatile uint32_t*>(ag.epoch);
+    const volatile uint32_t* arrived = reinterpret_cast<const volatile uint32_t*>(ag.peer_flag[ag.rank]);
+    const uint32_t step = *epoch + 1;
+    const uint32_t want = step * (ag.world - 1);
+    const long long t0 = clock64();
+    bool ok = true;
+    while (int32_t(*arrived - want) < 0) {
+        if (clock64() - t0 > 4000000000ll) {  // ~2 s: a missing peer raises a status word instead of a hang
+            ok = false;
+            break;
+        }
+        __nanosleep(100);
+    }
+    __threadfence_system();  // acquire side: the peers' stores are visible to whatever follows in this stream
+    *epoch = step;
+    if (!ok && status) atomicOr(status, 128u);
 }
 
 
@@ -570,7 +632,7 @@ bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
 
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                             uint32_t* status, bool constant_weights) {
+                             uint32_t* status, bool constant_weights, const GemvAllGather* ag) {
     // opt in to the large dynamic shared-memory carve-out once per device
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -597,6 +659,11 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     p.status = status;
     p.trace = g_gemv_trace;
     p.debug = g_gemv_debug;
+    p.ag = GemvAllGather{};
+    if (ag) {
+        if (out_f32 || ag->world < 1 || ag->world > 8 || ag->rank >= ag->world) return cudaErrorInvalidValue;
+        p.ag = *ag;
+    }
     const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
     cudaLaunchConfig_t cfg = {};
@@ -612,6 +679,12 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     cfg.numAttrs = constant_weights ? 1 : 0;
     if (out_f32) return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<3, true>, p);
     return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<2, false>, p);
+}
+
+cudaError_t launch_allgather_wait(const GemvAllGather& ag, cudaStream_t stream, uint32_t* status) {
+    if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world) return cudaErrorInvalidValue;
+    allgather_wait_kernel<<<1, 32, 0, stream>>>(ag, status);
+    return cudaGetLastError();
 }
 
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,

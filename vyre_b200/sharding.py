@@ -251,3 +251,67 @@ def expert_parallel_moe_ffn(x, w_router, ops: KernelOps, experts: int, topk: int
     idx, wts = route(x, w_router, experts, topk)
     out = expert_parallel_layer(x, idx.cpu().numpy(), wts, experts, ops, group, max_rows)
     return out, idx, wts
+
+
+# ---- column-parallel decode GEMV with the all-gather fused into the kernel's epilogue (peer stores over NVLink) ------
+class PeerAllGather:
+    """Gather buffers for vyb_k_int4_gemv_allgather: [2][world][m][n] bf16 per rank plus a 32-bit arrival counter, in
+    symmetric memory so that every rank holds device addresses of every peer's copy. Step s lands in half s % 2."""
+
+    def __init__(self, m: int, n: int, group=None):
+        import os
+
+        import torch
+        import torch.distributed as dist
+
+        from . import ffi
+
+        self.ffi, self.torch = ffi, torch
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("the fused all-gather addresses at most 8 peers")
+        self.m, self.n = m, n
+        self.data_bytes = (2 * self.world * m * n * 2 + 255) & ~255
+        total = self.data_bytes + 256
+        if self.world > 1:
+            # plain peer mappings are all the kernel needs; no NVLink multicast object is bound to the buffer
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm
+
+            self.buf = symm.empty(total, dtype=torch.uint8, device="cuda")
+            self.buf.zero_()
+            torch.cuda.synchronize()
+            self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.zeros(total, dtype=torch.uint8, device="cuda")
+            self.handle = None
+            ptrs = [self.buf.data_ptr()]
+        self.local = torch.zeros(64, dtype=torch.int32, device="cuda")  # [0] steps completed, [16] CTA tickets
+        self.ctx = ffi.AllGatherCtx()
+        self.ctx.world, self.ctx.rank = self.world, self.rank
+        for r in range(self.world):
+            self.ctx.peer_out[r] = ptrs[r]
+            self.ctx.peer_flag[r] = ptrs[r] + self.data_bytes
+        self.ctx.epoch = self.local.data_ptr()
+        self.ctx.ticket = self.local.data_ptr() + 64
+        self.steps = 0
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group)  # every counter is zero before anybody launches
+
+    def halves(self):
+        """The two [world, m, n] bf16 views of the local gather buffer."""
+        t = self.buf[: 2 * self.world * self.m * self.n * 2].view(self.torch.bfloat16)
+        return t.view(2, self.world, self.m, self.n)
+
+    def launch(self, x, w, s, k: int, stream, status, flags: int = 0):
+        """One step on `stream`: GEMV with peer stores, then the bounded wait for all peers. Returns the half index."""
+        lib = self.ffi.lib()
+        sp = C.c_void_p(stream)
+        self.ffi.check(lib.vyb_k_int4_gemv_allgather(x.data_ptr(), w.data_ptr(), s.data_ptr(), C.byref(self.ctx), self.m,
+                                                     self.n, k, 128, flags, sp, C.c_void_p(status.data_ptr())))
+        self.ffi.check(lib.vyb_k_allgather_wait(C.byref(self.ctx), sp, C.c_void_p(status.data_ptr())))
+        half = self.steps & 1
+        self.steps += 1
+        return half
