@@ -9,7 +9,9 @@ activations; launches rotate over 8 resident copies of the weights (242 MB > the
 streams its weights from HBM. Timing is CUDA events on the launching stream, max over ranks.
 
 For N > 1 the linear is sharded column-parallel: every rank owns a [14336, 4096] shard of a 14336*N-row
-linear (weak scaling) and each step ends with an NCCL all-gather of the bf16 outputs.
+linear (weak scaling) and each step's bf16 outputs are all-gathered by this library's own peer-store kernel over
+NVLink (one CTA on a side stream, bounded completion checks), overlapped with the next GEMV and verified once
+against NCCL's all-gather before timing.
 
 `--impl reference` times the CPU restatement of the reference engine (oracle/) on the host cores over a bounded
 row sample of the same workload.
@@ -291,13 +293,20 @@ def run_native(args) -> None:
         ws.append(torch.from_numpy(np.roll(w_np, c, axis=0)).cuda())
         ss.append(torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda())
     y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
-    y_all = torch.zeros((world, m, N_OUT), dtype=torch.bfloat16, device="cuda") if world > 1 else None
+    # N > 1: the all-gather is this library's peer-store kernel over NVLink (symmetric memory), not NCCL
+    pag = None
+    if world > 1:
+        from vyre_b200 import sharding
+
+        pag = sharding.PeerAllGather(m, N_OUT)
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     stream = torch.cuda.Stream()
 
-    def launch(c: int):
+    side = torch.cuda.Stream()
+
+    def launch(c: int, out=None):
         # weights are graph constants: the launch may overlap the tail of the previous one (see the header)
-        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), (y if out is None else out).data_ptr(), m, N_OUT, K_IN,
                                        GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
                                        C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
 
@@ -308,14 +317,41 @@ def run_native(args) -> None:
     graph = torch.cuda.CUDAGraph()
     with torch.cuda.stream(stream):
         with torch.cuda.graph(graph, stream=stream):
-            for c in range(COPIES):
-                launch(c)
-                if world > 1:
-                    dist.all_gather_into_tensor(y_all.view(-1), y.view(-1))
+            if pag is None:
+                for c in range(COPIES):
+                    launch(c)
+            else:
+                # GEMV c writes this rank's slice of buffer half c % 2; a one-CTA push kernel on a side stream copies
+                # it to every peer and signals them while GEMV c+1 already runs; GEMV c+2 (same half) waits for it.
+                pushed = [None] * COPIES
+                for c in range(COPIES):
+                    half = c & 1
+                    if c >= 2:
+                        stream.wait_event(pushed[c - 2])
+                    launch(c, pag.local_slice(half))
+                    ready = torch.cuda.Event()
+                    ready.record(stream)
+                    side.wait_event(ready)
+                    pag.push(half, side.cuda_stream, status)
+                    pushed[c] = torch.cuda.Event()
+                    pushed[c].record(side)
+                stream.wait_stream(side)
+                # the replay ends with the bounded wait for its own gathers: nothing is left in flight
+                pag.wait(stream.cuda_stream, status)
     # parity guard inside the bench: the last copy's output must match the contract path bit for bit
     with torch.cuda.stream(stream):
         graph.replay()
     stream.synchronize()
+    if pag is not None:
+        # the gathered result of the graph's last step (odd step index: half 1) against NCCL's all-gather of the
+        # plain kernel's output for the same weight copy
+        launch(COPIES - 1)
+        stream.synchronize()
+        want_all = torch.empty((world, m, N_OUT), dtype=torch.bfloat16, device="cuda")
+        dist.all_gather_into_tensor(want_all.view(-1), y.view(-1))
+        torch.cuda.synchronize()
+        assert torch.equal(pag.halves()[1].view(torch.int16), want_all.view(torch.int16)), "fused all-gather differs from NCCL"
+        y = pag.halves()[1][rank]
     y_ref = y.clone()
 
     for _ in range(warmup // COPIES):
@@ -359,6 +395,7 @@ def run_native(args) -> None:
     if dist:
         del graph
         torch.cuda.synchronize()
+        pag = None
         dist.barrier()
         dist.destroy_process_group()
         dist = None
@@ -454,7 +491,7 @@ def run_native(args) -> None:
         "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16xint4->f32", "data": "synthetic",
         "config": {"workload": f"int4 group-quantized decode GEMV M={m} N={N_OUT} K={K_IN} g={GROUP} (config 2)",
-                   "per_gpu_shard": [N_OUT, K_IN], "parallelism": f"column-parallel x{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                   "per_gpu_shard": [N_OUT, K_IN], "parallelism": f"column-parallel x{world}" + (" + peer-store all-gather over NVLink on a side stream" if world > 1 else ""),
                    "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
                    "launch": f"CUDA graph of {COPIES} launches, programmatic dependent launch (constant weights)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -463,7 +500,7 @@ def run_native(args) -> None:
                      "frac_of_nominal_8tbs": achieved / 8000.0},
         "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cpu_threads, "kind": "port", "sample": cpu_sample,
                          "ms_per_gemv": round(cpu_dt * 1e3, 2)},
-        "e2e": e2e, "gpu_launches": steps, "clocks": clocks, "other_batches": extra,
+        "e2e": e2e, "gpu_launches": steps * (2 if world > 1 else 1) + (steps // COPIES if world > 1 else 0), "clocks": clocks, "other_batches": extra,
     }
     print(json.dumps(line))
 

@@ -103,11 +103,26 @@ def _worker(rank: int, world: int, port: int, q):
         dist.all_gather_into_tensor(want_all.view(-1), y_local.view(-1))
         for step in range(5):  # both halves, several times
             half = pag.launch(tx2, tw2_, ts2_, k, cur, status, flags=ffi.LAUNCH_CONSTANT_WEIGHTS if step % 2 else 0)
+            pag.wait(cur, status)
             torch.cuda.synchronize()
             assert half == step % 2
             assert status.cpu().tolist() == [0, 0, 0, 0]
             assert torch.equal(pag.halves()[half].view(torch.int16), want_all.view(torch.int16)), f"step {step}"
             pag.halves()[half].zero_()      # the next use of this half must be written again by every rank
+            torch.cuda.synchronize()
+            dist.barrier()
+        # the same gather as a kernel of its own (plain GEMV into the local slice, then the push kernel)
+        pag2 = sharding.PeerAllGather(m, n)
+        for step in range(4):
+            half = step & 1
+            ffi.check(L.vyb_k_int4_gemv_ex(tx2.data_ptr(), tw2_.data_ptr(), ts2_.data_ptr(), pag2.local_slice(half).data_ptr(),
+                                           m, n, k, 128, ffi.DT_BF16, 0, C.c_void_p(cur), C.c_void_p(status.data_ptr())))
+            pag2.push(half, cur, status)
+            pag2.wait(cur, status)
+            torch.cuda.synchronize()
+            assert status.cpu().tolist() == [0, 0, 0, 0]
+            assert torch.equal(pag2.halves()[half].view(torch.int16), want_all.view(torch.int16)), f"push step {step}"
+            pag2.halves()[half].zero_()
             torch.cuda.synchronize()
             dist.barrier()
         q.put((rank, "ok"))

@@ -962,6 +962,16 @@ int32_t vyb_k_int4_gemv_allgather(const void* x_bf16, const void* w_packed, cons
                          "int4 gemv with all-gather epilogue");
 }
 
+int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32_t m, uint32_t n, void* stream,
+                             uint32_t* status) {
+    vybk::GemvAllGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    if (half > 1 || m == 0 || n == 0 || (uint64_t(m) * n) % 8)
+        return fail_invalid_program("Fix: all-gather push needs half in {0,1} and m*n a multiple of 8 (16-byte stores).");
+    return launch_result(vybk::launch_allgather_push(ag, half, m, n, static_cast<cudaStream_t>(stream), status),
+                         "all-gather push");
+}
+
 int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status) {
     vybk::GemvAllGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;

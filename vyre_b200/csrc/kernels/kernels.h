@@ -26,6 +26,8 @@ struct GemvAllGather {
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                              uint32_t* status, bool constant_weights = false, const GemvAllGather* ag = nullptr);
+cudaError_t launch_allgather_push(const GemvAllGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
+                                  uint32_t* status);
 cudaError_t launch_allgather_wait(const GemvAllGather& ag, cudaStream_t stream, uint32_t* status);
 // any group size dividing k, k % 8 == 0, any m; plain loads, no TMA
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,

@@ -172,6 +172,7 @@ _STATUS_FUNCS = {
     "vyb_k_quantize_per_token_int8": [_P, _P, _P, _U, _U, _P],
     "vyb_k_int8_gemm_i32": [_P, _P, _P, _U, _U, _U, _P, _P],
     "vyb_k_int4_gemv_allgather": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_allgather_push": [_P, _U, _U, _U, _P, _P],
     "vyb_k_allgather_wait": [_P, _P, _P],
     "vyb_k_moe_route": [_P, _P, _P, _P, _U, _U, _U, _U, _P],
     "vyb_k_rows_gather_bf16": [_P, _P, _P, _U, _U, _P],

@@ -306,12 +306,25 @@ class PeerAllGather:
         return t.view(2, self.world, self.m, self.n)
 
     def launch(self, x, w, s, k: int, stream, status, flags: int = 0):
-        """One step on `stream`: GEMV with peer stores, then the bounded wait for all peers. Returns the half index."""
+        """One launch on `stream`: GEMV whose epilogue stores into every rank's buffer. Returns the half it fills."""
         lib = self.ffi.lib()
-        sp = C.c_void_p(stream)
         self.ffi.check(lib.vyb_k_int4_gemv_allgather(x.data_ptr(), w.data_ptr(), s.data_ptr(), C.byref(self.ctx), self.m,
-                                                     self.n, k, 128, flags, sp, C.c_void_p(status.data_ptr())))
-        self.ffi.check(lib.vyb_k_allgather_wait(C.byref(self.ctx), sp, C.c_void_p(status.data_ptr())))
+                                                     self.n, k, 128, flags, C.c_void_p(stream),
+                                                     C.c_void_p(status.data_ptr())))
         half = self.steps & 1
         self.steps += 1
         return half
+
+    def local_slice(self, half: int):
+        """This rank's [m, n] slice of a buffer half: the output of a plain GEMV that `push` then sends to the peers."""
+        return self.halves()[half][self.rank]
+
+    def push(self, half: int, stream, status):
+        """Send the local slice of `half` to every peer (kernel on `stream`, normally a side stream)."""
+        self.ffi.check(self.ffi.lib().vyb_k_allgather_push(C.byref(self.ctx), half, self.m, self.n, C.c_void_p(stream),
+                                                           C.c_void_p(status.data_ptr())))
+
+    def wait(self, stream, status):
+        """Bounded device-side wait on `stream` until every gather launched so far is complete in local memory."""
+        self.ffi.check(self.ffi.lib().vyb_k_allgather_wait(C.byref(self.ctx), C.c_void_p(stream),
+                                                           C.c_void_p(status.data_ptr())))
