@@ -152,17 +152,17 @@ def run_reference(args) -> None:
 NCU_DRAM_BYTES_PER_LAUNCH = {1: 30346368}
 
 
-def run_quick_gemm(args) -> None:
-    """A few plain launches of one of the tensor-core GEMMs (the cases profiled under ncu); one JSON line."""
+def measure_case(case: str, shape, steps: int, warmup: int) -> dict:
+    """Times plain launches of one of the tensor-core paths (prefill GEMM, int8 GEMM, fused MoE layer) with CUDA events."""
     import torch
 
     from vyre_b200 import ffi
 
     L = ffi.lib()
-    m, n, k = args.shape
+    m, n, k = shape
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    if args.case == "prefill":
+    if case == "prefill":
         x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
         w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
         s = (torch.rand((n, k // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
@@ -172,7 +172,7 @@ def run_quick_gemm(args) -> None:
             ffi.check(L.vyb_k_int4_prefill_gemm(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), m, n, k, GROUP,
                                                 ffi.DT_BF16, stream, C.c_void_p(status.data_ptr())))
         unit, scale = "TFLOP/s", 1e12
-    elif args.case == "moe":
+    elif case == "moe":
         # --shape TOKENS INTER HIDDEN; 8 experts, top-2 (config 4 is --shape 4096 14336 4096)
         experts, topk = 8, 2
         tokens, inter, hidden = m, n, k
@@ -204,22 +204,27 @@ def run_quick_gemm(args) -> None:
             ffi.check(L.vyb_k_int8_gemm_i32(a.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k, stream,
                                             C.c_void_p(status.data_ptr())))
         unit, scale = "TOP/s", 1e12
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         launch()
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         launch()
     end.record()
     torch.cuda.synchronize()
-    us = start.elapsed_time(end) * 1e3 / max(1, args.steps)
+    us = start.elapsed_time(end) * 1e3 / max(1, steps)
     assert status.cpu().tolist() == [0, 0, 0, 0]
-    line = {"quick": True, "case": args.case, "shape": [m, n, k], "steps": args.steps, "us_per_launch": us,
+    line = {"quick": True, "case": case, "shape": [m, n, k], "steps": steps, "us_per_launch": us,
             "rate": 2.0 * m * n * k / (us * 1e-6) / scale, "unit": unit}
-    if args.case == "moe":
+    if case == "moe":
         line["tokens_per_s"] = m / (us * 1e-6)
-    print(json.dumps(line))
+    return line
+
+
+def run_quick_gemm(args) -> None:
+    """The cases profiled under ncu; one JSON line."""
+    print(json.dumps(measure_case(args.case, args.shape, args.steps, args.warmup)))
 
 
 def run_quick(args) -> None:
@@ -350,7 +355,7 @@ def run_native(args) -> None:
         want_all = torch.empty((world, m, N_OUT), dtype=torch.bfloat16, device="cuda")
         dist.all_gather_into_tensor(want_all.view(-1), y.view(-1))
         torch.cuda.synchronize()
-        assert torch.equal(pag.halves()[1].view(torch.int16), want_all.view(torch.int16)), "fused all-gather differs from NCCL"
+        assert torch.equal(pag.halves()[1].view(torch.int16), want_all.view(torch.int16)), "peer-store all-gather differs from NCCL"
         y = pag.halves()[1][rank]
     y_ref = y.clone()
 
@@ -484,6 +489,23 @@ def run_native(args) -> None:
         dev.free_resident(h)
     dev.release()
 
+    # ---- the other configurations of the path, kernel-level, a few launches each (reported beside the headline) -----
+    secondary = {}
+    try:
+        bf16_peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+    except Exception:
+        bf16_peak = 1590.0
+    c3 = measure_case("prefill", [2048, 14336, 4096], 20, 5)
+    secondary["int4_prefill_gemm_config3"] = {"tflops": round(c3["rate"], 1), "us_per_launch": round(c3["us_per_launch"], 1),
+                                              "frac_of_bf16_burst_peak": round(c3["rate"] / bf16_peak, 3)}
+    c5 = measure_case("int8gemm", [4096, 28672, 8192], 10, 3)
+    secondary["int8_gemm_config5"] = {"tops": round(c5["rate"], 1), "us_per_launch": round(c5["us_per_launch"], 1),
+                                      "frac_of_2x_bf16_burst_peak": round(c5["rate"] / (2 * bf16_peak), 3)}
+    c4 = measure_case("moe", [4096, 14336, 4096], 5, 2)
+    secondary["moe_ffn_config4"] = {"tokens_per_s": round(c4["tokens_per_s"]), "ms_per_layer": round(c4["us_per_launch"] / 1e3, 3),
+                                    "expert_tflops": round(c4["rate"], 1)}
+    torch.cuda.empty_cache()
+
     cpu_gbs, cpu_dt, cpu_sample, cpu_threads = cpu_reference_rate(m, budget_s=12.0)
 
     line = {
@@ -500,7 +522,7 @@ def run_native(args) -> None:
                      "frac_of_nominal_8tbs": achieved / 8000.0},
         "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cpu_threads, "kind": "port", "sample": cpu_sample,
                          "ms_per_gemv": round(cpu_dt * 1e3, 2)},
-        "e2e": e2e, "gpu_launches": steps * (2 if world > 1 else 1) + (steps // COPIES if world > 1 else 0), "clocks": clocks, "other_batches": extra,
+        "e2e": e2e, "gpu_launches": steps * (2 if world > 1 else 1) + (steps // COPIES if world > 1 else 0), "clocks": clocks, "other_batches": extra, "secondary": secondary,
     }
     print(json.dumps(line))
 

@@ -409,32 +409,25 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
 int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                            uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,
                            void* stream, uint32_t* status);
-/* Column-parallel decode GEMV with the all-gather fused into its epilogue (no counterpart in the reference, whose
- * backends are single-device; the sharding follows from its one-output-per-invocation kernels,
- * vyre-libs/src/nn/linear/inner/linear_4bit.rs:710-742). One process per GPU; rank r owns n rows of the weight
- * and stores its bf16 outputs into slice r of EVERY rank's gather buffer [2][world][m][n] over peer memory
- * (NVLink), then bumps each peer's arrival counter and the local launch counter. Launch s uses buffer half
- * s % 2; before it overwrites a half it checks (bounded) that every peer has completed all earlier launches, so a
- * consumer of the gathered [world][m][n] must run, on every rank, between the launch that produced it and the next
- * launch on that rank's stream, after vyb_k_allgather_wait - which waits (bounded, ~2 s, status bit 128) until
- * every gather launched so far on this stream is complete in local memory.
- * peer_out / peer_flag: device addresses valid on THIS rank for every rank's buffer / 32-bit arrival counter
- * (own rank included); epoch, ticket: local 32-bit words. All counters zero before the first launch. */
+/* All-gather of column-parallel outputs over peer memory (NVLink), one process per GPU (no counterpart in the
+ * reference, whose backends are single-device; the sharding follows from its one-output-per-invocation kernels,
+ * vyre-libs/src/nn/linear/inner/linear_4bit.rs:710-742). Every rank owns a gather buffer [2][world][m][n] bf16 that
+ * all ranks can address. A plain GEMV (vyb_k_int4_gemv_ex) writes this rank's [m, n] slice into half `half` of the
+ * local buffer (peer_out[rank] + ((half * world + rank) * m * n) elements); vyb_k_allgather_push copies it to every
+ * peer, bumps their arrival counters and advances the local launch counter. Halves alternate; before a push
+ * overwrites a half it checks (bounded) that every peer has completed all earlier pushes, so a consumer of the
+ * gathered [world][m][n] must run, on every rank, before that rank's next push, after vyb_k_allgather_wait - which
+ * waits (bounded, ~2 s, status bit 128) until every gather pushed so far by this rank is complete in local memory.
+ * On a side stream the push overlaps the next GEMV; the caller orders it after the GEMV that wrote the slice and
+ * before the GEMV that overwrites that half again.
+ * peer_out / peer_flag: device addresses valid on THIS rank for every rank's buffer / 32-bit arrival counter (own
+ * rank included); epoch: a local 32-bit word. All counters zero before the first push. m * n a multiple of 8. */
 typedef struct vyb_allgather_ctx {
     uint32_t world, rank;
     uint64_t peer_out[8];
     uint64_t peer_flag[8];
     uint64_t epoch;
-    uint64_t ticket;
 } vyb_allgather_ctx;
-int32_t vyb_k_int4_gemv_allgather(const void* x_bf16, const void* w_packed, const void* scale_bf16,
-                                  const vyb_allgather_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
-                                  uint32_t flags, void* stream, uint32_t* status);
-/* The same gather as a kernel of its own: a plain GEMV (vyb_k_int4_gemv_ex) has written this rank's [m, n] slice
- * into half `half` of the local buffer (peer_out[rank] + ((half * world + rank) * m * n) bf16); the push copies it to
- * every peer, signals them and advances the local counter. On a side stream it overlaps the next GEMV; the caller
- * orders it after the GEMV that wrote the slice and before the GEMV that overwrites that half again. Same
- * counters and bounded checks as the fused form; use one form per context. */
 int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32_t m, uint32_t n, void* stream,
                              uint32_t* status);
 int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status);

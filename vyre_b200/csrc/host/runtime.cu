@@ -919,12 +919,12 @@ int32_t launch_result(cudaError_t e, const char* what) {
 }  // namespace
 
 namespace {
-int32_t to_gather(const vyb_allgather_ctx* ctx, vybk::GemvAllGather* ag) {
+int32_t to_gather(const vyb_allgather_ctx* ctx, vybk::PeerGather* ag) {
     if (!ctx) return fail_invalid_program("Fix: pass a non-null all-gather context.");
     if (ctx->world < 1 || ctx->world > 8 || ctx->rank >= ctx->world)
         return fail_invalid_program("Fix: the all-gather context needs 1 <= world <= 8 and rank < world, got world=" +
                                     std::to_string(ctx->world) + " rank=" + std::to_string(ctx->rank) + ".");
-    if (!ctx->epoch || !ctx->ticket) return fail_invalid_program("Fix: the all-gather context needs local epoch and ticket words.");
+    if (!ctx->epoch) return fail_invalid_program("Fix: the all-gather context needs a local launch-counter word.");
     for (uint32_t r = 0; r < ctx->world; ++r)
         if (!ctx->peer_out[r] || !ctx->peer_flag[r])
             return fail_invalid_program("Fix: the all-gather context needs a gather buffer and an arrival counter for every rank.");
@@ -935,36 +935,13 @@ int32_t to_gather(const vyb_allgather_ctx* ctx, vybk::GemvAllGather* ag) {
         ag->peer_flag[r] = ctx->peer_flag[r];
     }
     ag->epoch = ctx->epoch;
-    ag->ticket = ctx->ticket;
     return VYB_OK;
 }
 }  // namespace
 
-int32_t vyb_k_int4_gemv_allgather(const void* x_bf16, const void* w_packed, const void* scale_bf16,
-                                  const vyb_allgather_ctx* ctx, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
-                                  uint32_t flags, void* stream, uint32_t* status) {
-    if (!x_bf16 || !w_packed || !scale_bf16) return fail_invalid_program("Fix: pass non-null device pointers.");
-    vybk::GemvAllGather ag;
-    if (int32_t rc = to_gather(ctx, &ag)) return rc;
-    if (!vybk::int4_gemv_supported(m, n, k, group_size))
-        return fail_unsupported("int4 gemv shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
-                                std::to_string(k) + " group=" + std::to_string(group_size) +
-                                " (needs 1 <= m <= 8, group 128, k a multiple of 1024)");
-    if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) |
-         reinterpret_cast<uintptr_t>(scale_bf16)) & 15)
-        return fail_invalid_program("Fix: int4 gemv operands must be 16-byte aligned (bulk copies start on 16-byte boundaries).");
-    int sms = 0;
-    if (int32_t rc = current_sm_count(&sms)) return rc;
-    void* y_local = reinterpret_cast<void*>(ag.peer_out[ag.rank]);
-    return launch_result(vybk::launch_int4_gemv(x_bf16, w_packed, scale_bf16, y_local, m, n, k, 0, sms,
-                                                static_cast<cudaStream_t>(stream), status,
-                                                (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0, &ag),
-                         "int4 gemv with all-gather epilogue");
-}
-
 int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32_t m, uint32_t n, void* stream,
                              uint32_t* status) {
-    vybk::GemvAllGather ag;
+    vybk::PeerGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;
     if (half > 1 || m == 0 || n == 0 || (uint64_t(m) * n) % 8)
         return fail_invalid_program("Fix: all-gather push needs half in {0,1} and m*n a multiple of 8 (16-byte stores).");
@@ -973,7 +950,7 @@ int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32
 }
 
 int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status) {
-    vybk::GemvAllGather ag;
+    vybk::PeerGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;
     return launch_result(vybk::launch_allgather_wait(ag, static_cast<cudaStream_t>(stream), status), "all-gather wait");
 }

@@ -64,22 +64,16 @@ constexpr int X_PITCH = KBLOCK + 16;  // byte pitch of one staged activation row
 constexpr int SMEM_RED = RED_SLOTS * RED_SLOT_FLOATS * 4 + 2048;  // reduction slots; doubles as X staging in the prologue
 constexpr int SMEM_CTRL = 256;
 constexpr int SMEM_TOTAL = SMEM_RING + SMEM_RED + SMEM_CTRL;
-// all-gather launches stage the CTA's outputs (a contiguous row range, up to AG_STAGE_ROWS rows x 8 batch rows of bf16)
-// in shared memory so that ONE warp issues all peer stores and a single system-scope fence per CTA
-constexpr int AG_STAGE_ROWS = 1024;
-constexpr int SMEM_AG_STAGE = AG_STAGE_ROWS * 8 * 2;
-constexpr int SMEM_TOTAL_AG = SMEM_TOTAL + SMEM_AG_STAGE;
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr long long WAIT_CLOCKS = 2000000000ll;  // about a second at boost clocks
 
 static_assert(STAGE_BYTES % 128 == 0, "stage must stay 128-byte aligned");
-static_assert(SMEM_TOTAL_AG <= 232448, "shared memory budget");
+static_assert(SMEM_TOTAL <= 232448, "shared memory budget");
 
 struct Ctrl {
     unsigned long long full[STAGES];
     unsigned long long empty[STAGES];
     unsigned long long red_full[RED_SLOTS];  // 16 arrivals: every warp left its partial of the tile in the slot
-    unsigned long long ag_done;              // 16 arrivals: every warp's peer stores are fenced (all-gather epilogue)
     unsigned int abort_flag;
 };
 static_assert(sizeof(Ctrl) <= SMEM_CTRL, "control block");
@@ -151,9 +145,6 @@ struct Params {
     uint32_t* status;
     unsigned long long* trace;  // optional: per-CTA timeline (64 slots each), tuning aid only
     uint32_t debug;             // tuning aid: bit0 = skip the math, bit1 = split the tile copy in 4
-    // all-gather epilogue (world > 1): every rank stores its outputs straight into every peer's gather buffer
-    // [2][world][m][n] (double-buffered by step parity) over NVLink and then bumps the peer's arrival counter
-    GemvAllGather ag;
 };
 
 template <int LIMBS, bool OUT_F32>
@@ -162,7 +153,6 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     uint8_t* ring = smem;
     float* red = reinterpret_cast<float*>(smem + SMEM_RING);
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + SMEM_RING + SMEM_RED);
-    __nv_bfloat16* ag_stage = reinterpret_cast<__nv_bfloat16*>(smem + SMEM_TOTAL);  // present in all-gather launches only
     volatile unsigned int* abort_flag = &ctrl->abort_flag;
 
     const int warp = threadIdx.x >> 5;
@@ -242,12 +232,6 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     // activations may come from the preceding kernel: everything that reads x or writes y runs after this point,
     // only the (constant) weight stream of the producer warp starts before it
     if (warp != WARPS) asm volatile("griddepcontrol.wait;" ::: "memory");
-    // launches completed so far on this rank (advanced by the last CTA of every all-gather launch) select the buffer half
-    uint32_t ag_epoch = 0, ag_parity = 0;
-    if (p.ag.world != 0 && warp != WARPS) {
-        ag_epoch = *reinterpret_cast<const volatile uint32_t*>(p.ag.epoch);
-        ag_parity = ag_epoch & 1u;
-    }
     if (coop) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -265,7 +249,6 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
                 mbar_init(smem_u32(&ctrl->empty[s]), WARPS);
             }
             for (int s = 0; s < RED_SLOTS; ++s) mbar_init(smem_u32(&ctrl->red_full[s]), WARPS);
-            mbar_init(smem_u32(&ctrl->ag_done), WARPS);
             ctrl->abort_flag = 0;
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -487,16 +470,10 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
             const uint32_t row = i < 2 ? row_lo : row_lo + 8;
             const uint32_t col = 2 * t + (i & 1);
             if (row < r1 && col < p.m) {
-                if constexpr (OUT_F32) {
+                if constexpr (OUT_F32)
                     static_cast<float*>(p.y)[size_t(col) * p.n + row] = vals[i];
-                } else {
-                    const __nv_bfloat16 v = __float2bfloat16_rn(vals[i]);
-                    if (p.ag.world != 0) {
-                        ag_stage[col * AG_STAGE_ROWS + (row - r0)] = v;  // sent to every rank at the end of the kernel
-                    } else {
-                        static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = v;
-                    }
-                }
+                else
+                    static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(vals[i]);
             }
         }
         return true;
@@ -538,120 +515,8 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     if (alive && ntiles > 0 && uint32_t(warp) == (ntiles - 1) % WARPS) alive = reduce_tile(ntiles - 1);
     stamp(31);
     if (!alive && lane == 0 && p.status) atomicOr(p.status, 1u);
-    if (p.ag.world != 0) {
-        // All-gather epilogue. Every warp has left its outputs in the staging area and arrives; warp 0 waits (bounded)
-        // for the 16 warps, checks (bounded) that every peer has completed all earlier launches - then whatever
-        // consumed the buffer half written two launches ago has run, because consumers sit between a peer's
-        // launches in its stream; peers run in step, so this is normally already true - and stores the CTA's row
-        // range into this rank's slice of every rank's gather buffer. One system-scope fence per CTA, then a ticket:
-        // the CTA that takes the last ticket of the launch bumps every peer's arrival counter (all stores of all
-        // CTAs are visible there by then) and advances the local launch counter. The next launch of the stream
-        // may already be streaming its weights meanwhile.
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&ctrl->ag_done));
-        if (warp == 0) {
-            bool ok = mbar_wait(smem_u32(&ctrl->ag_done), 0, abort_flag);
-            if (ok && lane == 0 && p.ag.world > 1) {
-                const volatile uint32_t* arrived = reinterpret_cast<const volatile uint32_t*>(p.ag.peer_flag[p.ag.rank]);
-                const uint32_t want = ag_epoch * (p.ag.world - 1);
-                const long long t0 = clock64();
-                while (int32_t(*arrived - want) < 0) {
-                    if (clock64() - t0 > 4000000000ll) {
-                        if (p.status) atomicOr(p.status, 128u);
-                        break;
-                    }
-                    __nanosleep(64);
-                }
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                const uint32_t rows = r1 - r0;
-                for (uint32_t r = 0; r < p.ag.world; ++r) {
-                    __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.ag.peer_out[r]) +
-                                          (size_t(ag_parity) * p.ag.world + p.ag.rank) * p.m * p.n + r0;
-                    for (uint32_t col = 0; col < p.m; ++col)
-                        for (uint32_t i = lane; i < rows; i += 32) base[size_t(col) * p.n + i] = ag_stage[col * AG_STAGE_ROWS + i];
-                }
-                __threadfence_system();
-                __syncwarp();
-                if (lane == 0) {
-                    const unsigned int ticket = atomicAdd(reinterpret_cast<unsigned int*>(p.ag.ticket), 1u);
-                    if (ticket == gridDim.x - 1) {
-                        *reinterpret_cast<volatile unsigned int*>(p.ag.ticket) = 0;  // next launch starts from zero
-                        __threadfence_system();
-                        for (uint32_t r = 0; r < p.ag.world; ++r)
-                            if (r != p.ag.rank) atomicAdd_system(reinterpret_cast<unsigned int*>(p.ag.peer_flag[r]), 1u);
-                        *reinterpret_cast<volatile uint32_t*>(p.ag.epoch) = ag_epoch + 1;
-                    }
-                }
-            } else if (lane == 0 && p.status) {
-                atomicOr(p.status, 64u);
-            }
-        }
-    }
 }
 
-// Gather completion for a consumer: waits (bounded) until every peer's launches up to the local launch count have
-// bumped the local arrival counter, i.e. every gather started so far on this stream is complete in local memory.
-__global__ void __launch_bounds__(32) allgather_wait_kernel(const GemvAllGather ag, uint32_t* status) {
-    if (threadIdx.x != 0) return;
-    const uint32_t done = *reinterpret_cast<const volatile uint32_t*>(ag.epoch);
-    const volatile uint32_t* arrived = reinterpret_cast<const volatile uint32_t*>(ag.peer_flag[ag.rank]);
-    const uint32_t want = done * (ag.world - 1);
-    const long long t0 = clock64();
-    bool ok = true;
-    while (int32_t(*arrived - want) < 0) {
-        if (clock64() - t0 > 4000000000ll) {  // ~2 s: a missing peer raises a status word instead of a hang
-            ok = false;
-            break;
-        }
-        __nanosleep(100);
-    }
-    __threadfence_system();  // acquire side: the peers' stores are visible to whatever follows in this stream
-    if (!ok && status) atomicOr(status, 128u);
-}
-
-
-// All-gather of a slice that a plain launch has already written into this rank's gather buffer (half `half`): one CTA
-// checks (bounded) that every peer completed all earlier pushes, copies the [m, n] slice into the same place of every
-// peer's buffer with 16-byte stores over NVLink, fences once at system scope, bumps every peer's arrival counter and
-// advances the local counter. Run on a side stream it keeps the collective off the critical path of the next GEMV.
-__global__ void __launch_bounds__(256) allgather_push_kernel(const GemvAllGather ag, uint32_t half, uint32_t m, uint32_t n,
-                                                              uint32_t* status) {
-    __shared__ uint32_t s_epoch;
-    if (threadIdx.x == 0) {
-        const uint32_t done = *reinterpret_cast<const volatile uint32_t*>(ag.epoch);
-        s_epoch = done;
-        if (ag.world > 1) {
-            const volatile uint32_t* arrived = reinterpret_cast<const volatile uint32_t*>(ag.peer_flag[ag.rank]);
-            const uint32_t want = done * (ag.world - 1);
-            const long long t0 = clock64();
-            while (int32_t(*arrived - want) < 0) {
-                if (clock64() - t0 > 4000000000ll) {
-                    if (status) atomicOr(status, 128u);
-                    break;
-                }
-                __nanosleep(64);
-            }
-        }
-    }
-    __syncthreads();
-    const size_t slice_vecs = size_t(m) * n * 2 / 16;
-    const size_t slice_off = (size_t(half) * ag.world + ag.rank) * slice_vecs;
-    const uint4* src = reinterpret_cast<const uint4*>(ag.peer_out[ag.rank]) + slice_off;
-    for (uint32_t r = 0; r < ag.world; ++r) {
-        if (r == ag.rank) continue;
-        uint4* dst = reinterpret_cast<uint4*>(ag.peer_out[r]) + slice_off;
-        for (size_t i = threadIdx.x; i < slice_vecs; i += blockDim.x) dst[i] = src[i];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        for (uint32_t r = 0; r < ag.world; ++r)
-            if (r != ag.rank) atomicAdd_system(reinterpret_cast<unsigned int*>(ag.peer_flag[r]), 1u);
-        *reinterpret_cast<volatile uint32_t*>(ag.epoch) = s_epoch + 1;
-    }
-}
 
 // ---- fallback: any group size dividing k, any batch; warp per output row, plain 32-bit loads -------------------
 __global__ void __launch_bounds__(256) int4_linear_generic_kernel(const uint16_t* __restrict__ x,
@@ -705,7 +570,7 @@ bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
 
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                             uint32_t* status, bool constant_weights, const GemvAllGather* ag) {
+                             uint32_t* status, bool constant_weights) {
     // opt in to the large dynamic shared-memory carve-out once per device
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -714,7 +579,7 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
         cudaError_t e = cudaFuncSetAttribute(int4_gemv_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             SMEM_TOTAL_AG);
+                                             SMEM_TOTAL);
         if (e == cudaSuccess)
             e = cudaFuncSetAttribute(int4_gemv_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return e;
@@ -732,18 +597,12 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     p.status = status;
     p.trace = g_gemv_trace;
     p.debug = g_gemv_debug;
-    p.ag = GemvAllGather{};
-    if (ag) {
-        if (out_f32 || ag->world < 1 || ag->world > 8 || ag->rank >= ag->world) return cudaErrorInvalidValue;
-        p.ag = *ag;
-    }
     const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = ag ? SMEM_TOTAL_AG : SMEM_TOTAL;
-    if (ag && (n + grid - 1) / grid > uint32_t(AG_STAGE_ROWS)) return cudaErrorNotSupported;  // rows per CTA must fit the staging area
+    cfg.dynamicSmemBytes = SMEM_TOTAL;
     cfg.stream = stream;
     cudaLaunchAttribute attr = {};
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -753,19 +612,6 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     cfg.numAttrs = constant_weights ? 1 : 0;
     if (out_f32) return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<3, true>, p);
     return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<2, false>, p);
-}
-
-cudaError_t launch_allgather_push(const GemvAllGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
-                                  uint32_t* status) {
-    if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world || half > 1 || (size_t(m) * n) % 8) return cudaErrorInvalidValue;
-    allgather_push_kernel<<<1, 256, 0, stream>>>(ag, half, m, n, status);
-    return cudaGetLastError();
-}
-
-cudaError_t launch_allgather_wait(const GemvAllGather& ag, cudaStream_t stream, uint32_t* status) {
-    if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world) return cudaErrorInvalidValue;
-    allgather_wait_kernel<<<1, 32, 0, stream>>>(ag, status);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,

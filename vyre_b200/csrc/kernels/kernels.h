@@ -13,22 +13,21 @@ namespace vybk {
 void set_int4_gemv_trace(unsigned long long* device_buffer);  // tuning aid: per-CTA timeline, nullptr = off
 void set_int4_gemv_debug(uint32_t flags);                     // tuning aid: see int4_gemv.cu
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
-// All-gather epilogue of the decode GEMV over peer memory (column-parallel linear, one process per GPU): rank r's
-// outputs go straight into slice r of every rank's gather buffer [2][world][m][n] bf16 (double-buffered by step
-// parity); arrival counters and the step counter are 32-bit words in device memory, zero before the first step.
-struct GemvAllGather {
-    uint32_t world = 0, rank = 0;
-    unsigned long long peer_out[8] = {};   // base of every rank's gather buffer (own rank included)
-    unsigned long long peer_flag[8] = {};  // every rank's arrival counter (own rank: the one the wait kernel polls)
-    unsigned long long epoch = 0;          // local: steps completed
-    unsigned long long ticket = 0;         // local: CTA tickets of the running launch
-};
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                             uint32_t* status, bool constant_weights = false, const GemvAllGather* ag = nullptr);
-cudaError_t launch_allgather_push(const GemvAllGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
+                             uint32_t* status, bool constant_weights = false);
+// ---- all-gather of column-parallel outputs over peer memory (allgather_push.cu) ------------------------------------
+// gather buffers [2][world][m][n] bf16 per rank; arrival counters and the launch counter are 32-bit device words,
+// zero before the first push
+struct PeerGather {
+    uint32_t world = 0, rank = 0;
+    unsigned long long peer_out[8] = {};   // base of every rank's gather buffer (own rank included)
+    unsigned long long peer_flag[8] = {};  // every rank's arrival counter (own rank: the one this rank polls)
+    unsigned long long epoch = 0;          // local: pushes completed
+};
+cudaError_t launch_allgather_push(const PeerGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
                                   uint32_t* status);
-cudaError_t launch_allgather_wait(const GemvAllGather& ag, cudaStream_t stream, uint32_t* status);
+cudaError_t launch_allgather_wait(const PeerGather& ag, cudaStream_t stream, uint32_t* status);
 // any group size dividing k, k % 8 == 0, any m; plain loads, no TMA
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,
                                        uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32,

@@ -37,7 +37,7 @@ class AllGatherCtx(C.Structure):
     """vyb_allgather_ctx: peer addresses of the gather buffers / arrival counters and the local step words."""
 
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("peer_out", C.c_uint64 * 8), ("peer_flag", C.c_uint64 * 8),
-                ("epoch", C.c_uint64), ("ticket", C.c_uint64)]
+                ("epoch", C.c_uint64)]
 
 
 class ResidentHandle(C.Structure):
@@ -171,7 +171,6 @@ _STATUS_FUNCS = {
     "vyb_k_int4_prefill_gemm": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_quantize_per_token_int8": [_P, _P, _P, _U, _U, _P],
     "vyb_k_int8_gemm_i32": [_P, _P, _P, _U, _U, _U, _P, _P],
-    "vyb_k_int4_gemv_allgather": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_allgather_push": [_P, _U, _U, _U, _P, _P],
     "vyb_k_allgather_wait": [_P, _P, _P],
     "vyb_k_moe_route": [_P, _P, _P, _P, _U, _U, _U, _U, _P],

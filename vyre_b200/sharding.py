@@ -253,10 +253,10 @@ def expert_parallel_moe_ffn(x, w_router, ops: KernelOps, experts: int, topk: int
     return out, idx, wts
 
 
-# ---- column-parallel decode GEMV with the all-gather fused into the kernel's epilogue (peer stores over NVLink) ------
+# ---- all-gather of column-parallel outputs by the library's peer-store kernel (NVLink, symmetric memory) -------------
 class PeerAllGather:
-    """Gather buffers for vyb_k_int4_gemv_allgather: [2][world][m][n] bf16 per rank plus a 32-bit arrival counter, in
-    symmetric memory so that every rank holds device addresses of every peer's copy. Step s lands in half s % 2."""
+    """Gather buffers for vyb_k_allgather_push: [2][world][m][n] bf16 per rank plus a 32-bit arrival counter, in
+    symmetric memory so that every rank holds device addresses of every peer's copy. Halves are used alternately."""
 
     def __init__(self, m: int, n: int, group=None):
         import os
@@ -287,15 +287,13 @@ class PeerAllGather:
             self.buf = torch.zeros(total, dtype=torch.uint8, device="cuda")
             self.handle = None
             ptrs = [self.buf.data_ptr()]
-        self.local = torch.zeros(64, dtype=torch.int32, device="cuda")  # [0] steps completed, [16] CTA tickets
+        self.local = torch.zeros(64, dtype=torch.int32, device="cuda")  # [0] pushes completed
         self.ctx = ffi.AllGatherCtx()
         self.ctx.world, self.ctx.rank = self.world, self.rank
         for r in range(self.world):
             self.ctx.peer_out[r] = ptrs[r]
             self.ctx.peer_flag[r] = ptrs[r] + self.data_bytes
         self.ctx.epoch = self.local.data_ptr()
-        self.ctx.ticket = self.local.data_ptr() + 64
-        self.steps = 0
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier(group)  # every counter is zero before anybody launches
@@ -304,16 +302,6 @@ class PeerAllGather:
         """The two [world, m, n] bf16 views of the local gather buffer."""
         t = self.buf[: 2 * self.world * self.m * self.n * 2].view(self.torch.bfloat16)
         return t.view(2, self.world, self.m, self.n)
-
-    def launch(self, x, w, s, k: int, stream, status, flags: int = 0):
-        """One launch on `stream`: GEMV whose epilogue stores into every rank's buffer. Returns the half it fills."""
-        lib = self.ffi.lib()
-        self.ffi.check(lib.vyb_k_int4_gemv_allgather(x.data_ptr(), w.data_ptr(), s.data_ptr(), C.byref(self.ctx), self.m,
-                                                     self.n, k, 128, flags, C.c_void_p(stream),
-                                                     C.c_void_p(status.data_ptr())))
-        half = self.steps & 1
-        self.steps += 1
-        return half
 
     def local_slice(self, half: int):
         """This rank's [m, n] slice of a buffer half: the output of a plain GEMV that `push` then sends to the peers."""
