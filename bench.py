@@ -308,11 +308,14 @@ def run_native(args) -> None:
     stream = torch.cuda.Stream()
 
     side = torch.cuda.Stream()
+    # with a concurrent push kernel the GEMV leaves one SM free: sharing an SM with the weight stream (140 KB of bulk
+    # copies in flight) made every memory access of the push wait microseconds
+    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS | (ffi.LAUNCH_LEAVE_ONE_SM if world > 1 else 0)
 
     def launch(c: int, out=None):
         # weights are graph constants: the launch may overlap the tail of the previous one (see the header)
         ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), (y if out is None else out).data_ptr(), m, N_OUT, K_IN,
-                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
+                                       GROUP, ffi.DT_BF16, gemv_flags,
                                        C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
 
     with torch.cuda.stream(stream):

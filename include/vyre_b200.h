@@ -406,6 +406,9 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
  * precedes this launch in the stream; the kernel is then launched with programmatic stream serialization and
  * starts streaming them while the preceding kernel drains. Activations and outputs still wait for it. */
 #define VYB_LAUNCH_CONSTANT_WEIGHTS 1u
+/* Launch on one SM fewer than the device has, so that a small kernel of another stream (vyb_k_allgather_push) finds
+ * an SM whose memory pipeline is not saturated by the weight stream. */
+#define VYB_LAUNCH_LEAVE_ONE_SM 2u
 int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                            uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,
                            void* stream, uint32_t* status);

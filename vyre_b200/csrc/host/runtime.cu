@@ -885,6 +885,7 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
         cudaGetLastError();
         return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
     }
+    if ((flags & VYB_LAUNCH_LEAVE_ONE_SM) && sms > 1) --sms;  // room for a concurrent small kernel (the all-gather push)
     e = vybk::launch_int4_gemv(x_bf16, w_packed, scale_bf16, y, m, n, k, out_dtype == VYB_DT_F32 ? 1u : 0u, sms,
                                static_cast<cudaStream_t>(stream), status, (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0);
     if (e != cudaSuccess) {

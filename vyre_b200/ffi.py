@@ -16,6 +16,7 @@ DT_U32, DT_I32, DT_F16, DT_BF16, DT_F32, DT_U8, DT_I8, DT_I4 = 0x01, 0x02, 0x09,
 ACCESS_READ_ONLY, ACCESS_READ_WRITE, ACCESS_OUTPUT, ACCESS_WORKGROUP = 0, 1, 2, 3
 BIND_HOST, BIND_RESIDENT = 0, 1
 LAUNCH_CONSTANT_WEIGHTS = 1
+LAUNCH_LEAVE_ONE_SM = 2
 
 ERR_DEVICE_OUT_OF_MEMORY = 1001
 ERR_UNSUPPORTED_FEATURE = 1002
