@@ -54,18 +54,18 @@ constexpr int B_BYTES = (MAX_BN / 2) * BK * 2;       // 16 KB: this CTA's half o
 constexpr int RAW_BYTES = (MAX_BN / 2) * RAW_KB * (BK / 2);  // 16 KB: 128 rows x 128 bytes (256 k), 128-byte swizzle
 constexpr int B_RING = 0, A_RING = B_STAGES * B_BYTES, RAW_RING = A_RING + A_STAGES * A_BYTES;
 constexpr int RING_BYTES = RAW_RING + RAW_STAGES * RAW_BYTES;
-constexpr int DEQ_GROUPS = 2, DEQ_GROUP_WARPS = 4;
+constexpr int DEQ_GROUPS = 3, DEQ_GROUP_WARPS = 4;
 // Warp roles are laid out by scheduler (warp id % 4 selects the SM sub-partition): the two single-thread roles that
 // pace the pipeline, TMA (warp 0) and MMA (warp 4), share sub-partition 0 with only one epilogue warp, so the
 // instruction-heavy dequantisation warps (sub-partitions 1-3) never compete with them for issue slots.
 constexpr int TMA_WARP = 0, MMA_WARP = 4;
-constexpr int NUM_WARPS = 16;
+constexpr int NUM_WARPS = 20;
 constexpr int THREADS = NUM_WARPS * 32;
-// epilogue: warps 8 (TMEM lanes 0-31), 1, 2, 3; dequant: warps 5,6,7, 9,10,11, 13,14; warps 12 and 15 idle
+// epilogue: warps 8 (TMEM lanes 0-31), 1, 2, 3; dequant: the twelve warps >= 5 off sub-partition 0; warps 12, 16 idle
 __device__ __forceinline__ bool is_epilogue_warp(int w) { return w == 8 || (w >= 1 && w <= 3); }
-__device__ __forceinline__ int dequant_index(int w) {  // 0..7, or -1
-    if ((w & 3) == 0 || w < 5 || w > 14) return -1;
-    return (w - 5) - (w > 8 ? 1 : 0) - (w > 12 ? 1 : 0);
+__device__ __forceinline__ int dequant_index(int w) {  // 0..11, or -1
+    if ((w & 3) == 0 || w < 5) return -1;
+    return (w - 5) - ((w - 4) >> 2);  // skip the warps of sub-partition 0 (8, 12, 16)
 }
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = RING_BYTES + 1024 + 512;
@@ -158,7 +158,7 @@ int4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
         for (int s = 0; s < RAW_STAGES; ++s) {
             mbar_init(smem_u32(&bars->raw_full[s]), 1);
-            mbar_init(smem_u32(&bars->raw_empty[s]), DEQ_GROUPS * DEQ_GROUP_WARPS * (RAW_KB / DEQ_GROUPS));
+            mbar_init(smem_u32(&bars->raw_empty[s]), RAW_KB * DEQ_GROUP_WARPS);  // each stage: the four warps of one group
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(smem_u32(&bars->acc_full[a]), 1);
@@ -336,9 +336,8 @@ int4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
     } else if (deq_idx >= 0) {
         // ------------------------------------ dequant warps ------------------------------------
-        const uint32_t dgroup = uint32_t(deq_idx) / DEQ_GROUP_WARPS;  // takes the stages with (stage & 1) == dgroup
+        const uint32_t dgroup = uint32_t(deq_idx) / DEQ_GROUP_WARPS;  // takes the stages with stage % DEQ_GROUPS == dgroup
         const uint32_t r = (uint32_t(deq_idx) % DEQ_GROUP_WARPS) * 32 + lane;  // weight row of this thread
-        const uint32_t n_own = k_blocks / DEQ_GROUPS;  // stages of one tile this warp handles (k_blocks % 4 == 0)
         const uint32_t gdiv = p.group / BK;            // stages per scale group
         uint32_t it_base = 0, raw_base = 0;
         bool ok = true;
@@ -348,16 +347,19 @@ int4_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const uint16_t* srow = p.scales + size_t(row_valid ? weight_row0(c) + r : 0) * groups;
             // Each stage needs one group scale per row. The loads run four of this warp's stages ahead (a queue of
             // four registers): one stage ahead is not enough, an L2 hit costs more than a stage takes.
+            // this group's stages of the tile: global stage numbers congruent to dgroup modulo DEQ_GROUPS
+            const uint32_t kb_first = (dgroup + DEQ_GROUPS - it_base % DEQ_GROUPS) % DEQ_GROUPS;
+            const uint32_t n_own = kb_first < k_blocks ? (k_blocks - kb_first + DEQ_GROUPS - 1) / DEQ_GROUPS : 0u;
             uint32_t q[4];
 #pragma unroll
             for (uint32_t d = 0; d < 4; ++d)
-                q[d] = (row_valid && d < n_own) ? uint32_t(srow[(dgroup + DEQ_GROUPS * d) / gdiv]) : 0u;
+                q[d] = (row_valid && d < n_own) ? uint32_t(srow[(kb_first + DEQ_GROUPS * d) / gdiv]) : 0u;
             for (uint32_t j0 = 0; j0 < n_own && ok; j0 += 4) {
 #pragma unroll
               for (uint32_t u = 0; u < 4; ++u) {
                 const uint32_t j = j0 + u;
                 if (j >= n_own || !ok) break;
-                const uint32_t kb = DEQ_GROUPS * j + dgroup, it = it_base + kb;
+                const uint32_t kb = DEQ_GROUPS * j + kb_first, it = it_base + kb;
                 const uint32_t r_it = raw_base + kb / RAW_KB, rs = r_it % RAW_STAGES, bs = it % B_STAGES;
                 const uint32_t sv = q[u];
                 const uint32_t s2 = sv | (sv << 16);  // this stage's group scale in both bf16 halves
