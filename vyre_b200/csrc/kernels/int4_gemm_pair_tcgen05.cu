@@ -10,14 +10,15 @@
 // weights that are dequantised, the bf16 tile bytes written to shared memory and the operand bytes the tensor
 // core reads from it - the three things that bound the single-CTA kernel.
 //
-// Roles per CTA (16 warps, placed by SM sub-partition = warp id % 4): warp 0 TMA producer (activation box -> the
+// Roles per CTA (20 warps, placed by SM sub-partition = warp id % 4): warp 0 TMA producer (activation box -> the
 // LEADER's barrier with the pair form of the tensor load; packed-weight box -> a local barrier), warp 4 TMEM owner
-// (+ MMA issuer in the leader); warps 8, 1, 2, 3 epilogue (tcgen05.ld -> global); warps 5-7, 9-11, 13, 14
-// dequantisation in two groups of four: group g takes the stages with (stage & 1) == g, one weight row per
-// thread, so two stages are always in flight. Activation and dequantised tiles share a 5-stage ring of 64 k with one
-// "consumed" barrier per CTA (two tcgen05.commit per stage); packed weights arrive 256 k at a time as 128-byte
-// swizzled rows (3 slots) - 32-byte rows cost four times the TMA requests and starved the pipeline. Group scales
-// are prefetched four stages ahead into registers (an L2 hit takes longer than a stage).
+// (+ MMA issuer in the leader); warps 8, 1, 2, 3 epilogue (tcgen05.ld -> global); the twelve warps >= 5 outside
+// sub-partition 0 dequantise in three groups of four: group g takes the stages with stage % 3 == g, one weight row
+// per thread, so three stages are always in flight (one group per stage could not keep up with the MMAs).
+// Activation and dequantised tiles share a 6-stage ring of 64 k with one "consumed" barrier per CTA (two
+// tcgen05.commit per stage); packed weights arrive 256 k at a time as 128-byte swizzled rows (2 slots) - 32-byte
+// rows cost four times the TMA requests and starved the pipeline. Group scales are prefetched four stages ahead
+// into registers (an L2 hit takes longer than a stage).
 // In glu mode the leader dequantises the gate rows and the peer the up rows of the same 128 output columns, so the
 // epilogue finds g in accumulator columns [0, BN/2) and u in [BN/2, BN) of its own TMEM.
 // BN is 256 unless the problem is narrower (a multiple of 32, or 64 for glu).
@@ -46,8 +47,8 @@ constexpr int BM = 128;  // activation rows per CTA (256 per pair)
 constexpr int BK = 64;   // bf16 elements per stage row (128 bytes)
 constexpr int UMMA_K = 16;
 constexpr int MAX_BN = 256;
-constexpr int STAGES = 5;  // activation and dequantised tiles share one ring index and one 'consumed' barrier
-constexpr int A_STAGES = STAGES, B_STAGES = STAGES, RAW_STAGES = 3, RAW_AHEAD = 1;
+constexpr int STAGES = 6;  // activation and dequantised tiles share one ring index and one 'consumed' barrier
+constexpr int A_STAGES = STAGES, B_STAGES = STAGES, RAW_STAGES = 2, RAW_AHEAD = 1;
 constexpr int RAW_KB = 4;  // k-blocks per packed-weight load: 128-byte rows, a quarter of the TMA requests of 32-byte rows
 constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int B_BYTES = (MAX_BN / 2) * BK * 2;       // 16 KB: this CTA's half of the dequantised tile
