@@ -366,13 +366,14 @@ def run_native(args) -> None:
         with torch.cuda.stream(stream):
             graph.replay()
     stream.synchronize()
-    if dist:
-        dist.barrier()
-    torch.cuda.synchronize()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
+    # the barrier comes after the sampler's start-up so that every rank enters the timed region together
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
     lo = sampler.mark()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
