@@ -481,6 +481,28 @@ int32_t vyb_k_moe_experts_int4(const void* x_sorted, const void* w13, const void
                                void* stream, uint32_t* status);
 int32_t vyb_k_moe_combine(const void* y_rows, const void* pos_u32, const void* routing_w, void* out_bf16, uint32_t tokens,
                           uint32_t hidden, uint32_t topk, void* stream);
+/* Expert-parallel form of the MoE FFN layer, one process per GPU, with dispatch and combine done by this library's
+ * kernels over peer memory (NVLink) - no host read-back, no NCCL call inside the layer (no counterpart in the
+ * reference, whose backends are single-device; experts are independent programs, expert_mlp.rs:18-150, routing is
+ * per token, gating.rs:19-69). Rank r owns experts [r * E / world, (r + 1) * E / world): w13 / s13 / w2 / s2 hold only
+ * those. Every rank passes its own tokens; results and routing come back for exactly those tokens. The call is
+ * collective: every rank must enqueue it the same number of times. Device-side waits are bounded (~2 s, status bit
+ * 256). vyb_k_moe_ep_sizes fills the offsets of ctx and returns the byte sizes of the symmetric region (allocated
+ * so that every rank can address every peer's copy, zero-filled; peer_base[r] = its address as seen from this rank)
+ * and of the local scratch (zero-filled once); tokens_total bounds the rows that can land on one rank. */
+typedef struct vyb_moe_ep_ctx {
+    uint32_t world, rank;
+    uint64_t peer_base[8];
+    uint64_t off_counts, off_flags, off_src, off_xg, off_yhome;
+} vyb_moe_ep_ctx;
+int32_t vyb_k_moe_ep_sizes(uint32_t tokens_local_max, uint32_t tokens_total, uint32_t hidden, uint32_t inter,
+                           uint32_t experts, uint32_t topk, uint32_t world, vyb_moe_ep_ctx* ctx, uint64_t* symmetric_bytes,
+                           uint64_t* local_bytes);
+int32_t vyb_k_moe_ep_ffn_int4(const vyb_moe_ep_ctx* ctx, const void* x_bf16, const void* w_router_bf16, const void* w13,
+                              const void* s13, const void* w2, const void* s2, void* out_bf16, void* routing_idx,
+                              void* routing_w, void* local_scratch, uint32_t tokens, uint32_t tokens_total, uint32_t hidden,
+                              uint32_t inter, uint32_t experts, uint32_t topk, uint32_t group_size, void* stream,
+                              uint32_t* status);
 /* No counterpart in the reference. vyb_k_quantize_per_token_int8 followed by vyb_k_int8_gemm_i32 (x_scale_f32 [m],
  * y_i32 [m,n]) for callers that must not allocate device memory: the quantised activations go to a fixed 8 MiB
  * device array that belongs to the loaded library, so m * k <= 8388608 (larger shapes are InvalidProgram). All

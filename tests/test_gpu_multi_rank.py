@@ -68,6 +68,16 @@ def _worker(rank: int, world: int, port: int, q):
         assert torch.equal(idx, ref_idx[t0:t1]) and torch.equal(wts, ref_w[t0:t1])
         assert torch.equal(out.view(torch.int16), ref_out[t0:t1].view(torch.int16))
 
+        # ---- the same layer with device-side dispatch / combine over peer memory: several layers in a row ------------
+        dep = sharding.DeviceExpertParallel(twr, ops.w13, ops.s13, ops.w2, ops.s2, hidden, inter, experts, topk,
+                                            tokens_local_max=t1 - t0, tokens_total=tokens)
+        for rep in range(3):
+            out2, idx2, wts2 = dep.forward(tx[t0:t1].contiguous())
+            torch.cuda.synchronize()
+            assert dep.status.cpu().tolist() == [0, 0, 0, 0], f"layer {rep}"
+            assert torch.equal(idx2, ref_idx[t0:t1]) and torch.equal(wts2, ref_w[t0:t1])
+            assert torch.equal(out2.view(torch.int16), ref_out[t0:t1].view(torch.int16)), f"layer {rep}"
+
         # ---- column-parallel dynamic int8 linear + all-gather ----------------------------------------------------
         m, n, k = 256, 1000, 512
         g = torch.Generator().manual_seed(5)

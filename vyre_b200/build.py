@@ -38,6 +38,7 @@ SOURCES = {
     "kernels/int4_gemm_pair_tcgen05.cu": [],
     "kernels/moe_ffn.cu": [],
     "kernels/allgather_push.cu": [],
+    "kernels/moe_ep.cu": [],
     "kernels/int8_dynamic_static_scratch.cu": [],
 }
 

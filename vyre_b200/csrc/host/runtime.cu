@@ -1049,6 +1049,54 @@ int32_t vyb_k_moe_combine(const void* y_rows, const void* pos_u32, const void* r
                          "moe_combine");
 }
 
+int32_t vyb_k_moe_ep_sizes(uint32_t tokens_local_max, uint32_t tokens_total, uint32_t hidden, uint32_t inter,
+                           uint32_t experts, uint32_t topk, uint32_t world, vyb_moe_ep_ctx* ctx, uint64_t* symmetric_bytes,
+                           uint64_t* local_bytes) {
+    if (!ctx || !symmetric_bytes || !local_bytes) return fail_invalid_program("Fix: pass non-null out-pointers.");
+    if (world < 1 || world > 8 || experts == 0 || experts % world || topk == 0 || tokens_total == 0 || tokens_local_max == 0)
+        return fail_invalid_program("Fix: expert-parallel sizes need 1 <= world <= 8, experts divisible by world, nonzero tokens and topk.");
+    vybk::MoeEp c;
+    size_t total = 0;
+    vybk::moe_ep_symmetric_layout(tokens_local_max, tokens_total, hidden, experts, topk, world, &c, &total);
+    ctx->off_counts = c.off_counts;
+    ctx->off_flags = c.off_flags;
+    ctx->off_src = c.off_src;
+    ctx->off_xg = c.off_xg;
+    ctx->off_yhome = c.off_yhome;
+    *symmetric_bytes = total;
+    *local_bytes = vybk::moe_ep_local_bytes(tokens_local_max, tokens_total, hidden, inter, experts, topk, world);
+    return VYB_OK;
+}
+
+int32_t vyb_k_moe_ep_ffn_int4(const vyb_moe_ep_ctx* ctx, const void* x_bf16, const void* w_router_bf16, const void* w13,
+                              const void* s13, const void* w2, const void* s2, void* out_bf16, void* routing_idx,
+                              void* routing_w, void* local_scratch, uint32_t tokens, uint32_t tokens_total, uint32_t hidden,
+                              uint32_t inter, uint32_t experts, uint32_t topk, uint32_t group_size, void* stream,
+                              uint32_t* status) {
+    if (!ctx || !x_bf16 || !w_router_bf16 || !w13 || !s13 || !w2 || !s2 || !out_bf16 || !routing_idx || !routing_w || !local_scratch)
+        return fail_invalid_program("Fix: pass non-null device pointers and context.");
+    if (ctx->world < 1 || ctx->world > 8 || ctx->rank >= ctx->world)
+        return fail_invalid_program("Fix: the expert-parallel context needs 1 <= world <= 8 and rank < world.");
+    vybk::MoeEp c;
+    c.world = ctx->world;
+    c.rank = ctx->rank;
+    for (uint32_t r = 0; r < 8; ++r) c.peer_base[r] = ctx->peer_base[r];
+    for (uint32_t r = 0; r < ctx->world; ++r)
+        if (!c.peer_base[r]) return fail_invalid_program("Fix: the expert-parallel context needs the symmetric region of every rank.");
+    c.off_counts = ctx->off_counts;
+    c.off_flags = ctx->off_flags;
+    c.off_src = ctx->off_src;
+    c.off_xg = ctx->off_xg;
+    c.off_yhome = ctx->off_yhome;
+    int sms = 0;
+    if (int32_t rc = current_sm_count(&sms)) return rc;
+    return launch_result(vybk::launch_moe_ep_ffn(c, x_bf16, w_router_bf16, w13, s13, w2, s2, out_bf16,
+                                                 static_cast<uint32_t*>(routing_idx), static_cast<float*>(routing_w),
+                                                 local_scratch, tokens, tokens_total, hidden, inter, experts, topk, group_size,
+                                                 sms, static_cast<cudaStream_t>(stream), status),
+                         "expert-parallel moe_ffn_int4");
+}
+
 int32_t vyb_k_moe_ffn_int4_scratch_bytes(uint32_t tokens, uint32_t hidden, uint32_t inter, uint32_t experts,
                                          uint32_t topk, uint64_t* bytes) {
     if (!bytes) return fail_invalid_program("Fix: pass a non-null byte-count out-pointer.");

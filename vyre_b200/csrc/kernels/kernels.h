@@ -74,6 +74,23 @@ cudaError_t launch_moe_experts_int4(const void* x_sorted, const void* w13, const
 cudaError_t launch_moe_combine(const void* y_rows, const uint32_t* pos, const float* routing_w, void* out_bf16,
                                uint32_t tokens, uint32_t hidden, uint32_t topk, int sm_count, cudaStream_t stream);
 
+// ---- expert-parallel MoE FFN with device-side dispatch / combine over peer memory (moe_ep.cu) -----------------------
+struct MoeEp {
+    uint32_t world = 0, rank = 0;
+    unsigned long long peer_base[8] = {};  // base of every rank's symmetric region (own rank included)
+    unsigned long long off_counts = 0, off_flags = 0, off_src = 0, off_xg = 0, off_yhome = 0;  // same on every rank
+};
+uint32_t moe_ep_max_rows(uint32_t tokens_total, uint32_t experts, uint32_t topk, uint32_t world);
+void moe_ep_symmetric_layout(uint32_t tokens_local_max, uint32_t tokens_total, uint32_t hidden, uint32_t experts,
+                             uint32_t topk, uint32_t world, MoeEp* c, size_t* total_bytes);
+size_t moe_ep_local_bytes(uint32_t tokens_local_max, uint32_t tokens_total, uint32_t hidden, uint32_t inter, uint32_t experts,
+                          uint32_t topk, uint32_t world);
+cudaError_t launch_moe_ep_ffn(const MoeEp& c, const void* x_bf16, const void* w_router_bf16, const void* w13, const void* s13,
+                              const void* w2, const void* s2, void* out_bf16, uint32_t* routing_idx, float* routing_w,
+                              void* local_scratch, uint32_t tokens, uint32_t tokens_total, uint32_t hidden, uint32_t inter,
+                              uint32_t experts, uint32_t topk, uint32_t group, int sm_count, cudaStream_t stream,
+                              uint32_t* status);
+
 // ---- int8 x int8 -> int32 GEMM on tcgen05 + per-token activation quantiser (int8_gemm_tcgen05.cu) --------------
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,

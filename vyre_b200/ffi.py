@@ -41,6 +41,13 @@ class AllGatherCtx(C.Structure):
                 ("epoch", C.c_uint64)]
 
 
+class MoeEpCtx(C.Structure):
+    """vyb_moe_ep_ctx: peer addresses of the symmetric regions and the offsets inside them."""
+
+    _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("peer_base", C.c_uint64 * 8), ("off_counts", C.c_uint64),
+                ("off_flags", C.c_uint64), ("off_src", C.c_uint64), ("off_xg", C.c_uint64), ("off_yhome", C.c_uint64)]
+
+
 class ResidentHandle(C.Structure):
     _fields_ = [("owner", C.c_uint64), ("id", C.c_uint64)]
 
@@ -178,6 +185,8 @@ _STATUS_FUNCS = {
     "vyb_k_rows_gather_bf16": [_P, _P, _P, _U, _U, _P],
     "vyb_k_moe_experts_int4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_moe_combine": [_P, _P, _P, _P, _U, _U, _U, _P],
+    "vyb_k_moe_ep_sizes": [_U, _U, _U, _U, _U, _U, _U, _P, _P, _P],
+    "vyb_k_moe_ep_ffn_int4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_moe_ffn_int4_scratch_bytes": [_U, _U, _U, _U, _U, _P],
     "vyb_k_moe_ffn_int4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, C.c_uint64, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_linear_int8_dynamic_static_scratch": [_P, _P, _P, _P, _U, _U, _U, _P, _P],

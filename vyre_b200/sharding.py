@@ -316,3 +316,69 @@ class PeerAllGather:
         """Bounded device-side wait on `stream` until every gather launched so far is complete in local memory."""
         self.ffi.check(self.ffi.lib().vyb_k_allgather_wait(C.byref(self.ctx), C.c_void_p(stream),
                                                            C.c_void_p(status.data_ptr())))
+
+
+# ---- expert-parallel MoE FFN with device-side dispatch / combine (peer stores over NVLink, symmetric memory) --------
+class DeviceExpertParallel:
+    """One MoE FFN layer over the ranks of a group with no host read-back: vyb_k_moe_ep_ffn_int4.
+
+    Holds the symmetric region (count matrix, arrival counters, expert-sorted activations, return addresses, per-pair
+    results) and the local scratch. `w13`, `s13`, `w2`, `s2` are this rank's experts only. Collective: every rank
+    calls `forward` the same number of times."""
+
+    def __init__(self, w_router, w13, s13, w2, s2, hidden: int, inter: int, experts: int, topk: int, tokens_local_max: int,
+                 tokens_total: int, group_size: int = 128, group=None):
+        import os
+
+        import torch
+        import torch.distributed as dist
+
+        from . import ffi
+
+        self.ffi, self.torch = ffi, torch
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.w_router, self.w13, self.s13, self.w2, self.s2 = w_router, w13, s13, w2, s2
+        self.hidden, self.inter, self.experts, self.topk, self.group_size = hidden, inter, experts, topk, group_size
+        self.tokens_local_max, self.tokens_total = tokens_local_max, tokens_total
+        self.ctx = ffi.MoeEpCtx()
+        sym_bytes, local_bytes = C.c_uint64(0), C.c_uint64(0)
+        ffi.check(ffi.lib().vyb_k_moe_ep_sizes(tokens_local_max, tokens_total, hidden, inter, experts, topk, self.world,
+                                               C.byref(self.ctx), C.byref(sym_bytes), C.byref(local_bytes)))
+        if self.world > 1:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings are all that is needed
+            import torch.distributed._symmetric_memory as symm
+
+            self.region = symm.empty(sym_bytes.value, dtype=torch.uint8, device="cuda")
+            self.region.zero_()
+            torch.cuda.synchronize()
+            self.handle = symm.rendezvous(self.region, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.region = torch.zeros(sym_bytes.value, dtype=torch.uint8, device="cuda")
+            self.handle = None
+            ptrs = [self.region.data_ptr()]
+        self.ctx.world, self.ctx.rank = self.world, self.rank
+        for r in range(self.world):
+            self.ctx.peer_base[r] = ptrs[r]
+        self.local = torch.zeros(local_bytes.value, dtype=torch.uint8, device="cuda")
+        self.status = torch.zeros(4, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group)  # every counter is zero before anybody launches
+
+    def forward(self, x, stream=None):
+        """x: this rank's tokens [tokens, hidden] bf16. Returns (out bf16 [tokens, hidden], idx int32, wts f32)."""
+        torch = self.torch
+        tokens = x.shape[0]
+        if tokens > self.tokens_local_max:
+            raise ValueError(f"{tokens} tokens exceed the {self.tokens_local_max} this instance was sized for")
+        out = torch.empty((tokens, self.hidden), dtype=torch.bfloat16, device="cuda")
+        idx = torch.empty((tokens, self.topk), dtype=torch.int32, device="cuda")
+        wts = torch.empty((tokens, self.topk), dtype=torch.float32, device="cuda")
+        s = torch.cuda.current_stream().cuda_stream if stream is None else stream
+        self.ffi.check(self.ffi.lib().vyb_k_moe_ep_ffn_int4(
+            C.byref(self.ctx), x.data_ptr(), self.w_router.data_ptr(), self.w13.data_ptr(), self.s13.data_ptr(),
+            self.w2.data_ptr(), self.s2.data_ptr(), out.data_ptr(), idx.data_ptr(), wts.data_ptr(), self.local.data_ptr(),
+            tokens, self.tokens_total, self.hidden, self.inter, self.experts, self.topk, self.group_size, C.c_void_p(s),
+            C.c_void_p(self.status.data_ptr())))
+        return out, idx, wts
