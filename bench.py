@@ -562,11 +562,20 @@ def run_moe_ep(args) -> None:
     s13 = (torch.rand((local, 2, inter, hidden // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
     w2 = torch.randint(0, 256, (local, hidden, inter // 2), dtype=torch.uint8, device="cuda")
     s2 = (torch.rand((local, hidden, inter // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
-    ops = sharding.KernelOps(w13, s13, w2, s2, hidden, inter, local, GROUP)
-    max_rows = ((tokens_total * topk + 255) // 256) * 256 + local * 256  # worst case: every pair lands on this rank
+    if args.ep == "host":
+        # exchange planned on the host (one read-back of the routing), rows moved by NCCL all-to-all
+        ops = sharding.KernelOps(w13, s13, w2, s2, hidden, inter, local, GROUP)
+        max_rows = ((tokens_total * topk + 255) // 256) * 256 + local * 256  # worst case: every pair lands on this rank
 
-    def step():
-        return sharding.expert_parallel_moe_ffn(x, wr, ops, experts, topk, max_rows=max_rows)
+        def step():
+            return sharding.expert_parallel_moe_ffn(x, wr, ops, experts, topk, max_rows=max_rows)
+    else:
+        # dispatch and combine by the library's own kernels over peer memory, nothing read back by the host
+        ops = sharding.DeviceExpertParallel(wr, w13, s13, w2, s2, hidden, inter, experts, topk, tokens_local_max=tokens,
+                                            tokens_total=tokens_total, group_size=GROUP)
+
+        def step():
+            return ops.forward(x)
 
     for _ in range(max(3, args.warmup)):
         step()
@@ -595,7 +604,7 @@ def run_moe_ep(args) -> None:
             "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16xint4->f32", "data": "synthetic",
             "config": {"workload": f"int4 MoE FFN layer, {tokens_total} tokens, hidden {hidden}, inter {inter}, {experts} experts "
-                                   f"top-{topk} (config 4)", "parallelism": f"expert-parallel x{world}, NCCL all-to-all (dispatch + combine)",
+                                   f"top-{topk} (config 4)", "parallelism": f"expert-parallel x{world}, " + ("host-planned NCCL all-to-all" if args.ep == "host" else "device-side dispatch/combine over peer memory (NVLink)"),
                        "tokens_per_rank": tokens, "experts_per_rank": local},
             "expert_tflops": flops / (ms * 1e-3) / 1e12}))
 
@@ -615,6 +624,8 @@ def main() -> None:
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
     ap.add_argument("--workload", default="gemv", choices=["gemv", "moe"],
                     help="gemv: the headline decode GEMV; moe: the expert-parallel MoE FFN layer (--shape TOKENS INTER HIDDEN)")
+    ap.add_argument("--ep", default="device", choices=["device", "host"],
+                    help="--workload moe: device-side dispatch/combine over peer memory, or host-planned NCCL all-to-all")
     ap.add_argument("--quick", action="store_true",
                     help="kernel-only run without graphs, end-to-end leg or CPU baseline (the case profiled under ncu)")
     args = ap.parse_args()
