@@ -21,8 +21,11 @@ namespace {
 
 constexpr long long WAIT_CLOCKS = 4000000000ll;
 
-__device__ __forceinline__ bool wait_arrivals(const PeerGather& ag, uint32_t launches) {
+// a wait that has run out once is not repeated: later calls return at once, so a broken run ends quickly with its
+// status word set instead of spending the clock limit on every launch
+__device__ __forceinline__ bool wait_arrivals(const PeerGather& ag, uint32_t launches, const uint32_t* status) {
     if (ag.world <= 1) return true;
+    if (status && (*reinterpret_cast<const volatile uint32_t*>(status) & 128u)) return false;
     const volatile uint32_t* arrived = reinterpret_cast<const volatile uint32_t*>(ag.peer_flag[ag.rank]);
     const uint32_t want = launches * (ag.world - 1);
     const long long t0 = clock64();
@@ -39,7 +42,7 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PeerGather ag
     if (threadIdx.x == 0) {
         const uint32_t done = *reinterpret_cast<const volatile uint32_t*>(ag.epoch);
         s_epoch = done;
-        if (!wait_arrivals(ag, done) && status) atomicOr(status, 128u);
+        if (!wait_arrivals(ag, done, status) && status) atomicOr(status, 128u);
     }
     __syncthreads();
     const size_t slice_vecs = size_t(m) * n * 2 / 16;
@@ -62,7 +65,7 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PeerGather ag
 __global__ void __launch_bounds__(32) allgather_wait_kernel(const PeerGather ag, uint32_t* status) {
     if (threadIdx.x != 0) return;
     const uint32_t done = *reinterpret_cast<const volatile uint32_t*>(ag.epoch);
-    const bool ok = wait_arrivals(ag, done);
+    const bool ok = wait_arrivals(ag, done, status);
     __threadfence_system();  // acquire side: the peers' stores are visible to whatever follows in this stream
     if (!ok && status) atomicOr(status, 128u);
 }

@@ -49,7 +49,10 @@ __device__ __forceinline__ uint8_t* sym(const MoeEp& c, uint32_t rank, unsigned 
 __device__ __forceinline__ uint32_t* flag_of(const MoeEp& c, uint32_t rank, uint32_t which) {
     return reinterpret_cast<uint32_t*>(sym(c, rank, c.off_flags)) + which;
 }
-__device__ bool wait_flag(const MoeEp& c, uint32_t which, uint32_t want) {
+// a wait that has run out once is not repeated: later calls return at once, so a broken run ends quickly with its
+// status word set instead of spending the clock limit in every phase of every layer
+__device__ bool wait_flag(const MoeEp& c, uint32_t which, uint32_t want, const uint32_t* status) {
+    if (status && (*reinterpret_cast<const volatile uint32_t*>(status) & 256u)) return false;
     const volatile uint32_t* f = flag_of(c, c.rank, which);
     const long long t0 = clock64();
     while (int32_t(*f - want) < 0) {
@@ -92,7 +95,7 @@ ep_plan_kernel(const MoeEp c, const Local* __restrict__ local, const uint32_t* _
     __shared__ uint32_t s_warp_cnt[MAX_EXPERTS][32];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t el = experts / c.world;
-    if (tid == 0 && !wait_flag(c, FLAG_COUNT, (local->epoch + 1) * c.world) && status) atomicOr(status, 256u);
+    if (tid == 0 && !wait_flag(c, FLAG_COUNT, (local->epoch + 1) * c.world, status) && status) atomicOr(status, 256u);
     __syncthreads();
     const volatile uint32_t* counts = reinterpret_cast<const volatile uint32_t*>(sym(c, c.rank, c.off_counts));
     for (uint32_t i = tid; i < c.world * experts; i += blockDim.x) s_counts[i / experts][i % experts] = counts[i];
@@ -214,7 +217,7 @@ __global__ void __launch_bounds__(32)
 ep_wait_kernel(const MoeEp c, Local* local, uint32_t which, uint32_t advance_epoch, uint32_t* status) {
     if (threadIdx.x != 0) return;
     const uint32_t e = *reinterpret_cast<volatile uint32_t*>(&local->epoch);
-    if (!wait_flag(c, which, (e + 1) * c.world) && status) atomicOr(status, 256u);
+    if (!wait_flag(c, which, (e + 1) * c.world, status) && status) atomicOr(status, 256u);
     __threadfence_system();
     if (advance_epoch) *reinterpret_cast<volatile uint32_t*>(&local->epoch) = e + 1;
 }
