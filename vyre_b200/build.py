@@ -34,6 +34,7 @@ SOURCES = {
     "kernels/int4_gemv.cu": [],
     "kernels/int8_linear.cu": [],
     "kernels/int8_gemm_tcgen05.cu": [],
+    "kernels/int8_gemm_pair_tcgen05.cu": [],
     "kernels/int4_prefill_tcgen05.cu": [],
     "kernels/int4_gemm_pair_tcgen05.cu": [],
     "kernels/moe_ffn.cu": [],

@@ -857,13 +857,6 @@ void vyb_completion_free(vyb_completion* c) {
     delete c;
 }
 
-// tuning aid (not part of the ABI header): device buffer of 64 u64 per CTA, or NULL to switch tracing off
-void vyb_debug_set_int4_gemv_trace(void* device_buffer) {
-    vybk::set_int4_gemv_trace(static_cast<unsigned long long*>(device_buffer));
-}
-
-void vyb_debug_set_int4_gemv_flags(uint32_t flags) { vybk::set_int4_gemv_debug(flags); }
-
 // ---- kernel-level entry points ----------------------------------------------------------------------------------------------
 int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                            uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,

@@ -143,8 +143,6 @@ struct Params {
     void* y;
     uint32_t m, n, k, groups;  // groups = k / 128
     uint32_t* status;
-    unsigned long long* trace;  // optional: per-CTA timeline (64 slots each), tuning aid only
-    uint32_t debug;             // tuning aid: bit0 = skip the math, bit1 = split the tile copy in 4
 };
 
 template <int LIMBS, bool OUT_F32>
@@ -157,14 +155,6 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    auto stamp = [&](int slot) {
-        if (p.trace && lane == 0 && (warp == 0 || warp == WARPS)) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            p.trace[size_t(blockIdx.x) * 64 + slot] = t;
-        }
-    };
-    stamp(0);
     // Programmatic dependent launch: let the next kernel in the stream begin its own launch and weight prefetch
     // now; it still waits (griddepcontrol.wait) before touching activations or outputs. No-ops for plain launches.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -192,15 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
         const uint32_t bar = smem_u32(&ctrl->full[s]);
         uint8_t* stage = ring + size_t(s) * STAGE_BYTES;
         if (contiguous) {
-            if ((p.debug & 2u) && rows_valid == TILE_ROWS) {
-                if (lane == 0) mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
-                __syncwarp();
-                if (lane < 4)
-                    bulk_g2s(smem_u32(stage + lane * 4 * kbytes), p.w + size_t(row_base + lane * 4) * row_bytes, 4 * kbytes, bar);
-                if (lane == 4)
-                    bulk_g2s(smem_u32(stage + STAGE_W_BYTES), p.scales + size_t(row_base) * p.groups, rows_valid * sbytes, bar);
-                __syncwarp();
-            } else if (lane == 0) {
+            if (lane == 0) {
                 mbar_arrive_expect_tx(bar, rows_valid * (kbytes + sbytes));
                 bulk_g2s(smem_u32(stage), p.w + size_t(row_base) * row_bytes, rows_valid * kbytes, bar);
                 bulk_g2s(smem_u32(stage + STAGE_W_BYTES), p.scales + size_t(row_base) * p.groups, rows_valid * sbytes,
@@ -261,15 +243,12 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
             if (u >= STAGES) ok = mbar_wait(smem_u32(&ctrl->empty[u % STAGES]), ((u / STAGES) - 1) & 1, abort_flag);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            if (u < 16) stamp(32 + u);
             produce(u);
-            if (u < 16) stamp(48 + u);
         }
         if (!ok && lane == 0 && p.status) atomicOr(p.status, 2u);
         return;
     }
     asm volatile("bar.sync 2, %0;" ::"n"(THREADS) : "memory");
-    stamp(1);
 
     const int g = lane >> 2;  // mma row group; batch row of the B fragment
     const int t = lane & 3;
@@ -389,7 +368,6 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     } else if (nkb == 1) {
         load_x(0);
     }
-    stamp(2);
 
     // Register image of one 128-k group of this warp's slice: 16 B of each of the two fragment rows + 2 scales.
     // The loop below keeps one half in flight from shared memory while it does the math of the other.
@@ -486,19 +464,16 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
     for (uint32_t u = 0; u < units && alive; ++u) {
         const uint32_t tile = u / nkb, kb = u - tile * nkb;
         if (nkb != 1) load_x(kb);
-        if (u < 9) stamp(3 + 3 * u);
         const bool active = kb * KBLOCK + warp * WARP_K < p.k;
         load_half(u, 1, hb);
         release(u);  // both halves of the unit have been read: the stage may be refilled while the math runs
-        if (active && !(p.debug & 1u)) math_half(ha, xb[0], dq[0], out);
+        if (active) math_half(ha, xb[0], dq[0], out);
         if (u + 1 < units) {  // next unit's first half goes to registers behind the math of this unit's second
             alive = wait_full(u + 1);
             if (!alive) break;
             load_half(u + 1, 0, ha);
         }
-        if (u < 9) stamp(4 + 3 * u);
-        if (active && !(p.debug & 1u)) math_half(hb, xb[1], dq[1], out);
-        if (u < 9) stamp(5 + 3 * u);
+        if (active) math_half(hb, xb[1], dq[1], out);
         if (kb + 1 == nkb) {
             // cross-warp reduction of the tile: every warp leaves its 16x8 partial in the tile's slot and arrives
             // on the slot barrier; warp (tile % 16) sums the slot one tile LATER, when the barrier has long
@@ -513,7 +488,6 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
         }
     }
     if (alive && ntiles > 0 && uint32_t(warp) == (ntiles - 1) % WARPS) alive = reduce_tile(ntiles - 1);
-    stamp(31);
     if (!alive && lane == 0 && p.status) atomicOr(p.status, 1u);
 }
 
@@ -556,13 +530,7 @@ __global__ void __launch_bounds__(256) int4_linear_generic_kernel(const uint16_t
     }
 }
 
-unsigned long long* g_gemv_trace = nullptr;
-uint32_t g_gemv_debug = 0;
-
 }  // namespace
-
-void set_int4_gemv_trace(unsigned long long* t) { g_gemv_trace = t; }
-void set_int4_gemv_debug(uint32_t flags) { g_gemv_debug = flags; }
 
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
     return m >= 1 && m <= 8 && n >= 1 && group == 128 && k >= 1024 && k % 1024 == 0;
@@ -595,8 +563,6 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     p.k = k;
     p.groups = k / 128;
     p.status = status;
-    p.trace = g_gemv_trace;
-    p.debug = g_gemv_debug;
     const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
     cudaLaunchConfig_t cfg = {};

@@ -10,8 +10,6 @@ namespace vybk {
 // ---- decode GEMV / skinny GEMM (int4_gemv.cu) ---------------------------------------------------------------
 // y[m,n] = cast( sum_k x[m,k] * (q[n,k]-8) * s[n,k/128] ), m <= 8, group 128, k % 1024 == 0.
 // out_dtype: 0 = bf16, 1 = f32. status: optional 4-word device buffer set non-zero when a bounded wait ran out.
-void set_int4_gemv_trace(unsigned long long* device_buffer);  // tuning aid: per-CTA timeline, nullptr = off
-void set_int4_gemv_debug(uint32_t flags);                     // tuning aid: see int4_gemv.cu
 bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
@@ -95,6 +93,10 @@ cudaError_t launch_moe_ep_ffn(const MoeEp& c, const void* x_bf16, const void* w_
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
                              int sm_count, cudaStream_t stream, uint32_t* status);
+// CTA-pair form (int8_gemm_pair_tcgen05.cu): 256 x 256 tiles on two SMs
+bool int8_gemm_pair_supported(uint32_t m, uint32_t n, uint32_t k);
+cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
+                                  int sm_count, cudaStream_t stream, uint32_t* status);
 cudaError_t launch_quantize_per_token_int8(const void* x_bf16, int8_t* q, float* scales, uint32_t m, uint32_t k,
                                            cudaStream_t stream);
 
