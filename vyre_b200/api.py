@@ -416,12 +416,34 @@ class BindingSet:
         self.artifact = artifact_digest
         self.resources: dict[int, object] = {}
         self.invocation_grid = None
+        self._marshalled = None
 
     def insert_host(self, value_id: int, data) -> None:
         self.resources[value_id] = np.ascontiguousarray(data)
+        self._marshalled = None
 
     def insert_resident(self, value_id: int, handle) -> None:
         self.resources[value_id] = handle
+        self._marshalled = None
+
+    def marshal(self):
+        """The C array of vyb_binding for this set (built once; a set that is submitted again and again - same
+        buffers, new contents - costs no per-submit marshalling)."""
+        if self._marshalled is None:
+            arr = (ffi.Binding * max(1, len(self.resources)))()
+            keep = []
+            for i, (vid, res) in enumerate(sorted(self.resources.items())):
+                arr[i].value_id = vid
+                if isinstance(res, ffi.ResidentHandle):
+                    arr[i].kind = ffi.BIND_RESIDENT
+                    arr[i].resident = res
+                else:
+                    arr[i].kind = ffi.BIND_HOST
+                    arr[i].host_ptr = res.ctypes.data
+                    arr[i].len = res.nbytes
+                    keep.append(res)
+            self._marshalled = (arr, keep, len(self.resources))
+        return self._marshalled
 
     def set_invocation_grid(self, grid) -> None:
         if any(g == 0 for g in grid):
@@ -506,18 +528,7 @@ class ArtifactInstance:
         return dict(backend=i.backend.decode(), device=i.device.decode(), generation=i.generation)
 
     def submit(self, bindings: BindingSet, leave_resident: bool = False, config: ffi.DispatchConfig | None = None):
-        arr = (ffi.Binding * max(1, len(bindings.resources)))()
-        keep = []
-        for i, (vid, res) in enumerate(sorted(bindings.resources.items())):
-            arr[i].value_id = vid
-            if isinstance(res, ffi.ResidentHandle):
-                arr[i].kind = ffi.BIND_RESIDENT
-                arr[i].resident = res
-            else:
-                arr[i].kind = ffi.BIND_HOST
-                arr[i].host_ptr = res.ctypes.data
-                arr[i].len = res.nbytes
-                keep.append(res)
+        arr, keep, count = bindings.marshal()
         cfg = config or ffi.DispatchConfig()
         if bindings.invocation_grid:
             for a in range(3):
@@ -525,7 +536,7 @@ class ArtifactInstance:
         if leave_resident:
             cfg.leave_resident = 1
         out = C.c_void_p()
-        check(ffi.lib().vyb_submit(self._h, bindings.artifact, arr, len(bindings.resources), C.byref(cfg),
+        check(ffi.lib().vyb_submit(self._h, bindings.artifact, arr, count, C.byref(cfg),
                                    C.byref(out)))
         return Submission(out.value, keep)
 

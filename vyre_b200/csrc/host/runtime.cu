@@ -104,6 +104,26 @@ struct vyb_instance {
     uint32_t* status_dev = nullptr;   // 4 words, raised by kernels whose bounded waits ran out
     uint32_t* status_host = nullptr;  // pinned mirror
 
+    // events are recycled: creating and destroying three per submission costs more than the launch itself
+    std::vector<cudaEvent_t> timing_events, plain_events;
+    cudaEvent_t acquire_event(bool timing) {
+        auto& pool = timing ? timing_events : plain_events;
+        if (!pool.empty()) {
+            cudaEvent_t e = pool.back();
+            pool.pop_back();
+            return e;
+        }
+        cudaEvent_t e = nullptr;
+        if (timing)
+            cudaEventCreate(&e);
+        else
+            cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+        return e;
+    }
+    void release_event(cudaEvent_t e, bool timing) {
+        if (e) (timing ? timing_events : plain_events).push_back(e);
+    }
+
     void* acquire_pinned(size_t len) {
         for (auto& b : pinned)
             if (!b.in_use && b.cap >= len) {
@@ -155,6 +175,8 @@ void instance_unref(vyb_instance* i) {
         cudaStreamSynchronize(i->stream);
         cudaStreamDestroy(i->stream);
     }
+    for (cudaEvent_t e : i->timing_events) cudaEventDestroy(e);
+    for (cudaEvent_t e : i->plain_events) cudaEventDestroy(e);
     for (auto& b : i->pinned) cudaFreeHost(b.ptr);
     for (auto& b : i->temps) cudaFree(b.ptr);
     if (i->scratch) cudaFree(i->scratch);
@@ -725,9 +747,9 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
             sub->outputs.push_back(o);
         }
     }
-    cudaEventCreate(&sub->start);
-    cudaEventCreate(&sub->end);
-    cudaEventCreateWithFlags(&sub->done, cudaEventDisableTiming);
+    sub->start = inst->acquire_event(true);  // inst->mu is held for the whole submission
+    sub->end = inst->acquire_event(true);
+    sub->done = inst->acquire_event(false);
     cudaEventRecord(sub->start, inst->stream);
     cudaGetLastError();  // a non-sticky error left by an unrelated earlier call must not be blamed on this launch
     cudaError_t e = dispatch(inst, slot_ptr, inst->stream);
@@ -736,9 +758,9 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
         cudaGetLastError();
         cudaStreamSynchronize(inst->stream);
         cleanup();
-        cudaEventDestroy(sub->start);
-        cudaEventDestroy(sub->end);
-        cudaEventDestroy(sub->done);
+        inst->release_event(sub->start, true);
+        inst->release_event(sub->end, true);
+        inst->release_event(sub->done, false);
         if (e == cudaErrorNotSupported) return fail_unsupported("operator `" + p.op_id + "`");
         return fail_dispatch(int(e), "kernel launch failed: " + cuda_msg(e));
     }
@@ -785,9 +807,12 @@ int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion) {
             if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
         }
     }
-    cudaEventDestroy(s->start);
-    cudaEventDestroy(s->end);
-    cudaEventDestroy(s->done);
+    {
+        std::lock_guard<std::mutex> ilk(inst->mu);
+        inst->release_event(s->start, true);
+        inst->release_event(s->end, true);
+        inst->release_event(s->done, false);
+    }
     s->consumed = true;
     auto release_outputs = [&]() {
         std::lock_guard<std::mutex> ilk(inst->mu);
