@@ -266,3 +266,33 @@ def test_missing_device_is_a_structured_failure_not_a_fallback():
                                    ffi.DT_BF16, None, None)
     assert rc == ffi.ERR_DISPATCH_FAILED
     assert b"Fix:" in ffi.lib().vyb_last_error_message()
+
+
+def test_multi_gpu_contexts_are_validated_on_the_host():
+    """Argument checks of the peer-memory entry points run before any device work: wrong worlds, missing peer
+    addresses and unsupported sizes are structured errors with Fix: text."""
+    import ctypes as C
+
+    from vyre_b200 import ffi
+
+    L = ffi.lib()
+    ctx = ffi.AllGatherCtx()
+    ctx.world, ctx.rank = 0, 0
+    assert L.vyb_k_allgather_wait(C.byref(ctx), None, None) == ffi.ERR_INVALID_PROGRAM
+    assert "Fix:" in L.vyb_last_error_message().decode()
+    ctx.world, ctx.rank = 2, 2
+    assert L.vyb_k_allgather_push(C.byref(ctx), 0, 1, 8, None, None) == ffi.ERR_INVALID_PROGRAM
+    ctx.world, ctx.rank, ctx.epoch = 2, 0, 4096
+    ctx.peer_out[0], ctx.peer_flag[0] = 4096, 8192          # rank 1's addresses are missing
+    assert L.vyb_k_allgather_push(C.byref(ctx), 0, 1, 8, None, None) == ffi.ERR_INVALID_PROGRAM
+    assert "every rank" in L.vyb_last_error_message().decode()
+
+    ep = ffi.MoeEpCtx()
+    sym, loc = C.c_uint64(0), C.c_uint64(0)
+    assert L.vyb_k_moe_ep_sizes(512, 4096, 4096, 14336, 8, 2, 3, C.byref(ep), C.byref(sym), C.byref(loc)) == ffi.ERR_INVALID_PROGRAM
+    assert L.vyb_k_moe_ep_sizes(512, 4096, 4096, 14336, 8, 2, 8, C.byref(ep), C.byref(sym), C.byref(loc)) == 0
+    # worst case: all 8192 pairs of the job on one rank -> 8192 + 256 rows of 8 KB in, 1024 pairs of 8 KB back
+    assert sym.value >= (8192 + 256) * 4096 * 2 + 512 * 2 * 4096 * 2 and ep.off_xg % 256 == 0 and ep.off_yhome > ep.off_xg
+    assert loc.value >= (8192 + 256) * (14336 + 4096) * 2
+    ep.world, ep.rank = 9, 0
+    assert L.vyb_k_moe_ep_ffn_int4(C.byref(ep), 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 16, 16, 256, 256, 8, 2, 128, None, None) == ffi.ERR_INVALID_PROGRAM
