@@ -45,6 +45,21 @@ def test_int8_gemm_bit_exact(m, n, k):
     assert np.array_equal(got, want)
 
 
+def test_int8_gemm_cta_pair_kernel_ragged_shape_bit_exact():
+    """Enough 256 x 256 tiles for the CTA-pair kernel (two waves on 74 pairs), ragged in every dimension: checked on
+    the first, a middle and the last rows against the oracle, and on every element against torch's int64 matmul."""
+    m, n, k = 2050, 4500, 272
+    rng = np.random.default_rng(99)
+    a = rng.integers(-127, 128, size=(m, k), dtype=np.int8)
+    w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    assert ((m + 255) // 256) * ((n + 255) // 256) >= 148
+    got = gemm_raw(a, w)
+    for lo, hi in ((0, 8), (1020, 1030), (m - 6, m)):
+        assert np.array_equal(got[lo:hi], oracle.int8_gemm_i32(a, w, m, n, k, row_begin=lo, row_end=hi))
+    full = (torch.from_numpy(a).cuda().to(torch.float64) @ torch.from_numpy(w).cuda().to(torch.float64).T).to(torch.int32)
+    assert np.array_equal(got, full.cpu().numpy())  # |sum| < 2^53: the f64 product is exact
+
+
 def test_int8_gemm_extremes_do_not_wrap():
     m, n, k = 128, 256, 8192
     a = np.full((m, k), -127, dtype=np.int8)

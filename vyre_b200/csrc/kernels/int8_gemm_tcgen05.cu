@@ -234,8 +234,11 @@ bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k) {
 
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
                              int sm_count, cudaStream_t stream, uint32_t* status) {
-    // above 128 rows the CTA-pair kernel (256 x 256 tiles on two SMs) takes over
-    if (int8_gemm_pair_supported(m, n, k) && sm_count >= 2) return launch_int8_gemm_pair(a, w, out, m, n, k, sm_count, stream, status);
+    // from two waves of 256 x 256 pair tiles on, the CTA-pair kernel takes over (below that, 128 x 256 tiles on single
+    // SMs fill the machine better)
+    const uint32_t pair_tiles = ((m + 255) / 256) * ((n + 255) / 256);
+    if (int8_gemm_pair_supported(m, n, k) && sm_count >= 2 && pair_tiles >= 2 * uint32_t(sm_count / 2))
+        return launch_int8_gemm_pair(a, w, out, m, n, k, sm_count, stream, status);
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);

@@ -93,7 +93,7 @@ cudaError_t launch_moe_ep_ffn(const MoeEp& c, const void* x_bf16, const void* w_
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
                              int sm_count, cudaStream_t stream, uint32_t* status);
-// CTA-pair form (int8_gemm_pair_tcgen05.cu): 256 x 256 tiles on two SMs; launch_int8_gemm uses it above 128 rows
+// CTA-pair form (int8_gemm_pair_tcgen05.cu): 256 x 256 tiles on two SMs; launch_int8_gemm uses it from two waves of pair tiles on
 bool int8_gemm_pair_supported(uint32_t m, uint32_t n, uint32_t k);
 cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
                                   int sm_count, cudaStream_t stream, uint32_t* status);
