@@ -63,6 +63,7 @@ typedef struct vyb_payload vyb_payload;       /* vyre_megakernel::TargetPayload 
 typedef struct vyb_device vyb_device;         /* vyre_driver Device + ArtifactMaterializer */
 typedef struct vyb_instance vyb_instance;     /* vyre_driver ArtifactInstance */
 typedef struct vyb_submission vyb_submission; /* vyre_driver Submission */
+typedef struct vyb_prepared vyb_prepared;     /* a BindingSet frozen for replay (no counterpart in the reference) */
 typedef struct vyb_completion vyb_completion; /* vyre_driver Completion */
 
 /* vyre-driver/src/backend/resource.rs:22-84 (ResidentHandle = owner + id) */
@@ -382,6 +383,24 @@ void vyb_instance_free(vyb_instance* i);
  * library-owned non-default stream. `config` may be NULL. */
 int32_t vyb_submit(vyb_instance* instance, const uint8_t artifact_digest[32], const vyb_binding* bindings,
                    size_t n_bindings, const vyb_dispatch_config* config, vyb_submission** submission);
+/* A binding set validated once and frozen into a single device-side graph (copy of the host inputs in, kernels,
+ * copy of the outputs and of the status words out), for a caller that submits the same artifact with the same
+ * resident buffers over and over and only changes its host inputs. No counterpart in the reference, whose
+ * ArtifactSession::submit (vyre-runtime/src/artifact_admission.rs:152-496) validates and stages every BindingSet
+ * anew; the result of a replay equals that of vyb_submit with the same bindings. vyb_prepare runs one ordinary
+ * submission first (full validation). vyb_prepared_submit copies the bytes of `host_updates` (host bindings of
+ * input value ids; the others keep their last contents) and replays; one submission per prepared set may be in
+ * flight: the completion's output views live in the set's buffers until the completion is freed. Resident
+ * buffers bound to the set count as in flight (vyb_free refuses them) until vyb_prepared_free. */
+int32_t vyb_prepare(vyb_instance* instance, const uint8_t artifact_digest[32], const vyb_binding* bindings,
+                    size_t n_bindings, vyb_prepared** prepared);
+int32_t vyb_prepared_submit(vyb_prepared* prepared, const vyb_binding* host_updates, size_t n_updates,
+                            vyb_submission** submission);
+int32_t vyb_prepared_free(vyb_prepared* prepared);
+/* Host-side injection for recovery tests, like vyb_device_mark_lost: writes `word` into the instance's kernel
+ * status words exactly where a kernel whose bounded wait ran out would raise it; the NEXT submission on the
+ * instance then fails with DispatchFailed and later ones succeed again. No device fault is provoked. */
+int32_t vyb_instance_inject_status(vyb_instance* instance, uint32_t word);
 /* Submission::is_ready / wait (artifact_lifecycle.rs:112-117); wait consumes the submission */
 int32_t vyb_submission_is_ready(const vyb_submission* s);
 int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion);
@@ -397,6 +416,11 @@ void vyb_completion_free(vyb_completion* c);
  * All pointers are DEVICE pointers, `stream` is a cudaStream_t. `status` is an optional device pointer to
  * 4 u32 words that a kernel with bounded waits sets non-zero when a wait ran out (never a trap). */
 
+/* Tensor-core peak microbenchmark (no counterpart in the reference: its bench reports no roofline for tensor
+ * work, vyre-bench/src/api/metric.rs:109-118): every SM issues `iters` rounds of four tcgen05.mma (128 x 256 tiles,
+ * kind::i8 when int8 != 0, else bf16) from operands resident in shared memory. *ops_per_launch receives the
+ * integer or floating-point operations one launch performs; the caller times launches with events. */
+int32_t vyb_k_tensor_peak(uint32_t int8, uint32_t iters, void* stream, uint32_t* status, double* ops_per_launch);
 /* y[m,n] = bf16|f32( sum_k x[m,k] * (q[n,k]-8) * s[n,k/group] ), m <= 8 per pass, HBM-bound decode path */
 int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,

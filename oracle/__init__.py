@@ -14,15 +14,19 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_build", "libvyre_oracle.so")
+_BASE_SO = os.path.join(_HERE, "_build", "libvyre_cpu_baseline.so")
 _LIB = None
+_BASE = None
 
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 
 
 def build(force: bool = False) -> str:
-    src = os.path.join(_HERE, "vyre_oracle.cpp")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
-        subprocess.run(["make", "-C", _HERE], check=True, stdout=subprocess.DEVNULL)
+    stale = force
+    for so, src in ((_SO, "vyre_oracle.cpp"), (_BASE_SO, "cpu_baseline.cpp")):
+        stale = stale or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(os.path.join(_HERE, src))
+    if stale:
+        subprocess.run(["make", "-C", _HERE, "all"], check=True, stdout=subprocess.DEVNULL)
     return _SO
 
 
@@ -61,6 +65,24 @@ def _c(a, dt):
 
 def num_threads() -> int:
     return int(lib().vyo_num_threads())
+
+
+def cpu_baseline_int4_gemv(x_f32, w_packed, scale_bf16, m: int, n: int, k: int, group: int = 128, zp: int = 8) -> np.ndarray:
+    """The reference bench's CPU loop (f32, sequential k, one task per output; vyre-bench/src/cases/
+    quantized_linear.rs:447-463) for the row-major int4 GEMV, built -O3: the thing bench.py TIMES on the host cores.
+    Not the checker."""
+    global _BASE
+    if _BASE is None:
+        if not os.path.exists(_BASE_SO):
+            build()
+        _BASE = C.CDLL(_BASE_SO)
+    x = _c(x_f32, np.float32)
+    w = _c(w_packed, np.uint8)
+    s = _c(scale_bf16, np.uint16)
+    out = np.empty((m, n), np.float32)
+    _BASE.vyo_cpu_baseline_int4_gemv(_p(x), _p(w), _p(s), _p(out), C.c_uint32(m), C.c_uint32(n), C.c_uint32(k),
+                                     C.c_uint32(group), C.c_int32(zp))
+    return out
 
 
 # ---- bf16 helpers (numpy has no bf16: carried as uint16 bit patterns) -------------------------

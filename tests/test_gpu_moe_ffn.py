@@ -125,6 +125,15 @@ def test_moe_ffn_config4_full_size_sampled_tokens():
     # size-independent properties: every token has two distinct experts, weights are softmax probabilities
     assert np.all(got[1] < experts) and np.all(got[1][:, 0] != got[1][:, 1])
     assert np.all(got[2] > 0) and np.all(got[2].sum(axis=1) <= 1.0 + 1e-6) and np.all(got[2][:, 0] >= got[2][:, 1])
-    sel = np.array([0, 1, 777, 2048, 4095])
+    # 72 tokens: nine routed to each expert as first choice (so every expert's weights are checked), spread over the batch
+    first = got[1][:, 0]
+    sel = np.sort(np.concatenate([np.nonzero(first == e)[0][np.linspace(0, np.count_nonzero(first == e) - 1, 9).astype(int)]
+                                  for e in range(experts)]))
+    assert len(np.unique(sel)) == 72
     want = oracle.moe_ffn_int4(x, wr, w13, s13, w2, s2, sel, hidden, inter, experts, topk, mode=1)
-    check_against_oracle(got[0][sel], got[1][sel], got[2][sel], *want, x[sel], wr, max_tie_frac=0.5)
+    # Routing may differ from the oracle only at near-ties of the bf16 router logits (checked as such), here at most 3 of
+    # 72 tokens. Outputs: a flipped bf16 ulp of ONE expert output (2^-8 of it) survives the weighted sum of two experts,
+    # and an expert output can be several times the RMS of the sum, so the honest bound against max(|want|, RMS) is
+    # 2e-2, not the 1e-2 that holds per expert output. 94.6 % of these outputs are bit-identical (the down projection sums
+    # 14336 terms: more single-ulp flips than at the small shapes, which assert 95 %).
+    check_against_oracle(got[0][sel], got[1][sel], got[2][sel], *want, x[sel], wr, max_tie_frac=0.05, min_identical=0.93)

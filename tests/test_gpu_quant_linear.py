@@ -81,6 +81,58 @@ def test_decode_gemv_exact_on_dyadic_inputs(dev):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+def _outlier_inputs(m, n, k, log2_ratio, outlier_nibble, seed):
+    """N(0,1) activations with ONE element per 128-k group scaled by 2^log2_ratio (the usual shape of LLM activation
+    outliers). outlier_nibble = 8 gives the outlier positions weight zero in every row, so the outputs are carried
+    entirely by the small elements of each group; None leaves the weights random."""
+    x, w, s = synth.int4_linear_inputs(m, n, k, seed=seed)
+    rng = np.random.default_rng(seed + 1000)
+    xf = synth.bf16_bits_to_f32(x).reshape(m, k).copy()
+    w = w.copy()
+    for g in range(k // 128):
+        pos = g * 128 + rng.integers(0, 128, size=m)
+        xf[np.arange(m), pos] = rng.choice([-1.0, 1.0], size=m) * (1.0 + rng.random(m)) * 2.0 ** log2_ratio
+        if outlier_nibble is not None:
+            for p in np.unique(pos):
+                byte = w[:, p // 2]
+                w[:, p // 2] = (byte & 0xF0) | outlier_nibble if p % 2 == 0 else (byte & 0x0F) | (outlier_nibble << 4)
+    return synth.f32_to_bf16_bits(xf.astype(np.float32)), w, s
+
+
+@pytest.mark.parametrize("m", [1, 2, 4, 8])
+@pytest.mark.parametrize("log2_ratio", [6, 10, 14])
+@pytest.mark.parametrize("outlier_nibble", [8, None])
+def test_decode_gemv_outlier_activations(dev, m, log2_ratio, outlier_nibble):
+    # the kernel carries activations as block-floating integers per 128-k group: an outlier must not wash out the
+    # small elements of its group, not even when the outlier itself meets a zero weight
+    n, k = 1024, 4096
+    x, w, s = _outlier_inputs(m, n, k, log2_ratio, outlier_nibble, seed=log2_ratio + m)
+    got32 = run_int4(dev, x, w, s, m, n, k, out_dtype=ffi.DT_F32)
+    want32 = oracle.int4_rowmajor_linear(x, w, s, m, n, k, out_dtype=oracle.DT_F32)
+    assert rel_err(got32, want32) <= TOL_F32_ACC
+    got = run_int4(dev, x, w, s, m, n, k)
+    want = oracle.int4_rowmajor_linear(x, w, s, m, n, k)
+    err = rel_err(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want))
+    if m > 1 and log2_ratio == 14 and outlier_nibble == 8:
+        # The stated limit of the batched bf16 path: it keeps 26 bits per group (exact for elements within 2^-18 of the
+        # group's largest). Here EVERY output is carried by elements 2^-14 and more below an outlier that meets a zero
+        # weight, and outputs near zero (the floor of rel_err) see up to twice the bf16 window. A single row, and every
+        # row of an f32 output, is converted with 57 bits and stays inside the window (asserted above).
+        assert err <= 2 * TOL_BF16_OUT, err
+    else:
+        assert err <= TOL_BF16_OUT, err
+
+
+def test_decode_gemv_other_row_lengths_with_outliers(dev):
+    # k that is not 2048 or 4096 takes the bulk-copy kernel, which keeps 22 bits per group: exact for elements within
+    # 2^-14 of their group's maximum
+    m, n, k = 3, 320, 3072
+    x, w, s = _outlier_inputs(m, n, k, 10, 8, seed=77)
+    got32 = run_int4(dev, x, w, s, m, n, k, out_dtype=ffi.DT_F32)
+    want32 = oracle.int4_rowmajor_linear(x, w, s, m, n, k, out_dtype=oracle.DT_F32)
+    assert rel_err(got32, want32) <= TOL_F32_ACC
+
+
 def test_decode_gemv_larger_batches_and_generic_fallback(dev):
     # batch > 8 loops the skinny kernel; group != 128 or k % 1024 != 0 takes the plain-load kernel
     for (m, n, k, g) in [(13, 96, 1024, 128), (20, 40, 2048, 128), (3, 50, 512, 64), (2, 33, 1280, 128), (4, 20, 256, 32)]:

@@ -541,6 +541,46 @@ class ArtifactInstance:
         return Submission(out.value, keep)
 
 
+class PreparedSubmission:
+    """A binding set validated once and frozen into one device-side graph (vyb_prepare): a submission is then a copy of
+    the changed host inputs plus a single graph launch. One submission per prepared set may be in flight."""
+
+    def __init__(self, instance: ArtifactInstance, bindings: BindingSet):
+        arr, keep, count = bindings.marshal()
+        out = C.c_void_p()
+        check(ffi.lib().vyb_prepare(instance._h, bindings.artifact, arr, count, C.byref(out)))
+        self._h = C.c_void_p(out.value)
+        self._instance = instance
+        self._updates: dict[tuple, tuple] = {}
+
+    def submit(self, host_inputs: dict | None = None) -> Submission:
+        """host_inputs: {value_id: array} for the host-bound inputs whose bytes changed (copied in here)."""
+        items = sorted((host_inputs or {}).items())
+        key = tuple((vid, a.ctypes.data, a.nbytes) for vid, a in items)
+        if key not in self._updates:  # same arrays again and again: marshalled once
+            arr = (ffi.Binding * max(1, len(items)))()
+            for i, (vid, a) in enumerate(items):
+                if not a.flags["C_CONTIGUOUS"]:
+                    raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: pass C-contiguous arrays to a prepared submission.")
+                arr[i].value_id, arr[i].kind, arr[i].host_ptr, arr[i].len = vid, ffi.BIND_HOST, a.ctypes.data, a.nbytes
+            self._updates = {key: (arr, [a for _, a in items], len(items))}
+        arr, keep, count = self._updates[key]
+        out = C.c_void_p()
+        check(ffi.lib().vyb_prepared_submit(self._h, arr, count, C.byref(out)))
+        return Submission(out.value, keep)
+
+    def free(self) -> None:
+        if self._h is not None:
+            h, self._h = self._h, None
+            check(ffi.lib().vyb_prepared_free(h))
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
 class ArtifactSession:
     """vyre_runtime::ArtifactSession: compile -> attach target -> materialize -> submit
     (vyre-runtime/src/artifact_admission.rs:152-496)."""
@@ -584,6 +624,9 @@ class ArtifactSession:
 
     def submit(self, bindings: BindingSet, **kw) -> Submission:
         return self.instance.submit(bindings, **kw)
+
+    def prepare(self, bindings: BindingSet) -> PreparedSubmission:
+        return PreparedSubmission(self.instance, bindings)
 
     def submit_and_wait(self, bindings: BindingSet, **kw) -> Completion:
         return self.instance.submit(bindings, **kw).wait()

@@ -32,6 +32,7 @@ SOURCES = {
     "host/runtime.cu": [],
     "kernels/ref_ops.cu": ["-ftz=true", "-prec-div=true", "-prec-sqrt=true", "-fmad=false"],
     "kernels/int4_gemv.cu": [],
+    "kernels/int4_gemv_halfsm.cu": [],
     "kernels/int8_linear.cu": [],
     "kernels/int8_gemm_tcgen05.cu": [],
     "kernels/int8_gemm_pair_tcgen05.cu": [],
@@ -41,6 +42,7 @@ SOURCES = {
     "kernels/allgather_push.cu": [],
     "kernels/moe_ep.cu": [],
     "kernels/int8_dynamic_static_scratch.cu": [],
+    "kernels/tensor_peak.cu": [],
 }
 
 

@@ -194,16 +194,41 @@ struct OutputSlot {
 };
 }  // namespace
 
+struct vyb_prepared;
+
 struct vyb_submission {
     vyb_instance* inst = nullptr;
     cudaEvent_t start = nullptr, end = nullptr, done = nullptr;
     std::vector<void*> temps;
+    std::vector<void*> staged;  // pinned copies of the caller's host inputs (the BindingSet owns its bytes)
     std::vector<OutputSlot> outputs;
     std::vector<uint64_t> resident_ids;
+    uint32_t* status_host = nullptr;  // this submission's own pinned copy of the kernel status words
+    vyb_prepared* prepared = nullptr;  // set when the submission replays a prepared graph (buffers belong to it)
     bool consumed = false;
 };
 
+// A validated binding set frozen into one CUDA graph: H2D of the host inputs, the kernels, D2H of the outputs and of
+// the status words. Replayed with a single graph launch per submission.
+struct vyb_prepared {
+    vyb_instance* inst = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    struct HostInput {
+        uint32_t value_id;
+        void* staging;  // pinned
+        size_t len;
+    };
+    std::vector<HostInput> inputs;
+    std::vector<OutputSlot> outputs;
+    std::vector<void*> temps;
+    std::vector<uint64_t> resident_ids;
+    uint32_t* status_host = nullptr;
+    cudaEvent_t done = nullptr;
+    bool busy = false;  // one submission of a prepared set in flight at a time
+};
+
 struct vyb_completion {
+    vyb_prepared* prepared = nullptr;  // outputs live in the prepared set's buffers; freeing the completion releases it
     vyb_instance* inst = nullptr;
     Digest artifact{};
     std::vector<OutputSlot> outputs;
@@ -214,6 +239,19 @@ struct vyb_completion {
 namespace {
 
 uint32_t rt_dtype(uint32_t tag) { return tag == VYB_DT_BF16 ? 1u : tag == VYB_DT_F16 ? 2u : 0u; }
+
+// Programs whose kernels write every byte of every output: the zero fill of a backend-allocated output would be
+// overwritten at once (the reference zero-fills because its generated kernels may skip padded elements).
+bool overwrites_every_output_byte(const Program& p) {
+    switch (p.kind) {
+        case OpKind::LinearInt4GroupedRowmajor:
+        case OpKind::LinearInt8WeightOnly:
+        case OpKind::LinearInt8Dynamic:
+            return true;
+        default:
+            return false;
+    }
+}
 
 // Launch the kernels of one program. `b[slot]` is the device pointer bound to the BufferDecl binding slot.
 cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
@@ -462,10 +500,20 @@ int32_t vyb_upload_at(vyb_device* d, vyb_resident_handle h, size_t offset_bytes,
             return fail_invalid_program("Fix: resident upload of " + std::to_string(len) + " bytes at offset " +
                                         std::to_string(offset_bytes) + " exceeds the " + std::to_string(r->len) +
                                         "-byte allocation; allocate a larger buffer or split the upload.");
+        // a dispatch in flight may be reading or writing the buffer on another stream (resident.rs:185-190, 287-364)
+        if (r->inflight)
+            return fail_invalid_program("Fix: resident buffer is bound to a dispatch in flight; wait for the pending "
+                                        "submission (or free the prepared set that holds it) before uploading.");
+        r->inflight++;  // keeps vyb_free away while the copy runs
         dst = static_cast<uint8_t*>(r->ptr) + offset_bytes;
     }
     cudaSetDevice(d->ordinal);
     cudaError_t e = cudaMemcpy(dst, bytes, len, cudaMemcpyHostToDevice);
+    {
+        std::lock_guard<std::mutex> lk(d->mu);
+        auto it = d->residents.find(h.id);
+        if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
+    }
     if (e != cudaSuccess) return fail_dispatch(int(e), "resident upload failed: " + cuda_msg(e));
     clear_error();
     return VYB_OK;
@@ -486,10 +534,16 @@ int32_t vyb_download_range(vyb_device* d, vyb_resident_handle h, size_t offset_b
             return fail_invalid_program("Fix: resident download of " + std::to_string(len) + " bytes at offset " +
                                         std::to_string(offset_bytes) + " exceeds the " + std::to_string(r->len) +
                                         "-byte allocation.");
+        r->inflight++;  // keeps vyb_free away while the copy runs; reading beside a dispatch in flight is the caller's call
         src = static_cast<const uint8_t*>(r->ptr) + offset_bytes;
     }
     cudaSetDevice(d->ordinal);
     cudaError_t e = cudaMemcpy(dst, src, len, cudaMemcpyDeviceToHost);
+    {
+        std::lock_guard<std::mutex> lk(d->mu);
+        auto it = d->residents.find(h.id);
+        if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
+    }
     if (e != cudaSuccess) return fail_dispatch(int(e), "resident download failed: " + cuda_msg(e));
     clear_error();
     return VYB_OK;
@@ -645,6 +699,8 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
     void* slot_ptr[16] = {nullptr};
     auto cleanup = [&]() {
         for (void* t : sub->temps) inst->release_temp(t);
+        for (void* t : sub->staged) inst->release_pinned(t);
+        if (sub->status_host) inst->release_pinned(sub->status_host);
         for (auto& o : sub->outputs)
             if (o.host) inst->release_pinned(o.host);
         std::lock_guard<std::mutex> lk(d->mu);
@@ -722,10 +778,20 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
             }
             sub->temps.push_back(dev_ptr);
             cudaError_t e = cudaSuccess;
-            if (is_input)
-                e = cudaMemcpyAsync(dev_ptr, b->host_ptr, need, cudaMemcpyHostToDevice, inst->stream);
-            else
+            if (is_input) {
+                // host bytes are copied in at submit, as BindingSet::insert_host does
+                // (vyre-driver/src/backend/artifact_lifecycle.rs:34-96): the caller may reuse its buffer at once
+                void* stage = inst->acquire_pinned(need);
+                if (!stage) {
+                    cleanup();
+                    return fail_oom(need, 0);
+                }
+                sub->staged.push_back(stage);
+                std::memcpy(stage, b->host_ptr, need);
+                e = cudaMemcpyAsync(dev_ptr, stage, need, cudaMemcpyHostToDevice, inst->stream);
+            } else if (!overwrites_every_output_byte(p)) {
                 e = cudaMemsetAsync(dev_ptr, 0, need, inst->stream);  // backend-allocated outputs start zeroed
+            }
             if (e != cudaSuccess) {
                 cleanup();
                 return fail_dispatch(int(e), "input staging failed: " + cuda_msg(e));
@@ -766,10 +832,29 @@ int32_t vyb_submit(vyb_instance* inst, const uint8_t artifact_digest[32], const 
     }
     for (auto& o : sub->outputs)
         if (o.host) cudaMemcpyAsync(o.host, o.dev_ptr, o.len, cudaMemcpyDeviceToHost, inst->stream);
-    cudaMemcpyAsync(inst->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
+    // every submission reads the status words into its OWN pinned slot and clears them on the stream right after,
+    // so a word raised by one submission is never reported for another
+    sub->status_host = static_cast<uint32_t*>(inst->acquire_pinned(16));
+    if (sub->status_host) {
+        sub->status_host[0] = 0;
+        cudaMemcpyAsync(sub->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
+        cudaMemsetAsync(inst->status_dev, 0, 16, inst->stream);
+    }
     cudaEventRecord(sub->done, inst->stream);
     inst->refs.fetch_add(1);  // released by the completion (or by a failed wait)
     *submission = sub.release();
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_instance_inject_status(vyb_instance* inst, uint32_t word) {
+    if (!inst) return fail_invalid_program("Fix: pass a non-null instance.");
+    std::lock_guard<std::mutex> ilk(inst->mu);
+    cudaSetDevice(inst->dev->ordinal);
+    // stream-ordered, like a kernel whose bounded wait ran out: the next submission on this instance reads it
+    cudaError_t e = cudaMemcpyAsync(inst->status_dev, &word, 4, cudaMemcpyHostToDevice, inst->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(inst->stream);
+    if (e != cudaSuccess) return fail_dispatch(int(e), "status injection failed: " + cuda_msg(e));
     clear_error();
     return VYB_OK;
 }
@@ -784,65 +869,67 @@ int32_t vyb_submission_wait(vyb_submission* s, vyb_completion** completion) {
     if (s->consumed) return fail_invalid_program("Fix: completion may be consumed only once.");
     vyb_instance* inst = s->inst;
     vyb_device* d = inst->dev;
+    vyb_prepared* prep = s->prepared;
     cudaSetDevice(d->ordinal);
     cudaError_t e = cudaEventSynchronize(s->done);
     float ms = 0.0f;
-    const bool timed = e == cudaSuccess && cudaEventElapsedTime(&ms, s->start, s->end) == cudaSuccess;
-    uint32_t status = 0;
+    const bool timed = e == cudaSuccess && s->start && cudaEventElapsedTime(&ms, s->start, s->end) == cudaSuccess;
+    // the status words this submission itself read back (never another submission's)
+    const uint32_t status = e == cudaSuccess && s->status_host ? s->status_host[0] : 0;
     {
         std::lock_guard<std::mutex> ilk(inst->mu);
         for (void* t : s->temps) inst->release_temp(t);
-        if (e == cudaSuccess) {
-            status = inst->status_host[0];
-            if (status) {
-                cudaMemsetAsync(inst->status_dev, 0, 16, inst->stream);
-                inst->status_host[0] = 0;
-            }
+        for (void* t : s->staged) inst->release_pinned(t);
+        if (!prep && s->status_host) inst->release_pinned(s->status_host);
+        if (!prep) {
+            inst->release_event(s->start, true);
+            inst->release_event(s->end, true);
+            inst->release_event(s->done, false);
         }
     }
-    {
+    if (!prep) {
         std::lock_guard<std::mutex> lk(d->mu);
         for (uint64_t id : s->resident_ids) {
             auto it = d->residents.find(id);
             if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
         }
     }
-    {
-        std::lock_guard<std::mutex> ilk(inst->mu);
-        inst->release_event(s->start, true);
-        inst->release_event(s->end, true);
-        inst->release_event(s->done, false);
-    }
     s->consumed = true;
     auto release_outputs = [&]() {
         std::lock_guard<std::mutex> ilk(inst->mu);
+        if (prep) {
+            prep->busy = false;
+            return;
+        }
         for (auto& o : s->outputs)
             if (o.host) inst->release_pinned(o.host);
     };
-    if (e != cudaSuccess) {
+    if (e != cudaSuccess || status) {
         cudaGetLastError();
         release_outputs();
         delete s;
-        instance_unref(inst);
+        // decide and word the failure while the device object is certainly alive: the submission may hold the last
+        // reference to the instance, and the instance the last one to the device
+        int32_t rc;
         const bool lost = e == cudaErrorIllegalAddress || e == cudaErrorLaunchFailure || e == cudaErrorHardwareStackError ||
                           e == cudaErrorIllegalInstruction || e == cudaErrorECCUncorrectable || e == cudaErrorDevicesUnavailable;
-        if (lost) {
+        if (e != cudaSuccess && lost) {
             vyb_device_mark_lost(d, cuda_msg(e).c_str());
-            return fail_device_lost(d->device_name, d->generation.load(), cuda_msg(e));
+            rc = fail_device_lost(d->device_name, d->generation.load(), cuda_msg(e));
+        } else if (e != cudaSuccess) {
+            rc = fail_dispatch(int(e), "submission failed: " + cuda_msg(e));
+        } else {
+            rc = fail_dispatch(int(status), "a bounded device-side wait ran out (kernel status word " +
+                                                std::to_string(status) + "); the kernel drained without completing");
         }
-        return fail_dispatch(int(e), "submission failed: " + cuda_msg(e));
-    }
-    if (status) {
-        release_outputs();
-        delete s;
         instance_unref(inst);
-        return fail_dispatch(int(status), "a bounded device-side wait ran out (kernel status word " +
-                                              std::to_string(status) + "); the kernel drained without completing");
+        return rc;
     }
     auto c = std::make_unique<vyb_completion>();
     c->inst = inst;
+    c->prepared = prep;
     c->artifact = inst->artifact;
-    c->outputs = std::move(s->outputs);
+    c->outputs = prep ? prep->outputs : std::move(s->outputs);
     c->has_device_ns = timed;
     c->device_ns = timed ? uint64_t(double(ms) * 1.0e6) : 0;
     delete s;
@@ -875,11 +962,211 @@ void vyb_completion_free(vyb_completion* c) {
     if (!c) return;
     {
         std::lock_guard<std::mutex> ilk(c->inst->mu);
-        for (auto& o : c->outputs)
-            if (o.host) c->inst->release_pinned(o.host);
+        if (c->prepared) {
+            c->prepared->busy = false;  // its buffers may be written by the next replay
+        } else {
+            for (auto& o : c->outputs)
+                if (o.host) c->inst->release_pinned(o.host);
+        }
     }
     instance_unref(c->inst);
     delete c;
+}
+
+// ---- prepared binding sets: one CUDA graph per set, one graph launch per submission ---------------------------------
+int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const vyb_binding* bindings, size_t n_bindings,
+                    vyb_prepared** prepared) {
+    if (!prepared) return fail_invalid_program("Fix: pass a non-null prepared out-pointer.");
+    // one ordinary submission first: it validates the bindings exactly as vyb_submit does and runs every one-time
+    // kernel configuration call outside stream capture
+    {
+        vyb_submission* sub = nullptr;
+        if (int32_t rc = vyb_submit(inst, artifact_digest, bindings, n_bindings, nullptr, &sub)) return rc;
+        vyb_completion* c = nullptr;
+        if (int32_t rc = vyb_submission_wait(sub, &c)) return rc;
+        vyb_completion_free(c);
+    }
+    vyb_device* d = inst->dev;
+    const Program& p = inst->program;
+    std::lock_guard<std::mutex> ilk(inst->mu);
+    cudaSetDevice(d->ordinal);
+    auto prep = std::make_unique<vyb_prepared>();
+    prep->inst = inst;
+    void* slot_ptr[16] = {nullptr};
+    std::vector<std::pair<void*, size_t>> zero_fill;
+    auto undo = [&]() {
+        for (void* t : prep->temps) inst->release_temp(t);
+        for (auto& in : prep->inputs) inst->release_pinned(in.staging);
+        for (auto& o : prep->outputs)
+            if (o.host) inst->release_pinned(o.host);
+        if (prep->status_host) inst->release_pinned(prep->status_host);
+        if (prep->done) inst->release_event(prep->done, false);
+        std::lock_guard<std::mutex> lk(d->mu);
+        for (uint64_t id : prep->resident_ids) {
+            auto it = d->residents.find(id);
+            if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
+        }
+    };
+    for (const BufferDecl& bd : p.buffers) {
+        if (bd.access == VYB_ACCESS_WORKGROUP) continue;
+        const size_t need = size_t(bd.count) * dtype_size_bytes(bd.dtype);
+        const size_t logical = bd.has_output_byte_range ? size_t(bd.output_byte_end - bd.output_byte_begin) : need;
+        const vyb_binding* b = nullptr;
+        for (size_t i = 0; i < n_bindings; ++i)
+            if (bindings[i].value_id == bd.binding) b = &bindings[i];
+        const bool is_input = bd.access == VYB_ACCESS_READ_ONLY || bd.access == VYB_ACCESS_READ_WRITE;
+        const bool is_output = bd.access == VYB_ACCESS_OUTPUT || bd.access == VYB_ACCESS_READ_WRITE;
+        void* dev_ptr = nullptr;
+        if (b && b->kind == VYB_BIND_RESIDENT) {
+            std::lock_guard<std::mutex> lk(d->mu);
+            Resident* r = nullptr;
+            if (int32_t rc = d->resolve(b->resident, "CUDA resident dispatch", &r)) {
+                undo();
+                return rc;
+            }
+            r->inflight++;  // held for the life of the prepared set: the graph has the pointer baked in
+            prep->resident_ids.push_back(b->resident.id);
+            dev_ptr = r->ptr;
+        } else {
+            dev_ptr = inst->acquire_temp(need);
+            if (!dev_ptr) {
+                undo();
+                return fail_oom(need, 0);
+            }
+            prep->temps.push_back(dev_ptr);
+            if (is_input) {
+                void* stage = inst->acquire_pinned(need);
+                if (!stage) {
+                    undo();
+                    return fail_oom(need, 0);
+                }
+                std::memcpy(stage, b->host_ptr, need);
+                prep->inputs.push_back({bd.binding, stage, need});
+            } else if (!overwrites_every_output_byte(p)) {
+                zero_fill.push_back({dev_ptr, need});
+            }
+        }
+        slot_ptr[bd.binding] = dev_ptr;
+        if (is_output) {
+            OutputSlot o;
+            o.value_id = bd.binding;
+            o.dev_ptr = static_cast<uint8_t*>(dev_ptr) + (bd.has_output_byte_range ? bd.output_byte_begin : 0);
+            o.len = logical;
+            o.host = inst->acquire_pinned(logical);
+            if (!o.host) {
+                undo();
+                return fail_oom(logical, 0);
+            }
+            prep->outputs.push_back(o);
+        }
+    }
+    prep->status_host = static_cast<uint32_t*>(inst->acquire_pinned(16));
+    prep->done = inst->acquire_event(false);
+    if (!prep->status_host || !prep->done) {
+        undo();
+        return fail_oom(16, 0);
+    }
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(inst->stream, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+        for (auto& in : prep->inputs) {
+            void* dst = slot_ptr[in.value_id];
+            cudaMemcpyAsync(dst, in.staging, in.len, cudaMemcpyHostToDevice, inst->stream);
+        }
+        for (auto& z : zero_fill) cudaMemsetAsync(z.first, 0, z.second, inst->stream);
+        cudaError_t le = dispatch(inst, slot_ptr, inst->stream);
+        for (auto& o : prep->outputs) cudaMemcpyAsync(o.host, o.dev_ptr, o.len, cudaMemcpyDeviceToHost, inst->stream);
+        cudaMemcpyAsync(prep->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
+        cudaMemsetAsync(inst->status_dev, 0, 16, inst->stream);
+        e = cudaStreamEndCapture(inst->stream, &graph);
+        if (e == cudaSuccess && le != cudaSuccess) e = le;
+    }
+    if (e == cudaSuccess) e = cudaGraphInstantiate(&prep->exec, graph, 0);
+    if (graph) cudaGraphDestroy(graph);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        undo();
+        return fail_dispatch(int(e), "capturing the prepared submission failed: " + cuda_msg(e));
+    }
+    inst->refs.fetch_add(1);
+    *prepared = prep.release();
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_prepared_submit(vyb_prepared* prep, const vyb_binding* host_updates, size_t n_updates, vyb_submission** submission) {
+    if (!prep || !submission || (!host_updates && n_updates))
+        return fail_invalid_program("Fix: pass a non-null prepared set, updates and submission out-pointer.");
+    vyb_instance* inst = prep->inst;
+    vyb_device* d = inst->dev;
+    if (int32_t rc = d->check_alive("submission")) return rc;
+    if (inst->generation != d->generation.load())
+        return fail_device_lost(d->device_name, inst->generation, "the instance belongs to a previous device generation");
+    std::lock_guard<std::mutex> ilk(inst->mu);
+    if (prep->busy)
+        return fail_invalid_program(
+            "Fix: the previous submission of this prepared set has not been waited for and freed; prepare one set per "
+            "submission in flight.");
+    for (size_t i = 0; i < n_updates; ++i) {
+        const vyb_binding& b = host_updates[i];
+        vyb_prepared::HostInput* in = nullptr;
+        for (auto& cand : prep->inputs)
+            if (cand.value_id == b.value_id) in = &cand;
+        if (!in || b.kind != VYB_BIND_HOST)
+            return fail_invalid_program("Fix: value id " + std::to_string(b.value_id) +
+                                        " is not a host input of this prepared set; only host-bound inputs can be updated.");
+        if (b.len != in->len || !b.host_ptr)
+            return fail_invalid_program("Fix: host bytes for value id " + std::to_string(b.value_id) + " must be exactly " +
+                                        std::to_string(in->len) + " bytes.");
+        std::memcpy(in->staging, b.host_ptr, in->len);  // copied in, like a fresh BindingSet
+    }
+    cudaSetDevice(d->ordinal);
+    prep->status_host[0] = 0;
+    cudaError_t e = cudaGraphLaunch(prep->exec, inst->stream);
+    if (e == cudaSuccess) e = cudaEventRecord(prep->done, inst->stream);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "replaying the prepared submission failed: " + cuda_msg(e));
+    }
+    prep->busy = true;
+    auto sub = std::make_unique<vyb_submission>();
+    sub->inst = inst;
+    sub->prepared = prep;
+    sub->done = prep->done;
+    sub->status_host = prep->status_host;
+    inst->refs.fetch_add(1);
+    *submission = sub.release();
+    clear_error();
+    return VYB_OK;
+}
+
+int32_t vyb_prepared_free(vyb_prepared* prep) {
+    if (!prep) return VYB_OK;
+    vyb_instance* inst = prep->inst;
+    vyb_device* d = inst->dev;
+    {
+        std::lock_guard<std::mutex> ilk(inst->mu);
+        if (prep->busy)
+            return fail_invalid_program("Fix: wait for and free the pending submission before freeing the prepared set.");
+        cudaSetDevice(d->ordinal);
+        if (prep->exec) cudaGraphExecDestroy(prep->exec);
+        for (void* t : prep->temps) inst->release_temp(t);
+        for (auto& in : prep->inputs) inst->release_pinned(in.staging);
+        for (auto& o : prep->outputs)
+            if (o.host) inst->release_pinned(o.host);
+        inst->release_pinned(prep->status_host);
+        inst->release_event(prep->done, false);
+    }
+    {
+        std::lock_guard<std::mutex> lk(d->mu);
+        for (uint64_t id : prep->resident_ids) {
+            auto it = d->residents.find(id);
+            if (it != d->residents.end() && it->second.inflight) it->second.inflight--;
+        }
+    }
+    delete prep;
+    instance_unref(inst);
+    return VYB_OK;
 }
 
 // ---- kernel-level entry points ----------------------------------------------------------------------------------------------
@@ -972,6 +1259,19 @@ int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_
     vybk::PeerGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;
     return launch_result(vybk::launch_allgather_wait(ag, static_cast<cudaStream_t>(stream), status), "all-gather wait");
+}
+
+int32_t vyb_k_tensor_peak(uint32_t int8, uint32_t iters, void* stream, uint32_t* status, double* ops_per_launch) {
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e == cudaSuccess)
+        e = vybk::launch_tensor_peak(int8, iters, sms, static_cast<cudaStream_t>(stream), status, ops_per_launch);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "tensor peak launch failed: " + cuda_msg(e) + "; there is no CPU path");
+    }
+    return VYB_OK;
 }
 
 int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,

@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             // power-of-two step: |x| / delta < 2^(8*LIMBS - 1); exponent clamped so that 1/delta stays finite
             int e = int((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
-            e = max(e, -100);
+            e = max(e, -90);
             const int de = e - (8 * LIMBS - 2);                                   // delta = 2^de
             const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);    // 2^-de
             float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);        // delta / 16
@@ -317,7 +317,7 @@ __global__ void __launch_bounds__(THREADS, 1) int4_gemv_kernel(const Params p) {
 #pragma unroll
             for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 16 lanes = 1 group
             int e = int((__float_as_uint(amax) >> 23) & 0xFFu) - 127;
-            e = max(e, -100);
+            e = max(e, -90);
             const int de = e - (8 * LIMBS - 2);
             const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);
             float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);
@@ -539,6 +539,21 @@ bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                              uint32_t* status, bool constant_weights) {
+    // Whole rows of 2048 or 4096 k: the half-SM kernel, whose launches overlap on every SM. bf16 outputs go four batch
+    // rows at a time (26-bit block-floating activations, 57-bit for a single row); f32 outputs one row at a time, so
+    // that every row gets the single-row precision.
+    if (int4_gemv_halfsm_supported(1, n, k, 128)) {
+        const size_t out_elem = out_f32 ? 4 : 2;
+        const uint32_t step = out_f32 ? 1 : 4;
+        for (uint32_t b0 = 0; b0 < m; b0 += step) {
+            const uint32_t mb = m - b0 < step ? m - b0 : step;
+            cudaError_t e = launch_int4_gemv_halfsm(static_cast<const uint16_t*>(x_bf16) + size_t(b0) * k, w_packed, scale_bf16,
+                                                    static_cast<uint8_t*>(y) + size_t(b0) * n * out_elem, mb, n, k, out_f32,
+                                                    sm_count, stream, status, constant_weights);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
     // opt in to the large dynamic shared-memory carve-out once per device
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
@@ -546,10 +561,10 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     if (de != cudaSuccess) return de;
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        cudaError_t e = cudaFuncSetAttribute(int4_gemv_kernel<2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e = cudaFuncSetAttribute(int4_gemv_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              SMEM_TOTAL);
         if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(int4_gemv_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+            e = cudaFuncSetAttribute(int4_gemv_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
         if (e != cudaSuccess) return e;
         configured.fetch_or(bit, std::memory_order_release);
     }
@@ -576,8 +591,8 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     // with constant weights the launch may overlap the tail of the preceding kernel of the stream
     cfg.attrs = &attr;
     cfg.numAttrs = constant_weights ? 1 : 0;
-    if (out_f32) return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<3, true>, p);
-    return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<2, false>, p);
+    if (out_f32) return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<4, true>, p);
+    return cudaLaunchKernelEx(&cfg, int4_gemv_kernel<3, false>, p);
 }
 
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,

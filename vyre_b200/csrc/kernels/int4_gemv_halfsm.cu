@@ -1,0 +1,553 @@
+// Decode GEMV for group-quantized int4 weights, batch <= 4, k <= 4096: the half-SM form.
+//
+//   y[m, n] = cast( sum_k x[m, k] * (q[n, k] - 8) * s[n, k / 128] )
+//
+// A decode GEMV moves about 200 KB of weights per SM and launch, a few microseconds of HBM time, so what a
+// launch costs beyond its bytes (start-up, the first loads' latency, the last tile's reduction, the gap to the
+// next launch) weighs as much as the stream itself. This kernel is shaped so that consecutive launches of a
+// stream overlap on every SM:
+//
+//  * One CTA per SM and launch, and that CTA takes LESS THAN HALF of an SM: 512 threads at <= 64 registers (batch
+//    <= 2, k = 4096) or 256 threads at <= 128 registers, and 113 KB of shared memory. With programmatic dependent launch the next launch's CTA becomes resident beside
+//    this one, prefetches three tiles of (constant) weights and only then waits for this launch to finish before
+//    it touches activations or outputs. While launch N works through the tail of its rows, launch N+1's weights
+//    are already on their way, so HBM does not idle at a launch boundary. The trigger
+//    (griddepcontrol.launch_dependents) is the first instruction of the kernel.
+//  * Each warp owns a fixed slice of k (256 or 512 wide) and runs its OWN three-deep pipeline over the 16-row tiles:
+//    16-byte cp.async copies (the load/store path, which streams finer-grained than 32 KB bulk copies: a warp
+//    refills its few KB as soon as it has read them) into a private region of shared memory, completion by
+//    cp.async.wait_group, no barrier between warps anywhere in the stream. Rows are stored with their 16-byte
+//    chunks XOR-swizzled by the row number so that the fragment loads of eight rows hit eight bank groups.
+//  * Math runs on the integer tensor path (mma.sync.m16n8k32, u8 x s8 -> s32) with ONE logic instruction per eight
+//    weights. A packed byte b = 16 q1 + q0 holds the weights of elements 2j and 2j+1. With integer activations
+//    X0, X1:  b * (16 X0) + (b & 0xF0) * (X1 - 16 X0) = 16 (q0 X0 + q1 X1). So the raw bytes are one A operand as
+//    they are, the masked bytes (`w & 0xF0F0F0F0`) the other, and the two B operands (16 X0 and X1 - 16 X0) are
+//    prepared once per CTA. The zero point costs nothing per weight either: sum 16 (q - 8) X = sum 16 q X -
+//    128 sum X, and -128 sum X (per group, known once the activations are converted) is what the group's
+//    accumulators start from.
+//  * Activations are converted once per CTA to block-floating integers: per (batch row, 128-k group) a power-of-two
+//    step delta = 2^(e_max - 25) and X = rint(x / delta), |X| < 2^26; the B values above stay below 2^31 and are
+//    written as four balanced base-256 digits d0..d3 in [-128, 127]. bf16 carries 8 significant bits, so every
+//    element within 2^-18 of its group's largest is represented EXACTLY; a smaller one is rounded to 2^-26 of the
+//    group maximum. The four digits of a batch row occupy four of the eight B-operand columns of the MMA (two batch
+//    rows per MMA). A single batch row has all eight columns: a warp whose slice holds an element below that 2^-18
+//    converts it with eight digits (|X| < 2^57, exact down to 2^-49 of the largest) at no cost in the stream. The integer sums are exact; per group the digit sums are recombined (d0 + 256 d1 in integers,
+//    the 65536 between digit pairs folded into the f32 factor) and scaled by s * delta / 16 in f32, the only place
+//    rounding happens.
+//  * The activation fragments of a warp's k slice stay in registers for the whole kernel, so shared memory is
+//    read once per weight byte. Per tile each warp leaves a 16 x batch partial in its own corner of shared
+//    memory; after the last tile (or every few tiles, when a CTA owns many) one barrier, and every thread sums the
+//    warps' partials of one output in fixed order (deterministic).
+//
+// Nothing in the kernel waits on another warp except that barrier, and nothing waits on a flag or an mbarrier: it
+// cannot hang.
+//
+// Replaces the generated scalar kernel of vyre-libs/src/nn/linear/inner/linear_4bit.rs:399-775 (one warp per
+// output, 4-byte loads, scalar f32 FMA) for the row-major layout of
+// vyre-primitives/src/math/quantized/programs.rs:186-300.
+#include <cuda_bf16.h>
+
+#include <atomic>
+
+#include "kernels.h"
+
+namespace vybk {
+namespace {
+
+constexpr int TILE_ROWS = 16;
+constexpr int STAGES = 3;
+constexpr int SMEM_W = STAGES * TILE_ROWS * 2048;             // weight stages of all warps: 3 tiles of 16 rows x 4096 k
+constexpr int SMEM_S = STAGES * TILE_ROWS * 64;               // their scales
+constexpr int SMEM_RED = 12288;                               // per-warp partial sums; the activation scratch of the prologue
+constexpr int SMEM_TOTAL = SMEM_W + SMEM_S + SMEM_RED;
+
+static_assert(2 * (SMEM_TOTAL + 1024) <= 233472, "two CTAs must fit one SM");
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// D(16x8, s32) = A(16x32, u8, row) * B(32x8, s8, col) + C
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1, int c0, int c1, int c2, int c3) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1), "r"(c2), "r"(c3));
+}
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+
+struct Params {
+    const uint16_t* x;
+    const uint8_t* w;
+    const uint16_t* scales;
+    void* y;
+    uint32_t m, n;
+    uint32_t tiles_per_cta, tiles_rem;  // whole 16-row tiles per CTA; the first tiles_rem CTAs own one more
+};
+
+// NM = MMAs per 16 rows x 32 k = ceil(m / 2); W warps, each owning GPW 128-k groups of every row: k = 128 GPW W
+template <int NM, int GPW, int W, bool OUT_F32>
+__global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Params p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    // let the next launch of the stream become resident beside this one at once; it waits (griddepcontrol.wait)
+    // before it reads activations or writes outputs. A no-op for plain launches.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    constexpr uint32_t K = 128u * GPW * W;
+    constexpr uint32_t ROW_BYTES = K / 2;            // packed bytes of one row of W
+    constexpr uint32_t PITCH = GPW * 64;             // of which this warp owns (= row pitch of its stages)
+    constexpr uint32_t CPR = GPW * 4;                // 16-byte chunks per row slice
+    constexpr uint32_t RPI = 32 / CPR;               // rows covered by one warp-wide cp.async
+    constexpr uint32_t NCP = TILE_ROWS / RPI;        // cp.async instructions per tile and lane
+    constexpr uint32_t WSTAGE = TILE_ROWS * PITCH;   // bytes of one warp's share of a tile
+    constexpr uint32_t SSTAGE = TILE_ROWS * GPW * 2; // and of its scales
+    constexpr uint32_t MM = 2 * NM;                  // batch rows of a partial
+    constexpr uint32_t PART = TILE_ROWS * MM * 4;    // bytes of one warp's partial of one tile
+    constexpr uint32_t PRIV = SMEM_RED / W;          // bytes of partials (and prologue scratch) a warp owns
+    constexpr uint32_t FLUSH = PRIV / PART;          // tiles between two reductions
+    static_assert(PRIV >= 2 * GPW * 128, "the activation scratch must fit a warp's own area");
+    static_assert(GPW == 2 || GPW == 4, "a warp owns 256 or 512 k");
+    static_assert(RPI % 2 == 0, "the row parity of a lane must not depend on the copy index");
+    static_assert(W * STAGES * (WSTAGE + SSTAGE) <= SMEM_W + SMEM_S, "stages must fit");
+
+    uint8_t* red = smem + SMEM_W + SMEM_S;
+
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    // whole tiles per CTA, the first tiles_rem CTAs one more than the rest
+    const uint32_t first_tile = blockIdx.x * p.tiles_per_cta + min(blockIdx.x, p.tiles_rem);
+    const uint32_t r0 = first_tile * TILE_ROWS;
+    const uint32_t r1 = min(p.n, r0 + (p.tiles_per_cta + (blockIdx.x < p.tiles_rem ? 1u : 0u)) * TILE_ROWS);
+    const uint32_t nrows = r1 - r0;
+    const uint32_t ntiles = (nrows + TILE_ROWS - 1) / TILE_ROWS;
+    uint8_t* my_w = smem + warp * (STAGES * WSTAGE);             // this warp's private weight stages
+    uint8_t* my_s = smem + SMEM_W + warp * (STAGES * SSTAGE);    // and their scales
+
+    // ---- this warp's private weight pipeline: one commit group per tile, STAGES tiles deep ---------------------
+    // Lane l of copy i moves chunk l % CPR of row i * RPI + l / CPR. Odd rows are stored with the two 64-byte halves of
+    // every 128 bytes swapped: a 128-bit fragment load is served a quarter warp at a time (rows 2q and 2q+1, four
+    // consecutive chunks each), and the swap puts those eight chunks into eight different 16-byte bank groups.
+    const uint32_t cp_row = lane / CPR, cp_chunk = lane % CPR;
+    const uint8_t* cp_src = p.w + size_t(r0 + cp_row) * ROW_BYTES + warp * PITCH + cp_chunk * 16;
+    const uint32_t cp_dst = smem_u32(my_w) + cp_row * PITCH + ((cp_chunk ^ ((cp_row & 1u) << 2)) << 4);
+    const uint32_t sc_row = lane / (GPW / 2), sc_unit = lane % (GPW / 2);  // 4-byte units of scales
+    const uint16_t* sc_src = p.scales + size_t(r0 + sc_row) * (K / 128) + warp * GPW + sc_unit * 2;
+    const uint32_t sc_dst = smem_u32(my_s) + sc_row * (GPW * 2) + sc_unit * 4;
+    uint32_t issue_stage = 0, issue_rows = nrows;  // stage offset index and rows left for the next tile to issue
+    auto issue_tile = [&]() {
+        if (issue_rows > 0) {
+            const uint32_t dst = cp_dst + issue_stage * WSTAGE;
+            if (issue_rows >= TILE_ROWS) {  // every tile but possibly the last
+#pragma unroll
+                for (uint32_t i = 0; i < NCP; ++i) cp_async_16(dst + i * RPI * PITCH, cp_src + i * RPI * ROW_BYTES);
+                if (GPW == 4 || sc_row < TILE_ROWS) cp_async_4(sc_dst + issue_stage * SSTAGE, sc_src);
+            } else {
+#pragma unroll
+                for (uint32_t i = 0; i < NCP; ++i)
+                    if (cp_row + i * RPI < issue_rows) cp_async_16(dst + i * RPI * PITCH, cp_src + i * RPI * ROW_BYTES);
+                if (sc_row < issue_rows) cp_async_4(sc_dst + issue_stage * SSTAGE, sc_src);
+            }
+            cp_src += TILE_ROWS * ROW_BYTES;
+            sc_src += TILE_ROWS * (K / 128);
+            issue_rows = issue_rows > TILE_ROWS ? issue_rows - TILE_ROWS : 0u;
+            issue_stage = issue_stage == STAGES - 1 ? 0u : issue_stage + 1;
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int u = 0; u < STAGES; ++u) issue_tile();  // weights are constants: prefetched before the dependency wait
+
+    const uint32_t g = lane >> 2;  // A/D fragment row, B fragment column
+    const uint32_t t = lane & 3;
+
+    // ---- activations: everything below reads x, so the previous launch of the stream must be complete ----
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t xb[NM][GPW][8];  // [mma][group of this warp][byte block 0 | 1][operand 0 | 1][bytes 0-3 | 4-7]
+    float dq[NM][GPW];        // delta / 16 of (batch row of this lane's D columns, group), x 65536 for the high digit pair
+    int corr[NM][GPW];        // -128 x (sum of the group's X, low or high 16-bit part) for this lane's D columns: zero point
+#pragma unroll
+    for (int nm = 0; nm < NM; ++nm)
+#pragma unroll
+        for (int c = 0; c < GPW; ++c) {
+            dq[nm][c] = 0.0f;
+            corr[nm][c] = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) xb[nm][c][i] = 0u;
+        }
+    {
+        // Every warp converts its OWN k slice (16 elements per lane) and hands the digits to the lanes that need them
+        // through scratch that only this warp touches: its own area of partial sums, which nobody else reads before the
+        // first reduction barrier. No CTA barrier.
+        constexpr uint32_t DIGIT_BYTES = GPW * 128;  // one digit of the slice: 8 bytes of each operand per 16 elements
+        auto scratch = [&](uint32_t off) -> uint8_t* { return red + warp * PRIV + off; };
+        const bool has = lane < GPW * 8;  // 16 elements per lane cover the slice
+#pragma unroll
+        for (int j = 0; j < 2 * NM; ++j) {
+            if (uint32_t(j) >= p.m) break;
+            uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
+            if (has) {
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * K + warp * (GPW * 128) + lane * 16);
+                x0 = __ldcg(src);
+                x1 = __ldcg(src + 1);
+            }
+            const uint32_t r[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};  // r[i] = elements 2i (low half), 2i+1
+            // largest magnitude of the group as an integer maximum of |bits| (positive floats order like their bits, and a
+            // NaN, which a float maximum would drop, orders above infinity)
+            uint32_t amax = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = max(amax, max((r[i] << 16) & 0x7FFF0000u, r[i] & 0x7FFF0000u));
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 8 lanes = 1 group
+            const int ebits = int(amax >> 23);  // biased exponent; 255 = Inf or NaN in the group
+            if constexpr (NM == 1) {
+                // A single batch row has all eight B columns to itself. When some element of this warp's slice lies more
+                // than 2^18 below its group's largest (four digits would round it), the slice is converted with eight
+                // digits instead: |X| < 2^57, exact for every element within 2^-49 of the largest.
+                if (p.m == 1) {
+                    bool small = false;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int e0 = int((r[i] >> 7) & 0xFFu), e1 = int((r[i] >> 23) & 0xFFu);
+                        small |= ((r[i] & 0x7FFFu) != 0 && e0 < ebits - 18) | ((r[i] & 0x7FFF0000u) != 0 && e1 < ebits - 18);
+                    }
+                    if (__any_sync(0xffffffffu, small)) {
+                        const int ew = max(ebits - 127, -60);
+                        float delta16 = __uint_as_float(uint32_t(127 + ew - 60) << 23);  // delta / 16, delta = 2^(ew - 56)
+                        if (ebits == 255) delta16 = __uint_as_float(0x7FC00000u);
+                        uint32_t zl[2][8], zh[2][8];  // [operand][byte]: digits 0-3 and 4-7 of its value
+                        int psum[4] = {0, 0, 0, 0};   // sums of the four balanced 16-bit parts of X
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            long long X[2];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                const uint32_t b = h ? (r[i] >> 16) : (r[i] & 0xFFFFu);
+                                const int eb = int((b >> 7) & 0xFFu);
+                                const long long m8 = eb ? (long long)((b & 0x7Fu) | 0x80u) : 0ll;  // x = m8 * 2^(eb - 134)
+                                const int sh = eb - ew - 78;                                        // X = m8 * 2^sh
+                                long long v = sh >= 0 ? (m8 << min(sh, 50)) : (sh > -10 ? ((m8 + (1ll << (-sh - 1))) >> -sh) : 0ll);
+                                X[h] = (b & 0x8000u) ? -v : v;
+                                const long long Y = X[h] + 0x0000800080008000ll;
+                                psum[0] += int(Y & 0xFFFF) - 0x8000;
+                                psum[1] += int((Y >> 16) & 0xFFFF) - 0x8000;
+                                psum[2] += int((Y >> 32) & 0xFFFF) - 0x8000;
+                                psum[3] += int(Y >> 48);
+                            }
+                            const long long V0 = X[0] << 4, V1 = X[1] - V0;
+                            const unsigned long long Z0 = (unsigned long long)(V0 + 0x0080808080808080ll) ^ 0x0080808080808080ull;
+                            const unsigned long long Z1 = (unsigned long long)(V1 + 0x0080808080808080ll) ^ 0x0080808080808080ull;
+                            zl[0][i] = uint32_t(Z0); zh[0][i] = uint32_t(Z0 >> 32);
+                            zl[1][i] = uint32_t(Z1); zh[1][i] = uint32_t(Z1 >> 32);
+                        }
+#pragma unroll
+                        for (int d = 0; d < 4; ++d)
+#pragma unroll
+                            for (int o = 1; o < 8; o <<= 1) psum[d] += __shfl_xor_sync(0xffffffffu, psum[d], o);
+                        uint32_t dig8[8][4];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+#pragma unroll
+                            for (int half = 0; half < 2; ++half) {
+                                const uint32_t* z = half ? zh[q >> 1] : zl[q >> 1];
+                                const int b = (q & 1) * 4;
+                                const uint32_t t0 = __byte_perm(z[b], z[b + 1], 0x5140), t1 = __byte_perm(z[b], z[b + 1], 0x7362);
+                                const uint32_t t2 = __byte_perm(z[b + 2], z[b + 3], 0x5140), t3 = __byte_perm(z[b + 2], z[b + 3], 0x7362);
+                                dig8[4 * half + 0][q] = __byte_perm(t0, t2, 0x5410);
+                                dig8[4 * half + 1][q] = __byte_perm(t0, t2, 0x7632);
+                                dig8[4 * half + 2][q] = __byte_perm(t1, t3, 0x5410);
+                                dig8[4 * half + 3][q] = __byte_perm(t1, t3, 0x7632);
+                            }
+                        }
+#pragma unroll
+                        for (int ph = 0; ph < 4; ++ph) {
+                            if (has) {
+                                *reinterpret_cast<uint4*>(scratch(lane * 16)) =
+                                    make_uint4(dig8[2 * ph][0], dig8[2 * ph][1], dig8[2 * ph][2], dig8[2 * ph][3]);
+                                *reinterpret_cast<uint4*>(scratch(DIGIT_BYTES + lane * 16)) =
+                                    make_uint4(dig8[2 * ph + 1][0], dig8[2 * ph + 1][1], dig8[2 * ph + 1][2], dig8[2 * ph + 1][3]);
+                            }
+                            __syncwarp();
+                            if ((g >> 1) == uint32_t(ph)) {  // B column g holds digit g
+#pragma unroll
+                                for (int c = 0; c < GPW; ++c) {
+                                    const uint8_t* src = scratch((g & 1) * DIGIT_BYTES + c * 128) + t * 32;
+                                    const uint4 a = *reinterpret_cast<const uint4*>(src);
+                                    const uint4 b = *reinterpret_cast<const uint4*>(src + 16);
+                                    uint32_t(&dst)[8] = xb[0][c];
+                                    dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+                                    dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+                                }
+                            }
+                            __syncwarp();
+                        }
+                        // D columns 2t, 2t+1 hold digits 2t, 2t+1: the 16-bit part t of X, weight 65536^t
+#pragma unroll
+                        for (int c = 0; c < GPW; ++c) {
+                            const float d = __shfl_sync(0xffffffffu, delta16, c * 8);
+                            int sp[4];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) sp[q] = __shfl_sync(0xffffffffu, psum[q], c * 8);
+                            dq[0][c] = d * __uint_as_float((127u + 16u * t) << 23);
+                            corr[0][c] = (t == 0 ? sp[0] : t == 1 ? sp[1] : t == 2 ? sp[2] : sp[3]) * -128;
+                        }
+                        break;
+                    }
+                }
+            }
+            const int e = max(ebits - 127, -90);
+            const int de = e - 25;                                              // delta = 2^de, |x / delta| < 2^26
+            const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);  // 2^-de
+            float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);      // delta / 16
+            if (ebits == 255) delta16 = __uint_as_float(0x7FC00000u);  // Inf/NaN activations poison their group's outputs
+            // per packed byte i (elements 2i, 2i+1): operand 0 = 16 X0, operand 1 = X1 - 16 X0, each as four balanced
+            // base-256 digits at once: with Y = V + 0x808080 the low three bytes of Y, top bit flipped, are d0..d2 in
+            // [-128, 127] and the top byte of Y is d3. Also the sums of the low and high 16-bit parts of X.
+            uint32_t z0[8], z1[8];
+            int sum_lo = 0, sum_hi = 0;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int X0 = __float2int_rn(bf16_lo(r[i]) * inv_delta), X1 = __float2int_rn(bf16_hi(r[i]) * inv_delta);
+                const int V0 = X0 << 4, V1 = X1 - V0;
+                z0[i] = uint32_t(V0 + 0x00808080) ^ 0x00808080u;
+                z1[i] = uint32_t(V1 + 0x00808080) ^ 0x00808080u;
+                const int Y0 = X0 + 0x8000, Y1 = X1 + 0x8000;  // X = (Y >> 16) * 65536 + ((Y & 0xFFFF) - 0x8000)
+                sum_hi += (Y0 >> 16) + (Y1 >> 16);
+                sum_lo += int(Y0 & 0xFFFF) + int(Y1 & 0xFFFF) - 0x10000;
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, o);
+                sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, o);
+            }
+            // byte transpose: dig[d] = digit d of (operand 0 bytes 0-3, operand 0 bytes 4-7, operand 1 bytes 0-3, 4-7)
+            uint32_t dig[4][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t* z = (q & 2) ? z1 : z0;
+                const int b = (q & 1) * 4;
+                const uint32_t t0 = __byte_perm(z[b], z[b + 1], 0x5140), t1 = __byte_perm(z[b], z[b + 1], 0x7362);
+                const uint32_t t2 = __byte_perm(z[b + 2], z[b + 3], 0x5140), t3 = __byte_perm(z[b + 2], z[b + 3], 0x7362);
+                dig[0][q] = __byte_perm(t0, t2, 0x5410);
+                dig[1][q] = __byte_perm(t0, t2, 0x7632);
+                dig[2][q] = __byte_perm(t1, t3, 0x5410);
+                dig[3][q] = __byte_perm(t1, t3, 0x7632);
+            }
+#pragma unroll
+            for (int ph = 0; ph < 2; ++ph) {
+                if (has) {
+                    *reinterpret_cast<uint4*>(scratch(lane * 16)) = make_uint4(dig[2 * ph][0], dig[2 * ph][1], dig[2 * ph][2], dig[2 * ph][3]);
+                    *reinterpret_cast<uint4*>(scratch(DIGIT_BYTES + lane * 16)) =
+                        make_uint4(dig[2 * ph + 1][0], dig[2 * ph + 1][1], dig[2 * ph + 1][2], dig[2 * ph + 1][3]);
+                }
+                __syncwarp();
+                // B column g holds digit g % 4 of batch row 2 nm + g / 4; this lane's 16 weight bytes of group c were
+                // converted by lanes 8c + 2t (byte block 0) and 8c + 2t + 1 (byte block 1)
+                if ((g >> 2) == uint32_t(j & 1) && ((g >> 1) & 1) == uint32_t(ph)) {
+#pragma unroll
+                    for (int c = 0; c < GPW; ++c) {
+                        const uint8_t* src = scratch((g & 1) * DIGIT_BYTES + c * 128) + t * 32;
+                        const uint4 a = *reinterpret_cast<const uint4*>(src);
+                        const uint4 b = *reinterpret_cast<const uint4*>(src + 16);
+                        uint32_t(&dst)[8] = xb[j >> 1][c];
+                        dst[0] = a.x; dst[1] = a.y; dst[2] = a.z; dst[3] = a.w;
+                        dst[4] = b.x; dst[5] = b.y; dst[6] = b.z; dst[7] = b.w;
+                    }
+                }
+                __syncwarp();
+            }
+            // D columns 2t, 2t+1 hold digits 2 (t & 1), +1 of batch row 2 nm + t / 2; group c was converted by lanes 8c..
+#pragma unroll
+            for (int c = 0; c < GPW; ++c) {
+                const float d = __shfl_sync(0xffffffffu, delta16, c * 8);
+                const int sl = __shfl_sync(0xffffffffu, sum_lo, c * 8), sh = __shfl_sync(0xffffffffu, sum_hi, c * 8);
+                if ((t >> 1) == uint32_t(j & 1)) {
+                    dq[j >> 1][c] = d * ((t & 1) ? 65536.0f : 1.0f);
+                    corr[j >> 1][c] = ((t & 1) ? sh : sl) * -128;
+                }
+            }
+        }
+    }
+
+    // sum the warps' partials of the tiles [first, first + count) in warp order and store the outputs
+    auto reduce_tiles = [&](uint32_t first, uint32_t count) {
+        __syncthreads();
+        for (uint32_t idx = threadIdx.x; idx < count * (TILE_ROWS * MM); idx += W * 32) {
+            const uint32_t col = idx % MM, row = r0 + first * TILE_ROWS + idx / MM;
+            const float* src = reinterpret_cast<const float*>(red) + idx;  // [tile][row][col] inside a warp's area
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < W; ++w) sum += src[w * (PRIV / 4)];
+            if (row < r1 && col < p.m) {
+                if constexpr (OUT_F32)
+                    static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
+                else
+                    static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
+            }
+        }
+    };
+
+    // fragment addresses inside a stage: chunk 4c + t of row g (and g + 8), halves swapped in odd rows
+    const uint32_t lds_base = g * PITCH + (t << 4);
+    const uint32_t lds_even = lds_base + ((g & 1u) << 6);         // group 0 (and 2: +128)
+    const uint32_t lds_odd = lds_base + (((g & 1u) ^ 1u) << 6);   // group 1 (and 3: +128)
+    const uint32_t lds_scale = g * (GPW * 2);
+
+    uint32_t stage = 0, pending = 0;  // pending: tiles whose partials wait in shared memory
+    float* part = reinterpret_cast<float*>(red + warp * PRIV) + g * MM + (t >> 1);
+    for (uint32_t u = 0; u < ntiles; ++u) {
+        cp_async_wait<STAGES - 1>();  // this thread's copies of tile u have landed ...
+        __syncwarp();                 // ... and so have the other lanes'
+        const uint8_t* ws = my_w + stage * WSTAGE;
+        const uint8_t* ss = my_s + stage * SSTAGE + lds_scale;
+        stage = stage == STAGES - 1 ? 0u : stage + 1;
+        uint4 wl[GPW], wh[GPW];
+#pragma unroll
+        for (int c = 0; c < GPW; ++c) {
+            const uint8_t* src = ws + ((c & 1) ? lds_odd : lds_even) + (c >> 1) * 128;
+            wl[c] = *reinterpret_cast<const uint4*>(src);
+            wh[c] = *reinterpret_cast<const uint4*>(src + 8 * PITCH);
+        }
+        // bf16 scales of this warp's groups: row g in sa, row g + 8 in sb
+        uint32_t sa[GPW / 2], sb[GPW / 2];
+        if constexpr (GPW == 4) {
+            const uint2 a = *reinterpret_cast<const uint2*>(ss);
+            const uint2 b = *reinterpret_cast<const uint2*>(ss + 8 * GPW * 2);
+            sa[0] = a.x; sa[1] = a.y; sb[0] = b.x; sb[1] = b.y;
+        } else {
+            sa[0] = *reinterpret_cast<const uint32_t*>(ss);
+            sb[0] = *reinterpret_cast<const uint32_t*>(ss + 8 * GPW * 2);
+        }
+        // the whole slice of the tile sits in registers: refill the stage while the math runs
+        __syncwarp();
+        issue_tile();
+
+        float P[NM][2];
+#pragma unroll
+        for (int nm = 0; nm < NM; ++nm) P[nm][0] = P[nm][1] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < GPW; ++c) {
+            int acc[NM][4];
+            const uint32_t lo[4] = {wl[c].x, wl[c].y, wl[c].z, wl[c].w};
+            const uint32_t hi[4] = {wh[c].x, wh[c].y, wh[c].z, wh[c].w};
+#pragma unroll
+            for (int blk = 0; blk < 2; ++blk) {
+                // raw bytes against 16 X0, then masked bytes against X1 - 16 X0
+                const uint32_t a0 = lo[2 * blk], a1 = hi[2 * blk], a2 = lo[2 * blk + 1], a3 = hi[2 * blk + 1];
+                const uint32_t m0 = a0 & 0xF0F0F0F0u, m1 = a1 & 0xF0F0F0F0u, m2 = a2 & 0xF0F0F0F0u, m3 = a3 & 0xF0F0F0F0u;
+#pragma unroll
+                for (int nm = 0; nm < NM; ++nm) {
+                    if (blk == 0)  // the group's accumulators start from the zero-point term (all of it in the low digit)
+                        mma_u8s8(acc[nm], a0, a1, a2, a3, xb[nm][c][0], xb[nm][c][1], corr[nm][c], 0, corr[nm][c], 0);
+                    else
+                        mma_u8s8(acc[nm], a0, a1, a2, a3, xb[nm][c][4], xb[nm][c][5], acc[nm][0], acc[nm][1], acc[nm][2], acc[nm][3]);
+                    mma_u8s8(acc[nm], m0, m1, m2, m3, xb[nm][c][4 * blk + 2], xb[nm][c][4 * blk + 3], acc[nm][0], acc[nm][1],
+                             acc[nm][2], acc[nm][3]);
+                }
+            }
+            const float s_lo = (c & 1) ? bf16_hi(sa[c >> 1]) : bf16_lo(sa[c >> 1]);
+            const float s_hi = (c & 1) ? bf16_hi(sb[c >> 1]) : bf16_lo(sb[c >> 1]);
+#pragma unroll
+            for (int nm = 0; nm < NM; ++nm) {
+                // |accumulators| < 2^22 per group and |zero-point term| < 2^29: d_lo + 256 d_hi stays below 2^31
+                const float v_lo = float(acc[nm][0] + (acc[nm][1] << 8));
+                const float v_hi = float(acc[nm][2] + (acc[nm][3] << 8));
+                P[nm][0] = fmaf(s_lo * dq[nm][c], v_lo, P[nm][0]);
+                P[nm][1] = fmaf(s_hi * dq[nm][c], v_hi, P[nm][1]);
+            }
+        }
+        // low and high digit pairs of a batch row sit in neighbouring lanes; a single batch row may use all four pairs
+#pragma unroll
+        for (int nm = 0; nm < NM; ++nm) {
+            P[nm][0] += __shfl_xor_sync(0xffffffffu, P[nm][0], 1);
+            P[nm][1] += __shfl_xor_sync(0xffffffffu, P[nm][1], 1);
+        }
+        if (NM == 1 && p.m == 1) {
+            P[0][0] += __shfl_xor_sync(0xffffffffu, P[0][0], 2);
+            P[0][1] += __shfl_xor_sync(0xffffffffu, P[0][1], 2);
+        }
+        if ((t & 1) == 0 && !(NM == 1 && p.m == 1 && t != 0)) {
+#pragma unroll
+            for (int nm = 0; nm < NM; ++nm) {
+                part[pending * (PART / 4) + 2 * nm] = P[nm][0];
+                part[pending * (PART / 4) + 8 * MM + 2 * nm] = P[nm][1];
+            }
+        }
+        if (++pending == FLUSH && u + 1 < ntiles) {  // a CTA with many tiles: sum what has piled up and start over
+            reduce_tiles(u + 1 - FLUSH, FLUSH);
+            __syncthreads();
+            pending = 0;
+        }
+    }
+    cp_async_wait<0>();
+    if (pending) reduce_tiles(ntiles - pending, pending);
+}
+
+}  // namespace
+
+bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
+    return m >= 1 && m <= 4 && n >= 1 && group == 128 && (k == 2048 || k == 4096);
+}
+
+cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                    uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
+                                    uint32_t* status, bool constant_weights) {
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaError_t de = cudaGetDevice(&dev);
+    if (de != cudaSuccess) return de;
+    const uint64_t bit = 1ull << (dev & 63);
+    using Kernel = void (*)(const Params);
+    // [variant][f32 out]: 0: batch <= 2, k 4096; 1: batch <= 2, k 2048; 2: batch <= 4, k 4096; 3: batch <= 4, k 2048
+    static const Kernel kernels[4][2] = {
+        {int4_gemv_halfsm_kernel<1, 4, 8, false>, int4_gemv_halfsm_kernel<1, 4, 8, true>},
+        {int4_gemv_halfsm_kernel<1, 2, 8, false>, int4_gemv_halfsm_kernel<1, 2, 8, true>},
+        {int4_gemv_halfsm_kernel<2, 4, 8, false>, int4_gemv_halfsm_kernel<2, 4, 8, true>},
+        {int4_gemv_halfsm_kernel<2, 2, 8, false>, int4_gemv_halfsm_kernel<2, 2, 8, true>}};
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        for (int i = 0; i < 8; ++i) {
+            const void* f = (const void*)kernels[i >> 1][i & 1];
+            cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (e != cudaSuccess) return e;
+        }
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    Params p;
+    p.x = static_cast<const uint16_t*>(x_bf16);
+    p.w = static_cast<const uint8_t*>(w_packed);
+    p.scales = static_cast<const uint16_t*>(scale_bf16);
+    p.y = y;
+    p.m = m;
+    p.n = n;
+    (void)status;  // nothing in this kernel can time out
+    // One CTA per SM, whole 16-row tiles each, the remainder spread one tile per CTA (14336 rows on 148 SMs: eight
+    // CTAs with 7 tiles, the others with 6). Measured against 128 CTAs x 7 tiles and against two CTAs per SM (which
+    // leave no room for the next launch): this split is the fastest.
+    const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
+    const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
+    p.tiles_per_cta = tiles / grid;
+    p.tiles_rem = tiles % grid;
+    const int variant = (m <= 2 ? 0 : 2) + (k == 4096 ? 0 : 1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = SMEM_TOTAL;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr = {};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = constant_weights ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernels[variant][out_f32 ? 1 : 0], p);
+}
+
+}  // namespace vybk

@@ -7,8 +7,9 @@
 // free byte of device memory to its cache and pinned the rest, a host thread inside a region where the allocator's
 // lock must not be taken, or a library embedded in a process whose memory budget was fixed at start-up. For them
 // this file offers the same two kernels (per-token quantiser, then the tcgen05 int8 GEMM) with `xq` placed in a
-// file-scope device array of fixed size. The array is part of the loaded module, so no call here reserves or
-// returns device memory.
+// file-scope device array of fixed size. The array belongs to the module that holds these kernels: the device
+// memory for it is reserved when that module is loaded on a device, which with lazy module loading happens during
+// the first, set-up call on that device (see below) and never after it.
 //
 // Rules that follow from sharing one array:
 //   * m * k must not exceed STATIC_SCRATCH_BYTES (8 MiB); larger shapes are refused before anything is launched.
@@ -93,7 +94,7 @@ extern "C" int32_t vyb_k_linear_int8_dynamic_static_scratch(const void* x_bf16, 
                                     ", or use vyb_k_quantize_per_token_int8 + vyb_k_int8_gemm_i32 with your own buffer.");
     if (!vybk::int8_gemm_supported(m, n, k))
         return fail_unsupported("int8 gemm shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
-                                std::to_string(k) + " (needs k a multiple of 16 and at most 133000)");
+                                std::to_string(k) + " (needs k a multiple of 16 and at most 132096)");
     if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_i8) | reinterpret_cast<uintptr_t>(y_i32)) & 15)
         return fail_invalid_program("Fix: dynamic int8 linear operands must be 16-byte aligned (TMA tensor maps need it).");
     int dev = 0, sms = 0;

@@ -188,7 +188,7 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 }  // namespace
 
 bool int8_gemm_pair_supported(uint32_t m, uint32_t n, uint32_t k) {
-    return m > 128 && n >= 1 && k >= 16 && k % 16 == 0 && k <= 133000;
+    return m > 128 && n >= 1 && k >= 16 && k % 16 == 0 && k <= 132096;
 }
 
 cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,

@@ -228,8 +228,9 @@ cudaError_t launch_quantize_per_token_int8(const void* x_bf16, int8_t* q, float*
 }
 
 bool int8_gemm_supported(uint32_t m, uint32_t n, uint32_t k) {
-    // tensor-map strides must be multiples of 16 bytes; K * 127^2 must stay below 2^31
-    return m >= 1 && n >= 1 && k >= 16 && k % 16 == 0 && k <= 133000;
+    // tensor-map strides must be multiples of 16 bytes; the int32 sums must not wrap: activations are clamped to
+    // +-127 but a weight may be -128, so k * 127 * 128 must stay below 2^31 (k <= 132104)
+    return m >= 1 && n >= 1 && k >= 16 && k % 16 == 0 && k <= 132096;
 }
 
 cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,

@@ -14,6 +14,11 @@ bool int4_gemv_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                              uint32_t* status, bool constant_weights = false);
+// half-SM form (int4_gemv_halfsm.cu): m <= 4, k 2048 or 4096; launch_int4_gemv routes to it
+bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
+cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                    uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
+                                    uint32_t* status, bool constant_weights);
 // ---- all-gather of column-parallel outputs over peer memory (allgather_push.cu) ------------------------------------
 // gather buffers [2][world][m][n] bf16 per rank; arrival counters and the launch counter are 32-bit device words,
 // zero before the first push
@@ -99,6 +104,10 @@ cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out
                                   int sm_count, cudaStream_t stream, uint32_t* status);
 cudaError_t launch_quantize_per_token_int8(const void* x_bf16, int8_t* q, float* scales, uint32_t m, uint32_t k,
                                            cudaStream_t stream);
+
+// ---- tensor-core peak microbenchmark (tensor_peak.cu): MMAs from shared-memory operands only; for the bench's roofline
+cudaError_t launch_tensor_peak(uint32_t int8, uint32_t iters, int sm_count, cudaStream_t stream, uint32_t* status,
+                               double* ops_per_launch);
 
 // ---- the same two kernels with the quantised activations in a fixed device array (int8_dynamic_static_scratch.cu)
 size_t int8_dynamic_static_scratch_limit();

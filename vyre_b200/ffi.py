@@ -169,10 +169,15 @@ _STATUS_FUNCS = {
     "vyb_materialize": [_P, _P, _P, _PP],
     "vyb_instance_device": [_P, C.POINTER(DeviceIdentity)],
     "vyb_submit": [_P, C.c_char_p, C.POINTER(Binding), C.c_size_t, C.POINTER(DispatchConfig), _PP],
+    "vyb_prepare": [_P, C.c_char_p, C.POINTER(Binding), C.c_size_t, _PP],
+    "vyb_prepared_submit": [_P, C.POINTER(Binding), C.c_size_t, _PP],
+    "vyb_prepared_free": [_P],
+    "vyb_instance_inject_status": [_P, _U],
     "vyb_submission_is_ready": [_P],
     "vyb_submission_wait": [_P, _PP],
     "vyb_completion_output": [_P, _U, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
     "vyb_completion_device_ns": [_P, C.POINTER(C.c_uint64)],
+    "vyb_k_tensor_peak": [_U, _U, _P, _P, C.POINTER(C.c_double)],
     "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int4_gemv_ex": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int8_weight_only_linear": [_P, _P, _P, _P, _U, _U, _U, _P],
