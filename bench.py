@@ -2,19 +2,21 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
 
-Headline (N=1): the int4 group-quantized decode GEMV of the benchmark's second configuration
-(W u4 [14336, 4096], group 128, bf16 scales, x bf16 [M=1, 4096]), reported as achieved HBM GB/s =
-algorithmic bytes per launch / device time per launch. A step is one GEMV launch over one batch of
-activations; launches rotate over 8 resident copies of the weights (242 MB > the 126 MB L2) so every step
-streams its weights from HBM. Timing is CUDA events on the launching stream, max over ranks.
+Headline: the int4 group-quantized decode GEMV of the benchmark's second configuration (W u4 [14336, 4096], group
+128, bf16 scales, x bf16 [M=1, 4096]), reported as achieved HBM GB/s = algorithmic bytes / device time. A STEP is one
+pass over 8 resident copies of the weights (8 GEMV launches, captured in one CUDA graph): 242 MB > the 126 MB L2, so
+every launch streams its weights from HBM. W warm-up steps, then exactly K timed steps, CUDA events on the launching
+stream, max over ranks.
 
-For N > 1 the linear is sharded column-parallel: every rank owns a [14336, 4096] shard of a 14336*N-row
-linear (weak scaling) and each step's bf16 outputs are all-gathered by this library's own peer-store kernel over
-NVLink (one CTA on a side stream, bounded completion checks), overlapped with the next GEMV and verified once
-against NCCL's all-gather before timing.
+For N > 1 the linear is sharded column-parallel: every rank owns a [14336, 4096] shard of a 14336*N-row linear (weak
+scaling) and each launch's bf16 outputs are all-gathered by this library's own peer-store kernel over NVLink (one CTA
+per peer on a side stream, bounded completion checks), overlapped with the next GEMV and verified once against NCCL's
+all-gather before timing. The same run also measures, at every N, the two sharded configurations of the path and
+prints them under `secondary`: the expert-parallel MoE FFN layer (config 4, 4096 tokens in total, strong scaling) and
+the column-parallel int8 linear (config 5, N sharded over the ranks, peer-store gather of the int32 outputs).
 
-`--impl reference` times the CPU restatement of the reference engine (oracle/) on the host cores over a bounded
-row sample of the same workload.
+`--impl reference` times the reference bench's CPU loop (oracle/cpu_baseline.cpp) on all host cores over the same
+workload: a step is the same 8 GEMVs.
 """
 from __future__ import annotations
 
@@ -28,8 +30,6 @@ import sys
 import threading
 import time
 
-import numpy as np
-
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -37,6 +37,12 @@ if ROOT not in sys.path:
 N_OUT, K_IN, GROUP = 14336, 4096, 128
 COPIES = 8
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+METRIC = "int4_decode_gemv_hbm_gbs"
+
+
+def workload_name(m: int) -> str:
+    return f"int4 group-quantized decode GEMV M={m} N={N_OUT} K={K_IN} g={GROUP} (config 2), step = {COPIES} launches over {COPIES} rotating weight copies"
 
 
 def algorithmic_bytes(m: int, n: int = N_OUT, k: int = K_IN, group: int = GROUP) -> int:
@@ -44,13 +50,25 @@ def algorithmic_bytes(m: int, n: int = N_OUT, k: int = K_IN, group: int = GROUP)
     return n * k // 2 + n * (k // group) * 2 + m * k * 2 + m * n * 2
 
 
-def measured_peaks() -> tuple[float, str]:
-    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def measured_peaks() -> dict:
     try:
-        with open(p) as fh:
-            return float(json.load(fh)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "kind": "measured"}
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "bf16_tflops_sustained": 1400.0, "kind": "fallback"}
+
+
+def cpu_model() -> str:
+    try:
+        with open("/proc/cpuinfo") as fh:
+            for line in fh:
+                if line.startswith("model name"):
+                    return line.split(":", 1)[1].strip()
+    except Exception:
+        pass
+    return "unknown"
 
 
 class ClockSampler:
@@ -81,11 +99,9 @@ class ClockSampler:
     def mark(self):
         return len(self.rows)
 
-    def stop(self, lo: int = 0, hi: int | None = None) -> dict:
+    def summary(self, lo: int = 0, hi: int | None = None) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.12)
-        self.proc.terminate()
         rows = self.rows[lo:hi] or self.rows[-3:]
         sm, mx, reasons = [], [], set()
         for r in rows:
@@ -100,60 +116,105 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
 
+    def stop(self):
+        if self.proc is not None:
+            time.sleep(0.12)
+            self.proc.terminate()
 
-def cpu_reference_rate(m: int, budget_s: float, steps: int | None = None, warmup: int = 0):
-    """Times the CPU restatement of the reference engine on a bounded row sample of the GEMV workload.
-    Returns (GB/s, seconds per step, sample description, threads)."""
-    import oracle
+
+# ---------------------------------------------------------------------------------------------------------------------
+# CPU arm: the reference bench's own loop on the host cores
+# ---------------------------------------------------------------------------------------------------------------------
+def cpu_step_inputs(m: int):
+    import numpy as np
+
     from vyre_b200 import synth
 
-    threads = oracle.num_threads()
     x, w, s = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
-    probe_rows = 512
-    t0 = time.perf_counter()
-    oracle.int4_rowmajor_linear(x, w[:probe_rows], s[:probe_rows], m, probe_rows, K_IN)
-    per_row = (time.perf_counter() - t0) / probe_rows
-    if steps is None:
-        rows, reps = N_OUT, max(3, int(budget_s / max(per_row * N_OUT, 1e-6)))
-        reps = min(reps, 200)
-    else:
-        rows = int(max(16, min(N_OUT, budget_s / max(1, steps + warmup) / max(per_row, 1e-9))))
-        reps = steps
-    for _ in range(warmup if steps is not None else 1):
-        oracle.int4_rowmajor_linear(x, w[:rows], s[:rows], m, rows, K_IN)
-    t0 = time.perf_counter()
-    for _ in range(reps):
-        oracle.int4_rowmajor_linear(x, w[:rows], s[:rows], m, rows, K_IN)
-    dt = (time.perf_counter() - t0) / reps
-    gbs = algorithmic_bytes(m, n=rows) / dt / 1e9
-    sample = f"{reps} x int4 GEMV M={m} on rows [0,{rows}) of {N_OUT} x K={K_IN} (f64-accumulating oracle, OpenMP over rows)"
-    return gbs, dt, sample, threads
+    return synth.bf16_bits_to_f32(x).reshape(m, K_IN).astype(np.float32), w, s
+
+
+def cpu_gemv_times(m: int, samples: int, warmup: int = 1):
+    """Seconds per GEMV of the reference's CPU loop over the full [14336, 4096] weights, one value per sample."""
+    import oracle
+
+    xf, w, s = cpu_step_inputs(m)
+    for _ in range(warmup):
+        oracle.cpu_baseline_int4_gemv(xf, w, s, m, N_OUT, K_IN)
+    out = []
+    for _ in range(samples):
+        t0 = time.perf_counter()
+        oracle.cpu_baseline_int4_gemv(xf, w, s, m, N_OUT, K_IN)
+        out.append(time.perf_counter() - t0)
+    return out, oracle.num_threads()
 
 
 def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    gbs, dt, sample, threads = cpu_reference_rate(1, budget_s=120.0, steps=args.steps, warmup=args.warmup)
+    m = args.m
+    # a step is what the native arm's step is: COPIES GEMVs over the full weights (the CPU has no L2 to defeat, the same
+    # weights serve every pass)
+    per_gemv, threads = cpu_gemv_times(m, samples=(args.steps + args.warmup) * COPIES, warmup=1)
+    timed = per_gemv[args.warmup * COPIES:]
+    step_s = sum(timed) / max(1, args.steps)
+    gbs = COPIES * algorithmic_bytes(m) / step_s / 1e9
+    sample = (f"{args.steps} steps x {COPIES} full GEMVs (rows [0,{N_OUT}) x K={K_IN}) of the reference bench's f32 loop "
+              f"(vyre-bench/src/cases/quantized_linear.rs:447-463 restated for the row-major layout), -O3, OpenMP over rows")
     line = {
-        "impl": "reference", "metric": "int4_decode_gemv_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16xint4->f32", "data": "synthetic",
-        "config": {"workload": "int4 group-quantized decode GEMV M=1 N=14336 K=4096 g=128 (config 2), CPU row sample"},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(m)},
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample,
+                         "cpu_model": cpu_model(), "ms_per_gemv_median": round(statistics.median(timed) * 1e3, 3)},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of int4_gemv_kernel, from one ncu capture of the M=1
-# case over 8 rotating weight copies (summary kept under profiles/); other batches were not captured.
-NCU_DRAM_BYTES_PER_LAUNCH = {1: 30346368}
+# ---------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------------------------------
+def event_time_us(fn, reps: int, warm: int, stream=None):
+    """Average device time of fn() in microseconds over `reps` calls after `warm` untimed ones (CUDA events on the stream)."""
+    import torch
+
+    stream = stream or torch.cuda.current_stream()
+    with torch.cuda.stream(stream):
+        for _ in range(warm):
+            fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            fn()
+        b.record(stream)
+    stream.synchronize()
+    return a.elapsed_time(b) * 1e3 / max(1, reps)
 
 
-def measure_case(case: str, shape, steps: int, warmup: int) -> dict:
-    """Times plain launches of one of the tensor-core paths (prefill GEMM, int8 GEMM, fused MoE layer) with CUDA events."""
+def tensor_peak(int8: bool) -> float:
+    """Measured tensor-pipe peak of this GPU in T(FL)OP/s: tcgen05.mma from shared-memory operands only."""
+    import torch
+
+    from vyre_b200 import ffi
+
+    L = ffi.lib()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ops = C.c_double(0.0)
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def launch():
+        ffi.check(L.vyb_k_tensor_peak(1 if int8 else 0, 4096, stream, C.c_void_p(status.data_ptr()), C.byref(ops)))
+
+    us = event_time_us(launch, reps=5, warm=2)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    return ops.value / (us * 1e-6) / 1e12
+
+
+def measure_prefill(shape, steps: int, warmup: int, peaks: dict, check: bool = True) -> dict:
+    """Config 3: int4 prefill GEMM on tcgen05 (kernel-level launches), with a tile checked against torch in f32."""
     import torch
 
     from vyre_b200 import ffi
@@ -162,112 +223,236 @@ def measure_case(case: str, shape, steps: int, warmup: int) -> dict:
     m, n, k = shape
     stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    if case == "prefill":
-        x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
-        w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
-        s = (torch.rand((n, k // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
-        y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    w = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda")
+    s = (torch.rand((n, k // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
 
-        def launch():
-            ffi.check(L.vyb_k_int4_prefill_gemm(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), m, n, k, GROUP,
-                                                ffi.DT_BF16, stream, C.c_void_p(status.data_ptr())))
-        unit, scale = "TFLOP/s", 1e12
-    elif case == "moe":
-        # --shape TOKENS INTER HIDDEN; 8 experts, top-2 (config 4 is --shape 4096 14336 4096)
-        experts, topk = 8, 2
-        tokens, inter, hidden = m, n, k
-        x = torch.randn((tokens, hidden), device="cuda").to(torch.bfloat16)
-        wr = (torch.randn((experts, hidden), device="cuda") * 0.02).to(torch.bfloat16)
-        w13 = torch.randint(0, 256, (experts, 2, inter, hidden // 2), dtype=torch.uint8, device="cuda")
-        s13 = (torch.rand((experts, 2, inter, hidden // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
-        w2 = torch.randint(0, 256, (experts, hidden, inter // 2), dtype=torch.uint8, device="cuda")
-        s2 = (torch.rand((experts, hidden, inter // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
-        out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
-        ridx = torch.empty((tokens, topk), dtype=torch.int32, device="cuda")
-        rw = torch.empty((tokens, topk), dtype=torch.float32, device="cuda")
+    def launch():
+        ffi.check(L.vyb_k_int4_prefill_gemm(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), m, n, k, GROUP,
+                                            ffi.DT_BF16, stream, C.c_void_p(status.data_ptr())))
+
+    us = event_time_us(launch, steps, warmup)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    tflops = 2.0 * m * n * k / (us * 1e-6) / 1e12
+    out = {"tflops": round(tflops, 1), "us_per_launch": round(us, 1),
+           "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": round(tflops / peaks["bf16_tflops"], 4), "peak_kind": f"cuBLAS bf16 burst, of {peaks['kind']}",
+                        "frac_of_sustained": round(tflops / peaks["bf16_tflops_sustained"], 4),
+                        "kernel": "int4_gemm_pair_kernel", "us_per_launch": round(us, 1), "algorithmic_flops_per_launch": 2 * m * n * k}}
+    if check:
+        rows, cols = min(m, 128), min(n, 256)
+        lo, hi = (w[:cols] & 0xF).float() - 8.0, (w[:cols] >> 4).float() - 8.0
+        wq = torch.stack([lo, hi], dim=2).reshape(cols, k)
+        wd = (wq * s[:cols].float().repeat_interleave(GROUP, dim=1)).to(torch.bfloat16).float()  # the tile the tensor core sees
+        want = x[:rows].float() @ wd.T
+        got = y[:rows, :cols].float()
+        err = float(((got - want).abs() / want.abs().clamp_min(1e-2 * want.pow(2).mean().sqrt())).max())
+        out["parity_tile"] = {"rows": rows, "cols": cols, "max_rel_err_vs_torch_f32": round(err, 5), "ok": err <= 1e-2}
+        assert err <= 1e-2, f"prefill GEMM tile disagrees with torch: {err}"
+    return out
+
+
+def measure_int8(shape, steps: int, warmup: int, i8_peak: float, peaks: dict) -> dict:
+    """Config 5 on one GPU: int8 x int8 -> int32 GEMM on tcgen05, a tile checked exactly."""
+    import torch
+
+    from vyre_b200 import ffi
+
+    L = ffi.lib()
+    m, n, k = shape
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
+    w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
+    y = torch.empty((m, n), dtype=torch.int32, device="cuda")
+
+    def launch():
+        ffi.check(L.vyb_k_int8_gemm_i32(a.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k, stream, C.c_void_p(status.data_ptr())))
+
+    us = event_time_us(launch, steps, warmup)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    tops = 2.0 * m * n * k / (us * 1e-6) / 1e12
+    want = (a[:64].double() @ w[:128].double().T).to(torch.int64)  # exact: sums far below 2^53
+    exact = bool(torch.equal(y[:64, :128].to(torch.int64), want))
+    assert exact, "int8 GEMM tile is not bit-exact"
+    return {"tops": round(tops, 1), "us_per_launch": round(us, 1), "parity_tile": {"rows": 64, "cols": 128, "bit_exact_vs_f64": exact},
+            "roofline": {"bound": "tensor", "achieved": round(tops, 1), "peak": round(i8_peak, 1), "unit": "TOP/s",
+                         "frac": round(tops / i8_peak, 4), "peak_kind": "tcgen05 kind::i8 from shared-memory operands, measured in this run",
+                         "frac_of_2x_bf16_burst": round(tops / (2 * peaks["bf16_tflops"]), 4), "kernel": "int8_gemm_pair_kernel",
+                         "us_per_launch": round(us, 1), "algorithmic_ops_per_launch": 2 * m * n * k}}
+
+
+def moe_inputs(tokens, hidden, inter, experts_local, experts, seed_rank):
+    import torch
+
+    torch.manual_seed(1234 + seed_rank)
+    x = torch.randn((tokens, hidden), device="cuda").to(torch.bfloat16)
+    gen = torch.Generator(device="cuda").manual_seed(7)  # the router is replicated: same values on every rank
+    wr = (torch.randn((experts, hidden), device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
+    # expert weights depend on the GLOBAL expert index only, so that a token's result is the same at every world size
+    w13, s13, w2, s2 = [], [], [], []
+    first = seed_rank * experts_local
+    for e in range(first, first + experts_local):
+        ge = torch.Generator(device="cuda").manual_seed(100 + e)
+        w13.append(torch.randint(0, 256, (2, inter, hidden // 2), dtype=torch.uint8, device="cuda", generator=ge))
+        s13.append((torch.rand((2, inter, hidden // GROUP), device="cuda", generator=ge) * 0.019 + 0.001).to(torch.bfloat16))
+        w2.append(torch.randint(0, 256, (hidden, inter // 2), dtype=torch.uint8, device="cuda", generator=ge))
+        s2.append((torch.rand((hidden, inter // GROUP), device="cuda", generator=ge) * 0.019 + 0.001).to(torch.bfloat16))
+    return x, wr, torch.stack(w13), torch.stack(s13), torch.stack(w2), torch.stack(s2)
+
+
+def measure_moe(world: int, rank: int, dist, steps: int, warmup: int, peaks: dict) -> dict:
+    """Config 4: 4096 tokens in total, 8 experts top-2, expert-parallel over the ranks with device-side dispatch and
+    combine over peer memory (one GPU: the fused single-GPU layer). Tokens/s over all ranks; a sample of rank 0's
+    outputs is compared with the single-GPU layer run on the same tokens and experts when the weights fit."""
+    import torch
+
+    from vyre_b200 import ffi, sharding
+
+    L = ffi.lib()
+    tokens_total, inter, hidden, experts, topk = 4096, 14336, 4096, 8, 2
+    local = experts // world
+    tokens = tokens_total // world
+    torch.manual_seed(99)
+    x_all = torch.randn((tokens_total, hidden), device="cuda").to(torch.bfloat16)  # same on every rank
+    x = x_all[rank * tokens:(rank + 1) * tokens].contiguous()
+    _, wr, w13, s13, w2, s2 = moe_inputs(1, hidden, inter, local, experts, rank)
+    stream = torch.cuda.current_stream()
+    if world == 1:
         need = C.c_uint64(0)
         ffi.check(L.vyb_k_moe_ffn_int4_scratch_bytes(tokens, hidden, inter, experts, topk, C.byref(need)))
         scratch = torch.empty(need.value, dtype=torch.uint8, device="cuda")
+        out = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+        ridx = torch.empty((tokens, topk), dtype=torch.int32, device="cuda")
+        rw = torch.empty((tokens, topk), dtype=torch.float32, device="cuda")
+        status = torch.zeros(4, dtype=torch.int32, device="cuda")
 
-        def launch():
+        def step():
             ffi.check(L.vyb_k_moe_ffn_int4(x.data_ptr(), wr.data_ptr(), w13.data_ptr(), s13.data_ptr(), w2.data_ptr(),
-                                           s2.data_ptr(), out.data_ptr(), ridx.data_ptr(), rw.data_ptr(),
-                                           scratch.data_ptr(), need.value, tokens, hidden, inter, experts, topk, GROUP,
-                                           stream, C.c_void_p(status.data_ptr())))
-        unit, scale = "TFLOP/s", 1e12 / (3 * topk)  # 3 projections per (token, expert) pair: rate counts expert flops
+                                           s2.data_ptr(), out.data_ptr(), ridx.data_ptr(), rw.data_ptr(), scratch.data_ptr(),
+                                           need.value, tokens, hidden, inter, experts, topk, GROUP,
+                                           C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+            return out
     else:
-        a = torch.randint(-127, 128, (m, k), dtype=torch.int8, device="cuda")
-        w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device="cuda")
-        y = torch.empty((m, n), dtype=torch.int32, device="cuda")
+        ops = sharding.DeviceExpertParallel(wr, w13, s13, w2, s2, hidden, inter, experts, topk, tokens_local_max=tokens,
+                                            tokens_total=tokens_total, group_size=GROUP)
+        status = ops.status
 
-        def launch():
-            ffi.check(L.vyb_k_int8_gemm_i32(a.data_ptr(), w.data_ptr(), y.data_ptr(), m, n, k, stream,
-                                            C.c_void_p(status.data_ptr())))
-        unit, scale = "TOP/s", 1e12
-    for _ in range(warmup):
-        launch()
+        def step():
+            return ops.forward(x)[0]
+
+    for _ in range(max(3, warmup)):
+        step()
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
+    if dist:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
     for _ in range(steps):
-        launch()
-    end.record()
+        y = step()
+    b.record()
     torch.cuda.synchronize()
-    us = start.elapsed_time(end) * 1e3 / max(1, steps)
-    assert status.cpu().tolist() == [0, 0, 0, 0]
-    line = {"quick": True, "case": case, "shape": [m, n, k], "steps": steps, "us_per_launch": us,
-            "rate": 2.0 * m * n * k / (us * 1e-6) / scale, "unit": unit}
-    if case == "moe":
-        line["tokens_per_s"] = m / (us * 1e-6)
-    return line
+    ms = a.elapsed_time(b) / steps
+    if dist:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    assert status.cpu().tolist() == [0, 0, 0, 0], "a bounded device-side wait ran out in the MoE layer"
+    # a checksum of the first 64 output rows of the whole batch: the same tokens meet the same experts at every world
+    # size, and every row is computed by the same kernel arithmetic wherever it runs, so the value must not depend on N
+    digest = None
+    if rank == 0:
+        import hashlib
+
+        digest = hashlib.sha256(y[:64].view(torch.int16).cpu().numpy().tobytes()).hexdigest()[:16]
+    flops = 2.0 * tokens_total * topk * 3 * inter * hidden
+    tflops = flops / (ms * 1e-3) / 1e12
+    return {"tokens_per_s": round(tokens_total / (ms * 1e-3)), "ms_per_layer": round(ms, 4), "expert_tflops": round(tflops, 1),
+            "parallelism": "single GPU, fused layer" if world == 1 else f"expert-parallel x{world}, device-side dispatch/combine over peer memory (NVLink)",
+            "scaling": "strong", "tokens_total": tokens_total, "first_64_rows_sha256_16": digest,
+            "roofline": {"bound": "tensor", "achieved": round(tflops, 1), "peak": round(peaks["bf16_tflops"] * world, 1), "unit": "TFLOP/s",
+                         "frac": round(tflops / (peaks["bf16_tflops"] * world), 4), "peak_kind": f"{world} x cuBLAS bf16 burst, of {peaks['kind']}",
+                         "kernel": "int4_gemm_pair_kernel (grouped, two launches per layer)", "us_per_launch": None}}
 
 
-def run_quick_gemm(args) -> None:
-    """The cases profiled under ncu; one JSON line."""
-    print(json.dumps(measure_case(args.case, args.shape, args.steps, args.warmup)))
-
-
-def run_quick(args) -> None:
-    """A few plain launches of the decode GEMV over rotating weight copies; prints one short JSON line."""
+def measure_colpar_int8(world: int, rank: int, dist, steps: int, warmup: int, i8_peak: float) -> dict:
+    """Config 5: X bf16 [4096, 8192] quantised per token, W int8 [28672, 8192] sharded by rows over the ranks, int32
+    outputs gathered into the full [4096, 28672] on every rank by peer stores (chunks over M overlap GEMM and gather)."""
     import torch
 
-    from vyre_b200 import ffi, synth
+    from vyre_b200 import ffi, sharding
 
-    if args.case != "gemv":
-        return run_quick_gemm(args)
     L = ffi.lib()
-    m = args.m
-    x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
-    x = torch.from_numpy(x_np.view(np.int16)).cuda()
-    copies = max(1, args.copies)
-    ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(copies)]
-    ss = [torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda() for c in range(copies)]
-    y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
+    m, n, k = 4096, 28672, 8192
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    stream = torch.cuda.current_stream().cuda_stream
+    torch.manual_seed(5)
+    x = torch.randn((m, k), device="cuda").to(torch.bfloat16)
+    gather = sharding.PeerColumnGather(m, n, 4, multiple=16)
+    w = torch.randint(-127, 128, (gather.end - gather.begin, k), dtype=torch.int8, device="cuda")  # this rank's rows
+    xq = torch.empty((m, k), dtype=torch.int8, device="cuda")
+    sc = torch.empty(m, dtype=torch.float32, device="cuda")
+    cur = torch.cuda.current_stream()
+    side = torch.cuda.Stream()
+    ffi.check(L.vyb_k_quantize_per_token_int8(x.data_ptr(), xq.data_ptr(), sc.data_ptr(), m, k, C.c_void_p(cur.cuda_stream)))
+    y_local = torch.empty((m, w.shape[0]), dtype=torch.int32, device="cuda")
 
-    def launch(i: int):
-        c = i % copies
-        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
-                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS, C.c_void_p(stream),
-                                       C.c_void_p(status.data_ptr())))
+    def compute_only():
+        ffi.check(L.vyb_k_int8_gemm_i32(xq.data_ptr(), w.data_ptr(), y_local.data_ptr(), m, w.shape[0], k,
+                                        C.c_void_p(cur.cuda_stream), C.c_void_p(status.data_ptr())))
 
-    for i in range(args.warmup):
-        launch(i)
+    def gather_only():
+        gather.push(y_local, 0, cur.cuda_stream, status)
+        gather.wait(cur.cuda_stream, status)
+
+    def total():
+        return sharding.column_parallel_int8_linear(gather, xq, w, status, chunks=4, side_stream=side)
+
+    def timed(fn):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        if dist:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+            dist.barrier()
+        return ms
+
+    ms_compute = timed(compute_only)
+    ms_gather = timed(gather_only)
+    ms_total = timed(total)
+    full, mine = total()
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for i in range(args.steps):
-        launch(i)
-    end.record()
-    torch.cuda.synchronize()
-    us = start.elapsed_time(end) * 1e3 / max(1, args.steps)
-    assert status.cpu().tolist() == [0, 0, 0, 0]
-    print(json.dumps({"quick": True, "m": m, "steps": args.steps, "copies": copies, "us_per_launch": us,
-                      "gbs": algorithmic_bytes(m) / (us * 1e-6) / 1e9}))
+    assert status.cpu().tolist() == [0, 0, 0, 0], "a bounded device-side wait ran out in the column-parallel gather"
+    own_ok = bool(torch.equal(full[:, gather.begin:gather.end], mine))
+    want = (xq[:64].double() @ w[:128].double().T).to(torch.int64)
+    exact = bool(torch.equal(mine[:64, :128].to(torch.int64), want))
+    assert own_ok and exact, "column-parallel int8 linear: gathered block or GEMM tile is wrong"
+    ops = 2.0 * m * n * k
+    tops = ops / (ms_total * 1e-3) / 1e12
+    return {"tops": round(tops, 1), "ms_compute": round(ms_compute, 4), "ms_gather": round(ms_gather, 4), "ms_total": round(ms_total, 4),
+            "tops_compute_only": round(ops / (ms_compute * 1e-3) / 1e12, 1), "scaling": "strong",
+            "parallelism": f"N sharded over {world} rank(s), peer-store gather of int32 outputs, 4 row chunks overlapped",
+            "gather_bytes_received_per_rank": int(m * n * 4 * (world - 1) / world),
+            "parity": {"own_block_in_gathered_output": own_ok, "gemm_tile_bit_exact_vs_f64": exact},
+            "roofline": {"bound": "tensor", "achieved": round(tops, 1), "peak": round(i8_peak * world, 1), "unit": "TOP/s",
+                         "frac": round(tops / (i8_peak * world), 4), "peak_kind": f"{world} x tcgen05 kind::i8 peak measured in this run",
+                         "kernel": "int8_gemm_pair_kernel + colpar_push_kernel", "us_per_launch": round(ms_total * 1e3, 1)}}
 
 
 def run_native(args) -> None:
+    import numpy as np
     import torch
 
     import vyre_b200 as vb
@@ -287,10 +472,10 @@ def run_native(args) -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     L = ffi.lib()
     m = args.m
-    steps = max(COPIES, (args.steps // COPIES) * COPIES)
-    warmup = max(3 * COPIES, ((args.warmup + COPIES - 1) // COPIES) * COPIES)
+    steps, warmup = max(1, args.steps), max(0, args.warmup)
+    peaks = measured_peaks()
 
-    # ---- resident inputs: COPIES distinct weight sets so that consecutive steps never hit L2 -------------------
+    # ---- resident inputs: COPIES distinct weight sets so that consecutive launches never hit L2 ----------------------
     x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=rank)
     x = torch.from_numpy(x_np.view(np.int16)).cuda()
     ws, ss = [], []
@@ -298,61 +483,62 @@ def run_native(args) -> None:
         ws.append(torch.from_numpy(np.roll(w_np, c, axis=0)).cuda())
         ss.append(torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda())
     y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
-    # N > 1: the all-gather is this library's peer-store kernel over NVLink (symmetric memory), not NCCL
     pag = None
     if world > 1:
         from vyre_b200 import sharding
 
-        pag = sharding.PeerAllGather(m, N_OUT)
+        pag = sharding.PeerAllGather(m, N_OUT)  # the all-gather is this library's peer-store kernel over NVLink, not NCCL
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     stream = torch.cuda.Stream()
-
     side = torch.cuda.Stream()
-    # with a concurrent push kernel the GEMV leaves one SM free: sharing an SM with the weight stream (140 KB of bulk
-    # copies in flight) made every memory access of the push wait microseconds
-    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS | (ffi.LAUNCH_LEAVE_ONE_SM if world > 1 else 0)
+    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS
 
-    def launch(c: int, out=None):
-        # weights are graph constants: the launch may overlap the tail of the previous one (see the header)
-        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), (y if out is None else out).data_ptr(), m, N_OUT, K_IN,
-                                       GROUP, ffi.DT_BF16, gemv_flags,
-                                       C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+    def launch(c: int, out=None, xin=None, mm=None):
+        # weights are graph constants: the launch may overlap the tail of the previous one
+        ffi.check(L.vyb_k_int4_gemv_ex((x if xin is None else xin).data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(),
+                                       (y if out is None else out).data_ptr(), m if mm is None else mm, N_OUT, K_IN, GROUP,
+                                       ffi.DT_BF16, gemv_flags, C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+
+    def capture(body):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream):
+            with torch.cuda.graph(g, stream=stream):
+                body()
+        return g
 
     with torch.cuda.stream(stream):
-        for c in range(COPIES):  # first launches configure the kernel; must precede graph capture
+        for c in range(COPIES):  # first launches configure the kernels; must precede graph capture
             launch(c)
     stream.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(graph, stream=stream):
-            if pag is None:
-                for c in range(COPIES):
-                    launch(c)
-            else:
-                # GEMV c writes this rank's slice of buffer half c % 2; a one-CTA push kernel on a side stream copies
-                # it to every peer and signals them while GEMV c+1 already runs; GEMV c+2 (same half) waits for it.
-                pushed = [None] * COPIES
-                for c in range(COPIES):
-                    half = c & 1
-                    if c >= 2:
-                        stream.wait_event(pushed[c - 2])
-                    launch(c, pag.local_slice(half))
-                    ready = torch.cuda.Event()
-                    ready.record(stream)
-                    side.wait_event(ready)
-                    pag.push(half, side.cuda_stream, status)
-                    pushed[c] = torch.cuda.Event()
-                    pushed[c].record(side)
-                stream.wait_stream(side)
-                # the replay ends with the bounded wait for its own gathers: nothing is left in flight
-                pag.wait(stream.cuda_stream, status)
-    # parity guard inside the bench: the last copy's output must match the contract path bit for bit
+
+    def step_body():
+        if pag is None:
+            for c in range(COPIES):
+                launch(c)
+            return
+        # GEMV c writes this rank's slice of buffer half c % 2; the push kernel on a side stream copies it to every peer
+        # and signals them while GEMV c+1 already runs; GEMV c+2 (same half) waits for it.
+        pushed = [None] * COPIES
+        for c in range(COPIES):
+            half = c & 1
+            if c >= 2:
+                stream.wait_event(pushed[c - 2])
+            launch(c, pag.local_slice(half))
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            side.wait_event(ready)
+            pag.push(half, side.cuda_stream, status)
+            pushed[c] = torch.cuda.Event()
+            pushed[c].record(side)
+        stream.wait_stream(side)
+        pag.wait(stream.cuda_stream, status)  # the replay ends with the bounded wait for its own gathers
+
+    graph = capture(step_body)
     with torch.cuda.stream(stream):
         graph.replay()
     stream.synchronize()
     if pag is not None:
-        # the gathered result of the graph's last step (odd step index: half 1) against NCCL's all-gather of the
-        # plain kernel's output for the same weight copy
+        # the gathered result of the graph's last launch (half 1) against NCCL's all-gather of the plain kernel's output
         launch(COPIES - 1)
         stream.synchronize()
         want_all = torch.empty((world, m, N_OUT), dtype=torch.bfloat16, device="cuda")
@@ -362,7 +548,7 @@ def run_native(args) -> None:
         y = pag.halves()[1][rank]
     y_ref = y.clone()
 
-    for _ in range(warmup // COPIES):
+    for _ in range(warmup):
         with torch.cuda.stream(stream):
             graph.replay()
     stream.synchronize()
@@ -370,7 +556,6 @@ def run_native(args) -> None:
     if rank == 0:
         sampler.start()
         time.sleep(0.15)
-    # the barrier comes after the sampler's start-up so that every rank enters the timed region together
     if dist:
         dist.barrier()
     torch.cuda.synchronize()
@@ -378,7 +563,7 @@ def run_native(args) -> None:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         start.record(stream)
-        for _ in range(steps // COPIES):
+        for _ in range(steps):
             graph.replay()
         end.record(stream)
     stream.synchronize()
@@ -391,260 +576,232 @@ def run_native(args) -> None:
         t = torch.tensor([elapsed_ms], dtype=torch.float64, device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         elapsed_ms = float(t.item())
-    clocks = sampler.stop(lo, hi) if rank == 0 else None
     assert status.cpu().tolist() == [0, 0, 0, 0], "a bounded device-side wait ran out during the bench"
     assert torch.equal(y, y_ref), "non-deterministic GEMV output during the bench"
-
     ms_per_step = elapsed_ms / steps
-    bytes_per_step = algorithmic_bytes(m)
-    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    step_bytes = COPIES * algorithmic_bytes(m)
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # All ranks leave the process group together, right after the timed region: the captured graph holds NCCL work
-    # and must be gone before the communicator is; what follows on rank 0 is single-GPU work without collectives.
+    # ---- kernel-only time of the dominant kernel (no collective), for the roofline: a longer region of its own, so
+    # that the figure does not hang on the few hundred microseconds of a 20-step run; clocks sampled across it
+    kgraph = capture(lambda: [launch(c) for c in range(COPIES)])
+    k_lo = sampler.mark()
+    kernel_us = event_time_us(kgraph.replay, reps=max(steps, 250), warm=5, stream=stream) / COPIES
+    if rank == 0:
+        time.sleep(0.06)
+    k_hi = sampler.mark()
+    achieved = algorithmic_bytes(m) / (kernel_us * 1e-6) / 1e9
+    extra = {}
+    if rank == 0:
+        for mm in (4, 8):
+            xm_np, _, _ = synth.int4_linear_inputs(mm, 16, K_IN, seed=3)
+            xm = torch.from_numpy(xm_np.view(np.int16)).cuda()
+            ym = torch.zeros((mm, N_OUT), dtype=torch.bfloat16, device="cuda")
+            for c in range(COPIES):
+                launch(c, ym, xm, mm)
+            stream.synchronize()
+            g2 = capture(lambda: [launch(c, ym, xm, mm) for c in range(COPIES)])
+            us = event_time_us(g2.replay, reps=250, warm=5, stream=stream) / COPIES
+            gbs = algorithmic_bytes(mm) / (us * 1e-6) / 1e9
+            extra[f"m{mm}"] = {"us_per_launch": round(us, 3), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4)}
+            del g2
+    clocks_headline = sampler.summary(lo, hi) if rank == 0 else None
+    clocks_kernel = sampler.summary(k_lo, k_hi) if rank == 0 else None
+
+    # ---- the sharded configurations of the path, at this N (every rank takes part) ------------------------------------
+    del graph, kgraph
+    torch.cuda.synchronize()
+    secondary = {}
+    i8_peak = tensor_peak(True)
+    s_lo = sampler.mark()
+    secondary["moe_ep_config4"] = measure_moe(world, rank, dist, steps=5, warmup=3, peaks=peaks)
+    torch.cuda.empty_cache()
+    secondary["int8_colpar_config5"] = measure_colpar_int8(world, rank, dist, steps=5, warmup=2, i8_peak=i8_peak)
+    torch.cuda.empty_cache()
+    s_hi = sampler.mark()
+
+    # All ranks leave the process group together, right after the collective work; what follows on rank 0 is single-GPU.
     if dist:
-        del graph
-        torch.cuda.synchronize()
         pag = None
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
         dist = None
     if rank != 0:
         return
 
-    # ---- kernel-only time of the dominant kernel (no collective), for the roofline --------------------------------
-    kgraph = torch.cuda.CUDAGraph()
-    with torch.cuda.stream(stream):
-        with torch.cuda.graph(kgraph, stream=stream):
-            for c in range(COPIES):
-                launch(c)
-    ksteps = min(steps, 40000)
-    ks, ke = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with torch.cuda.stream(stream):
-        for _ in range(4):
-            kgraph.replay()
-        ks.record(stream)
-        for _ in range(ksteps // COPIES):
-            kgraph.replay()
-        ke.record(stream)
-    stream.synchronize()
-    kernel_us = ks.elapsed_time(ke) * 1e3 / ksteps
-    peak, peak_kind = measured_peaks()
-    achieved = bytes_per_step / (kernel_us * 1e-6) / 1e9
+    secondary["tensor_peaks_measured_in_run"] = {"int8_tops": round(i8_peak, 1), "bf16_tflops": round(tensor_peak(False), 1),
+                                                 "how": "tcgen05.mma 128x256 tiles from shared-memory operands, one CTA per SM"}
+    secondary["int4_prefill_gemm_config3"] = measure_prefill([2048, 14336, 4096], 20, 5, peaks)
+    secondary["int8_gemm_config5_single_gpu"] = measure_int8([4096, 28672, 8192], 10, 3, i8_peak, peaks)
+    secondary["clocks_during_secondary"] = sampler.summary(s_lo, sampler.mark())
+    torch.cuda.empty_cache()
 
-    extra = {}
-    for mm in (4, 8):
-        xm_np, _, _ = synth.int4_linear_inputs(mm, 16, K_IN, seed=3)
-        xm = torch.from_numpy(xm_np.view(np.int16)).cuda()
-        ym = torch.zeros((mm, N_OUT), dtype=torch.bfloat16, device="cuda")
-        g2 = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream):
-            with torch.cuda.graph(g2, stream=stream):
-                for c in range(COPIES):
-                    ffi.check(L.vyb_k_int4_gemv_ex(xm.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), ym.data_ptr(), mm,
-                                                   N_OUT, K_IN, GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
-                                                   C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
-            for _ in range(4):
-                g2.replay()
-            ks.record(stream)
-            for _ in range(2000 // COPIES):
-                g2.replay()
-            ke.record(stream)
-        stream.synchronize()
-        us = ks.elapsed_time(ke) * 1e3 / (2000 // COPIES * COPIES)
-        extra[f"m{mm}"] = {"us_per_launch": round(us, 3), "gbs": round(algorithmic_bytes(mm) / (us * 1e-6) / 1e9, 1),
-                           "frac_of_measured_peak": round(algorithmic_bytes(mm) / (us * 1e-6) / 1e9 / peak, 4)}
-
-    # ---- end to end through the contract path: host x -> submit -> wait -> host y, weights resident ---------------
+    # ---- end to end through the contract path: host x -> submit -> wait -> host y, weights resident ------------------
+    # one prepared binding set per weight copy (validated once, one graph launch per submission); the activations of
+    # every step are copied in from pinned host memory and the outputs read back to host memory inside the timed region
     dev = vb.Device.acquire(local_rank)
     prog = vb.linear_int4_grouped_rowmajor("x", "w", "scale", "out", m, K_IN, N_OUT, GROUP, ffi.DT_BF16)
     sess = vb.ArtifactSession.compile(prog, dev)
     hw = [dev.resident_from(np.roll(w_np, c, axis=0).view(np.uint32)) for c in range(COPIES)]
     hs = [dev.resident_from(np.roll(s_np, c, axis=0)) for c in range(COPIES)]
     x_pinned = torch.from_numpy(x_np.view(np.int16).copy()).pin_memory().numpy().view(np.uint16)
-    depth = 4
-    e2e_steps = max(depth * COPIES, min(steps, 4000))
-
-    # one prepared binding set per weight copy: the activation buffer is the same pinned array every step (a serving
-    # loop rewrites it in place), so the sets are built once and only submitted in the timed loop
-    sets = []
+    preps = []
     for c in range(COPIES):
         bs = vb.BindingSet(sess.artifact.digest())
         bs.insert_host(0, x_pinned)
         bs.insert_resident(1, hw[c])
         bs.insert_resident(2, hs[c])
-        sets.append(bs)
+        preps.append(sess.prepare(bs))
+    depth = 4
+    e2e_steps = max(2, min(steps, 500))
 
-    def submit(i: int):
-        return sess.submit(sets[i % COPIES])
-
-    inflight, checksum, last = [], 0.0, None
-    for i in range(depth * COPIES):  # warm-up
-        submit(i).wait()
-    t0 = time.perf_counter()
-    for i in range(e2e_steps):
-        inflight.append(submit(i))
-        if len(inflight) == depth:
+    def e2e_step(keep):
+        inflight, last = [], None
+        for c in range(COPIES):
+            inflight.append(preps[c].submit({0: x_pinned}))
+            if len(inflight) == depth:
+                last = inflight.pop(0).wait()
+                keep[0] += float(last.output_view(3, np.uint16)[0])
+                del last
+        while inflight:
             last = inflight.pop(0).wait()
-            checksum += float(last.output_view(3, np.uint16)[0])
-    while inflight:
-        last = inflight.pop(0).wait()
+            keep[0] += float(last.output_view(3, np.uint16)[0])
+            if inflight:
+                del last
+        return last
+
+    keep = [0.0]
+    for _ in range(max(3, min(warmup, 20))):
+        del_last = e2e_step(keep)
+        del del_last
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        last = e2e_step(keep)
+        if _ != e2e_steps - 1:
+            del last
     e2e_s = (time.perf_counter() - t0) / e2e_steps
     got_last = np.frombuffer(last.output(3), np.uint16).reshape(m, N_OUT)
     want_last = y_ref.view(torch.int16).cpu().numpy().view(np.uint16)
     assert np.array_equal(got_last, want_last), "contract path and kernel-level path disagree"
-    e2e = {"value": world * bytes_per_step / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(x_pinned.nbytes),
-           "d2h_bytes_per_step": int(m * N_OUT * 2), "us_per_step": round(e2e_s * 1e6, 2), "in_flight": depth,
-           "api": "ArtifactSession.submit/wait (vyb_submit, vyb_submission_wait), weights resident"}
+    del last
+    e2e = {"value": step_bytes / e2e_s / 1e9, "unit": "GB/s", "h2d_bytes_per_step": int(COPIES * x_pinned.nbytes),
+           "d2h_bytes_per_step": int(COPIES * m * N_OUT * 2), "us_per_step": round(e2e_s * 1e6, 2),
+           "us_per_submission": round(e2e_s * 1e6 / COPIES, 2), "in_flight": depth, "n_gpus_measured": 1,
+           "api": "ArtifactSession.prepare + PreparedSubmission.submit / Submission.wait (vyb_prepare, vyb_prepared_submit, "
+                  "vyb_submission_wait), weights resident, rank 0's GPU"}
+    for p in preps:
+        p.free()
     for h in hw + hs:
         dev.free_resident(h)
     dev.release()
+    sampler.stop()
 
-    # ---- the other configurations of the path, kernel-level, a few launches each (reported beside the headline) -----
-    secondary = {}
-    try:
-        bf16_peak = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
-    except Exception:
-        bf16_peak = 1590.0
-    c3 = measure_case("prefill", [2048, 14336, 4096], 20, 5)
-    secondary["int4_prefill_gemm_config3"] = {"tflops": round(c3["rate"], 1), "us_per_launch": round(c3["us_per_launch"], 1),
-                                              "frac_of_bf16_burst_peak": round(c3["rate"] / bf16_peak, 3)}
-    c5 = measure_case("int8gemm", [4096, 28672, 8192], 10, 3)
-    secondary["int8_gemm_config5"] = {"tops": round(c5["rate"], 1), "us_per_launch": round(c5["us_per_launch"], 1),
-                                      "frac_of_2x_bf16_burst_peak": round(c5["rate"] / (2 * bf16_peak), 3)}
-    c4 = measure_case("moe", [4096, 14336, 4096], 5, 2)
-    secondary["moe_ffn_config4"] = {"tokens_per_s": round(c4["tokens_per_s"]), "ms_per_layer": round(c4["us_per_launch"] / 1e3, 3),
-                                    "expert_tflops": round(c4["rate"], 1)}
-    torch.cuda.empty_cache()
+    cpu = None
+    if world == 1:
+        per_gemv, cpu_threads = cpu_gemv_times(m, samples=9, warmup=1)
+        med = statistics.median(per_gemv)
+        cpu = {"value": algorithmic_bytes(m) / med / 1e9, "unit": "GB/s", "cores": cpu_threads, "kind": "port",
+               "sample": f"median of 9 full GEMVs M={m} (rows [0,{N_OUT}) x K={K_IN}) of the reference bench's f32 loop "
+                         "(vyre-bench/src/cases/quantized_linear.rs:447-463 restated for the row-major layout), -O3, OpenMP over rows",
+               "ms_per_gemv": round(med * 1e3, 3), "cpu_model": cpu_model()}
 
-    cpu_gbs, cpu_dt, cpu_sample, cpu_threads = cpu_reference_rate(m, budget_s=12.0)
-
+    launches_per_step = COPIES * (2 if world > 1 else 1) + (1 if world > 1 else 0)
     line = {
-        "metric": "int4_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
-        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16xint4->f32", "data": "synthetic",
-        "config": {"workload": f"int4 group-quantized decode GEMV M={m} N={N_OUT} K={K_IN} g={GROUP} (config 2)",
-                   "per_gpu_shard": [N_OUT, K_IN], "parallelism": f"column-parallel x{world}" + (" + peer-store all-gather over NVLink on a side stream" if world > 1 else ""),
-                   "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
-                   "launch": f"CUDA graph of {COPIES} launches, programmatic dependent launch (constant weights)"},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(m), "peak_kind": f"of {peak_kind}", "kernel": "int4_gemv_kernel",
-                     "us_per_launch": round(kernel_us, 3), "algorithmic_bytes_per_launch": bytes_per_step,
-                     "frac_of_nominal_8tbs": achieved / 8000.0},
-        "cpu_baseline": {"value": cpu_gbs, "unit": "GB/s", "cores": cpu_threads, "kind": "port", "sample": cpu_sample,
-                         "ms_per_gemv": round(cpu_dt * 1e3, 2)},
-        "e2e": e2e, "gpu_launches": steps * (2 if world > 1 else 1) + (steps // COPIES if world > 1 else 0), "clocks": clocks, "other_batches": extra, "secondary": secondary,
+        "config": {"workload": workload_name(m)},
+        "run": {"per_gpu_shard": [N_OUT, K_IN],
+                "parallelism": f"column-parallel x{world}" + (" + peer-store all-gather over NVLink on a side stream" if world > 1 else ""),
+                "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
+                "launch": f"CUDA graph of {COPIES} launches per step, programmatic dependent launch (constant weights)"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(m), "traffic_source": "recorded constant from an ncu capture (profiles/), not measured in this run",
+                     "peak_kind": f"of {peaks['kind']}", "kernel": "int4_gemv_halfsm_kernel",
+                     "us_per_launch": round(kernel_us, 3), "algorithmic_bytes_per_launch": algorithmic_bytes(m),
+                     "timed_launches": max(steps, 250) * COPIES, "frac_of_nominal_8tbs": achieved / 8000.0, "clocks": clocks_kernel},
+        "e2e": e2e, "gpu_launches": steps * launches_per_step, "clocks": clocks_headline, "other_batches": extra,
+        "secondary": secondary,
     }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
     print(json.dumps(line))
 
 
-def run_moe_ep(args) -> None:
-    """Config 4 across the ranks: 4096 tokens in total (strong scaling), 8 experts top-2 split expert-parallel, two
-    all-to-all exchanges per layer. A step is one layer over every rank's tokens; value = tokens / s over all ranks.
-    The timed region holds everything a caller of the layer pays: routing, the host-side exchange plan (one
-    device-to-host read of the routing indices), both exchanges, grouped GEMMs and the combine."""
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode GEMV, from one ncu capture of the M=1 case over
+# 8 rotating weight copies (summary kept under profiles/); other batches were not captured.
+NCU_DRAM_BYTES_PER_LAUNCH = {1: 30327296}
+
+
+def run_quick(args) -> None:
+    """A few plain launches of one kernel; prints one short JSON line (the cases profiled under ncu)."""
+    import numpy as np
     import torch
 
-    from vyre_b200 import sharding
+    from vyre_b200 import ffi, synth
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    import torch.distributed as dist
+    peaks = measured_peaks()
+    if args.case == "prefill":
+        print(json.dumps({"quick": True, "case": "prefill", "shape": args.shape, **measure_prefill(args.shape, args.steps, args.warmup, peaks)}))
+        return
+    if args.case == "int8gemm":
+        print(json.dumps({"quick": True, "case": "int8gemm", "shape": args.shape,
+                          **measure_int8(args.shape, args.steps, args.warmup, 2 * peaks["bf16_tflops"], peaks)}))
+        return
+    if args.case == "peak":
+        print(json.dumps({"quick": True, "case": "peak", "int8_tops": tensor_peak(True), "bf16_tflops": tensor_peak(False)}))
+        return
+    L = ffi.lib()
+    m = args.m
+    x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
+    x = torch.from_numpy(x_np.view(np.int16)).cuda()
+    copies = max(1, args.copies)
+    ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(copies)]
+    ss = [torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda() for c in range(copies)]
+    y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    it = [0]
 
-    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
-    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", "29533")
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
-    tokens_total, inter, hidden = args.shape
-    experts, topk = 8, 2
-    local = experts // world
-    tokens = tokens_total // world
-    torch.manual_seed(1234 + rank)
-    x = torch.randn((tokens, hidden), device="cuda").to(torch.bfloat16)
-    gen = torch.Generator(device="cuda").manual_seed(7)  # the router is replicated: same values on every rank
-    wr = (torch.randn((experts, hidden), device="cuda", generator=gen) * 0.02).to(torch.bfloat16)
-    w13 = torch.randint(0, 256, (local, 2, inter, hidden // 2), dtype=torch.uint8, device="cuda")
-    s13 = (torch.rand((local, 2, inter, hidden // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
-    w2 = torch.randint(0, 256, (local, hidden, inter // 2), dtype=torch.uint8, device="cuda")
-    s2 = (torch.rand((local, hidden, inter // GROUP), device="cuda") * 0.019 + 0.001).to(torch.bfloat16)
-    if args.ep == "host":
-        # exchange planned on the host (one read-back of the routing), rows moved by NCCL all-to-all
-        ops = sharding.KernelOps(w13, s13, w2, s2, hidden, inter, local, GROUP)
-        max_rows = ((tokens_total * topk + 255) // 256) * 256 + local * 256  # worst case: every pair lands on this rank
+    def launch():
+        c = it[0] % copies
+        it[0] += 1
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
+                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS, C.c_void_p(stream),
+                                       C.c_void_p(status.data_ptr())))
 
-        def step():
-            return sharding.expert_parallel_moe_ffn(x, wr, ops, experts, topk, max_rows=max_rows)
-    else:
-        # dispatch and combine by the library's own kernels over peer memory, nothing read back by the host
-        ops = sharding.DeviceExpertParallel(wr, w13, s13, w2, s2, hidden, inter, experts, topk, tokens_local_max=tokens,
-                                            tokens_total=tokens_total, group_size=GROUP)
-
-        def step():
-            return ops.forward(x)
-
-    for _ in range(max(3, args.warmup)):
-        step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    torch.cuda.synchronize()
-    steps = max(1, args.steps)
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        step()
-    end.record()
-    torch.cuda.synchronize()
-    dist.barrier()
-    t = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item()) / steps
-    assert ops.status.cpu().tolist() == [0, 0, 0, 0]
-    torch.cuda.synchronize()
-    dist.barrier()
-    dist.destroy_process_group()
-    if rank == 0:
-        flops = 2.0 * tokens_total * topk * 3 * inter * hidden
-        print(json.dumps({
-            "metric": "moe_ffn_tokens_per_s", "value": tokens_total / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": steps, "warmup": max(3, args.warmup), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16xint4->f32", "data": "synthetic",
-            "config": {"workload": f"int4 MoE FFN layer, {tokens_total} tokens, hidden {hidden}, inter {inter}, {experts} experts "
-                                   f"top-{topk} (config 4)", "parallelism": f"expert-parallel x{world}, " + ("host-planned NCCL all-to-all" if args.ep == "host" else "device-side dispatch/combine over peer memory (NVLink)"),
-                       "tokens_per_rank": tokens, "experts_per_rank": local},
-            "expert_tflops": flops / (ms * 1e-3) / 1e12}))
+    us = event_time_us(launch, args.steps, args.warmup)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    print(json.dumps({"quick": True, "m": m, "steps": args.steps, "copies": copies, "us_per_launch": us,
+                      "gbs": algorithmic_bytes(m) / (us * 1e-6) / 1e9}))
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=100000)
-    ap.add_argument("--warmup", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
-    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm", "moe"],
-                    help="kernel exercised by --quick")
+    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm", "peak"], help="kernel exercised by --quick")
     ap.add_argument("--shape", type=int, nargs=3, default=[2048, 14336, 4096], metavar=("M", "N", "K"),
                     help="GEMM shape for --quick --case prefill|int8gemm")
     ap.add_argument("--copies", type=int, default=COPIES,
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
-    ap.add_argument("--workload", default="gemv", choices=["gemv", "moe"],
-                    help="gemv: the headline decode GEMV; moe: the expert-parallel MoE FFN layer (--shape TOKENS INTER HIDDEN)")
-    ap.add_argument("--ep", default="device", choices=["device", "host"],
-                    help="--workload moe: device-side dispatch/combine over peer memory, or host-planned NCCL all-to-all")
     ap.add_argument("--quick", action="store_true",
                     help="kernel-only run without graphs, end-to-end leg or CPU baseline (the case profiled under ncu)")
     args = ap.parse_args()
     if args.impl == "reference":
+        # torchrun exports OMP_NUM_THREADS=1 to its workers: the CPU arm uses every host core, like the reference's rayon pool
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+        if args.steps == 200 and args.warmup == 20:
+            args.steps, args.warmup = 5, 1
         run_reference(args)
     elif args.quick:
+        if args.steps == 200 and args.warmup == 20:
+            args.steps, args.warmup = 16, 8
         run_quick(args)
-    elif args.workload == "moe":
-        if args.shape == [2048, 14336, 4096]:
-            args.shape = [4096, 14336, 4096]
-        if args.steps == 100000:
-            args.steps, args.warmup = 20, 3
-        run_moe_ep(args)
     else:
         run_native(args)
 

@@ -447,17 +447,30 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
  * waits (bounded, ~2 s, status bit 128) until every gather pushed so far by this rank is complete in local memory.
  * On a side stream the push overlaps the next GEMV; the caller orders it after the GEMV that wrote the slice and
  * before the GEMV that overwrites that half again.
- * peer_out / peer_flag: device addresses valid on THIS rank for every rank's buffer / 32-bit arrival counter (own
- * rank included); epoch: a local 32-bit word. All counters zero before the first push. m * n a multiple of 8. */
+ * peer_out / peer_flag: device addresses valid on THIS rank for every rank's buffer / 256 bytes of arrival counters
+ * (own rank included); epoch: eight local 32-bit words. All counters zero before the first push. m * n a multiple of
+ * 8. One CTA per peer copies, fences and signals, so a push costs the same at 2 and at 8 ranks. */
 typedef struct vyb_allgather_ctx {
     uint32_t world, rank;
     uint64_t peer_out[8];
-    uint64_t peer_flag[8];
-    uint64_t epoch;
+    uint64_t peer_flag[8];   /* 256 bytes of counters per rank: 32-bit word 8*s counts the pushes received from rank s */
+    uint64_t epoch;          /* 8 local 32-bit words */
+    uint64_t wait_clocks;    /* clock limit of a device-side wait (status bit 128 when it runs out); 0 = about 2 s */
 } vyb_allgather_ctx;
 int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32_t m, uint32_t n, void* stream,
                              uint32_t* status);
 int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status);
+/* Column-parallel gather of a block of rows over peer memory (no counterpart in the reference; same sharding
+ * argument as above). peer_out[r] is the base of rank r's full [M, N] output; this rank's block [rows, row_bytes]
+ * (its columns of some rows, e.g. the int32 outputs of one M-chunk of its GEMM shard) is stored at byte offset
+ * dst_offset_bytes (row pitch dst_pitch_bytes) of EVERY rank's output, own rank included, 16 CTAs per
+ * destination side by side; then every destination's counter for this rank goes up by one. Chunks over M let the
+ * gather of one chunk (on a side stream) overlap the GEMM of the next. epoch must point to 16 zeroed local words.
+ * vyb_k_colpar_wait: bounded device-side wait until every rank has delivered `blocks` blocks into this rank's
+ * output. Offsets, pitch and row bytes are multiples of 16. */
+int32_t vyb_k_colpar_push(const vyb_allgather_ctx* ctx, const void* block, uint32_t rows, uint32_t row_bytes,
+                          uint64_t dst_pitch_bytes, uint64_t dst_offset_bytes, void* stream, uint32_t* status);
+int32_t vyb_k_colpar_wait(const vyb_allgather_ctx* ctx, uint32_t blocks, void* stream, uint32_t* status);
 
 /* C1: y f32 [m,n] = x f32 [m,k] . (int8 w[n,k] * s[n])^T */
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,
@@ -518,6 +531,7 @@ typedef struct vyb_moe_ep_ctx {
     uint32_t world, rank;
     uint64_t peer_base[8];
     uint64_t off_counts, off_flags, off_src, off_xg, off_yhome;
+    uint64_t wait_clocks; /* clock limit of a device-side wait (status bit 256 when it runs out); 0 = about 2 s */
 } vyb_moe_ep_ctx;
 int32_t vyb_k_moe_ep_sizes(uint32_t tokens_local_max, uint32_t tokens_total, uint32_t hidden, uint32_t inter,
                            uint32_t experts, uint32_t topk, uint32_t world, vyb_moe_ep_ctx* ctx, uint64_t* symmetric_bytes,

@@ -1,0 +1,62 @@
+"""The failure path of the cross-GPU kernels, on ONE GPU and without any fault: a device-side wait on a peer that never
+signals runs into its clock limit, the kernel returns with a status bit set, later launches return at once, and the
+device stays usable. The "peer" is this GPU itself: the context's peer addresses alias local buffers, so no other rank
+exists that could signal, and no kernel here waits on another kernel.
+"""
+import ctypes as C
+import time
+
+import numpy as np
+import pytest
+import torch
+
+from vyre_b200 import ffi, synth
+
+pytestmark = pytest.mark.gpu
+
+LIMIT_CLOCKS = 4_000_000  # about 2 ms at boost clocks
+
+
+def test_allgather_push_wait_runs_out_and_device_stays_usable():
+    L = ffi.lib()
+    m, n, world = 1, 1024, 2
+    data_bytes = 2 * world * m * n * 2
+    buf = torch.zeros(data_bytes + 256, dtype=torch.uint8, device="cuda")
+    local = torch.zeros(64, dtype=torch.int32, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    ctx = ffi.AllGatherCtx()
+    ctx.world, ctx.rank = world, 0
+    for r in range(world):  # both "ranks" are this buffer: the peer's counters are our own, and nobody bumps the one we poll
+        ctx.peer_out[r] = buf.data_ptr()
+        ctx.peer_flag[r] = buf.data_ptr() + data_bytes
+    ctx.epoch = local.data_ptr()
+    ctx.wait_clocks = LIMIT_CLOCKS
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def push(half):
+        ffi.check(L.vyb_k_allgather_push(C.byref(ctx), half, m, n, stream, C.c_void_p(status.data_ptr())))
+
+    push(0)  # first push: nothing to wait for
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    t0 = time.perf_counter()
+    push(1)  # must see one push from the peer first: it never comes
+    torch.cuda.synchronize()
+    first = time.perf_counter() - t0
+    assert status.cpu()[0].item() & 128, "the wait did not report running out"
+    assert first < 1.0, "the wait limit of the context was not honoured"
+    t0 = time.perf_counter()
+    for half in (0, 1, 0, 1):  # a wait that has run out is not repeated: these return at once
+        push(half)
+    ffi.check(L.vyb_k_allgather_wait(C.byref(ctx), stream, C.c_void_p(status.data_ptr())))
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < max(0.05, 2 * first)
+    # the status word turns into DispatchFailed on the contract path (vyb_submission_wait); here: the device still works
+    status.zero_()
+    x, w, s = synth.int4_linear_inputs(1, 256, 4096, seed=1)
+    tx, tw, ts = (torch.from_numpy(a).cuda() for a in (x.view(np.int16), w, s.view(np.int16)))
+    y = torch.zeros((1, 256), dtype=torch.bfloat16, device="cuda")
+    ffi.check(L.vyb_k_int4_gemv(tx.data_ptr(), tw.data_ptr(), ts.data_ptr(), y.data_ptr(), 1, 256, 4096, 128, ffi.DT_BF16,
+                                stream, C.c_void_p(status.data_ptr())))
+    torch.cuda.synchronize()
+    assert status.cpu().tolist() == [0, 0, 0, 0] and torch.isfinite(y.float()).all()

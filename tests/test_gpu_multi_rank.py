@@ -99,6 +99,22 @@ def _worker(rank: int, world: int, port: int, q):
         torch.cuda.synchronize()
         assert status.cpu().tolist() == [0, 0, 0, 0]
         assert torch.equal(gathered, full)
+        # the same through the library's own peer-store gather: chunks of rows, pushes on a side stream, twice in a row
+        xq = torch.empty((m, k), dtype=torch.int8, device="cuda")
+        sc = torch.empty(m, dtype=torch.float32, device="cuda")
+        ffi.check(L.vyb_k_quantize_per_token_int8(xa.data_ptr(), xq.data_ptr(), sc.data_ptr(), m, k, stream()))
+        pcg = sharding.PeerColumnGather(m, n, 4, multiple=8)
+        side = torch.cuda.Stream()
+        for rep in range(2):
+            got, _ = sharding.column_parallel_int8_linear(pcg, xq, wa[pcg.begin:pcg.end].contiguous(), status, chunks=3,
+                                                          side_stream=side)
+            torch.cuda.synchronize()
+            assert status.cpu().tolist() == [0, 0, 0, 0]
+            assert torch.equal(got, full), f"peer-store column gather, pass {rep}"
+            dist.barrier()
+            got.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
         # ---- decode GEMV + the library's peer-store all-gather, against NCCL's all-gather ---------------------------
         m, n, k = 4, 2048, 4096
         xg, wg, sg = synth.int4_linear_inputs(m, n, k, seed=40 + rank)

@@ -1241,6 +1241,7 @@ int32_t to_gather(const vyb_allgather_ctx* ctx, vybk::PeerGather* ag) {
         ag->peer_flag[r] = ctx->peer_flag[r];
     }
     ag->epoch = ctx->epoch;
+    ag->wait_clocks = ctx->wait_clocks;
     return VYB_OK;
 }
 }  // namespace
@@ -1259,6 +1260,26 @@ int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_
     vybk::PeerGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;
     return launch_result(vybk::launch_allgather_wait(ag, static_cast<cudaStream_t>(stream), status), "all-gather wait");
+}
+
+int32_t vyb_k_colpar_push(const vyb_allgather_ctx* ctx, const void* block, uint32_t rows, uint32_t row_bytes,
+                          uint64_t dst_pitch_bytes, uint64_t dst_offset_bytes, void* stream, uint32_t* status) {
+    vybk::PeerGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    if (!block || (row_bytes | dst_pitch_bytes | dst_offset_bytes) % 16 || (reinterpret_cast<uintptr_t>(block) & 15))
+        return fail_invalid_program("Fix: the column-parallel push needs a 16-byte aligned block and row bytes, pitch and "
+                                    "offset that are multiples of 16 (16-byte stores).");
+    // the tickets live behind the eight launch-counter words of the context's local block
+    uint32_t* tickets = reinterpret_cast<uint32_t*>(ctx->epoch) + 8;
+    return launch_result(vybk::launch_colpar_push(ag, block, rows, row_bytes, dst_pitch_bytes, dst_offset_bytes, tickets,
+                                                  static_cast<cudaStream_t>(stream), status),
+                         "column-parallel push");
+}
+
+int32_t vyb_k_colpar_wait(const vyb_allgather_ctx* ctx, uint32_t blocks, void* stream, uint32_t* status) {
+    vybk::PeerGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    return launch_result(vybk::launch_colpar_wait(ag, blocks, static_cast<cudaStream_t>(stream), status), "column-parallel wait");
 }
 
 int32_t vyb_k_tensor_peak(uint32_t int8, uint32_t iters, void* stream, uint32_t* status, double* ops_per_launch) {
@@ -1406,6 +1427,7 @@ int32_t vyb_k_moe_ep_ffn_int4(const vyb_moe_ep_ctx* ctx, const void* x_bf16, con
     c.off_src = ctx->off_src;
     c.off_xg = ctx->off_xg;
     c.off_yhome = ctx->off_yhome;
+    c.wait_clocks = ctx->wait_clocks;
     int sms = 0;
     if (int32_t rc = current_sm_count(&sms)) return rc;
     return launch_result(vybk::launch_moe_ep_ffn(c, x_bf16, w_router_bf16, w13, s13, w2, s2, out_bf16,

@@ -20,17 +20,24 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                                     uint32_t* status, bool constant_weights);
 // ---- all-gather of column-parallel outputs over peer memory (allgather_push.cu) ------------------------------------
-// gather buffers [2][world][m][n] bf16 per rank; arrival counters and the launch counter are 32-bit device words,
+// gather buffers [2][world][m][n] bf16 per rank; arrival counters and launch counters are 32-bit device words,
 // zero before the first push
 struct PeerGather {
     uint32_t world = 0, rank = 0;
     unsigned long long peer_out[8] = {};   // base of every rank's gather buffer (own rank included)
-    unsigned long long peer_flag[8] = {};  // every rank's arrival counter (own rank: the one this rank polls)
-    unsigned long long epoch = 0;          // local: pushes completed
+    unsigned long long peer_flag[8] = {};  // every rank's 256 bytes of arrival counters: word 8 s counts pushes from rank s
+    unsigned long long epoch = 0;          // local: 8 words, pushes completed per peer slot
+    unsigned long long wait_clocks = 0;    // clock limit of a device-side wait; 0 = about 2 s
 };
 cudaError_t launch_allgather_push(const PeerGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
                                   uint32_t* status);
 cudaError_t launch_allgather_wait(const PeerGather& ag, cudaStream_t stream, uint32_t* status);
+// column-parallel gather: this rank's [rows, row_bytes] block -> byte offset dst_offset_bytes (row pitch dst_pitch_bytes)
+// of EVERY rank's buffer peer_out[r], own rank included; tickets: 8 zeroed local words; then every destination's
+// counter for this rank goes up by one. launch_colpar_wait: until every rank has delivered `want` blocks here.
+cudaError_t launch_colpar_push(const PeerGather& ag, const void* src, uint32_t rows, uint32_t row_bytes, uint64_t dst_pitch_bytes,
+                               uint64_t dst_offset_bytes, uint32_t* tickets, cudaStream_t stream, uint32_t* status);
+cudaError_t launch_colpar_wait(const PeerGather& ag, uint32_t want, cudaStream_t stream, uint32_t* status);
 // any group size dividing k, k % 8 == 0, any m; plain loads, no TMA
 cudaError_t launch_int4_linear_generic(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y,
                                        uint32_t m, uint32_t n, uint32_t k, uint32_t group, uint32_t out_f32,
@@ -82,6 +89,7 @@ struct MoeEp {
     uint32_t world = 0, rank = 0;
     unsigned long long peer_base[8] = {};  // base of every rank's symmetric region (own rank included)
     unsigned long long off_counts = 0, off_flags = 0, off_src = 0, off_xg = 0, off_yhome = 0;  // same on every rank
+    unsigned long long wait_clocks = 0;  // clock limit of a device-side wait; 0 = about 2 s
 };
 uint32_t moe_ep_max_rows(uint32_t tokens_total, uint32_t experts, uint32_t topk, uint32_t world);
 void moe_ep_symmetric_layout(uint32_t tokens_local_max, uint32_t tokens_total, uint32_t hidden, uint32_t experts,

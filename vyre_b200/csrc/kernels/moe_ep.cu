@@ -54,9 +54,10 @@ __device__ __forceinline__ uint32_t* flag_of(const MoeEp& c, uint32_t rank, uint
 __device__ bool wait_flag(const MoeEp& c, uint32_t which, uint32_t want, const uint32_t* status) {
     if (status && (*reinterpret_cast<const volatile uint32_t*>(status) & 256u)) return false;
     const volatile uint32_t* f = flag_of(c, c.rank, which);
+    const long long limit = c.wait_clocks ? (long long)c.wait_clocks : WAIT_CLOCKS;
     const long long t0 = clock64();
     while (int32_t(*f - want) < 0) {
-        if (clock64() - t0 > WAIT_CLOCKS) return false;
+        if (clock64() - t0 > limit) return false;
         __nanosleep(64);
     }
     return true;

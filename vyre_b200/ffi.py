@@ -38,14 +38,15 @@ class AllGatherCtx(C.Structure):
     """vyb_allgather_ctx: peer addresses of the gather buffers / arrival counters and the local step words."""
 
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("peer_out", C.c_uint64 * 8), ("peer_flag", C.c_uint64 * 8),
-                ("epoch", C.c_uint64)]
+                ("epoch", C.c_uint64), ("wait_clocks", C.c_uint64)]
 
 
 class MoeEpCtx(C.Structure):
     """vyb_moe_ep_ctx: peer addresses of the symmetric regions and the offsets inside them."""
 
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("peer_base", C.c_uint64 * 8), ("off_counts", C.c_uint64),
-                ("off_flags", C.c_uint64), ("off_src", C.c_uint64), ("off_xg", C.c_uint64), ("off_yhome", C.c_uint64)]
+                ("off_flags", C.c_uint64), ("off_src", C.c_uint64), ("off_xg", C.c_uint64), ("off_yhome", C.c_uint64),
+                ("wait_clocks", C.c_uint64)]
 
 
 class ResidentHandle(C.Structure):
@@ -178,6 +179,8 @@ _STATUS_FUNCS = {
     "vyb_completion_output": [_P, _U, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
     "vyb_completion_device_ns": [_P, C.POINTER(C.c_uint64)],
     "vyb_k_tensor_peak": [_U, _U, _P, _P, C.POINTER(C.c_double)],
+    "vyb_k_colpar_push": [C.POINTER(AllGatherCtx), _P, _U, _U, C.c_uint64, C.c_uint64, _P, _P],
+    "vyb_k_colpar_wait": [C.POINTER(AllGatherCtx), _U, _P, _P],
     "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int4_gemv_ex": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int8_weight_only_linear": [_P, _P, _P, _P, _U, _U, _U, _P],

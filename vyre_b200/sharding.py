@@ -318,6 +318,103 @@ class PeerAllGather:
                                                            C.c_void_p(status.data_ptr())))
 
 
+class PeerColumnGather:
+    """Full [m, n_total] output of a column-parallel linear on every rank, assembled by vyb_k_colpar_push: every rank
+    stores its columns of a block of rows straight into every rank's buffer (peer stores over NVLink, symmetric
+    memory, no staging and no host-side interleave). Blocks are counted: `wait(blocks)` is the consumer-side check.
+    The buffer is reused call after call: start the next gather only when its consumers are done on every rank."""
+
+    def __init__(self, m: int, n_total: int, elem_bytes: int, group=None, multiple: int = 4):
+        import os
+
+        import torch
+        import torch.distributed as dist
+
+        from . import ffi
+
+        self.ffi, self.torch = ffi, torch
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > 8:
+            raise ValueError("the peer-store gather addresses at most 8 peers")
+        self.m, self.n, self.elem = m, n_total, elem_bytes
+        self.begin, self.end = column_shard(n_total, self.world, self.rank, multiple)
+        if (n_total * elem_bytes) % 16 or (self.begin * elem_bytes) % 16 or ((self.end - self.begin) * elem_bytes) % 16:
+            raise ValueError("rows, shard offsets and shard widths must be multiples of 16 bytes")
+        self.data_bytes = (m * n_total * elem_bytes + 255) & ~255
+        total = self.data_bytes + 256
+        if self.world > 1:
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings are all that is needed
+            import torch.distributed._symmetric_memory as symm
+
+            self.buf = symm.empty(total, dtype=torch.uint8, device="cuda")
+            self.buf.zero_()
+            torch.cuda.synchronize()
+            self.handle = symm.rendezvous(self.buf, group if group is not None else dist.group.WORLD)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buf = torch.zeros(total, dtype=torch.uint8, device="cuda")
+            self.handle = None
+            ptrs = [self.buf.data_ptr()]
+        self.local = torch.zeros(64, dtype=torch.int32, device="cuda")  # launch counters and tickets
+        self.ctx = ffi.AllGatherCtx()
+        self.ctx.world, self.ctx.rank = self.world, self.rank
+        for r in range(self.world):
+            self.ctx.peer_out[r] = ptrs[r]
+            self.ctx.peer_flag[r] = ptrs[r] + self.data_bytes
+        self.ctx.epoch = self.local.data_ptr()
+        self.blocks = 0  # blocks pushed so far by every rank (all ranks push the same number)
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group)
+
+    def output(self, dtype):
+        return self.buf[: self.m * self.n * self.elem].view(dtype).view(self.m, self.n)
+
+    def push(self, block, row0: int, stream, status):
+        """block: this rank's columns [rows, end - begin] of rows [row0, row0 + rows), contiguous."""
+        rows, width = block.shape
+        assert width == self.end - self.begin and block.is_contiguous()
+        self.ffi.check(self.ffi.lib().vyb_k_colpar_push(
+            C.byref(self.ctx), block.data_ptr(), rows, width * self.elem, self.n * self.elem,
+            (row0 * self.n + self.begin) * self.elem, C.c_void_p(stream), C.c_void_p(status.data_ptr())))
+        self.blocks += 1
+
+    def wait(self, stream, status):
+        self.ffi.check(self.ffi.lib().vyb_k_colpar_wait(C.byref(self.ctx), self.blocks, C.c_void_p(stream),
+                                                        C.c_void_p(status.data_ptr())))
+
+
+def column_parallel_int8_linear(gather: PeerColumnGather, xq, w_rows, status, chunks: int = 4, side_stream=None):
+    """y int32 [m, n_total] = xq int8 [m, k] . W^T with this rank holding rows [begin, end) of W: the GEMM runs in
+    `chunks` row chunks on the current stream, each chunk's columns are pushed to every rank on `side_stream` while the
+    next chunk's GEMM runs, and the call ends with the bounded wait for every rank's blocks. Returns the full output."""
+    import torch
+
+    from . import ffi
+
+    L = ffi.lib()
+    m, k = xq.shape
+    n_local = w_rows.shape[0]
+    cur = torch.cuda.current_stream()
+    side = side_stream or cur
+    y_local = torch.empty((m, n_local), dtype=torch.int32, device="cuda")
+    step = (m + chunks - 1) // chunks
+    for r0 in range(0, m, step):
+        rows = min(step, m - r0)
+        ffi.check(L.vyb_k_int8_gemm_i32(xq[r0:r0 + rows].data_ptr(), w_rows.data_ptr(), y_local[r0:r0 + rows].data_ptr(), rows,
+                                        n_local, k, C.c_void_p(cur.cuda_stream), C.c_void_p(status.data_ptr())))
+        if side is not cur:
+            ev = torch.cuda.Event()
+            ev.record(cur)
+            side.wait_event(ev)
+        gather.push(y_local[r0:r0 + rows], r0, side.cuda_stream, status)
+    if side is not cur:
+        cur.wait_stream(side)
+    gather.wait(cur.cuda_stream, status)
+    return gather.output(torch.int32), y_local
+
+
 # ---- expert-parallel MoE FFN with device-side dispatch / combine (peer stores over NVLink, symmetric memory) --------
 class DeviceExpertParallel:
     """One MoE FFN layer over the ranks of a group with no host read-back: vyb_k_moe_ep_ffn_int4.
