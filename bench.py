@@ -491,7 +491,10 @@ def run_native(args) -> None:
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     stream = torch.cuda.Stream()
     side = torch.cuda.Stream()
-    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS
+    # with a concurrent push kernel the GEMV leaves one SM free: two GEMV launches (the running one and the next, which
+    # prefetches beside it) fill every SM they use, and the push CTAs (one per peer, 256 threads, no shared memory: all
+    # of them fit one SM) would otherwise wait for a GEMV CTA to leave
+    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS | (ffi.LAUNCH_LEAVE_ONE_SM if world > 1 else 0)
 
     def launch(c: int, out=None, xin=None, mm=None):
         # weights are graph constants: the launch may overlap the tail of the previous one

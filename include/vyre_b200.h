@@ -328,6 +328,18 @@ const char* vyb_program_trap_message(const vyb_program* p);
 void vyb_program_fingerprint(const vyb_program* p, uint8_t out[32]); /* Program::fingerprint */
 void vyb_program_free(vyb_program* p);
 
+/* A program rebuilt from what a vyre Artifact carries: the op id (outermost Region generator) and the BufferDecls of
+ * its Program. This is what the TargetCompiler facet calls, because TargetCompiler::compile(&Artifact)
+ * (vyre-megakernel/src/target.rs:180-189, helper :253-322) is handed an Artifact, not builder arguments, and a
+ * Program keeps its dimensions as IR literals. `op_spec` (nullable) is the op's dimensions in builder order, taken
+ * from the Program's metadata map (docs/wire-format.md:104-111) when the producer attached them; without it the
+ * dimensions are recovered from the buffer counts. Either way every declaration is cross-checked against the rebuilt
+ * program (count, dtype, access per slot): a mismatch is InvalidProgram. Ops: linear_4bit, linear_4bit_affine_grouped
+ * (spec in_dim, out_dim, group_size, batch), int4 [batched_]matvec_f32_scaled under both id families (spec batch, rows,
+ * cols), moe_gate (spec num_experts, k), swiglu (spec n), int8_unpack (spec n, cols); others UnsupportedFeature. */
+int32_t vyb_program_from_op(const char* op_id, const vyb_buffer_decl* decls, uint32_t n_decls, const uint32_t* op_spec,
+                            uint32_t n_spec, vyb_program** program);
+
 /* ---- compile: ProgramGraph::from_program + vyre_megakernel::compile (vyre-megakernel/src/lib.rs:832) -- */
 int32_t vyb_compile(const vyb_program* program, vyb_artifact** artifact);
 void vyb_artifact_digest(const vyb_artifact* a, uint8_t out[32]);
@@ -490,6 +502,12 @@ int32_t vyb_k_quantize_per_token_int8(const void* x_bf16, void* q_i8, void* scal
  * reading of the reference's wrapping-u32 Matmul (vyre-libs/src/math/linalg/matmul.rs:17-60). k % 16 == 0. */
 int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
                             void* stream, uint32_t* status);
+/* Same with launch flags. VYB_LAUNCH_LEAVE_COPY_SMS: the persistent GEMM runs on 16 SMs fewer than the device has, so
+ * that a copy kernel of another stream (vyb_k_colpar_push of the previous row chunk) runs beside it instead of
+ * behind it. */
+#define VYB_LAUNCH_LEAVE_COPY_SMS 4u
+int32_t vyb_k_int8_gemm_i32_ex(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
+                               uint32_t flags, void* stream, uint32_t* status);
 /* The fused multi-token MoE FFN layer of vyb_nn_moe_ffn_int4 on raw device pointers (same operands, layouts and
  * results; batched composition of vyre-libs/src/nn/moe/{gating.rs:19,expert_mlp.rs:18,moe_layer.rs:33}). The caller
  * provides the scratch (expert-sorted rows, hidden activations, per-pair outputs, routing plan); its size comes

@@ -409,6 +409,24 @@ class Device:
         return ArtifactInstance(out.value, self)
 
 
+def program_from_op(op_id: str, buffers: list[dict], op_spec: list[int] | None = None) -> Program:
+    """Rebuilds a Program from what a vyre Artifact carries: the op id and the BufferDecls (dicts as Program.buffers()
+    returns them), optionally the op's dimensions in builder order (vyb_program_from_op)."""
+    arr = (ffi.BufferDecl * max(1, len(buffers)))()
+    keep = []
+    for i, b in enumerate(buffers):
+        name = b["name"].encode()
+        keep.append(name)
+        arr[i].name, arr[i].binding, arr[i].access, arr[i].dtype, arr[i].count = name, b["binding"], b["access"], b["dtype"], b["count"]
+        if b.get("output_byte_range"):
+            arr[i].has_output_byte_range = 1
+            arr[i].output_byte_begin, arr[i].output_byte_end = b["output_byte_range"]
+    spec = (C.c_uint32 * max(1, len(op_spec or [])))(*(op_spec or []))
+    out = C.c_void_p()
+    check(ffi.lib().vyb_program_from_op(op_id.encode(), arr, len(buffers), spec if op_spec else None, len(op_spec or []), C.byref(out)))
+    return Program(out.value)
+
+
 class BindingSet:
     """vyre_driver BindingSet: values keyed by ArtifactValueId (= buffer binding slot)."""
 

@@ -965,6 +965,115 @@ int32_t vyb_nn_moe_ffn_int4(const char* x, const char* w_router, const char* w13
 }
 
 // ---- accessors ----------------------------------------------------------------------------------------------------------------------
+// ---- Program from an op id plus the BufferDecls of a vyre Program -----------------------------------------------------
+// What TargetCompiler::compile(&Artifact) (vyre-megakernel/src/target.rs:180-189, helper :253-322) can call: it is
+// handed an Artifact, i.e. a Program whose dimensions are IR literals, not builder arguments. The op id (the outermost
+// Region generator) picks the builder; the dimensions come from the op spec when the caller attached one to the
+// Program's metadata map (docs/wire-format.md:104-111), else from the buffer counts; the rebuilt program's buffers are
+// then cross-checked against the declarations one by one.
+static const vyb_buffer_decl* decl_at(const vyb_buffer_decl* d, uint32_t n, uint32_t binding) {
+    for (uint32_t i = 0; i < n; ++i)
+        if (d[i].binding == binding && d[i].access != VYB_ACCESS_WORKGROUP) return &d[i];
+    return nullptr;
+}
+
+int32_t vyb_program_from_op(const char* op_id, const vyb_buffer_decl* decls, uint32_t n_decls, const uint32_t* op_spec,
+                            uint32_t n_spec, vyb_program** program) {
+    if (!op_id || !decls || !program) return fail_invalid_program("Fix: pass a non-null op id, buffer declarations and program out-pointer.");
+    const std::string id = op_id;
+    auto need = [&](uint32_t slots) -> bool {
+        for (uint32_t b = 0; b < slots; ++b)
+            if (!decl_at(decls, n_decls, b) || !decl_at(decls, n_decls, b)->name) return false;
+        return true;
+    };
+    auto count = [&](uint32_t b) -> uint64_t { return decl_at(decls, n_decls, b)->count; };
+    auto name = [&](uint32_t b) -> const char* { return decl_at(decls, n_decls, b)->name; };
+    auto bad_shape = [&](const std::string& what) {
+        return fail_invalid_program("Fix: the buffer counts of `" + id + "` do not describe a valid shape (" + what +
+                                    "); attach the op spec to the Program metadata or correct the declarations.");
+    };
+    vyb_program* out = nullptr;
+    int32_t rc = VYB_OK;
+    if (id == "vyre-libs::nn::linear_4bit_affine_grouped") {
+        // x=0, w=1, scale=2, zp=3, b=4, out=5 (linear_4bit.rs:757-771); spec = [in_dim, out_dim, group_size, batch]
+        if (!need(6)) return bad_shape("six buffers x, w, scale, zero_point, b, out expected");
+        uint64_t in_dim, out_dim, group, batch;
+        if (op_spec && n_spec >= 4) {
+            in_dim = op_spec[0]; out_dim = op_spec[1]; group = op_spec[2]; batch = op_spec[3];
+        } else {
+            out_dim = count(4);
+            if (!out_dim || (count(1) * 8) % out_dim) return bad_shape("packed words are not a multiple of out_dim");
+            in_dim = count(1) * 8 / out_dim;
+            if (!in_dim || count(0) % in_dim) return bad_shape("x is not a multiple of in_dim");
+            batch = count(0) / in_dim;
+            const uint64_t groups = count(2) / out_dim;
+            if (!groups || count(2) % out_dim || in_dim % groups) return bad_shape("scale sidecar is not groups x out_dim");
+            group = in_dim / groups;
+        }
+        rc = vyb_nn_linear_4bit_affine_grouped_batched(name(0), name(1), name(2), name(3), name(4), name(5), uint32_t(in_dim),
+                                                       uint32_t(out_dim), uint32_t(group), uint32_t(batch), &out);
+    } else if (id == "vyre-libs::nn::linear_4bit") {
+        if (!need(4)) return bad_shape("four buffers x, w, b, out expected");
+        const uint64_t in_dim = op_spec && n_spec >= 2 ? op_spec[0] : count(0);
+        const uint64_t out_dim = op_spec && n_spec >= 2 ? op_spec[1] : count(2);
+        rc = vyb_nn_linear_4bit(name(0), name(1), name(2), name(3), uint32_t(in_dim), uint32_t(out_dim), &out);
+    } else if (id == "vyre-libs::quant::int4_batched_matvec_f32_scaled" || id == "vyre-libs::quant::int4_matvec_f32_scaled" ||
+               id == "vyre-primitives::math::quantized::i4x8_batched_matvec_f32_scaled" ||
+               id == "vyre-primitives::math::quantized::i4x8_matvec_f32_scaled") {
+        // weights=0, x=1, scales=2, out=3 (programs.rs:217-225); spec = [batch, rows, cols]
+        if (!need(4)) return bad_shape("four buffers weights, x, scales, out expected");
+        uint64_t batch, rows, cols;
+        if (op_spec && n_spec >= 3) {
+            batch = op_spec[0]; rows = op_spec[1]; cols = op_spec[2];
+        } else {
+            rows = count(2);
+            if (!rows || count(3) % rows) return bad_shape("out is not batch x rows");
+            batch = count(3) / rows;
+            if (!batch || count(1) % batch) return bad_shape("x is not batch x cols");
+            cols = count(1) / batch;
+        }
+        const uint32_t lib = id.rfind("vyre-libs", 0) == 0 ? 1u : 0u;
+        if (id.find("batched") != std::string::npos)
+            rc = vyb_math_i4x8_batched_matvec_f32_scaled(name(0), name(1), name(2), name(3), uint32_t(batch), uint32_t(rows),
+                                                         uint32_t(cols), lib, &out);
+        else
+            rc = vyb_math_i4x8_matvec_f32_scaled(name(0), name(1), name(2), name(3), uint32_t(rows), uint32_t(cols), lib, &out);
+    } else if (id == "vyre-libs::nn::moe_gate") {
+        // scores=0, indices=1, weights=2 (gating.rs:56-68); spec = [num_experts, k]
+        if (!need(3)) return bad_shape("three buffers scores, indices, weights expected");
+        const uint64_t experts = op_spec && n_spec >= 2 ? op_spec[0] : count(0);
+        const uint64_t k = op_spec && n_spec >= 2 ? op_spec[1] : count(1);
+        rc = vyb_nn_moe_gate(name(0), name(1), name(2), uint32_t(experts), uint32_t(k), &out);
+    } else if (id == "vyre-libs::nn::swiglu") {
+        if (!need(3)) return bad_shape("three buffers gate, up, out expected");
+        rc = vyb_nn_swiglu_typed(name(0), name(1), name(2), uint32_t(op_spec && n_spec >= 1 ? op_spec[0] : count(0)),
+                                 decl_at(decls, n_decls, 0)->dtype, &out);
+    } else if (id == "vyre-libs::quant::int8_unpack") {
+        if (!need(3)) return bad_shape("three buffers packed, scales, out expected");
+        const uint64_t n = op_spec && n_spec >= 2 ? op_spec[0] : count(0);
+        const uint64_t rows = count(1);
+        if (!rows || n % rows) return bad_shape("packed values are not rows x cols");
+        rc = vyb_quant_int8_unpack(name(0), name(1), name(2), uint32_t(n), uint32_t(op_spec && n_spec >= 2 ? op_spec[1] : n / rows), &out);
+    } else {
+        return fail_unsupported("rebuilding a program for operator `" + id + "` from buffer declarations");
+    }
+    if (rc != VYB_OK) return rc;
+    // cross-check: every declared storage buffer must match the rebuilt program's buffer of the same slot
+    for (const BufferDecl& b : out->p.buffers) {
+        if (b.access == VYB_ACCESS_WORKGROUP) continue;
+        const vyb_buffer_decl* d = decl_at(decls, n_decls, b.binding);
+        if (!d || d->count != b.count || d->dtype != b.dtype || d->access != b.access) {
+            const std::string which = b.name;
+            delete out;
+            return fail_invalid_program("Fix: buffer `" + which + "` (slot " + std::to_string(b.binding) + ") of `" + id +
+                                        "` disagrees with the shape recovered from the op spec or the other buffers "
+                                        "(count, dtype or access differ); the artifact is not the program this op id names.");
+        }
+    }
+    *program = out;
+    return VYB_OK;
+}
+
 const char* vyb_program_op_id(const vyb_program* p) { return p ? p->p.op_id.c_str() : ""; }
 uint32_t vyb_program_buffer_count(const vyb_program* p) { return p ? uint32_t(p->p.buffers.size()) : 0; }
 int32_t vyb_program_buffer(const vyb_program* p, uint32_t index, vyb_buffer_decl* out) {

@@ -1477,10 +1477,15 @@ int32_t vyb_k_moe_ffn_int4(const void* x_bf16, const void* w_router_bf16, const 
 
 int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
                             void* stream, uint32_t* status) {
+    return vyb_k_int8_gemm_i32_ex(a_i8, w_i8, out_i32, m, n, k, 0, stream, status);
+}
+
+int32_t vyb_k_int8_gemm_i32_ex(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
+                               uint32_t flags, void* stream, uint32_t* status) {
     if (!a_i8 || !w_i8 || !out_i32) return fail_invalid_program("Fix: pass non-null device pointers.");
     if (!vybk::int8_gemm_supported(m, n, k))
         return fail_unsupported("int8 gemm shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
-                                std::to_string(k) + " (needs k a multiple of 16 and at most 133000)");
+                                std::to_string(k) + " (needs k a multiple of 16 and at most 132096)");
     if ((reinterpret_cast<uintptr_t>(a_i8) | reinterpret_cast<uintptr_t>(w_i8) | reinterpret_cast<uintptr_t>(out_i32)) & 15)
         return fail_invalid_program("Fix: int8 gemm operands must be 16-byte aligned (TMA tensor maps need it).");
     int dev = 0, sms = 0;
@@ -1490,6 +1495,7 @@ int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, u
         cudaGetLastError();
         return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
     }
+    if ((flags & VYB_LAUNCH_LEAVE_COPY_SMS) && sms > 32) sms -= 16;  // room for a concurrent copy kernel (the peer-store gather)
     e = vybk::launch_int8_gemm(static_cast<const int8_t*>(a_i8), static_cast<const int8_t*>(w_i8),
                                static_cast<int32_t*>(out_i32), m, n, k, sms, static_cast<cudaStream_t>(stream), status);
     if (e != cudaSuccess) {

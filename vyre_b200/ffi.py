@@ -17,6 +17,7 @@ ACCESS_READ_ONLY, ACCESS_READ_WRITE, ACCESS_OUTPUT, ACCESS_WORKGROUP = 0, 1, 2, 
 BIND_HOST, BIND_RESIDENT = 0, 1
 LAUNCH_CONSTANT_WEIGHTS = 1
 LAUNCH_LEAVE_ONE_SM = 2
+LAUNCH_LEAVE_COPY_SMS = 4
 
 ERR_DEVICE_OUT_OF_MEMORY = 1001
 ERR_UNSUPPORTED_FEATURE = 1002
@@ -150,6 +151,7 @@ _STATUS_FUNCS = {
     "vyb_nn_linear_int8_dynamic": [_S] * 4 + [_U] * 3 + [_PP],
     "vyb_nn_moe_ffn_int4": [_S] * 9 + [_U] * 6 + [_PP],
     "vyb_program_buffer": [_P, _U, C.POINTER(BufferDecl)],
+    "vyb_program_from_op": [_S, C.POINTER(BufferDecl), _U, C.POINTER(C.c_uint32), _U, _PP],
     "vyb_compile": [_P, _PP],
     "vyb_target_compile": [_P, _PP],
     "vyb_payload_bytes": [_P, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
@@ -187,6 +189,7 @@ _STATUS_FUNCS = {
     "vyb_k_int4_prefill_gemm": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_quantize_per_token_int8": [_P, _P, _P, _U, _U, _P],
     "vyb_k_int8_gemm_i32": [_P, _P, _P, _U, _U, _U, _P, _P],
+    "vyb_k_int8_gemm_i32_ex": [_P, _P, _P, _U, _U, _U, _U, _P, _P],
     "vyb_k_allgather_push": [_P, _U, _U, _U, _P, _P],
     "vyb_k_allgather_wait": [_P, _P, _P],
     "vyb_k_moe_route": [_P, _P, _P, _P, _U, _U, _U, _U, _P],

@@ -402,8 +402,10 @@ def column_parallel_int8_linear(gather: PeerColumnGather, xq, w_rows, status, ch
     step = (m + chunks - 1) // chunks
     for r0 in range(0, m, step):
         rows = min(step, m - r0)
-        ffi.check(L.vyb_k_int8_gemm_i32(xq[r0:r0 + rows].data_ptr(), w_rows.data_ptr(), y_local[r0:r0 + rows].data_ptr(), rows,
-                                        n_local, k, C.c_void_p(cur.cuda_stream), C.c_void_p(status.data_ptr())))
+        # every chunk but the first runs beside the push of the chunk before it: leave that copy kernel a few SMs
+        flags = ffi.LAUNCH_LEAVE_COPY_SMS if (side is not cur and r0 > 0) else 0
+        ffi.check(L.vyb_k_int8_gemm_i32_ex(xq[r0:r0 + rows].data_ptr(), w_rows.data_ptr(), y_local[r0:r0 + rows].data_ptr(), rows,
+                                           n_local, k, flags, C.c_void_p(cur.cuda_stream), C.c_void_p(status.data_ptr())))
         if side is not cur:
             ev = torch.cuda.Event()
             ev.record(cur)
