@@ -350,6 +350,10 @@ int32_t vyb_target_compile(const vyb_artifact* artifact, vyb_payload** payload);
 void vyb_payload_digest(const vyb_payload* p, uint8_t out[32]);
 void vyb_payload_neutral_artifact(const vyb_payload* p, uint8_t out[32]);
 const char* vyb_payload_format(const vyb_payload* p);
+/* Which hand-written kernel the payload's first launch module names: 0 = the kernel that replays the reference's
+ * evaluation order, 1.. = the kernels chosen from the op spec at target-compile time (the CUDA payload of the reference
+ * carries its PTX entry point in the same place: vyre-driver-cuda/src/backend/artifact_lifecycle.rs:69-130). */
+uint32_t vyb_payload_kernel_variant(const vyb_payload* p);
 /* TargetPayload::to_bytes / from_bytes (vyre-megakernel/src/envelope.rs); from_bytes re-authenticates */
 int32_t vyb_payload_bytes(const vyb_payload* p, const uint8_t** bytes, size_t* len);
 int32_t vyb_payload_from_bytes(const uint8_t* bytes, size_t len, vyb_payload** payload);

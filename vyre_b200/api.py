@@ -314,6 +314,9 @@ class TargetPayload:
     def format(self) -> str:
         return ffi.lib().vyb_payload_format(self._h).decode()
 
+    def kernel_variant(self) -> int:
+        return int(ffi.lib().vyb_payload_kernel_variant(self._h))
+
     def to_bytes(self) -> bytes:
         p = C.POINTER(C.c_uint8)()
         n = C.c_size_t()
@@ -617,6 +620,10 @@ class ArtifactSession:
 
     def envelope_bytes(self) -> bytes:
         return self.payload.to_bytes()
+
+    def kernel_variant(self) -> int:
+        """The hand-written kernel the target compiler chose for this program (0: reference evaluation order)."""
+        return self.payload.kernel_variant()
 
     def rematerialize(self) -> None:
         """Re-admit the same authenticated payload bytes on the device's current generation; never recompiles

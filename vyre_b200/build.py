@@ -31,6 +31,7 @@ SOURCES = {
     "host/artifact.cpp": [],
     "host/runtime.cu": [],
     "kernels/ref_ops.cu": ["-ftz=true", "-prec-div=true", "-prec-sqrt=true", "-fmad=false"],
+    "kernels/dropin_fast.cu": ["-ftz=true", "-fmad=false"],
     "kernels/int4_gemv.cu": [],
     "kernels/int4_gemv_halfsm.cu": [],
     "kernels/int8_linear.cu": [],

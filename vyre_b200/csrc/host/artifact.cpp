@@ -90,6 +90,18 @@ uint32_t select_kernel_variant(const Program& p) {
         }
         case OpKind::LinearInt8Dynamic: return KV_INT8_GEMM_TCGEN05;
         case OpKind::MoeFfnInt4: return KV_MOE_FUSED;
+        // the reference's own operators: small shapes keep the kernels that follow the reference's evaluation order
+        // (bit-exact against its interpreter), large ones get kernels shaped for the layout (same dequantisation,
+        // different summation order)
+        case OpKind::Linear4BitAffineGrouped: {
+            const uint64_t in_dim = p.params.u[0], out_dim = p.params.u[1], group = p.params.u[2], batch = p.params.u[3];
+            const bool big = in_dim * out_dim * batch >= (1ull << 24);
+            return big && in_dim % 8 == 0 && group % 8 == 0 && in_dim % group == 0 ? KV_AFFINE_GROUPED_OUTPUT_MAJOR : KV_GENERIC;
+        }
+        case OpKind::I4BatchedMatvec: {
+            const uint64_t batch = p.params.u[0], rows = p.params.u[1], cols = p.params.u[2];
+            return batch * rows * cols >= (1ull << 22) ? KV_I4_MATVEC_WARP_ROWS : KV_GENERIC;
+        }
         default: return KV_GENERIC;
     }
 }
@@ -273,6 +285,9 @@ void vyb_payload_neutral_artifact(const vyb_payload* p, uint8_t out[32]) {
     std::memcpy(out, p->p.neutral_artifact.data(), 32);
 }
 const char* vyb_payload_format(const vyb_payload* p) { return p->p.format.c_str(); }
+uint32_t vyb_payload_kernel_variant(const vyb_payload* p) {
+    return p && !p->p.modules.empty() ? p->p.modules.front().kernel_variant : 0u;
+}
 int32_t vyb_payload_bytes(const vyb_payload* p, const uint8_t** bytes, size_t* len) {
     if (!p || !bytes || !len) return fail_invalid_program("Fix: pass non-null payload, bytes and len pointers.");
     *bytes = p->p.bytes.data();

@@ -133,6 +133,8 @@ enum KernelVariant : uint32_t {
     KV_INT4_PREFILL_TCGEN05 = 2,
     KV_INT8_GEMM_TCGEN05 = 3,
     KV_MOE_FUSED = 4,
+    KV_AFFINE_GROUPED_OUTPUT_MAJOR = 5,  // the reference's own 4-bit layout, thread per output, 8 batch rows per weight
+    KV_I4_MATVEC_WARP_ROWS = 6,          // i4x8 matvec, warp per row
 };
 
 uint32_t select_kernel_variant(const Program& p);

@@ -262,6 +262,10 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
         case OpKind::Linear4Bit:
             return launch_linear_4bit((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2], (float*)b[3], u[0], u[1], s);
         case OpKind::Linear4BitAffineGrouped:
+            if (inst->variant == KV_AFFINE_GROUPED_OUTPUT_MAJOR && affine_grouped_fast_supported(u[0], u[1], u[2], u[3]))
+                return launch_affine_grouped_fast((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2],
+                                                  (const uint32_t*)b[3], (const float*)b[4], (float*)b[5], u[0], u[1], u[2],
+                                                  u[3], inst->dev->prop.multiProcessorCount, s);
             return launch_linear_4bit_affine_grouped((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2],
                                                      (const uint32_t*)b[3], (const float*)b[4], (float*)b[5], u[0], u[1],
                                                      u[2], u[3], s);
@@ -271,6 +275,9 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             return launch_i4_dot_f32_scaled((const uint32_t*)b[0], (const uint32_t*)b[1], (const float*)b[2],
                                             (const float*)b[3], (float*)b[4], u[0], s);
         case OpKind::I4BatchedMatvec:
+            if (inst->variant == KV_I4_MATVEC_WARP_ROWS && i4_matvec_fast_supported(u[0], u[1], u[2]))
+                return launch_i4_matvec_fast((const uint32_t*)b[0], (const float*)b[1], (const float*)b[2], (float*)b[3], u[0],
+                                             u[1], u[2], s);
             return launch_i4_batched_matvec((const uint32_t*)b[0], (const float*)b[1], (const float*)b[2], (float*)b[3],
                                             u[0], u[1], u[2], s);
         case OpKind::I4BatchedMatmul:

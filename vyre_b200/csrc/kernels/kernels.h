@@ -142,6 +142,15 @@ cudaError_t launch_i4_batched_matmul_top1(const uint32_t* w, const uint32_t* act
 cudaError_t launch_int8_unpack(const uint32_t* packed, const float* scales, float* out, uint32_t n, uint32_t cols,
                                cudaStream_t s);
 cudaError_t launch_int8_pack(const uint32_t* in, uint32_t* out, uint32_t n, cudaStream_t s);
+// ---- the same two reference operators at large shapes (dropin_fast.cu): the reference's layouts and dequantisation,
+// a summation order of their own. The *_supported predicates are pure functions of the op spec.
+bool affine_grouped_fast_supported(uint32_t in_dim, uint32_t out_dim, uint32_t group, uint32_t batch);
+bool i4_matvec_fast_supported(uint32_t batch, uint32_t rows, uint32_t cols);
+cudaError_t launch_affine_grouped_fast(const float* x, const uint32_t* w, const float* scale, const uint32_t* zp,
+                                       const float* b, float* out, uint32_t in_dim, uint32_t out_dim, uint32_t group,
+                                       uint32_t batch, int sm_count, cudaStream_t s);
+cudaError_t launch_i4_matvec_fast(const uint32_t* w, const float* x, const float* scales, float* out, uint32_t batch,
+                                  uint32_t rows, uint32_t cols, cudaStream_t s);
 // dtype: 0 = f32, 1 = bf16, 2 = f16
 cudaError_t launch_linear_rows(const void* x, const void* w, const void* bias, void* out, uint32_t rows,
                                uint32_t in_dim, uint32_t out_dim, uint32_t dtype, uint32_t out_in, cudaStream_t s);

@@ -223,6 +223,7 @@ _OTHER_FUNCS = {
     "vyb_payload_digest": (None, [_P, C.c_char_p]),
     "vyb_payload_neutral_artifact": (None, [_P, C.c_char_p]),
     "vyb_payload_format": (C.c_char_p, [_P]),
+    "vyb_payload_kernel_variant": (C.c_uint32, [_P]),
     "vyb_payload_free": (None, [_P]),
     "vyb_device_release": (None, [_P]),
     "vyb_instance_artifact_digest": (None, [_P, C.c_char_p]),
