@@ -288,6 +288,8 @@ def measure_dropin_1m(local_rank: int, samples: int = 30) -> dict:
     `nn.linear_4bit_affine_grouped.1m` (vyre-bench/src/cases/quantized_linear.rs:30-40: in_dim 256, out_dim 4096, group 64,
     batch 256), every buffer resident, device time of one dispatch from the events that bracket it in the contract path
     (the reference samples device timestamps the same way, over the same buffers again and again)."""
+    import numpy as np
+
     import vyre_b200 as vb
 
     k, n, g, b = 256, 4096, 64, 256

@@ -259,6 +259,19 @@ int32_t vyb_nn_linear_rows_no_bias_out_in_typed(const char* x, const char* w, co
 /* vyre-libs/src/math/linalg/matmul.rs:17-60 (wrapping u32) */
 int32_t vyb_math_matmul(const char* a, const char* b, const char* out, uint32_t m, uint32_t k, uint32_t n,
                         vyb_program** program);
+/* vyre-libs/src/math/linalg/matmul.rs:138-271 (MatmulBias: out[i, j] = sum_k a[i, k] * b[k, j] + bias[j], wrapping u32;
+ * buffers a=0, b=1, bias=2, out=3) and matmul_tiled/ops.rs:261-337 + program.rs:105-200 (the tiled form declares two
+ * workgroup tiles and an output padded to 16 x 16 tiles with the logical bytes as its readback range) */
+int32_t vyb_math_matmul_bias(const char* a, const char* b, const char* bias, const char* out, uint32_t m, uint32_t k,
+                             uint32_t n, vyb_program** program);
+int32_t vyb_math_matmul_bias_tiled(const char* a, const char* b, const char* bias, const char* out, uint32_t m, uint32_t k,
+                                   uint32_t n, uint32_t tile, vyb_program** program);
+/* vyre-libs/src/nn/linear/inner/builder.rs:139-162 (nn::linear: out[i] = sum_k x[k] * w[k, i] + b[i] over MatmulBias with
+ * m = 1; hands over to linear_tiled with tile 32 from in_dim * out_dim >= 1024) and tiled.rs:13-50 (nn::linear_tiled) */
+int32_t vyb_nn_linear(const char* x, const char* w, const char* b, const char* out, uint32_t in_dim, uint32_t out_dim,
+                      vyb_program** program);
+int32_t vyb_nn_linear_tiled(const char* x, const char* w, const char* b, const char* out, uint32_t in_dim, uint32_t out_dim,
+                            uint32_t tile, vyb_program** program);
 
 /* vyre-libs/src/nn/moe/gating.rs:19; softmax_top_k.rs:25; top_k.rs:18 */
 int32_t vyb_nn_moe_gate(const char* input_scores, const char* output_indices, const char* output_weights,

@@ -100,6 +100,14 @@ def pack_rows(values, rows, cols):
     return (nib << (4 * np.arange(8, dtype=np.uint32))).sum(axis=2, dtype=np.uint64).astype(np.uint32).reshape(-1)
 
 
+def exact_matvec(w, x, scales, batch, rows, cols):
+    wpr = (cols + 7) // 8
+    nib = ((w.reshape(rows, wpr, 1) >> (4 * np.arange(8, dtype=np.uint32))) & 0xF).reshape(rows, wpr * 8)[:, :cols].astype(np.int8)
+    signed = np.where(nib >= 8, nib - 16, nib).astype(np.float64)
+    xs = x.reshape(batch, cols).astype(np.float64)
+    return ((xs @ signed.T) * scales.astype(np.float64)[None, :]).reshape(-1)
+
+
 # (batch, rows, cols): decode shapes, then rows / batch that fill no tile, a row whose last word is partial (cols % 8 = 4)
 # and rows that are not 16-byte multiples (cols % 4 = 2: the scalar path for every word)
 MATVEC_SHAPES = [(1, 14336, 4096), (8, 4096, 4096), (11, 1001, 4100), (3, 777, 4102), (64, 256, 256)]
@@ -123,8 +131,13 @@ def test_i4_matvec_large_shapes_take_the_warp_row_kernel_and_match_the_oracle(de
     got = as_f32(sess.run_host([w, x, scales])[0])
     want = oracle.i4x8_batched_matvec_f32_scaled(w, x, scales, batch, rows, cols)
     assert bits(got).tolist() == bits(want).tolist()
+    # random data. The reference order is one f32 chain over the whole row, which by itself sits up to ~1e-3 from the
+    # exact sum at 4096 columns (partial sums of a few hundred, 4096 roundings); a per-element 1e-4 window around THAT
+    # value would measure the oracle's rounding, not this kernel's. So: (a) max error relative to the largest output
+    # within 1e-4 (f32 accumulation), and (b) against the exact f64 result this kernel is about as close as the reference order or closer
     x = rng.standard_normal(batch * cols).astype(np.float32)
-    got = as_f32(sess.run_host([w, x, scales])[0])
-    want = oracle.i4x8_batched_matvec_f32_scaled(w, x, scales, batch, rows, cols)
-    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
-    assert (err <= DRIFT * np.maximum(1.0, np.abs(want))).all(), float(err.max())
+    got = as_f32(sess.run_host([w, x, scales])[0]).astype(np.float64)
+    want = oracle.i4x8_batched_matvec_f32_scaled(w, x, scales, batch, rows, cols).astype(np.float64)
+    assert np.abs(got - want).max() <= DRIFT * max(1.0, np.abs(want).max())
+    exact = exact_matvec(w, x, scales, batch, rows, cols)
+    assert np.abs(got - exact).max() <= 1.5 * np.abs(want - exact).max() + 4 * np.spacing(np.float32(np.abs(want).max()))

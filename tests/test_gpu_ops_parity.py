@@ -194,6 +194,23 @@ def test_int8_and_matmul_and_linear_rows(dev):
     b = rng.integers(0, 2**32, size=(9, 7), dtype=np.uint32)
     got = as_u32(run(dev, vb.matmul("a", "b", "o", 5, 9, 7), [a, b])[0])
     assert got.tolist() == oracle.matmul_u32(a, b, None, 5, 9, 7).tolist()
+    # registry fixtures: matmul_bias (vyre-libs/src/math/linalg/matmul.rs:708-731), nn::linear (nn/linear/inner/tiled.rs:150-186)
+    assert as_u32(run(dev, vb.matmul_bias("a", "b", "bias", "out", 2, 2, 2), [u32(1, 2, 3, 4), u32(5, 6, 7, 8), u32(10, 20)])[0]
+                  ).tolist() == [29, 42, 53, 70]
+    assert as_u32(run(dev, vb.matmul_bias_tiled("a", "b", "bias", "out", 2, 2, 2, 2), [u32(1, 2, 3, 4), u32(5, 6, 7, 8), u32(10, 20)])[0]
+                  ).tolist() == [29, 42, 53, 70]
+    assert as_u32(run(dev, vb.linear("x", "w", "b", "out", 4, 4), [np.arange(4, dtype=np.uint32), np.arange(16, dtype=np.uint32),
+                                                                   u32(0, 0, 0, 0)])[0]).tolist() == [56, 62, 68, 74]
+    # wrapping products at sizes that fill no tile, through the flat, the tiled and the linear builders
+    for m, k, n in [(1, 1, 1), (33, 65, 31), (70, 100, 129), (1, 300, 257)]:
+        a = rng.integers(0, 2**32, size=(m, k), dtype=np.uint32)
+        b = rng.integers(0, 2**32, size=(k, n), dtype=np.uint32)
+        bias = rng.integers(0, 2**32, size=n, dtype=np.uint32)
+        want = oracle.matmul_u32(a, b, bias, m, k, n).tolist()
+        assert as_u32(run(dev, vb.matmul_bias("a", "b", "bias", "out", m, k, n), [a, b, bias])[0]).tolist() == want
+        assert as_u32(run(dev, vb.matmul_bias_tiled("a", "b", "bias", "out", m, k, n, 32), [a, b, bias])[0]).tolist() == want
+        if m == 1:
+            assert as_u32(run(dev, vb.linear("x", "w", "b", "out", k, n), [a, b, bias])[0]).tolist() == want
     for dt, odt in [(ffi.DT_F32, oracle.DT_F32), (ffi.DT_BF16, oracle.DT_BF16), (ffi.DT_F16, oracle.DT_F16)]:
         x = rng.standard_normal((3, 40)).astype(np.float32)
         w = rng.standard_normal((40, 6)).astype(np.float32)

@@ -317,6 +317,13 @@ def test_matmul_u32_wraps():
     assert np.array(oracle.matmul_u32(a, b, None, 1, 2, 1), dtype=np.uint32).view(np.int32).tolist() == [4]
 
 
+def test_matmul_bias_and_linear_registry_fixtures():
+    # vyre-libs/src/math/linalg/matmul.rs:708-731; vyre-libs/src/nn/linear/inner/tiled.rs:150-186
+    assert oracle.matmul_u32(u32(1, 2, 3, 4), u32(5, 6, 7, 8), u32(10, 20), 2, 2, 2).tolist() == [29, 42, 53, 70]
+    assert oracle.matmul_u32(np.arange(4, dtype=np.uint32), np.arange(16, dtype=np.uint32), u32(0, 0, 0, 0), 1, 4, 4).tolist() == [
+        56, 62, 68, 74]
+
+
 # --- compositions (unpinned by reference fixtures; self-consistency with the pinned pieces) -----------------
 def test_int4_rowmajor_composition_matches_primitive_layout():
     rng = np.random.default_rng(0)

@@ -46,3 +46,28 @@ def test_int4_matvec_and_gate_programs_from_op_ids():
     with pytest.raises(vb.BackendError) as e:
         api.program_from_op("vyre-libs::nn::attention", [dict(name="q", binding=0, access=0, dtype=ffi.DT_F32, count=4)])
     assert e.value.code == ffi.ERR_UNSUPPORTED_FEATURE
+
+
+def test_matmul_bias_and_linear_programs_from_op_ids():
+    # vyre-libs/src/math/linalg/matmul.rs:252-268 (a, b, bias, out), vyre-libs/src/nn/linear/inner/builder.rs:139-162
+    prog = vb.matmul_bias("a", "b", "bias", "out", 5, 9, 7)
+    assert prog.op_id == "vyre-libs::math::matmul_bias" and [b["binding"] for b in prog.buffers()] == [0, 1, 2, 3]
+    roundtrip(prog, [5, 9, 7])
+    small = vb.linear("x", "w", "b", "out", 4, 4)  # the registry fixture's shape stays on the flat form
+    assert small.op_id == "vyre-libs::nn::linear" and [b["count"] for b in small.buffers()] == [4, 16, 4, 4]
+    roundtrip(small, [4, 4])
+    # from in_dim * out_dim >= 1024 the builder hands over to the tiled form (builder.rs:147-152, tiled.rs:13-14):
+    # two workgroup tiles of 32 x 16 and an output padded to whole 16 x 16 tiles, read back over its logical bytes
+    big = vb.linear("x", "w", "b", "out", 64, 40)
+    assert big.op_id == "vyre-libs::nn::linear_tiled"
+    bufs = {b["name"]: b for b in big.buffers()}
+    assert bufs["matmul_a_tile"]["count"] == 512 and bufs["matmul_b_tile"]["count"] == 512
+    assert bufs["out"]["count"] == 3 * 256 and bufs["out"]["output_byte_range"] == (0, 40 * 4) and bufs["out"]["binding"] == 3
+    roundtrip(big, [64, 40, 32])
+    assert vb.linear_tiled("x", "w", "b", "out", 64, 40, 32).fingerprint() == big.fingerprint()
+    for bad in [(0, 4), (4, 0), (1 << 17, 1 << 16)]:
+        with pytest.raises(vb.BackendError) as e:
+            vb.linear("x", "w", "b", "out", *bad)
+        assert e.value.code == ffi.ERR_INVALID_PROGRAM and "Fix:" in str(e.value)
+    with pytest.raises(vb.BackendError, match="needs the op spec"):
+        api.program_from_op("vyre-libs::math::matmul", [b for b in vb.matmul("a", "b", "o", 2, 3, 4).buffers()])

@@ -195,6 +195,23 @@ def matmul(a, b, out, m, k, n):
     return _build("vyb_math_matmul", a, b, out, m, k, n)
 
 
+def matmul_bias(a, b, bias, out, m, k, n):
+    return _build("vyb_math_matmul_bias", a, b, bias, out, m, k, n)
+
+
+def matmul_bias_tiled(a, b, bias, out, m, k, n, tile):
+    return _build("vyb_math_matmul_bias_tiled", a, b, bias, out, m, k, n, tile)
+
+
+def linear(x, w, b, out, in_dim, out_dim):
+    """vyre_libs::nn::linear: u32 `out[i] = sum_k x[k] * w[k, i] + b[i]` (tiled form from in_dim * out_dim >= 1024)."""
+    return _build("vyb_nn_linear", x, w, b, out, in_dim, out_dim)
+
+
+def linear_tiled(x, w, b, out, in_dim, out_dim, tile):
+    return _build("vyb_nn_linear_tiled", x, w, b, out, in_dim, out_dim, tile)
+
+
 def moe_gate(input_scores, output_indices, output_weights, num_experts, k):
     return _build("vyb_nn_moe_gate", input_scores, output_indices, output_weights, num_experts, k)
 

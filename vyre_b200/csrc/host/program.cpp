@@ -663,25 +663,108 @@ int32_t vyb_nn_linear_rows_no_bias_out_in_typed(const char* x, const char* w, co
     return linear_rows_impl(x, w, nullptr, out, rows, in_dim, out_dim, dtype, true, program);
 }
 
-// ---- Matmul (matmul.rs:17-60): u32 wrapping ---------------------------------------------------------------------
-int32_t vyb_math_matmul(const char* a, const char* b, const char* out, uint32_t m, uint32_t k, uint32_t n,
-                        vyb_program** program) {
-    VYB_REQUIRE_NAMES(a, b, out);
-    if (m == 0 || k == 0 || n == 0)
-        return fail_invalid_program("Fix: matmul requires nonzero m, k and n.");
-    uint32_t ac, bc, oc;
-    if (!checked_mul(m, k, &ac) || !checked_mul(k, n, &bc) || !checked_mul(m, n, &oc))
-        return fail_invalid_program("Fix: matmul element counts overflow u32; shard the product.");
+// ---- Matmul / MatmulBias (matmul.rs:17-136, 138-271) and nn::linear over them: u32 wrapping ----------------------
+namespace {
+// matmul_tiled/program.rs:105-200 for the cooperative (non-MMA) path, which is the one a U32 product takes: the
+// default [16, 16, 1] workgroup gives 16 x 16 output tiles on 256 flat lanes, two workgroup tiles of tile x 16 values,
+// and an output padded to whole tiles with the logical bytes as its readback range.
+int32_t tiled_matmul_program(const char* op_id, const char* a, const char* b, const char* bias, const char* out,
+                             uint32_t m, uint32_t k, uint32_t n, uint32_t tile, vyb_program** program) {
+    uint32_t ac, bc, oc, a_tile, b_tile, tiles, padded;
+    if (!checked_mul(m, k, &ac) || !checked_mul(k, n, &bc) || !checked_mul(m, n, &oc) || !checked_mul(16, tile, &a_tile) ||
+        !checked_mul(tile, 16, &b_tile) || !checked_mul(div_ceil(m, 16), div_ceil(n, 16), &tiles) ||
+        !checked_mul(tiles, 256, &padded))
+        return fail_invalid_program(std::string("Fix: ") + op_id + " element counts overflow u32; shard the product.");
     Program p;
-    p.op_id = "vyre-libs::math::matmul";
+    p.op_id = op_id;
     p.kind = OpKind::MatmulU32;
     p.workgroup = {256, 1, 1};
     p.params.u[0] = m;
     p.params.u[1] = k;
     p.params.u[2] = n;
-    p.buffers = {storage(a, 0, VYB_ACCESS_READ_ONLY, VYB_DT_U32, ac),
-                 storage(b, 1, VYB_ACCESS_READ_ONLY, VYB_DT_U32, bc), output(out, 2, VYB_DT_U32, oc)};
+    p.params.u[3] = bias ? 1 : 0;
+    p.params.u[4] = tile;
+    p.buffers = {storage(a, 0, VYB_ACCESS_READ_ONLY, VYB_DT_U32, ac), storage(b, 1, VYB_ACCESS_READ_ONLY, VYB_DT_U32, bc)};
+    if (bias) p.buffers.push_back(storage(bias, 2, VYB_ACCESS_READ_ONLY, VYB_DT_U32, n));
+    p.buffers.push_back(workgroup("matmul_a_tile", a_tile, VYB_DT_U32));
+    p.buffers.push_back(workgroup("matmul_b_tile", b_tile, VYB_DT_U32));
+    BufferDecl o = output(out, bias ? 3 : 2, VYB_DT_U32, padded);
+    o.has_output_byte_range = true;
+    o.output_byte_begin = 0;
+    o.output_byte_end = uint64_t(oc) * 4;
+    p.buffers.push_back(o);
     return emit(program, std::move(p));
+}
+
+int32_t flat_matmul_program(const char* op_id, const char* a, const char* b, const char* bias, const char* out, uint32_t m,
+                            uint32_t k, uint32_t n, vyb_program** program) {
+    uint32_t ac, bc, oc;
+    if (!checked_mul(m, k, &ac) || !checked_mul(k, n, &bc) || !checked_mul(m, n, &oc))
+        return fail_invalid_program(std::string("Fix: ") + op_id + " element counts overflow u32; shard the product.");
+    Program p;
+    p.op_id = op_id;
+    p.kind = OpKind::MatmulU32;
+    p.workgroup = {256, 1, 1};
+    p.params.u[0] = m;
+    p.params.u[1] = k;
+    p.params.u[2] = n;
+    p.params.u[3] = bias ? 1 : 0;
+    p.buffers = {storage(a, 0, VYB_ACCESS_READ_ONLY, VYB_DT_U32, ac), storage(b, 1, VYB_ACCESS_READ_ONLY, VYB_DT_U32, bc)};
+    if (bias) p.buffers.push_back(storage(bias, 2, VYB_ACCESS_READ_ONLY, VYB_DT_U32, n));
+    p.buffers.push_back(output(out, bias ? 3 : 2, VYB_DT_U32, oc));
+    return emit(program, std::move(p));
+}
+}  // namespace
+
+int32_t vyb_math_matmul(const char* a, const char* b, const char* out, uint32_t m, uint32_t k, uint32_t n,
+                        vyb_program** program) {
+    VYB_REQUIRE_NAMES(a, b, out);
+    if (m == 0 || k == 0 || n == 0)
+        return fail_invalid_program("Fix: matmul requires nonzero m, k and n.");
+    return flat_matmul_program("vyre-libs::math::matmul", a, b, nullptr, out, m, k, n, program);
+}
+
+int32_t vyb_math_matmul_bias(const char* a, const char* b, const char* bias, const char* out, uint32_t m, uint32_t k,
+                             uint32_t n, vyb_program** program) {
+    VYB_REQUIRE_NAMES(a, b, bias, out);
+    if (m == 0 || k == 0 || n == 0)
+        return fail_invalid_program("Fix: matmul_bias requires nonzero m, k and n.");
+    return flat_matmul_program("vyre-libs::math::matmul_bias", a, b, bias, out, m, k, n, program);
+}
+
+int32_t vyb_math_matmul_bias_tiled(const char* a, const char* b, const char* bias, const char* out, uint32_t m, uint32_t k,
+                                   uint32_t n, uint32_t tile, vyb_program** program) {
+    VYB_REQUIRE_NAMES(a, b, bias, out);
+    if (m == 0 || k == 0 || n == 0 || tile == 0)
+        return fail_invalid_program("Fix: matmul_bias_tiled requires nonzero m, k, n and tile.");
+    return tiled_matmul_program("vyre-libs::math::matmul_bias_tiled", a, b, bias, out, m, k, n, tile, program);
+}
+
+// nn::linear (vyre-libs/src/nn/linear/inner/builder.rs:139-162): out[i] = sum_k x[k] * w[k, i] + b[i]; from
+// in_dim * out_dim >= 1024 on the builder hands over to linear_tiled with tile 32 (tiled.rs:13-50)
+int32_t vyb_nn_linear_tiled(const char* x, const char* w, const char* b, const char* out, uint32_t in_dim, uint32_t out_dim,
+                            uint32_t tile, vyb_program** program) {
+    VYB_REQUIRE_NAMES(x, w, b, out);
+    if (in_dim == 0) return fail_invalid_program("Fix: linear_tiled in_dim=0 is invalid: empty reduction");
+    if (out_dim == 0) return fail_invalid_program("Fix: linear_tiled out_dim=0 is invalid: empty output");
+    if (tile == 0) return fail_invalid_program("Fix: linear_tiled tile=0 is invalid: tile width must be > 0");
+    uint32_t work;
+    if (!checked_mul(in_dim, out_dim, &work))
+        return fail_invalid_program("Fix: linear_tiled in_dim*out_dim overflows u32; reduce dimensions.");
+    return tiled_matmul_program("vyre-libs::nn::linear_tiled", x, w, b, out, 1, in_dim, out_dim, tile, program);
+}
+
+int32_t vyb_nn_linear(const char* x, const char* w, const char* b, const char* out, uint32_t in_dim, uint32_t out_dim,
+                      vyb_program** program) {
+    VYB_REQUIRE_NAMES(x, w, b, out);
+    uint32_t work;
+    if (checked_mul(in_dim, out_dim, &work) && work >= 1024)
+        return vyb_nn_linear_tiled(x, w, b, out, in_dim, out_dim, 32, program);
+    if (in_dim == 0 || out_dim == 0)
+        return fail_invalid_program("Fix: vyre-libs::nn::linear build failed: x and out need at least one element each.");
+    if (!checked_mul(in_dim, out_dim, &work))
+        return fail_invalid_program("Fix: linear in_dim*out_dim overflows u32; reduce dimensions.");
+    return flat_matmul_program("vyre-libs::nn::linear", x, w, b, out, 1, in_dim, out_dim, program);
 }
 
 // ---- MoE (gating.rs:19-69, softmax_top_k.rs:25-101, top_k.rs:18-60) -----------------------------------------------
@@ -1054,6 +1137,35 @@ int32_t vyb_program_from_op(const char* op_id, const vyb_buffer_decl* decls, uin
         const uint64_t rows = count(1);
         if (!rows || n % rows) return bad_shape("packed values are not rows x cols");
         rc = vyb_quant_int8_unpack(name(0), name(1), name(2), uint32_t(n), uint32_t(op_spec && n_spec >= 2 ? op_spec[1] : n / rows), &out);
+    } else if (id == "vyre-libs::math::matmul" || id == "vyre-libs::math::matmul_bias") {
+        // a=0, b=1, [bias=2,] out=last (matmul.rs:120-131, 252-268); spec = [m, k, n] (m cannot be recovered from the
+        // counts alone unless bias gives n)
+        const bool bias = id.back() == 's';
+        if (!need(bias ? 4 : 3)) return bad_shape(bias ? "four buffers a, b, bias, out expected" : "three buffers a, b, out expected");
+        uint64_t m, k, n;
+        if (op_spec && n_spec >= 3) {
+            m = op_spec[0]; k = op_spec[1]; n = op_spec[2];
+        } else if (bias) {
+            n = count(2);
+            if (!n || count(1) % n || count(3) % n) return bad_shape("b and out are not multiples of the bias length");
+            k = count(1) / n;
+            m = count(3) / n;
+        } else {
+            return bad_shape("matmul needs the op spec [m, k, n]: three counts m*k, k*n, m*n do not fix it uniquely");
+        }
+        rc = bias ? vyb_math_matmul_bias(name(0), name(1), name(2), name(3), uint32_t(m), uint32_t(k), uint32_t(n), &out)
+                  : vyb_math_matmul(name(0), name(1), name(2), uint32_t(m), uint32_t(k), uint32_t(n), &out);
+    } else if (id == "vyre-libs::nn::linear" || id == "vyre-libs::nn::linear_tiled") {
+        // x=0, w=1, b=2, out=3 (builder.rs:139-162, tiled.rs:20-50); spec = [in_dim, out_dim, tile]
+        if (!need(4)) return bad_shape("four buffers x, w, b, out expected");
+        const uint64_t in_dim = op_spec && n_spec >= 2 ? op_spec[0] : count(0);
+        const uint64_t out_dim = op_spec && n_spec >= 2 ? op_spec[1] : count(2);
+        if (id == "vyre-libs::nn::linear")
+            rc = flat_matmul_program("vyre-libs::nn::linear", name(0), name(1), name(2), name(3), 1, uint32_t(in_dim),
+                                     uint32_t(out_dim), &out);
+        else
+            rc = vyb_nn_linear_tiled(name(0), name(1), name(2), name(3), uint32_t(in_dim), uint32_t(out_dim),
+                                     op_spec && n_spec >= 3 ? op_spec[2] : 32u, &out);
     } else {
         return fail_unsupported("rebuilding a program for operator `" + id + "` from buffer declarations");
     }

@@ -294,8 +294,11 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             return launch_linear_rows(b[0], b[1], has_bias ? b[2] : nullptr, has_bias ? b[3] : b[2], u[0], u[1], u[2],
                                       rt_dtype(u[3]), u[4], s);
         }
-        case OpKind::MatmulU32:
-            return launch_matmul_u32((const uint32_t*)b[0], (const uint32_t*)b[1], (uint32_t*)b[2], u[0], u[1], u[2], s);
+        case OpKind::MatmulU32: {  // u[3]: bias bound at slot 2, output at slot 3
+            const bool has_bias = u[3] != 0;
+            return launch_matmul_u32((const uint32_t*)b[0], (const uint32_t*)b[1], has_bias ? (const uint32_t*)b[2] : nullptr,
+                                     (uint32_t*)(has_bias ? b[3] : b[2]), u[0], u[1], u[2], s);
+        }
         case OpKind::MoeGate: return launch_moe_gate((const float*)b[0], (uint32_t*)b[1], (float*)b[2], u[2], u[0], u[1], s);
         case OpKind::SoftmaxTopK:
             return launch_softmax_top_k((const float*)b[0], (uint32_t*)b[1], (float*)b[2], (float*)b[3], (uint32_t*)b[4],

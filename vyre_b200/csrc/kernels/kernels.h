@@ -154,8 +154,8 @@ cudaError_t launch_i4_matvec_fast(const uint32_t* w, const float* x, const float
 // dtype: 0 = f32, 1 = bf16, 2 = f16
 cudaError_t launch_linear_rows(const void* x, const void* w, const void* bias, void* out, uint32_t rows,
                                uint32_t in_dim, uint32_t out_dim, uint32_t dtype, uint32_t out_in, cudaStream_t s);
-cudaError_t launch_matmul_u32(const uint32_t* a, const uint32_t* b, uint32_t* out, uint32_t m, uint32_t k, uint32_t n,
-                              cudaStream_t s);
+cudaError_t launch_matmul_u32(const uint32_t* a, const uint32_t* b, const uint32_t* bias, uint32_t* out, uint32_t m,
+                              uint32_t k, uint32_t n, cudaStream_t s);
 cudaError_t launch_moe_gate(const float* scores, uint32_t* idx, float* weights, uint32_t tokens, uint32_t experts,
                             uint32_t k, cudaStream_t s);
 cudaError_t launch_softmax_top_k(const float* scores, uint32_t* out_idx, float* out_w, float* best_vals,

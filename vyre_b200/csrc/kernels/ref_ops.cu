@@ -165,15 +165,39 @@ __global__ void linear_rows_kernel(const void* x, const void* w, const void* bia
     store_typed(out, index, dt, acc);
 }
 
-// vyre-libs/src/math/linalg/matmul.rs:17-60
-__global__ void matmul_u32_kernel(const uint32_t* a, const uint32_t* b, uint32_t* out, uint32_t m, uint32_t k,
-                                  uint32_t n) {
-    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= m * n) return;
-    const uint32_t i = idx / n, j = idx % n;
-    uint32_t acc = 0;
-    for (uint32_t kk = 0; kk < k; ++kk) acc += a[size_t(i) * k + kk] * b[size_t(kk) * n + j];
-    out[idx] = acc;
+// vyre-libs/src/math/linalg/matmul.rs:17-60 (matmul), :138-271,330-380 (matmul_bias: out = acc + bias[col]); the same
+// result serves nn::linear (m = 1; vyre-libs/src/nn/linear/inner/builder.rs:363-391) and the tiled forms
+// (matmul_tiled/program.rs). u32 arithmetic wraps, so every summation order gives the same bits: 32x32 output tiles,
+// operands staged in shared memory 32 k at a time.
+__global__ void __launch_bounds__(256) matmul_u32_kernel(const uint32_t* __restrict__ a, const uint32_t* __restrict__ b,
+                                                         const uint32_t* __restrict__ bias, uint32_t* __restrict__ out,
+                                                         uint32_t m, uint32_t k, uint32_t n) {
+    __shared__ uint32_t as[32][33], bs[32][33];
+    const uint32_t tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 8 row groups x 32 columns; 4 rows per thread
+    const uint32_t row0 = blockIdx.y * 32, col0 = blockIdx.x * 32;
+    uint32_t acc[4] = {0, 0, 0, 0};
+    for (uint32_t k0 = 0; k0 < k; k0 += 32) {
+        for (uint32_t r = ty; r < 32; r += 8) {
+            as[r][tx] = (row0 + r < m && k0 + tx < k) ? a[size_t(row0 + r) * k + k0 + tx] : 0u;
+            bs[r][tx] = (k0 + r < k && col0 + tx < n) ? b[size_t(k0 + r) * n + col0 + tx] : 0u;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (uint32_t kk = 0; kk < 32; ++kk) {
+            const uint32_t bv = bs[kk][tx];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[r] += as[ty + 8 * r][kk] * bv;
+        }
+        __syncthreads();
+    }
+    const uint32_t col = col0 + tx;
+    if (col >= n) return;
+    const uint32_t bv = bias ? bias[col] : 0u;
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const uint32_t row = row0 + ty + 8 * r;
+        if (row < m) out[size_t(row) * n + col] = acc[r] + bv;
+    }
 }
 
 // vyre-libs/src/nn/moe/gating.rs:71-147; one thread per token, experts staged in shared memory
@@ -353,9 +377,11 @@ cudaError_t launch_linear_rows(const void* x, const void* w, const void* bias, v
                                                                            dtype, out_in);
     return cudaGetLastError();
 }
-cudaError_t launch_matmul_u32(const uint32_t* a, const uint32_t* b, uint32_t* out, uint32_t m, uint32_t k, uint32_t n,
-                              cudaStream_t s) {
-    matmul_u32_kernel<<<blocks(uint64_t(m) * n, 256), 256, 0, s>>>(a, b, out, m, k, n);
+cudaError_t launch_matmul_u32(const uint32_t* a, const uint32_t* b, const uint32_t* bias, uint32_t* out, uint32_t m,
+                              uint32_t k, uint32_t n, cudaStream_t s) {
+    const uint32_t gy = (m + 31) / 32;
+    if (gy > 65535u) return cudaErrorInvalidValue;
+    matmul_u32_kernel<<<dim3((n + 31) / 32, gy), 256, 0, s>>>(a, b, bias, out, m, k, n);
     return cudaGetLastError();
 }
 cudaError_t launch_moe_gate(const float* scores, uint32_t* idx, float* weights, uint32_t tokens, uint32_t experts,

@@ -139,6 +139,10 @@ _STATUS_FUNCS = {
     "vyb_nn_linear_rows_no_bias_typed": [_S] * 3 + [_U] * 4 + [_PP],
     "vyb_nn_linear_rows_no_bias_out_in_typed": [_S] * 3 + [_U] * 4 + [_PP],
     "vyb_math_matmul": [_S] * 3 + [_U] * 3 + [_PP],
+    "vyb_math_matmul_bias": [_S] * 4 + [_U] * 3 + [_PP],
+    "vyb_math_matmul_bias_tiled": [_S] * 4 + [_U] * 4 + [_PP],
+    "vyb_nn_linear": [_S] * 4 + [_U] * 2 + [_PP],
+    "vyb_nn_linear_tiled": [_S] * 4 + [_U] * 3 + [_PP],
     "vyb_nn_moe_gate": [_S] * 3 + [_U, _U, _PP],
     "vyb_nn_softmax_top_k": [_S] * 3 + [_U, _U, _PP],
     "vyb_nn_top_k": [_S, _S, _U, _U, _PP],
