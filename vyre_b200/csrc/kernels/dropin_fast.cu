@@ -27,98 +27,150 @@
 namespace vybk {
 namespace {
 
-constexpr int BT = 8;        // batch rows per block
-constexpr int KCHUNK = 256;  // activations staged per step: BT x KCHUNK floats = 8 KB
+constexpr int MV_BT = 8;     // batch rows per block of the matvec kernel
 
-// block (TX outputs, KS k-slices); grid (ceil(N / TX), ceil(B / BT))
-template <int TX, int KS>
+// Block: TX x KS threads. Thread (tx, ty) owns OT outputs (i = block base + tx + o * TX: for a fixed o a warp reads 128
+// contiguous bytes of one k-block row of W) and the ty-th run of consecutive words of every KCHUNK-deep chunk of k.
+// BT batch rows share every dequantised weight; BT * KCHUNK activations (16 KB) are staged per chunk, so few batch rows
+// mean deep chunks and many weight words in flight per thread. The words of the NEXT chunk are loaded into registers
+// before this chunk's barrier, so the global loads overlap the staging of x and the arithmetic.
+// grid (ceil(N / (TX * OT)), ceil(B / BT)).
+template <int TX, int OT, int KS, int BT, int KCHUNK>
 __global__ void __launch_bounds__(TX* KS) affine_grouped_fast_kernel(const float* __restrict__ x, const uint32_t* __restrict__ w,
                                                                       const float* __restrict__ scale,
                                                                       const uint32_t* __restrict__ zp,
                                                                       const float* __restrict__ bias, float* __restrict__ out,
                                                                       uint32_t in_dim, uint32_t out_dim, uint32_t group,
-                                                                      uint32_t batch) {
-    __shared__ __align__(16) float xs[BT][KCHUNK];
-    __shared__ float red[KS > 1 ? KS : 1][BT][TX];
+                                                                      int group_shift, uint32_t batch) {
+    constexpr int WPT = (KCHUNK / 8) / KS;
+    constexpr int XS = BT * KCHUNK, RED = KS * BT * OT * TX;
+    __shared__ __align__(16) float smem[XS > RED ? XS : RED];
+    float(*xs)[KCHUNK] = reinterpret_cast<float(*)[KCHUNK]>(smem);
     const uint32_t tx = threadIdx.x, ty = threadIdx.y;
-    const uint32_t i = blockIdx.x * TX + tx;
+    const uint32_t i0 = blockIdx.x * (TX * OT) + tx;
     const uint32_t b0 = blockIdx.y * BT;
     const uint32_t nb = min(uint32_t(BT), batch - b0);
-    const bool live = i < out_dim;
-    float acc[BT];
+    const uint32_t words = in_dim / 8;
+    float acc[BT][OT];
 #pragma unroll
-    for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
+    for (int b = 0; b < BT; ++b)
+#pragma unroll
+        for (int o = 0; o < OT; ++o) acc[b][o] = 0.0f;
+    uint32_t wcur[WPT][OT], wnext[WPT][OT];
+    auto fetch = [&](uint32_t (&dst)[WPT][OT], uint32_t k0) {
+#pragma unroll
+        for (int j = 0; j < WPT; ++j) {
+            const uint32_t kw = k0 / 8 + ty * WPT + j;
+#pragma unroll
+            for (int o = 0; o < OT; ++o) {
+                const uint32_t i = i0 + o * TX;
+                dst[j][o] = (kw < words && i < out_dim) ? __ldg(w + size_t(kw) * out_dim + i) : 0u;
+            }
+        }
+    };
+    fetch(wcur, 0);
     uint32_t cur_group = 0xFFFFFFFFu;
-    float s = 0.0f, zero_off = 0.0f;
+    float s[OT], zero_off[OT];
+#pragma unroll
+    for (int o = 0; o < OT; ++o) s[o] = zero_off[o] = 0.0f;
     for (uint32_t k0 = 0; k0 < in_dim; k0 += KCHUNK) {
         const uint32_t kc = min(uint32_t(KCHUNK), in_dim - k0);
+        fetch(wnext, k0 + KCHUNK);  // past the end: zeros, never used
         __syncthreads();
-        for (uint32_t e = ty * TX + tx; e < BT * KCHUNK; e += TX * KS) {
-            const uint32_t b = e / KCHUNK, k = e % KCHUNK;
-            xs[b][k] = (b < nb && k < kc) ? x[size_t(b0 + b) * in_dim + k0 + k] : 0.0f;
+        for (uint32_t e = ty * TX + tx; e < BT * (KCHUNK / 4); e += TX * KS) {  // float4 per thread; in_dim % 8 == 0
+            const uint32_t b = e / (KCHUNK / 4), k = (e % (KCHUNK / 4)) * 4;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (b < nb && k < kc) v = __ldg(reinterpret_cast<const float4*>(x + size_t(b0 + b) * in_dim + k0 + k));
+            *reinterpret_cast<float4*>(&xs[b][k]) = v;
         }
         __syncthreads();
-        if (!live) continue;
-        // the chunk's words are dealt to the k-slices round robin
-        for (uint32_t wi = ty; wi < kc / 8; wi += KS) {
-            const uint32_t k = k0 + wi * 8;
-            const uint32_t word = w[size_t(k >> 3) * out_dim + i];
-            const uint32_t g = k / group;
-            if (g != cur_group) {  // in_dim % 8 == 0 and the builder requires group % 8 == 0 here: a word never straddles groups
-                cur_group = g;
-                s = scale[size_t(g) * out_dim + i];
-                zero_off = __fmaf_rn(float(zp[size_t(g) * out_dim + i]), __fmaf_rn(-1.0f, s, -0.0f), -0.0f);
-            }
-            float wv[8];
 #pragma unroll
-            for (int n = 0; n < 8; ++n) wv[n] = __fmaf_rn(float((word >> (4 * n)) & 0xFu), s, zero_off);
+        for (int j = 0; j < WPT; ++j) {
+            const uint32_t wi = ty * WPT + j;  // same for the whole warp
+            if (wi * 8 < kc) {
+                const uint32_t k = k0 + wi * 8;
+                const uint32_t g = group_shift >= 0 ? (k >> group_shift) : k / group;
+                if (g != cur_group) {  // group % 8 == 0: a word never straddles two groups
+                    cur_group = g;
 #pragma unroll
-            for (int b = 0; b < BT; ++b) {
-                const float4 xa = *reinterpret_cast<const float4*>(&xs[b][wi * 8]);
-                const float4 xb = *reinterpret_cast<const float4*>(&xs[b][wi * 8 + 4]);
-                float a = acc[b];
-                a = __fmaf_rn(xa.x, wv[0], a);
-                a = __fmaf_rn(xa.y, wv[1], a);
-                a = __fmaf_rn(xa.z, wv[2], a);
-                a = __fmaf_rn(xa.w, wv[3], a);
-                a = __fmaf_rn(xb.x, wv[4], a);
-                a = __fmaf_rn(xb.y, wv[5], a);
-                a = __fmaf_rn(xb.z, wv[6], a);
-                a = __fmaf_rn(xb.w, wv[7], a);
-                acc[b] = a;
+                    for (int o = 0; o < OT; ++o) {
+                        const uint32_t i = min(i0 + o * TX, out_dim - 1);
+                        s[o] = scale[size_t(g) * out_dim + i];
+                        zero_off[o] = __fmaf_rn(float(zp[size_t(g) * out_dim + i]), __fmaf_rn(-1.0f, s[o], -0.0f), -0.0f);
+                    }
+                }
+                float wv[OT][8];
+#pragma unroll
+                for (int o = 0; o < OT; ++o) {
+                    const uint32_t lo = wcur[j][o] & 0x0F0F0F0Fu, hi = (wcur[j][o] >> 4) & 0x0F0F0F0Fu;  // nibbles 0,2,4,6 / 1,3,5,7
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) {
+                        // f32(nibble) without the conversion unit: 0x4B0000nn is 2^23 + nn, and the subtraction is exact
+                        const float even = __fsub_rn(__uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7540 + n)), 8388608.0f);
+                        const float odd = __fsub_rn(__uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7540 + n)), 8388608.0f);
+                        wv[o][2 * n] = __fmaf_rn(even, s[o], zero_off[o]);
+                        wv[o][2 * n + 1] = __fmaf_rn(odd, s[o], zero_off[o]);
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    const float4 xa = *reinterpret_cast<const float4*>(&xs[b][wi * 8]);
+                    const float4 xb = *reinterpret_cast<const float4*>(&xs[b][wi * 8 + 4]);
+#pragma unroll
+                    for (int o = 0; o < OT; ++o) {
+                        float a = acc[b][o];
+                        a = __fmaf_rn(xa.x, wv[o][0], a);
+                        a = __fmaf_rn(xa.y, wv[o][1], a);
+                        a = __fmaf_rn(xa.z, wv[o][2], a);
+                        a = __fmaf_rn(xa.w, wv[o][3], a);
+                        a = __fmaf_rn(xb.x, wv[o][4], a);
+                        a = __fmaf_rn(xb.y, wv[o][5], a);
+                        a = __fmaf_rn(xb.z, wv[o][6], a);
+                        a = __fmaf_rn(xb.w, wv[o][7], a);
+                        acc[b][o] = a;
+                    }
+                }
             }
+        }
+#pragma unroll
+        for (int j = 0; j < WPT; ++j)
+#pragma unroll
+            for (int o = 0; o < OT; ++o) wcur[j][o] = wnext[j][o];
+    }
+    // fold the k-slices in a fixed order (deterministic), every thread takes its share of the batch rows
+    __syncthreads();
+    float* red = smem;  // [KS][BT][OT * TX]
+#pragma unroll
+    for (int b = 0; b < BT; ++b)
+#pragma unroll
+        for (int o = 0; o < OT; ++o) red[(ty * BT + b) * (OT * TX) + o * TX + tx] = acc[b][o];
+    __syncthreads();
+    for (uint32_t b = ty; b < nb; b += KS) {
+#pragma unroll
+        for (int o = 0; o < OT; ++o) {
+            const uint32_t i = i0 + o * TX;
+            if (i >= out_dim) continue;
+            float v = red[b * (OT * TX) + o * TX + tx];
+#pragma unroll
+            for (int y = 1; y < KS; ++y) v += red[(y * BT + b) * (OT * TX) + o * TX + tx];
+            out[size_t(b0 + b) * out_dim + i] = bias[i] + v;
         }
     }
-    if (KS > 1) {
-#pragma unroll
-        for (int b = 0; b < BT; ++b) red[ty][b][tx] = acc[b];
-        __syncthreads();
-        if (ty != 0) return;
-#pragma unroll
-        for (int b = 0; b < BT; ++b) {
-            float v = red[0][b][tx];
-            for (int y = 1; y < KS; ++y) v += red[y][b][tx];  // fixed order: deterministic
-            acc[b] = v;
-        }
-    }
-    if (!live) return;
-    const float bi = bias[i];
-    for (uint32_t b = 0; b < nb; ++b) out[size_t(b0 + b) * out_dim + i] = bi + acc[b];
 }
 
-// one warp per row, 8 rows per block; grid (ceil(rows / 8), ceil(batch / BT))
+// one warp per row, 8 rows per block; grid (ceil(rows / 8), ceil(batch / MV_BT))
 __global__ void __launch_bounds__(256) i4_matvec_fast_kernel(const uint32_t* __restrict__ w, const float* __restrict__ x,
                                                              const float* __restrict__ scales, float* __restrict__ out,
                                                              uint32_t batch, uint32_t rows, uint32_t cols) {
     const uint32_t row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    const uint32_t b0 = blockIdx.y * BT;
-    const uint32_t nb = min(uint32_t(BT), batch - b0);
+    const uint32_t b0 = blockIdx.y * MV_BT;
+    const uint32_t nb = min(uint32_t(MV_BT), batch - b0);
     if (row >= rows) return;
     const uint32_t wpr = (cols + 7) / 8;
     const uint32_t* wr = w + size_t(row) * wpr;
-    float acc[BT];
+    float acc[MV_BT];
 #pragma unroll
-    for (int b = 0; b < BT; ++b) acc[b] = 0.0f;
+    for (int b = 0; b < MV_BT; ++b) acc[b] = 0.0f;
     for (uint32_t wi = lane; wi < wpr; wi += 32) {
         const uint32_t word = wr[wi];
         const uint32_t c0 = wi * 8;
@@ -127,7 +179,7 @@ __global__ void __launch_bounds__(256) i4_matvec_fast_kernel(const uint32_t* __r
         for (int n = 0; n < 8; ++n) wv[n] = float(int32_t(word << (28 - 4 * n)) >> 28);  // signed nibble
         if (c0 + 8 <= cols && (cols & 3u) == 0) {
 #pragma unroll
-            for (int b = 0; b < BT; ++b) {
+            for (int b = 0; b < MV_BT; ++b) {
                 if (uint32_t(b) < nb) {
                     const float4 xa = __ldg(reinterpret_cast<const float4*>(x + size_t(b0 + b) * cols + c0));
                     const float4 xb = __ldg(reinterpret_cast<const float4*>(x + size_t(b0 + b) * cols + c0 + 4));
@@ -151,7 +203,7 @@ __global__ void __launch_bounds__(256) i4_matvec_fast_kernel(const uint32_t* __r
     }
     const float sc = scales[row];
 #pragma unroll
-    for (int b = 0; b < BT; ++b) {
+    for (int b = 0; b < MV_BT; ++b) {
         float v = acc[b];
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
         if (lane == 0 && uint32_t(b) < nb) out[size_t(b0 + b) * rows + row] = v * sc;
@@ -168,24 +220,36 @@ bool i4_matvec_fast_supported(uint32_t batch, uint32_t rows, uint32_t cols) {
     return uint64_t(batch) * rows * cols >= (1ull << 22);
 }
 
+namespace {
+template <int TX, int OT, int KS, int BT, int KCHUNK>
+cudaError_t launch_affine_cfg(const float* x, const uint32_t* w, const float* scale, const uint32_t* zp, const float* b, float* out,
+                              uint32_t in_dim, uint32_t out_dim, uint32_t group, uint32_t batch, cudaStream_t s) {
+    const int shift = (group & (group - 1)) == 0 ? __builtin_ctz(group) : -1;
+    const dim3 grid((out_dim + TX * OT - 1) / (TX * OT), (batch + BT - 1) / BT);
+    if (grid.y > 65535u) return cudaErrorInvalidValue;
+    affine_grouped_fast_kernel<TX, OT, KS, BT, KCHUNK><<<grid, dim3(TX, KS), 0, s>>>(x, w, scale, zp, b, out, in_dim, out_dim, group, shift, batch);
+    return cudaGetLastError();
+}
+}  // namespace
+
 cudaError_t launch_affine_grouped_fast(const float* x, const uint32_t* w, const float* scale, const uint32_t* zp,
                                        const float* b, float* out, uint32_t in_dim, uint32_t out_dim, uint32_t group,
                                        uint32_t batch, int sm_count, cudaStream_t s) {
-    const uint32_t by = (batch + BT - 1) / BT;
-    // enough blocks of 128 outputs to fill the GPU twice over: no k split; else 64 outputs x 16 k-slices
-    if (uint64_t((out_dim + 127) / 128) * by >= uint64_t(2 * sm_count)) {
-        affine_grouped_fast_kernel<128, 2><<<dim3((out_dim + 127) / 128, by), dim3(128, 2), 0, s>>>(x, w, scale, zp, b, out, in_dim,
-                                                                                                     out_dim, group, batch);
-    } else {
-        affine_grouped_fast_kernel<64, 16><<<dim3((out_dim + 63) / 64, by), dim3(64, 16), 0, s>>>(x, w, scale, zp, b, out, in_dim,
-                                                                                                   out_dim, group, batch);
-    }
-    return cudaGetLastError();
+    // batch rows per block: every row beyond the batch is wasted arithmetic, every row within it reuses the dequantised weight
+    const int bt = batch >= 12 ? 16 : batch >= 3 ? 8 : 2;
+    // 128 outputs per block (two per thread) when that still gives every SM a block, else 32 outputs and a deeper k split
+    const bool wide = uint64_t((out_dim + 127) / 128) * ((batch + bt - 1) / bt) >= uint64_t(sm_count);
+#define VYB_AFFINE(TX, OT, KS, BT, KC) \
+    launch_affine_cfg<TX, OT, KS, BT, KC>(x, w, scale, zp, b, out, in_dim, out_dim, group, batch, s)
+    if (bt == 2) return VYB_AFFINE(32, 1, 8, 2, 2048);  // 32 words (128 B) per thread and chunk in flight, twice over
+    if (wide) return bt == 16 ? VYB_AFFINE(64, 2, 4, 16, 256) : VYB_AFFINE(64, 2, 4, 8, 512);
+    return bt == 16 ? VYB_AFFINE(32, 1, 8, 16, 256) : VYB_AFFINE(32, 1, 8, 8, 512);
+#undef VYB_AFFINE
 }
 
 cudaError_t launch_i4_matvec_fast(const uint32_t* w, const float* x, const float* scales, float* out, uint32_t batch,
                                   uint32_t rows, uint32_t cols, cudaStream_t s) {
-    i4_matvec_fast_kernel<<<dim3((rows + 7) / 8, (batch + BT - 1) / BT), 256, 0, s>>>(w, x, scales, out, batch, rows, cols);
+    i4_matvec_fast_kernel<<<dim3((rows + 7) / 8, (batch + MV_BT - 1) / MV_BT), 256, 0, s>>>(w, x, scales, out, batch, rows, cols);
     return cudaGetLastError();
 }
 
