@@ -60,6 +60,7 @@ constexpr int SMEM_W = STAGES * TILE_ROWS * 2048;             // weight stages o
 constexpr int SMEM_S = STAGES * TILE_ROWS * 64;               // their scales
 constexpr int SMEM_RED = 12288;                               // per-warp partial sums; the activation scratch of the prologue
 constexpr int SMEM_TOTAL = SMEM_W + SMEM_S + SMEM_RED;
+constexpr uint32_t PACE_NS = 400;
 
 static_assert(2 * (SMEM_TOTAL + 1024) <= 233472, "two CTAs must fit one SM");
 
@@ -92,6 +93,7 @@ struct Params {
     void* y;
     uint32_t m, n;
     uint32_t tiles_per_cta, tiles_rem;  // whole 16-row tiles per CTA; the first tiles_rem CTAs own one more
+    uint32_t pace_ns;                   // pause between the prefetched tiles (0: none)
 };
 
 // NM = MMAs per 16 rows x 32 k = ceil(m / 2); W warps, each owning GPW 128-k groups of every row: k = 128 GPW W
@@ -162,8 +164,15 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
         }
         cp_async_commit();
     };
+    // Weights are constants: prefetched before the dependency wait. Under programmatic dependent launch this CTA arrives
+    // on its SM just when its predecessor is about to be released and load its activations through the same load/store
+    // queue, so the prefetch is paced (about PACE_NS between tiles) rather than issued as one 96 KB burst that the
+    // predecessor's few activation loads would have to queue behind. This CTA has microseconds to spare here.
 #pragma unroll
-    for (int u = 0; u < STAGES; ++u) issue_tile();  // weights are constants: prefetched before the dependency wait
+    for (int u = 0; u < STAGES; ++u) {
+        if (u > 0 && p.pace_ns) __nanosleep(p.pace_ns);
+        issue_tile();
+    }
 
     const uint32_t g = lane >> 2;  // A/D fragment row, B fragment column
     const uint32_t t = lane & 3;
@@ -207,17 +216,39 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));  // 8 lanes = 1 group
             const int ebits = int(amax >> 23);  // biased exponent; 255 = Inf or NaN in the group
+            const int e = max(ebits - 127, -90);
+            const int de = e - 25;                                              // delta = 2^de, |x / delta| < 2^26
+            const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);  // 2^-de
+            float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);      // delta / 16
+            if (ebits == 255) delta16 = __uint_as_float(0x7FC00000u);  // Inf/NaN activations poison their group's outputs
+            // per packed byte i (elements 2i, 2i+1): operand 0 = 16 X0, operand 1 = X1 - 16 X0, each as four balanced
+            // base-256 digits at once: with Y = V + 0x808080 the low three bytes of Y, top bit flipped, are d0..d2 in
+            // [-128, 127] and the top byte of Y is d3. Also the sums of the low and high 16-bit parts of X.
+            uint32_t z0[8], z1[8];
+            int sum_lo = 0, sum_hi = 0;
+            bool small = false;  // some nonzero element was rounded: |x / delta| < 2^7 cannot hold its 8 significant bits
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int X0 = __float2int_rn(bf16_lo(r[i]) * inv_delta), X1 = __float2int_rn(bf16_hi(r[i]) * inv_delta);
+                if (NM == 1) small |= ((r[i] & 0x7FFFu) != 0 && abs(X0) < 128) | ((r[i] & 0x7FFF0000u) != 0 && abs(X1) < 128);
+                const int V0 = X0 << 4, V1 = X1 - V0;
+                z0[i] = uint32_t(V0 + 0x00808080) ^ 0x00808080u;
+                z1[i] = uint32_t(V1 + 0x00808080) ^ 0x00808080u;
+                const int Y0 = X0 + 0x8000, Y1 = X1 + 0x8000;  // X = (Y >> 16) * 65536 + ((Y & 0xFFFF) - 0x8000)
+                sum_hi += (Y0 >> 16) + (Y1 >> 16);
+                sum_lo += int(Y0 & 0xFFFF) + int(Y1 & 0xFFFF) - 0x10000;
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, o);
+                sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, o);
+            }
             if constexpr (NM == 1) {
                 // A single batch row has all eight B columns to itself. When some element of this warp's slice lies more
-                // than 2^18 below its group's largest (four digits would round it), the slice is converted with eight
-                // digits instead: |X| < 2^57, exact for every element within 2^-49 of the largest.
+                // than 2^18 below its group's largest (four digits have just rounded it: a nonzero bf16 whose integer
+                // image has fewer than its 8 significant bits), the slice is converted again with eight digits:
+                // |X| < 2^57, exact for every element within 2^-49 of the largest.
                 if (p.m == 1) {
-                    bool small = false;
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int e0 = int((r[i] >> 7) & 0xFFu), e1 = int((r[i] >> 23) & 0xFFu);
-                        small |= ((r[i] & 0x7FFFu) != 0 && e0 < ebits - 18) | ((r[i] & 0x7FFF0000u) != 0 && e1 < ebits - 18);
-                    }
                     if (__any_sync(0xffffffffu, small)) {
                         const int ew = max(ebits - 127, -60);
                         float delta16 = __uint_as_float(uint32_t(127 + ew - 60) << 23);  // delta / 16, delta = 2^(ew - 56)
@@ -302,31 +333,6 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
                     }
                 }
             }
-            const int e = max(ebits - 127, -90);
-            const int de = e - 25;                                              // delta = 2^de, |x / delta| < 2^26
-            const float inv_delta = __uint_as_float(uint32_t(127 - de) << 23);  // 2^-de
-            float delta16 = __uint_as_float(uint32_t(127 + de - 4) << 23);      // delta / 16
-            if (ebits == 255) delta16 = __uint_as_float(0x7FC00000u);  // Inf/NaN activations poison their group's outputs
-            // per packed byte i (elements 2i, 2i+1): operand 0 = 16 X0, operand 1 = X1 - 16 X0, each as four balanced
-            // base-256 digits at once: with Y = V + 0x808080 the low three bytes of Y, top bit flipped, are d0..d2 in
-            // [-128, 127] and the top byte of Y is d3. Also the sums of the low and high 16-bit parts of X.
-            uint32_t z0[8], z1[8];
-            int sum_lo = 0, sum_hi = 0;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int X0 = __float2int_rn(bf16_lo(r[i]) * inv_delta), X1 = __float2int_rn(bf16_hi(r[i]) * inv_delta);
-                const int V0 = X0 << 4, V1 = X1 - V0;
-                z0[i] = uint32_t(V0 + 0x00808080) ^ 0x00808080u;
-                z1[i] = uint32_t(V1 + 0x00808080) ^ 0x00808080u;
-                const int Y0 = X0 + 0x8000, Y1 = X1 + 0x8000;  // X = (Y >> 16) * 65536 + ((Y & 0xFFFF) - 0x8000)
-                sum_hi += (Y0 >> 16) + (Y1 >> 16);
-                sum_lo += int(Y0 & 0xFFFF) + int(Y1 & 0xFFFF) - 0x10000;
-            }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, o);
-                sum_hi += __shfl_xor_sync(0xffffffffu, sum_hi, o);
-            }
             // byte transpose: dig[d] = digit d of (operand 0 bytes 0-3, operand 0 bytes 4-7, operand 1 bytes 0-3, 4-7)
             uint32_t dig[4][4];
 #pragma unroll
@@ -402,6 +408,30 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
 
     uint32_t stage = 0, pending = 0;  // pending: tiles whose partials wait in shared memory
     float* part = reinterpret_cast<float*>(red + warp * PRIV) + g * MM + (t >> 1);
+    float Pq[NM][2];                  // the previous tile's per-lane partials, not yet summed across lanes
+    bool have_q = false;
+    // low and high digit pairs of a batch row sit in neighbouring lanes; a single batch row may use all four pairs
+    auto fold_partials = [&]() {
+        if (!have_q) return;
+        have_q = false;
+#pragma unroll
+        for (int nm = 0; nm < NM; ++nm) {
+            Pq[nm][0] += __shfl_xor_sync(0xffffffffu, Pq[nm][0], 1);
+            Pq[nm][1] += __shfl_xor_sync(0xffffffffu, Pq[nm][1], 1);
+        }
+        if (NM == 1 && p.m == 1) {
+            Pq[0][0] += __shfl_xor_sync(0xffffffffu, Pq[0][0], 2);
+            Pq[0][1] += __shfl_xor_sync(0xffffffffu, Pq[0][1], 2);
+        }
+        if ((t & 1) == 0 && !(NM == 1 && p.m == 1 && t != 0)) {
+#pragma unroll
+            for (int nm = 0; nm < NM; ++nm) {
+                part[pending * (PART / 4) + 2 * nm] = Pq[nm][0];
+                part[pending * (PART / 4) + 8 * MM + 2 * nm] = Pq[nm][1];
+            }
+        }
+        ++pending;
+    };
     for (uint32_t u = 0; u < ntiles; ++u) {
         cp_async_wait<STAGES - 1>();  // this thread's copies of tile u have landed ...
         __syncwarp();                 // ... and so have the other lanes'
@@ -428,64 +458,104 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
         // the whole slice of the tile sits in registers: refill the stage while the math runs
         __syncwarp();
         issue_tile();
+        fold_partials();  // of the previous tile
 
         float P[NM][2];
 #pragma unroll
         for (int nm = 0; nm < NM; ++nm) P[nm][0] = P[nm][1] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < GPW; ++c) {
-            int acc[NM][4];
-            const uint32_t lo[4] = {wl[c].x, wl[c].y, wl[c].z, wl[c].w};
-            const uint32_t hi[4] = {wh[c].x, wh[c].y, wh[c].z, wh[c].w};
+        if constexpr (NM == 1) {
+            // The four MMAs of a group form a dependent chain (about 25 cycles each), so the groups are interleaved: every
+            // step issues one MMA of each group, and a group's next MMA finds its accumulators ready.
+            int acc[GPW][NM][4];
 #pragma unroll
             for (int blk = 0; blk < 2; ++blk) {
-                // raw bytes against 16 X0, then masked bytes against X1 - 16 X0
-                const uint32_t a0 = lo[2 * blk], a1 = hi[2 * blk], a2 = lo[2 * blk + 1], a3 = hi[2 * blk + 1];
-                const uint32_t m0 = a0 & 0xF0F0F0F0u, m1 = a1 & 0xF0F0F0F0u, m2 = a2 & 0xF0F0F0F0u, m3 = a3 & 0xF0F0F0F0u;
+                // raw bytes against 16 X0 ...
 #pragma unroll
-                for (int nm = 0; nm < NM; ++nm) {
-                    if (blk == 0)  // the group's accumulators start from the zero-point term (all of it in the low digit)
-                        mma_u8s8(acc[nm], a0, a1, a2, a3, xb[nm][c][0], xb[nm][c][1], corr[nm][c], 0, corr[nm][c], 0);
-                    else
-                        mma_u8s8(acc[nm], a0, a1, a2, a3, xb[nm][c][4], xb[nm][c][5], acc[nm][0], acc[nm][1], acc[nm][2], acc[nm][3]);
-                    mma_u8s8(acc[nm], m0, m1, m2, m3, xb[nm][c][4 * blk + 2], xb[nm][c][4 * blk + 3], acc[nm][0], acc[nm][1],
-                             acc[nm][2], acc[nm][3]);
+                for (int c = 0; c < GPW; ++c) {
+                    const uint32_t a0 = blk ? wl[c].z : wl[c].x, a1 = blk ? wh[c].z : wh[c].x;
+                    const uint32_t a2 = blk ? wl[c].w : wl[c].y, a3 = blk ? wh[c].w : wh[c].y;
+#pragma unroll
+                    for (int nm = 0; nm < NM; ++nm) {
+                        if (blk == 0)  // the group's accumulators start from the zero-point term (all of it in the low digit)
+                            mma_u8s8(acc[c][nm], a0, a1, a2, a3, xb[nm][c][0], xb[nm][c][1], corr[nm][c], 0, corr[nm][c], 0);
+                        else
+                            mma_u8s8(acc[c][nm], a0, a1, a2, a3, xb[nm][c][4], xb[nm][c][5], acc[c][nm][0], acc[c][nm][1],
+                                     acc[c][nm][2], acc[c][nm][3]);
+                    }
+                }
+                // ... then masked bytes against X1 - 16 X0
+#pragma unroll
+                for (int c = 0; c < GPW; ++c) {
+                    const uint32_t m0 = (blk ? wl[c].z : wl[c].x) & 0xF0F0F0F0u, m1 = (blk ? wh[c].z : wh[c].x) & 0xF0F0F0F0u;
+                    const uint32_t m2 = (blk ? wl[c].w : wl[c].y) & 0xF0F0F0F0u, m3 = (blk ? wh[c].w : wh[c].y) & 0xF0F0F0F0u;
+#pragma unroll
+                    for (int nm = 0; nm < NM; ++nm)
+                        mma_u8s8(acc[c][nm], m0, m1, m2, m3, xb[nm][c][4 * blk + 2], xb[nm][c][4 * blk + 3], acc[c][nm][0],
+                                 acc[c][nm][1], acc[c][nm][2], acc[c][nm][3]);
                 }
             }
-            const float s_lo = (c & 1) ? bf16_hi(sa[c >> 1]) : bf16_lo(sa[c >> 1]);
-            const float s_hi = (c & 1) ? bf16_hi(sb[c >> 1]) : bf16_lo(sb[c >> 1]);
 #pragma unroll
-            for (int nm = 0; nm < NM; ++nm) {
-                // |accumulators| < 2^22 per group and |zero-point term| < 2^29: d_lo + 256 d_hi stays below 2^31
-                const float v_lo = float(acc[nm][0] + (acc[nm][1] << 8));
-                const float v_hi = float(acc[nm][2] + (acc[nm][3] << 8));
-                P[nm][0] = fmaf(s_lo * dq[nm][c], v_lo, P[nm][0]);
-                P[nm][1] = fmaf(s_hi * dq[nm][c], v_hi, P[nm][1]);
+            for (int c = 0; c < GPW; ++c) {
+                const float s_lo = (c & 1) ? bf16_hi(sa[c >> 1]) : bf16_lo(sa[c >> 1]);
+                const float s_hi = (c & 1) ? bf16_hi(sb[c >> 1]) : bf16_lo(sb[c >> 1]);
+#pragma unroll
+                for (int nm = 0; nm < NM; ++nm) {
+                    // |accumulators| < 2^22 per group and |zero-point term| < 2^29: d_lo + 256 d_hi stays below 2^31
+                    const float v_lo = float(acc[c][nm][0] + (acc[c][nm][1] << 8));
+                    const float v_hi = float(acc[c][nm][2] + (acc[c][nm][3] << 8));
+                    P[nm][0] = fmaf(s_lo * dq[nm][c], v_lo, P[nm][0]);
+                    P[nm][1] = fmaf(s_hi * dq[nm][c], v_hi, P[nm][1]);
+                }
+            }
+        } else {  // two MMAs per step already overlap; interleaving the groups as well costs registers this variant lacks
+#pragma unroll
+            for (int c = 0; c < GPW; ++c) {
+                int acc[NM][4];
+                const uint32_t lo[4] = {wl[c].x, wl[c].y, wl[c].z, wl[c].w};
+                const uint32_t hi[4] = {wh[c].x, wh[c].y, wh[c].z, wh[c].w};
+#pragma unroll
+                for (int blk = 0; blk < 2; ++blk) {
+                    // raw bytes against 16 X0, then masked bytes against X1 - 16 X0
+                    const uint32_t a0 = lo[2 * blk], a1 = hi[2 * blk], a2 = lo[2 * blk + 1], a3 = hi[2 * blk + 1];
+                    const uint32_t m0 = a0 & 0xF0F0F0F0u, m1 = a1 & 0xF0F0F0F0u, m2 = a2 & 0xF0F0F0F0u, m3 = a3 & 0xF0F0F0F0u;
+#pragma unroll
+                    for (int nm = 0; nm < NM; ++nm) {
+                        if (blk == 0)  // the group's accumulators start from the zero-point term (all of it in the low digit)
+                            mma_u8s8(acc[nm], a0, a1, a2, a3, xb[nm][c][0], xb[nm][c][1], corr[nm][c], 0, corr[nm][c], 0);
+                        else
+                            mma_u8s8(acc[nm], a0, a1, a2, a3, xb[nm][c][4], xb[nm][c][5], acc[nm][0], acc[nm][1], acc[nm][2], acc[nm][3]);
+                        mma_u8s8(acc[nm], m0, m1, m2, m3, xb[nm][c][4 * blk + 2], xb[nm][c][4 * blk + 3], acc[nm][0], acc[nm][1],
+                                 acc[nm][2], acc[nm][3]);
+                    }
+                }
+                const float s_lo = (c & 1) ? bf16_hi(sa[c >> 1]) : bf16_lo(sa[c >> 1]);
+                const float s_hi = (c & 1) ? bf16_hi(sb[c >> 1]) : bf16_lo(sb[c >> 1]);
+#pragma unroll
+                for (int nm = 0; nm < NM; ++nm) {
+                    // |accumulators| < 2^22 per group and |zero-point term| < 2^29: d_lo + 256 d_hi stays below 2^31
+                    const float v_lo = float(acc[nm][0] + (acc[nm][1] << 8));
+                    const float v_hi = float(acc[nm][2] + (acc[nm][3] << 8));
+                    P[nm][0] = fmaf(s_lo * dq[nm][c], v_lo, P[nm][0]);
+                    P[nm][1] = fmaf(s_hi * dq[nm][c], v_hi, P[nm][1]);
+                }
             }
         }
-        // low and high digit pairs of a batch row sit in neighbouring lanes; a single batch row may use all four pairs
+        // The cross-lane sum of this tile's partials (shuffles, each waiting for the one before) is left for the next
+        // iteration, where it runs under the latency of that tile's shared-memory loads.
 #pragma unroll
         for (int nm = 0; nm < NM; ++nm) {
-            P[nm][0] += __shfl_xor_sync(0xffffffffu, P[nm][0], 1);
-            P[nm][1] += __shfl_xor_sync(0xffffffffu, P[nm][1], 1);
+            Pq[nm][0] = P[nm][0];
+            Pq[nm][1] = P[nm][1];
         }
-        if (NM == 1 && p.m == 1) {
-            P[0][0] += __shfl_xor_sync(0xffffffffu, P[0][0], 2);
-            P[0][1] += __shfl_xor_sync(0xffffffffu, P[0][1], 2);
-        }
-        if ((t & 1) == 0 && !(NM == 1 && p.m == 1 && t != 0)) {
-#pragma unroll
-            for (int nm = 0; nm < NM; ++nm) {
-                part[pending * (PART / 4) + 2 * nm] = P[nm][0];
-                part[pending * (PART / 4) + 8 * MM + 2 * nm] = P[nm][1];
-            }
-        }
-        if (++pending == FLUSH && u + 1 < ntiles) {  // a CTA with many tiles: sum what has piled up and start over
+        have_q = true;
+        if (pending + 1 == FLUSH && u + 1 < ntiles) {  // a CTA with many tiles: sum what has piled up and start over
+            fold_partials();
             reduce_tiles(u + 1 - FLUSH, FLUSH);
             __syncthreads();
             pending = 0;
         }
     }
+    fold_partials();
     cp_async_wait<0>();
     if (pending) reduce_tiles(ntiles - pending, pending);
 }
@@ -528,6 +598,7 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     p.y = y;
     p.m = m;
     p.n = n;
+    p.pace_ns = constant_weights ? PACE_NS : 0u;
     (void)status;  // nothing in this kernel can time out
     // One CTA per SM, whole 16-row tiles each, the remainder spread one tile per CTA (14336 rows on 148 SMs: eight
     // CTAs with 7 tiles, the others with 6). Measured against 128 CTAs x 7 tiles and against two CTAs per SM (which
