@@ -9,14 +9,14 @@ every launch streams its weights from HBM. W warm-up steps, then exactly K timed
 stream, max over ranks.
 
 For N > 1 the linear is sharded column-parallel: every rank owns a [14336, 4096] shard of a 14336*N-row linear (weak
-scaling) and each launch's bf16 outputs are all-gathered by this library's own peer-store kernel over NVLink (one CTA
-per peer on a side stream, bounded completion checks), overlapped with the next GEMV and verified once against NCCL's
-all-gather before timing. The same run also measures, at every N, the two sharded configurations of the path and
+scaling) and each launch's bf16 outputs are all-gathered by the launch itself: the reduction that produces an output
+stores it into every rank's gather buffer (peer stores over NVLink, bounded completion checks), verified once against
+NCCL's all-gather before timing. The same run also measures, at every N, the two sharded configurations of the path and
 prints them under `secondary`: the expert-parallel MoE FFN layer (config 4, 4096 tokens in total, strong scaling) and
 the column-parallel int8 linear (config 5, N sharded over the ranks, peer-store gather of the int32 outputs).
 
 `--impl reference` times the reference bench's CPU loop (oracle/cpu_baseline.cpp) on all host cores over the same
-workload: a step is the same 8 GEMVs.
+workload: a step is the same 64 GEMVs.
 """
 from __future__ import annotations
 
@@ -562,14 +562,10 @@ def run_native(args) -> None:
     if world > 1:
         from vyre_b200 import sharding
 
-        pag = sharding.PeerAllGather(m, N_OUT)  # the all-gather is this library's peer-store kernel over NVLink, not NCCL
+        pag = sharding.PeerAllGather(m, N_OUT)  # the all-gather is this library's own, by peer stores over NVLink, not NCCL
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     stream = torch.cuda.Stream()
-    side = torch.cuda.Stream()
-    # with a concurrent push kernel the GEMV leaves one SM free: two GEMV launches (the running one and the next, which
-    # prefetches beside it) fill every SM they use, and the push CTAs (one per peer, 256 threads, no shared memory: all
-    # of them fit one SM) would otherwise wait for a GEMV CTA to leave
-    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS | (ffi.LAUNCH_LEAVE_ONE_SM if world > 1 else 0)
+    gemv_flags = ffi.LAUNCH_CONSTANT_WEIGHTS
 
     def launch(c: int, out=None, xin=None, mm=None):
         # weights are graph constants: the launch may overlap the tail of the previous one
@@ -594,22 +590,12 @@ def run_native(args) -> None:
             for c in range(LAUNCHES):
                 launch(c % COPIES)
             return
-        # GEMV c writes this rank's slice of buffer half c % 2; the push kernel on a side stream copies it to every peer
-        # and signals them while GEMV c+1 already runs; GEMV c+2 (same half) waits for it.
-        pushed = [None] * LAUNCHES
+        # GEMV c stores its outputs straight into buffer half c % 2 of every rank: GEMV and all-gather are one launch (peer
+        # stores over NVLink from the reduction that produces the outputs), the launches stay one programmatic chain, and
+        # the replay ends with the bounded wait for its own gathers
         for c in range(LAUNCHES):
-            half = c & 1
-            if c >= 2:
-                stream.wait_event(pushed[c - 2])
-            launch(c % COPIES, pag.local_slice(half))
-            ready = torch.cuda.Event()
-            ready.record(stream)
-            side.wait_event(ready)
-            pag.push(half, side.cuda_stream, status)
-            pushed[c] = torch.cuda.Event()
-            pushed[c].record(side)
-        stream.wait_stream(side)
-        pag.wait(stream.cuda_stream, status)  # the replay ends with the bounded wait for its own gathers
+            pag.gemv(c & 1, x, ws[c % COPIES], ss[c % COPIES], K_IN, stream.cuda_stream, status, gemv_flags)
+        pag.wait(stream.cuda_stream, status)
 
     graph = capture(step_body)
     with torch.cuda.stream(stream):
@@ -787,14 +773,14 @@ def run_native(args) -> None:
                          "(vyre-bench/src/cases/quantized_linear.rs:447-463 restated for the row-major layout), -O3, OpenMP over rows",
                "ms_per_gemv": round(med * 1e3, 3), "cpu_model": cpu_model()}
 
-    launches_per_step = LAUNCHES * (2 if world > 1 else 1) + (1 if world > 1 else 0)
+    launches_per_step = LAUNCHES + (1 if world > 1 else 0)
     line = {
         "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16xint4->f32", "data": "synthetic",
         "config": {"workload": workload_name(m)},
         "run": {"per_gpu_shard": [N_OUT, K_IN],
-                "parallelism": f"column-parallel x{world}" + (" + peer-store all-gather over NVLink on a side stream" if world > 1 else ""),
+                "parallelism": f"column-parallel x{world}" + (" + all-gather by peer stores from the GEMV's own reduction (NVLink), one launch" if world > 1 else ""),
                 "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
                 "launch": f"CUDA graph of {LAUNCHES} launches per step ({PASSES} passes over the {COPIES} copies), programmatic dependent launch (constant weights)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],

@@ -475,7 +475,10 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
  * gathered [world][m][n] must run, on every rank, before that rank's next push, after vyb_k_allgather_wait - which
  * waits (bounded, ~2 s, status bit 128) until every gather pushed so far by this rank is complete in local memory.
  * On a side stream the push overlaps the next GEMV; the caller orders it after the GEMV that wrote the slice and
- * before the GEMV that overwrites that half again.
+ * before the GEMV that overwrites that half again. The buffer may hold more than two such slots ([slots][world][m][n],
+ * `half` then is the slot index): a chain of GEMVs that each write a slot of their own needs no edge back from the
+ * pushes into the chain, so consecutive GEMVs keep their programmatic dependency (the push CTAs, 128 threads at no
+ * more than 32 registers, become resident beside the GEMV's).
  * peer_out / peer_flag: device addresses valid on THIS rank for every rank's buffer / 256 bytes of arrival counters
  * (own rank included); epoch: eight local 32-bit words. All counters zero before the first push. m * n a multiple of
  * 8. One CTA per peer copies, fences and signals, so a push costs the same at 2 and at 8 ranks. */
@@ -483,12 +486,25 @@ typedef struct vyb_allgather_ctx {
     uint32_t world, rank;
     uint64_t peer_out[8];
     uint64_t peer_flag[8];   /* 256 bytes of counters per rank: 32-bit word 8*s counts the pushes received from rank s */
-    uint64_t epoch;          /* 8 local 32-bit words */
+    uint64_t epoch;          /* 16 local 32-bit words, zero before the first launch */
     uint64_t wait_clocks;    /* clock limit of a device-side wait (status bit 128 when it runs out); 0 = about 2 s */
+    uint64_t slots;          /* slots of the gather buffer; 0 = the two halves. A push into slot s waits only until every peer
+                              * has completed all but the last slots - 2 of the pushes this rank has completed */
 } vyb_allgather_ctx;
 int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32_t m, uint32_t n, void* stream,
                              uint32_t* status);
 int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status);
+/* The decode GEMV of a column-parallel shard and its all-gather in ONE launch (no counterpart in the reference): the
+ * reduction that produces an output stores it, as bf16, into this rank's [m, n] slice of buffer half `half` on every
+ * rank (peer stores over NVLink; same buffers and counters as vyb_k_allgather_push). Consecutive launches stay one
+ * programmatic chain (VYB_LAUNCH_CONSTANT_WEIGHTS), nothing runs on a side stream, and no CTA fences at system scope:
+ * the arrival signal of a launch is sent by the next launch of this kind or by vyb_k_allgather_wait, which a stream
+ * must run before it reads a gathered result. Halves must alternate from launch to launch; before it overwrites a
+ * half on a peer a launch checks (bounded, status bit 128) that the peer has signalled its previous launch. epoch must
+ * point to 16 zeroed local words. 1 <= m <= 4, group 128, k 2048 or 4096. */
+int32_t vyb_k_int4_gemv_allgather(const vyb_allgather_ctx* ctx, uint32_t half, const void* x_bf16, const void* w_packed,
+                                  const void* scale_bf16, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
+                                  uint32_t flags, void* stream, uint32_t* status);
 /* Column-parallel gather of a block of rows over peer memory (no counterpart in the reference; same sharding
  * argument as above). peer_out[r] is the base of rank r's full [M, N] output; this rank's block [rows, row_bytes]
  * (its columns of some rows, e.g. the int32 outputs of one M-chunk of its GEMM shard) is stored at byte offset

@@ -140,6 +140,20 @@ def _worker(rank: int, world: int, port: int, q):
             pag2.halves()[half].zero_()
             torch.cuda.synchronize()
             dist.barrier()
+        # ---- GEMV and gather in one launch (peer stores from the reduction), a chain of launches, then the wait ------
+        pag3 = sharding.PeerAllGather(m, n)
+        for rounds in range(2):
+            for step in range(6):  # halves alternate; programmatic chain, no host sync in between
+                pag3.gemv(step & 1, tx2, tw2_, ts2_, k, cur, status, ffi.LAUNCH_CONSTANT_WEIGHTS)
+            pag3.wait(cur, status)
+            torch.cuda.synchronize()
+            assert status.cpu().tolist() == [0, 0, 0, 0]
+            for half in (0, 1):
+                assert torch.equal(pag3.halves()[half].view(torch.int16), want_all.view(torch.int16)), f"fused gather {rounds}/{half}"
+            dist.barrier()
+            pag3.halves().zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
         q.put((rank, "ok"))
     except Exception as exc:  # noqa: BLE001 - reported to the parent
         import traceback

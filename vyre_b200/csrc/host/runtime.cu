@@ -1252,6 +1252,7 @@ int32_t to_gather(const vyb_allgather_ctx* ctx, vybk::PeerGather* ag) {
     }
     ag->epoch = ctx->epoch;
     ag->wait_clocks = ctx->wait_clocks;
+    ag->slots = ctx->slots;
     return VYB_OK;
 }
 }  // namespace
@@ -1260,10 +1261,37 @@ int32_t vyb_k_allgather_push(const vyb_allgather_ctx* ctx, uint32_t half, uint32
                              uint32_t* status) {
     vybk::PeerGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;
-    if (half > 1 || m == 0 || n == 0 || (uint64_t(m) * n) % 8)
-        return fail_invalid_program("Fix: all-gather push needs half in {0,1} and m*n a multiple of 8 (16-byte stores).");
+    if (half >= (ctx->slots ? ctx->slots : 2) || m == 0 || n == 0 || (uint64_t(m) * n) % 8)
+        return fail_invalid_program("Fix: all-gather push needs a slot index below the context's slot count (two unless the "
+                                    "context says otherwise) and m*n a multiple of 8 (16-byte stores).");
     return launch_result(vybk::launch_allgather_push(ag, half, m, n, static_cast<cudaStream_t>(stream), status),
                          "all-gather push");
+}
+
+int32_t vyb_k_int4_gemv_allgather(const vyb_allgather_ctx* ctx, uint32_t half, const void* x_bf16, const void* w_packed,
+                                  const void* scale_bf16, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size, uint32_t flags,
+                                  void* stream, uint32_t* status) {
+    vybk::PeerGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    if (!x_bf16 || !w_packed || !scale_bf16) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (half > 1) return fail_invalid_program("Fix: the gather buffer has two halves: pass half 0 or 1, alternating from launch to launch.");
+    if (!vybk::int4_gemv_halfsm_supported(m, n, k, group_size))
+        return fail_unsupported("gathering int4 gemv shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
+                                std::to_string(k) + " group=" + std::to_string(group_size) +
+                                " (needs 1 <= m <= 4, group 128, k 2048 or 4096)");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(scale_bf16)) & 15)
+        return fail_invalid_program("Fix: int4 gemv operands must be 16-byte aligned.");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    return launch_result(vybk::launch_int4_gemv_halfsm(x_bf16, w_packed, scale_bf16, nullptr, m, n, k, 0, sms,
+                                                       static_cast<cudaStream_t>(stream), status,
+                                                       (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0, &ag, half),
+                         "gathering int4 gemv");
 }
 
 int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_t* status) {

@@ -18,39 +18,26 @@
 #include <stdint.h>
 
 #include "kernels.h"
+#include "peer_gather.cuh"
 
 namespace vybk {
 namespace {
 
-constexpr long long WAIT_CLOCKS = 4000000000ll;
-constexpr uint32_t COUNTER_STRIDE = 8;  // 32-bit words between the counters of two source ranks (one 32-byte sector each)
-
-__device__ __forceinline__ const volatile uint32_t* counter_from(const PeerGather& ag, uint32_t owner, uint32_t source) {
-    return reinterpret_cast<const volatile uint32_t*>(ag.peer_flag[owner]) + source * COUNTER_STRIDE;
-}
-// Has rank `source` completed `launches` pushes into this rank's buffer? Bounded; a wait that has run out once is not
-// repeated: later calls return at once, so a broken run ends quickly with its status word set.
-__device__ __forceinline__ bool wait_pushes_from(const PeerGather& ag, uint32_t source, uint32_t launches, const uint32_t* status) {
-    if (status && (*reinterpret_cast<const volatile uint32_t*>(status) & 128u)) return false;
-    const volatile uint32_t* arrived = counter_from(ag, ag.rank, source);
-    const long long limit = ag.wait_clocks ? (long long)ag.wait_clocks : WAIT_CLOCKS;
-    const long long t0 = clock64();
-    while (int32_t(*arrived - launches) < 0) {
-        if (clock64() - t0 > limit) return false;
-        __nanosleep(64);
-    }
-    return true;
-}
-
-// one CTA per peer
-__global__ void __launch_bounds__(256) allgather_push_kernel(const PeerGather ag, uint32_t half, uint32_t m, uint32_t n,
+// One CTA per peer, and a small one: 128 threads at no more than 32 registers and a few bytes of shared memory, so that
+// it becomes resident BESIDE the two decode-GEMV CTAs an SM holds under programmatic dependent launch (those take 512
+// threads, 61440 of the 65536 registers and all but 4 KB of the shared memory). A larger push CTA would have to wait for
+// a GEMV CTA to leave, or the GEMV would have to keep an SM free and lose the pairing of consecutive launches on it.
+__global__ void __launch_bounds__(128, 16) allgather_push_kernel(const PeerGather ag, uint32_t half, uint32_t m, uint32_t n,
                                                              uint32_t* status) {
     const uint32_t peer = blockIdx.x < ag.rank ? blockIdx.x : blockIdx.x + 1;
     volatile uint32_t* my_epoch = reinterpret_cast<volatile uint32_t*>(ag.epoch) + blockIdx.x;  // pushes this CTA slot has done
     __shared__ uint32_t s_done;
     if (threadIdx.x == 0) {
         s_done = *my_epoch;
-        if (!wait_pushes_from(ag, peer, s_done, status) && status) atomicOr(status, 128u);
+        // with two halves: the peer has completed every push this rank has; with more slots the same minus the slots
+        // that separate this push from the last one into the same slot
+        const uint32_t slack = ag.slots > 2 ? uint32_t(ag.slots) - 2u : 0u;
+        if (s_done > slack && !wait_pushes_from(ag, peer, s_done - slack, status) && status) atomicOr(status, 128u);
     }
     __syncthreads();
     const size_t slice_vecs = size_t(m) * n * 2 / 16;
@@ -62,11 +49,12 @@ __global__ void __launch_bounds__(256) allgather_push_kernel(const PeerGather ag
     __syncthreads();
     if (threadIdx.x == 0) {
         atomicAdd_system(const_cast<uint32_t*>(counter_from(ag, peer, ag.rank)), 1u);
-        *my_epoch = s_done + 1;
+        atomicAdd(const_cast<uint32_t*>(my_epoch), 1u);  // pushes of several streams may run side by side
     }
 }
 
 __global__ void __launch_bounds__(32) allgather_wait_kernel(const PeerGather ag, uint32_t* status) {
+    send_owed_signal(ag, threadIdx.x);  // of a fused GEMV launch before this kernel in the stream
     const uint32_t done = *reinterpret_cast<const volatile uint32_t*>(ag.epoch);
     bool ok = true;
     if (threadIdx.x < ag.world && threadIdx.x != ag.rank) ok = wait_pushes_from(ag, threadIdx.x, done, status);
@@ -144,9 +132,9 @@ cudaError_t launch_colpar_wait(const PeerGather& ag, uint32_t want, cudaStream_t
 
 cudaError_t launch_allgather_push(const PeerGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
                                   uint32_t* status) {
-    if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world || half > 1 || (size_t(m) * n) % 8) return cudaErrorInvalidValue;
+    if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world || half >= (ag.slots ? ag.slots : 2) || (size_t(m) * n) % 8) return cudaErrorInvalidValue;
     if (ag.world == 1) return cudaSuccess;  // nobody to send to
-    allgather_push_kernel<<<ag.world - 1, 256, 0, stream>>>(ag, half, m, n, status);
+    allgather_push_kernel<<<ag.world - 1, 128, 0, stream>>>(ag, half, m, n, status);
     return cudaGetLastError();
 }
 

@@ -50,6 +50,7 @@
 #include <atomic>
 
 #include "kernels.h"
+#include "peer_gather.cuh"
 
 namespace vybk {
 namespace {
@@ -94,10 +95,20 @@ struct Params {
     uint32_t m, n;
     uint32_t tiles_per_cta, tiles_rem;  // whole 16-row tiles per CTA; the first tiles_rem CTAs own one more
     uint32_t pace_ns;                   // pause between the prefetched tiles (0: none)
+    // the gathering form only: the outputs go to this rank's slice of buffer half `half` on EVERY rank
+    PeerGather ag;
+    uint32_t half;
+    uint32_t* status;
 };
 
 // NM = MMAs per 16 rows x 32 k = ceil(m / 2); W warps, each owning GPW 128-k groups of every row: k = 128 GPW W
-template <int NM, int GPW, int W, bool OUT_F32>
+// GATHER: a column-parallel shard whose bf16 outputs are stored straight into every rank's gather buffer (peer stores over
+// NVLink from the reduction that produces them), so that the all-gather is part of the launch and consecutive launches
+// stay one programmatic chain. No CTA fences at system scope: the arrival signal of launch d is sent by whatever runs
+// next on the stream (launch d + 1 or the wait kernel), when launch d is complete and its stores are visible. Before it
+// stores into a peer's half, a launch checks (bounded) that this peer has signalled launch d - 1: then the peer is past
+// whatever consumed launch d - 2 from the same half. Buffer halves must alternate from launch to launch.
+template <int NM, int GPW, int W, bool OUT_F32, bool GATHER>
 __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // let the next launch of the stream become resident beside this one at once; it waits (griddepcontrol.wait)
@@ -179,6 +190,11 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
 
     // ---- activations: everything below reads x, so the previous launch of the stream must be complete ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t launch_index = 0;  // GATHER: how many gathering launches this rank has completed before this one
+    if constexpr (GATHER) {
+        launch_index = *(reinterpret_cast<const volatile uint32_t*>(p.ag.epoch) + EPOCH_INDEX + p.half);
+        if (blockIdx.x == 0 && warp == 0) send_owed_signal(p.ag, lane);  // the previous launch's arrival
+    }
     uint32_t xb[NM][GPW][8];  // [mma][group of this warp][byte block 0 | 1][operand 0 | 1][bytes 0-3 | 4-7]
     float dq[NM][GPW];        // delta / 16 of (batch row of this lane's D columns, group), x 65536 for the high digit pair
     int corr[NM][GPW];        // -128 x (sum of the group's X, low or high 16-bit part) for this lane's D columns: zero point
@@ -383,7 +399,16 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
     }
 
     // sum the warps' partials of the tiles [first, first + count) in warp order and store the outputs
+    bool peers_checked = false;
     auto reduce_tiles = [&](uint32_t first, uint32_t count) {
+        if constexpr (GATHER) {
+            // every peer has signalled its launch before this one (sent when this launch began over there, microseconds
+            // ago): its consumers of the half about to be overwritten have run. Bounded; status bit 128 when it runs out.
+            if (!peers_checked && warp == 0 && lane < p.ag.world && lane != p.ag.rank &&
+                !wait_pushes_from(p.ag, lane, launch_index, p.status) && p.status)
+                atomicOr(p.status, 128u);
+            peers_checked = true;
+        }
         __syncthreads();
         for (uint32_t idx = threadIdx.x; idx < count * (TILE_ROWS * MM); idx += W * 32) {
             const uint32_t col = idx % MM, row = r0 + first * TILE_ROWS + idx / MM;
@@ -392,10 +417,15 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
 #pragma unroll
             for (int w = 0; w < W; ++w) sum += src[w * (PRIV / 4)];
             if (row < r1 && col < p.m) {
-                if constexpr (OUT_F32)
+                if constexpr (GATHER) {
+                    const size_t at = (size_t(p.half) * p.ag.world + p.ag.rank) * p.m * p.n + size_t(col) * p.n + row;
+                    const __nv_bfloat16 v = __float2bfloat16_rn(sum);
+                    for (uint32_t q = 0; q < p.ag.world; ++q) reinterpret_cast<__nv_bfloat16*>(p.ag.peer_out[q])[at] = v;
+                } else if constexpr (OUT_F32) {
                     static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
-                else
+                } else {
                     static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
+                }
             }
         }
     };
@@ -558,6 +588,16 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
     fold_partials();
     cp_async_wait<0>();
     if (pending) reduce_tiles(ntiles - pending, pending);
+    if constexpr (GATHER) {
+        // one CTA hands the launch index to the next launch (which reads the other half's word), counts the launch for the
+        // wait kernel and leaves the arrival signal owed
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            volatile uint32_t* e = reinterpret_cast<volatile uint32_t*>(p.ag.epoch);
+            e[EPOCH_INDEX + (p.half ^ 1u)] = launch_index + 1;
+            for (uint32_t i = 0; i + 1 < p.ag.world || i == 0; ++i) e[i] = launch_index + 1;
+            e[EPOCH_OWED] = 1;
+        }
+    }
 }
 
 }  // namespace
@@ -568,22 +608,23 @@ bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t gro
 
 cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                                    uint32_t* status, bool constant_weights) {
+                                    uint32_t* status, bool constant_weights, const PeerGather* gather, uint32_t half) {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t de = cudaGetDevice(&dev);
     if (de != cudaSuccess) return de;
     const uint64_t bit = 1ull << (dev & 63);
     using Kernel = void (*)(const Params);
-    // [variant][f32 out]: 0: batch <= 2, k 4096; 1: batch <= 2, k 2048; 2: batch <= 4, k 4096; 3: batch <= 4, k 2048
-    static const Kernel kernels[4][2] = {
-        {int4_gemv_halfsm_kernel<1, 4, 8, false>, int4_gemv_halfsm_kernel<1, 4, 8, true>},
-        {int4_gemv_halfsm_kernel<1, 2, 8, false>, int4_gemv_halfsm_kernel<1, 2, 8, true>},
-        {int4_gemv_halfsm_kernel<2, 4, 8, false>, int4_gemv_halfsm_kernel<2, 4, 8, true>},
-        {int4_gemv_halfsm_kernel<2, 2, 8, false>, int4_gemv_halfsm_kernel<2, 2, 8, true>}};
+    // [variant][0: bf16 out, 1: f32 out, 2: bf16 out into the gather buffers]: 0: batch <= 2, k 4096; 1: batch <= 2, k 2048;
+    // 2: batch <= 4, k 4096; 3: batch <= 4, k 2048
+    static const Kernel kernels[4][3] = {
+        {int4_gemv_halfsm_kernel<1, 4, 8, false, false>, int4_gemv_halfsm_kernel<1, 4, 8, true, false>, int4_gemv_halfsm_kernel<1, 4, 8, false, true>},
+        {int4_gemv_halfsm_kernel<1, 2, 8, false, false>, int4_gemv_halfsm_kernel<1, 2, 8, true, false>, int4_gemv_halfsm_kernel<1, 2, 8, false, true>},
+        {int4_gemv_halfsm_kernel<2, 4, 8, false, false>, int4_gemv_halfsm_kernel<2, 4, 8, true, false>, int4_gemv_halfsm_kernel<2, 4, 8, false, true>},
+        {int4_gemv_halfsm_kernel<2, 2, 8, false, false>, int4_gemv_halfsm_kernel<2, 2, 8, true, false>, int4_gemv_halfsm_kernel<2, 2, 8, false, true>}};
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        for (int i = 0; i < 8; ++i) {
-            const void* f = (const void*)kernels[i >> 1][i & 1];
+        for (int i = 0; i < 12; ++i) {
+            const void* f = (const void*)kernels[i / 3][i % 3];
             cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
             if (e == cudaSuccess)
                 e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -599,7 +640,9 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     p.m = m;
     p.n = n;
     p.pace_ns = constant_weights ? PACE_NS : 0u;
-    (void)status;  // nothing in this kernel can time out
+    p.status = status;  // only the gathering form has a wait that can run out
+    p.half = half & 1u;
+    if (gather) p.ag = *gather;
     // One CTA per SM, whole 16-row tiles each, the remainder spread one tile per CTA (14336 rows on 148 SMs: eight
     // CTAs with 7 tiles, the others with 6). Measured against 128 CTAs x 7 tiles and against two CTAs per SM (which
     // leave no room for the next launch): this split is the fastest.
@@ -618,7 +661,7 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = constant_weights ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernels[variant][out_f32 ? 1 : 0], p);
+    return cudaLaunchKernelEx(&cfg, kernels[variant][gather ? 2 : out_f32 ? 1 : 0], p);
 }
 
 }  // namespace vybk

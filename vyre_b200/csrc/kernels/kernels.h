@@ -7,6 +7,8 @@
 
 namespace vybk {
 
+struct PeerGather;  // defined below: the peer addresses of a gather
+
 // ---- decode GEMV / skinny GEMM (int4_gemv.cu) ---------------------------------------------------------------
 // y[m,n] = cast( sum_k x[m,k] * (q[n,k]-8) * s[n,k/128] ), m <= 8, group 128, k % 1024 == 0.
 // out_dtype: 0 = bf16, 1 = f32. status: optional 4-word device buffer set non-zero when a bounded wait ran out.
@@ -18,7 +20,8 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
 bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                                    uint32_t* status, bool constant_weights);
+                                    uint32_t* status, bool constant_weights, const PeerGather* gather = nullptr,
+                                    uint32_t half = 0);
 // ---- all-gather of column-parallel outputs over peer memory (allgather_push.cu) ------------------------------------
 // gather buffers [2][world][m][n] bf16 per rank; arrival counters and launch counters are 32-bit device words,
 // zero before the first push
@@ -28,6 +31,7 @@ struct PeerGather {
     unsigned long long peer_flag[8] = {};  // every rank's 256 bytes of arrival counters: word 8 s counts pushes from rank s
     unsigned long long epoch = 0;          // local: 8 words, pushes completed per peer slot
     unsigned long long wait_clocks = 0;    // clock limit of a device-side wait; 0 = about 2 s
+    unsigned long long slots = 0;          // slots of the gather buffer ([slots][world][m][n]); 0 = two halves
 };
 cudaError_t launch_allgather_push(const PeerGather& ag, uint32_t half, uint32_t m, uint32_t n, cudaStream_t stream,
                                   uint32_t* status);

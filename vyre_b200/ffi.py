@@ -39,7 +39,7 @@ class AllGatherCtx(C.Structure):
     """vyb_allgather_ctx: peer addresses of the gather buffers / arrival counters and the local step words."""
 
     _fields_ = [("world", C.c_uint32), ("rank", C.c_uint32), ("peer_out", C.c_uint64 * 8), ("peer_flag", C.c_uint64 * 8),
-                ("epoch", C.c_uint64), ("wait_clocks", C.c_uint64)]
+                ("epoch", C.c_uint64), ("wait_clocks", C.c_uint64), ("slots", C.c_uint64)]
 
 
 class MoeEpCtx(C.Structure):
@@ -196,6 +196,7 @@ _STATUS_FUNCS = {
     "vyb_k_int8_gemm_i32_ex": [_P, _P, _P, _U, _U, _U, _U, _P, _P],
     "vyb_k_allgather_push": [_P, _U, _U, _U, _P, _P],
     "vyb_k_allgather_wait": [_P, _P, _P],
+    "vyb_k_int4_gemv_allgather": [_P, _U, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_moe_route": [_P, _P, _P, _P, _U, _U, _U, _U, _P],
     "vyb_k_rows_gather_bf16": [_P, _P, _P, _U, _U, _P],
     "vyb_k_moe_experts_int4": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],

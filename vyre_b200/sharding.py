@@ -258,7 +258,7 @@ class PeerAllGather:
     """Gather buffers for vyb_k_allgather_push: [2][world][m][n] bf16 per rank plus a 32-bit arrival counter, in
     symmetric memory so that every rank holds device addresses of every peer's copy. Halves are used alternately."""
 
-    def __init__(self, m: int, n: int, group=None):
+    def __init__(self, m: int, n: int, group=None, slots: int = 2):
         import os
 
         import torch
@@ -270,8 +270,10 @@ class PeerAllGather:
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > 8:
             raise ValueError("the fused all-gather addresses at most 8 peers")
-        self.m, self.n = m, n
-        self.data_bytes = (2 * self.world * m * n * 2 + 255) & ~255
+        if slots < 2:
+            raise ValueError("a gather buffer has at least two slots")
+        self.m, self.n, self.slots = m, n, slots
+        self.data_bytes = (slots * self.world * m * n * 2 + 255) & ~255
         total = self.data_bytes + 256
         if self.world > 1:
             # plain peer mappings are all the kernel needs; no NVLink multicast object is bound to the buffer
@@ -294,14 +296,16 @@ class PeerAllGather:
             self.ctx.peer_out[r] = ptrs[r]
             self.ctx.peer_flag[r] = ptrs[r] + self.data_bytes
         self.ctx.epoch = self.local.data_ptr()
+        self.ctx.slots = slots
         torch.cuda.synchronize()
         if self.world > 1:
             dist.barrier(group)  # every counter is zero before anybody launches
 
     def halves(self):
-        """The two [world, m, n] bf16 views of the local gather buffer."""
-        t = self.buf[: 2 * self.world * self.m * self.n * 2].view(self.torch.bfloat16)
-        return t.view(2, self.world, self.m, self.n)
+        """The [world, m, n] bf16 views of the local gather buffer, one per slot (two unless more were asked for)."""
+        slots = getattr(self, "slots", 2)
+        t = self.buf[: slots * self.world * self.m * self.n * 2].view(self.torch.bfloat16)
+        return t.view(slots, self.world, self.m, self.n)
 
     def local_slice(self, half: int):
         """This rank's [m, n] slice of a buffer half: the output of a plain GEMV that `push` then sends to the peers."""
@@ -311,6 +315,14 @@ class PeerAllGather:
         """Send the local slice of `half` to every peer (kernel on `stream`, normally a side stream)."""
         self.ffi.check(self.ffi.lib().vyb_k_allgather_push(C.byref(self.ctx), half, self.m, self.n, C.c_void_p(stream),
                                                            C.c_void_p(status.data_ptr())))
+
+    def gemv(self, half: int, x, w, scales, k: int, stream, status, flags: int = 0):
+        """The shard's decode GEMV and its all-gather in one launch (vyb_k_int4_gemv_allgather): the bf16 outputs go
+        straight into this rank's slice of buffer `half` on every rank. Alternate the halves; run `wait` on the stream
+        before a gathered result is read."""
+        self.ffi.check(self.ffi.lib().vyb_k_int4_gemv_allgather(
+            C.byref(self.ctx), half, x.data_ptr(), w.data_ptr(), scales.data_ptr(), self.m, self.n, k, 128, flags,
+            C.c_void_p(stream), C.c_void_p(status.data_ptr())))
 
     def wait(self, stream, status):
         """Bounded device-side wait on `stream` until every gather launched so far is complete in local memory."""
