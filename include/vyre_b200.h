@@ -516,6 +516,16 @@ int32_t vyb_k_int4_gemv_allgather(const vyb_allgather_ctx* ctx, uint32_t half, c
 int32_t vyb_k_colpar_push(const vyb_allgather_ctx* ctx, const void* block, uint32_t rows, uint32_t row_bytes,
                           uint64_t dst_pitch_bytes, uint64_t dst_offset_bytes, void* stream, uint32_t* status);
 int32_t vyb_k_colpar_wait(const vyb_allgather_ctx* ctx, uint32_t blocks, void* stream, uint32_t* status);
+/* The int8 GEMM of a column-parallel shard and the gather of its int32 outputs in ONE kernel (no counterpart in the
+ * reference): the epilogue that reads a tile's accumulators out of tensor memory stores them at byte offset
+ * dst_offset_bytes (row pitch dst_pitch_bytes) of EVERY rank's full output peer_out[r] - plain 16-byte peer stores over
+ * NVLink for the other ranks - while the MMA warp is already on the next tile, so the transfer overlaps the math tile
+ * by tile and no copy kernel or staging buffer exists. A one-warp kernel behind it in the stream raises every
+ * destination's counter for this rank by one (one block delivered); vyb_k_colpar_wait is the consumer-side check as
+ * before. m > 128 (the paired tcgen05 kernel), n a multiple of 4. */
+int32_t vyb_k_int8_gemm_i32_gather(const vyb_allgather_ctx* ctx, const void* a_i8, const void* w_i8, uint32_t m, uint32_t n,
+                                   uint32_t k, uint64_t dst_pitch_bytes, uint64_t dst_offset_bytes, void* stream,
+                                   uint32_t* status);
 
 /* C1: y f32 [m,n] = x f32 [m,k] . (int8 w[n,k] * s[n])^T */
 int32_t vyb_k_int8_weight_only_linear(const void* x_f32, const void* w_i8, const void* scale_f32, void* y_f32,

@@ -105,9 +105,9 @@ def _worker(rank: int, world: int, port: int, q):
         ffi.check(L.vyb_k_quantize_per_token_int8(xa.data_ptr(), xq.data_ptr(), sc.data_ptr(), m, k, stream()))
         pcg = sharding.PeerColumnGather(m, n, 4, multiple=8)
         side = torch.cuda.Stream()
-        for rep in range(2):
+        for rep in range(4):  # twice by copy kernels behind row chunks, twice by the GEMM's own gathering epilogue
             got, _ = sharding.column_parallel_int8_linear(pcg, xq, wa[pcg.begin:pcg.end].contiguous(), status, chunks=3,
-                                                          side_stream=side)
+                                                          side_stream=side, fused=rep >= 2)
             torch.cuda.synchronize()
             assert status.cpu().tolist() == [0, 0, 0, 0]
             assert torch.equal(got, full), f"peer-store column gather, pass {rep}"

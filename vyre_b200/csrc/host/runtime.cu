@@ -1314,6 +1314,34 @@ int32_t vyb_k_colpar_push(const vyb_allgather_ctx* ctx, const void* block, uint3
                          "column-parallel push");
 }
 
+int32_t vyb_k_int8_gemm_i32_gather(const vyb_allgather_ctx* ctx, const void* a_i8, const void* w_i8, uint32_t m, uint32_t n,
+                                   uint32_t k, uint64_t dst_pitch_bytes, uint64_t dst_offset_bytes, void* stream,
+                                   uint32_t* status) {
+    vybk::PeerGather ag;
+    if (int32_t rc = to_gather(ctx, &ag)) return rc;
+    if (!a_i8 || !w_i8) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if ((dst_pitch_bytes | dst_offset_bytes) % 16 || n % 4)
+        return fail_invalid_program("Fix: the gathering GEMM needs a pitch and an offset that are multiples of 16 bytes and n a "
+                                    "multiple of 4 (16-byte stores into every rank's output).");
+    if (!vybk::int8_gemm_pair_supported(m, n, k))
+        return fail_unsupported("gathering int8 gemm shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" +
+                                std::to_string(k) + " (needs m > 128, k a multiple of 16 and at most 132096); run "
+                                "vyb_k_int8_gemm_i32 and vyb_k_colpar_push instead");
+    if ((reinterpret_cast<uintptr_t>(a_i8) | reinterpret_cast<uintptr_t>(w_i8)) & 15)
+        return fail_invalid_program("Fix: int8 gemm operands must be 16-byte aligned (TMA tensor maps need it).");
+    int sms = 0;
+    if (int32_t rc = current_sm_count(&sms)) return rc;
+    vybk::GemmGatherOut go;
+    go.count = ag.world;
+    for (uint32_t r = 0; r < ag.world; ++r) go.dst[r] = ag.peer_out[r];
+    go.pitch = dst_pitch_bytes / 4;
+    go.col_off = dst_offset_bytes / 4;
+    cudaError_t e = vybk::launch_int8_gemm_pair_gather(static_cast<const int8_t*>(a_i8), static_cast<const int8_t*>(w_i8), go, m, n,
+                                                       k, sms, static_cast<cudaStream_t>(stream), status);
+    if (e == cudaSuccess) e = vybk::launch_colpar_signal(ag, static_cast<cudaStream_t>(stream));
+    return launch_result(e, "gathering int8 gemm");
+}
+
 int32_t vyb_k_colpar_wait(const vyb_allgather_ctx* ctx, uint32_t blocks, void* stream, uint32_t* status) {
     vybk::PeerGather ag;
     if (int32_t rc = to_gather(ctx, &ag)) return rc;

@@ -97,6 +97,15 @@ colpar_push_kernel(const PeerGather ag, const uint4* __restrict__ src, uint32_t 
     (void)status;
 }
 
+// After a gathering GEMM (whose epilogue stored this rank's block into every rank's output): one more block delivered
+// everywhere. Runs after that GEMM in its stream, so the block is complete and visible; one thread per destination.
+__global__ void __launch_bounds__(32) colpar_signal_kernel(const PeerGather ag) {
+    if (threadIdx.x < ag.world) {
+        __threadfence_system();
+        atomicAdd_system(const_cast<uint32_t*>(counter_from(ag, threadIdx.x, ag.rank)), 1u);
+    }
+}
+
 // bounded wait until every rank (own included) has delivered `want` blocks into this rank's buffer
 __global__ void __launch_bounds__(32) colpar_wait_kernel(const PeerGather ag, uint32_t want, uint32_t* status) {
     bool ok = true;
@@ -121,6 +130,12 @@ cudaError_t launch_colpar_push(const PeerGather& ag, const void* src, uint32_t r
     if (per_dest > rows) per_dest = rows;
     colpar_push_kernel<<<ag.world * per_dest, 256, 0, stream>>>(ag, static_cast<const uint4*>(src), rows, row_bytes / 16,
                                                                  dst_pitch_bytes / 16, dst_offset_bytes / 16, per_dest, tickets, status);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_colpar_signal(const PeerGather& ag, cudaStream_t stream) {
+    if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world) return cudaErrorInvalidValue;
+    colpar_signal_kernel<<<1, 32, 0, stream>>>(ag);
     return cudaGetLastError();
 }
 

@@ -30,7 +30,9 @@ constexpr int TMA_WARP = 0, MMA_WARP = 4;
 constexpr int NUM_WARPS = 9;
 constexpr int THREADS = NUM_WARPS * 32;
 constexpr int TMEM_COLS = 512;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GSTAGE_PITCH = 36;                       // 32-bit words per staged row: 16-byte aligned, conflict-free v4 stores
+constexpr int GSTAGE_BYTES = 4 * 32 * GSTAGE_PITCH * 4;  // one 32 x 32 block per epilogue warp (the gathering form)
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256 + GSTAGE_BYTES;
 
 struct Bars {
     unsigned long long full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
@@ -42,10 +44,12 @@ __device__ __forceinline__ bool is_epilogue_warp(int w) { return w == 8 || (w >=
 
 __global__ void __launch_bounds__(THREADS, 1)
 int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                      int32_t* __restrict__ out, uint32_t M, uint32_t N, uint32_t K, uint32_t* status) {
+                      int32_t* __restrict__ out, uint32_t M, uint32_t N, uint32_t K, uint32_t* status,
+                      const GemmGatherOut go) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     Bars* bars = reinterpret_cast<Bars*>(tiles + STAGES * STAGE_BYTES);
+    uint32_t* gstage = reinterpret_cast<uint32_t*>(tiles + STAGES * STAGE_BYTES + 256);  // behind the barriers
     volatile unsigned int* abort_flag = &bars->abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
@@ -158,15 +162,40 @@ int8_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 tmem_ld_wait();
                 const uint32_t col0 = n0 + c * 32;
                 if (row < M && col0 < N) {
-                    int32_t* dst = out + size_t(row) * N + col0;
-                    if (col0 + 32 <= N && (N & 3u) == 0) {
+                    if (go.count == 0) {
+                        int32_t* dst = out + size_t(row) * N + col0;
+                        if (col0 + 32 <= N && (N & 3u) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                    } else {
-                        for (int j = 0; j < 32; ++j)
-                            if (col0 + j < N) dst[j] = int32_t(r[j]);
+                            for (int j = 0; j < 8; ++j)
+                                reinterpret_cast<uint4*>(dst)[j] = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                        } else {
+                            for (int j = 0; j < 32; ++j)
+                                if (col0 + j < N) dst[j] = int32_t(r[j]);
+                        }
                     }
+                }
+                if (go.count != 0) {
+                    // The gathering form: this rank's columns go straight into every rank's full output (peer stores over
+                    // NVLink for the others) while the MMA warp is already on the next tile. A lane holds one ROW of the
+                    // 32 x 32 block; stored like that, every 16-byte store of a warp would land in a different row. The
+                    // block goes through shared memory instead, and eight lanes store 128 contiguous bytes of a row.
+                    uint32_t* stage = gstage + quad * (32 * GSTAGE_PITCH);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(stage + lane * GSTAGE_PITCH + 4 * j) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    __syncwarp();
+                    const uint32_t sub = lane >> 3, chunk = lane & 7;  // four rows per store instruction
+                    const uint32_t col = col0 + chunk * 4;
+#pragma unroll
+                    for (int rr = 0; rr < 8; ++rr) {
+                        const uint32_t brow = rr * 4 + sub, grow = m0 + quad * 32 + brow;
+                        const uint4 v = *reinterpret_cast<const uint4*>(stage + brow * GSTAGE_PITCH + chunk * 4);
+                        if (grow < M && col < N) {  // N is a multiple of 4: a 16-byte piece is inside or outside
+                            const size_t at = size_t(grow) * go.pitch + go.col_off + col;
+                            for (uint32_t d = 0; d < go.count; ++d) *reinterpret_cast<uint4*>(reinterpret_cast<int32_t*>(go.dst[d]) + at) = v;
+                        }
+                    }
+                    __syncwarp();
                 }
             }
             tc_fence_before();
@@ -191,8 +220,9 @@ bool int8_gemm_pair_supported(uint32_t m, uint32_t n, uint32_t k) {
     return m > 128 && n >= 1 && k >= 16 && k % 16 == 0 && k <= 132096;
 }
 
-cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
-                                  int sm_count, cudaStream_t stream, uint32_t* status) {
+namespace {
+cudaError_t launch_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k, int sm_count,
+                        cudaStream_t stream, uint32_t* status, const GemmGatherOut& go) {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -222,8 +252,23 @@ cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, int8_gemm_pair_kernel, ma, mw, out, m, n, k, status);
+    e = cudaLaunchKernelEx(&cfg, int8_gemm_pair_kernel, ma, mw, out, m, n, k, status, go);
     return e != cudaSuccess ? e : cudaGetLastError();
+}
+}  // namespace
+
+cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
+                                  int sm_count, cudaStream_t stream, uint32_t* status) {
+    return launch_pair(a, w, out, m, n, k, sm_count, stream, status, GemmGatherOut{});
+}
+
+cudaError_t launch_int8_gemm_pair_gather(const int8_t* a, const int8_t* w, const GemmGatherOut& go, uint32_t m, uint32_t n,
+                                         uint32_t k, int sm_count, cudaStream_t stream, uint32_t* status) {
+    if (go.count < 1 || go.count > 8 || (go.pitch | go.col_off | n) % 4 || !int8_gemm_pair_supported(m, n, k))
+        return cudaErrorInvalidValue;
+    for (uint32_t d = 0; d < go.count; ++d)
+        if (!go.dst[d] || (go.dst[d] & 15)) return cudaErrorInvalidValue;
+    return launch_pair(a, w, nullptr, m, n, k, sm_count, stream, status, go);
 }
 
 }  // namespace vybk

@@ -112,6 +112,16 @@ cudaError_t launch_int8_gemm(const int8_t* a, const int8_t* w, int32_t* out, uin
                              int sm_count, cudaStream_t stream, uint32_t* status);
 // CTA-pair form (int8_gemm_pair_tcgen05.cu): 256 x 256 tiles on two SMs; launch_int8_gemm uses it from two waves of pair tiles on
 bool int8_gemm_pair_supported(uint32_t m, uint32_t n, uint32_t k);
+// Where a gathering GEMM stores its int32 outputs: the same [m, n] block at element offset col_off (row pitch `pitch`
+// elements) of `count` buffers, normally every rank's full output (peer addresses). count == 0: the plain `out`.
+struct GemmGatherOut {
+    unsigned long long dst[8] = {};
+    uint32_t count = 0, pad = 0;
+    unsigned long long pitch = 0, col_off = 0;
+};
+cudaError_t launch_int8_gemm_pair_gather(const int8_t* a, const int8_t* w, const GemmGatherOut& go, uint32_t m, uint32_t n,
+                                         uint32_t k, int sm_count, cudaStream_t stream, uint32_t* status);
+cudaError_t launch_colpar_signal(const PeerGather& ag, cudaStream_t stream);
 cudaError_t launch_int8_gemm_pair(const int8_t* a, const int8_t* w, int32_t* out, uint32_t m, uint32_t n, uint32_t k,
                                   int sm_count, cudaStream_t stream, uint32_t* status);
 cudaError_t launch_quantize_per_token_int8(const void* x_bf16, int8_t* q, float* scales, uint32_t m, uint32_t k,

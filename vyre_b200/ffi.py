@@ -196,6 +196,7 @@ _STATUS_FUNCS = {
     "vyb_k_int8_gemm_i32_ex": [_P, _P, _P, _U, _U, _U, _U, _P, _P],
     "vyb_k_allgather_push": [_P, _U, _U, _U, _P, _P],
     "vyb_k_allgather_wait": [_P, _P, _P],
+    "vyb_k_int8_gemm_i32_gather": [_P, _P, _P, _U, _U, _U, C.c_uint64, C.c_uint64, _P, _P],
     "vyb_k_int4_gemv_allgather": [_P, _U, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_moe_route": [_P, _P, _P, _P, _U, _U, _U, _U, _P],
     "vyb_k_rows_gather_bf16": [_P, _P, _P, _U, _U, _P],

@@ -392,15 +392,28 @@ class PeerColumnGather:
             (row0 * self.n + self.begin) * self.elem, C.c_void_p(stream), C.c_void_p(status.data_ptr())))
         self.blocks += 1
 
+    def gemm(self, xq, w_rows, stream, status):
+        """xq int8 [m, k] . w_rows^T (this rank's rows [begin, end) of W), the int32 outputs stored by the GEMM's own
+        epilogue into every rank's full output (vyb_k_int8_gemm_i32_gather): one block delivered everywhere."""
+        m, k = xq.shape
+        assert m == self.m and w_rows.shape[0] == self.end - self.begin and self.elem == 4
+        self.ffi.check(self.ffi.lib().vyb_k_int8_gemm_i32_gather(
+            C.byref(self.ctx), xq.data_ptr(), w_rows.data_ptr(), m, w_rows.shape[0], k, self.n * self.elem,
+            self.begin * self.elem, C.c_void_p(stream), C.c_void_p(status.data_ptr())))
+        self.blocks += 1
+
     def wait(self, stream, status):
         self.ffi.check(self.ffi.lib().vyb_k_colpar_wait(C.byref(self.ctx), self.blocks, C.c_void_p(stream),
                                                         C.c_void_p(status.data_ptr())))
 
 
-def column_parallel_int8_linear(gather: PeerColumnGather, xq, w_rows, status, chunks: int = 4, side_stream=None):
-    """y int32 [m, n_total] = xq int8 [m, k] . W^T with this rank holding rows [begin, end) of W: the GEMM runs in
-    `chunks` row chunks on the current stream, each chunk's columns are pushed to every rank on `side_stream` while the
-    next chunk's GEMM runs, and the call ends with the bounded wait for every rank's blocks. Returns the full output."""
+def column_parallel_int8_linear(gather: PeerColumnGather, xq, w_rows, status, chunks: int = 4, side_stream=None,
+                                fused: bool = True):
+    """y int32 [m, n_total] = xq int8 [m, k] . W^T with this rank holding rows [begin, end) of W. With more than 128
+    rows (the paired tcgen05 kernel) and `fused`, GEMM and gather are one kernel: the epilogue stores every tile into
+    every rank's output. Otherwise the GEMM runs in `chunks` row chunks on the current stream, each chunk's columns are
+    pushed to every rank on `side_stream` while the next chunk's GEMM runs. Either way the call ends with the bounded
+    wait for every rank's blocks. Returns the full output (and the local block of the chunked path, else None)."""
     import torch
 
     from . import ffi
@@ -409,6 +422,10 @@ def column_parallel_int8_linear(gather: PeerColumnGather, xq, w_rows, status, ch
     m, k = xq.shape
     n_local = w_rows.shape[0]
     cur = torch.cuda.current_stream()
+    if fused and m > 128 and n_local % 4 == 0 and k % 16 == 0:
+        gather.gemm(xq, w_rows, cur.cuda_stream, status)
+        gather.wait(cur.cuda_stream, status)
+        return gather.output(torch.int32), None
     side = side_stream or cur
     y_local = torch.empty((m, n_local), dtype=torch.int32, device="cuda")
     step = (m + chunks - 1) // chunks
