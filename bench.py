@@ -656,7 +656,7 @@ def run_native(args) -> None:
     # that the figure does not hang on the few hundred microseconds of a 20-step run; clocks sampled across it
     kgraph = capture(lambda: [launch(c % COPIES) for c in range(LAUNCHES)])
     k_lo = sampler.mark()
-    kernel_reps = max(steps, 60)
+    kernel_reps = args.kernel_reps or max(steps, 60)
     kernel_us = event_time_us(kgraph.replay, reps=kernel_reps, warm=3, stream=stream) / LAUNCHES
     if rank == 0:
         time.sleep(0.06)
@@ -672,7 +672,7 @@ def run_native(args) -> None:
                 launch(c, ym, xm, mm)
             stream.synchronize()
             g2 = capture(lambda: [launch(c % COPIES, ym, xm, mm) for c in range(LAUNCHES)])
-            us = event_time_us(g2.replay, reps=40, warm=3, stream=stream) / LAUNCHES
+            us = event_time_us(g2.replay, reps=min(40, kernel_reps), warm=3, stream=stream) / LAUNCHES
             gbs = algorithmic_bytes(mm) / (us * 1e-6) / 1e9
             extra[f"m{mm}"] = {"us_per_launch": round(us, 3), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4)}
             del g2
@@ -804,7 +804,7 @@ def run_native(args) -> None:
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode GEMV, from one ncu capture of the M=1 case over
 # 8 rotating weight copies (summary kept under profiles/); other batches were not captured.
-NCU_DRAM_BYTES_PER_LAUNCH = {1: 30327296}
+NCU_DRAM_BYTES_PER_LAUNCH = {1: 30331648}
 
 
 def run_quick(args) -> None:
@@ -864,6 +864,8 @@ def main() -> None:
     ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm", "peak", "dropin"], help="kernel exercised by --quick")
     ap.add_argument("--shape", type=int, nargs=3, default=[2048, 14336, 4096], metavar=("M", "N", "K"),
                     help="GEMM shape for --quick --case prefill|int8gemm")
+    ap.add_argument("--kernel-reps", type=int, default=0,
+                    help="graph replays of the kernel-only roofline region (0: max(steps, 60)); small values shorten a profiler's launch list")
     ap.add_argument("--copies", type=int, default=COPIES,
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
     ap.add_argument("--quick", action="store_true",
