@@ -372,6 +372,34 @@ int32_t vyb_payload_bytes(const vyb_payload* p, const uint8_t** bytes, size_t* l
 int32_t vyb_payload_from_bytes(const uint8_t* bytes, size_t len, vyb_payload** payload);
 void vyb_payload_free(vyb_payload* p);
 
+/* ---- safetensors ingestion (vyre-safetensors/src/lib.rs:108-260, 871-907: SafetensorIndex::open) ---------------------
+ * One shard's header, read and validated without touching tensor payloads: 8-byte prefix, header <= 64 MiB, a JSON
+ * object of {dtype, shape, data_offsets} (`__metadata__` ignored, duplicate names refused), every range inside the
+ * payload, byte length = shape x dtype width, no overlaps, at most 1 000 000 tensors, names of 1..4096 bytes. The
+ * identity is (BLAKE3 of the exact header bytes, file length, payload start) as in SafetensorShardIdentity
+ * (lib.rs:98-106). Entries come in canonical name order. dtype tags follow SafetensorDtype's declaration order
+ * (BOOL 0, U8, I8, U16, I16, U32, I32, U64, I64, F16, BF16, F32, F64, F8_E4M3, F8_E5M2 14). vyb_safetensors_require is
+ * SafetensorRequirement (lib.rs:262-271). vyb_safetensors_upload moves a tensor's bytes from the file into a resident
+ * buffer (vyb_alloc) in bounded pieces through vyb_upload_at: weights then bind as resident values with the contract's
+ * Constant lifetime. Sharded indexes and full-checkpoint content identities (lib.rs:330-640) are not rebuilt. */
+typedef struct vyb_safetensors vyb_safetensors;
+typedef struct vyb_safetensor_entry {
+    const char* name;
+    uint32_t dtype;
+    const char* dtype_name;
+    uint32_t rank;
+    const uint64_t* shape;
+    uint64_t file_begin, file_end; /* absolute byte range in the shard file */
+} vyb_safetensor_entry;
+int32_t vyb_safetensors_open(const char* path, vyb_safetensors** out);
+void vyb_safetensors_free(vyb_safetensors* st);
+void vyb_safetensors_identity(const vyb_safetensors* st, uint8_t header_digest[32], uint64_t* file_len, uint64_t* data_start);
+uint32_t vyb_safetensors_count(const vyb_safetensors* st);
+int32_t vyb_safetensors_entry(const vyb_safetensors* st, uint32_t index, vyb_safetensor_entry* out);
+int32_t vyb_safetensors_find(const vyb_safetensors* st, const char* name, uint32_t* index);
+int32_t vyb_safetensors_require(const vyb_safetensors* st, const char* name, const char* dtype_name, const uint64_t* shape,
+                                uint32_t rank, uint32_t* index);
+
 /* ---- Device (artifact_lifecycle.rs:21-30) + ArtifactMaterializer (artifact_lifecycle.rs:132-186) ------- */
 int32_t vyb_device_acquire(int32_t ordinal, vyb_device** device);
 int32_t vyb_device_identity_of(const vyb_device* d, vyb_device_identity* out);
@@ -393,6 +421,9 @@ int32_t vyb_upload_at(vyb_device* d, vyb_resident_handle h, size_t offset_bytes,
 int32_t vyb_download(vyb_device* d, vyb_resident_handle h, void* dst, size_t len);
 int32_t vyb_download_range(vyb_device* d, vyb_resident_handle h, size_t offset_bytes, void* dst, size_t len);
 int32_t vyb_free(vyb_device* d, vyb_resident_handle h);
+/* a tensor of an indexed safetensors shard, file -> resident buffer at byte offset dst_offset */
+int32_t vyb_safetensors_upload(const vyb_safetensors* st, uint32_t index, vyb_device* device, vyb_resident_handle handle,
+                               uint64_t dst_offset);
 /* raw device pointer of a resident buffer, for hosts that share the CUDA context */
 int32_t vyb_resident_device_ptr(vyb_device* d, vyb_resident_handle h, void** device_ptr, size_t* len);
 

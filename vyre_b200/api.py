@@ -11,6 +11,7 @@ Every call goes through libvyre_b200.so; nothing here computes.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -680,3 +681,64 @@ class ArtifactSession:
     def run_host(self, inputs: list) -> list[bytes]:
         c = self.submit_and_wait(self.host_bindings(inputs))
         return self.ordered_outputs(c)
+
+
+# ---- safetensors ingestion (vyre-safetensors/src/lib.rs:108-260) --------------------------------------------------------
+class SafetensorIndex:
+    """vyre_safetensors::SafetensorIndex: the validated metadata of one shard; tensor bytes go straight from the file
+    into resident device buffers (`load_resident`), where they bind as `Constant` values."""
+
+    def __init__(self, handle, path: str):
+        self._h = C.c_void_p(handle)
+        self.path = path
+
+    @staticmethod
+    def open(path: str) -> "SafetensorIndex":
+        out = C.c_void_p()
+        check(ffi.lib().vyb_safetensors_open(os.fsencode(path), C.byref(out)))
+        return SafetensorIndex(out.value, path)
+
+    def __del__(self):
+        try:
+            if self._h:
+                ffi.lib().vyb_safetensors_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    def identity(self) -> dict:
+        """SafetensorShardIdentity: BLAKE3 of the exact header bytes, file length, payload start."""
+        digest = C.create_string_buffer(32)
+        flen, start = C.c_uint64(), C.c_uint64()
+        ffi.lib().vyb_safetensors_identity(self._h, digest, C.byref(flen), C.byref(start))
+        return {"header_digest": digest.raw, "file_len": flen.value, "data_start": start.value}
+
+    def _entry(self, index: int) -> dict:
+        e = ffi.SafetensorEntry()
+        check(ffi.lib().vyb_safetensors_entry(self._h, index, C.byref(e)))
+        return {"name": e.name.decode(), "dtype": e.dtype_name.decode(), "shape": [e.shape[i] for i in range(e.rank)],
+                "file_range": (e.file_begin, e.file_end), "index": index}
+
+    def tensors(self) -> list[dict]:
+        """Tensors in canonical name order."""
+        return [self._entry(i) for i in range(ffi.lib().vyb_safetensors_count(self._h))]
+
+    def tensor(self, name: str) -> dict:
+        idx = C.c_uint32()
+        check(ffi.lib().vyb_safetensors_find(self._h, name.encode(), C.byref(idx)))
+        return self._entry(idx.value)
+
+    def require(self, name: str, dtype: str, shape) -> dict:
+        """SafetensorRequirement: the tensor must be stored with exactly this dtype and shape."""
+        arr = (C.c_uint64 * max(1, len(shape)))(*shape)
+        idx = C.c_uint32()
+        check(ffi.lib().vyb_safetensors_require(self._h, name.encode(), dtype.encode(), arr, len(shape), C.byref(idx)))
+        return self._entry(idx.value)
+
+    def load_resident(self, device: "Device", name: str, handle=None, offset: int = 0):
+        """Allocate a resident buffer of the tensor's size (unless `handle` is given) and fill it from the file."""
+        e = self.tensor(name)
+        nbytes = e["file_range"][1] - e["file_range"][0]
+        h = handle if handle is not None else device.allocate_resident(max(nbytes, 1))
+        check(ffi.lib().vyb_safetensors_upload(self._h, e["index"], device._h, h, offset))
+        return h

@@ -101,6 +101,11 @@ class PlannerEvidence(C.Structure):
                 ("output_drift_abs_tolerance", C.c_float)]
 
 
+class SafetensorEntry(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_uint32), ("dtype_name", C.c_char_p), ("rank", C.c_uint32),
+                ("shape", C.POINTER(C.c_uint64)), ("file_begin", C.c_uint64), ("file_end", C.c_uint64)]
+
+
 class Binding(C.Structure):
     _fields_ = [("value_id", C.c_uint32), ("kind", C.c_int32), ("host_ptr", C.c_void_p), ("len", C.c_size_t),
                 ("resident", ResidentHandle)]
@@ -156,6 +161,11 @@ _STATUS_FUNCS = {
     "vyb_nn_moe_ffn_int4": [_S] * 9 + [_U] * 6 + [_PP],
     "vyb_program_buffer": [_P, _U, C.POINTER(BufferDecl)],
     "vyb_program_from_op": [_S, C.POINTER(BufferDecl), _U, C.POINTER(C.c_uint32), _U, _PP],
+    "vyb_safetensors_open": [_S, _PP],
+    "vyb_safetensors_entry": [_P, _U, C.POINTER(SafetensorEntry)],
+    "vyb_safetensors_find": [_P, _S, C.POINTER(C.c_uint32)],
+    "vyb_safetensors_require": [_P, _S, _S, C.POINTER(C.c_uint64), _U, C.POINTER(C.c_uint32)],
+    "vyb_safetensors_upload": [_P, _U, _P, ResidentHandle, C.c_uint64],
     "vyb_compile": [_P, _PP],
     "vyb_target_compile": [_P, _PP],
     "vyb_payload_bytes": [_P, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
@@ -228,6 +238,9 @@ _OTHER_FUNCS = {
     "vyb_artifact_free": (None, [_P]),
     "vyb_payload_digest": (None, [_P, C.c_char_p]),
     "vyb_payload_neutral_artifact": (None, [_P, C.c_char_p]),
+    "vyb_safetensors_free": (None, [_P]),
+    "vyb_safetensors_identity": (None, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "vyb_safetensors_count": (C.c_uint32, [_P]),
     "vyb_payload_format": (C.c_char_p, [_P]),
     "vyb_payload_kernel_variant": (C.c_uint32, [_P]),
     "vyb_payload_free": (None, [_P]),
