@@ -372,6 +372,68 @@ int32_t vyb_payload_bytes(const vyb_payload* p, const uint8_t** bytes, size_t* l
 int32_t vyb_payload_from_bytes(const uint8_t* bytes, size_t len, vyb_payload** payload);
 void vyb_payload_free(vyb_payload* p);
 
+/* ---- ProgramGraph (vyre-foundation/src/ir_inner/model/program_graph.rs:20-648) -----------------------------------------
+ * Executable Programs connected by typed values. Construction order is the topological schedule (add_node appends a
+ * node after all of its producers). A ValueContract is dtype + shape + access + lifetime (:44-56; lifetimes in the
+ * reference's order, :31-42); only statically known dimensions exist here (ShapeDim::Symbol is not rebuilt). Every port
+ * is checked against the Program's buffer (:541-634: element type, element count, access) and against the value it
+ * connects to (:343-360: dtype, shape, lifetime); names are unique over nodes and values; a buffer or a value is bound
+ * once per node; a retained successor must consume and preserve the value it replaces (:363-384). Violations are
+ * InvalidProgram errors that carry the reference's wording. vyb_graph_from_program is ProgramGraph::from_program
+ * (:225-270); vyb_graph_value reports the value's liveness interval in schedule indices (:486-503). The graph is host
+ * metadata: a runtime walks the schedule and submits one materialised Program per node, values bound as resident
+ * buffers (the Python mirror's GraphSession does exactly that). */
+#define VYB_LIFETIME_CONSTANT 0u
+#define VYB_LIFETIME_INVOCATION 1u
+#define VYB_LIFETIME_RETAINED 2u
+#define VYB_LIFETIME_OUTPUT 3u
+typedef struct vyb_graph vyb_graph;
+typedef struct vyb_value_contract {
+    uint32_t dtype;
+    uint32_t access;   /* VYB_ACCESS_READ_ONLY or VYB_ACCESS_READ_WRITE (a declared output buffer is ReadWrite) */
+    uint32_t lifetime; /* VYB_LIFETIME_* */
+    uint32_t rank;
+    uint64_t shape[6];
+} vyb_value_contract;
+typedef struct vyb_graph_input {
+    const char* buffer; /* Program-local buffer name */
+    uint32_t value;     /* connected graph value */
+    vyb_value_contract contract;
+} vyb_graph_input;
+typedef struct vyb_graph_output {
+    const char* buffer;
+    const char* name; /* stable graph value name */
+    vyb_value_contract contract;
+    int64_t retained_successor_of; /* value id, or -1 */
+} vyb_graph_output;
+typedef struct vyb_graph_value_info {
+    const char* name;
+    vyb_value_contract contract;
+    int64_t producer; /* node id, or -1 for external values */
+    uint32_t n_consumers;
+    int64_t retained_successor_of;
+    uint32_t live_start, live_end;
+} vyb_graph_value_info;
+typedef struct vyb_graph_node_info {
+    const char* name;
+    const vyb_program* program; /* owned by the graph */
+    uint32_t n_inputs, n_outputs;
+} vyb_graph_node_info;
+int32_t vyb_graph_new(vyb_graph** graph);
+void vyb_graph_free(vyb_graph* g);
+int32_t vyb_graph_add_external_value(vyb_graph* g, const char* name, const vyb_value_contract* contract, uint32_t* value_id);
+int32_t vyb_graph_add_node(vyb_graph* g, const char* name, const vyb_program* program, const vyb_graph_input* inputs,
+                           uint32_t n_inputs, const vyb_graph_output* outputs, uint32_t n_outputs, uint32_t* node_id,
+                           uint32_t* output_value_ids);
+int32_t vyb_graph_from_program(const char* node_name, const vyb_program* program, vyb_graph** graph);
+uint32_t vyb_graph_node_count(const vyb_graph* g);
+uint32_t vyb_graph_value_count(const vyb_graph* g);
+int32_t vyb_graph_value(const vyb_graph* g, uint32_t id, vyb_graph_value_info* out);
+int32_t vyb_graph_node(const vyb_graph* g, uint32_t id, vyb_graph_node_info* out);
+int32_t vyb_graph_node_input(const vyb_graph* g, uint32_t node, uint32_t index, vyb_graph_input* out);
+int32_t vyb_graph_node_output(const vyb_graph* g, uint32_t node, uint32_t index, vyb_graph_output* out, uint32_t* value_id);
+void vyb_graph_digest(const vyb_graph* g, uint8_t out[32]);
+
 /* ---- safetensors ingestion (vyre-safetensors/src/lib.rs:108-260, 871-907: SafetensorIndex::open) ---------------------
  * One shard's header, read and validated without touching tensor payloads: 8-byte prefix, header <= 64 MiB, a JSON
  * object of {dtype, shape, data_offsets} (`__metadata__` ignored, duplicate names refused), every range inside the

@@ -1,0 +1,97 @@
+"""ProgramGraphs on the device: GraphSession walks the schedule, one materialised Program per node, values as resident
+buffers, constants uploaded once (or loaded from a safetensors shard). Checked against the oracle's composition of the
+same nodes: byte-exact for the reference-order dense nodes, within the path's bf16 tolerance for the quantized ones."""
+import json
+import struct
+
+import numpy as np
+import pytest
+
+import oracle
+import vyre_b200 as vb
+from vyre_b200 import api, ffi, synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    d = vb.Device.acquire(0)
+    yield d
+    d.release()
+
+
+@pytest.mark.parametrize("dtype,odt", [(ffi.DT_F32, oracle.DT_F32), (ffi.DT_BF16, oracle.DT_BF16)])
+def test_dense_gated_mlp_graph_matches_the_oracle_composition(dev, dtype, odt):
+    batch, seq, h, inter = 2, 3, 40, 24
+    rows = batch * seq
+    rng = np.random.default_rng(3)
+    f = lambda *shape: rng.standard_normal(shape).astype(np.float32)  # noqa: E731
+    x, wg, wu, wd = f(rows, h), f(inter, h) * 0.3, f(inter, h) * 0.3, f(h, inter) * 0.3
+    if dtype == ffi.DT_BF16:
+        x, wg, wu, wd = (oracle.f32_to_bf16_bits(a) for a in (x, wg, wu, wd))
+    sess = api.GraphSession(api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(batch, seq, h, inter, dtype)), dev)
+    try:
+        sess.set_constant("mlp.gate_proj.weight", wg)
+        sess.set_constant("mlp.up_proj.weight", wu)
+        sess.set_constant("mlp.down_proj.weight", wd)
+        for _ in range(2):  # a session runs again and again over the same constants
+            got = sess.run({"mlp.normalized": x})["mlp.down"]
+        gate = oracle.linear_rows(x, wg, None, rows, h, inter, dtype=odt, weight_out_in=True)
+        up = oracle.linear_rows(x, wu, None, rows, h, inter, dtype=odt, weight_out_in=True)
+        act = oracle.swiglu(gate, up, dtype=odt)
+        want = oracle.linear_rows(act, wd, None, rows, inter, h, dtype=odt, weight_out_in=True)
+        if dtype == ffi.DT_F32:
+            # the projections are byte-exact against the oracle; SwiGLU's exp sits in the reference's 128-ULP window
+            np.testing.assert_allclose(np.frombuffer(got, np.float32), want, rtol=2e-5, atol=1e-6)
+        else:
+            a, b = oracle.bf16_bits_to_f32(np.frombuffer(got, np.uint16)), oracle.bf16_bits_to_f32(want)
+            assert np.abs(a - b).max() <= 2 ** -7 * max(1.0, np.abs(b).max())  # one bf16 ulp of the activation, propagated
+        with pytest.raises(vb.BackendError, match="bind the graph input"):
+            sess.run({})
+        with pytest.raises(vb.BackendError, match="needs .* bytes by its contract"):
+            sess.run({"mlp.normalized": x[:1]})
+    finally:
+        sess.close()
+
+
+def test_quantized_gated_mlp_graph_with_constants_from_a_safetensors_shard(dev, tmp_path):
+    rows, h, inter = 3, 2048, 4096  # both projections take the decode GEMV
+    x, wg, sg = synth.int4_linear_inputs(rows, inter, h, seed=5)
+    _, wu, su = synth.int4_linear_inputs(rows, inter, h, seed=6)
+    _, wd, sd = synth.int4_linear_inputs(rows, h, inter, seed=7)
+    x = oracle.f32_to_bf16_bits(oracle.bf16_bits_to_f32(x) * 0.25)
+    tensors = {"mlp.gate_proj.qweight": wg, "mlp.gate_proj.scales": sg, "mlp.up_proj.qweight": wu, "mlp.up_proj.scales": su,
+               "mlp.down_proj.qweight": wd, "mlp.down_proj.scales": sd}
+    header, blob = {}, b""
+    for name, a in tensors.items():
+        raw = a.tobytes()
+        header[name] = {"dtype": "U8" if a.dtype == np.uint8 else "BF16", "shape": list(a.shape), "data_offsets": [len(blob), len(blob) + len(raw)]}
+        blob += raw
+    hdr = json.dumps(header).encode()
+    path = tmp_path / "mlp.safetensors"
+    path.write_bytes(struct.pack("<Q", len(hdr)) + hdr + blob)
+
+    graph = api.quantized_gated_mlp_graph(api.QuantizedGatedMlpSpec(rows, h, inter))
+    sess = api.GraphSession(graph, dev)
+    try:
+        idx = api.SafetensorIndex.open(str(path))
+        for name in tensors:
+            sess.set_constant(name, handle=idx.load_resident(dev, name))
+        got = oracle.bf16_bits_to_f32(np.frombuffer(sess.run({"mlp.normalized": x})["mlp.down"], np.uint16)).reshape(rows, h)
+        gate = oracle.int4_rowmajor_linear(x, wg, sg, rows, inter, h)
+        up = oracle.int4_rowmajor_linear(x, wu, su, rows, inter, h)
+        act = oracle.swiglu(gate.reshape(-1), up.reshape(-1), dtype=oracle.DT_BF16)
+        want = oracle.bf16_bits_to_f32(oracle.int4_rowmajor_linear(act, wd, sd, rows, h, inter)).reshape(rows, h)
+        scale = np.sqrt((want ** 2).mean())
+        assert np.abs(got - want).max() <= 2e-2 * max(scale, np.abs(want).max() * 0.1), (np.abs(got - want).max(), scale)
+        # and byte for byte against the same three operators submitted one by one
+        def op(prog, arrays):
+            return vb.ArtifactSession.compile(prog, dev).run_host(arrays)[0]
+        g1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, h, inter, 128, ffi.DT_BF16), [x, wg.view(np.uint32), sg]), np.uint16)
+        u1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, h, inter, 128, ffi.DT_BF16), [x, wu.view(np.uint32), su]), np.uint16)
+        a1 = np.frombuffer(op(vb.swiglu_typed("g", "u", "o", rows * inter, ffi.DT_BF16), [g1, u1]), np.uint16)
+        d1 = op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, inter, h, 128, ffi.DT_BF16), [a1, wd.view(np.uint32), sd])
+        assert sess.run({"mlp.normalized": x})["mlp.down"] == d1
+    finally:
+        sess.close()

@@ -27,12 +27,13 @@ def _b(s: str) -> bytes:
 class Program:
     """vyre_foundation::ir::Program as the native facet sees it (buffers, workgroup size, op region id)."""
 
-    def __init__(self, handle: int):
+    def __init__(self, handle: int, owner=None):
         self._h = C.c_void_p(handle)
+        self._owner = owner  # a graph that owns the program: keeps it alive, and the handle is not freed here
 
     def __del__(self):
         try:
-            if self._h:
+            if self._h and self._owner is None:
                 ffi.lib().vyb_program_free(self._h)
         except Exception:
             pass
@@ -742,3 +743,285 @@ class SafetensorIndex:
         h = handle if handle is not None else device.allocate_resident(max(nbytes, 1))
         check(ffi.lib().vyb_safetensors_upload(self._h, e["index"], device._h, h, offset))
         return h
+
+
+# ---- ProgramGraph (vyre-foundation/src/ir_inner/model/program_graph.rs) ---------------------------------------------------
+_DT_SIZE = {ffi.DT_U32: 4, ffi.DT_I32: 4, ffi.DT_F16: 2, ffi.DT_BF16: 2, ffi.DT_F32: 4, ffi.DT_U8: 1, ffi.DT_I8: 1}
+
+
+def value_contract(dtype: int, shape, lifetime: int, access: int = ffi.ACCESS_READ_ONLY) -> ffi.ValueContract:
+    """ValueContract { dtype, shape, access, lifetime } (program_graph.rs:44-56); dimensions are statically known."""
+    c = ffi.ValueContract()
+    c.dtype, c.access, c.lifetime, c.rank = dtype, access, lifetime, len(shape)
+    if len(shape) > 6:
+        raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: a value contract holds at most six dimensions.")
+    for i, d in enumerate(shape):
+        c.shape[i] = d
+    return c
+
+
+def _contract_dict(c: ffi.ValueContract) -> dict:
+    return {"dtype": c.dtype, "access": c.access, "lifetime": c.lifetime, "shape": [int(c.shape[i]) for i in range(c.rank)]}
+
+
+class ProgramGraph:
+    """vyre_foundation::ir::ProgramGraph: Programs connected by typed values; construction order is the schedule."""
+
+    def __init__(self, handle=None):
+        if handle is None:
+            out = C.c_void_p()
+            check(ffi.lib().vyb_graph_new(C.byref(out)))
+            handle = out.value
+        self._h = C.c_void_p(handle)
+
+    def __del__(self):
+        try:
+            if self._h:
+                ffi.lib().vyb_graph_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+    @staticmethod
+    def from_program(node_name: str, program: Program) -> "ProgramGraph":
+        out = C.c_void_p()
+        check(ffi.lib().vyb_graph_from_program(node_name.encode(), program._h, C.byref(out)))
+        return ProgramGraph(out.value)
+
+    def add_external_value(self, name: str, contract: ffi.ValueContract) -> int:
+        vid = C.c_uint32()
+        check(ffi.lib().vyb_graph_add_external_value(self._h, name.encode(), C.byref(contract), C.byref(vid)))
+        return vid.value
+
+    def add_node(self, name: str, program: Program, inputs: list, outputs: list):
+        """inputs: [(buffer, value id, contract)], outputs: [(buffer, value name, contract[, retained_successor_of])].
+        Returns (node id, [output value ids])."""
+        ins = (ffi.GraphInput * max(1, len(inputs)))()
+        keep = []
+        for i, (buf, val, con) in enumerate(inputs):
+            b = buf.encode()
+            keep.append(b)
+            ins[i].buffer, ins[i].value, ins[i].contract = b, val, con
+        outs = (ffi.GraphOutput * max(1, len(outputs)))()
+        for i, o in enumerate(outputs):
+            b, n = o[0].encode(), o[1].encode()
+            keep += [b, n]
+            outs[i].buffer, outs[i].name, outs[i].contract = b, n, o[2]
+            outs[i].retained_successor_of = o[3] if len(o) > 3 and o[3] is not None else -1
+        nid = C.c_uint32()
+        vids = (C.c_uint32 * max(1, len(outputs)))()
+        check(ffi.lib().vyb_graph_add_node(self._h, name.encode(), program._h, ins, len(inputs), outs, len(outputs), C.byref(nid), vids))
+        return nid.value, [vids[i] for i in range(len(outputs))]
+
+    def values(self) -> list[dict]:
+        L, out = ffi.lib(), []
+        for i in range(L.vyb_graph_value_count(self._h)):
+            v = ffi.GraphValueInfo()
+            check(L.vyb_graph_value(self._h, i, C.byref(v)))
+            out.append({"id": i, "name": v.name.decode(), "contract": _contract_dict(v.contract),
+                        "producer": None if v.producer < 0 else int(v.producer), "consumers": v.n_consumers,
+                        "retained_successor_of": None if v.retained_successor_of < 0 else int(v.retained_successor_of),
+                        "live": (v.live_start, v.live_end)})
+        return out
+
+    def nodes(self) -> list[dict]:
+        L, out = ffi.lib(), []
+        for i in range(L.vyb_graph_node_count(self._h)):
+            n = ffi.GraphNodeInfo()
+            check(L.vyb_graph_node(self._h, i, C.byref(n)))
+            ins, outs = [], []
+            for k in range(n.n_inputs):
+                p = ffi.GraphInput()
+                check(L.vyb_graph_node_input(self._h, i, k, C.byref(p)))
+                ins.append({"buffer": p.buffer.decode(), "value": p.value, "contract": _contract_dict(p.contract)})
+            for k in range(n.n_outputs):
+                p, vid = ffi.GraphOutput(), C.c_uint32()
+                check(L.vyb_graph_node_output(self._h, i, k, C.byref(p), C.byref(vid)))
+                outs.append({"buffer": p.buffer.decode(), "name": p.name.decode(), "value": vid.value, "contract": _contract_dict(p.contract)})
+            out.append({"id": i, "name": n.name.decode(), "program": Program(n.program, owner=self), "inputs": ins, "outputs": outs})
+        return out
+
+    def schedule(self) -> list[int]:
+        return list(range(ffi.lib().vyb_graph_node_count(self._h)))
+
+    def digest(self) -> bytes:
+        buf = C.create_string_buffer(32)
+        ffi.lib().vyb_graph_digest(self._h, buf)
+        return buf.raw
+
+
+class GraphSession:
+    """Runs a ProgramGraph on a device: one materialised artifact per node, every value a resident buffer. `Constant`
+    external values are uploaded once (`set_constant`, or a resident handle from `SafetensorIndex.load_resident`);
+    `Invocation` external values are uploaded per run; produced values stay on the device between nodes; `Output`
+    values are read back at the end of `run`."""
+
+    def __init__(self, graph: ProgramGraph, device: "Device"):
+        self.graph, self.device = graph, device
+        self.values, self.nodes = graph.values(), graph.nodes()
+        self.sessions = [ArtifactSession.compile(n["program"], device) for n in self.nodes]
+        self.handles: dict[int, object] = {}
+        self._owned: list = []
+        for v in self.values:
+            if v["producer"] is not None or v["contract"]["lifetime"] == ffi.LIFETIME_INVOCATION:
+                self.handles[v["id"]] = self._alloc(v)
+
+    def _bytes(self, v: dict) -> int:
+        n = 1
+        for d in v["contract"]["shape"]:
+            n *= d
+        return max(1, n * _DT_SIZE[v["contract"]["dtype"]])
+
+    def _alloc(self, v: dict):
+        h = self.device.allocate_resident(self._bytes(v))
+        self._owned.append(h)
+        return h
+
+    def _by_name(self, name: str) -> dict:
+        for v in self.values:
+            if v["name"] == name:
+                return v
+        raise BackendError(ffi.ERR_INVALID_PROGRAM, f"Fix: the graph has no value named `{name}`.")
+
+    def set_constant(self, name: str, data=None, handle=None) -> None:
+        v = self._by_name(name)
+        if v["producer"] is not None or v["contract"]["lifetime"] not in (ffi.LIFETIME_CONSTANT, ffi.LIFETIME_RETAINED):
+            raise BackendError(ffi.ERR_INVALID_PROGRAM, f"Fix: `{name}` is not an external Constant or Retained value.")
+        if handle is None:
+            a = np.ascontiguousarray(data)
+            if a.nbytes != self._bytes(v):
+                raise BackendError(ffi.ERR_INVALID_PROGRAM,
+                                   f"Fix: constant `{name}` needs {self._bytes(v)} bytes by its contract, got {a.nbytes}.")
+            handle = self.device.resident_from(a)
+            self._owned.append(handle)
+        self.handles[v["id"]] = handle
+
+    def run(self, inputs: dict) -> dict:
+        """inputs: {external Invocation value name: array}. Returns {Output value name: bytes}."""
+        for v in self.values:
+            if v["producer"] is None and v["contract"]["lifetime"] == ffi.LIFETIME_INVOCATION:
+                if v["name"] not in inputs:
+                    raise BackendError(ffi.ERR_INVALID_PROGRAM, f"Fix: bind the graph input `{v['name']}`.")
+                a = np.ascontiguousarray(inputs[v["name"]])
+                if a.nbytes != self._bytes(v):
+                    raise BackendError(ffi.ERR_INVALID_PROGRAM,
+                                       f"Fix: graph input `{v['name']}` needs {self._bytes(v)} bytes by its contract, got {a.nbytes}.")
+                self.device.upload_resident(self.handles[v["id"]], a)
+            elif v["producer"] is None and v["id"] not in self.handles:
+                raise BackendError(ffi.ERR_INVALID_PROGRAM, f"Fix: set the constant `{v['name']}` before running the graph.")
+        for node, sess in zip(self.nodes, self.sessions):
+            slot = {b["name"]: b["binding"] for b in sess._buffers}
+            bs = BindingSet(sess.artifact.digest())
+            for port in node["inputs"] + node["outputs"]:
+                bs.insert_resident(slot[port["buffer"]], self.handles[port["value"]])
+            done = sess.submit(bs, leave_resident=True).wait()
+            del done
+        out = {}
+        for v in self.values:
+            if v["contract"]["lifetime"] == ffi.LIFETIME_OUTPUT:
+                out[v["name"]] = self.device.download_resident(self.handles[v["id"]], self._bytes(v)).tobytes()
+        return out
+
+    def close(self) -> None:
+        for h in self._owned:
+            try:
+                self.device.free_resident(h)
+            except Exception:
+                pass
+        self._owned = []
+
+
+@dataclass
+class QuantizedGatedMlpSpec:
+    """Dimensions of a gated MLP with int4 group-quantized projections (the serving-layout form of
+    vyre_libs::nn::model::DenseGatedMlpSpec, dense_gated_mlp.rs:15-29): bf16 activations, row-major packed weights."""
+    rows: int
+    hidden_dim: int
+    intermediate_dim: int
+    group_size: int = 128
+
+
+def quantized_gated_mlp_graph(spec: QuantizedGatedMlpSpec) -> ProgramGraph:
+    """gate_proj and up_proj (int4 weights, `Constant`), SwiGLU, down_proj: the projection / activation / projection
+    part of vyre_libs::nn::model::dense_gated_mlp_graph (dense_gated_mlp.rs:59-370) over this backend's quantized
+    linears, with the same value names. The norm and the residual add of that template are not on this path."""
+    r, h, i, g = spec.rows, spec.hidden_dim, spec.intermediate_dim, spec.group_size
+    if min(r, h, i, g) <= 0:
+        raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: rows, hidden_dim, intermediate_dim and group_size must be nonzero.")
+    bf16 = ffi.DT_BF16
+    inv, const, outl = ffi.LIFETIME_INVOCATION, ffi.LIFETIME_CONSTANT, ffi.LIFETIME_OUTPUT
+    ro, rw = ffi.ACCESS_READ_ONLY, ffi.ACCESS_READ_WRITE
+    read_hidden = value_contract(bf16, [r, h], inv, ro)
+    read_inter, write_inter = value_contract(bf16, [r, i], inv, ro), value_contract(bf16, [r, i], inv, rw)
+    # packed weights are declared as 32-bit words of eight nibbles (vyre-primitives/src/math/quantized/programs.rs:217-225)
+    up_w, up_s = value_contract(ffi.DT_U32, [i, h // 8], const), value_contract(bf16, [i, h // g], const)
+    down_w, down_s = value_contract(ffi.DT_U32, [h, i // 8], const), value_contract(bf16, [h, i // g], const)
+    graph = ProgramGraph()
+    x = graph.add_external_value("mlp.normalized", read_hidden)
+    gw = graph.add_external_value("mlp.gate_proj.qweight", up_w)
+    gs = graph.add_external_value("mlp.gate_proj.scales", up_s)
+    uw = graph.add_external_value("mlp.up_proj.qweight", up_w)
+    us = graph.add_external_value("mlp.up_proj.scales", up_s)
+    dw = graph.add_external_value("mlp.down_proj.qweight", down_w)
+    ds = graph.add_external_value("mlp.down_proj.scales", down_s)
+
+    def proj(name, out_name, inp, inp_contract, w, wc, s, sc, k, n, out_contract):
+        prog = linear_int4_grouped_rowmajor("input", "weight", "scale", "output", r, k, n, g, bf16)
+        _, (val,) = graph.add_node(name, prog, [("input", inp, inp_contract), ("weight", w, wc), ("scale", s, sc)],
+                                   [("output", out_name, out_contract)])
+        return val
+
+    gate = proj("mlp.gate_proj", "mlp.gate", x, read_hidden, gw, up_w, gs, up_s, h, i, write_inter)
+    up = proj("mlp.up_proj", "mlp.up", x, read_hidden, uw, up_w, us, up_s, h, i, write_inter)
+    _, (act,) = graph.add_node("mlp.swiglu", swiglu_typed("gate", "up", "output", r * i, bf16),
+                               [("gate", gate, read_inter), ("up", up, read_inter)], [("output", "mlp.activated", write_inter)])
+    proj("mlp.down_proj", "mlp.down", act, read_inter, dw, down_w, ds, down_s, i, h, value_contract(bf16, [r, h], outl, rw))
+    return graph
+
+
+@dataclass
+class DenseGatedMlpSpec:
+    """vyre_libs::nn::model::DenseGatedMlpSpec (dense_gated_mlp.rs:15-29) without the norm epsilon: batch x sequence token
+    rows, F16 / BF16 / F32 activations and weights."""
+    batch: int
+    sequence: int
+    hidden_dim: int
+    intermediate_dim: int
+    dtype: int = ffi.DT_F32
+
+
+def dense_gated_mlp_graph(spec: DenseGatedMlpSpec) -> ProgramGraph:
+    """The projection nodes of vyre_libs::nn::model::dense_gated_mlp_graph (dense_gated_mlp.rs:59-370) with the reference's
+    own node programs, value names, shapes and lifetimes: bias-free gate / up projections
+    (`linear_rows_no_bias_out_in_typed`), SwiGLU, bias-free down projection; weights are `Constant` values of shape
+    [out, in]. The learned RMSNorm in front and the residual add behind are not on this path: the graph's input is
+    `mlp.normalized` and its output `mlp.down`."""
+    if min(spec.batch, spec.sequence, spec.hidden_dim, spec.intermediate_dim) <= 0:
+        raise BackendError(ffi.ERR_INVALID_PROGRAM,
+                           "Fix: dense gated MLP primitive construction failed: batch, sequence, hidden_dim, and intermediate_dim must be nonzero")
+    if spec.dtype not in (ffi.DT_F16, ffi.DT_BF16, ffi.DT_F32):
+        raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: dense gated MLP primitive construction failed: dtype must be F16, BF16, or F32")
+    rows, h, i, dt = spec.batch * spec.sequence, spec.hidden_dim, spec.intermediate_dim, spec.dtype
+    if rows >= 1 << 32 or rows * max(h, i) >= 1 << 32 or h * i >= 1 << 32:
+        raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: dense gated MLP primitive construction failed: element counts overflow u32")
+    inv, const, outl = ffi.LIFETIME_INVOCATION, ffi.LIFETIME_CONSTANT, ffi.LIFETIME_OUTPUT
+    ro, rw = ffi.ACCESS_READ_ONLY, ffi.ACCESS_READ_WRITE
+    hidden_shape, inter_shape = [spec.batch, spec.sequence, h], [spec.batch, spec.sequence, i]
+    read_hidden = value_contract(dt, hidden_shape, inv, ro)
+    read_inter, write_inter = value_contract(dt, inter_shape, inv, ro), value_contract(dt, inter_shape, inv, rw)
+    up_w, down_w = value_contract(dt, [i, h], const), value_contract(dt, [h, i], const)
+    graph = ProgramGraph()
+    x = graph.add_external_value("mlp.normalized", read_hidden)
+    gate_w = graph.add_external_value("mlp.gate_proj.weight", up_w)
+    up_wv = graph.add_external_value("mlp.up_proj.weight", up_w)
+    down_wv = graph.add_external_value("mlp.down_proj.weight", down_w)
+    _, (gate,) = graph.add_node("mlp.gate_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, h, i, dt),
+                                [("input", x, read_hidden), ("weight", gate_w, up_w)], [("output", "mlp.gate", write_inter)])
+    _, (up,) = graph.add_node("mlp.up_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, h, i, dt),
+                              [("input", x, read_hidden), ("weight", up_wv, up_w)], [("output", "mlp.up", write_inter)])
+    _, (act,) = graph.add_node("mlp.swiglu", swiglu_typed("gate", "up", "output", rows * i, dt),
+                               [("gate", gate, read_inter), ("up", up, read_inter)], [("output", "mlp.activated", write_inter)])
+    graph.add_node("mlp.down_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, i, h, dt),
+                   [("input", act, read_inter), ("weight", down_wv, down_w)],
+                   [("output", "mlp.down", value_contract(dt, hidden_shape, outl, rw))])
+    return graph

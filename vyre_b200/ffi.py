@@ -101,6 +101,30 @@ class PlannerEvidence(C.Structure):
                 ("output_drift_abs_tolerance", C.c_float)]
 
 
+class ValueContract(C.Structure):
+    _fields_ = [("dtype", C.c_uint32), ("access", C.c_uint32), ("lifetime", C.c_uint32), ("rank", C.c_uint32), ("shape", C.c_uint64 * 6)]
+
+
+class GraphInput(C.Structure):
+    _fields_ = [("buffer", C.c_char_p), ("value", C.c_uint32), ("contract", ValueContract)]
+
+
+class GraphOutput(C.Structure):
+    _fields_ = [("buffer", C.c_char_p), ("name", C.c_char_p), ("contract", ValueContract), ("retained_successor_of", C.c_int64)]
+
+
+class GraphValueInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("contract", ValueContract), ("producer", C.c_int64), ("n_consumers", C.c_uint32),
+                ("retained_successor_of", C.c_int64), ("live_start", C.c_uint32), ("live_end", C.c_uint32)]
+
+
+class GraphNodeInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("program", C.c_void_p), ("n_inputs", C.c_uint32), ("n_outputs", C.c_uint32)]
+
+
+LIFETIME_CONSTANT, LIFETIME_INVOCATION, LIFETIME_RETAINED, LIFETIME_OUTPUT = 0, 1, 2, 3
+
+
 class SafetensorEntry(C.Structure):
     _fields_ = [("name", C.c_char_p), ("dtype", C.c_uint32), ("dtype_name", C.c_char_p), ("rank", C.c_uint32),
                 ("shape", C.POINTER(C.c_uint64)), ("file_begin", C.c_uint64), ("file_end", C.c_uint64)]
@@ -161,6 +185,15 @@ _STATUS_FUNCS = {
     "vyb_nn_moe_ffn_int4": [_S] * 9 + [_U] * 6 + [_PP],
     "vyb_program_buffer": [_P, _U, C.POINTER(BufferDecl)],
     "vyb_program_from_op": [_S, C.POINTER(BufferDecl), _U, C.POINTER(C.c_uint32), _U, _PP],
+    "vyb_graph_new": [_PP],
+    "vyb_graph_add_external_value": [_P, _S, C.POINTER(ValueContract), C.POINTER(C.c_uint32)],
+    "vyb_graph_add_node": [_P, _S, _P, C.POINTER(GraphInput), _U, C.POINTER(GraphOutput), _U, C.POINTER(C.c_uint32),
+                           C.POINTER(C.c_uint32)],
+    "vyb_graph_from_program": [_S, _P, _PP],
+    "vyb_graph_value": [_P, _U, C.POINTER(GraphValueInfo)],
+    "vyb_graph_node": [_P, _U, C.POINTER(GraphNodeInfo)],
+    "vyb_graph_node_input": [_P, _U, _U, C.POINTER(GraphInput)],
+    "vyb_graph_node_output": [_P, _U, _U, C.POINTER(GraphOutput), C.POINTER(C.c_uint32)],
     "vyb_safetensors_open": [_S, _PP],
     "vyb_safetensors_entry": [_P, _U, C.POINTER(SafetensorEntry)],
     "vyb_safetensors_find": [_P, _S, C.POINTER(C.c_uint32)],
@@ -238,6 +271,10 @@ _OTHER_FUNCS = {
     "vyb_artifact_free": (None, [_P]),
     "vyb_payload_digest": (None, [_P, C.c_char_p]),
     "vyb_payload_neutral_artifact": (None, [_P, C.c_char_p]),
+    "vyb_graph_free": (None, [_P]),
+    "vyb_graph_node_count": (C.c_uint32, [_P]),
+    "vyb_graph_value_count": (C.c_uint32, [_P]),
+    "vyb_graph_digest": (None, [_P, C.c_char_p]),
     "vyb_safetensors_free": (None, [_P]),
     "vyb_safetensors_identity": (None, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vyb_safetensors_count": (C.c_uint32, [_P]),
