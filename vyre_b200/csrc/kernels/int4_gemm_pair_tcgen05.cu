@@ -462,6 +462,11 @@ cudaError_t launch_int4_gemm_pair(const void* x_bf16, const void* w_packed, cons
     Params p{};
     p.m_tiles = (m + 2 * BM - 1) / (2 * BM);
     p.bn = choose_bn(n, glu != 0);
+    // Few tiles (a decode-sized batch, or one expert's rows on an expert-parallel rank): with 256-wide tiles a handful of
+    // tiles beyond one wave of CTA pairs costs a whole second wave (5 row tiles x 16 column tiles = 80 tiles on 74 pairs
+    // is two waves). 128-wide tiles halve that granularity; they amortise the activation operand less well, which only
+    // matters once there are many waves.
+    if (!glu && p.bn == 256 && uint64_t(p.m_tiles) * ((n + 255) / 256) < 4ull * pairs_avail) p.bn = 128;
     const uint32_t cols = glu ? p.bn / 2 : p.bn;
     p.n_tiles = (n + cols - 1) / cols;
     p.scales = static_cast<const uint16_t*>(scale_bf16);

@@ -15,6 +15,8 @@
 // with vyre-libs/src/nn/activation/swiglu.rs:26 (expert), vyre-libs/src/nn/moe/moe_layer.rs:33-121 (combine); the
 // reference ops are single-token, this is their batched composition.
 #include <cuda_bf16.h>
+
+#include <algorithm>
 #include <float.h>
 
 #include "kernels.h"
@@ -31,7 +33,7 @@ __device__ __forceinline__ float bf16_bits_to_float(uint32_t b) { return __uint_
 
 // ---- router + gate: one warp per token; a CTA keeps the router weights in shared memory and walks many tokens -------
 template <bool WR_IN_SMEM>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 moe_router_gate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w_router, uint32_t* __restrict__ idx,
                        float* __restrict__ wts, uint32_t tokens, uint32_t hidden, uint32_t experts, uint32_t topk) {
     extern __shared__ __align__(16) uint8_t s_dyn[];
@@ -47,21 +49,56 @@ moe_router_gate_kernel(const uint16_t* __restrict__ x, const uint16_t* __restric
     }
     for (uint32_t t = blockIdx.x * 8 + warp; t < tokens; t += gridDim.x * 8) {
     const uint16_t* xr = x + size_t(t) * hidden;
+    // The token's row is fetched whole before any arithmetic (up to 16 independent 16-byte loads per lane, 8 K elements
+    // per warp): with one load per 256-element step, as before, a token cost sixteen dependent trips to L2 / HBM. The
+    // arithmetic order is unchanged (a lane sums its own elements in k order, lanes fold by shuffles).
+    constexpr uint32_t XCHUNKS = 16;
+    uint4 xrow[XCHUNKS];
+    const uint32_t nchunks = (hidden + 255) / 256;
+    if (nchunks <= XCHUNKS) {
+#pragma unroll
+        for (uint32_t c = 0; c < XCHUNKS; ++c) {
+            const uint32_t k = c * 256 + lane * 8;
+            xrow[c] = k < hidden ? __ldg(reinterpret_cast<const uint4*>(xr + k)) : make_uint4(0, 0, 0, 0);
+        }
+    }
     for (uint32_t e0 = 0; e0 < experts; e0 += 8) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const uint32_t ne = min(8u, experts - e0);
-        for (uint32_t k = lane * 8; k < hidden; k += 256) {  // hidden % 8 == 0
-            const uint4 xv = *reinterpret_cast<const uint4*>(xr + k);
-            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-            for (uint32_t e = 0; e < 8; ++e) {
-                if (e < ne) {
-                    const uint4 wv = *reinterpret_cast<const uint4*>(wr + size_t(e0 + e) * hidden + k);
-                    const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        for (uint32_t c = 0; c < XCHUNKS; ++c) {
+            const uint32_t k = c * 256 + lane * 8;  // hidden % 8 == 0
+            if (nchunks <= XCHUNKS && k < hidden) {
+                const uint4 xv = xrow[c];
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        acc[e] = fmaf(bf16_bits_to_float(xw[q] & 0xFFFFu), bf16_bits_to_float(ww[q] & 0xFFFFu), acc[e]);
-                        acc[e] = fmaf(bf16_bits_to_float(xw[q] >> 16), bf16_bits_to_float(ww[q] >> 16), acc[e]);
+                for (uint32_t e = 0; e < 8; ++e) {
+                    if (e < ne) {
+                        const uint4 wv = *reinterpret_cast<const uint4*>(wr + size_t(e0 + e) * hidden + k);
+                        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            acc[e] = fmaf(bf16_bits_to_float(xw[q] & 0xFFFFu), bf16_bits_to_float(ww[q] & 0xFFFFu), acc[e]);
+                            acc[e] = fmaf(bf16_bits_to_float(xw[q] >> 16), bf16_bits_to_float(ww[q] >> 16), acc[e]);
+                        }
+                    }
+                }
+            }
+        }
+        if (nchunks > XCHUNKS) {  // rows longer than 4096 elements: the plain loop
+            for (uint32_t k = lane * 8; k < hidden; k += 256) {
+                const uint4 xv = *reinterpret_cast<const uint4*>(xr + k);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (uint32_t e = 0; e < 8; ++e) {
+                    if (e < ne) {
+                        const uint4 wv = *reinterpret_cast<const uint4*>(wr + size_t(e0 + e) * hidden + k);
+                        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            acc[e] = fmaf(bf16_bits_to_float(xw[q] & 0xFFFFu), bf16_bits_to_float(ww[q] & 0xFFFFu), acc[e]);
+                            acc[e] = fmaf(bf16_bits_to_float(xw[q] >> 16), bf16_bits_to_float(ww[q] >> 16), acc[e]);
+                        }
                     }
                 }
             }
@@ -122,7 +159,8 @@ cudaError_t launch_router_gate(const uint16_t* x, const uint16_t* w_router, uint
             if (e != cudaSuccess) return e;
             configured[dev & 63] = true;
         }
-        const uint32_t grid = min(want_blocks, uint32_t(sm_count));
+        const uint32_t per_sm = uint32_t(std::max<size_t>(1, std::min<size_t>(2, (200 * 1024) / std::max<size_t>(wr_bytes, 1))));
+        const uint32_t grid = min(want_blocks, uint32_t(sm_count) * per_sm);
         moe_router_gate_kernel<true><<<grid, 256, wr_bytes, stream>>>(x, w_router, idx, wts, tokens, hidden, experts, topk);
     } else {
         moe_router_gate_kernel<false><<<want_blocks, 256, 0, stream>>>(x, w_router, idx, wts, tokens, hidden, experts, topk);
