@@ -649,9 +649,9 @@ def run_native(args) -> None:
             for c in range(LAUNCHES):
                 launch(c % COPIES)
             return
-        # GEMV c stores its outputs straight into buffer half c % 2 of every rank: GEMV and all-gather are one launch (peer
-        # stores over NVLink from the reduction that produces the outputs), the launches stay one programmatic chain, and
-        # the replay ends with the bounded wait for its own gathers
+        # GEMV and all-gather are one kernel and one programmatic chain: launch c writes buffer half c % 2 on this rank and,
+        # by peer stores over NVLink from the same kernel, on every other rank. The replay ends with the bounded wait for its
+        # own gathers. (The pipelined form, where launch c + 1 carries launch c's outputs over, measured no faster.)
         for c in range(LAUNCHES):
             pag.gemv(c & 1, x, ws[c % COPIES], ss[c % COPIES], K_IN, stream.cuda_stream, status, gemv_flags)
         pag.wait(stream.cuda_stream, status)
@@ -839,7 +839,7 @@ def run_native(args) -> None:
         "dtype": "bf16xint4->f32", "data": "synthetic",
         "config": {"workload": workload_name(m)},
         "run": {"per_gpu_shard": [N_OUT, K_IN],
-                "parallelism": f"column-parallel x{world}" + (" + all-gather by peer stores from the GEMV's own reduction (NVLink), one launch" if world > 1 else ""),
+                "parallelism": f"column-parallel x{world}" + (" + all-gather by peer stores over NVLink from the GEMV kernel itself, one launch" if world > 1 else ""),
                 "l2_policy": f"inputs larger than L2: {COPIES} rotating weight copies = {COPIES * (N_OUT * K_IN // 2) / 1e6:.0f} MB",
                 "launch": f"CUDA graph of {LAUNCHES} launches per step ({PASSES} passes over the {COPIES} copies), programmatic dependent launch (constant weights)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],

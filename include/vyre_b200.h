@@ -594,7 +594,12 @@ int32_t vyb_k_allgather_wait(const vyb_allgather_ctx* ctx, void* stream, uint32_
  * the arrival signal of a launch is sent by the next launch of this kind or by vyb_k_allgather_wait, which a stream
  * must run before it reads a gathered result. Halves must alternate from launch to launch; before it overwrites a
  * half on a peer a launch checks (bounded, status bit 128) that the peer has signalled its previous launch. epoch must
- * point to 16 zeroed local words. 1 <= m <= 4, group 128, k 2048 or 4096. */
+ * point to 16 zeroed local words. 1 <= m <= 4, group 128, k 2048 or 4096.
+ * VYB_LAUNCH_PIPELINED_GATHER: a launch cannot end before its peer stores have drained (an NVLink round trip), which
+ * delays the next launch of a dependent chain. With this flag a launch stores its outputs into the LOCAL buffer only;
+ * the NEXT launch of this kind (same m and n) carries them to the peers right after its dependency wait, so that the
+ * stores drain under its own work, and vyb_k_allgather_wait carries the last slice over. A gathered result is complete
+ * one launch later. Do not mix flagged and unflagged launches between two waits. */
 int32_t vyb_k_int4_gemv_allgather(const vyb_allgather_ctx* ctx, uint32_t half, const void* x_bf16, const void* w_packed,
                                   const void* scale_bf16, uint32_t m, uint32_t n, uint32_t k, uint32_t group_size,
                                   uint32_t flags, void* stream, uint32_t* status);
@@ -642,6 +647,7 @@ int32_t vyb_k_int8_gemm_i32(const void* a_i8, const void* w_i8, void* out_i32, u
  * that a copy kernel of another stream (vyb_k_colpar_push of the previous row chunk) runs beside it instead of
  * behind it. */
 #define VYB_LAUNCH_LEAVE_COPY_SMS 4u
+#define VYB_LAUNCH_PIPELINED_GATHER 8u /* vyb_k_int4_gemv_allgather: see there */
 int32_t vyb_k_int8_gemm_i32_ex(const void* a_i8, const void* w_i8, void* out_i32, uint32_t m, uint32_t n, uint32_t k,
                                uint32_t flags, void* stream, uint32_t* status);
 /* The fused multi-token MoE FFN layer of vyb_nn_moe_ffn_int4 on raw device pointers (same operands, layouts and

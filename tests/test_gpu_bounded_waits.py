@@ -94,6 +94,17 @@ def test_gathering_gemv_single_rank_matches_plain_kernel_and_keeps_its_books():
             assert torch.equal(pag.halves()[half][0].view(torch.int16), want.view(torch.int16)), (m, n, k, half)
         words = pag.local.cpu().tolist()
         assert words[0] == 5 and words[10] == 4 and words[11] == 5 and words[12] == 0, words[:16]
+        # the pipelined form keeps its outputs local until the next launch (or the wait) carries them over
+        pag.halves().zero_()
+        for step in range(5, 8):
+            pag.gemv(step & 1, tx, tw, ts, k, stream, status, ffi.LAUNCH_CONSTANT_WEIGHTS | ffi.LAUNCH_PIPELINED_GATHER)
+        torch.cuda.synchronize()
+        assert pag.local.cpu().tolist()[13] == 2  # launch 7 wrote half 1 (marker = half + 1) and left it to its successor
+        pag.wait(stream, status)
+        torch.cuda.synchronize()
+        assert status.cpu().tolist() == [0, 0, 0, 0] and pag.local.cpu().tolist()[13] == 0
+        for half in (0, 1):
+            assert torch.equal(pag.halves()[half][0].view(torch.int16), want.view(torch.int16)), (m, n, k, half, "pipelined")
 
 
 def test_gathering_gemv_wait_on_a_silent_peer_runs_out():

@@ -142,9 +142,10 @@ def _worker(rank: int, world: int, port: int, q):
             dist.barrier()
         # ---- GEMV and gather in one launch (peer stores from the reduction), a chain of launches, then the wait ------
         pag3 = sharding.PeerAllGather(m, n)
-        for rounds in range(2):
+        for rounds in range(4):  # two rounds with the stores in the producing launch, two with the pipelined form
+            flags = ffi.LAUNCH_CONSTANT_WEIGHTS | (ffi.LAUNCH_PIPELINED_GATHER if rounds >= 2 else 0)
             for step in range(6):  # halves alternate; programmatic chain, no host sync in between
-                pag3.gemv(step & 1, tx2, tw2_, ts2_, k, cur, status, ffi.LAUNCH_CONSTANT_WEIGHTS)
+                pag3.gemv(step & 1, tx2, tw2_, ts2_, k, cur, status, flags)
             pag3.wait(cur, status)
             torch.cuda.synchronize()
             assert status.cpu().tolist() == [0, 0, 0, 0]

@@ -1290,7 +1290,8 @@ int32_t vyb_k_int4_gemv_allgather(const vyb_allgather_ctx* ctx, uint32_t half, c
     }
     return launch_result(vybk::launch_int4_gemv_halfsm(x_bf16, w_packed, scale_bf16, nullptr, m, n, k, 0, sms,
                                                        static_cast<cudaStream_t>(stream), status,
-                                                       (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0, &ag, half),
+                                                       (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0, &ag, half,
+                                                       (flags & VYB_LAUNCH_PIPELINED_GATHER) != 0),
                          "gathering int4 gemv");
 }
 

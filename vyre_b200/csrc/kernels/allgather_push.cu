@@ -53,9 +53,32 @@ __global__ void __launch_bounds__(128, 16) allgather_push_kernel(const PeerGathe
     }
 }
 
-__global__ void __launch_bounds__(32) allgather_wait_kernel(const PeerGather ag, uint32_t* status) {
-    send_owed_signal(ag, threadIdx.x);  // of a fused GEMV launch before this kernel in the stream
-    const uint32_t done = *reinterpret_cast<const volatile uint32_t*>(ag.epoch);
+__global__ void __launch_bounds__(256) allgather_wait_kernel(const PeerGather ag, uint32_t* status) {
+    volatile uint32_t* e = reinterpret_cast<volatile uint32_t*>(ag.epoch);
+    if (threadIdx.x < 32) send_owed_signal(ag, threadIdx.x);  // of a fused GEMV launch before this kernel in the stream
+    const uint32_t done = e[0];
+    const uint32_t pending = e[EPOCH_PUSH];
+    __syncthreads();
+    if (pending != 0) {
+        // the last launch of a pipelined chain left its slice in local memory: carry it to the peers and signal it
+        bool fine = true;
+        if (threadIdx.x < ag.world && threadIdx.x != ag.rank && done >= 2) fine = wait_pushes_from(ag, threadIdx.x, done - 2, status);
+        if (!fine && status) atomicOr(status, 128u);
+        __syncthreads();
+        const size_t elems = size_t(e[EPOCH_PUSH_M]) * e[EPOCH_PUSH_N];
+        const size_t base = (size_t(pending - 1) * ag.world + ag.rank) * elems;
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(ag.peer_out[ag.rank]) + base;
+        for (size_t i = threadIdx.x; i < elems; i += blockDim.x) {
+            const uint16_t v = src[i];
+            for (uint32_t q = 0; q < ag.world; ++q)
+                if (q != ag.rank) reinterpret_cast<uint16_t*>(ag.peer_out[q])[base + i] = v;
+        }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < ag.world && threadIdx.x != ag.rank)
+            atomicAdd_system(const_cast<uint32_t*>(counter_from(ag, threadIdx.x, ag.rank)), 1u);
+        if (threadIdx.x == 0) e[EPOCH_PUSH] = 0;
+    }
     bool ok = true;
     if (threadIdx.x < ag.world && threadIdx.x != ag.rank) ok = wait_pushes_from(ag, threadIdx.x, done, status);
     __threadfence_system();  // acquire side: the peers' stores are visible to whatever follows in this stream
@@ -155,7 +178,7 @@ cudaError_t launch_allgather_push(const PeerGather& ag, uint32_t half, uint32_t 
 
 cudaError_t launch_allgather_wait(const PeerGather& ag, cudaStream_t stream, uint32_t* status) {
     if (ag.world < 1 || ag.world > 8 || ag.rank >= ag.world) return cudaErrorInvalidValue;
-    allgather_wait_kernel<<<1, 32, 0, stream>>>(ag, status);
+    allgather_wait_kernel<<<1, 256, 0, stream>>>(ag, status);
     return cudaGetLastError();
 }
 

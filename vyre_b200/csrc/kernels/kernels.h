@@ -21,7 +21,7 @@ bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t gro
 cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                                     uint32_t* status, bool constant_weights, const PeerGather* gather = nullptr,
-                                    uint32_t half = 0);
+                                    uint32_t half = 0, bool pipelined = false);
 // ---- all-gather of column-parallel outputs over peer memory (allgather_push.cu) ------------------------------------
 // gather buffers [2][world][m][n] bf16 per rank; arrival counters and launch counters are 32-bit device words,
 // zero before the first push

@@ -13,6 +13,8 @@ constexpr uint32_t PEER_COUNTER_STRIDE = 8;           // 32-bit words between th
 // local words of a context (PeerGather::epoch): [0, 8) pushes completed per peer slot, [8, 10) tickets,
 // [10, 12) the launch index handed from one fused GEMV launch to the next (one word per buffer half), [12] a signal owed
 constexpr uint32_t EPOCH_TICKET = 8, EPOCH_INDEX = 10, EPOCH_OWED = 12;
+// [13] a slice that still has to be pushed to the peers (1 + its buffer half; 0: none), [14], [15] its batch rows and width
+constexpr uint32_t EPOCH_PUSH = 13, EPOCH_PUSH_M = 14, EPOCH_PUSH_N = 15;
 
 __device__ __forceinline__ const volatile uint32_t* counter_from(const PeerGather& ag, uint32_t owner, uint32_t source) {
     return reinterpret_cast<const volatile uint32_t*>(ag.peer_flag[owner]) + source * PEER_COUNTER_STRIDE;

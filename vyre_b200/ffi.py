@@ -18,6 +18,7 @@ BIND_HOST, BIND_RESIDENT = 0, 1
 LAUNCH_CONSTANT_WEIGHTS = 1
 LAUNCH_LEAVE_ONE_SM = 2
 LAUNCH_LEAVE_COPY_SMS = 4
+LAUNCH_PIPELINED_GATHER = 8
 
 ERR_DEVICE_OUT_OF_MEMORY = 1001
 ERR_UNSUPPORTED_FEATURE = 1002
