@@ -102,6 +102,34 @@ struct Params {
     uint32_t* status;
 };
 
+// Pipelined gathering form, kept out of line (the kernel below runs at the edge of its register budget): carry the
+// predecessor's slice, which sits in the other buffer half of local memory, to the peers. The stores drain under this
+// launch's tiles. The peers are past whatever consumed the slice this one replaces when they have signalled two launches
+// back (a signal sent a whole launch ago, so this does not wait in a healthy run). Bounded; status bit 128.
+__device__ __noinline__ void gather_carry(const Params& p, uint32_t r0, uint32_t nrows) {
+    const uint32_t lane = threadIdx.x & 31;
+    volatile uint32_t* e = reinterpret_cast<volatile uint32_t*>(p.ag.epoch);
+    const uint32_t pending = e[EPOCH_PUSH];
+    uint32_t pushed = 0;
+    if (pending == (p.half ^ 1u) + 1 && p.ag.world > 1) {  // halves alternate: the slice left by the launch before
+        const uint32_t index = e[EPOCH_INDEX + p.half];
+        if (lane < p.ag.world && lane != p.ag.rank && index >= 2 && !wait_pushes_from(p.ag, lane, index - 2, p.status) && p.status)
+            atomicOr(p.status, 128u);
+        __syncwarp();
+        const size_t base = (size_t(pending - 1) * p.ag.world + p.ag.rank) * p.m * p.n;
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(p.ag.peer_out[p.ag.rank]) + base;
+        for (uint32_t i = threadIdx.x; i < nrows * p.m; i += blockDim.x) {
+            const size_t at = size_t(i / nrows) * p.n + r0 + i % nrows;
+            const uint16_t v = __ldcg(src + at);
+            for (uint32_t q = 0; q < p.ag.world; ++q)
+                if (q != p.ag.rank) reinterpret_cast<uint16_t*>(p.ag.peer_out[q])[base + at] = v;
+        }
+        pushed = 1;
+    }
+    // what this launch carries over is complete when the launch ends: the signal for it is owed to the next launch
+    if (blockIdx.x == 0 && threadIdx.x == 0) e[EPOCH_OWED] = pushed;
+}
+
 // NM = MMAs per 16 rows x 32 k = ceil(m / 2); W warps, each owning GPW 128-k groups of every row: k = 128 GPW W
 // GATHER: a column-parallel shard whose bf16 outputs are stored straight into every rank's gather buffer (peer stores over
 // NVLink from the reduction that produces them), so that the all-gather is part of the launch and consecutive launches
@@ -109,13 +137,12 @@ struct Params {
 // next on the stream (launch d + 1 or the wait kernel), when launch d is complete and its stores are visible. Before it
 // stores into a peer's half, a launch checks (bounded) that this peer has signalled launch d - 1: then the peer is past
 // whatever consumed launch d - 2 from the same half. Buffer halves must alternate from launch to launch.
-// Pipelined form: a launch cannot end before its peer stores have drained (an NVLink round trip), and the next launch's
-// activations wait for exactly that. So launch d stores into the LOCAL buffer only and leaves its slice to launch d + 1,
-// whose CTAs copy their own rows of it to the peers right after the dependency wait: those stores drain under launch
-// d + 1's six tiles. The arrival signal for slice d is then sent by launch d + 2 (or the wait kernel, which also pushes
-// the last slice). A gathered result is complete one launch later than in the plain form.
+// Pipelined form (Params::pipelined): a launch cannot end before its peer stores have drained (an NVLink round trip), and
+// the next launch's activations wait for exactly that. So launch d stores into the LOCAL buffer only and leaves its slice
+// to launch d + 1, whose CTAs copy their own rows of it to the peers right after the dependency wait (gather_carry). The
+// arrival signal for slice d is then sent by launch d + 2, or by the wait kernel, which also carries the last slice over.
 template <int NM, int GPW, int W, bool OUT_F32, bool GATHER>
-__global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Params p) {
+__global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // let the next launch of the stream become resident beside this one at once; it waits (griddepcontrol.wait)
     // before it reads activations or writes outputs. A no-op for plain launches.
@@ -196,35 +223,11 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
 
     // ---- activations: everything below reads x, so the previous launch of the stream must be complete ----
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    // GATHER: how many gathering launches this rank has completed before this one is read from the word of this launch's
-    // buffer half wherever it is needed (the previous launch wrote it, this launch writes only the other half's word), so
-    // that nothing of the gather lives in a register across the tile loop: that loop has none to spare.
-    auto launch_index_now = [&]() -> uint32_t {
-        return *(reinterpret_cast<const volatile uint32_t*>(p.ag.epoch) + EPOCH_INDEX + p.half);
-    };
+    uint32_t launch_index = 0;  // GATHER: how many gathering launches this rank has completed before this one
     if constexpr (GATHER) {
+        launch_index = *(reinterpret_cast<const volatile uint32_t*>(p.ag.epoch) + EPOCH_INDEX + p.half);
         if (blockIdx.x == 0 && warp == 0) send_owed_signal(p.ag, lane);  // the previous launch's arrival
-    }
-    // Pipelined gather, part one: everything this launch needs in order to carry its predecessor's slice to the peers is
-    // LOADED here, right behind the dependency wait and beside the activation loads below, and used only after the
-    // activations are converted, so that the extra round trips to L2 hide under that work: the pending marker, this
-    // thread's element(s) of the slice (it sits in the other buffer half), and (lanes < world) the peer's arrival counter.
-    uint32_t carry_pending = 0, peer_arrived = 0, carry_index = 0;
-    constexpr uint32_t CARRY = (TILE_ROWS * 7 * 2 * NM + W * 32 - 1) / (W * 32);  // elements per thread: at most 7 tiles x batch rows
-    uint16_t carry[CARRY];
-    if constexpr (GATHER) {
-        if (p.pipelined && p.ag.world > 1) {
-            carry_pending = *(reinterpret_cast<const volatile uint32_t*>(p.ag.epoch) + EPOCH_PUSH);
-            carry_index = launch_index_now();
-            if (lane < p.ag.world && lane != p.ag.rank) peer_arrived = *counter_from(p.ag, p.ag.rank, lane);
-            const size_t base = (size_t(p.half ^ 1u) * p.ag.world + p.ag.rank) * p.m * p.n;  // halves alternate
-            const uint16_t* src = reinterpret_cast<const uint16_t*>(p.ag.peer_out[p.ag.rank]) + base;
-#pragma unroll
-            for (uint32_t c = 0; c < CARRY; ++c) {
-                const uint32_t i = threadIdx.x + c * (W * 32);
-                carry[c] = i < nrows * p.m ? __ldcg(src + size_t(i / nrows) * p.n + r0 + i % nrows) : uint16_t(0);
-            }
-        }
+        if (p.pipelined) gather_carry(p, r0, nrows);
     }
     uint32_t xb[NM][GPW][8];  // [mma][group of this warp][byte block 0 | 1][operand 0 | 1][bytes 0-3 | 4-7]
     float dq[NM][GPW];        // delta / 16 of (batch row of this lane's D columns, group), x 65536 for the high digit pair
@@ -429,36 +432,17 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
         }
     }
 
-    // Pipelined gather, part two: the stores. The peers are past whatever consumed the slice this one replaces when they
-    // have signalled two launches back (sent a whole launch ago: the counter loaded above normally says so already;
-    // otherwise a bounded wait, status bit 128). Every warp checks for itself, so no barrier is needed.
-    if constexpr (GATHER) {
-        uint32_t pushed = 0;  // this launch carries its predecessor's slice to the peers
-        if (p.pipelined && carry_pending != 0 && carry_pending == (p.half ^ 1u) + 1 && p.ag.world > 1 && nrows * p.m <= CARRY * W * 32) {
-            bool ok = true;
-            if (lane < p.ag.world && lane != p.ag.rank && carry_index >= 2 && int32_t(peer_arrived - (carry_index - 2)) < 0)
-                ok = wait_pushes_from(p.ag, lane, carry_index - 2, p.status);
-            if (!ok && p.status) atomicOr(p.status, 128u);
-            __syncwarp();
-            const size_t base = (size_t(carry_pending - 1) * p.ag.world + p.ag.rank) * p.m * p.n;
-#pragma unroll
-            for (uint32_t c = 0; c < CARRY; ++c) {
-                const uint32_t i = threadIdx.x + c * (W * 32);
-                if (i < nrows * p.m) {
-                    const size_t at = base + size_t(i / nrows) * p.n + r0 + i % nrows;
-                    for (uint32_t q = 0; q < p.ag.world; ++q)
-                        if (q != p.ag.rank) reinterpret_cast<uint16_t*>(p.ag.peer_out[q])[at] = carry[c];
-                }
-            }
-            pushed = 1;
-        }
-        // what this launch carries over is complete when the launch ends: the signal for it is owed to the next launch
-        if (p.pipelined && blockIdx.x == 0 && threadIdx.x == 0)
-            *(reinterpret_cast<volatile uint32_t*>(p.ag.epoch) + EPOCH_OWED) = pushed;
-    }
-
     // sum the warps' partials of the tiles [first, first + count) in warp order and store the outputs
+    bool peers_checked = false;
     auto reduce_tiles = [&](uint32_t first, uint32_t count) {
+        if constexpr (GATHER) {
+            // every peer has signalled its launch before this one (sent when this launch began over there, microseconds
+            // ago): its consumers of the half about to be overwritten have run. Bounded; status bit 128 when it runs out.
+            if (!peers_checked && !p.pipelined && warp == 0 && lane < p.ag.world && lane != p.ag.rank &&
+                !wait_pushes_from(p.ag, lane, launch_index, p.status) && p.status)
+                atomicOr(p.status, 128u);
+            peers_checked = true;
+        }
         __syncthreads();
         for (uint32_t idx = threadIdx.x; idx < count * (TILE_ROWS * MM); idx += W * 32) {
             const uint32_t col = idx % MM, row = r0 + first * TILE_ROWS + idx / MM;
@@ -467,7 +451,13 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
 #pragma unroll
             for (int w = 0; w < W; ++w) sum += src[w * (PRIV / 4)];
             if (row < r1 && col < p.m) {
-                if constexpr (OUT_F32) {
+                if constexpr (GATHER) {
+                    const size_t at = (size_t(p.half) * p.ag.world + p.ag.rank) * p.m * p.n + size_t(col) * p.n + row;
+                    const __nv_bfloat16 v = __float2bfloat16_rn(sum);
+                    // plain form: every rank's buffer; pipelined form: this rank's only (the next launch carries it over)
+                    const uint32_t q0 = p.pipelined ? p.ag.rank : 0u, q1 = p.pipelined ? p.ag.rank + 1 : p.ag.world;
+                    for (uint32_t q = q0; q < q1; ++q) reinterpret_cast<__nv_bfloat16*>(p.ag.peer_out[q])[at] = v;
+                } else if constexpr (OUT_F32) {
                     static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
                 } else {
                     static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
@@ -542,52 +532,45 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
         if constexpr (NM == 1) {
             // The four MMAs of a group form a dependent chain (about 25 cycles each), so the groups are interleaved: every
             // step issues one MMA of each group, and a group's next MMA finds its accumulators ready.
-            constexpr int IL = GPW;  // all groups at once (two at a time was measured slower: the allocator spills more, not less)
+            int acc[GPW][NM][4];
 #pragma unroll
-            for (int c0 = 0; c0 < GPW; c0 += IL) {
-                int acc[IL][NM][4];
+            for (int blk = 0; blk < 2; ++blk) {
+                // raw bytes against 16 X0 ...
 #pragma unroll
-                for (int blk = 0; blk < 2; ++blk) {
-                    // raw bytes against 16 X0 ...
-#pragma unroll
-                    for (int ci = 0; ci < IL; ++ci) {
-                        const int c = c0 + ci;
-                        const uint32_t a0 = blk ? wl[c].z : wl[c].x, a1 = blk ? wh[c].z : wh[c].x;
-                        const uint32_t a2 = blk ? wl[c].w : wl[c].y, a3 = blk ? wh[c].w : wh[c].y;
-#pragma unroll
-                        for (int nm = 0; nm < NM; ++nm) {
-                            if (blk == 0)  // the group's accumulators start from the zero-point term (all of it in the low digit)
-                                mma_u8s8(acc[ci][nm], a0, a1, a2, a3, xb[nm][c][0], xb[nm][c][1], corr[nm][c], 0, corr[nm][c], 0);
-                            else
-                                mma_u8s8(acc[ci][nm], a0, a1, a2, a3, xb[nm][c][4], xb[nm][c][5], acc[ci][nm][0], acc[ci][nm][1],
-                                         acc[ci][nm][2], acc[ci][nm][3]);
-                        }
-                    }
-                    // ... then masked bytes against X1 - 16 X0
-#pragma unroll
-                    for (int ci = 0; ci < IL; ++ci) {
-                        const int c = c0 + ci;
-                        const uint32_t m0 = (blk ? wl[c].z : wl[c].x) & 0xF0F0F0F0u, m1 = (blk ? wh[c].z : wh[c].x) & 0xF0F0F0F0u;
-                        const uint32_t m2 = (blk ? wl[c].w : wl[c].y) & 0xF0F0F0F0u, m3 = (blk ? wh[c].w : wh[c].y) & 0xF0F0F0F0u;
-#pragma unroll
-                        for (int nm = 0; nm < NM; ++nm)
-                            mma_u8s8(acc[ci][nm], m0, m1, m2, m3, xb[nm][c][4 * blk + 2], xb[nm][c][4 * blk + 3], acc[ci][nm][0],
-                                     acc[ci][nm][1], acc[ci][nm][2], acc[ci][nm][3]);
-                    }
-                }
-#pragma unroll
-                for (int ci = 0; ci < IL; ++ci) {
-                    const int c = c0 + ci;
-                    const float s_lo = (c & 1) ? bf16_hi(sa[c >> 1]) : bf16_lo(sa[c >> 1]);
-                    const float s_hi = (c & 1) ? bf16_hi(sb[c >> 1]) : bf16_lo(sb[c >> 1]);
+                for (int c = 0; c < GPW; ++c) {
+                    const uint32_t a0 = blk ? wl[c].z : wl[c].x, a1 = blk ? wh[c].z : wh[c].x;
+                    const uint32_t a2 = blk ? wl[c].w : wl[c].y, a3 = blk ? wh[c].w : wh[c].y;
 #pragma unroll
                     for (int nm = 0; nm < NM; ++nm) {
-                        // |accumulators| < 2^22 per group and |zero-point term| < 2^29: d_lo + 256 d_hi stays below 2^31
-                        const float v_lo = float(acc[ci][nm][0] + (acc[ci][nm][1] << 8));
-                        const float v_hi = float(acc[ci][nm][2] + (acc[ci][nm][3] << 8));
-                        P[nm][0] = fmaf(s_lo * dq[nm][c], v_lo, P[nm][0]);
-                        P[nm][1] = fmaf(s_hi * dq[nm][c], v_hi, P[nm][1]);
+                        if (blk == 0)  // the group's accumulators start from the zero-point term (all of it in the low digit)
+                            mma_u8s8(acc[c][nm], a0, a1, a2, a3, xb[nm][c][0], xb[nm][c][1], corr[nm][c], 0, corr[nm][c], 0);
+                        else
+                            mma_u8s8(acc[c][nm], a0, a1, a2, a3, xb[nm][c][4], xb[nm][c][5], acc[c][nm][0], acc[c][nm][1],
+                                     acc[c][nm][2], acc[c][nm][3]);
                     }
+                }
+                // ... then masked bytes against X1 - 16 X0
+#pragma unroll
+                for (int c = 0; c < GPW; ++c) {
+                    const uint32_t m0 = (blk ? wl[c].z : wl[c].x) & 0xF0F0F0F0u, m1 = (blk ? wh[c].z : wh[c].x) & 0xF0F0F0F0u;
+                    const uint32_t m2 = (blk ? wl[c].w : wl[c].y) & 0xF0F0F0F0u, m3 = (blk ? wh[c].w : wh[c].y) & 0xF0F0F0F0u;
+#pragma unroll
+                    for (int nm = 0; nm < NM; ++nm)
+                        mma_u8s8(acc[c][nm], m0, m1, m2, m3, xb[nm][c][4 * blk + 2], xb[nm][c][4 * blk + 3], acc[c][nm][0],
+                                 acc[c][nm][1], acc[c][nm][2], acc[c][nm][3]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < GPW; ++c) {
+                const float s_lo = (c & 1) ? bf16_hi(sa[c >> 1]) : bf16_lo(sa[c >> 1]);
+                const float s_hi = (c & 1) ? bf16_hi(sb[c >> 1]) : bf16_lo(sb[c >> 1]);
+#pragma unroll
+                for (int nm = 0; nm < NM; ++nm) {
+                    // |accumulators| < 2^22 per group and |zero-point term| < 2^29: d_lo + 256 d_hi stays below 2^31
+                    const float v_lo = float(acc[c][nm][0] + (acc[c][nm][1] << 8));
+                    const float v_hi = float(acc[c][nm][2] + (acc[c][nm][3] << 8));
+                    P[nm][0] = fmaf(s_lo * dq[nm][c], v_lo, P[nm][0]);
+                    P[nm][1] = fmaf(s_hi * dq[nm][c], v_hi, P[nm][1]);
                 }
             }
         } else {  // two MMAs per step already overlap; interleaving the groups as well costs registers this variant lacks
@@ -642,30 +625,10 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const Param
     cp_async_wait<0>();
     if (pending) reduce_tiles(ntiles - pending, pending);
     if constexpr (GATHER) {
-        // The reduction above is the plain kernel's, into this rank's own slice (p.y points there): the tile loop and the
-        // reduction inside it are the same code in every variant. The plain gathering form now copies this CTA's rows to
-        // the peers; the pipelined form leaves that to the next launch.
-        if (!p.pipelined && p.ag.world > 1) {
-            // every peer has signalled its launch before this one (sent when this launch began over there, microseconds
-            // ago): its consumers of the half about to be overwritten have run. Bounded; status bit 128 when it runs out.
-            if (warp == 0 && lane < p.ag.world && lane != p.ag.rank && !wait_pushes_from(p.ag, lane, launch_index_now(), p.status) &&
-                p.status)
-                atomicOr(p.status, 128u);
-            __syncthreads();  // also: this CTA's outputs are written
-            const size_t base = (size_t(p.half) * p.ag.world + p.ag.rank) * p.m * p.n;
-            const uint16_t* src = static_cast<const uint16_t*>(p.y);
-            for (uint32_t i = threadIdx.x; i < nrows * p.m; i += W * 32) {
-                const size_t at = size_t(i / nrows) * p.n + r0 + i % nrows;
-                const uint16_t v = src[at];
-                for (uint32_t q = 0; q < p.ag.world; ++q)
-                    if (q != p.ag.rank) reinterpret_cast<uint16_t*>(p.ag.peer_out[q])[base + at] = v;
-            }
-        }
         // one CTA hands the launch index to the next launch (which reads the other half's word), counts the launch for the
         // wait kernel and leaves the arrival signal owed
         if (blockIdx.x == 0 && threadIdx.x == 0) {
             volatile uint32_t* e = reinterpret_cast<volatile uint32_t*>(p.ag.epoch);
-            const uint32_t launch_index = launch_index_now();
             e[EPOCH_INDEX + (p.half ^ 1u)] = launch_index + 1;
             for (uint32_t i = 0; i + 1 < p.ag.world || i == 0; ++i) e[i] = launch_index + 1;
             if (p.pipelined) {
@@ -722,10 +685,7 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     p.status = status;  // only the gathering form has a wait that can run out
     p.half = half & 1u;
     p.pipelined = pipelined ? 1u : 0u;
-    if (gather) {
-        p.ag = *gather;
-        p.y = reinterpret_cast<uint16_t*>(gather->peer_out[gather->rank]) + (size_t(half & 1u) * gather->world + gather->rank) * m * n;
-    }
+    if (gather) p.ag = *gather;
     // One CTA per SM, whole 16-row tiles each, the remainder spread one tile per CTA (14336 rows on 148 SMs: eight
     // CTAs with 7 tiles, the others with 6). Measured against 128 CTAs x 7 tiles and against two CTAs per SM (which
     // leave no room for the next launch): this split is the fastest.
