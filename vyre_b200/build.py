@@ -36,6 +36,7 @@ SOURCES = {
     "kernels/dropin_fast.cu": ["-ftz=true", "-fmad=false"],
     "kernels/int4_gemv.cu": [],
     "kernels/int4_gemv_halfsm.cu": [],
+    "kernels/int4_gemv_batch8.cu": [],
     "kernels/int8_linear.cu": [],
     "kernels/int8_gemm_tcgen05.cu": [],
     "kernels/int8_gemm_pair_tcgen05.cu": [],
