@@ -39,6 +39,11 @@ extern "C" {
 #define VYB_ERR_COOPERATIVE_RESIDENCY_EXCEEDED 1007
 #define VYB_ERR_DEVICE_LOST 1008
 #define VYB_ERR_UNKNOWN 1999
+/* DispatchError of the self-substrate wrappers (vyre-self-substrate/src/optimizer/dispatcher.rs:100-120): Rejected,
+ * BadInputs, BackendError; the message carries the reference's Display prefix */
+#define VYB_ERR_DISPATCH_REJECTED 2001
+#define VYB_ERR_DISPATCH_BAD_INPUTS 2002
+#define VYB_ERR_DISPATCH_BACKEND 2003
 
 /* ---- DataType tags: vyre-spec/src/data_type.rs:2-8,227-257 ---------------------------------------- */
 #define VYB_DT_U32 0x01u
@@ -531,6 +536,49 @@ int32_t vyb_completion_output(const vyb_completion* c, uint32_t value_id, const 
 uint32_t vyb_completion_output_count(const vyb_completion* c);
 int32_t vyb_completion_device_ns(const vyb_completion* c, uint64_t* ns);
 void vyb_completion_free(vyb_completion* c);
+
+/* ---- scratch-reusing callers of the packed-int4 primitives -----------------------------------------------
+ * vyre-self-substrate/src/math/quantized_dispatch.rs:30-90 and quantized_dispatch/{unpack,dot,matvec,batched_matvec,
+ * batched_matmul,top1}.rs: the `*_via_with_scratch_into` functions. Host slices in (pointer + element count), host
+ * slice out (the caller provides exactly the documented number of elements), the shape checks and `Fix:` texts of
+ * the reference, one dispatch per call. The dispatcher is the device the scratch was made for. ONE scratch type
+ * serves all six wrappers (the reference has one struct per wrapper, each a Program cache plus staging vectors): it
+ * caches per (wrapper, shape) the Program, Artifact, TargetPayload and ArtifactInstance, so a repeated shape costs
+ * one submission. Calls on one scratch are serialised. Errors: VYB_ERR_DISPATCH_*. A scratch made with a NULL device
+ * validates shapes and refuses every dispatch (Rejected). */
+typedef struct vyb_quantized_scratch vyb_quantized_scratch;
+int32_t vyb_quantized_scratch_new(vyb_device* device, vyb_quantized_scratch** scratch);
+void vyb_quantized_scratch_free(vyb_quantized_scratch* scratch);
+void vyb_quantized_scratch_stats(const vyb_quantized_scratch* scratch, uint64_t* cached, uint64_t* hits, uint64_t* misses);
+/* unpack.rs:36-84: out_lanes has lane_count i32 */
+int32_t vyb_unpack_i4x8_via(vyb_quantized_scratch* scratch, const uint32_t* packed_words, size_t packed_len,
+                            uint32_t lane_count, int32_t* out_lanes);
+/* dot.rs:44-91: out has one f32 */
+int32_t vyb_i4x8_dot_f32_scaled_via(vyb_quantized_scratch* scratch, const uint32_t* lhs_packed, size_t lhs_len,
+                                    const uint32_t* rhs_packed, size_t rhs_len, float lhs_scale, float rhs_scale,
+                                    uint32_t lane_count, float* out);
+/* matvec.rs:45-110: out has rows f32 */
+int32_t vyb_i4x8_matvec_f32_scaled_via(vyb_quantized_scratch* scratch, const uint32_t* weights_packed, size_t weights_len,
+                                       const float* x, size_t x_len, const float* row_scales, size_t row_scales_len,
+                                       uint32_t rows, uint32_t cols, float* out);
+/* batched_matvec.rs:47-132: out has batch * rows f32 */
+int32_t vyb_i4x8_batched_matvec_f32_scaled_via(vyb_quantized_scratch* scratch, const uint32_t* weights_packed,
+                                               size_t weights_len, const float* x_batches, size_t x_len,
+                                               const float* row_scales, size_t row_scales_len, uint32_t batch,
+                                               uint32_t rows, uint32_t cols, float* out);
+/* batched_matmul.rs:45-108 (shape rule shapes.rs:12-76): out has batch * rows f32 */
+int32_t vyb_i4x8_batched_matmul_f32_scaled_via(vyb_quantized_scratch* scratch, const uint32_t* weights_packed,
+                                               size_t weights_len, const uint32_t* activation_batches_packed,
+                                               size_t activations_len, const float* row_scales, size_t row_scales_len,
+                                               const float* batch_scales, size_t batch_scales_len, uint32_t batch,
+                                               uint32_t rows, uint32_t cols, float* out);
+/* top1.rs:44-126: scores_out and indices_out have batch elements each */
+int32_t vyb_i4x8_batched_matmul_top1_f32_scaled_via(vyb_quantized_scratch* scratch, const uint32_t* weights_packed,
+                                                    size_t weights_len, const uint32_t* activation_batches_packed,
+                                                    size_t activations_len, const float* row_scales,
+                                                    size_t row_scales_len, const float* batch_scales,
+                                                    size_t batch_scales_len, uint32_t batch, uint32_t rows,
+                                                    uint32_t cols, float* scores_out, uint32_t* indices_out);
 
 /* ---- kernel-level entry points ------------------------------------------------------------------------
  * For a host that owns its buffers and stream (what the Rust shim's resident path calls after resolving

@@ -1025,3 +1025,95 @@ def dense_gated_mlp_graph(spec: DenseGatedMlpSpec) -> ProgramGraph:
                    [("input", act, read_inter), ("weight", down_wv, down_w)],
                    [("output", "mlp.down", value_contract(dt, hidden_shape, outl, rw))])
     return graph
+
+
+# ---- scratch-reusing callers of the packed-int4 primitives (vyre-self-substrate/src/math/quantized_dispatch.rs) -----------
+class QuantizedScratch:
+    """Caller-owned scratch of the `*_via_with_scratch_into` wrappers: per (wrapper, shape) the compiled chain down to the
+    ArtifactInstance, so that a repeated shape costs one submission. The reference keeps one scratch struct per wrapper
+    (quantized_dispatch.rs:30-72); here one object serves all six. The dispatcher is the device it was made for."""
+
+    def __init__(self, device: Device | None):
+        out = C.c_void_p()
+        check(ffi.lib().vyb_quantized_scratch_new(device._h if device is not None else None, C.byref(out)))
+        self._h, self._dev = out, device
+
+    def close(self) -> None:
+        if self._h is not None:
+            h, self._h = self._h, None
+            ffi.lib().vyb_quantized_scratch_free(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def stats(self) -> dict:
+        c, h, m = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        ffi.lib().vyb_quantized_scratch_stats(self._h, C.byref(c), C.byref(h), C.byref(m))
+        return {"cached": c.value, "hits": h.value, "misses": m.value}
+
+
+def _u32(a):
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def unpack_i4x8_via(scratch: QuantizedScratch, packed_words, lane_count: int) -> np.ndarray:
+    """unpack.rs:14-84."""
+    p, out = _u32(packed_words), np.empty(max(lane_count, 1), dtype=np.int32)
+    check(ffi.lib().vyb_unpack_i4x8_via(scratch._h, p.ctypes.data, p.size, lane_count, out.ctypes.data))
+    return out[:lane_count]
+
+
+def i4x8_dot_f32_scaled_via(scratch: QuantizedScratch, lhs_packed, rhs_packed, lhs_scale: float, rhs_scale: float,
+                            lane_count: int) -> float:
+    """dot.rs:14-91."""
+    a, b, out = _u32(lhs_packed), _u32(rhs_packed), np.empty(1, dtype=np.float32)
+    check(ffi.lib().vyb_i4x8_dot_f32_scaled_via(scratch._h, a.ctypes.data, a.size, b.ctypes.data, b.size, lhs_scale, rhs_scale,
+                                                lane_count, out.ctypes.data))
+    return float(out[0])
+
+
+def i4x8_matvec_f32_scaled_via(scratch: QuantizedScratch, weights_packed, x, row_scales, rows: int, cols: int) -> np.ndarray:
+    """matvec.rs:14-110."""
+    w, xv, rs, out = _u32(weights_packed), _f32(x), _f32(row_scales), np.empty(max(rows, 1), dtype=np.float32)
+    check(ffi.lib().vyb_i4x8_matvec_f32_scaled_via(scratch._h, w.ctypes.data, w.size, xv.ctypes.data, xv.size, rs.ctypes.data,
+                                                   rs.size, rows, cols, out.ctypes.data))
+    return out[:rows]
+
+
+def i4x8_batched_matvec_f32_scaled_via(scratch: QuantizedScratch, weights_packed, x_batches, row_scales, batch: int, rows: int,
+                                       cols: int) -> np.ndarray:
+    """batched_matvec.rs:14-132."""
+    w, xv, rs = _u32(weights_packed), _f32(x_batches), _f32(row_scales)
+    out = np.empty(max(batch * rows, 1), dtype=np.float32)
+    check(ffi.lib().vyb_i4x8_batched_matvec_f32_scaled_via(scratch._h, w.ctypes.data, w.size, xv.ctypes.data, xv.size,
+                                                           rs.ctypes.data, rs.size, batch, rows, cols, out.ctypes.data))
+    return out[:batch * rows]
+
+
+def i4x8_batched_matmul_f32_scaled_via(scratch: QuantizedScratch, weights_packed, activation_batches_packed, row_scales,
+                                       batch_scales, batch: int, rows: int, cols: int) -> np.ndarray:
+    """batched_matmul.rs:14-108."""
+    w, a, rs, bs = _u32(weights_packed), _u32(activation_batches_packed), _f32(row_scales), _f32(batch_scales)
+    out = np.empty(max(batch * rows, 1), dtype=np.float32)
+    check(ffi.lib().vyb_i4x8_batched_matmul_f32_scaled_via(scratch._h, w.ctypes.data, w.size, a.ctypes.data, a.size,
+                                                           rs.ctypes.data, rs.size, bs.ctypes.data, bs.size, batch, rows, cols,
+                                                           out.ctypes.data))
+    return out[:batch * rows]
+
+
+def i4x8_batched_matmul_top1_f32_scaled_via(scratch: QuantizedScratch, weights_packed, activation_batches_packed, row_scales,
+                                            batch_scales, batch: int, rows: int, cols: int):
+    """top1.rs:14-126: (scores, indices)."""
+    w, a, rs, bs = _u32(weights_packed), _u32(activation_batches_packed), _f32(row_scales), _f32(batch_scales)
+    scores, idx = np.empty(max(batch, 1), dtype=np.float32), np.empty(max(batch, 1), dtype=np.uint32)
+    check(ffi.lib().vyb_i4x8_batched_matmul_top1_f32_scaled_via(scratch._h, w.ctypes.data, w.size, a.ctypes.data, a.size,
+                                                                rs.ctypes.data, rs.size, bs.ctypes.data, bs.size, batch, rows,
+                                                                cols, scores.ctypes.data, idx.ctypes.data))
+    return scores[:batch], idx[:batch]

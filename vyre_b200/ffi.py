@@ -25,6 +25,7 @@ ERR_UNSUPPORTED_FEATURE = 1002
 ERR_DISPATCH_FAILED = 1005
 ERR_INVALID_PROGRAM = 1006
 ERR_DEVICE_LOST = 1008
+ERR_DISPATCH_REJECTED, ERR_DISPATCH_BAD_INPUTS, ERR_DISPATCH_BACKEND = 2001, 2002, 2003
 
 
 class BackendError(RuntimeError):
@@ -200,6 +201,13 @@ _STATUS_FUNCS = {
     "vyb_safetensors_find": [_P, _S, C.POINTER(C.c_uint32)],
     "vyb_safetensors_require": [_P, _S, _S, C.POINTER(C.c_uint64), _U, C.POINTER(C.c_uint32)],
     "vyb_safetensors_upload": [_P, _U, _P, ResidentHandle, C.c_uint64],
+    "vyb_quantized_scratch_new": [_P, _PP],
+    "vyb_unpack_i4x8_via": [_P, _P, C.c_size_t, _U, _P],
+    "vyb_i4x8_dot_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, C.c_float, C.c_float, _U, _P],
+    "vyb_i4x8_matvec_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _U, _U, _P],
+    "vyb_i4x8_batched_matvec_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _U, _U, _U, _P],
+    "vyb_i4x8_batched_matmul_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _U, _U, _U, _P],
+    "vyb_i4x8_batched_matmul_top1_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _U, _U, _U, _P, _P],
     "vyb_compile": [_P, _PP],
     "vyb_target_compile": [_P, _PP],
     "vyb_payload_bytes": [_P, C.POINTER(C.POINTER(C.c_uint8)), C.POINTER(C.c_size_t)],
@@ -278,6 +286,8 @@ _OTHER_FUNCS = {
     "vyb_graph_digest": (None, [_P, C.c_char_p]),
     "vyb_safetensors_free": (None, [_P]),
     "vyb_safetensors_identity": (None, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "vyb_quantized_scratch_free": (None, [_P]),
+    "vyb_quantized_scratch_stats": (None, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vyb_safetensors_count": (C.c_uint32, [_P]),
     "vyb_payload_format": (C.c_char_p, [_P]),
     "vyb_payload_kernel_variant": (C.c_uint32, [_P]),
