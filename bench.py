@@ -359,6 +359,60 @@ def measure_dropin_1m(local_rank: int, samples: int = 30, shape=(256, 4096, 64, 
             "device_ns_samples": ns}
 
 
+def measure_k_quant(local_rank: int, peaks: dict, samples: int = 20, shape=(4096, 4096)) -> list:
+    """GGML K-quant fused linears (vyre-libs/src/nn/quant/ggml.rs:338-385) at a decode shape through the reference's op ids:
+    buffers resident, device time of one dispatch from the events of the contract path, one f64 check per run."""
+    import numpy as np
+
+    import vyre_b200 as vb
+
+    in_dim, out_dim = shape
+    out = []
+    dev = vb.Device.acquire(local_rank)
+    for bits, build, name in ((4, vb.q4_k_linear, "q4_k_linear"), (2, vb.q2_k_linear, "q2_k_linear")):
+        rng = np.random.default_rng(bits)
+        block, wpb = (32, 4) if bits == 4 else (16, 1)
+        blocks = in_dim * out_dim // block
+        packed = rng.integers(0, 2**32, size=blocks * wpb, dtype=np.uint32)
+        scales = rng.uniform(0.01, 0.2, size=blocks).astype(np.float32)
+        mins = (-rng.uniform(0.0, 1.0, size=blocks)).astype(np.float32)
+        x, b = rng.standard_normal(in_dim).astype(np.float32), rng.standard_normal(out_dim).astype(np.float32)
+        sess = vb.ArtifactSession.compile(build("x", "p", "s", "m", "b", "o", in_dim, out_dim), dev)
+        handles = [dev.resident_from(a) for a in (x, packed, scales, mins, b)] + [dev.allocate_resident(out_dim * 4)]
+        bs = vb.BindingSet(sess.artifact.digest())
+        for slot, h in enumerate(handles):
+            bs.insert_resident(slot, h)
+        ns = []
+        for i in range(samples + 3):
+            done = sess.submit(bs, leave_resident=True).wait()
+            if i >= 3:
+                ns.append(done.device_ns)
+            del done
+        got = dev.download_resident(handles[5], out_dim * 4).view(np.float32)
+        vpw = 32 // bits
+        q = ((packed.reshape(-1, 1) >> (bits * np.arange(vpw, dtype=np.uint32))) & ((1 << bits) - 1)).reshape(in_dim, out_dim)
+        deq = q.astype(np.float64) * np.repeat(scales.astype(np.float64), block).reshape(in_dim, out_dim) + \
+            np.repeat(mins.astype(np.float64), block).reshape(in_dim, out_dim)
+        want = x.astype(np.float64) @ deq + b
+        err = float(np.abs(got - want).max() / np.abs(want).max())
+        assert err <= 1e-4, f"{name} disagrees with the f64 restatement: {err}"
+        for h in handles:
+            dev.free_resident(h)
+        ns.sort()
+        p50 = ns[len(ns) // 2]
+        abytes = packed.nbytes + scales.nbytes + mins.nbytes + x.nbytes + b.nbytes + out_dim * 4
+        gbs = abytes / (p50 * 1e-9) / 1e9
+        out.append({"case": f"{name} in={in_dim} out={out_dim}", "op_id": f"vyre-libs::quant::{name}", "kernel_variant": sess.kernel_variant(),
+                    "device_us_per_dispatch": {"p50": round(p50 / 1e3, 2), "min": round(ns[0] / 1e3, 2), "samples": len(ns)},
+                    "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                 "frac": round(gbs / peaks["hbm_gbs"], 4), "algorithmic_bytes_per_dispatch": abytes,
+                                 "kernel": "k_quant_linear_fast_kernel",
+                                 "note": "one dispatch per sample between two events (event overhead included); the buffers fit L2"},
+                    "parity": {"max_rel_err_vs_f64": err, "tolerance": 1e-4}})
+    dev.release()
+    return out
+
+
 def metric_stats(samples) -> dict:
     """vyre-bench MetricStats (vyre-bench/SCHEMA.md, `MetricStats` object) of integer samples."""
     v = sorted(int(x) for x in samples)
@@ -760,6 +814,7 @@ def run_native(args) -> None:
     secondary["int8_gemm_config5_single_gpu"] = measure_int8([4096, 28672, 8192], 10, 3, i8_peak, peaks)
     secondary["dropin_1m"] = measure_dropin_1m(local_rank)
     secondary["dropin_decode_shape"] = measure_dropin_1m(local_rank, shape=(K_IN, N_OUT, GROUP, 1), peaks=peaks)
+    secondary["k_quant_linear"] = measure_k_quant(local_rank, peaks)
     secondary["clocks_during_secondary"] = sampler.summary(s_lo, sampler.mark())
     torch.cuda.empty_cache()
 
@@ -881,7 +936,7 @@ def run_quick(args) -> None:
     if args.case == "dropin":
         first = measure_dropin_1m(0)
         first.pop("device_ns_samples", None)
-        print(json.dumps({"quick": True, "dropin_1m": first,
+        print(json.dumps({"quick": True, "k_quant": measure_k_quant(0, peaks), "dropin_1m": first,
                           "dropin_decode_shape": [measure_dropin_1m(0, shape=(K_IN, N_OUT, GROUP, bb), peaks=peaks) for bb in (1, 4, 8)]}))
         return
     if args.case == "peak":

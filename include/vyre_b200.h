@@ -288,6 +288,26 @@ int32_t vyb_nn_top_k(const char* input, const char* output_indices, uint32_t n, 
 int32_t vyb_nn_swiglu(const char* gate, const char* up, const char* output, uint32_t n, vyb_program** program);
 int32_t vyb_nn_swiglu_typed(const char* gate, const char* up, const char* output, uint32_t n, uint32_t dtype,
                             vyb_program** program);
+/* residual_add / residual_add_typed: vyre-libs/src/nn/activation/residual_add.rs:8-52 (out = cast(f32 sum)) */
+int32_t vyb_nn_residual_add(const char* residual, const char* branch, const char* output, uint32_t n, vyb_program** program);
+int32_t vyb_nn_residual_add_typed(const char* residual, const char* branch, const char* output, uint32_t n, uint32_t dtype,
+                                  vyb_program** program);
+/* learned_rms_norm / gated_rms_norm: vyre-libs/src/nn/norm/gated_rms_norm.rs:35-247 (f32 sum of squares in row order,
+ * 1 / sqrt(mean + eps), rounding to dtype, learned scale, optional SiLU gate, one final cast) */
+int32_t vyb_nn_learned_rms_norm(const char* input, const char* weight, const char* output, uint32_t rows, uint32_t hidden,
+                                float eps, uint32_t dtype, vyb_program** program);
+int32_t vyb_nn_gated_rms_norm(const char* input, const char* weight, const char* gate, const char* output, uint32_t rows,
+                              uint32_t hidden, float eps, uint32_t dtype, vyb_program** program);
+/* GGML K-quants with per-block f32 scale / min sidecars: vyre-libs/src/nn/quant/ggml.rs:28-120 (unpack), 217-400 (fused
+ * dequant + linear over the k-major weight stream, out = x @ dequant(w) + b) */
+int32_t vyb_quant_q4_k_unpack(const char* packed, const char* scales, const char* mins, const char* output, uint32_t n,
+                              vyb_program** program);
+int32_t vyb_quant_q2_k_unpack(const char* packed, const char* scales, const char* mins, const char* output, uint32_t n,
+                              vyb_program** program);
+int32_t vyb_quant_q4_k_linear(const char* x, const char* w_packed, const char* w_scales, const char* w_mins, const char* b,
+                              const char* out, uint32_t in_dim, uint32_t out_dim, vyb_program** program);
+int32_t vyb_quant_q2_k_linear(const char* x, const char* w_packed, const char* w_scales, const char* w_mins, const char* b,
+                              const char* out, uint32_t in_dim, uint32_t out_dim, vyb_program** program);
 /* vyre-libs/src/nn/moe/expert_mlp.rs:18 */
 int32_t vyb_nn_expert_mlp(const char* x, const char* w_gate, const char* b_gate, const char* w_up, const char* b_up,
                           const char* w_down, const char* b_down, const char* out, uint32_t in_dim,

@@ -299,3 +299,38 @@ def moe_ffn_int4(x_bf16, w_router_bf16, w13, s13, w2, s2, tokens, hidden, inter,
                            C.c_uint32(hidden), C.c_uint32(inter), C.c_uint32(experts), C.c_uint32(topk),
                            C.c_uint32(group), C.c_uint32(mode), _p(out), _p(idx), _p(wts))
     return out.reshape(tok.size, hidden), idx.reshape(tok.size, topk), wts.reshape(tok.size, topk)
+
+
+# ---- operators either side of the feed-forward block, GGML K-quant linears ------------------------------------------
+def residual_add(residual, branch, dtype=DT_F32) -> np.ndarray:
+    nd = _NP_OF[dtype]
+    r, b = _c(residual, nd), _c(branch, nd)
+    out = np.zeros(r.size, dtype=nd)
+    lib().vyo_residual_add(_p(r), _p(b), _p(out), C.c_uint32(r.size), C.c_uint32(dtype))
+    return out
+
+
+def rms_norm(x, weight, rows: int, hidden: int, eps: float, dtype=DT_F32, gate=None, weight_dtype=None) -> np.ndarray:
+    """learned_rms_norm (gate=None) and gated_rms_norm."""
+    nd = _NP_OF[dtype]
+    wd = dtype if weight_dtype is None else weight_dtype
+    xv, wv = _c(x, nd), _c(weight, _NP_OF[wd])
+    gv = None if gate is None else _c(gate, nd)
+    out = np.zeros(rows * hidden, dtype=nd)
+    lib().vyo_rms_norm(_p(xv), _p(wv), _p(gv) if gv is not None else None, _p(out), C.c_uint32(rows), C.c_uint32(hidden),
+                       C.c_float(eps), C.c_uint32(dtype), C.c_uint32(wd))
+    return out
+
+
+def k_quant_unpack(packed, scales, mins, n: int, bits: int) -> np.ndarray:
+    p, s, m = _c(packed, np.uint32), _c(scales, np.float32), _c(mins, np.float32)
+    out = np.zeros(n, dtype=np.float32)
+    lib().vyo_k_quant_unpack(_p(p), _p(s), _p(m), _p(out), C.c_uint32(n), C.c_uint32(bits))
+    return out
+
+
+def k_quant_linear(x, packed, scales, mins, b, in_dim: int, out_dim: int, bits: int) -> np.ndarray:
+    xv, p, s, m, bv = _c(x, np.float32), _c(packed, np.uint32), _c(scales, np.float32), _c(mins, np.float32), _c(b, np.float32)
+    out = np.zeros(out_dim, dtype=np.float32)
+    lib().vyo_k_quant_linear(_p(xv), _p(p), _p(s), _p(m), _p(bv), _p(out), C.c_uint32(in_dim), C.c_uint32(out_dim), C.c_uint32(bits))
+    return out

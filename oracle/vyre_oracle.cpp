@@ -668,3 +668,71 @@ VYO_API int vyo_num_threads(void) {
     return 1;
 #endif
 }
+
+// ---- the operators either side of the feed-forward block, and the GGML K-quant linears ---------------------------
+
+// vyre-libs/src/nn/activation/residual_add.rs:10-52 over unary.rs:44-76: out = cast(dtype, f32(residual) + f32(branch))
+VYO_API void vyo_residual_add(const void* residual, const void* branch, void* out, uint32_t n, uint32_t dtype) {
+    for (uint32_t i = 0; i < n; ++i) store_typed(out, i, dtype, f_add(load_typed(residual, i, dtype), load_typed(branch, i, dtype)));
+}
+
+// vyre-libs/src/nn/norm/gated_rms_norm.rs:123-247. Per element: sum_squares = sequential f32 sum of x^2 over the row;
+// normalized = x * (1 / sqrt(sum_squares / hidden + eps))  (InverseSqrt = 1.0 / sqrtf, vyre-reference/src/ieee754.rs:60-70);
+// rounded to dtype; times f32(weight[col]); with a gate: times gate / (1 + exp(-gate)); one final cast to dtype.
+VYO_API void vyo_rms_norm(const void* input, const void* weight, const void* gate, void* out, uint32_t rows, uint32_t hidden,
+                          float eps, uint32_t dtype, uint32_t weight_dtype) {
+    for (uint32_t r = 0; r < rows; ++r) {
+        float sum = 0.0f;
+        for (uint32_t c = 0; c < hidden; ++c) {
+            const float v = load_typed(input, size_t(r) * hidden + c, dtype);
+            sum = f_add(sum, f_mul(v, v));
+        }
+        const float inv = f_div(1.0f, canon(std::sqrt(canon(f_add(f_div(sum, float(hidden)), eps)))));
+        for (uint32_t c = 0; c < hidden; ++c) {
+            const size_t i = size_t(r) * hidden + c;
+            float normalized = f_mul(load_typed(input, i, dtype), inv);
+            if (dtype == DT_BF16) normalized = bf16_to_f32(f32_to_bf16(normalized));
+            else if (dtype == DT_F16) normalized = f16_to_f32(f32_to_f16(normalized));
+            float v = f_mul(normalized, load_typed(weight, c, weight_dtype));
+            if (gate) {
+                const float g = load_typed(gate, i, dtype);
+                v = f_mul(v, f_div(g, f_add(1.0f, f_exp(f_neg(g)))));
+            }
+            store_typed(out, i, dtype, v);
+        }
+    }
+}
+
+// vyre-libs/src/nn/quant/ggml.rs:28-120 (k_quant_unpack): bits = 4 (Q4_K: blocks of 32, 4 words) or 2 (Q2_K: blocks
+// of 16, 1 word); out[i] = f32(q_i) * scale[block] + min[block]
+static inline uint32_t k_quant_value(const uint32_t* packed, uint32_t linear, uint32_t bits, uint32_t* block) {
+    const uint32_t block_size = bits == 4 ? 32u : 16u, values_per_byte = 8u / bits, words_per_block = bits == 4 ? 4u : 1u;
+    const uint32_t block_idx = linear / block_size, within = linear % block_size;
+    const uint32_t byte_idx = within / values_per_byte, value_shift = (within % values_per_byte) * bits;
+    const uint32_t word = packed[size_t(block_idx) * words_per_block + byte_idx / 4];
+    *block = block_idx;
+    return (word >> ((byte_idx % 4) * 8 + value_shift)) & ((1u << bits) - 1u);
+}
+VYO_API void vyo_k_quant_unpack(const uint32_t* packed, const float* scales, const float* mins, float* out, uint32_t n,
+                                uint32_t bits) {
+    for (uint32_t i = 0; i < n; ++i) {
+        uint32_t block;
+        const uint32_t q = k_quant_value(packed, i, bits, &block);
+        out[i] = f_add(f_mul(float(q), scales[block]), mins[block]);
+    }
+}
+// ggml.rs:217-333 (k_quant_linear): out[i] = b[i] + sum_k x[k] * (q(k * out_dim + i) * scale + min), k ascending,
+// every product and sum rounded on its own
+VYO_API void vyo_k_quant_linear(const float* x, const uint32_t* packed, const float* scales, const float* mins, const float* b,
+                                float* out, uint32_t in_dim, uint32_t out_dim, uint32_t bits) {
+    for (uint32_t i = 0; i < out_dim; ++i) {
+        float acc = canon(b[i]);
+        for (uint32_t k = 0; k < in_dim; ++k) {
+            uint32_t block;
+            const uint32_t q = k_quant_value(packed, k * out_dim + i, bits, &block);
+            const float weight = f_add(f_mul(float(q), scales[block]), mins[block]);
+            acc = f_add(acc, f_mul(x[k], weight));
+        }
+        out[i] = acc;
+    }
+}

@@ -27,20 +27,24 @@ def test_dense_gated_mlp_graph_matches_the_oracle_composition(dev, dtype, odt):
     rows = batch * seq
     rng = np.random.default_rng(3)
     f = lambda *shape: rng.standard_normal(shape).astype(np.float32)  # noqa: E731
-    x, wg, wu, wd = f(rows, h), f(inter, h) * 0.3, f(inter, h) * 0.3, f(h, inter) * 0.3
+    x, wg, wu, wd = f(rows, h) * 2.0, f(inter, h) * 0.3, f(inter, h) * 0.3, f(h, inter) * 0.3
+    wn = (1.0 + 0.1 * f(h)).astype(np.float32)
     if dtype == ffi.DT_BF16:
-        x, wg, wu, wd = (oracle.f32_to_bf16_bits(a) for a in (x, wg, wu, wd))
-    sess = api.GraphSession(api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(batch, seq, h, inter, dtype)), dev)
+        x, wg, wu, wd, wn = (oracle.f32_to_bf16_bits(a) for a in (x, wg, wu, wd, wn))
+    sess = api.GraphSession(api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(batch, seq, h, inter, dtype, norm_eps=1e-5)), dev)
     try:
+        sess.set_constant("post_attention_layernorm.weight", wn)
         sess.set_constant("mlp.gate_proj.weight", wg)
         sess.set_constant("mlp.up_proj.weight", wu)
         sess.set_constant("mlp.down_proj.weight", wd)
         for _ in range(2):  # a session runs again and again over the same constants
-            got = sess.run({"mlp.normalized": x})["mlp.down"]
-        gate = oracle.linear_rows(x, wg, None, rows, h, inter, dtype=odt, weight_out_in=True)
-        up = oracle.linear_rows(x, wu, None, rows, h, inter, dtype=odt, weight_out_in=True)
+            got = sess.run({"residual": x})["mlp.block_output"]
+        normed = oracle.rms_norm(x, wn, rows, h, 1e-5, dtype=odt)
+        gate = oracle.linear_rows(normed, wg, None, rows, h, inter, dtype=odt, weight_out_in=True)
+        up = oracle.linear_rows(normed, wu, None, rows, h, inter, dtype=odt, weight_out_in=True)
         act = oracle.swiglu(gate, up, dtype=odt)
-        want = oracle.linear_rows(act, wd, None, rows, inter, h, dtype=odt, weight_out_in=True)
+        down = oracle.linear_rows(act, wd, None, rows, inter, h, dtype=odt, weight_out_in=True)
+        want = oracle.residual_add(x, down, dtype=odt)
         if dtype == ffi.DT_F32:
             # the projections are byte-exact against the oracle; SwiGLU's exp sits in the reference's 128-ULP window
             np.testing.assert_allclose(np.frombuffer(got, np.float32), want, rtol=2e-5, atol=1e-6)
@@ -50,7 +54,7 @@ def test_dense_gated_mlp_graph_matches_the_oracle_composition(dev, dtype, odt):
         with pytest.raises(vb.BackendError, match="bind the graph input"):
             sess.run({})
         with pytest.raises(vb.BackendError, match="needs .* bytes by its contract"):
-            sess.run({"mlp.normalized": x[:1]})
+            sess.run({"residual": x[:1]})
     finally:
         sess.close()
 

@@ -358,3 +358,52 @@ def test_per_token_int8_quantisation_rule_and_int32_gemm():
     w = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
     got = oracle.int8_gemm_i32(q, w, m, n, k)
     assert np.array_equal(got, q.astype(np.int32) @ w.astype(np.int32).T)
+
+
+# ---- operators either side of the feed-forward block; GGML K-quants ----------------------------------------------------
+def test_residual_add_registered_fixture():
+    # vyre-libs/src/nn/activation/residual_add.rs:53-76 (OperationRegistration test_inputs / expected_output)
+    out = oracle.residual_add([1.0, -2.0, 3.5, 0.0], [0.5, 4.0, -1.5, -0.0])
+    assert out.tolist() == [1.5, 2.0, 2.0, 0.0]
+
+
+def test_k_quant_reference_fixtures():
+    # vyre-libs/src/nn/quant/ggml.rs:392-425 (q4_k_unpack_simple)
+    out = oracle.k_quant_unpack([0x76543210, 0xFEDCBA98, 0, 0], [1.0], [0.0], 16, bits=4)
+    assert out.tolist() == [float(i) for i in range(16)]
+    # ggml.rs:427-452 (q2_k_unpack_simple): 0xE4 = 11_10_01_00
+    out = oracle.k_quant_unpack([0xE4E4E4E4], [1.0], [0.0], 16, bits=2)
+    assert out.tolist() == [0.0, 1.0, 2.0, 3.0] * 4
+    # ggml.rs:454-474 (q4_k_linear_reads_blocks_created_by_output_dimension)
+    x = np.zeros(32, np.float32)
+    x[31] = 1.0
+    out = oracle.k_quant_linear(x, [0x11111111] * 8, [1.0, 2.0], [0.0, 0.0], [0.5, 1.5], 32, 2, bits=4)
+    assert out.tolist() == [2.5, 3.5]
+
+
+def test_rms_norm_follows_the_stated_order():
+    # no vector of the reference pins this operator (gated_rms_norm.rs has no test module): the restatement is checked
+    # against the formula of its doc comment evaluated step by step in numpy f32
+    rng = np.random.default_rng(3)
+    rows, hidden, eps = 3, 37, np.float32(1e-5)
+    x = rng.standard_normal((rows, hidden)).astype(np.float32)
+    w = rng.standard_normal(hidden).astype(np.float32)
+    got = oracle.rms_norm(x, w, rows, hidden, float(eps)).reshape(rows, hidden)
+    for r in range(rows):
+        s = np.float32(0.0)
+        for v in x[r]:
+            s = np.float32(s + np.float32(v * v))
+        inv = np.float32(1.0) / np.sqrt(np.float32(np.float32(s / np.float32(hidden)) + eps))
+        want = (x[r] * inv).astype(np.float32) * w
+        assert np.array_equal(got[r].view(np.uint32), want.astype(np.float32).view(np.uint32))
+    # bf16: the normalised value is rounded to bf16 before the learned scale, and the result once more
+    xb, wb = oracle.f32_to_bf16_bits(x), oracle.f32_to_bf16_bits(w)
+    gb = oracle.rms_norm(xb, wb, rows, hidden, float(eps), dtype=oracle.DT_BF16).reshape(rows, hidden)
+    xf, wf = oracle.bf16_bits_to_f32(xb).reshape(rows, hidden), oracle.bf16_bits_to_f32(wb)
+    for r in range(rows):
+        s = np.float32(0.0)
+        for v in xf[r]:
+            s = np.float32(s + np.float32(v * v))
+        inv = np.float32(1.0) / np.sqrt(np.float32(np.float32(s / np.float32(hidden)) + eps))
+        n16 = oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits((xf[r] * inv).astype(np.float32)))
+        assert np.array_equal(gb[r], oracle.f32_to_bf16_bits((n16 * wf).astype(np.float32)))

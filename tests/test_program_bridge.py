@@ -71,3 +71,19 @@ def test_matmul_bias_and_linear_programs_from_op_ids():
         assert e.value.code == ffi.ERR_INVALID_PROGRAM and "Fix:" in str(e.value)
     with pytest.raises(vb.BackendError, match="needs the op spec"):
         api.program_from_op("vyre-libs::math::matmul", [b for b in vb.matmul("a", "b", "o", 2, 3, 4).buffers()])
+
+
+def test_norm_residual_and_k_quant_programs_from_op_ids():
+    import struct
+
+    eps_bits = struct.unpack("<I", struct.pack("<f", 1e-6))[0]
+    cases = [(vb.residual_add_typed("r", "b", "o", 96, ffi.DT_BF16), None),
+             (vb.learned_rms_norm("i", "w", "o", 3, 64, 1e-6, ffi.DT_F16), [eps_bits]),
+             (vb.gated_rms_norm("i", "w", "g", "o", 2, 128, 1e-6, ffi.DT_F32), [eps_bits]),
+             (vb.q4_k_unpack("p", "s", "m", "o", 100), None), (vb.q2_k_unpack("p", "s", "m", "o", 100), None),
+             (vb.q4_k_linear("x", "p", "s", "m", "b", "o", 96, 33), None), (vb.q2_k_linear("x", "p", "s", "m", "b", "o", 96, 33), None)]
+    for prog, spec in cases:
+        again = api.program_from_op(prog.op_id, prog.buffers(), spec)
+        assert again.fingerprint() == prog.fingerprint(), prog.op_id
+    with pytest.raises(vb.BackendError, match="eps"):  # the norm's eps is not recoverable from buffer counts
+        api.program_from_op("vyre-libs::nn::learned_rms_norm", vb.learned_rms_norm("i", "w", "o", 3, 64, 1e-6, ffi.DT_F32).buffers())

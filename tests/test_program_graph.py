@@ -89,12 +89,16 @@ def test_retained_successors():
 def test_gated_mlp_templates():
     g = api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(batch=2, sequence=3, hidden_dim=8, intermediate_dim=12, dtype=ffi.DT_BF16))
     names = [n["name"] for n in g.nodes()]
-    assert names == ["mlp.gate_proj", "mlp.up_proj", "mlp.swiglu", "mlp.down_proj"]
+    assert names == ["mlp.norm", "mlp.gate_proj", "mlp.up_proj", "mlp.swiglu", "mlp.down_proj", "mlp.residual"]
     vals = {v["name"]: v for v in g.values()}
     assert vals["mlp.gate_proj.weight"]["contract"] == {"dtype": ffi.DT_BF16, "access": RO, "lifetime": CONST, "shape": [12, 8]}
-    assert vals["mlp.down_proj.weight"]["contract"]["shape"] == [8, 12] and vals["mlp.down"]["contract"]["lifetime"] == OUT
+    assert vals["mlp.down_proj.weight"]["contract"]["shape"] == [8, 12] and vals["mlp.block_output"]["contract"]["lifetime"] == OUT
+    assert vals["post_attention_layernorm.weight"]["contract"] == {"dtype": ffi.DT_BF16, "access": RO, "lifetime": CONST, "shape": [8]}
+    assert vals["residual"]["consumers"] == 2  # the norm and the residual add (dense_gated_mlp.rs:171-200, 331-346)
     assert vals["mlp.normalized"]["consumers"] == 2 and vals["mlp.activated"]["contract"]["shape"] == [2, 3, 12]
-    assert [n["program"].op_id for n in g.nodes()][2] == "vyre-libs::nn::swiglu"
+    assert [n["program"].op_id for n in g.nodes()] == ["vyre-libs::nn::learned_rms_norm", "vyre-libs::nn::linear_rows", "vyre-libs::nn::linear_rows",
+                                                       "vyre-libs::nn::swiglu", "vyre-libs::nn::linear_rows", "vyre-libs::nn::residual_add"]
+    assert g.digest() != api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(2, 3, 8, 12, ffi.DT_BF16, norm_eps=1e-5)).digest()
     same = api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(2, 3, 8, 12, ffi.DT_BF16))
     other = api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(2, 3, 8, 16, ffi.DT_BF16))
     assert g.digest() == same.digest() != other.digest()
@@ -103,4 +107,4 @@ def test_gated_mlp_templates():
     q = api.quantized_gated_mlp_graph(api.QuantizedGatedMlpSpec(rows=4, hidden_dim=256, intermediate_dim=512))
     qv = {v["name"]: v for v in q.values()}
     assert qv["mlp.gate_proj.qweight"]["contract"] == {"dtype": ffi.DT_U32, "access": RO, "lifetime": CONST, "shape": [512, 32]}
-    assert qv["mlp.down_proj.scales"]["contract"]["shape"] == [256, 4] and [n["name"] for n in q.nodes()] == names
+    assert qv["mlp.down_proj.scales"]["contract"]["shape"] == [256, 4] and [n["name"] for n in q.nodes()] == names[1:5]

@@ -234,6 +234,38 @@ def swiglu_typed(gate, up, output, n, dtype):
     return _build("vyb_nn_swiglu_typed", gate, up, output, n, dtype)
 
 
+def residual_add(residual, branch, output, n):
+    return _build("vyb_nn_residual_add", residual, branch, output, n)
+
+
+def residual_add_typed(residual, branch, output, n, dtype):
+    return _build("vyb_nn_residual_add_typed", residual, branch, output, n, dtype)
+
+
+def learned_rms_norm(input, weight, output, rows, hidden, eps, dtype):  # noqa: A002 - the reference's argument name
+    return _build("vyb_nn_learned_rms_norm", input, weight, output, rows, hidden, C.c_float(eps), dtype)
+
+
+def gated_rms_norm(input, weight, gate, output, rows, hidden, eps, dtype):  # noqa: A002
+    return _build("vyb_nn_gated_rms_norm", input, weight, gate, output, rows, hidden, C.c_float(eps), dtype)
+
+
+def q4_k_unpack(packed, scales, mins, output, n):
+    return _build("vyb_quant_q4_k_unpack", packed, scales, mins, output, n)
+
+
+def q2_k_unpack(packed, scales, mins, output, n):
+    return _build("vyb_quant_q2_k_unpack", packed, scales, mins, output, n)
+
+
+def q4_k_linear(x, w_packed, w_scales, w_mins, b, out, in_dim, out_dim):
+    return _build("vyb_quant_q4_k_linear", x, w_packed, w_scales, w_mins, b, out, in_dim, out_dim)
+
+
+def q2_k_linear(x, w_packed, w_scales, w_mins, b, out, in_dim, out_dim):
+    return _build("vyb_quant_q2_k_linear", x, w_packed, w_scales, w_mins, b, out, in_dim, out_dim)
+
+
 def expert_mlp(x, w_gate, b_gate, w_up, b_up, w_down, b_down, out, in_dim, hidden_dim, out_dim):
     return _build("vyb_nn_expert_mlp", x, w_gate, b_gate, w_up, b_up, w_down, b_down, out, in_dim, hidden_dim,
                   out_dim)
@@ -981,21 +1013,21 @@ def quantized_gated_mlp_graph(spec: QuantizedGatedMlpSpec) -> ProgramGraph:
 
 @dataclass
 class DenseGatedMlpSpec:
-    """vyre_libs::nn::model::DenseGatedMlpSpec (dense_gated_mlp.rs:15-29) without the norm epsilon: batch x sequence token
-    rows, F16 / BF16 / F32 activations and weights."""
+    """vyre_libs::nn::model::DenseGatedMlpSpec (dense_gated_mlp.rs:15-29): batch x sequence token rows, the RMSNorm epsilon,
+    F16 / BF16 / F32 activations and weights."""
     batch: int
     sequence: int
     hidden_dim: int
     intermediate_dim: int
     dtype: int = ffi.DT_F32
+    norm_eps: float = 1e-6
 
 
-def dense_gated_mlp_graph(spec: DenseGatedMlpSpec) -> ProgramGraph:
-    """The projection nodes of vyre_libs::nn::model::dense_gated_mlp_graph (dense_gated_mlp.rs:59-370) with the reference's
-    own node programs, value names, shapes and lifetimes: bias-free gate / up projections
-    (`linear_rows_no_bias_out_in_typed`), SwiGLU, bias-free down projection; weights are `Constant` values of shape
-    [out, in]. The learned RMSNorm in front and the residual add behind are not on this path: the graph's input is
-    `mlp.normalized` and its output `mlp.down`."""
+def dense_gated_mlp_graph(spec: DenseGatedMlpSpec, output_lifetime: int = ffi.LIFETIME_OUTPUT) -> ProgramGraph:
+    """vyre_libs::nn::model::dense_gated_mlp_graph (dense_gated_mlp.rs:59-370) with the reference's own node programs,
+    value names, shapes and lifetimes: learned RMSNorm of the residual stream (`mlp.norm`), bias-free gate / up projections
+    (`linear_rows_no_bias_out_in_typed`), SwiGLU, bias-free down projection, residual add (`mlp.residual`). Weights are
+    `Constant` values ([out, in] projections, [hidden] norm weight); the input is `residual`, the output `mlp.block_output`."""
     if min(spec.batch, spec.sequence, spec.hidden_dim, spec.intermediate_dim) <= 0:
         raise BackendError(ffi.ERR_INVALID_PROGRAM,
                            "Fix: dense gated MLP primitive construction failed: batch, sequence, hidden_dim, and intermediate_dim must be nonzero")
@@ -1004,26 +1036,31 @@ def dense_gated_mlp_graph(spec: DenseGatedMlpSpec) -> ProgramGraph:
     rows, h, i, dt = spec.batch * spec.sequence, spec.hidden_dim, spec.intermediate_dim, spec.dtype
     if rows >= 1 << 32 or rows * max(h, i) >= 1 << 32 or h * i >= 1 << 32:
         raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: dense gated MLP primitive construction failed: element counts overflow u32")
-    inv, const, outl = ffi.LIFETIME_INVOCATION, ffi.LIFETIME_CONSTANT, ffi.LIFETIME_OUTPUT
+    inv, const = ffi.LIFETIME_INVOCATION, ffi.LIFETIME_CONSTANT
     ro, rw = ffi.ACCESS_READ_ONLY, ffi.ACCESS_READ_WRITE
     hidden_shape, inter_shape = [spec.batch, spec.sequence, h], [spec.batch, spec.sequence, i]
-    read_hidden = value_contract(dt, hidden_shape, inv, ro)
+    read_hidden, write_hidden = value_contract(dt, hidden_shape, inv, ro), value_contract(dt, hidden_shape, inv, rw)
     read_inter, write_inter = value_contract(dt, inter_shape, inv, ro), value_contract(dt, inter_shape, inv, rw)
-    up_w, down_w = value_contract(dt, [i, h], const), value_contract(dt, [h, i], const)
+    norm_w, up_w, down_w = value_contract(dt, [h], const), value_contract(dt, [i, h], const), value_contract(dt, [h, i], const)
     graph = ProgramGraph()
-    x = graph.add_external_value("mlp.normalized", read_hidden)
+    residual = graph.add_external_value("residual", read_hidden)
+    norm_wv = graph.add_external_value("post_attention_layernorm.weight", norm_w)
     gate_w = graph.add_external_value("mlp.gate_proj.weight", up_w)
     up_wv = graph.add_external_value("mlp.up_proj.weight", up_w)
     down_wv = graph.add_external_value("mlp.down_proj.weight", down_w)
+    _, (x,) = graph.add_node("mlp.norm", learned_rms_norm("input", "weight", "output", rows, h, spec.norm_eps, dt),
+                             [("input", residual, read_hidden), ("weight", norm_wv, norm_w)], [("output", "mlp.normalized", write_hidden)])
     _, (gate,) = graph.add_node("mlp.gate_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, h, i, dt),
                                 [("input", x, read_hidden), ("weight", gate_w, up_w)], [("output", "mlp.gate", write_inter)])
     _, (up,) = graph.add_node("mlp.up_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, h, i, dt),
                               [("input", x, read_hidden), ("weight", up_wv, up_w)], [("output", "mlp.up", write_inter)])
     _, (act,) = graph.add_node("mlp.swiglu", swiglu_typed("gate", "up", "output", rows * i, dt),
                                [("gate", gate, read_inter), ("up", up, read_inter)], [("output", "mlp.activated", write_inter)])
-    graph.add_node("mlp.down_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, i, h, dt),
-                   [("input", act, read_inter), ("weight", down_wv, down_w)],
-                   [("output", "mlp.down", value_contract(dt, hidden_shape, outl, rw))])
+    _, (down,) = graph.add_node("mlp.down_proj", linear_rows_no_bias_out_in_typed("input", "weight", "output", rows, i, h, dt),
+                                [("input", act, read_inter), ("weight", down_wv, down_w)], [("output", "mlp.down", write_hidden)])
+    graph.add_node("mlp.residual", residual_add_typed("residual", "branch", "output", rows * h, dt),
+                   [("residual", residual, read_hidden), ("branch", down, read_hidden)],
+                   [("output", "mlp.block_output", value_contract(dt, hidden_shape, output_lifetime, rw))])
     return graph
 
 

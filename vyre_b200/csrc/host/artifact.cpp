@@ -102,6 +102,10 @@ uint32_t select_kernel_variant(const Program& p) {
             const uint64_t batch = p.params.u[0], rows = p.params.u[1], cols = p.params.u[2];
             return batch * rows * cols >= (1ull << 22) ? KV_I4_MATVEC_WARP_ROWS : KV_GENERIC;
         }
+        case OpKind::KQuantLinear: {
+            const uint64_t in_dim = p.params.u[0], out_dim = p.params.u[1], bits = p.params.u[2];
+            return in_dim * out_dim >= (1ull << 20) && out_dim % (4 * (32 / bits)) == 0 ? KV_K_QUANT_WORD_COLUMNS : KV_GENERIC;
+        }
         default: return KV_GENERIC;
     }
 }
@@ -208,6 +212,13 @@ const char* const SUPPORTED_OPS[] = {
     "vyre-libs::nn::moe::expert_mlp",
     "vyre-libs::nn::moe_layer_accumulate",
     "vyre-libs::nn::swiglu",
+    "vyre-libs::nn::residual_add",
+    "vyre-libs::nn::learned_rms_norm",
+    "vyre-libs::nn::gated_rms_norm",
+    "vyre-libs::quant::q4_k_unpack",
+    "vyre-libs::quant::q2_k_unpack",
+    "vyre-libs::quant::q4_k_linear",
+    "vyre-libs::quant::q2_k_linear",
     "vyre-b200::nn::linear_int4_grouped_rowmajor",
     "vyre-b200::nn::linear_int8_weight_only",
     "vyre-b200::nn::linear_int8_dynamic",

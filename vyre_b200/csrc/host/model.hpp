@@ -51,6 +51,10 @@ enum class OpKind : uint32_t {
     Swiglu = 16,
     ExpertMlp = 17,
     MoeLayerAccumulate = 18,
+    ResidualAdd = 19,
+    RmsNorm = 20,      // learned_rms_norm and gated_rms_norm
+    KQuantUnpack = 21, // q4_k_unpack, q2_k_unpack
+    KQuantLinear = 22, // q4_k_linear, q2_k_linear
     // serving-layout operators
     LinearInt4GroupedRowmajor = 32,
     LinearInt8WeightOnly = 33,
@@ -135,6 +139,7 @@ enum KernelVariant : uint32_t {
     KV_MOE_FUSED = 4,
     KV_AFFINE_GROUPED_OUTPUT_MAJOR = 5,  // the reference's own 4-bit layout, thread per output, 8 batch rows per weight
     KV_I4_MATVEC_WARP_ROWS = 6,          // i4x8 matvec, warp per row
+    KV_K_QUANT_WORD_COLUMNS = 7,         // K-quant linear: thread per packed word column, k slices folded in fixed order
 };
 
 uint32_t select_kernel_variant(const Program& p);

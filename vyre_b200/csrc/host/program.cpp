@@ -852,6 +852,137 @@ int32_t vyb_nn_swiglu_typed(const char* gate, const char* up, const char* output
     return swiglu_impl(gate, up, output_name, n, dtype, program);
 }
 
+// ---- residual_add (residual_add.rs:8-52 over unary.rs:44-76) ----------------------------------------------------------
+static int32_t residual_add_impl(const char* residual, const char* branch, const char* out, uint32_t n, uint32_t dtype,
+                                 vyb_program** program) {
+    const char* id = "vyre-libs::nn::residual_add";
+    if (n == 0) return emit(program, trap_program(id, out, dtype, "Fix: residual_add requires n > 0"));
+    Program p;
+    p.op_id = id;
+    p.kind = OpKind::ResidualAdd;
+    p.workgroup = {64, 1, 1};
+    p.params.u[0] = n;
+    p.params.u[1] = dtype;
+    p.buffers = {storage(residual, 0, VYB_ACCESS_READ_ONLY, dtype, n), storage(branch, 1, VYB_ACCESS_READ_ONLY, dtype, n),
+                 output(out, 2, dtype, n)};
+    return emit(program, std::move(p));
+}
+int32_t vyb_nn_residual_add(const char* residual, const char* branch, const char* output_name, uint32_t n,
+                            vyb_program** program) {
+    VYB_REQUIRE_NAMES(residual, branch, output_name);
+    return residual_add_impl(residual, branch, output_name, n, VYB_DT_F32, program);
+}
+int32_t vyb_nn_residual_add_typed(const char* residual, const char* branch, const char* output_name, uint32_t n,
+                                  uint32_t dtype, vyb_program** program) {
+    VYB_REQUIRE_NAMES(residual, branch, output_name);
+    if (n == 0) return fail_invalid_program("Fix: residual_add_typed requires n > 0");
+    if (dtype != VYB_DT_F16 && dtype != VYB_DT_BF16 && dtype != VYB_DT_F32)
+        return fail_invalid_program("Fix: residual_add_typed supports F16, BF16, or F32 tensors; got tag " +
+                                    std::to_string(dtype));
+    return residual_add_impl(residual, branch, output_name, n, dtype, program);
+}
+
+// ---- learned_rms_norm / gated_rms_norm (gated_rms_norm.rs:35-247) -------------------------------------------------------
+static int32_t rms_norm_impl(const char* input, const char* weight, const char* gate, const char* out, uint32_t rows,
+                             uint32_t hidden, float eps, uint32_t dtype, uint32_t weight_dtype, vyb_program** program) {
+    auto floating = [](uint32_t t) { return t == VYB_DT_F16 || t == VYB_DT_BF16 || t == VYB_DT_F32; };
+    if (rows == 0 || hidden == 0)
+        return fail_invalid_program("Fix: gated RMSNorm requires nonzero rows and hidden size; got rows=" + std::to_string(rows) +
+                                    ", hidden=" + std::to_string(hidden));
+    if (!floating(dtype) || !floating(weight_dtype))
+        return fail_invalid_program("Fix: gated RMSNorm supports F16, BF16, or F32 source tensors; got tag " +
+                                    std::to_string(floating(dtype) ? weight_dtype : dtype));
+    if (uint64_t(rows) * hidden > 0xFFFFFFFFull)
+        return fail_invalid_program("Fix: gated RMSNorm rows*hidden overflows u32; split the tensor");
+    const uint32_t total = rows * hidden;
+    Program p;
+    p.op_id = gate ? "vyre-libs::nn::gated_rms_norm" : "vyre-libs::nn::learned_rms_norm";
+    p.kind = OpKind::RmsNorm;
+    p.workgroup = {64, 1, 1};
+    p.params.u[0] = rows;
+    p.params.u[1] = hidden;
+    std::memcpy(&p.params.u[2], &eps, 4);
+    p.params.u[3] = dtype;
+    p.params.u[4] = weight_dtype;
+    p.params.u[5] = gate ? 1u : 0u;
+    p.buffers = {storage(input, 0, VYB_ACCESS_READ_ONLY, dtype, total), storage(weight, 1, VYB_ACCESS_READ_ONLY, weight_dtype, hidden)};
+    if (gate) p.buffers.push_back(storage(gate, 2, VYB_ACCESS_READ_ONLY, dtype, total));
+    p.buffers.push_back(output(out, gate ? 3 : 2, dtype, total));
+    return emit(program, std::move(p));
+}
+int32_t vyb_nn_learned_rms_norm(const char* input, const char* weight, const char* output_name, uint32_t rows,
+                                uint32_t hidden, float eps, uint32_t dtype, vyb_program** program) {
+    VYB_REQUIRE_NAMES(input, weight, output_name);
+    return rms_norm_impl(input, weight, nullptr, output_name, rows, hidden, eps, dtype, dtype, program);
+}
+int32_t vyb_nn_gated_rms_norm(const char* input, const char* weight, const char* gate, const char* output_name,
+                              uint32_t rows, uint32_t hidden, float eps, uint32_t dtype, vyb_program** program) {
+    VYB_REQUIRE_NAMES(input, weight, gate, output_name);
+    return rms_norm_impl(input, weight, gate, output_name, rows, hidden, eps, dtype, dtype, program);
+}
+
+// ---- GGML K-quants (ggml.rs:28-400): Q4_K blocks of 32 weights in 4 words, Q2_K blocks of 16 weights in 1 word ----------
+static int32_t k_quant_unpack_impl(uint32_t bits, const char* packed, const char* scales, const char* mins, const char* out,
+                                   uint32_t n, vyb_program** program) {
+    const std::string id = bits == 4 ? "vyre-libs::quant::q4_k_unpack" : "vyre-libs::quant::q2_k_unpack";
+    if (n == 0) return fail_invalid_program("Fix: " + id + " n=0 is invalid");
+    const uint32_t block_size = bits == 4 ? 32u : 16u, words_per_block = bits == 4 ? 4u : 1u;
+    const uint64_t blocks = (uint64_t(n) + block_size - 1) / block_size;
+    if (blocks * words_per_block > 0xFFFFFFFFull) return fail_invalid_program("Fix: " + id + " packed word count overflows u32");
+    Program p;
+    p.op_id = id;
+    p.kind = OpKind::KQuantUnpack;
+    p.workgroup = {256, 1, 1};
+    p.params.u[0] = n;
+    p.params.u[1] = bits;
+    p.buffers = {storage(packed, 0, VYB_ACCESS_READ_ONLY, VYB_DT_U32, uint32_t(blocks * words_per_block)),
+                 storage(scales, 1, VYB_ACCESS_READ_ONLY, VYB_DT_F32, uint32_t(blocks)),
+                 storage(mins, 2, VYB_ACCESS_READ_ONLY, VYB_DT_F32, uint32_t(blocks)), output(out, 3, VYB_DT_F32, n)};
+    return emit(program, std::move(p));
+}
+int32_t vyb_quant_q4_k_unpack(const char* packed, const char* scales, const char* mins, const char* output_name, uint32_t n,
+                              vyb_program** program) {
+    VYB_REQUIRE_NAMES(packed, scales, mins, output_name);
+    return k_quant_unpack_impl(4, packed, scales, mins, output_name, n, program);
+}
+int32_t vyb_quant_q2_k_unpack(const char* packed, const char* scales, const char* mins, const char* output_name, uint32_t n,
+                              vyb_program** program) {
+    VYB_REQUIRE_NAMES(packed, scales, mins, output_name);
+    return k_quant_unpack_impl(2, packed, scales, mins, output_name, n, program);
+}
+static int32_t k_quant_linear_impl(uint32_t bits, const char* x, const char* w_packed, const char* w_scales, const char* w_mins,
+                                   const char* b, const char* out, uint32_t in_dim, uint32_t out_dim, vyb_program** program) {
+    const std::string id = bits == 4 ? "vyre-libs::quant::q4_k_linear" : "vyre-libs::quant::q2_k_linear";
+    if (in_dim == 0 || out_dim == 0) return fail_invalid_program("Fix: " + id + " all dims must be > 0");
+    if (uint64_t(in_dim) * out_dim > 0xFFFFFFFFull) return fail_invalid_program("Fix: " + id + " dimensions overflow u32");
+    const uint32_t block_size = bits == 4 ? 32u : 16u, words_per_block = bits == 4 ? 4u : 1u;
+    const uint64_t blocks = (uint64_t(in_dim) * out_dim + block_size - 1) / block_size;
+    if (blocks * words_per_block > 0xFFFFFFFFull) return fail_invalid_program("Fix: " + id + " packed word count overflows u32");
+    Program p;
+    p.op_id = id;
+    p.kind = OpKind::KQuantLinear;
+    p.workgroup = {64, 1, 1};
+    p.params.u[0] = in_dim;
+    p.params.u[1] = out_dim;
+    p.params.u[2] = bits;
+    p.buffers = {storage(x, 0, VYB_ACCESS_READ_ONLY, VYB_DT_F32, in_dim),
+                 storage(w_packed, 1, VYB_ACCESS_READ_ONLY, VYB_DT_U32, uint32_t(blocks * words_per_block)),
+                 storage(w_scales, 2, VYB_ACCESS_READ_ONLY, VYB_DT_F32, uint32_t(blocks)),
+                 storage(w_mins, 3, VYB_ACCESS_READ_ONLY, VYB_DT_F32, uint32_t(blocks)),
+                 storage(b, 4, VYB_ACCESS_READ_ONLY, VYB_DT_F32, out_dim), output(out, 5, VYB_DT_F32, out_dim)};
+    return emit(program, std::move(p));
+}
+int32_t vyb_quant_q4_k_linear(const char* x, const char* w_packed, const char* w_scales, const char* w_mins, const char* b,
+                              const char* out, uint32_t in_dim, uint32_t out_dim, vyb_program** program) {
+    VYB_REQUIRE_NAMES(x, w_packed, w_scales, w_mins, b, out);
+    return k_quant_linear_impl(4, x, w_packed, w_scales, w_mins, b, out, in_dim, out_dim, program);
+}
+int32_t vyb_quant_q2_k_linear(const char* x, const char* w_packed, const char* w_scales, const char* w_mins, const char* b,
+                              const char* out, uint32_t in_dim, uint32_t out_dim, vyb_program** program) {
+    VYB_REQUIRE_NAMES(x, w_packed, w_scales, w_mins, b, out);
+    return k_quant_linear_impl(2, x, w_packed, w_scales, w_mins, b, out, in_dim, out_dim, program);
+}
+
 // ---- expert_mlp (expert_mlp.rs:18-150) ---------------------------------------------------------------------------------
 int32_t vyb_nn_expert_mlp(const char* x, const char* w_gate, const char* b_gate, const char* w_up, const char* b_up,
                           const char* w_down, const char* b_down, const char* out, uint32_t in_dim,
@@ -1131,6 +1262,33 @@ int32_t vyb_program_from_op(const char* op_id, const vyb_buffer_decl* decls, uin
         if (!need(3)) return bad_shape("three buffers gate, up, out expected");
         rc = vyb_nn_swiglu_typed(name(0), name(1), name(2), uint32_t(op_spec && n_spec >= 1 ? op_spec[0] : count(0)),
                                  decl_at(decls, n_decls, 0)->dtype, &out);
+    } else if (id == "vyre-libs::nn::residual_add") {
+        if (!need(3)) return bad_shape("three buffers residual, branch, out expected");
+        rc = vyb_nn_residual_add_typed(name(0), name(1), name(2), uint32_t(count(0)), decl_at(decls, n_decls, 0)->dtype, &out);
+    } else if (id == "vyre-libs::nn::learned_rms_norm" || id == "vyre-libs::nn::gated_rms_norm") {
+        // input=0, weight=1, [gate=2,] out; hidden = count(weight), rows = count(input) / hidden; spec = [eps bits]
+        const bool gated = id == "vyre-libs::nn::gated_rms_norm";
+        if (!need(gated ? 4 : 3)) return bad_shape(gated ? "four buffers input, weight, gate, out expected" : "three buffers input, weight, out expected");
+        const uint64_t hidden = count(1);
+        if (!hidden || count(0) % hidden) return bad_shape("input elements are not rows x hidden");
+        if (!op_spec || n_spec < 1) return bad_shape("the op spec must carry eps as f32 bits");
+        float eps;
+        std::memcpy(&eps, &op_spec[0], 4);
+        if (gated)
+            rc = vyb_nn_gated_rms_norm(name(0), name(1), name(2), name(3), uint32_t(count(0) / hidden), uint32_t(hidden), eps,
+                                       decl_at(decls, n_decls, 0)->dtype, &out);
+        else
+            rc = vyb_nn_learned_rms_norm(name(0), name(1), name(2), uint32_t(count(0) / hidden), uint32_t(hidden), eps,
+                                         decl_at(decls, n_decls, 0)->dtype, &out);
+    } else if (id == "vyre-libs::quant::q4_k_unpack" || id == "vyre-libs::quant::q2_k_unpack") {
+        if (!need(4)) return bad_shape("four buffers packed, scales, mins, out expected");
+        rc = id == "vyre-libs::quant::q4_k_unpack" ? vyb_quant_q4_k_unpack(name(0), name(1), name(2), name(3), uint32_t(count(3)), &out)
+                                                   : vyb_quant_q2_k_unpack(name(0), name(1), name(2), name(3), uint32_t(count(3)), &out);
+    } else if (id == "vyre-libs::quant::q4_k_linear" || id == "vyre-libs::quant::q2_k_linear") {
+        if (!need(6)) return bad_shape("six buffers x, w_packed, w_scales, w_mins, b, out expected");
+        rc = id == "vyre-libs::quant::q4_k_linear"
+                 ? vyb_quant_q4_k_linear(name(0), name(1), name(2), name(3), name(4), name(5), uint32_t(count(0)), uint32_t(count(5)), &out)
+                 : vyb_quant_q2_k_linear(name(0), name(1), name(2), name(3), name(4), name(5), uint32_t(count(0)), uint32_t(count(5)), &out);
     } else if (id == "vyre-libs::quant::int8_unpack") {
         if (!need(3)) return bad_shape("three buffers packed, scales, out expected");
         const uint64_t n = op_spec && n_spec >= 2 ? op_spec[0] : count(0);

@@ -306,6 +306,23 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
         case OpKind::TopK:
             return launch_top_k((const float*)b[0], (uint32_t*)b[1], (float*)b[2], (uint32_t*)b[3], u[0], u[1], s);
         case OpKind::Swiglu: return launch_swiglu(b[0], b[1], b[2], u[0], rt_dtype(u[1]), s);
+        case OpKind::ResidualAdd: return launch_residual_add(b[0], b[1], b[2], u[0], rt_dtype(u[1]), s);
+        case OpKind::RmsNorm: {
+            float eps;
+            std::memcpy(&eps, &u[2], 4);
+            const bool gated = u[5] != 0;
+            return launch_rms_norm(b[0], b[1], gated ? b[2] : nullptr, gated ? b[3] : b[2], u[0], u[1], eps, rt_dtype(u[3]),
+                                   rt_dtype(u[4]), s);
+        }
+        case OpKind::KQuantUnpack:
+            return launch_k_quant_unpack((const uint32_t*)b[0], (const float*)b[1], (const float*)b[2], (float*)b[3], u[0], u[1], s);
+        case OpKind::KQuantLinear:
+            if (inst->variant == KV_K_QUANT_WORD_COLUMNS && k_quant_linear_fast_supported(u[0], u[1], u[2]))
+                return launch_k_quant_linear_fast((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2], (const float*)b[3],
+                                                  (const float*)b[4], (float*)b[5], (float*)inst->scratch, u[0], u[1], u[2],
+                                                  inst->dev->prop.multiProcessorCount, s);
+            return launch_k_quant_linear((const float*)b[0], (const uint32_t*)b[1], (const float*)b[2], (const float*)b[3],
+                                         (const float*)b[4], (float*)b[5], u[0], u[1], u[2], s);
         case OpKind::ExpertMlp:
             return launch_expert_mlp((const float*)b[0], (const float*)b[1], (const float*)b[2], (const float*)b[3],
                                      (const float*)b[4], (const float*)b[5], (const float*)b[6], (float*)b[7],
@@ -358,6 +375,7 @@ size_t scratch_bytes_for(const Program& p) {
     switch (p.kind) {
         case OpKind::ExpertMlp: return size_t(p.params.u[1]) * 4;
         case OpKind::LinearInt8Dynamic: return size_t(p.params.u[0]) * p.params.u[1];
+        case OpKind::KQuantLinear: return vybk::k_quant_linear_fast_scratch_bytes(p.params.u[1]);
         case OpKind::MoeFfnInt4:
             return vybk::moe_ffn_int4_scratch_bytes(p.params.u[0], p.params.u[1], p.params.u[2], p.params.u[3], p.params.u[4]);
         default: return 0;

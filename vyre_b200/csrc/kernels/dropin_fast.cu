@@ -22,6 +22,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "kernels.h"
 
 namespace vybk {
@@ -250,6 +252,118 @@ cudaError_t launch_affine_grouped_fast(const float* x, const uint32_t* w, const 
 cudaError_t launch_i4_matvec_fast(const uint32_t* w, const float* x, const float* scales, float* out, uint32_t batch,
                                   uint32_t rows, uint32_t cols, cudaStream_t s) {
     i4_matvec_fast_kernel<<<dim3((rows + 7) / 8, (batch + MV_BT - 1) / MV_BT), 256, 0, s>>>(w, x, scales, out, batch, rows, cols);
+    return cudaGetLastError();
+}
+
+
+// ---- GGML K-quant linear at size (vyre-libs/src/nn/quant/ggml.rs:217-333) ------------------------------------------------
+// The weight stream is k-major with neighbouring outputs in neighbouring nibbles (2-bit fields for Q2_K), so a thread owns
+// FOUR neighbouring packed word COLUMNS (one 16-byte load per k row: 32 outputs for Q4_K, 64 for Q2_K) and a warp reads 512
+// contiguous bytes of one k row. The k range is cut into up to K_QUANT_K_CHUNKS chunks across blockIdx.y so that decode
+// shapes fill the GPU and every thread has eight independent 16-byte loads in flight (the loop is latency-bound
+// otherwise); inside a block eight k slices are folded through shared memory in slice order, the chunk's partial row goes
+// to scratch, and a second launch adds the chunks in chunk order and the bias (deterministic).
+// out[i] = b[i] + sum_k x[k] * (q * scale + min) with scale and minimum applied per word (x * scale once, x * min once):
+// the reference's map in another summation order.
+template <int BITS, int KS>
+__global__ void __launch_bounds__(32 * KS) k_quant_linear_fast_kernel(const float* __restrict__ x, const uint32_t* __restrict__ packed,
+                                                                      const float* __restrict__ scales, const float* __restrict__ mins,
+                                                                      float* __restrict__ partial, uint32_t in_dim, uint32_t out_dim,
+                                                                      uint32_t k_per_chunk) {
+    constexpr int VPW = 32 / BITS;                  // outputs per packed word
+    constexpr int OPT = 4 * VPW;                    // outputs per thread
+    constexpr uint32_t BLOCK = BITS == 4 ? 32 : 16; // weights per scale / min
+    extern __shared__ float red[];                  // [KS][32][OPT + 1]: a thread's row padded by one word, no bank conflicts
+    constexpr uint32_t PITCH = 32 * (OPT + 1);
+    const uint32_t tx = threadIdx.x, ky = threadIdx.y;
+    const uint32_t quads_per_row = out_dim / OPT;
+    const uint32_t quad = blockIdx.x * 32 + tx;
+    const uint32_t k_begin = blockIdx.y * k_per_chunk, k_end = min(in_dim, k_begin + k_per_chunk);
+    float acc[OPT];
+#pragma unroll
+    for (int j = 0; j < OPT; ++j) acc[j] = 0.f;
+    if (quad < quads_per_row) {
+        const uint32_t i0 = quad * OPT;
+        const uint4* wp = reinterpret_cast<const uint4*>(packed);
+#pragma unroll 8
+        for (uint32_t k = k_begin + ky; k < k_end; k += KS) {
+            const uint4 w4 = __ldg(wp + size_t(k) * quads_per_row + quad);
+            const uint32_t words[4] = {w4.x, w4.y, w4.z, w4.w};
+            const float xk = __ldg(x + k);
+            const size_t lin = size_t(k) * out_dim + i0;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const uint32_t blk = uint32_t((lin + w * VPW) / BLOCK);
+                const float xs = xk * __ldg(scales + blk), xm = xk * __ldg(mins + blk);
+#pragma unroll
+                for (int j = 0; j < VPW; ++j) {
+                    // the field as an f32 without an integer conversion: 2^23 + q has q in its low mantissa bits
+                    const float q = __uint_as_float(0x4B000000u | ((words[w] >> (j * BITS)) & ((1u << BITS) - 1u))) - 8388608.0f;
+                    acc[w * VPW + j] = fmaf(q, xs, acc[w * VPW + j] + xm);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < OPT; ++j) red[ky * PITCH + tx * (OPT + 1) + j] = acc[j];
+    __syncthreads();
+    for (uint32_t o = ky * 32 + tx; o < 32 * OPT; o += 32 * KS) {
+        const uint32_t i = blockIdx.x * 32 * OPT + o;
+        if (i >= out_dim) continue;
+        float sum = 0.f;
+#pragma unroll
+        for (int s = 0; s < KS; ++s) sum += red[s * PITCH + (o / OPT) * (OPT + 1) + o % OPT];
+        partial[size_t(blockIdx.y) * out_dim + i] = sum;
+    }
+}
+
+__global__ void k_quant_fold_kernel(const float* __restrict__ partial, const float* __restrict__ b, float* __restrict__ out,
+                                    uint32_t out_dim, uint32_t chunks) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= out_dim) return;
+    float sum = 0.f;
+#pragma unroll 16
+    for (uint32_t c = 0; c < chunks; ++c) sum += __ldg(partial + size_t(c) * out_dim + i);
+    out[i] = sum + b[i];
+}
+
+bool k_quant_linear_fast_supported(uint32_t in_dim, uint32_t out_dim, uint32_t bits) {
+    return (bits == 4 || bits == 2) && in_dim >= 1 && out_dim >= 1 && out_dim % (4 * (32 / bits)) == 0;
+}
+
+size_t k_quant_linear_fast_scratch_bytes(uint32_t out_dim) { return size_t(K_QUANT_K_CHUNKS) * out_dim * 4; }
+
+cudaError_t launch_k_quant_linear_fast(const float* x, const uint32_t* packed, const float* scales, const float* mins,
+                                       const float* b, float* out, float* partial, uint32_t in_dim, uint32_t out_dim,
+                                       uint32_t bits, int sm_count, cudaStream_t s) {
+    constexpr int KS = 8;
+    const uint32_t opt = 4 * (32 / bits);
+    const uint32_t xblocks = (out_dim / opt + 31) / 32;
+    // about two blocks per SM, 64 k rows per chunk at least (eight loads in flight per thread)
+    uint32_t chunks = (2u * uint32_t(sm_count) + xblocks - 1) / xblocks;
+    chunks = chunks > K_QUANT_K_CHUNKS ? K_QUANT_K_CHUNKS : chunks;
+    const uint32_t by_rows = (in_dim + 63) / 64;
+    chunks = chunks > by_rows ? by_rows : chunks;
+    const uint32_t k_per_chunk = (in_dim + chunks - 1) / chunks;
+    chunks = (in_dim + k_per_chunk - 1) / k_per_chunk;
+    const dim3 grid(xblocks, chunks), block(32, KS);
+    const size_t smem = size_t(KS) * 32 * (opt + 1) * 4;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaError_t de = cudaGetDevice(&dev);
+    if (de != cudaSuccess) return de;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        cudaError_t e = cudaFuncSetAttribute(k_quant_linear_fast_kernel<2, KS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             int(size_t(KS) * 32 * 65 * 4));
+        if (e != cudaSuccess) return e;
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    if (bits == 4)
+        k_quant_linear_fast_kernel<4, KS><<<grid, block, smem, s>>>(x, packed, scales, mins, partial, in_dim, out_dim, k_per_chunk);
+    else
+        k_quant_linear_fast_kernel<2, KS><<<grid, block, smem, s>>>(x, packed, scales, mins, partial, in_dim, out_dim, k_per_chunk);
+    k_quant_fold_kernel<<<(out_dim + 255) / 256, 256, 0, s>>>(partial, b, out, out_dim, chunks);
     return cudaGetLastError();
 }
 

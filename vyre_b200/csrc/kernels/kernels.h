@@ -182,6 +182,23 @@ cudaError_t launch_softmax_top_k(const float* scores, uint32_t* out_idx, float* 
 cudaError_t launch_top_k(const float* in, uint32_t* out_idx, float* best_vals, uint32_t* best_idxs, uint32_t n,
                          uint32_t k, cudaStream_t s);
 cudaError_t launch_swiglu(const void* gate, const void* up, void* out, uint32_t n, uint32_t dtype, cudaStream_t s);
+cudaError_t launch_residual_add(const void* residual, const void* branch, void* out, uint32_t n, uint32_t dtype, cudaStream_t s);
+// learned_rms_norm (gate == nullptr) and gated_rms_norm; dtypes: 0 f32, 1 bf16, 2 f16
+cudaError_t launch_rms_norm(const void* input, const void* weight, const void* gate, void* out, uint32_t rows, uint32_t hidden,
+                            float eps, uint32_t dtype, uint32_t weight_dtype, cudaStream_t s);
+// GGML K-quants with per-block f32 scale / min sidecars; bits = 4 (Q4_K) or 2 (Q2_K)
+cudaError_t launch_k_quant_unpack(const uint32_t* packed, const float* scales, const float* mins, float* out, uint32_t n,
+                                  uint32_t bits, cudaStream_t s);
+// K-quant linear at size (dropin_fast.cu; kernel variant 7): out_dim a multiple of the outputs of four packed words; `partial`
+// is scratch of k_quant_linear_fast_scratch_bytes(out_dim) bytes (one partial output row per k chunk)
+constexpr uint32_t K_QUANT_K_CHUNKS = 64;
+bool k_quant_linear_fast_supported(uint32_t in_dim, uint32_t out_dim, uint32_t bits);
+size_t k_quant_linear_fast_scratch_bytes(uint32_t out_dim);
+cudaError_t launch_k_quant_linear_fast(const float* x, const uint32_t* packed, const float* scales, const float* mins,
+                                       const float* b, float* out, float* partial, uint32_t in_dim, uint32_t out_dim,
+                                       uint32_t bits, int sm_count, cudaStream_t s);
+cudaError_t launch_k_quant_linear(const float* x, const uint32_t* packed, const float* scales, const float* mins, const float* b,
+                                  float* out, uint32_t in_dim, uint32_t out_dim, uint32_t bits, cudaStream_t s);
 // hidden_scratch: f32 [hidden]
 cudaError_t launch_expert_mlp(const float* x, const float* wg, const float* bg, const float* wu, const float* bu,
                               const float* wd, const float* bd, float* out, float* hidden_scratch, uint32_t in_dim,

@@ -285,6 +285,83 @@ __global__ void swiglu_kernel(const void* gate, const void* up, void* out, uint3
     store_typed(out, i, dt, fmul(g, fmul(u, sig)));
 }
 
+// vyre-libs/src/nn/activation/residual_add.rs:40-52: cast(dtype, f32(residual) + f32(branch))
+__global__ void residual_add_kernel(const void* residual, const void* branch, void* out, uint32_t n, uint32_t dt) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    store_typed(out, i, dt, fadd(load_typed(residual, i, dt), load_typed(branch, i, dt)));
+}
+
+// vyre-libs/src/nn/norm/gated_rms_norm.rs:123-247. The reference recomputes the row's sum of squares in every
+// invocation, one f32 chain over the row in index order; here one block owns a row: its threads stage the row through
+// shared memory (coalesced), thread 0 runs that same chain once, and all threads then normalise (x * (1 / sqrt(mean +
+// eps)), rounded to dtype, times f32(weight), times gate / (1 + exp(-gate)) with a gate, one cast). Same values.
+__global__ void rms_norm_kernel(const void* input, const void* weight, const void* gate, void* out, uint32_t hidden, float eps,
+                                uint32_t dt, uint32_t wdt) {
+    __shared__ float tile[1024];
+    __shared__ float inv_shared;
+    const size_t base = size_t(blockIdx.x) * hidden;
+    float sum = 0.0f;
+    for (uint32_t c0 = 0; c0 < hidden; c0 += 1024) {
+        const uint32_t len = min(1024u, hidden - c0);
+        for (uint32_t c = threadIdx.x; c < len; c += blockDim.x) {
+            const float v = load_typed(input, base + c0 + c, dt);
+            tile[c] = fmul(v, v);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (uint32_t c = 0; c < len; ++c) sum = fadd(sum, tile[c]);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) inv_shared = fdiv(1.0f, __fsqrt_rn(fadd(fdiv(sum, float(hidden)), eps)));
+    __syncthreads();
+    const float inv = inv_shared;
+    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float normalized = fmul(load_typed(input, base + c, dt), inv);
+        if (dt == 1) normalized = __bfloat162float(__float2bfloat16_rn(normalized));
+        else if (dt == 2) normalized = __half2float(__float2half_rn(normalized));
+        float v = fmul(normalized, load_typed(weight, c, wdt));
+        if (gate) {
+            const float g = load_typed(gate, base + c, dt);
+            v = fmul(v, fdiv(g, fadd(1.0f, expf(-g))));
+        }
+        store_typed(out, base + c, dt, v);
+    }
+}
+
+// vyre-libs/src/nn/quant/ggml.rs:28-120 and 217-333. bits = 4: blocks of 32 weights in 4 words; bits = 2: blocks of 16 in 1
+__device__ __forceinline__ uint32_t k_quant_value(const uint32_t* packed, uint32_t linear, uint32_t bits, uint32_t* block) {
+    const uint32_t block_size = bits == 4 ? 32u : 16u, values_per_byte = 8u / bits, words_per_block = bits == 4 ? 4u : 1u;
+    const uint32_t block_idx = linear / block_size, within = linear % block_size;
+    const uint32_t byte_idx = within / values_per_byte, value_shift = (within % values_per_byte) * bits;
+    const uint32_t word = packed[size_t(block_idx) * words_per_block + byte_idx / 4];
+    *block = block_idx;
+    return (word >> ((byte_idx % 4) * 8 + value_shift)) & ((1u << bits) - 1u);
+}
+__global__ void k_quant_unpack_kernel(const uint32_t* packed, const float* scales, const float* mins, float* out, uint32_t n,
+                                      uint32_t bits) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    uint32_t block;
+    const uint32_t q = k_quant_value(packed, i, bits, &block);
+    out[i] = fadd(fmul(float(q), scales[block]), mins[block]);
+}
+// thread per output, k ascending, every product and sum rounded on its own. Neighbouring outputs sit in neighbouring
+// nibbles of the k-major weight stream, so a warp reads 16 (Q4_K) or 8 (Q2_K) contiguous bytes per k.
+__global__ void k_quant_linear_kernel(const float* x, const uint32_t* packed, const float* scales, const float* mins,
+                                      const float* b, float* out, uint32_t in_dim, uint32_t out_dim, uint32_t bits) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= out_dim) return;
+    float acc = b[i];
+    for (uint32_t k = 0; k < in_dim; ++k) {
+        uint32_t block;
+        const uint32_t q = k_quant_value(packed, k * out_dim + i, bits, &block);
+        const float weight = fadd(fmul(float(q), scales[block]), mins[block]);
+        acc = fadd(acc, fmul(x[k], weight));
+    }
+    out[i] = acc;
+}
+
 // vyre-libs/src/nn/moe/expert_mlp.rs:46-150 split in two launches: hidden activations once, then the down
 // projection (the reference recomputes the hidden vector per output thread; values are identical).
 __global__ void expert_hidden_kernel(const float* x, const float* wg, const float* bg, const float* wu,
@@ -401,6 +478,25 @@ cudaError_t launch_softmax_top_k(const float* scores, uint32_t* out_idx, float* 
 cudaError_t launch_top_k(const float* in, uint32_t* out_idx, float* best_vals, uint32_t* best_idxs, uint32_t n,
                          uint32_t k, cudaStream_t s) {
     top_k_kernel<<<1, 1, 0, s>>>(in, out_idx, best_vals, best_idxs, n, k);
+    return cudaGetLastError();
+}
+cudaError_t launch_residual_add(const void* residual, const void* branch, void* out, uint32_t n, uint32_t dtype, cudaStream_t s) {
+    residual_add_kernel<<<blocks(n, 256), 256, 0, s>>>(residual, branch, out, n, dtype);
+    return cudaGetLastError();
+}
+cudaError_t launch_rms_norm(const void* input, const void* weight, const void* gate, void* out, uint32_t rows, uint32_t hidden,
+                            float eps, uint32_t dtype, uint32_t weight_dtype, cudaStream_t s) {
+    rms_norm_kernel<<<rows, 256, 0, s>>>(input, weight, gate, out, hidden, eps, dtype, weight_dtype);
+    return cudaGetLastError();
+}
+cudaError_t launch_k_quant_unpack(const uint32_t* packed, const float* scales, const float* mins, float* out, uint32_t n,
+                                  uint32_t bits, cudaStream_t s) {
+    k_quant_unpack_kernel<<<blocks(n, 256), 256, 0, s>>>(packed, scales, mins, out, n, bits);
+    return cudaGetLastError();
+}
+cudaError_t launch_k_quant_linear(const float* x, const uint32_t* packed, const float* scales, const float* mins, const float* b,
+                                  float* out, uint32_t in_dim, uint32_t out_dim, uint32_t bits, cudaStream_t s) {
+    k_quant_linear_kernel<<<blocks(out_dim, 64), 64, 0, s>>>(x, packed, scales, mins, b, out, in_dim, out_dim, bits);
     return cudaGetLastError();
 }
 cudaError_t launch_swiglu(const void* gate, const void* up, void* out, uint32_t n, uint32_t dtype, cudaStream_t s) {

@@ -179,6 +179,14 @@ _STATUS_FUNCS = {
     "vyb_nn_top_k": [_S, _S, _U, _U, _PP],
     "vyb_nn_swiglu": [_S] * 3 + [_U, _PP],
     "vyb_nn_swiglu_typed": [_S] * 3 + [_U, _U, _PP],
+    "vyb_nn_residual_add": [_S] * 3 + [_U, _PP],
+    "vyb_nn_residual_add_typed": [_S] * 3 + [_U, _U, _PP],
+    "vyb_nn_learned_rms_norm": [_S] * 3 + [_U, _U, C.c_float, _U, _PP],
+    "vyb_nn_gated_rms_norm": [_S] * 4 + [_U, _U, C.c_float, _U, _PP],
+    "vyb_quant_q4_k_unpack": [_S] * 4 + [_U, _PP],
+    "vyb_quant_q2_k_unpack": [_S] * 4 + [_U, _PP],
+    "vyb_quant_q4_k_linear": [_S] * 6 + [_U, _U, _PP],
+    "vyb_quant_q2_k_linear": [_S] * 6 + [_U, _U, _PP],
     "vyb_nn_expert_mlp": [_S] * 8 + [_U] * 3 + [_PP],
     "vyb_nn_moe_layer_route_and_accumulate": [_S] * 7 + [_U] * 4 + [_PP],
     "vyb_nn_linear_int4_grouped_rowmajor": [_S] * 4 + [_U] * 5 + [_PP],
