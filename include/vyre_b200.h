@@ -557,6 +557,30 @@ uint32_t vyb_completion_output_count(const vyb_completion* c);
 int32_t vyb_completion_device_ns(const vyb_completion* c, uint64_t* ns);
 void vyb_completion_free(vyb_completion* c);
 
+/* ---- the reference's authenticated wire frames -----------------------------------------------------------
+ * vyre-megakernel frames its three layers alike (lib.rs:1326-1355, envelope.rs:763-860):
+ *   magic[4] | schema u16 LE | body_len u32 LE | body (compact serde_json) | BLAKE3(domain | schema | body_len u64 | body)
+ * layer 0: VMK0 neutral artifact (schema 4), 1: VTP0 target payload (schema 3), 2: VME0 envelope (schema 2).
+ * vyb_frame_encode / _decode are the framing alone (decode runs the reference's checks in its order: length, magic,
+ * schema, declared length, digest). vyb_payload_to_vtp0 writes this backend's payload as a TargetPayloadBody
+ * (envelope.rs:182-192) bound to the neutral artifact digest the caller holds (Artifact::digest() of vyre's own
+ * compiler); `value_ids` maps the program's bound buffers, in declaration order, to ArtifactValueIds (NULL: the
+ * binding slots). vyb_envelope_to_vme0 wraps one neutral frame and payload frames as an EnvelopeBody
+ * (envelope.rs:383-389) and refuses a payload bound to another artifact. The VMK0 body is the reference compiler's
+ * output: it is authenticated and carried here, never produced. Frames handed out are freed with vyb_frame_free. */
+int32_t vyb_frame_encode(uint32_t layer, const uint8_t* body, size_t body_len, uint8_t** frame, size_t* frame_len);
+int32_t vyb_frame_decode(uint32_t layer, const uint8_t* frame, size_t frame_len, const uint8_t** body, size_t* body_len,
+                         uint8_t digest[32]);
+void vyb_frame_free(uint8_t* frame);
+int32_t vyb_payload_to_vtp0(const vyb_payload* payload, const uint8_t neutral_artifact[32], uint32_t node_id,
+                            const uint32_t* value_ids, uint32_t n_value_ids, uint8_t** frame, size_t* frame_len);
+int32_t vyb_payload_from_vtp0(const uint8_t* frame, size_t frame_len, vyb_payload** payload, uint8_t neutral_artifact[32]);
+int32_t vyb_envelope_to_vme0(const uint8_t* vmk0, size_t vmk0_len, const uint8_t* const* vtp0, const size_t* vtp0_len,
+                             uint32_t n_payloads, uint8_t** frame, size_t* frame_len);
+/* index 0: the neutral artifact's frame, 1..n: the payload frames; inner may be NULL to only authenticate and count */
+int32_t vyb_envelope_from_vme0(const uint8_t* frame, size_t frame_len, uint32_t index, uint8_t** inner, size_t* inner_len,
+                               uint32_t* n_payloads);
+
 /* ---- scratch-reusing callers of the packed-int4 primitives -----------------------------------------------
  * vyre-self-substrate/src/math/quantized_dispatch.rs:30-90 and quantized_dispatch/{unpack,dot,matvec,batched_matvec,
  * batched_matmul,top1}.rs: the `*_via_with_scratch_into` functions. Host slices in (pointer + element count), host

@@ -1154,3 +1154,64 @@ def i4x8_batched_matmul_top1_f32_scaled_via(scratch: QuantizedScratch, weights_p
                                                                 rs.ctypes.data, rs.size, bs.ctypes.data, bs.size, batch, rows,
                                                                 cols, scores.ctypes.data, idx.ctypes.data))
     return scores[:batch], idx[:batch]
+
+
+# ---- the reference's wire frames (vyre-megakernel/src/lib.rs:1326-1355, envelope.rs:763-860) ---------------------------------
+FRAME_VMK0, FRAME_VTP0, FRAME_VME0 = 0, 1, 2
+
+
+def _take_frame(ptr, n) -> bytes:
+    try:
+        return C.string_at(ptr, n.value)
+    finally:
+        ffi.lib().vyb_frame_free(ptr)
+
+
+def frame_encode(layer: int, body: bytes) -> bytes:
+    out, n = C.c_void_p(), C.c_size_t()
+    check(ffi.lib().vyb_frame_encode(layer, body, len(body), C.byref(out), C.byref(n)))
+    return _take_frame(out, n)
+
+
+def frame_decode(layer: int, frame: bytes) -> tuple[bytes, bytes]:
+    """(body, digest) of an authenticated frame."""
+    body, n, digest = C.c_void_p(), C.c_size_t(), C.create_string_buffer(32)
+    buf = C.create_string_buffer(frame, len(frame))
+    check(ffi.lib().vyb_frame_decode(layer, buf, len(frame), C.byref(body), C.byref(n), digest))
+    return C.string_at(body, n.value), digest.raw
+
+
+def payload_to_vtp0(payload: TargetPayload, neutral_artifact: bytes, node_id: int = 0, value_ids: list[int] | None = None) -> bytes:
+    """TargetPayload::to_bytes of the reference for this backend's payload, bound to `neutral_artifact` (32 bytes)."""
+    ids = (C.c_uint32 * max(1, len(value_ids or [])))(*(value_ids or []))
+    out, n = C.c_void_p(), C.c_size_t()
+    check(ffi.lib().vyb_payload_to_vtp0(payload._h, neutral_artifact, node_id, ids if value_ids else None, len(value_ids or []),
+                                        C.byref(out), C.byref(n)))
+    return _take_frame(out, n)
+
+
+def payload_from_vtp0(frame: bytes) -> tuple[TargetPayload, bytes]:
+    out, neutral = C.c_void_p(), C.create_string_buffer(32)
+    check(ffi.lib().vyb_payload_from_vtp0(frame, len(frame), C.byref(out), neutral))
+    return TargetPayload(out.value), neutral.raw
+
+
+def envelope_to_vme0(vmk0: bytes, payload_frames: list[bytes]) -> bytes:
+    k = len(payload_frames)
+    ptrs = (C.c_char_p * max(1, k))(*payload_frames)
+    lens = (C.c_size_t * max(1, k))(*[len(f) for f in payload_frames])
+    out, n = C.c_void_p(), C.c_size_t()
+    check(ffi.lib().vyb_envelope_to_vme0(vmk0, len(vmk0), ptrs, lens, k, C.byref(out), C.byref(n)))
+    return _take_frame(out, n)
+
+
+def envelope_from_vme0(frame: bytes) -> tuple[bytes, list[bytes]]:
+    """(neutral artifact frame, payload frames) of an authenticated envelope."""
+    count = C.c_uint32()
+    check(ffi.lib().vyb_envelope_from_vme0(frame, len(frame), 0, None, None, C.byref(count)))
+    parts = []
+    for i in range(count.value + 1):
+        out, n = C.c_void_p(), C.c_size_t()
+        check(ffi.lib().vyb_envelope_from_vme0(frame, len(frame), i, C.byref(out), C.byref(n), None))
+        parts.append(_take_frame(out, n))
+    return parts[0], parts[1:]

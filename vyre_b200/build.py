@@ -32,6 +32,7 @@ SOURCES = {
     "host/safetensors.cpp": [],
     "host/graph.cpp": [],
     "host/substrate.cpp": [],
+    "host/frames.cpp": [],
     "host/runtime.cu": [],
     "kernels/ref_ops.cu": ["-ftz=true", "-prec-div=true", "-prec-sqrt=true", "-fmad=false"],
     "kernels/dropin_fast.cu": ["-ftz=true", "-fmad=false"],

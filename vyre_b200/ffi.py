@@ -210,6 +210,12 @@ _STATUS_FUNCS = {
     "vyb_safetensors_require": [_P, _S, _S, C.POINTER(C.c_uint64), _U, C.POINTER(C.c_uint32)],
     "vyb_safetensors_upload": [_P, _U, _P, ResidentHandle, C.c_uint64],
     "vyb_quantized_scratch_new": [_P, _PP],
+    "vyb_frame_encode": [_U, _P, C.c_size_t, _PP, C.POINTER(C.c_size_t)],
+    "vyb_frame_decode": [_U, _P, C.c_size_t, _PP, C.POINTER(C.c_size_t), C.c_char_p],
+    "vyb_payload_to_vtp0": [_P, C.c_char_p, _U, _P, _U, _PP, C.POINTER(C.c_size_t)],
+    "vyb_payload_from_vtp0": [_P, C.c_size_t, _PP, C.c_char_p],
+    "vyb_envelope_to_vme0": [_P, C.c_size_t, _P, _P, _U, _PP, C.POINTER(C.c_size_t)],
+    "vyb_envelope_from_vme0": [_P, C.c_size_t, _U, _PP, C.POINTER(C.c_size_t), C.POINTER(C.c_uint32)],
     "vyb_unpack_i4x8_via": [_P, _P, C.c_size_t, _U, _P],
     "vyb_i4x8_dot_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, C.c_float, C.c_float, _U, _P],
     "vyb_i4x8_matvec_f32_scaled_via": [_P, _P, C.c_size_t, _P, C.c_size_t, _P, C.c_size_t, _U, _U, _P],
@@ -295,6 +301,7 @@ _OTHER_FUNCS = {
     "vyb_safetensors_free": (None, [_P]),
     "vyb_safetensors_identity": (None, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vyb_quantized_scratch_free": (None, [_P]),
+    "vyb_frame_free": (None, [_P]),
     "vyb_quantized_scratch_stats": (None, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vyb_safetensors_count": (C.c_uint32, [_P]),
     "vyb_payload_format": (C.c_char_p, [_P]),
