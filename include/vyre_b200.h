@@ -531,7 +531,8 @@ void vyb_instance_free(vyb_instance* i);
 int32_t vyb_submit(vyb_instance* instance, const uint8_t artifact_digest[32], const vyb_binding* bindings,
                    size_t n_bindings, const vyb_dispatch_config* config, vyb_submission** submission);
 /* A binding set validated once and frozen into a single device-side graph (copy of the host inputs in, kernels,
- * copy of the outputs and of the status words out), for a caller that submits the same artifact with the same
+ * copy of the outputs out; small outputs that a kernel writes completely are stored by the kernel straight into the
+ * set's mapped pinned host buffer, and the status words live in a mapped pinned slot of the set), for a caller that submits the same artifact with the same
  * resident buffers over and over and only changes its host inputs. No counterpart in the reference, whose
  * ArtifactSession::submit (vyre-runtime/src/artifact_admission.rs:152-496) validates and stages every BindingSet
  * anew; the result of a replay equals that of vyb_submit with the same bindings. vyb_prepare runs one ordinary

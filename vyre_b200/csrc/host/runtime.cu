@@ -191,6 +191,7 @@ struct OutputSlot {
     void* dev_ptr = nullptr;
     size_t len = 0;
     void* host = nullptr;  // pinned readback target, nullptr when left resident
+    bool direct = false;   // prepared sets: the kernel writes straight into `host` (mapped pinned memory), no copy node
 };
 }  // namespace
 
@@ -1002,6 +1003,7 @@ void vyb_completion_free(vyb_completion* c) {
 }
 
 // ---- prepared binding sets: one CUDA graph per set, one graph launch per submission ---------------------------------
+constexpr size_t DIRECT_OUTPUT_BYTES = 256 * 1024;
 int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const vyb_binding* bindings, size_t n_bindings,
                     vyb_prepared** prepared) {
     if (!prepared) return fail_invalid_program("Fix: pass a non-null prepared out-pointer.");
@@ -1045,6 +1047,7 @@ int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const
         const bool is_input = bd.access == VYB_ACCESS_READ_ONLY || bd.access == VYB_ACCESS_READ_WRITE;
         const bool is_output = bd.access == VYB_ACCESS_OUTPUT || bd.access == VYB_ACCESS_READ_WRITE;
         void* dev_ptr = nullptr;
+        void* direct_host = nullptr;
         if (b && b->kind == VYB_BIND_RESIDENT) {
             std::lock_guard<std::mutex> lk(d->mu);
             Resident* r = nullptr;
@@ -1055,6 +1058,17 @@ int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const
             r->inflight++;  // held for the life of the prepared set: the graph has the pointer baked in
             prep->resident_ids.push_back(b->resident.id);
             dev_ptr = r->ptr;
+        } else if (!is_input && is_output && !bd.has_output_byte_range && need <= DIRECT_OUTPUT_BYTES &&
+                   overwrites_every_output_byte(p)) {
+            // A small output that its kernel writes completely: the kernel stores straight into mapped pinned host memory
+            // (posted writes over PCIe, a few hundred transactions), which saves the device buffer and the copy node.
+            direct_host = inst->acquire_pinned(need);
+            if (!direct_host || cudaHostGetDevicePointer(&dev_ptr, direct_host, 0) != cudaSuccess) {
+                cudaGetLastError();
+                if (direct_host) inst->release_pinned(direct_host);
+                undo();
+                return fail_oom(need, 0);
+            }
         } else {
             dev_ptr = inst->acquire_temp(need);
             if (!dev_ptr) {
@@ -1080,7 +1094,8 @@ int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const
             o.value_id = bd.binding;
             o.dev_ptr = static_cast<uint8_t*>(dev_ptr) + (bd.has_output_byte_range ? bd.output_byte_begin : 0);
             o.len = logical;
-            o.host = inst->acquire_pinned(logical);
+            o.direct = direct_host != nullptr;
+            o.host = direct_host ? direct_host : inst->acquire_pinned(logical);
             if (!o.host) {
                 undo();
                 return fail_oom(logical, 0);
@@ -1102,10 +1117,21 @@ int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const
             cudaMemcpyAsync(dst, in.staging, in.len, cudaMemcpyHostToDevice, inst->stream);
         }
         for (auto& z : zero_fill) cudaMemsetAsync(z.first, 0, z.second, inst->stream);
+        // The kernels of a prepared set raise their status words straight in the set's own mapped pinned slot (they touch it
+        // only when a bounded wait runs out), so the graph needs no status copy and no reset node: the host clears the
+        // slot before every replay and reads it after the set's event.
+        uint32_t* const shared_status = inst->status_dev;
+        void* own_status = nullptr;
+        if (cudaHostGetDevicePointer(&own_status, prep->status_host, 0) == cudaSuccess) inst->status_dev = static_cast<uint32_t*>(own_status);
         cudaError_t le = dispatch(inst, slot_ptr, inst->stream);
-        for (auto& o : prep->outputs) cudaMemcpyAsync(o.host, o.dev_ptr, o.len, cudaMemcpyDeviceToHost, inst->stream);
-        cudaMemcpyAsync(prep->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
-        cudaMemsetAsync(inst->status_dev, 0, 16, inst->stream);
+        inst->status_dev = shared_status;
+        for (auto& o : prep->outputs)
+            if (!o.direct) cudaMemcpyAsync(o.host, o.dev_ptr, o.len, cudaMemcpyDeviceToHost, inst->stream);
+        if (!own_status) {
+            cudaGetLastError();
+            cudaMemcpyAsync(prep->status_host, inst->status_dev, 16, cudaMemcpyDeviceToHost, inst->stream);
+            cudaMemsetAsync(inst->status_dev, 0, 16, inst->stream);
+        }
         e = cudaStreamEndCapture(inst->stream, &graph);
         if (e == cudaSuccess && le != cudaSuccess) e = le;
     }
@@ -1149,7 +1175,7 @@ int32_t vyb_prepared_submit(vyb_prepared* prep, const vyb_binding* host_updates,
         std::memcpy(in->staging, b.host_ptr, in->len);  // copied in, like a fresh BindingSet
     }
     cudaSetDevice(d->ordinal);
-    prep->status_host[0] = 0;
+    std::memset(prep->status_host, 0, 16);
     cudaError_t e = cudaGraphLaunch(prep->exec, inst->stream);
     if (e == cudaSuccess) e = cudaEventRecord(prep->done, inst->stream);
     if (e != cudaSuccess) {
