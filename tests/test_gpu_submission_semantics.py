@@ -93,3 +93,36 @@ def test_prepared_submissions_equal_ordinary_ones(dev):
     prep.free()
     dev.free_resident(hw)
     dev.free_resident(hs)
+
+
+@pytest.mark.parametrize("m,n,out_dtype", [(8, 4096, ffi.DT_F32),     # 128 KB: the kernel stores into the set's mapped host buffer
+                                           (8, 14336, ffi.DT_F32),    # 448 KB: device buffer plus a copy node
+                                           (40, 2048, ffi.DT_BF16)])  # the tensor-core path (batch > 8), 160 KB, direct
+def test_prepared_outputs_direct_or_copied_equal_ordinary_submissions(dev, m, n, out_dtype):
+    k = 4096
+    x, w, s = synth.int4_linear_inputs(m, n, k, seed=21)
+    prog = vb.linear_int4_grouped_rowmajor("x", "w", "scale", "out", m, k, n, 128, out_dtype)
+    sess = vb.ArtifactSession.compile(prog, dev)
+    hw, hs = dev.resident_from(w.view(np.uint32)), dev.resident_from(s)
+    bs = vb.BindingSet(sess.artifact.digest())
+    bs.insert_host(0, x)
+    bs.insert_resident(1, hw)
+    bs.insert_resident(2, hs)
+    want = sess.submit(bs).wait().output(3)
+    prep = sess.prepare(bs)
+    for _ in range(3):  # replays reuse the same output buffer
+        done = prep.submit({0: x}).wait()
+        assert done.output(3) == want
+        del done
+    x2 = synth.int4_linear_inputs(m, 16, k, seed=22)[0]
+    bs2 = vb.BindingSet(sess.artifact.digest())
+    bs2.insert_host(0, x2)
+    bs2.insert_resident(1, hw)
+    bs2.insert_resident(2, hs)
+    want2 = sess.submit(bs2).wait().output(3)
+    done = prep.submit({0: x2}).wait()
+    assert done.output(3) == want2 and want2 != want
+    del done
+    prep.free()
+    dev.free_resident(hw)
+    dev.free_resident(hs)
