@@ -944,27 +944,50 @@ def run_quick(args) -> None:
         return
     L = ffi.lib()
     m = args.m
-    x_np, w_np, s_np = synth.int4_linear_inputs(m, N_OUT, K_IN, seed=0)
+    n_out = args.rows or N_OUT
+    x_np, w_np, s_np = synth.int4_linear_inputs(m, n_out, K_IN, seed=0)
     x = torch.from_numpy(x_np.view(np.int16)).cuda()
     copies = max(1, args.copies)
     ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(copies)]
     ss = [torch.from_numpy(np.roll(s_np, c, axis=0).view(np.int16)).cuda() for c in range(copies)]
-    y = torch.zeros((m, N_OUT), dtype=torch.bfloat16, device="cuda")
+    y = torch.zeros((m, n_out), dtype=torch.bfloat16, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    stream = torch.cuda.current_stream().cuda_stream
     it = [0]
 
-    def launch():
+    def launch(stream=None):
         c = it[0] % copies
         it[0] += 1
-        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, N_OUT, K_IN,
-                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS, C.c_void_p(stream),
-                                       C.c_void_p(status.data_ptr())))
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, n_out, K_IN,
+                                       GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
+                                       C.c_void_p(stream or torch.cuda.current_stream().cuda_stream), C.c_void_p(status.data_ptr())))
 
-    us = event_time_us(launch, args.steps, args.warmup)
+    if args.graph:
+        # the headline's launch pattern for any batch and row count: a graph of LAUNCHES launches, replayed `steps` times
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(copies):
+                launch(side.cuda_stream)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(LAUNCHES):
+                    launch(side.cuda_stream)
+            for _ in range(max(3, args.warmup)):
+                graph.replay()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(side)
+            for _ in range(args.steps):
+                graph.replay()
+            b.record(side)
+        side.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (args.steps * LAUNCHES)
+    else:
+        us = event_time_us(launch, args.steps, args.warmup)
     assert status.cpu().tolist() == [0, 0, 0, 0]
-    print(json.dumps({"quick": True, "m": m, "steps": args.steps, "copies": copies, "us_per_launch": us,
-                      "gbs": algorithmic_bytes(m) / (us * 1e-6) / 1e9}))
+    gbs = algorithmic_bytes(m, n=n_out) / (us * 1e-6) / 1e9
+    print(json.dumps({"quick": True, "m": m, "rows": n_out, "graph": bool(args.graph), "steps": args.steps, "copies": copies,
+                      "us_per_launch": round(us, 3), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4)}))
 
 
 def main() -> None:
@@ -981,6 +1004,9 @@ def main() -> None:
                     help="graph replays of the kernel-only roofline region (0: max(steps, 60)); small values shorten a profiler's launch list")
     ap.add_argument("--copies", type=int, default=COPIES,
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
+    ap.add_argument("--rows", type=int, default=0, help="weight rows N in --quick --case gemv (0: the configuration's 14336)")
+    ap.add_argument("--graph", action="store_true",
+                    help="--quick --case gemv: time replays of a CUDA graph of 64 launches (the headline's launch pattern) instead of single launches")
     ap.add_argument("--quick", action="store_true",
                     help="kernel-only run without graphs, end-to-end leg or CPU baseline (the case profiled under ncu)")
     args = ap.parse_args()
