@@ -287,6 +287,45 @@ def measure_int8(shape, steps: int, warmup: int, i8_peak: float, peaks: dict) ->
                          "us_per_launch": round(us, 1), "algorithmic_ops_per_launch": 2 * m * n * k}}
 
 
+def measure_int8_weight_only(peaks: dict, reps: int = 200) -> dict:
+    """Config 1 (the reference-runnable case): f32 activations [16, 1024], int8 weights [1024, 1024] with per-channel f32
+    scales, dequantised on the fly. 1 MB of weights: a latency-sized launch, timed back to back over 16 rotating weight copies
+    and checked in full against torch f32 on the device."""
+    import numpy as np
+    import torch
+
+    from vyre_b200 import ffi, synth
+
+    L = ffi.lib()
+    m, n, k = 16, 1024, 1024
+    x_np, w_np, s_np = synth.int8_weight_only_inputs(m, n, k, seed=0)
+    x, sc = torch.from_numpy(x_np).cuda(), torch.from_numpy(s_np).cuda()
+    ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(16)]
+    y = torch.empty((m, n), dtype=torch.float32, device="cuda")
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    it = [0]
+
+    def launch():
+        c = it[0] % len(ws)
+        it[0] += 1
+        ffi.check(L.vyb_k_int8_weight_only_linear(x.data_ptr(), ws[c].data_ptr(), sc.data_ptr(), y.data_ptr(), m, n, k, stream))
+
+    us = event_time_us(launch, reps, 20)
+    it[0] = 0
+    launch()
+    torch.cuda.synchronize()
+    want = x.double() @ (ws[0].double() * sc.double()[:, None]).T
+    err = float(((y.double() - want).abs().max() / want.abs().max()).item())
+    assert err <= 1e-4, f"int8 weight-only linear disagrees with f64: {err}"
+    abytes = n * k + n * 4 + m * k * 4 + m * n * 4
+    gbs = abytes / (us * 1e-6) / 1e9
+    return {"shape": {"m": m, "n": n, "k": k}, "us_per_launch": round(us, 2), "gflops": round(2.0 * m * n * k / (us * 1e-6) / 1e9, 1),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": round(gbs / peaks["hbm_gbs"], 4),
+                         "algorithmic_bytes_per_launch": abytes, "kernel": "int8_weight_only_tiled_kernel",
+                         "note": "1.2 MB per launch: launch latency, not bandwidth, bounds this configuration; the weights fit L2"},
+            "parity": {"max_rel_err_vs_f64_full_output": err, "tolerance": 1e-4}}
+
+
 def measure_dropin_1m(local_rank: int, samples: int = 30, shape=(256, 4096, 64, 256), peaks: dict | None = None) -> dict:
     """The one workload the reference publishes on this path, through the reference's own operator id and layout:
     `nn.linear_4bit_affine_grouped.1m` (vyre-bench/src/cases/quantized_linear.rs:30-40: in_dim 256, out_dim 4096, group 64,
@@ -812,6 +851,7 @@ def run_native(args) -> None:
                                                  "how": "tcgen05.mma 128x256 tiles from shared-memory operands, one CTA per SM"}
     secondary["int4_prefill_gemm_config3"] = measure_prefill([2048, 14336, 4096], 20, 5, peaks)
     secondary["int8_gemm_config5_single_gpu"] = measure_int8([4096, 28672, 8192], 10, 3, i8_peak, peaks)
+    secondary["int8_weight_only_config1"] = measure_int8_weight_only(peaks)
     secondary["dropin_1m"] = measure_dropin_1m(local_rank)
     secondary["dropin_decode_shape"] = measure_dropin_1m(local_rank, shape=(K_IN, N_OUT, GROUP, 1), peaks=peaks)
     secondary["k_quant_linear"] = measure_k_quant(local_rank, peaks)
