@@ -124,6 +124,28 @@ def test_decode_gemv_outlier_activations(dev, m, log2_ratio, outlier_nibble):
         assert err <= TOL_BF16_OUT, err
 
 
+@pytest.mark.parametrize("m", [1, 2, 4, 8])
+@pytest.mark.parametrize("n,k", [(4096, 14336), (300, 8192), (70, 6144)])
+def test_decode_gemv_long_rows_run_k_block_by_k_block(dev, m, n, k):
+    # rows of 6144, 8192, 14336 (multiples of 2048 beyond 4096): one launch of the half-SM kernel per block of 4096 / 2048
+    # columns, the sums carried in f32 from launch to launch
+    x, w, s = synth.int4_linear_inputs(m, n, k, seed=k + m)
+    got = run_int4(dev, x, w, s, m, n, k)
+    want = oracle.int4_rowmajor_linear(x, w, s, m, n, k)
+    assert rel_err(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= TOL_BF16_OUT
+    got32 = run_int4(dev, x, w, s, m, n, k, out_dtype=ffi.DT_F32)
+    want32 = oracle.int4_rowmajor_linear(x, w, s, m, n, k, out_dtype=oracle.DT_F32)
+    assert rel_err(got32, want32) <= TOL_F32_ACC
+    # outliers in every group, the outlier on a zero weight: the per-block conversion keeps the small elements
+    x, w, s = _outlier_inputs(m, n, k, 10, 8, seed=k)
+    got32 = run_int4(dev, x, w, s, m, n, k, out_dtype=ffi.DT_F32)
+    want32 = oracle.int4_rowmajor_linear(x, w, s, m, n, k, out_dtype=oracle.DT_F32)
+    assert rel_err(got32, want32) <= TOL_F32_ACC
+    got = run_int4(dev, x, w, s, m, n, k)
+    want = oracle.int4_rowmajor_linear(x, w, s, m, n, k)
+    assert rel_err(synth.bf16_bits_to_f32(got), synth.bf16_bits_to_f32(want)) <= TOL_BF16_OUT
+
+
 def test_decode_gemv_other_row_lengths_with_outliers(dev):
     # k that is not 2048 or 4096 takes the bulk-copy kernel, which keeps 22 bits per group: exact for elements within
     # 2^-14 of their group's maximum

@@ -542,6 +542,20 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
     // Whole rows of 2048 or 4096 k: the half-SM kernel, whose launches overlap on every SM. bf16 outputs go four batch
     // rows at a time (26-bit block-floating activations, 57-bit for a single row); f32 outputs one row at a time, so
     // that every row gets the single-row precision.
+    // Rows of 6144, 8192, ... (multiples of 2048 beyond 4096): the half-SM kernel per k block, sums carried in f32. bf16
+    // outputs four batch rows at a time, f32 outputs one row at a time (single-row precision), like the whole-row path.
+    if (int4_gemv_kblocks_supported(1, n, k, 128)) {
+        const size_t out_elem = out_f32 ? 4 : 2;
+        const uint32_t step = out_f32 ? 1 : 4;
+        for (uint32_t b0 = 0; b0 < m; b0 += step) {
+            const uint32_t mb = m - b0 < step ? m - b0 : step;
+            cudaError_t e = launch_int4_gemv_kblocks(static_cast<const uint16_t*>(x_bf16) + size_t(b0) * k, w_packed, scale_bf16,
+                                                     static_cast<uint8_t*>(y) + size_t(b0) * n * out_elem, mb, n, k, out_f32,
+                                                     sm_count, stream, constant_weights);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
     // Three to eight batch rows (f32 outputs: from two rows): one launch on the f16 tensor path, eight batch rows per MMA
     if (m >= (out_f32 ? 2u : 3u) && int4_gemv_batch8_supported(m, n, k, 128))
         return launch_int4_gemv_batch8(x_bf16, w_packed, scale_bf16, y, m, n, k, out_f32, sm_count, stream, constant_weights);

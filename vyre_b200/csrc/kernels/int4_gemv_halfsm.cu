@@ -100,6 +100,11 @@ struct Params {
     uint32_t half;
     uint32_t pipelined;  // the peer stores of launch d are issued at the start of launch d + 1 and drain under its work
     uint32_t* status;
+    // the k-block form only (STRIDED): this launch covers K columns of a wider matrix
+    uint32_t row_bytes;     // packed bytes between two rows of W
+    uint32_t scale_stride;  // scales between two rows
+    uint32_t x_stride;      // elements between two batch rows of x
+    const float* acc_in;    // [m][n] f32 sums of the k blocks before this one (nullptr: none), added in the reduction
 };
 
 // Pipelined gathering form, kept out of line (the kernel below runs at the edge of its register budget): carry the
@@ -141,14 +146,14 @@ __device__ __noinline__ void gather_carry(const Params& p, uint32_t r0, uint32_t
 // the next launch's activations wait for exactly that. So launch d stores into the LOCAL buffer only and leaves its slice
 // to launch d + 1, whose CTAs copy their own rows of it to the peers right after the dependency wait (gather_carry). The
 // arrival signal for slice d is then sent by launch d + 2, or by the wait kernel, which also carries the last slice over.
-template <int NM, int GPW, int W, bool OUT_F32, bool GATHER>
+template <int NM, int GPW, int W, bool OUT_F32, bool GATHER, bool STRIDED = false>
 __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // let the next launch of the stream become resident beside this one at once; it waits (griddepcontrol.wait)
     // before it reads activations or writes outputs. A no-op for plain launches.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr uint32_t K = 128u * GPW * W;
-    constexpr uint32_t ROW_BYTES = K / 2;            // packed bytes of one row of W
+    constexpr uint32_t ROW_BYTES_DENSE = K / 2;      // packed bytes of one row of W when the launch covers whole rows
     constexpr uint32_t PITCH = GPW * 64;             // of which this warp owns (= row pitch of its stages)
     constexpr uint32_t CPR = GPW * 4;                // 16-byte chunks per row slice
     constexpr uint32_t RPI = 32 / CPR;               // rows covered by one warp-wide cp.async
@@ -165,6 +170,10 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     static_assert(W * STAGES * (WSTAGE + SSTAGE) <= SMEM_W + SMEM_S, "stages must fit");
 
     uint8_t* red = smem + SMEM_W + SMEM_S;
+    // whole rows: compile-time strides; a k block of a wider matrix (STRIDED): the strides of that matrix
+    const uint32_t ROW_BYTES = STRIDED ? p.row_bytes : ROW_BYTES_DENSE;
+    const uint32_t SCALE_STRIDE = STRIDED ? p.scale_stride : K / 128;
+    const uint32_t X_STRIDE = STRIDED ? p.x_stride : K;
 
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
@@ -185,7 +194,7 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     const uint8_t* cp_src = p.w + size_t(r0 + cp_row) * ROW_BYTES + warp * PITCH + cp_chunk * 16;
     const uint32_t cp_dst = smem_u32(my_w) + cp_row * PITCH + ((cp_chunk ^ ((cp_row & 1u) << 2)) << 4);
     const uint32_t sc_row = lane / (GPW / 2), sc_unit = lane % (GPW / 2);  // 4-byte units of scales
-    const uint16_t* sc_src = p.scales + size_t(r0 + sc_row) * (K / 128) + warp * GPW + sc_unit * 2;
+    const uint16_t* sc_src = p.scales + size_t(r0 + sc_row) * SCALE_STRIDE + warp * GPW + sc_unit * 2;
     const uint32_t sc_dst = smem_u32(my_s) + sc_row * (GPW * 2) + sc_unit * 4;
     uint32_t issue_stage = 0, issue_rows = nrows;  // stage offset index and rows left for the next tile to issue
     auto issue_tile = [&]() {
@@ -202,7 +211,7 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
                 if (sc_row < issue_rows) cp_async_4(sc_dst + issue_stage * SSTAGE, sc_src);
             }
             cp_src += TILE_ROWS * ROW_BYTES;
-            sc_src += TILE_ROWS * (K / 128);
+            sc_src += TILE_ROWS * SCALE_STRIDE;
             issue_rows = issue_rows > TILE_ROWS ? issue_rows - TILE_ROWS : 0u;
             issue_stage = issue_stage == STAGES - 1 ? 0u : issue_stage + 1;
         }
@@ -253,7 +262,7 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
             if (uint32_t(j) >= p.m) break;
             uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
             if (has) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * K + warp * (GPW * 128) + lane * 16);
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * X_STRIDE + warp * (GPW * 128) + lane * 16);
                 x0 = __ldcg(src);
                 x1 = __ldcg(src + 1);
             }
@@ -450,6 +459,9 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
             float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < W; ++w) sum += src[w * (PRIV / 4)];
+            if constexpr (STRIDED) {
+                if (p.acc_in && row < r1 && col < p.m) sum += p.acc_in[size_t(col) * p.n + row];
+            }
             if (row < r1 && col < p.m) {
                 if constexpr (GATHER) {
                     const size_t at = (size_t(p.half) * p.ag.world + p.ag.rank) * p.m * p.n + size_t(col) * p.n + row;
@@ -705,6 +717,83 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     cfg.attrs = &attr;
     cfg.numAttrs = constant_weights ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernels[variant][gather ? 2 : out_f32 ? 1 : 0], p);
+}
+
+// Rows longer than 4096: the k range is cut into blocks of 4096 (and one of 2048), each block is one launch of the k-block
+// form of the kernel above over the strided sub-matrix, and every launch adds the f32 sums of the blocks before it in its
+// reduction (the last one rounds to the output type). The launches form one programmatic chain like any other sequence of
+// GEMVs. bf16 outputs accumulate in a stream-ordered scratch allocation, f32 outputs in the output itself.
+bool int4_gemv_kblocks_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group) {
+    return m >= 1 && m <= 4 && n >= 1 && group == 128 && k > 4096 && k % 2048 == 0;
+}
+
+cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
+                                     bool constant_weights) {
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (dev & 63);
+    using Kernel = void (*)(const Params);
+    // [batch <= 2 | <= 4][k block 4096 | 2048][bf16 | f32 out]
+    static const Kernel kernels[2][2][2] = {
+        {{int4_gemv_halfsm_kernel<1, 4, 8, false, false, true>, int4_gemv_halfsm_kernel<1, 4, 8, true, false, true>},
+         {int4_gemv_halfsm_kernel<1, 2, 8, false, false, true>, int4_gemv_halfsm_kernel<1, 2, 8, true, false, true>}},
+        {{int4_gemv_halfsm_kernel<2, 4, 8, false, false, true>, int4_gemv_halfsm_kernel<2, 4, 8, true, false, true>},
+         {int4_gemv_halfsm_kernel<2, 2, 8, false, false, true>, int4_gemv_halfsm_kernel<2, 2, 8, true, false, true>}}};
+    if (!(configured.load(std::memory_order_acquire) & bit)) {
+        for (int i = 0; i < 8; ++i) {
+            const void* f = (const void*)kernels[i >> 2][(i >> 1) & 1][i & 1];
+            e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
+            if (e == cudaSuccess)
+                e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            if (e != cudaSuccess) return e;
+        }
+        configured.fetch_or(bit, std::memory_order_release);
+    }
+    float* sums = static_cast<float*>(y);  // f32 outputs accumulate in place
+    if (!out_f32) {
+        e = cudaMallocAsync(reinterpret_cast<void**>(&sums), size_t(m) * n * sizeof(float), stream);
+        if (e != cudaSuccess) return e;
+    }
+    const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
+    const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
+    for (uint32_t kb = 0; kb < k && e == cudaSuccess;) {
+        const uint32_t blk = k - kb >= 4096 ? 4096u : 2048u;
+        const bool last = kb + blk == k;
+        Params p{};
+        p.x = static_cast<const uint16_t*>(x_bf16) + kb;
+        p.w = static_cast<const uint8_t*>(w_packed) + kb / 2;
+        p.scales = static_cast<const uint16_t*>(scale_bf16) + kb / 128;
+        p.y = last ? y : static_cast<void*>(sums);
+        p.m = m;
+        p.n = n;
+        p.pace_ns = constant_weights ? PACE_NS : 0u;
+        p.tiles_per_cta = tiles / grid;
+        p.tiles_rem = tiles % grid;
+        p.row_bytes = k / 2;
+        p.scale_stride = k / 128;
+        p.x_stride = k;
+        p.acc_in = kb == 0 ? nullptr : sums;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(256);
+        cfg.dynamicSmemBytes = SMEM_TOTAL;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr = {};
+        attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr.val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = constant_weights ? 1 : 0;
+        e = cudaLaunchKernelEx(&cfg, kernels[m <= 2 ? 0 : 1][blk == 4096 ? 0 : 1][(last ? out_f32 != 0 : true) ? 1 : 0], p);
+        kb += blk;
+    }
+    if (!out_f32) {
+        const cudaError_t fe = cudaFreeAsync(sums, stream);
+        if (e == cudaSuccess) e = fe;
+    }
+    return e;
 }
 
 }  // namespace vybk

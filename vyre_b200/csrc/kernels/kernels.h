@@ -17,6 +17,11 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
                              uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                              uint32_t* status, bool constant_weights = false);
 // half-SM form (int4_gemv_halfsm.cu): m <= 4, k 2048 or 4096; launch_int4_gemv routes to it
+// rows longer than 4096 (k a multiple of 2048), m <= 4: one launch of the k-block form per 4096 / 2048 columns, sums carried in f32
+bool int4_gemv_kblocks_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
+cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
+                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
+                                     bool constant_weights);
 // f16 tensor path of the same launch shape (int4_gemv_batch8.cu): up to eight batch rows in one launch, k 2048 or 4096
 bool int4_gemv_batch8_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv_batch8(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
