@@ -822,6 +822,26 @@ def run_native(args) -> None:
             gbs = algorithmic_bytes(mm) / (us * 1e-6) / 1e9
             extra[f"m{mm}"] = {"us_per_launch": round(us, 3), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4)}
             del g2
+        # the down projection of the same feed-forward block: N=4096, K=14336 (the same bytes of weights and scales read as
+        # [4096, 14336 / 2] and [4096, 112]); rows longer than 4096 are cut into k blocks inside one launch
+        dn, dk = K_IN, N_OUT
+        xd = torch.from_numpy(synth.int4_linear_inputs(1, 16, dk, seed=4)[0].view(np.int16)).cuda()
+        yd = torch.zeros((1, dn), dtype=torch.bfloat16, device="cuda")
+
+        def launch_down(c):
+            ffi.check(L.vyb_k_int4_gemv_ex(xd.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), yd.data_ptr(), 1, dn, dk, GROUP,
+                                           ffi.DT_BF16, gemv_flags, C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+
+        with torch.cuda.stream(stream):
+            for c in range(COPIES):
+                launch_down(c)
+        stream.synchronize()
+        g3 = capture(lambda: [launch_down(c % COPIES) for c in range(LAUNCHES)])
+        us = event_time_us(g3.replay, reps=min(40, kernel_reps), warm=3, stream=stream) / LAUNCHES
+        gbs = algorithmic_bytes(1, n=dn, k=dk) / (us * 1e-6) / 1e9
+        extra["m1_n4096_k14336"] = {"us_per_call": round(us, 3), "launches_per_call": 1, "k_blocks": 7, "gbs": round(gbs, 1),
+                                    "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4)}
+        del g3
     clocks_headline = sampler.summary(lo, hi) if rank == 0 else None
     clocks_kernel = sampler.summary(k_lo, k_hi) if rank == 0 else None
 

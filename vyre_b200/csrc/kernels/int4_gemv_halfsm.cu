@@ -48,6 +48,9 @@
 #include <cuda_bf16.h>
 
 #include <atomic>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "kernels.h"
 #include "peer_gather.cuh"
@@ -105,7 +108,48 @@ struct Params {
     uint32_t scale_stride;  // scales between two rows
     uint32_t x_stride;      // elements between two batch rows of x
     const float* acc_in;    // [m][n] f32 sums of the k blocks before this one (nullptr: none), added in the reduction
+    // one launch over all k blocks (kblocks > 1): CTA i works on k block i % kblocks, leaves f32 partial rows in `part` and
+    // counts an arrival per 16-row tile; the CTA whose arrival completes a tile sums its kblocks partials in block order
+    uint32_t kblocks;
+    float* part;            // [kblocks][m][n]
+    uint32_t* tile_count;   // [tiles], zero between launches (the last arriver resets its word)
 };
+
+// k split inside one launch: count this CTA's arrival for the tiles [tile0, tile0 + count); where it is the last of the
+// k blocks to arrive, sum the partial rows in block order (deterministic) and store the outputs. Out of line.
+template <bool OUT_F32>
+__device__ __noinline__ void ksplit_finish(const Params& p, uint32_t tile0, uint32_t count, uint32_t* flags) {
+    __threadfence();
+    __syncthreads();  // every thread's partial stores are fenced; the shared-memory partials have been consumed
+    if (threadIdx.x < count) {
+        uint32_t* word = p.tile_count + tile0 + threadIdx.x;
+        const bool last = atomicAdd(word, 1u) == p.kblocks - 1;
+        if (last) atomicExch(word, 0u);
+        flags[threadIdx.x] = last ? 1u : 0u;
+    }
+    __syncthreads();
+    __threadfence();  // the other blocks' partial rows, published before their arrivals, are visible from here on
+    const uint32_t per_tile = 16 * p.m;
+    for (uint32_t idx = threadIdx.x; idx < count * per_tile; idx += blockDim.x) {
+        const uint32_t t = idx / per_tile, rem = idx % per_tile;
+        if (!flags[t]) continue;
+        const uint32_t col = rem / 16, row = (tile0 + t) * 16 + rem % 16;
+        if (row >= p.n) continue;
+        // all loads first (independent, one L2 round trip), then the sum in block order
+        const float* src = p.part + size_t(col) * p.n + row;
+        const size_t stride = size_t(p.m) * p.n;
+        float v[16];
+#pragma unroll
+        for (uint32_t b = 0; b < 16; ++b) v[b] = b < p.kblocks ? __ldcg(src + b * stride) : 0.f;
+        float sum = 0.f;
+#pragma unroll
+        for (uint32_t b = 0; b < 16; ++b) sum += v[b];
+        for (uint32_t b = 16; b < p.kblocks; ++b) sum += __ldcg(src + b * stride);
+        if (OUT_F32) static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
+        else static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
+    }
+    __syncthreads();
+}
 
 // Pipelined gathering form, kept out of line (the kernel below runs at the edge of its register budget): carry the
 // predecessor's slice, which sits in the other buffer half of local memory, to the peers. The stores drain under this
@@ -178,9 +222,20 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
     // whole tiles per CTA, the first tiles_rem CTAs one more than the rest
-    const uint32_t first_tile = blockIdx.x * p.tiles_per_cta + min(blockIdx.x, p.tiles_rem);
+    uint32_t first_tile = blockIdx.x * p.tiles_per_cta + min(blockIdx.x, p.tiles_rem);
+    uint32_t my_tiles = p.tiles_per_cta + (blockIdx.x < p.tiles_rem ? 1u : 0u);
+    uint32_t kblock = 0;  // STRIDED with kblocks > 1: the k block of this CTA; its tiles are split among the CTAs of that block
+    if constexpr (STRIDED) {
+        if (p.kblocks > 1) {
+            kblock = blockIdx.x % p.kblocks;
+            const uint32_t gi = blockIdx.x / p.kblocks, gn = (gridDim.x - kblock + p.kblocks - 1) / p.kblocks;
+            const uint32_t total = (p.n + TILE_ROWS - 1) / TILE_ROWS, per = total / gn, extra = total % gn;
+            first_tile = gi * per + min(gi, extra);
+            my_tiles = per + (gi < extra ? 1u : 0u);
+        }
+    }
     const uint32_t r0 = first_tile * TILE_ROWS;
-    const uint32_t r1 = min(p.n, r0 + (p.tiles_per_cta + (blockIdx.x < p.tiles_rem ? 1u : 0u)) * TILE_ROWS);
+    const uint32_t r1 = min(p.n, r0 + my_tiles * TILE_ROWS);
     const uint32_t nrows = r1 - r0;
     const uint32_t ntiles = (nrows + TILE_ROWS - 1) / TILE_ROWS;
     uint8_t* my_w = smem + warp * (STAGES * WSTAGE);             // this warp's private weight stages
@@ -191,10 +246,10 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     // every 128 bytes swapped: a 128-bit fragment load is served a quarter warp at a time (rows 2q and 2q+1, four
     // consecutive chunks each), and the swap puts those eight chunks into eight different 16-byte bank groups.
     const uint32_t cp_row = lane / CPR, cp_chunk = lane % CPR;
-    const uint8_t* cp_src = p.w + size_t(r0 + cp_row) * ROW_BYTES + warp * PITCH + cp_chunk * 16;
+    const uint8_t* cp_src = p.w + size_t(r0 + cp_row) * ROW_BYTES + kblock * (K / 2) + warp * PITCH + cp_chunk * 16;
     const uint32_t cp_dst = smem_u32(my_w) + cp_row * PITCH + ((cp_chunk ^ ((cp_row & 1u) << 2)) << 4);
     const uint32_t sc_row = lane / (GPW / 2), sc_unit = lane % (GPW / 2);  // 4-byte units of scales
-    const uint16_t* sc_src = p.scales + size_t(r0 + sc_row) * SCALE_STRIDE + warp * GPW + sc_unit * 2;
+    const uint16_t* sc_src = p.scales + size_t(r0 + sc_row) * SCALE_STRIDE + kblock * (K / 128) + warp * GPW + sc_unit * 2;
     const uint32_t sc_dst = smem_u32(my_s) + sc_row * (GPW * 2) + sc_unit * 4;
     uint32_t issue_stage = 0, issue_rows = nrows;  // stage offset index and rows left for the next tile to issue
     auto issue_tile = [&]() {
@@ -262,7 +317,7 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
             if (uint32_t(j) >= p.m) break;
             uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
             if (has) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * X_STRIDE + warp * (GPW * 128) + lane * 16);
+                const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * X_STRIDE + kblock * K + warp * (GPW * 128) + lane * 16);
                 x0 = __ldcg(src);
                 x1 = __ldcg(src + 1);
             }
@@ -461,6 +516,10 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
             for (int w = 0; w < W; ++w) sum += src[w * (PRIV / 4)];
             if constexpr (STRIDED) {
                 if (p.acc_in && row < r1 && col < p.m) sum += p.acc_in[size_t(col) * p.n + row];
+                if (p.kblocks > 1) {  // one launch over all k blocks: this block's partial row
+                    if (row < r1 && col < p.m) p.part[(size_t(kblock) * p.m + col) * p.n + row] = sum;
+                    continue;
+                }
             }
             if (row < r1 && col < p.m) {
                 if constexpr (GATHER) {
@@ -475,6 +534,9 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
                     static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
                 }
             }
+        }
+        if constexpr (STRIDED) {
+            if (p.kblocks > 1) ksplit_finish<OUT_F32>(p, first_tile + first, count, reinterpret_cast<uint32_t*>(red));
         }
     };
 
@@ -752,12 +814,84 @@ cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, c
         }
         configured.fetch_or(bit, std::memory_order_release);
     }
+    const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
+    // ---- one launch over all k blocks: needs a persistent workspace (partial rows and per-tile arrival words), one per
+    // (device, stream); allocated on first use outside stream capture. A CTA takes the tiles of ONE k block, so it converts
+    // one block of activations; the per-launch cost is paid once instead of once per block.
+    {
+        const uint32_t blk = k % 4096 == 0 ? 4096u : 2048u, kblocks = k / blk;
+        const size_t count_words = (size_t(tiles) + 63) & ~size_t(63);  // arrival words first, then the partial rows
+        const size_t need = (count_words + size_t(kblocks) * m * n) * 4;
+        struct Work {
+            void* ptr;
+            size_t bytes;
+        };
+        static std::mutex ws_mu;
+        static std::map<std::pair<int, cudaStream_t>, Work> ws;
+        void* work = nullptr;
+        {
+            std::lock_guard<std::mutex> lock(ws_mu);
+            auto it = ws.find({dev, stream});
+            if (it != ws.end() && it->second.bytes >= need) work = it->second.ptr;
+            if (!work) {
+                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+                if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+                if (cap == cudaStreamCaptureStatusNone) {
+                    // a larger workspace replaces a smaller one; the old one may still be in use by launches in flight on this
+                    // stream and is kept (a handful of shapes per process)
+                    const size_t bytes = need < (size_t(8) << 20) ? (size_t(8) << 20) : need;
+                    void* fresh = nullptr;
+                    if (cudaMalloc(&fresh, bytes) == cudaSuccess && cudaMemsetAsync(fresh, 0, bytes, stream) == cudaSuccess) {
+                        ws[{dev, stream}] = Work{fresh, bytes};
+                        work = fresh;
+                    } else {
+                        cudaGetLastError();
+                        if (fresh) cudaFree(fresh);
+                    }
+                }
+            }
+        }
+        if (work) {
+            uint32_t* counts = static_cast<uint32_t*>(work);  // zero between launches: the last arriver of a tile resets its word
+            float* part = reinterpret_cast<float*>(counts + count_words);
+            {
+                Params p{};
+                p.x = static_cast<const uint16_t*>(x_bf16);
+                p.w = static_cast<const uint8_t*>(w_packed);
+                p.scales = static_cast<const uint16_t*>(scale_bf16);
+                p.y = y;
+                p.m = m;
+                p.n = n;
+                p.pace_ns = constant_weights ? PACE_NS : 0u;
+                p.row_bytes = k / 2;
+                p.scale_stride = k / 128;
+                p.x_stride = k;
+                p.kblocks = kblocks;
+                p.part = part;
+                p.tile_count = counts;
+                const uint64_t units = uint64_t(tiles) * kblocks;
+                uint32_t grid = units < uint64_t(sm_count) ? uint32_t(units) : uint32_t(sm_count);
+                if (grid < kblocks) grid = kblocks;
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(grid);
+                cfg.blockDim = dim3(256);
+                cfg.dynamicSmemBytes = SMEM_TOTAL;
+                cfg.stream = stream;
+                cudaLaunchAttribute attr = {};
+                attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+                attr.val.programmaticStreamSerializationAllowed = 1;
+                cfg.attrs = &attr;
+                cfg.numAttrs = constant_weights ? 1 : 0;
+                return cudaLaunchKernelEx(&cfg, kernels[m <= 2 ? 0 : 1][blk == 4096 ? 0 : 1][out_f32 ? 1 : 0], p);
+            }
+        }
+    }
+    // ---- no workspace (first use under stream capture): one launch per k block
     float* sums = static_cast<float*>(y);  // f32 outputs accumulate in place
     if (!out_f32) {
         e = cudaMallocAsync(reinterpret_cast<void**>(&sums), size_t(m) * n * sizeof(float), stream);
         if (e != cudaSuccess) return e;
     }
-    const uint32_t tiles = (n + TILE_ROWS - 1) / TILE_ROWS;
     const uint32_t grid = tiles < uint32_t(sm_count) ? tiles : uint32_t(sm_count);
     for (uint32_t kb = 0; kb < k && e == cudaSuccess;) {
         const uint32_t blk = k - kb >= 4096 ? 4096u : 2048u;
