@@ -499,6 +499,8 @@ int32_t vyb_device_mark_lost(vyb_device* d, const char* reason);
  * vyre-runtime/src/artifact_admission.rs:271-291, then re-admits the same payload bytes). */
 int32_t vyb_device_reacquire(vyb_device* d);
 void vyb_device_release(vyb_device* d);
+/* a second owner of the same handle (the device stays acquired until every owner has released it) */
+void vyb_device_retain(vyb_device* d);
 
 /* resident buffers: vyre-driver-cuda/src/backend/resident.rs:138-201,426-443 */
 int32_t vyb_alloc(vyb_device* d, size_t byte_len, vyb_resident_handle* out);

@@ -88,3 +88,14 @@ def test_errors_leave_the_scratch_usable(scratch):
     w = oracle.pack_i4x8(np.array([1, -2, 3, -4, 5, -6, 7, -8, 1]))
     out = vb.i4x8_matvec_f32_scaled_via(scratch, w, np.ones(9, np.float32), np.array([2.0], np.float32), 1, 9)
     assert out.tolist() == [-6.0]
+
+
+def test_scratch_keeps_its_device_alive():
+    # the caller may release its device handle first; the scratch is a second owner until it is closed
+    d = vb.Device.acquire(0)
+    s = vb.QuantizedScratch(d)
+    d.release()
+    w = oracle.pack_i4x8(np.array([1, -2, 3, -4, 5, -6, 7, -8, 1]))
+    out = vb.i4x8_matvec_f32_scaled_via(s, w, np.ones(9, np.float32), np.array([2.0], np.float32), 1, 9)
+    assert out.tolist() == [-6.0]
+    s.close()

@@ -489,6 +489,9 @@ int32_t vyb_device_reacquire(vyb_device* d) {
 }
 
 void vyb_device_release(vyb_device* d) { device_unref(d); }
+void vyb_device_retain(vyb_device* d) {
+    if (d) d->refs.fetch_add(1);
+}
 
 // ---- resident buffers (vyre-driver-cuda/src/backend/resident.rs) -------------------------------------------------
 int32_t vyb_alloc(vyb_device* d, size_t byte_len, vyb_resident_handle* out) {

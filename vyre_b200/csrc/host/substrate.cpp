@@ -188,12 +188,14 @@ int32_t vyb_quantized_scratch_new(vyb_device* device, vyb_quantized_scratch** sc
     if (!scratch) return fail_invalid_program("Fix: pass an output pointer.");
     *scratch = new vyb_quantized_scratch();
     (*scratch)->device = device;
+    if (device) vyb_device_retain(device);  // the scratch materialises on this device until it is freed
     return VYB_OK;
 }
 
 void vyb_quantized_scratch_free(vyb_quantized_scratch* s) {
     if (!s) return;
     for (auto& kv : s->cache) drop(kv.second);
+    if (s->device) vyb_device_release(s->device);
     delete s;
 }
 

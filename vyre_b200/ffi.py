@@ -302,6 +302,7 @@ _OTHER_FUNCS = {
     "vyb_safetensors_identity": (None, [_P, C.c_char_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vyb_quantized_scratch_free": (None, [_P]),
     "vyb_frame_free": (None, [_P]),
+    "vyb_device_retain": (None, [_P]),
     "vyb_quantized_scratch_stats": (None, [_P, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "vyb_safetensors_count": (C.c_uint32, [_P]),
     "vyb_payload_format": (C.c_char_p, [_P]),
