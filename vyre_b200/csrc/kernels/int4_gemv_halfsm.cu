@@ -119,16 +119,18 @@ struct Params {
 // k blocks to arrive, sum the partial rows in block order (deterministic) and store the outputs. Out of line.
 template <bool OUT_F32>
 __device__ __noinline__ void ksplit_finish(const Params& p, uint32_t tile0, uint32_t count, uint32_t* flags) {
-    __threadfence();
-    __syncthreads();  // every thread's partial stores are fenced; the shared-memory partials have been consumed
+    __syncthreads();  // the CTA's partial stores are ordered before the fences below; the shared-memory partials are consumed
     if (threadIdx.x < count) {
+        __threadfence();  // cumulative: publishes the whole CTA's partial rows before the arrival
         uint32_t* word = p.tile_count + tile0 + threadIdx.x;
         const bool last = atomicAdd(word, 1u) == p.kblocks - 1;
-        if (last) atomicExch(word, 0u);
+        if (last) {
+            *word = 0u;       // nobody else touches the word until the next launch
+            __threadfence();  // the other blocks' partial rows, published before their arrivals, are visible from here on
+        }
         flags[threadIdx.x] = last ? 1u : 0u;
     }
     __syncthreads();
-    __threadfence();  // the other blocks' partial rows, published before their arrivals, are visible from here on
     const uint32_t per_tile = 16 * p.m;
     for (uint32_t idx = threadIdx.x; idx < count * per_tile; idx += blockDim.x) {
         const uint32_t t = idx / per_tile, rem = idx % per_tile;
@@ -206,14 +208,17 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     constexpr uint32_t SSTAGE = TILE_ROWS * GPW * 2; // and of its scales
     constexpr uint32_t MM = 2 * NM;                  // batch rows of a partial
     constexpr uint32_t PART = TILE_ROWS * MM * 4;    // bytes of one warp's partial of one tile
-    constexpr uint32_t PRIV = SMEM_RED / W;          // bytes of partials (and prologue scratch) a warp owns
+    // 2048-k rows leave the upper half of the weight stages unused: the partial sums go there, and four times as many tiles
+    // fit between two reductions
+    constexpr uint32_t RED_BYTES = GPW == 4 ? SMEM_RED : SMEM_W / 2;
+    constexpr uint32_t PRIV = RED_BYTES / W;         // bytes of partials (and prologue scratch) a warp owns
     constexpr uint32_t FLUSH = PRIV / PART;          // tiles between two reductions
     static_assert(PRIV >= 2 * GPW * 128, "the activation scratch must fit a warp's own area");
     static_assert(GPW == 2 || GPW == 4, "a warp owns 256 or 512 k");
     static_assert(RPI % 2 == 0, "the row parity of a lane must not depend on the copy index");
     static_assert(W * STAGES * (WSTAGE + SSTAGE) <= SMEM_W + SMEM_S, "stages must fit");
 
-    uint8_t* red = smem + SMEM_W + SMEM_S;
+    uint8_t* red = smem + (GPW == 4 ? SMEM_W + SMEM_S : SMEM_W / 2);
     // whole rows: compile-time strides; a k block of a wider matrix (STRIDED): the strides of that matrix
     const uint32_t ROW_BYTES = STRIDED ? p.row_bytes : ROW_BYTES_DENSE;
     const uint32_t SCALE_STRIDE = STRIDED ? p.scale_stride : K / 128;
