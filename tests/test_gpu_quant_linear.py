@@ -195,6 +195,50 @@ def test_kernel_level_entry_point_matches_contract_path(dev):
     assert rc == ffi.ERR_UNSUPPORTED_FEATURE and b"Fix:" in ffi.lib().vyb_last_error_message()
 
 
+def test_long_rows_first_use_under_stream_capture_and_workspace_reuse(dev):
+    # the one-launch k split needs a per-stream workspace that cannot be allocated while a stream is capturing: a first use
+    # under capture runs one launch per k block instead; later, un-captured calls on the stream get the workspace, and
+    # different shapes share it (its arrival words are zero between launches)
+    lib = ffi.lib()
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    cases = []
+    for (m, n, k) in [(2, 520, 8192), (1, 300, 14336), (4, 96, 6144)]:
+        x, w, s = synth.int4_linear_inputs(m, n, k, seed=n)
+        want = oracle.int4_rowmajor_linear(x, w, s, m, n, k)
+        t = tuple(torch.from_numpy(a).cuda() for a in (x.view(np.int16), w, s.view(np.int16)))
+        cases.append((m, n, k, t, torch.zeros((m, n), dtype=torch.bfloat16, device="cuda"), want))
+
+    def launch(case, stream):
+        m, n, k, (tx, tw, ts), ty, _ = case
+        ffi.check(lib.vyb_k_int4_gemv_ex(tx.data_ptr(), tw.data_ptr(), ts.data_ptr(), ty.data_ptr(), m, n, k, 128, ffi.DT_BF16,
+                                         ffi.LAUNCH_CONSTANT_WEIGHTS, C.c_void_p(stream.cuda_stream), C.c_void_p(status.data_ptr())))
+
+    def check(case):
+        got = synth.bf16_bits_to_f32(case[4].view(torch.int16).cpu().numpy().view(np.uint16))
+        assert rel_err(got, synth.bf16_bits_to_f32(case[5])) <= TOL_BF16_OUT
+        case[4].zero_()
+
+    fresh = torch.cuda.Stream()  # no call has run on this stream: no workspace yet
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(fresh):
+        with torch.cuda.graph(graph, stream=fresh):
+            for case in cases:
+                launch(case, fresh)
+        for _ in range(2):
+            graph.replay()
+    fresh.synchronize()
+    for case in cases:
+        check(case)
+    with torch.cuda.stream(fresh):  # un-captured: the workspace is made now and shared by the three shapes, twice over
+        for _ in range(2):
+            for case in cases:
+                launch(case, fresh)
+    fresh.synchronize()
+    for case in cases:
+        check(case)
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+
+
 def test_int8_weight_only_config1(dev):
     m, n, k = 16, 1024, 1024
     x, w, s = synth.int8_weight_only_inputs(m, n, k, seed=0)
