@@ -99,3 +99,24 @@ def test_quantized_gated_mlp_graph_with_constants_from_a_safetensors_shard(dev, 
         assert sess.run({"mlp.normalized": x})["mlp.down"] == d1
     finally:
         sess.close()
+    # the whole residual block over the same weights: RMSNorm in front, residual add behind, byte for byte against the
+    # five operators submitted one by one
+    whole = api.GraphSession(api.quantized_gated_mlp_graph(api.QuantizedGatedMlpSpec(rows, h, inter, norm_eps=1e-5)), dev)
+    try:
+        idx = api.SafetensorIndex.open(str(path))
+        for name in tensors:
+            whole.set_constant(name, handle=idx.load_resident(dev, name))
+        wn = oracle.f32_to_bf16_bits((1.0 + 0.1 * np.random.default_rng(8).standard_normal(h)).astype(np.float32))
+        whole.set_constant("post_attention_layernorm.weight", wn)
+        got = whole.run({"residual": x})["mlp.block_output"]
+        n1 = np.frombuffer(op(vb.learned_rms_norm("i", "w", "o", rows, h, 1e-5, ffi.DT_BF16), [x, wn]), np.uint16)
+        assert np.array_equal(n1, oracle.rms_norm(x, wn, rows, h, 1e-5, dtype=oracle.DT_BF16))
+        g1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, h, inter, 128, ffi.DT_BF16), [n1, wg.view(np.uint32), sg]), np.uint16)
+        u1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, h, inter, 128, ffi.DT_BF16), [n1, wu.view(np.uint32), su]), np.uint16)
+        a1 = np.frombuffer(op(vb.swiglu_typed("g", "u", "o", rows * inter, ffi.DT_BF16), [g1, u1]), np.uint16)
+        d1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, inter, h, 128, ffi.DT_BF16), [a1, wd.view(np.uint32), sd]), np.uint16)
+        assert got == op(vb.residual_add_typed("r", "b", "o", rows * h, ffi.DT_BF16), [x.reshape(-1), d1])
+        names = [n["name"] for n in whole.graph.nodes()] if hasattr(whole, "graph") else None
+        assert names is None or names == ["mlp.norm", "mlp.gate_proj", "mlp.up_proj", "mlp.swiglu", "mlp.down_proj", "mlp.residual"]
+    finally:
+        whole.close()

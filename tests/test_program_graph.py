@@ -108,3 +108,8 @@ def test_gated_mlp_templates():
     qv = {v["name"]: v for v in q.values()}
     assert qv["mlp.gate_proj.qweight"]["contract"] == {"dtype": ffi.DT_U32, "access": RO, "lifetime": CONST, "shape": [512, 32]}
     assert qv["mlp.down_proj.scales"]["contract"]["shape"] == [256, 4] and [n["name"] for n in q.nodes()] == names[1:5]
+    qw = api.quantized_gated_mlp_graph(api.QuantizedGatedMlpSpec(rows=4, hidden_dim=256, intermediate_dim=512, norm_eps=1e-6))
+    assert [n["name"] for n in qw.nodes()] == names
+    qwv = {v["name"]: v for v in qw.values()}
+    assert qwv["residual"]["consumers"] == 2 and qwv["mlp.block_output"]["contract"]["lifetime"] == OUT
+    assert qwv["mlp.down"]["contract"]["lifetime"] != OUT and qw.digest() != q.digest()

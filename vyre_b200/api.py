@@ -971,12 +971,15 @@ class QuantizedGatedMlpSpec:
     hidden_dim: int
     intermediate_dim: int
     group_size: int = 128
+    norm_eps: float | None = None  # a value makes the graph the whole residual block: RMSNorm in front, residual add behind
 
 
 def quantized_gated_mlp_graph(spec: QuantizedGatedMlpSpec) -> ProgramGraph:
-    """gate_proj and up_proj (int4 weights, `Constant`), SwiGLU, down_proj: the projection / activation / projection
-    part of vyre_libs::nn::model::dense_gated_mlp_graph (dense_gated_mlp.rs:59-370) over this backend's quantized
-    linears, with the same value names. The norm and the residual add of that template are not on this path."""
+    """gate_proj and up_proj (int4 weights, `Constant`), SwiGLU, down_proj: vyre_libs::nn::model::dense_gated_mlp_graph
+    (dense_gated_mlp.rs:59-370) over this backend's quantized linears, with the same value names. Without `norm_eps` the
+    graph is the projection / activation / projection part (input `mlp.normalized`, output `mlp.down`); with it the graph
+    is the reference's whole block: `residual` -> learned RMSNorm (bf16, `post_attention_layernorm.weight`) -> projections
+    -> residual add -> `mlp.block_output`."""
     r, h, i, g = spec.rows, spec.hidden_dim, spec.intermediate_dim, spec.group_size
     if min(r, h, i, g) <= 0:
         raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: rows, hidden_dim, intermediate_dim and group_size must be nonzero.")
@@ -989,7 +992,16 @@ def quantized_gated_mlp_graph(spec: QuantizedGatedMlpSpec) -> ProgramGraph:
     up_w, up_s = value_contract(ffi.DT_U32, [i, h // 8], const), value_contract(bf16, [i, h // g], const)
     down_w, down_s = value_contract(ffi.DT_U32, [h, i // 8], const), value_contract(bf16, [h, i // g], const)
     graph = ProgramGraph()
-    x = graph.add_external_value("mlp.normalized", read_hidden)
+    whole = spec.norm_eps is not None
+    write_hidden = value_contract(bf16, [r, h], inv, rw)
+    if whole:
+        residual = graph.add_external_value("residual", read_hidden)
+        norm_c = value_contract(bf16, [h], const)
+        norm_w = graph.add_external_value("post_attention_layernorm.weight", norm_c)
+        _, (x,) = graph.add_node("mlp.norm", learned_rms_norm("input", "weight", "output", r, h, spec.norm_eps, bf16),
+                                 [("input", residual, read_hidden), ("weight", norm_w, norm_c)], [("output", "mlp.normalized", write_hidden)])
+    else:
+        x = graph.add_external_value("mlp.normalized", read_hidden)
     gw = graph.add_external_value("mlp.gate_proj.qweight", up_w)
     gs = graph.add_external_value("mlp.gate_proj.scales", up_s)
     uw = graph.add_external_value("mlp.up_proj.qweight", up_w)
@@ -1007,7 +1019,12 @@ def quantized_gated_mlp_graph(spec: QuantizedGatedMlpSpec) -> ProgramGraph:
     up = proj("mlp.up_proj", "mlp.up", x, read_hidden, uw, up_w, us, up_s, h, i, write_inter)
     _, (act,) = graph.add_node("mlp.swiglu", swiglu_typed("gate", "up", "output", r * i, bf16),
                                [("gate", gate, read_inter), ("up", up, read_inter)], [("output", "mlp.activated", write_inter)])
-    proj("mlp.down_proj", "mlp.down", act, read_inter, dw, down_w, ds, down_s, i, h, value_contract(bf16, [r, h], outl, rw))
+    down = proj("mlp.down_proj", "mlp.down", act, read_inter, dw, down_w, ds, down_s, i, h,
+                write_hidden if whole else value_contract(bf16, [r, h], outl, rw))
+    if whole:
+        graph.add_node("mlp.residual", residual_add_typed("residual", "branch", "output", r * h, bf16),
+                       [("residual", residual, read_hidden), ("branch", down, read_hidden)],
+                       [("output", "mlp.block_output", value_contract(bf16, [r, h], outl, rw))])
     return graph
 
 
