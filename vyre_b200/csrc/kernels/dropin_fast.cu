@@ -160,6 +160,107 @@ __global__ void __launch_bounds__(TX* KS) affine_grouped_fast_kernel(const float
     }
 }
 
+// The same operator at decode batches (batch <= 4 per block): the whole activation rows stay in shared memory, thread
+// (tx, ty) owns output i = block base + tx and every KS-th word of each group, and scale and zero point are applied once
+// per group instead of once per weight:
+//     sum_k x_k (q_k - zp) s  =  s (sum_k x_k q_k  -  zp sum_k x_k),
+// with the activation sums of a thread's words of a group computed once per block. Per weight that leaves the nibble
+// extraction, one exact subtraction and one FMA per batch row (the kernel above spends thirteen instructions per weight at
+// batch 1). Same values as the operator's definition up to f32 summation order; exact whenever every partial sum is.
+// grid (ceil(N / 32), ceil(B / BT)), block 32 x KS; needs (group / 8) % KS == 0.
+template <int KS, int BT, int WPT>
+__global__ void __launch_bounds__(32 * KS) affine_grouped_decode_kernel(const float* __restrict__ x, const uint32_t* __restrict__ w,
+                                                                        const float* __restrict__ scale, const uint32_t* __restrict__ zp,
+                                                                        const float* __restrict__ bias, float* __restrict__ out,
+                                                                        uint32_t in_dim, uint32_t out_dim, uint32_t group, uint32_t batch) {
+    extern __shared__ __align__(16) float dsm[];
+    const uint32_t groups = in_dim / group, wpg = group / 8;  // words per group; WPT = wpg / KS of them are this thread's
+    constexpr uint32_t wpt = WPT;
+    float* xs = dsm;                                  // [BT][in_dim]
+    float* xsum = dsm + size_t(BT) * in_dim;          // [BT][groups][KS]: sum of x under the words (g, j * KS + ty)
+    float* red = xsum + size_t(BT) * groups * KS;     // [KS][BT][32]
+    const uint32_t tx = threadIdx.x, ty = threadIdx.y, tid = ty * 32 + tx;
+    const uint32_t i = blockIdx.x * 32 + tx, ic = min(i, out_dim - 1);
+    const uint32_t b0 = blockIdx.y * BT, nb = min(uint32_t(BT), batch - b0);
+    for (uint32_t e = tid; e < BT * (in_dim / 4); e += 32 * KS) {
+        const uint32_t b = e / (in_dim / 4), k = (e % (in_dim / 4)) * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < nb) v = __ldg(reinterpret_cast<const float4*>(x + size_t(b0 + b) * in_dim + k));
+        *reinterpret_cast<float4*>(xs + size_t(b) * in_dim + k) = v;
+    }
+    __syncthreads();
+    for (uint32_t e = tid; e < BT * groups * KS; e += 32 * KS) {
+        const uint32_t b = e / (groups * KS), g = (e / KS) % groups, y = e % KS;
+        float sum = 0.f;
+        for (uint32_t j = 0; j < wpt; ++j) {
+            const float* px = xs + size_t(b) * in_dim + (size_t(g) * wpg + j * KS + y) * 8;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) sum += px[n];
+        }
+        xsum[e] = sum;
+    }
+    __syncthreads();
+    float acc[BT];
+#pragma unroll
+    for (int b = 0; b < BT; ++b) acc[b] = 0.f;
+    constexpr int GB = 4;  // groups whose words, scales and zero points are loaded together: GB * WPT words in flight per thread
+    for (uint32_t g0 = 0; g0 < groups; g0 += GB) {
+        uint32_t words[GB][WPT];
+        float sc[GB], z[GB];
+#pragma unroll
+        for (int gg = 0; gg < GB; ++gg) {
+            const uint32_t g = min(g0 + gg, groups - 1);  // past the end: reloaded, not used
+#pragma unroll
+            for (int j = 0; j < WPT; ++j) words[gg][j] = __ldg(w + size_t(g * wpg + j * KS + ty) * out_dim + ic);
+            sc[gg] = __ldg(scale + size_t(g) * out_dim + ic);
+            z[gg] = float(__ldg(zp + size_t(g) * out_dim + ic));
+        }
+#pragma unroll
+        for (int gg = 0; gg < GB; ++gg) {
+            const uint32_t g = g0 + gg;
+            if (g >= groups) break;
+            float part[BT];
+#pragma unroll
+            for (int b = 0; b < BT; ++b) part[b] = 0.f;
+#pragma unroll
+            for (int j = 0; j < WPT; ++j) {
+                const uint32_t kw = g * wpg + j * KS + ty;
+                const uint32_t word = words[gg][j];
+                const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;  // nibbles 0,2,4,6 / 1,3,5,7
+                float q[8];
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    // f32(nibble) without the conversion unit: 0x4B0000nn is 2^23 + nn, and the subtraction is exact
+                    q[2 * n] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7540 + n)) - 8388608.0f;
+                    q[2 * n + 1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7540 + n)) - 8388608.0f;
+                }
+#pragma unroll
+                for (int b = 0; b < BT; ++b) {
+                    const float4 xa = *reinterpret_cast<const float4*>(xs + size_t(b) * in_dim + size_t(kw) * 8);
+                    const float4 xb = *reinterpret_cast<const float4*>(xs + size_t(b) * in_dim + size_t(kw) * 8 + 4);
+                    float a = part[b];
+                    a = fmaf(xa.x, q[0], a); a = fmaf(xa.y, q[1], a); a = fmaf(xa.z, q[2], a); a = fmaf(xa.w, q[3], a);
+                    a = fmaf(xb.x, q[4], a); a = fmaf(xb.y, q[5], a); a = fmaf(xb.z, q[6], a); a = fmaf(xb.w, q[7], a);
+                    part[b] = a;
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < BT; ++b)
+                acc[b] = fmaf(sc[gg], fmaf(-z[gg], xsum[(size_t(b) * groups + g) * KS + ty], part[b]), acc[b]);
+        }
+    }
+    // fold the k slices in slice order (deterministic)
+#pragma unroll
+    for (int b = 0; b < BT; ++b) red[(ty * BT + b) * 32 + tx] = acc[b];
+    __syncthreads();
+    for (uint32_t b = ty; b < nb; b += KS) {
+        if (i >= out_dim) continue;
+        float v = red[b * 32 + tx];
+        for (uint32_t y = 1; y < KS; ++y) v += red[(y * BT + b) * 32 + tx];
+        out[size_t(b0 + b) * out_dim + i] = bias[i] + v;
+    }
+}
+
 // one warp per row, 8 rows per block; grid (ceil(rows / 8), ceil(batch / MV_BT))
 __global__ void __launch_bounds__(256) i4_matvec_fast_kernel(const uint32_t* __restrict__ w, const float* __restrict__ x,
                                                              const float* __restrict__ scales, float* __restrict__ out,
@@ -237,6 +338,33 @@ cudaError_t launch_affine_cfg(const float* x, const uint32_t* w, const float* sc
 cudaError_t launch_affine_grouped_fast(const float* x, const uint32_t* w, const float* scale, const uint32_t* zp,
                                        const float* b, float* out, uint32_t in_dim, uint32_t out_dim, uint32_t group,
                                        uint32_t batch, int sm_count, cudaStream_t s) {
+    // decode batches: whole activation rows in shared memory, scale and zero point applied per group
+    constexpr int DKS = 8;
+    if (batch <= 4 && (group == 64 || group == 128) && in_dim <= 8192) {
+        const int dbt = batch == 1 ? 1 : batch == 2 ? 2 : 4;
+        const size_t smem = (size_t(dbt) * in_dim + size_t(dbt) * (in_dim / group) * DKS + size_t(DKS) * dbt * 32) * sizeof(float);
+        const dim3 grid((out_dim + 31) / 32, 1), block(32, DKS);
+        using Kernel = void (*)(const float*, const uint32_t*, const float*, const uint32_t*, const float*, float*, uint32_t, uint32_t,
+                                uint32_t, uint32_t);
+        static const Kernel kernels[2][3] = {
+            {affine_grouped_decode_kernel<DKS, 1, 1>, affine_grouped_decode_kernel<DKS, 2, 1>, affine_grouped_decode_kernel<DKS, 4, 1>},
+            {affine_grouped_decode_kernel<DKS, 1, 2>, affine_grouped_decode_kernel<DKS, 2, 2>, affine_grouped_decode_kernel<DKS, 4, 2>}};
+        static std::atomic<uint64_t> configured{0};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        const uint64_t bit = 1ull << (dev & 63);
+        if (!(configured.load(std::memory_order_acquire) & bit)) {
+            const int max_smem = int((size_t(4) * 8192 + size_t(4) * (8192 / 64) * DKS + size_t(DKS) * 4 * 32) * sizeof(float));
+            for (int v = 0; v < 6 && e == cudaSuccess; ++v)
+                e = cudaFuncSetAttribute((const void*)kernels[v / 3][v % 3], cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+            if (e != cudaSuccess) return e;
+            configured.fetch_or(bit, std::memory_order_release);
+        }
+        kernels[group == 128 ? 1 : 0][dbt == 1 ? 0 : dbt == 2 ? 1 : 2]<<<grid, block, smem, s>>>(x, w, scale, zp, b, out, in_dim, out_dim,
+                                                                                             group, batch);
+        return cudaGetLastError();
+    }
     // batch rows per block: every row beyond the batch is wasted arithmetic, every row within it reuses the dequantised weight
     const int bt = batch >= 12 ? 16 : batch >= 3 ? 8 : 2;
     // 128 outputs per block (two per thread) when that still gives every SM a block, else 32 outputs and a deeper k split
