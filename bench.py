@@ -378,7 +378,7 @@ def measure_dropin_1m(local_rank: int, samples: int = 30, shape=(256, 4096, 64, 
                 "kernel_variant": variant, "device_us_per_dispatch": {"p50": round(p50 / 1e3, 2), "min": round(ns[0] / 1e3, 2), "samples": len(ns)},
                 "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"] if peaks else None, "unit": "GB/s",
                              "frac": round(gbs / peaks["hbm_gbs"], 4) if peaks else None, "algorithmic_bytes_per_dispatch": abytes,
-                             "kernel": "affine_grouped_fast_kernel",
+                             "kernel": "affine_grouped_decode_kernel" if b <= 4 else "affine_grouped_fast_kernel",
                              "note": "one dispatch per sample between two events (event overhead included); the 33 MB of weights fit L2"},
                 "parity": {"max_abs_err_vs_f64_two_rows": err, "tolerance": 1e-4}}
     return {"case": "nn.linear_4bit_affine_grouped.1m", "op_id": "vyre-libs::nn::linear_4bit_affine_grouped",
