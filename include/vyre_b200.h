@@ -638,7 +638,14 @@ int32_t vyb_i4x8_batched_matmul_top1_f32_scaled_via(vyb_quantized_scratch* scrat
  * kind::i8 when int8 != 0, else bf16) from operands resident in shared memory. *ops_per_launch receives the
  * integer or floating-point operations one launch performs; the caller times launches with events. */
 int32_t vyb_k_tensor_peak(uint32_t int8, uint32_t iters, void* stream, uint32_t* status, double* ops_per_launch);
-/* y[m,n] = bf16|f32( sum_k x[m,k] * (q[n,k]-8) * s[n,k/group] ), m <= 8 per pass, HBM-bound decode path */
+/* y[m,n] = bf16|f32( sum_k x[m,k] * (q[n,k]-8) * s[n,k/group] ), m <= 8 per pass, HBM-bound decode path.
+ * group 128, k a multiple of 1024. Routing: k 2048 / 4096 with up to two rows (f32 outputs: one row per launch) runs
+ * the half-SM integer kernel, three to eight rows one launch on the f16 tensor path; k a larger multiple of 2048 is
+ * cut into k blocks inside one launch, which keeps a workspace per (device, stream) allocated on the first call that
+ * is not under stream capture (a first call under capture runs one launch per k block with a stream-ordered scratch
+ * allocation instead); other k run the bulk-copy kernel. Launches that share a stream are ordered; graphs captured
+ * on one stream must not be replayed concurrently on two streams when they hold long-row launches (they share that
+ * stream's workspace). */
 int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
                         uint32_t* status);
