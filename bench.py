@@ -810,7 +810,7 @@ def run_native(args) -> None:
     achieved = algorithmic_bytes(m) / (kernel_us * 1e-6) / 1e9
     extra = {}
     if rank == 0:
-        for mm in (4, 8):
+        for mm in (2, 4, 8):
             xm_np, _, _ = synth.int4_linear_inputs(mm, 16, K_IN, seed=3)
             xm = torch.from_numpy(xm_np.view(np.int16)).cuda()
             ym = torch.zeros((mm, N_OUT), dtype=torch.bfloat16, device="cuda")
