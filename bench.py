@@ -1005,7 +1005,8 @@ def run_quick(args) -> None:
     L = ffi.lib()
     m = args.m
     n_out = args.rows or N_OUT
-    x_np, w_np, s_np = synth.int4_linear_inputs(m, n_out, K_IN, seed=0)
+    k_in = args.k or K_IN
+    x_np, w_np, s_np = synth.int4_linear_inputs(m, n_out, k_in, seed=0)
     x = torch.from_numpy(x_np.view(np.int16)).cuda()
     copies = max(1, args.copies)
     ws = [torch.from_numpy(np.roll(w_np, c, axis=0)).cuda() for c in range(copies)]
@@ -1017,7 +1018,7 @@ def run_quick(args) -> None:
     def launch(stream=None):
         c = it[0] % copies
         it[0] += 1
-        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, n_out, K_IN,
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[c].data_ptr(), ss[c].data_ptr(), y.data_ptr(), m, n_out, k_in,
                                        GROUP, ffi.DT_BF16, ffi.LAUNCH_CONSTANT_WEIGHTS,
                                        C.c_void_p(stream or torch.cuda.current_stream().cuda_stream), C.c_void_p(status.data_ptr())))
 
@@ -1045,8 +1046,8 @@ def run_quick(args) -> None:
     else:
         us = event_time_us(launch, args.steps, args.warmup)
     assert status.cpu().tolist() == [0, 0, 0, 0]
-    gbs = algorithmic_bytes(m, n=n_out) / (us * 1e-6) / 1e9
-    print(json.dumps({"quick": True, "m": m, "rows": n_out, "graph": bool(args.graph), "steps": args.steps, "copies": copies,
+    gbs = algorithmic_bytes(m, n=n_out, k=k_in) / (us * 1e-6) / 1e9
+    print(json.dumps({"quick": True, "m": m, "rows": n_out, "k": k_in, "graph": bool(args.graph), "steps": args.steps, "copies": copies,
                       "us_per_launch": round(us, 3), "gbs": round(gbs, 1), "frac_of_measured_peak": round(gbs / peaks["hbm_gbs"], 4)}))
 
 
@@ -1065,6 +1066,7 @@ def main() -> None:
     ap.add_argument("--copies", type=int, default=COPIES,
                     help="weight copies rotated in --quick mode (1 keeps the weights L2-resident: compute-bound check)")
     ap.add_argument("--rows", type=int, default=0, help="weight rows N in --quick --case gemv (0: the configuration's 14336)")
+    ap.add_argument("--k", type=int, default=0, help="row length K in --quick --case gemv (0: the configuration's 4096)")
     ap.add_argument("--graph", action="store_true",
                     help="--quick --case gemv: time replays of a CUDA graph of 64 launches (the headline's launch pattern) instead of single launches")
     ap.add_argument("--quick", action="store_true",
