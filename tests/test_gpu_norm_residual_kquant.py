@@ -55,13 +55,29 @@ def test_residual_add_fixture_and_dtypes(dev):
 
 @pytest.mark.parametrize("rows,hidden", [(1, 1), (3, 37), (5, 1024), (2, 4096), (4, 1500)])
 @pytest.mark.parametrize("tag", [ffi.DT_F32, ffi.DT_BF16, ffi.DT_F16])
-def test_learned_rms_norm_is_bit_identical(dev, rows, hidden, tag):
+def test_learned_rms_norm_against_the_oracle(dev, rows, hidden, tag):
     rng = np.random.default_rng(rows * 7 + hidden)
     x, w = typed(rng.standard_normal(rows * hidden) * 3, tag), typed(1.0 + 0.1 * rng.standard_normal(hidden), tag)
     got = out_of(run(dev, vb.learned_rms_norm("input", "weight", "output", rows, hidden, 1e-6, tag), [x, w])[0], tag)
     want = oracle.rms_norm(x, w, rows, hidden, 1e-6, dtype=DT[tag])
-    assert np.array_equal(got.view(np.uint32 if tag == ffi.DT_F32 else np.uint16),
-                          want.view(np.uint32 if tag == ffi.DT_F32 else np.uint16))
+    sess_variant = vb.ArtifactSession.compile(vb.learned_rms_norm("input", "weight", "output", rows, hidden, 1e-6, tag), dev).kernel_variant()
+    if hidden < 2048:
+        assert sess_variant == 0
+        assert np.array_equal(got.view(np.uint32 if tag == ffi.DT_F32 else np.uint16),
+                              want.view(np.uint32 if tag == ffi.DT_F32 else np.uint16))
+    else:
+        # rows of 2048 elements and more: the sum of squares is a tree, not the reference's chain (kernel variant 8); the sum
+        # differs by f32 rounding, so f32 outputs agree to a few ulp and 16-bit outputs except for rare one-ulp flips
+        assert sess_variant == 8
+        if tag == ffi.DT_F32:
+            # the chain of 4096 additions carries about sqrt(4096) * 2^-24 = 4e-6 of rounding itself
+            assert np.abs(got - want).max() <= 3e-5 * np.abs(want).max()
+        else:
+            diff = np.abs(got.astype(np.int32) - want.astype(np.int32))
+            # a relative difference of a few 1e-6 in 1/rms moves a value across a rounding boundary of an 11-bit (f16) or
+            # 8-bit (bf16) significand about once in a thousand
+            # (a flipped normalised value times a weight above one can land two ulp away)
+            assert diff.max() <= 2 and np.mean(diff != 0) < 0.01
 
 
 def test_gated_rms_norm_within_the_exp_window(dev):

@@ -110,7 +110,9 @@ def test_quantized_gated_mlp_graph_with_constants_from_a_safetensors_shard(dev, 
         whole.set_constant("post_attention_layernorm.weight", wn)
         got = whole.run({"residual": x})["mlp.block_output"]
         n1 = np.frombuffer(op(vb.learned_rms_norm("i", "w", "o", rows, h, 1e-5, ffi.DT_BF16), [x, wn]), np.uint16)
-        assert np.array_equal(n1, oracle.rms_norm(x, wn, rows, h, 1e-5, dtype=oracle.DT_BF16))
+        # rows of 2048 elements take the tree form of the sum of squares: equal to the oracle's chain except for rare flips
+        nd = np.abs(n1.astype(np.int32) - oracle.rms_norm(x, wn, rows, h, 1e-5, dtype=oracle.DT_BF16).astype(np.int32))
+        assert nd.max() <= 2 and np.mean(nd != 0) < 0.01
         g1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, h, inter, 128, ffi.DT_BF16), [n1, wg.view(np.uint32), sg]), np.uint16)
         u1 = np.frombuffer(op(vb.linear_int4_grouped_rowmajor("x", "w", "s", "o", rows, h, inter, 128, ffi.DT_BF16), [n1, wu.view(np.uint32), su]), np.uint16)
         a1 = np.frombuffer(op(vb.swiglu_typed("g", "u", "o", rows * inter, ffi.DT_BF16), [g1, u1]), np.uint16)

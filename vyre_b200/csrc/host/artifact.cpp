@@ -102,6 +102,8 @@ uint32_t select_kernel_variant(const Program& p) {
             const uint64_t batch = p.params.u[0], rows = p.params.u[1], cols = p.params.u[2];
             return batch * rows * cols >= (1ull << 22) ? KV_I4_MATVEC_WARP_ROWS : KV_GENERIC;
         }
+        // long rows: the chain of `hidden` dependent additions becomes a tree (f32 rounding of the sum differs, about 1e-7)
+        case OpKind::RmsNorm: return p.params.u[1] >= 2048 ? KV_RMS_NORM_TREE : KV_GENERIC;
         case OpKind::KQuantLinear: {
             const uint64_t in_dim = p.params.u[0], out_dim = p.params.u[1], bits = p.params.u[2];
             return in_dim * out_dim >= (1ull << 20) && out_dim % (4 * (32 / bits)) == 0 ? KV_K_QUANT_WORD_COLUMNS : KV_GENERIC;

@@ -140,6 +140,7 @@ enum KernelVariant : uint32_t {
     KV_AFFINE_GROUPED_OUTPUT_MAJOR = 5,  // the reference's own 4-bit layout, thread per output, 8 batch rows per weight
     KV_I4_MATVEC_WARP_ROWS = 6,          // i4x8 matvec, warp per row
     KV_K_QUANT_WORD_COLUMNS = 7,         // K-quant linear: thread per packed word column, k slices folded in fixed order
+    KV_RMS_NORM_TREE = 8,                // RMSNorm rows of 2048 elements and more: sum of squares as a tree, not a chain
 };
 
 uint32_t select_kernel_variant(const Program& p);

@@ -313,7 +313,7 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             std::memcpy(&eps, &u[2], 4);
             const bool gated = u[5] != 0;
             return launch_rms_norm(b[0], b[1], gated ? b[2] : nullptr, gated ? b[3] : b[2], u[0], u[1], eps, rt_dtype(u[3]),
-                                   rt_dtype(u[4]), s);
+                                   rt_dtype(u[4]), inst->variant == KV_RMS_NORM_TREE, s);
         }
         case OpKind::KQuantUnpack:
             return launch_k_quant_unpack((const uint32_t*)b[0], (const float*)b[1], (const float*)b[2], (float*)b[3], u[0], u[1], s);

@@ -188,9 +188,10 @@ cudaError_t launch_top_k(const float* in, uint32_t* out_idx, float* best_vals, u
                          uint32_t k, cudaStream_t s);
 cudaError_t launch_swiglu(const void* gate, const void* up, void* out, uint32_t n, uint32_t dtype, cudaStream_t s);
 cudaError_t launch_residual_add(const void* residual, const void* branch, void* out, uint32_t n, uint32_t dtype, cudaStream_t s);
-// learned_rms_norm (gate == nullptr) and gated_rms_norm; dtypes: 0 f32, 1 bf16, 2 f16
+// learned_rms_norm (gate == nullptr) and gated_rms_norm; dtypes: 0 f32, 1 bf16, 2 f16; tree: the sum of squares as a
+// two-level tree (kernel variant 8) instead of the reference's chain
 cudaError_t launch_rms_norm(const void* input, const void* weight, const void* gate, void* out, uint32_t rows, uint32_t hidden,
-                            float eps, uint32_t dtype, uint32_t weight_dtype, cudaStream_t s);
+                            float eps, uint32_t dtype, uint32_t weight_dtype, bool tree, cudaStream_t s);
 // GGML K-quants with per-block f32 scale / min sidecars; bits = 4 (Q4_K) or 2 (Q2_K)
 cudaError_t launch_k_quant_unpack(const uint32_t* packed, const float* scales, const float* mins, float* out, uint32_t n,
                                   uint32_t bits, cudaStream_t s);

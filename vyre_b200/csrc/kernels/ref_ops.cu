@@ -329,6 +329,43 @@ __global__ void rms_norm_kernel(const void* input, const void* weight, const voi
     }
 }
 
+// The same operator for long rows: the row's sum of squares as a two-level tree (every thread a strided partial sum,
+// warp shuffles, eight warp sums added in warp order) instead of one chain of `hidden` dependent additions, which at
+// hidden = 4096 is 8 microseconds on one thread. Deterministic; differs from the chain by f32 rounding of the sum
+// (about 1e-7 relative), everything after the sum is the code above.
+__global__ void __launch_bounds__(256) rms_norm_tree_kernel(const void* input, const void* weight, const void* gate, void* out,
+                                                            uint32_t hidden, float eps, uint32_t dt, uint32_t wdt) {
+    __shared__ float warp_sum[8];
+    __shared__ float inv_shared;
+    const size_t base = size_t(blockIdx.x) * hidden;
+    float sum = 0.0f;
+    for (uint32_t c = threadIdx.x; c < hidden; c += 256) {
+        const float v = load_typed(input, base + c, dt);
+        sum = fadd(sum, fmul(v, v));
+    }
+    for (int o = 16; o > 0; o >>= 1) sum = fadd(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+    if ((threadIdx.x & 31) == 0) warp_sum[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < 8; ++w) total = fadd(total, warp_sum[w]);
+        inv_shared = fdiv(1.0f, __fsqrt_rn(fadd(fdiv(total, float(hidden)), eps)));
+    }
+    __syncthreads();
+    const float inv = inv_shared;
+    for (uint32_t c = threadIdx.x; c < hidden; c += 256) {
+        float normalized = fmul(load_typed(input, base + c, dt), inv);
+        if (dt == 1) normalized = __bfloat162float(__float2bfloat16_rn(normalized));
+        else if (dt == 2) normalized = __half2float(__float2half_rn(normalized));
+        float v = fmul(normalized, load_typed(weight, c, wdt));
+        if (gate) {
+            const float g = load_typed(gate, base + c, dt);
+            v = fmul(v, fdiv(g, fadd(1.0f, expf(-g))));
+        }
+        store_typed(out, base + c, dt, v);
+    }
+}
+
 // vyre-libs/src/nn/quant/ggml.rs:28-120 and 217-333. bits = 4: blocks of 32 weights in 4 words; bits = 2: blocks of 16 in 1
 __device__ __forceinline__ uint32_t k_quant_value(const uint32_t* packed, uint32_t linear, uint32_t bits, uint32_t* block) {
     const uint32_t block_size = bits == 4 ? 32u : 16u, values_per_byte = 8u / bits, words_per_block = bits == 4 ? 4u : 1u;
@@ -485,8 +522,9 @@ cudaError_t launch_residual_add(const void* residual, const void* branch, void* 
     return cudaGetLastError();
 }
 cudaError_t launch_rms_norm(const void* input, const void* weight, const void* gate, void* out, uint32_t rows, uint32_t hidden,
-                            float eps, uint32_t dtype, uint32_t weight_dtype, cudaStream_t s) {
-    rms_norm_kernel<<<rows, 256, 0, s>>>(input, weight, gate, out, hidden, eps, dtype, weight_dtype);
+                            float eps, uint32_t dtype, uint32_t weight_dtype, bool tree, cudaStream_t s) {
+    if (tree) rms_norm_tree_kernel<<<rows, 256, 0, s>>>(input, weight, gate, out, hidden, eps, dtype, weight_dtype);
+    else rms_norm_kernel<<<rows, 256, 0, s>>>(input, weight, gate, out, hidden, eps, dtype, weight_dtype);
     return cudaGetLastError();
 }
 cudaError_t launch_k_quant_unpack(const uint32_t* packed, const float* scales, const float* mins, float* out, uint32_t n,
