@@ -38,6 +38,30 @@ def build() -> dict:
     mo, midx, mwts = oracle.moe_ffn_int4(mx, mwr, mw13, ms13, mw2, ms2, np.arange(t), h, i, e, topk, mode=1)
     out.update(moe_x=mx, moe_wr=mwr, moe_w13=mw13, moe_s13=ms13, moe_w2=mw2, moe_s2=ms2, moe_out=mo, moe_idx=midx,
                moe_wts=mwts)
+    # residual add (bf16), learned RMSNorm (f32 and bf16, rows short enough for the chain-order sum), K-quant unpack and
+    # fused linear (4-bit and 2-bit): all bit-exact on the device
+    rng = np.random.default_rng(104)
+    ra = oracle.f32_to_bf16_bits((rng.standard_normal(300) * 8).astype(np.float32))
+    rb = oracle.f32_to_bf16_bits(rng.standard_normal(300).astype(np.float32))
+    out["res_a"], out["res_b"], out["res_out"] = ra, rb, oracle.residual_add(ra, rb, oracle.DT_BF16)
+    rows, hidden = 3, 200
+    nx = (rng.standard_normal(rows * hidden) * 3).astype(np.float32)
+    nw = (1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    out["norm_x"], out["norm_w"] = nx, nw
+    out["norm_out_f32"] = oracle.rms_norm(nx, nw, rows, hidden, 1e-6).reshape(rows, hidden)
+    nxb, nwb = oracle.f32_to_bf16_bits(nx), oracle.f32_to_bf16_bits(nw)
+    out["norm_out_bf16"] = oracle.rms_norm(nxb, nwb, rows, hidden, 1e-6, dtype=oracle.DT_BF16).reshape(rows, hidden)
+    in_dim, out_dim = 96, 33
+    for bits, block, wpb in ((4, 32, 4), (2, 16, 1)):
+        blocks = -(-(in_dim * out_dim) // block)
+        kp = rng.integers(0, 2**32, size=blocks * wpb, dtype=np.uint32)
+        ks = rng.uniform(0.01, 0.2, size=blocks).astype(np.float32)
+        km = (-rng.uniform(0.0, 1.0, size=blocks)).astype(np.float32)
+        kx, kb = rng.standard_normal(in_dim).astype(np.float32), rng.standard_normal(out_dim).astype(np.float32)
+        pre = f"q{bits}k_"
+        out[pre + "packed"], out[pre + "scales"], out[pre + "mins"], out[pre + "x"], out[pre + "b"] = kp, ks, km, kx, kb
+        out[pre + "unpacked"] = oracle.k_quant_unpack(kp, ks, km, in_dim * out_dim, bits)
+        out[pre + "y"] = oracle.k_quant_linear(kx, kp, ks, km, kb, in_dim, out_dim, bits)
     return out
 
 

@@ -90,3 +90,36 @@ def test_kernels_match_the_committed_vectors(gold):
     got = out.float().cpu().numpy().astype(np.float64)
     floor = float(np.sqrt(np.mean(want ** 2)))
     assert np.max(np.abs(got - want) / np.maximum(np.abs(want), floor)) <= 2e-2
+
+
+@pytest.mark.gpu
+def test_operators_around_the_block_match_the_committed_vectors(gold):
+    """Residual add, learned RMSNorm (chain-order rows) and the K-quant programs through the contract path: bit-exact."""
+    import vyre_b200 as vb
+    from vyre_b200 import ffi
+
+    dev = vb.Device.acquire(0)
+    try:
+        run = lambda program, inputs: vb.ArtifactSession.compile(program, dev).run_host(inputs)[0]  # noqa: E731
+        n = gold["res_a"].size
+        got = np.frombuffer(run(vb.residual_add_typed("r", "b", "o", n, ffi.DT_BF16), [gold["res_a"], gold["res_b"]]), np.uint16)
+        assert np.array_equal(got, gold["res_out"])
+        rows, hidden = gold["norm_out_f32"].shape
+        got = np.frombuffer(run(vb.learned_rms_norm("i", "w", "o", rows, hidden, 1e-6, ffi.DT_F32),
+                                [gold["norm_x"], gold["norm_w"]]), np.uint32)
+        assert np.array_equal(got, gold["norm_out_f32"].view(np.uint32).ravel())
+        from vyre_b200 import synth
+
+        xb, wb = synth.f32_to_bf16_bits(gold["norm_x"]), synth.f32_to_bf16_bits(gold["norm_w"])
+        got = np.frombuffer(run(vb.learned_rms_norm("i", "w", "o", rows, hidden, 1e-6, ffi.DT_BF16), [xb, wb]), np.uint16)
+        assert np.array_equal(got, gold["norm_out_bf16"].ravel())
+        for bits, unpack, linear in ((4, vb.q4_k_unpack, vb.q4_k_linear), (2, vb.q2_k_unpack, vb.q2_k_linear)):
+            g = {k: gold[f"q{bits}k_{k}"] for k in ("packed", "scales", "mins", "x", "b", "unpacked", "y")}
+            in_dim, out_dim = g["x"].size, g["b"].size
+            got = np.frombuffer(run(unpack("p", "s", "m", "o", in_dim * out_dim), [g["packed"], g["scales"], g["mins"]]), np.uint32)
+            assert np.array_equal(got, g["unpacked"].view(np.uint32))
+            got = np.frombuffer(run(linear("x", "p", "s", "m", "b", "o", in_dim, out_dim),
+                                    [g["x"], g["packed"], g["scales"], g["mins"], g["b"]]), np.uint32)
+            assert np.array_equal(got, g["y"].view(np.uint32))
+    finally:
+        dev.release()
