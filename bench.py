@@ -452,6 +452,89 @@ def measure_k_quant(local_rank: int, peaks: dict, samples: int = 20, shape=(4096
     return out
 
 
+def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter: int = 14336, layers: int = 3, reps: int = 30) -> dict:
+    """The decode residual block (vyre-libs/src/nn/model/dense_gated_mlp.rs:168-370 over int4 projections): RMSNorm, gate /
+    up projections, SwiGLU, down projection, residual add, `layers` blocks in a row with weights of their own (together
+    larger than L2), one CUDA graph. Timed twice: every operator its own launch (six per block), and with the norm in the
+    gate / up launches and the residual add in the down launch (four per block). Both must give the same bits."""
+    import numpy as np
+    import torch
+
+    from vyre_b200 import ffi, synth
+
+    L = ffi.lib()
+    bf16 = ffi.DT_BF16
+    rng = np.random.default_rng(11)
+    dev16 = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda()  # noqa: E731
+    weights = []
+    for layer in range(layers):
+        ent = {"nw": dev16(synth.f32_to_bf16_bits((1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)))}
+        for name, (n, k) in {"gate": (inter, hidden), "up": (inter, hidden), "down": (hidden, inter)}.items():
+            _, w, sc = synth.int4_linear_inputs(1, n, k, seed=17 * layer + len(name))
+            ent[name] = (torch.from_numpy(w).cuda(), dev16(sc))
+        weights.append(ent)
+    x0 = dev16(synth.f32_to_bf16_bits((rng.standard_normal((rows, hidden)) * 2).astype(np.float32)))
+    stream_h = [dev16(np.zeros((rows, hidden), np.uint16)) for _ in range(layers + 1)]
+    normed, act, down = (dev16(np.zeros((rows, d), np.uint16)) for d in (hidden, inter, hidden))
+    gate, up = (dev16(np.zeros((rows, inter), np.uint16)) for _ in range(2))
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    side = torch.cuda.Stream()
+    sp, st = C.c_void_p(side.cuda_stream), C.c_void_p(status.data_ptr())
+    flags = ffi.LAUNCH_CONSTANT_WEIGHTS
+    eps = C.c_float(1e-6)
+
+    def gemv(x, ws, y, n, k):
+        ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[0].data_ptr(), ws[1].data_ptr(), y.data_ptr(), rows, n, k, GROUP, bf16, flags, sp, st))
+
+    def block(x, ws, y, n, k, nw=None, res=None):
+        ffi.check(L.vyb_k_int4_linear_block(x.data_ptr(), nw.data_ptr() if nw is not None else None, eps, ws[0].data_ptr(),
+                                            ws[1].data_ptr(), res.data_ptr() if res is not None else None, y.data_ptr(), rows, n, k,
+                                            GROUP, flags, sp, st))
+
+    def separate():
+        for i, w in enumerate(weights):
+            h, out = stream_h[i], stream_h[i + 1]
+            ffi.check(L.vyb_k_rms_norm(h.data_ptr(), w["nw"].data_ptr(), normed.data_ptr(), rows, hidden, eps, bf16, sp))
+            gemv(normed, w["gate"], gate, inter, hidden)
+            gemv(normed, w["up"], up, inter, hidden)
+            ffi.check(L.vyb_k_swiglu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), rows * inter, bf16, sp))
+            gemv(act, w["down"], down, hidden, inter)
+            ffi.check(L.vyb_k_residual_add(h.data_ptr(), down.data_ptr(), out.data_ptr(), rows * hidden, bf16, sp))
+
+    def fused():
+        for i, w in enumerate(weights):
+            h, out = stream_h[i], stream_h[i + 1]
+            block(h, w["gate"], gate, inter, hidden, nw=w["nw"])
+            block(h, w["up"], up, inter, hidden, nw=w["nw"])
+            ffi.check(L.vyb_k_swiglu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), rows * inter, bf16, sp))
+            block(act, w["down"], out, hidden, inter, res=h)
+
+    results, finals = {}, []
+    for name, body, launches in (("separate_launches", separate, 6), ("fused_launches", fused, 4)):
+        stream_h[0].copy_(x0)
+        with torch.cuda.stream(side):
+            body()  # first launches configure the kernels and make the long-row workspace; must precede capture
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                body()
+        us = event_time_us(graph.replay, reps=reps, warm=3, stream=side) / layers
+        finals.append(stream_h[layers].clone())
+        results[name] = {"launches_per_block": launches, "us_per_block": round(us, 2)}
+    assert status.cpu().tolist() == [0, 0, 0, 0]
+    assert torch.equal(finals[0], finals[1]), "the fused block's output differs from the separate operators'"
+    wbytes = 3 * (hidden * inter // 2 + hidden * inter // GROUP * 2)
+    abytes = wbytes + rows * (4 * hidden + 3 * inter) * 2 + hidden * 2  # weights and scales; residual in / out, norm weight, gate / up / act
+    gbs = abytes / (results["fused_launches"]["us_per_block"] * 1e-6) / 1e9
+    return {"case": f"residual block rows={rows} hidden={hidden} inter={inter}, {layers} blocks per graph ({layers * wbytes >> 20} MiB of weights)",
+            **results, "same_bits": True,
+            "speedup": round(results["separate_launches"]["us_per_block"] / results["fused_launches"]["us_per_block"], 3),
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(gbs / peaks["hbm_gbs"], 4), "algorithmic_bytes_per_block": abytes,
+                         "kernel": "int4_gemv_halfsm_kernel (fused and k-block forms) + swiglu_kernel"}}
+
+
 def metric_stats(samples) -> dict:
     """vyre-bench MetricStats (vyre-bench/SCHEMA.md, `MetricStats` object) of integer samples."""
     v = sorted(int(x) for x in samples)
@@ -875,6 +958,7 @@ def run_native(args) -> None:
     secondary["dropin_1m"] = measure_dropin_1m(local_rank)
     secondary["dropin_decode_shape"] = measure_dropin_1m(local_rank, shape=(K_IN, N_OUT, GROUP, 1), peaks=peaks)
     secondary["k_quant_linear"] = measure_k_quant(local_rank, peaks)
+    secondary["residual_block_m1"] = measure_residual_block(peaks)
     secondary["clocks_during_secondary"] = sampler.summary(s_lo, sampler.mark())
     torch.cuda.empty_cache()
 
@@ -999,6 +1083,9 @@ def run_quick(args) -> None:
         print(json.dumps({"quick": True, "k_quant": measure_k_quant(0, peaks), "dropin_1m": first,
                           "dropin_decode_shape": [measure_dropin_1m(0, shape=(K_IN, N_OUT, GROUP, bb), peaks=peaks) for bb in (1, 4, 8)]}))
         return
+    if args.case == "block":
+        print(json.dumps({"quick": True, "case": "block", **measure_residual_block(peaks, rows=args.m, reps=args.steps)}))
+        return
     if args.case == "peak":
         print(json.dumps({"quick": True, "case": "peak", "int8_tops": tensor_peak(True), "bf16_tflops": tensor_peak(False)}))
         return
@@ -1058,7 +1145,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--m", type=int, default=1, help="decode batch (1, 4 or 8)")
-    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm", "peak", "dropin"], help="kernel exercised by --quick")
+    ap.add_argument("--case", default="gemv", choices=["gemv", "prefill", "int8gemm", "peak", "dropin", "block"], help="kernel exercised by --quick")
     ap.add_argument("--shape", type=int, nargs=3, default=[2048, 14336, 4096], metavar=("M", "N", "K"),
                     help="GEMM shape for --quick --case prefill|int8gemm")
     ap.add_argument("--kernel-reps", type=int, default=0,

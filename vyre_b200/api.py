@@ -282,6 +282,13 @@ def linear_int4_grouped_rowmajor(x, w_packed, scale, out, batch, in_dim, out_dim
                   out_dtype)
 
 
+def linear_int4_block(x, norm_weight, w_packed, scale, residual, out, batch, in_dim, out_dim, group_size, norm_eps=0.0):
+    """The int4 row-major projection as one node with a learned RMSNorm in front (`norm_weight` named) and / or a residual
+    add behind (`residual` named); pass None for the part that is absent."""
+    return _build("vyb_nn_linear_int4_block", x, None if norm_weight is None else _b(norm_weight), w_packed, scale,
+                  None if residual is None else _b(residual), out, batch, in_dim, out_dim, group_size, C.c_float(norm_eps))
+
+
 def linear_int8_weight_only(x, w, scale, out, batch, in_dim, out_dim):
     return _build("vyb_nn_linear_int8_weight_only", x, w, scale, out, batch, in_dim, out_dim)
 
@@ -875,6 +882,13 @@ class ProgramGraph:
 
     def schedule(self) -> list[int]:
         return list(range(ffi.lib().vyb_graph_node_count(self._h)))
+
+    def fuse_linear_blocks(self) -> tuple["ProgramGraph", int]:
+        """A copy in which RMSNorm nodes in front of int4 linears and residual adds behind them are taken into
+        `linear_int4_block` nodes wherever the decode kernel does the part in its own launch; (graph, nodes taken in)."""
+        out, n = C.c_void_p(), C.c_uint32()
+        check(ffi.lib().vyb_graph_fuse_linear_blocks(self._h, C.byref(out), C.byref(n)))
+        return ProgramGraph(out.value), n.value
 
     def digest(self) -> bytes:
         buf = C.create_string_buffer(32)

@@ -88,6 +88,17 @@ uint32_t select_kernel_variant(const Program& p) {
             if (prefill_ok && batch > 8) return KV_INT4_PREFILL_TCGEN05;
             return KV_GENERIC;
         }
+        case OpKind::LinearInt4Block: {
+            // decode shapes whose GEMV takes the norm and / or the residual add into its own launch; everything else runs
+            // the stand-alone kernels one after the other inside the node
+            const uint32_t batch = p.params.u[0], in_dim = p.params.u[1], group = p.params.u[3], parts = p.params.u[5];
+            const bool whole_rows = in_dim == 2048 || in_dim == 4096;
+            const bool k_blocks = in_dim > 4096 && in_dim % 2048 == 0 && (parts & 2u);  // only the residual add joins that form
+            if (group == 128 && ((whole_rows && batch <= 2) || (k_blocks && batch <= 4))) return KV_INT4_BLOCK_GEMV;
+            Program bare = p;
+            bare.kind = OpKind::LinearInt4GroupedRowmajor;
+            return select_kernel_variant(bare);
+        }
         case OpKind::LinearInt8Dynamic: return KV_INT8_GEMM_TCGEN05;
         case OpKind::MoeFfnInt4: return KV_MOE_FUSED;
         // the reference's own operators: small shapes keep the kernels that follow the reference's evaluation order
@@ -222,6 +233,7 @@ const char* const SUPPORTED_OPS[] = {
     "vyre-libs::quant::q4_k_linear",
     "vyre-libs::quant::q2_k_linear",
     "vyre-b200::nn::linear_int4_grouped_rowmajor",
+    "vyre-b200::nn::linear_int4_block",
     "vyre-b200::nn::linear_int8_weight_only",
     "vyre-b200::nn::linear_int8_dynamic",
     "vyre-b200::nn::moe_ffn_int4",

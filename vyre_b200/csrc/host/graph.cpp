@@ -5,6 +5,7 @@
 // value they replace. Only statically known dimensions exist here (the reference's ShapeDim::Symbol is not rebuilt).
 // The graph is host metadata: the runtime walks its schedule and submits one materialised Program per node.
 #include <algorithm>
+#include <cstring>
 #include <memory>
 #include <set>
 #include <string>
@@ -314,6 +315,180 @@ int32_t vyb_graph_node_output(const vyb_graph* g, uint32_t node, uint32_t index,
     to_c(o.contract, &out->contract);
     out->retained_successor_of = o.retained_successor_of;
     if (value_id) *value_id = o.value;
+    return VYB_OK;
+}
+
+// The residual block's projections with their neighbours taken in (dense_gated_mlp.rs:168-200: `mlp.norm` feeds gate_proj
+// and up_proj, `mlp.residual` follows down_proj): a copy of the graph in which
+//   * a bf16 learned RMSNorm node whose output is read only as the activation of int4 row-major linears (bf16 outputs) is
+//     dropped, and each of those linears becomes a linear_int4_block node that reads the norm's input and weight itself;
+//   * a bf16 residual add whose `branch` is produced by such a linear, and read by nothing else, is dropped, and the linear
+//     becomes (or stays) a linear_int4_block node that reads the residual and produces the add's output value.
+// Every other node and value is carried over with its name, contract and order. Values of the fused graph equal those of
+// the original (the block node rounds where the stand-alone operators round). `n_fused` counts the dropped nodes.
+int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint32_t* n_fused) {
+    if (!g || !fused) return fail_invalid_program("Fix: pass a graph and an out-pointer for the fused graph.");
+    const size_t nn = g->nodes.size();
+    auto is_linear = [&](const Node& n) {
+        if (n.program.p.kind != OpKind::LinearInt4GroupedRowmajor || n.program.p.params.u[4] != VYB_DT_BF16 || n.inputs.size() != 3 ||
+            n.outputs.size() != 1)
+            return false;
+        for (const BufferDecl& b : n.program.p.buffers)
+            if (b.name == "norm_weight" || b.name == "residual") return false;  // the names of the block node's added ports
+        return true;
+    };
+    // only where the decode kernel takes the part into its own launch (the target compiler's rule for the block node)
+    auto kernel_takes = [&](const Node& lin, uint32_t part) {
+        Program probe = lin.program.p;
+        probe.kind = OpKind::LinearInt4Block;
+        probe.params.u[5] = part;
+        return select_kernel_variant(probe) == KV_INT4_BLOCK_GEMV;
+    };
+    auto port_value = [](const Node& n, const std::string& buffer) -> int64_t {
+        for (const Input& in : n.inputs)
+            if (in.buffer == buffer) return in.value;
+        return -1;
+    };
+    struct Plan {
+        int64_t norm = -1;   // linear: the norm node taken into its prologue
+        int64_t resid = -1;  // linear: the residual-add node taken into its stores
+        bool dropped = false;
+    };
+    std::vector<Plan> plan(nn);
+    for (size_t i = 0; i < nn; ++i) {
+        const Node& n = g->nodes[i];
+        const Program& np = n.program.p;
+        if (np.kind == OpKind::RmsNorm && np.params.u[5] == 0 && np.params.u[3] == VYB_DT_BF16 && np.params.u[4] == VYB_DT_BF16 &&
+            n.inputs.size() == 2 && n.outputs.size() == 1) {
+            const Value& out = g->values[n.outputs[0].value];
+            bool ok = !out.consumers.empty() && out.contract.lifetime == VYB_LIFETIME_INVOCATION && out.retained_successor_of < 0;
+            for (uint32_t c : out.consumers) {
+                const Node& lin = g->nodes[c];
+                ok = ok && is_linear(lin) && kernel_takes(lin, 1u) &&
+                     port_value(lin, lin.program.p.buffers[0].name) == int64_t(n.outputs[0].value) &&
+                     lin.program.p.params.u[0] == np.params.u[0] && lin.program.p.params.u[1] == np.params.u[1];
+            }
+            if (ok) {
+                plan[i].dropped = true;
+                for (uint32_t c : out.consumers) plan[c].norm = int64_t(i);
+            }
+        }
+        if (np.kind == OpKind::ResidualAdd && np.params.u[1] == VYB_DT_BF16 && n.inputs.size() == 2 && n.outputs.size() == 1) {
+            // buffers: residual, branch, output (residual_add.rs:8-52)
+            const int64_t branch = port_value(n, np.buffers[1].name), residual = port_value(n, np.buffers[0].name);
+            if (branch < 0 || residual < 0) continue;
+            const Value& bv = g->values[size_t(branch)];
+            if (bv.producer < 0 || bv.consumers.size() != 1 || bv.contract.lifetime != VYB_LIFETIME_INVOCATION) continue;
+            const Node& lin = g->nodes[size_t(bv.producer)];
+            if (!is_linear(lin) || !kernel_takes(lin, 2u) || plan[size_t(bv.producer)].resid >= 0) continue;
+            if (uint64_t(lin.program.p.params.u[0]) * lin.program.p.params.u[2] != np.params.u[0]) continue;
+            // the residual must exist when the linear runs
+            const Value& rv = g->values[size_t(residual)];
+            if (rv.producer >= bv.producer) continue;
+            plan[i].dropped = true;
+            plan[size_t(bv.producer)].resid = int64_t(i);
+        }
+    }
+    std::unique_ptr<vyb_graph> out(new vyb_graph());
+    // values and nodes are re-created in the order of the original (value ids are creation order: an external value when it
+    // was declared, a node's outputs when the node was added), so that a graph with nothing to take in comes out identical
+    std::vector<int64_t> remap(g->values.size(), -1);
+    std::vector<bool> emitted(nn, false);
+    uint32_t dropped = 0;
+    auto emit_node = [&](size_t i) -> int32_t {
+        emitted[i] = true;
+        const Node& n = g->nodes[i];
+        if (plan[i].dropped) {
+            ++dropped;
+            return VYB_OK;
+        }
+        std::vector<Input> ins = n.inputs;
+        std::vector<Output> outs = n.outputs;
+        vyb_program* built = nullptr;
+        const vyb_program* program = &n.program;
+        if (plan[i].norm >= 0 || plan[i].resid >= 0) {
+            const Program& lp = n.program.p;
+            const Node* norm = plan[i].norm >= 0 ? &g->nodes[size_t(plan[i].norm)] : nullptr;
+            const Node* add = plan[i].resid >= 0 ? &g->nodes[size_t(plan[i].resid)] : nullptr;
+            float eps = 0.0f;
+            if (norm) std::memcpy(&eps, &norm->program.p.params.u[2], 4);
+            if (int32_t rc = vyb_nn_linear_int4_block(lp.buffers[0].name.c_str(), norm ? "norm_weight" : nullptr, lp.buffers[1].name.c_str(),
+                                                      lp.buffers[2].name.c_str(), add ? "residual" : nullptr, lp.buffers[3].name.c_str(),
+                                                      lp.params.u[0], lp.params.u[1], lp.params.u[2], lp.params.u[3], eps, &built))
+                return rc;
+            program = built;
+            if (norm) {
+                // the activation port now reads what the norm read; the norm's weight becomes a port of this node
+                const Program& np = norm->program.p;
+                for (Input& in : ins)
+                    if (in.buffer == lp.buffers[0].name)
+                        for (const Input& ni : norm->inputs)
+                            if (ni.buffer == np.buffers[0].name) {
+                                in.value = ni.value;
+                                in.contract = ni.contract;
+                            }
+                for (const Input& ni : norm->inputs)
+                    if (ni.buffer == np.buffers[1].name) {
+                        Input w = ni;
+                        w.buffer = "norm_weight";
+                        ins.push_back(w);
+                    }
+            }
+            if (add) {
+                const Program& ap = add->program.p;
+                for (const Input& ai : add->inputs)
+                    if (ai.buffer == ap.buffers[0].name) {
+                        Input r = ai;
+                        r.buffer = "residual";
+                        ins.push_back(r);
+                    }
+                outs[0].name = add->outputs[0].name;
+                outs[0].contract = add->outputs[0].contract;
+                outs[0].retained_successor_of = -1;
+            }
+        }
+        std::vector<vyb_graph_input> cin(ins.size());
+        std::vector<vyb_graph_output> cout(outs.size());
+        for (size_t k = 0; k < ins.size(); ++k) {
+            cin[k].buffer = ins[k].buffer.c_str();
+            cin[k].value = uint32_t(remap[ins[k].value]);
+            to_c(ins[k].contract, &cin[k].contract);
+        }
+        for (size_t k = 0; k < outs.size(); ++k) {
+            cout[k].buffer = outs[k].buffer.c_str();
+            cout[k].name = outs[k].name.c_str();
+            to_c(outs[k].contract, &cout[k].contract);
+            cout[k].retained_successor_of = outs[k].retained_successor_of < 0 ? -1 : remap[size_t(outs[k].retained_successor_of)];
+        }
+        std::vector<uint32_t> ids(std::max<size_t>(1, outs.size()));
+        const int32_t rc = vyb_graph_add_node(out.get(), n.name.c_str(), program, cin.data(), uint32_t(cin.size()), cout.data(),
+                                              uint32_t(cout.size()), nullptr, ids.data());
+        if (built) vyb_program_free(built);
+        if (rc) return rc;
+        // the values this node produced in the original graph (and, with the add taken in, the add's output) map to the new ones
+        for (size_t k = 0; k < n.outputs.size(); ++k) remap[n.outputs[k].value] = ids[k];
+        if (plan[i].resid >= 0) remap[g->nodes[size_t(plan[i].resid)].outputs[0].value] = ids[0];
+        return VYB_OK;
+    };
+    for (size_t v = 0; v < g->values.size(); ++v) {
+        const Value& val = g->values[v];
+        if (val.producer >= 0) {
+            if (!emitted[size_t(val.producer)])
+                if (int32_t rc = emit_node(size_t(val.producer))) return rc;
+            continue;
+        }
+        vyb_value_contract c;
+        to_c(val.contract, &c);
+        uint32_t id = 0;
+        if (int32_t rc = vyb_graph_add_external_value(out.get(), val.name.c_str(), &c, &id)) return rc;
+        remap[v] = id;
+    }
+    for (size_t i = 0; i < nn; ++i)  // nodes without outputs
+        if (!emitted[i])
+            if (int32_t rc = emit_node(i)) return rc;
+    if (n_fused) *n_fused = dropped;
+    *fused = out.release();
+    clear_error();
     return VYB_OK;
 }
 

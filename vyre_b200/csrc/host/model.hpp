@@ -60,6 +60,7 @@ enum class OpKind : uint32_t {
     LinearInt8WeightOnly = 33,
     LinearInt8Dynamic = 34,
     MoeFfnInt4 = 35,
+    LinearInt4Block = 36,  // the int4 projection with a learned RMSNorm in front and / or a residual add behind, one node
 };
 
 struct BufferDecl {
@@ -141,6 +142,7 @@ enum KernelVariant : uint32_t {
     KV_I4_MATVEC_WARP_ROWS = 6,          // i4x8 matvec, warp per row
     KV_K_QUANT_WORD_COLUMNS = 7,         // K-quant linear: thread per packed word column, k slices folded in fixed order
     KV_RMS_NORM_TREE = 8,                // RMSNorm rows of 2048 elements and more: sum of squares as a tree, not a chain
+    KV_INT4_BLOCK_GEMV = 9,              // decode GEMV with the norm in its prologue and / or the residual add in its stores
 };
 
 uint32_t select_kernel_variant(const Program& p);

@@ -1087,6 +1087,53 @@ int32_t vyb_nn_linear_int4_grouped_rowmajor(const char* x, const char* w_packed,
     return emit(program, std::move(p));
 }
 
+// The projection of a residual block as ONE node: learned RMSNorm (dense_gated_mlp.rs:168-200 `mlp.norm`, bf16) in front
+// when `norm_weight` is named, residual add (`mlp.residual`) behind when `residual` is named. Values are those of the three
+// operators run one after the other (every intermediate rounded to bf16 as the stand-alone operators round it).
+int32_t vyb_nn_linear_int4_block(const char* x, const char* norm_weight, const char* w_packed, const char* scale,
+                                 const char* residual, const char* out, uint32_t batch, uint32_t in_dim, uint32_t out_dim,
+                                 uint32_t group_size, float norm_eps, vyb_program** program) {
+    VYB_REQUIRE_NAMES(x, w_packed, scale, out);
+    if (!norm_weight && !residual)
+        return fail_invalid_program(
+            "Fix: linear_int4_block needs a norm weight, a residual, or both; use linear_int4_grouped_rowmajor for the bare projection.");
+    if (batch == 0 || in_dim == 0 || out_dim == 0 || group_size == 0)
+        return fail_invalid_program("Fix: linear_int4_block requires nonzero batch, in_dim, out_dim and group_size; got batch=" +
+                                    std::to_string(batch) + ", in_dim=" + std::to_string(in_dim) + ", out_dim=" +
+                                    std::to_string(out_dim) + ", group_size=" + std::to_string(group_size) + ".");
+    if (in_dim % 8 != 0)
+        return fail_invalid_program("Fix: linear_int4_block in_dim=" + std::to_string(in_dim) +
+                                    " is not divisible by 8; pad weights to a multiple of 8.");
+    if (in_dim % group_size != 0)
+        return fail_invalid_program("Fix: linear_int4_block in_dim=" + std::to_string(in_dim) + " is not a multiple of group_size=" +
+                                    std::to_string(group_size) + "; pad the last group.");
+    if (norm_weight && !(norm_eps >= 0.0f))
+        return fail_invalid_program("Fix: linear_int4_block needs a non-negative, finite-or-zero norm epsilon.");
+    uint32_t xc, wc, sc, oc;
+    if (!checked_mul(batch, in_dim, &xc) || !checked_mul(out_dim, in_dim / 8, &wc) ||
+        !checked_mul(out_dim, in_dim / group_size, &sc) || !checked_mul(batch, out_dim, &oc))
+        return fail_invalid_program("Fix: linear_int4_block element counts overflow u32; shard the projection.");
+    Program p;
+    p.op_id = "vyre-b200::nn::linear_int4_block";
+    p.kind = OpKind::LinearInt4Block;
+    p.workgroup = {256, 1, 1};
+    p.params.u[0] = batch;
+    p.params.u[1] = in_dim;
+    p.params.u[2] = out_dim;
+    p.params.u[3] = group_size;
+    p.params.u[4] = VYB_DT_BF16;
+    p.params.u[5] = (norm_weight ? 1u : 0u) | (residual ? 2u : 0u);
+    std::memcpy(&p.params.u[6], &norm_eps, 4);
+    uint32_t slot = 0;
+    p.buffers.push_back(storage(x, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, xc));
+    if (norm_weight) p.buffers.push_back(storage(norm_weight, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, in_dim));
+    p.buffers.push_back(storage(w_packed, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_U32, wc));
+    p.buffers.push_back(storage(scale, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, sc));
+    if (residual) p.buffers.push_back(storage(residual, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, oc));
+    p.buffers.push_back(output(out, slot++, VYB_DT_BF16, oc));
+    return emit(program, std::move(p));
+}
+
 int32_t vyb_nn_linear_int8_weight_only(const char* x, const char* w, const char* scale, const char* out,
                                        uint32_t batch, uint32_t in_dim, uint32_t out_dim, vyb_program** program) {
     VYB_REQUIRE_NAMES(x, w, scale, out);

@@ -246,12 +246,33 @@ uint32_t rt_dtype(uint32_t tag) { return tag == VYB_DT_BF16 ? 1u : tag == VYB_DT
 bool overwrites_every_output_byte(const Program& p) {
     switch (p.kind) {
         case OpKind::LinearInt4GroupedRowmajor:
+        case OpKind::LinearInt4Block:
         case OpKind::LinearInt8WeightOnly:
         case OpKind::LinearInt8Dynamic:
             return true;
         default:
             return false;
     }
+}
+
+// The int4 group-quantized projection y[batch][n] = x[batch][k] W^T by the kernel the payload names
+cudaError_t run_int4_linear(vyb_instance* inst, uint32_t variant, const void* x, const void* w, const void* scale, void* y,
+                            uint32_t batch, uint32_t k, uint32_t n, uint32_t group, uint32_t out_f32, cudaStream_t s) {
+    using namespace vybk;
+    const size_t out_elem = out_f32 ? 4 : 2;
+    if (variant == KV_INT4_PREFILL_TCGEN05 && int4_prefill_supported(batch, n, k, group))
+        return launch_int4_prefill(x, w, scale, y, batch, n, k, group, out_f32, inst->dev->prop.multiProcessorCount, s,
+                                   inst->status_dev);
+    if (variant == KV_INT4_GEMV_TMA && int4_gemv_supported(std::min(batch, 8u), n, k, group)) {
+        for (uint32_t b0 = 0; b0 < batch; b0 += 8) {
+            const uint32_t mb = std::min(8u, batch - b0);
+            cudaError_t e = launch_int4_gemv((const uint16_t*)x + size_t(b0) * k, w, scale, (uint8_t*)y + size_t(b0) * n * out_elem,
+                                             mb, n, k, out_f32, inst->dev->prop.multiProcessorCount, s, inst->status_dev);
+            if (e != cudaSuccess) return e;
+        }
+        return cudaSuccess;
+    }
+    return launch_int4_linear_generic(x, w, scale, y, batch, n, k, group, out_f32, s);
 }
 
 // Launch the kernels of one program. `b[slot]` is the device pointer bound to the BufferDecl binding slot.
@@ -331,23 +352,45 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
         case OpKind::MoeLayerAccumulate:
             return launch_moe_layer_accumulate((const float*)b[4], (const float*)b[5], (float*)b[6], u[3], u[2], s);
         case OpKind::LinearInt4GroupedRowmajor: {
-            const uint32_t batch = u[0], k = u[1], n = u[2], group = u[3];
-            const uint32_t out_f32 = u[4] == VYB_DT_F32 ? 1u : 0u;
-            const size_t out_elem = out_f32 ? 4 : 2;
-            if (inst->variant == KV_INT4_PREFILL_TCGEN05 && int4_prefill_supported(batch, n, k, group))
-                return launch_int4_prefill(b[0], b[1], b[2], b[3], batch, n, k, group, out_f32,
-                                           inst->dev->prop.multiProcessorCount, s, inst->status_dev);
-            if (inst->variant == KV_INT4_GEMV_TMA && int4_gemv_supported(std::min(batch, 8u), n, k, group)) {
-                for (uint32_t b0 = 0; b0 < batch; b0 += 8) {
-                    const uint32_t mb = std::min(8u, batch - b0);
-                    cudaError_t e = launch_int4_gemv((const uint16_t*)b[0] + size_t(b0) * k, b[1], b[2],
-                                                     (uint8_t*)b[3] + size_t(b0) * n * out_elem, mb, n, k, out_f32,
-                                                     inst->dev->prop.multiProcessorCount, s, inst->status_dev);
-                    if (e != cudaSuccess) return e;
-                }
-                return cudaSuccess;
+            return run_int4_linear(inst, inst->variant, b[0], b[1], b[2], b[3], u[0], u[1], u[2], u[3],
+                                   u[4] == VYB_DT_F32 ? 1u : 0u, s);
+        }
+        case OpKind::LinearInt4Block: {
+            // slots: x, [norm weight], packed weights, scales, [residual], out
+            const uint32_t batch = u[0], k = u[1], n = u[2], group = u[3], parts = u[5];
+            float eps;
+            std::memcpy(&eps, &u[6], 4);
+            uint32_t slot = 0;
+            const void* x = b[slot++];
+            const void* norm_w = (parts & 1u) ? b[slot++] : nullptr;
+            const void* w = b[slot++];
+            const void* scale = b[slot++];
+            const void* resid = (parts & 2u) ? b[slot++] : nullptr;
+            void* y = b[slot];
+            const int sms = inst->dev->prop.multiProcessorCount;
+            const bool gemv = inst->variant == KV_INT4_BLOCK_GEMV;
+            // whole rows of 2048 / 4096, one or two batch rows: norm, projection and residual add are ONE launch
+            if (gemv && batch <= 2 && int4_gemv_halfsm_supported(batch, n, k, group))
+                return launch_int4_gemv_halfsm(x, w, scale, y, batch, n, k, 0, sms, s, inst->status_dev, false, nullptr, 0, false,
+                                               norm_w, eps, resid);
+            // otherwise the stand-alone kernels in sequence: the norm into scratch (the tree form from 2048 elements on, as
+            // the stand-alone operator chooses), the projection, the residual add in place
+            if (norm_w) {
+                cudaError_t e = launch_rms_norm(x, norm_w, nullptr, inst->scratch, batch, k, eps, 1, 1, k >= 2048, s);
+                if (e != cudaSuccess) return e;
+                x = inst->scratch;
             }
-            return launch_int4_linear_generic(b[0], b[1], b[2], b[3], batch, n, k, group, out_f32, s);
+            if (gemv && resid && int4_gemv_kblocks_supported(batch, n, k, group)) {
+                // long rows: the residual is added where the last-arriving k block rounds the sums
+                bool added = false;
+                cudaError_t e = launch_int4_gemv_kblocks(x, w, scale, y, batch, n, k, 0, sms, s, false, resid, &added);
+                if (e != cudaSuccess || added) return e;
+            } else {
+                cudaError_t e = run_int4_linear(inst, gemv ? uint32_t(KV_INT4_GEMV_TMA) : inst->variant, x, w, scale, y, batch, k, n,
+                                                group, 0, s);
+                if (e != cudaSuccess) return e;
+            }
+            return resid ? launch_residual_add(resid, y, y, batch * n, 1, s) : cudaSuccess;
         }
         case OpKind::LinearInt8Dynamic: {
             const uint32_t rows = u[0], k = u[1], n = u[2];
@@ -377,6 +420,8 @@ size_t scratch_bytes_for(const Program& p) {
         case OpKind::ExpertMlp: return size_t(p.params.u[1]) * 4;
         case OpKind::LinearInt8Dynamic: return size_t(p.params.u[0]) * p.params.u[1];
         case OpKind::KQuantLinear: return vybk::k_quant_linear_fast_scratch_bytes(p.params.u[1]);
+        case OpKind::LinearInt4Block:  // the normalised activations, when the norm runs as its own kernel
+            return (p.params.u[5] & 1u) ? size_t(p.params.u[0]) * p.params.u[1] * 2 : 0;
         case OpKind::MoeFfnInt4:
             return vybk::moe_ffn_int4_scratch_bytes(p.params.u[0], p.params.u[1], p.params.u[2], p.params.u[3], p.params.u[4]);
         default: return 0;
@@ -1062,7 +1107,7 @@ int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const
             prep->resident_ids.push_back(b->resident.id);
             dev_ptr = r->ptr;
         } else if (!is_input && is_output && !bd.has_output_byte_range && need <= DIRECT_OUTPUT_BYTES &&
-                   overwrites_every_output_byte(p)) {
+                   overwrites_every_output_byte(p) && p.kind != OpKind::LinearInt4Block) {  // whose residual add may run in place
             // A small output that its kernel writes completely: the kernel stores straight into mapped pinned host memory
             // (posted writes over PCIe, a few hundred transactions), which saves the device buffer and the copy node.
             direct_host = inst->acquire_pinned(need);
@@ -1413,6 +1458,73 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
                         uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, void* stream,
                         uint32_t* status) {
     return vyb_k_int4_gemv_ex(x_bf16, w_packed, scale_bf16, y, m, n, k, group_size, out_dtype, 0, stream, status);
+}
+
+// ---- the residual block around a decode projection, on raw device pointers --------------------------------------------
+int32_t vyb_k_int4_linear_block(const void* x_bf16, const void* norm_weight_bf16, float norm_eps, const void* w_packed,
+                                const void* scale_bf16, const void* residual_bf16, void* y_bf16, uint32_t m, uint32_t n, uint32_t k,
+                                uint32_t group_size, uint32_t flags, void* stream, uint32_t* status) {
+    if (!x_bf16 || !w_packed || !scale_bf16 || !y_bf16) return fail_invalid_program("Fix: pass non-null device pointers.");
+    if (!norm_weight_bf16 && !residual_bf16)
+        return fail_invalid_program("Fix: pass a norm weight, a residual, or both; vyb_k_int4_gemv is the bare projection.");
+    const bool whole = m <= 2 && vybk::int4_gemv_halfsm_supported(m, n, k, group_size);
+    const bool blocks = !norm_weight_bf16 && vybk::int4_gemv_kblocks_supported(m, n, k, group_size);
+    if (!whole && !blocks)
+        return fail_unsupported("int4 block gemv shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" + std::to_string(k) +
+                                " group=" + std::to_string(group_size) +
+                                " (needs group 128 and m <= 2 with k 2048 or 4096, or the residual alone with m <= 4 and k a larger multiple of 2048)");
+    if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(scale_bf16) |
+         reinterpret_cast<uintptr_t>(norm_weight_bf16)) & 15)
+        return fail_invalid_program("Fix: int4 gemv operands must be 16-byte aligned.");
+    int dev = 0, sms = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail_dispatch(int(e), "no usable CUDA device for the launch (" + cuda_msg(e) + "); there is no CPU path");
+    }
+    const bool constant = (flags & VYB_LAUNCH_CONSTANT_WEIGHTS) != 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (whole)
+        return launch_result(vybk::launch_int4_gemv_halfsm(x_bf16, w_packed, scale_bf16, y_bf16, m, n, k, 0, sms, s, status, constant,
+                                                           nullptr, 0, false, norm_weight_bf16, norm_eps, residual_bf16),
+                             "int4 block gemv");
+    bool added = false;
+    e = vybk::launch_int4_gemv_kblocks(x_bf16, w_packed, scale_bf16, y_bf16, m, n, k, 0, sms, s, constant, residual_bf16, &added);
+    if (e == cudaSuccess && !added) e = vybk::launch_residual_add(residual_bf16, y_bf16, y_bf16, m * n, 1, s);
+    return launch_result(e, "int4 block gemv");
+}
+
+namespace {
+int32_t rt_float_dtype(uint32_t dtype, uint32_t* out) {
+    if (dtype != VYB_DT_F32 && dtype != VYB_DT_BF16 && dtype != VYB_DT_F16)
+        return fail_invalid_program("Fix: the element type must be F16, BF16, or F32.");
+    *out = rt_dtype(dtype);
+    return VYB_OK;
+}
+}  // namespace
+
+int32_t vyb_k_rms_norm(const void* input, const void* weight, void* output, uint32_t rows, uint32_t hidden, float eps,
+                       uint32_t dtype, void* stream) {
+    uint32_t dt = 0;
+    if (int32_t rc = rt_float_dtype(dtype, &dt)) return rc;
+    if (!input || !weight || !output || rows == 0 || hidden == 0)
+        return fail_invalid_program("Fix: pass non-null device pointers and nonzero rows and hidden size.");
+    return launch_result(vybk::launch_rms_norm(input, weight, nullptr, output, rows, hidden, eps, dt, dt, hidden >= 2048,
+                                               static_cast<cudaStream_t>(stream)),
+                         "rms norm");
+}
+int32_t vyb_k_residual_add(const void* residual, const void* branch, void* output, uint32_t n, uint32_t dtype, void* stream) {
+    uint32_t dt = 0;
+    if (int32_t rc = rt_float_dtype(dtype, &dt)) return rc;
+    if (!residual || !branch || !output || n == 0) return fail_invalid_program("Fix: pass non-null device pointers and n > 0.");
+    return launch_result(vybk::launch_residual_add(residual, branch, output, n, dt, static_cast<cudaStream_t>(stream)), "residual add");
+}
+int32_t vyb_k_swiglu(const void* gate, const void* up, void* output, uint32_t n, uint32_t dtype, void* stream) {
+    uint32_t dt = 0;
+    if (int32_t rc = rt_float_dtype(dtype, &dt)) return rc;
+    if (!gate || !up || !output || n == 0) return fail_invalid_program("Fix: pass non-null device pointers and n > 0.");
+    return launch_result(vybk::launch_swiglu(gate, up, output, n, dt, static_cast<cudaStream_t>(stream)), "swiglu");
 }
 
 int32_t vyb_k_int4_prefill_gemm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,

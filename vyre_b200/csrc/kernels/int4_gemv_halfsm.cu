@@ -113,7 +113,19 @@ struct Params {
     uint32_t kblocks;
     float* part;            // [kblocks][m][n]
     uint32_t* tile_count;   // [tiles], zero between launches (the last arriver resets its word)
+    // the residual block around the projection (FUSED instantiations; the k-block form honours `resid` as well): a learned
+    // RMSNorm of the activations in the prologue and a residual add in the output stores, with the roundings of the
+    // stand-alone operators (normalised value to bf16, times weight to bf16; sum to bf16, plus residual to bf16)
+    const uint16_t* norm_w;  // [k] bf16 (nullptr: no norm)
+    float norm_eps;
+    const uint16_t* resid;   // [m][n] bf16 (nullptr: no residual add)
 };
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
+// cast(bf16, f32(residual) + f32(branch)) with the branch already rounded to bf16 (vyre-libs/src/nn/activation/residual_add.rs:40-52)
+__device__ __forceinline__ __nv_bfloat16 add_residual(const uint16_t* resid, size_t at, float sum) {
+    return __float2bfloat16_rn(__fadd_rn(bf16_bits_to_float(__ldcg(resid + at)), __bfloat162float(__float2bfloat16_rn(sum))));
+}
 
 // k split inside one launch: count this CTA's arrival for the tiles [tile0, tile0 + count); where it is the last of the
 // k blocks to arrive, sum the partial rows in block order (deterministic) and store the outputs. Out of line.
@@ -147,8 +159,9 @@ __device__ __noinline__ void ksplit_finish(const Params& p, uint32_t tile0, uint
 #pragma unroll
         for (uint32_t b = 0; b < 16; ++b) sum += v[b];
         for (uint32_t b = 16; b < p.kblocks; ++b) sum += __ldcg(src + b * stride);
-        if (OUT_F32) static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
-        else static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
+        const size_t at = size_t(col) * p.n + row;
+        if (OUT_F32) static_cast<float*>(p.y)[at] = sum;
+        else static_cast<__nv_bfloat16*>(p.y)[at] = p.resid ? add_residual(p.resid, at, sum) : __float2bfloat16_rn(sum);
     }
     __syncthreads();
 }
@@ -192,7 +205,7 @@ __device__ __noinline__ void gather_carry(const Params& p, uint32_t r0, uint32_t
 // the next launch's activations wait for exactly that. So launch d stores into the LOCAL buffer only and leaves its slice
 // to launch d + 1, whose CTAs copy their own rows of it to the peers right after the dependency wait (gather_carry). The
 // arrival signal for slice d is then sent by launch d + 2, or by the wait kernel, which also carries the last slice over.
-template <int NM, int GPW, int W, bool OUT_F32, bool GATHER, bool STRIDED = false>
+template <int NM, int GPW, int W, bool OUT_F32, bool GATHER, bool STRIDED = false, bool FUSED = false>
 __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) uint8_t smem[];
     // let the next launch of the stream become resident beside this one at once; it waits (griddepcontrol.wait)
@@ -298,6 +311,40 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
         if (blockIdx.x == 0 && warp == 0) send_owed_signal(p.ag, lane);  // the previous launch's arrival
         if (p.pipelined) gather_carry(p, r0, nrows);
     }
+    // FUSED with a norm weight: 1 / sqrt(mean(x^2) + eps) of every batch row, the sum of squares in the order of the
+    // stand-alone operator's long-row form (thread t adds elements t, t + 256, ...; a butterfly over the warp; the eight
+    // warp sums in warp order), so that the fused launch gives the bits of norm-then-projection
+    float inv_rms[2 * NM];
+    if constexpr (FUSED) {
+        static_assert(W == 8 && !GATHER && !STRIDED && !OUT_F32, "the fused block is the dense bf16 form of 256 threads");
+        __shared__ float warp_sq[2 * NM][W];
+#pragma unroll
+        for (int j = 0; j < 2 * NM; ++j) inv_rms[j] = 0.0f;
+        if (p.norm_w) {
+#pragma unroll
+            for (int j = 0; j < 2 * NM; ++j) {
+                if (uint32_t(j) >= p.m) break;
+                const uint16_t* row = p.x + size_t(j) * K;
+                float sum = 0.0f;
+                for (uint32_t c = threadIdx.x; c < K; c += W * 32) {
+                    const float v = bf16_bits_to_float(__ldcg(row + c));
+                    sum = __fadd_rn(sum, __fmul_rn(v, v));
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, o));
+                if (lane == 0) warp_sq[j][warp] = sum;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int j = 0; j < 2 * NM; ++j) {
+                if (uint32_t(j) >= p.m) break;
+                float total = 0.0f;
+#pragma unroll
+                for (int w = 0; w < W; ++w) total = __fadd_rn(total, warp_sq[j][w]);
+                inv_rms[j] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(total, float(K)), p.norm_eps)));
+            }
+        }
+    }
     uint32_t xb[NM][GPW][8];  // [mma][group of this warp][byte block 0 | 1][operand 0 | 1][bytes 0-3 | 4-7]
     float dq[NM][GPW];        // delta / 16 of (batch row of this lane's D columns, group), x 65536 for the high digit pair
     int corr[NM][GPW];        // -128 x (sum of the group's X, low or high 16-bit part) for this lane's D columns: zero point
@@ -326,7 +373,21 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
                 x0 = __ldcg(src);
                 x1 = __ldcg(src + 1);
             }
-            const uint32_t r[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};  // r[i] = elements 2i (low half), 2i+1
+            uint32_t r[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};  // r[i] = elements 2i (low half), 2i+1
+            if constexpr (FUSED) {
+                if (p.norm_w && has) {  // x * inv to bf16, times the weight to bf16: the stand-alone operator's two roundings
+                    const uint4* wsrc = reinterpret_cast<const uint4*>(p.norm_w + warp * (GPW * 128) + lane * 16);
+                    const uint4 g0 = __ldg(wsrc), g1 = __ldg(wsrc + 1);
+                    const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    auto norm1 = [&](float x, float w) -> uint32_t {
+                        const float n = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x, inv_rms[j])));
+                        return uint32_t(__bfloat16_as_ushort(__float2bfloat16_rn(__fmul_rn(n, w))));
+                    };
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                        r[i] = norm1(bf16_lo(r[i]), bf16_lo(gw[i])) | (norm1(bf16_hi(r[i]), bf16_hi(gw[i])) << 16);
+                }
+            }
             // largest magnitude of the group as an integer maximum of |bits| (positive floats order like their bits, and a
             // NaN, which a float maximum would drop, orders above infinity)
             uint32_t amax = 0;
@@ -535,6 +596,9 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
                     for (uint32_t q = q0; q < q1; ++q) reinterpret_cast<__nv_bfloat16*>(p.ag.peer_out[q])[at] = v;
                 } else if constexpr (OUT_F32) {
                     static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
+                } else if constexpr (FUSED) {
+                    const size_t at = size_t(col) * p.n + row;
+                    static_cast<__nv_bfloat16*>(p.y)[at] = p.resid ? add_residual(p.resid, at, sum) : __float2bfloat16_rn(sum);
                 } else {
                     static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
                 }
@@ -729,7 +793,8 @@ bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t gro
 
 cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                                    uint32_t* status, bool constant_weights, const PeerGather* gather, uint32_t half, bool pipelined) {
+                                    uint32_t* status, bool constant_weights, const PeerGather* gather, uint32_t half, bool pipelined,
+                                    const void* norm_w, float norm_eps, const void* resid) {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t de = cudaGetDevice(&dev);
@@ -743,9 +808,14 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
         {int4_gemv_halfsm_kernel<1, 2, 8, false, false>, int4_gemv_halfsm_kernel<1, 2, 8, true, false>, int4_gemv_halfsm_kernel<1, 2, 8, false, true>},
         {int4_gemv_halfsm_kernel<2, 4, 8, false, false>, int4_gemv_halfsm_kernel<2, 4, 8, true, false>, int4_gemv_halfsm_kernel<2, 4, 8, false, true>},
         {int4_gemv_halfsm_kernel<2, 2, 8, false, false>, int4_gemv_halfsm_kernel<2, 2, 8, true, false>, int4_gemv_halfsm_kernel<2, 2, 8, false, true>}};
+    // the residual block (norm in front, residual add behind): batch <= 2, bf16 outputs; [k 4096 | 2048]
+    static const Kernel fused[2] = {int4_gemv_halfsm_kernel<1, 4, 8, false, false, false, true>,
+                                    int4_gemv_halfsm_kernel<1, 2, 8, false, false, false, true>};
+    const bool block = norm_w || resid;
+    if (block && (m > 2 || out_f32 || gather)) return cudaErrorInvalidValue;
     if (!(configured.load(std::memory_order_acquire) & bit)) {
-        for (int i = 0; i < 12; ++i) {
-            const void* f = (const void*)kernels[i / 3][i % 3];
+        for (int i = 0; i < 14; ++i) {
+            const void* f = i < 12 ? (const void*)kernels[i / 3][i % 3] : (const void*)fused[i - 12];
             cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL);
             if (e == cudaSuccess)
                 e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
@@ -753,7 +823,10 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
         }
         configured.fetch_or(bit, std::memory_order_release);
     }
-    Params p;
+    Params p{};
+    p.norm_w = static_cast<const uint16_t*>(norm_w);
+    p.norm_eps = norm_eps;
+    p.resid = static_cast<const uint16_t*>(resid);
     p.x = static_cast<const uint16_t*>(x_bf16);
     p.w = static_cast<const uint8_t*>(w_packed);
     p.scales = static_cast<const uint16_t*>(scale_bf16);
@@ -783,7 +856,7 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = constant_weights ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernels[variant][gather ? 2 : out_f32 ? 1 : 0], p);
+    return cudaLaunchKernelEx(&cfg, block ? fused[k == 4096 ? 0 : 1] : kernels[variant][gather ? 2 : out_f32 ? 1 : 0], p);
 }
 
 // Rows longer than 4096: the k range is cut into blocks of 4096 (and one of 2048), each block is one launch of the k-block
@@ -796,7 +869,9 @@ bool int4_gemv_kblocks_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t gr
 
 cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                      uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                                     bool constant_weights) {
+                                     bool constant_weights, const void* resid, bool* resid_added) {
+    if (resid_added) *resid_added = false;
+    if (resid && out_f32) return cudaErrorInvalidValue;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -874,6 +949,8 @@ cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, c
                 p.kblocks = kblocks;
                 p.part = part;
                 p.tile_count = counts;
+                p.resid = static_cast<const uint16_t*>(resid);  // added where the last arriver rounds the sums
+                if (resid && resid_added) *resid_added = true;
                 const uint64_t units = uint64_t(tiles) * kblocks;
                 uint32_t grid = units < uint64_t(sm_count) ? uint32_t(units) : uint32_t(sm_count);
                 if (grid < kblocks) grid = kblocks;

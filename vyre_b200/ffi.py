@@ -190,6 +190,7 @@ _STATUS_FUNCS = {
     "vyb_nn_expert_mlp": [_S] * 8 + [_U] * 3 + [_PP],
     "vyb_nn_moe_layer_route_and_accumulate": [_S] * 7 + [_U] * 4 + [_PP],
     "vyb_nn_linear_int4_grouped_rowmajor": [_S] * 4 + [_U] * 5 + [_PP],
+    "vyb_nn_linear_int4_block": [_S] * 6 + [_U] * 4 + [C.c_float, _PP],
     "vyb_nn_linear_int8_weight_only": [_S] * 4 + [_U] * 3 + [_PP],
     "vyb_nn_linear_int8_dynamic": [_S] * 4 + [_U] * 3 + [_PP],
     "vyb_nn_moe_ffn_int4": [_S] * 9 + [_U] * 6 + [_PP],
@@ -200,6 +201,7 @@ _STATUS_FUNCS = {
     "vyb_graph_add_node": [_P, _S, _P, C.POINTER(GraphInput), _U, C.POINTER(GraphOutput), _U, C.POINTER(C.c_uint32),
                            C.POINTER(C.c_uint32)],
     "vyb_graph_from_program": [_S, _P, _PP],
+    "vyb_graph_fuse_linear_blocks": [_P, _PP, C.POINTER(C.c_uint32)],
     "vyb_graph_value": [_P, _U, C.POINTER(GraphValueInfo)],
     "vyb_graph_node": [_P, _U, C.POINTER(GraphNodeInfo)],
     "vyb_graph_node_input": [_P, _U, _U, C.POINTER(GraphInput)],
@@ -255,6 +257,10 @@ _STATUS_FUNCS = {
     "vyb_k_colpar_wait": [C.POINTER(AllGatherCtx), _U, _P, _P],
     "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int4_gemv_ex": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_int4_linear_block": [_P, _P, C.c_float, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_rms_norm": [_P, _P, _P, _U, _U, C.c_float, _U, _P],
+    "vyb_k_residual_add": [_P, _P, _P, _U, _U, _P],
+    "vyb_k_swiglu": [_P, _P, _P, _U, _U, _P],
     "vyb_k_int8_weight_only_linear": [_P, _P, _P, _P, _U, _U, _U, _P],
     "vyb_k_int4_prefill_gemm": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_quantize_per_token_int8": [_P, _P, _P, _U, _U, _P],
