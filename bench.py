@@ -456,7 +456,8 @@ def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter
     """The decode residual block (vyre-libs/src/nn/model/dense_gated_mlp.rs:168-370 over int4 projections): RMSNorm, gate /
     up projections, SwiGLU, down projection, residual add, `layers` blocks in a row with weights of their own (together
     larger than L2), one CUDA graph. Timed twice: every operator its own launch (six per block), and with the norm in the
-    gate / up launches and the residual add in the down launch (four per block). Both must give the same bits."""
+    gate / up launches, SwiGLU in the up launch's stores and the residual add in the down launch's (three per block, one
+    programmatic chain). Both must give the same bits."""
     import numpy as np
     import torch
 
@@ -486,10 +487,10 @@ def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter
     def gemv(x, ws, y, n, k):
         ffi.check(L.vyb_k_int4_gemv_ex(x.data_ptr(), ws[0].data_ptr(), ws[1].data_ptr(), y.data_ptr(), rows, n, k, GROUP, bf16, flags, sp, st))
 
-    def block(x, ws, y, n, k, nw=None, res=None):
-        ffi.check(L.vyb_k_int4_linear_block(x.data_ptr(), nw.data_ptr() if nw is not None else None, eps, ws[0].data_ptr(),
-                                            ws[1].data_ptr(), res.data_ptr() if res is not None else None, y.data_ptr(), rows, n, k,
-                                            GROUP, flags, sp, st))
+    def block(x, ws, y, n, k, nw=None, res=None, gate_in=None):
+        opt = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+        ffi.check(L.vyb_k_int4_linear_block(x.data_ptr(), opt(nw), eps, ws[0].data_ptr(), ws[1].data_ptr(), opt(gate_in), opt(res),
+                                            y.data_ptr(), rows, n, k, GROUP, flags, sp, st))
 
     def separate():
         for i, w in enumerate(weights):
@@ -504,13 +505,18 @@ def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter
     def fused():
         for i, w in enumerate(weights):
             h, out = stream_h[i], stream_h[i + 1]
-            block(h, w["gate"], gate, inter, hidden, nw=w["nw"])
-            block(h, w["up"], up, inter, hidden, nw=w["nw"])
-            ffi.check(L.vyb_k_swiglu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), rows * inter, bf16, sp))
+            if rows <= 2:
+                block(h, w["gate"], gate, inter, hidden, nw=w["nw"])
+                block(h, w["up"], act, inter, hidden, nw=w["nw"], gate_in=gate)
+            else:  # three and four rows run gate / up on the f16 tensor path, which takes neither norm nor SwiGLU
+                ffi.check(L.vyb_k_rms_norm(h.data_ptr(), w["nw"].data_ptr(), normed.data_ptr(), rows, hidden, eps, bf16, sp))
+                gemv(normed, w["gate"], gate, inter, hidden)
+                gemv(normed, w["up"], up, inter, hidden)
+                ffi.check(L.vyb_k_swiglu(gate.data_ptr(), up.data_ptr(), act.data_ptr(), rows * inter, bf16, sp))
             block(act, w["down"], out, hidden, inter, res=h)
 
     results, finals = {}, []
-    for name, body, launches in (("separate_launches", separate, 6), ("fused_launches", fused, 4)):
+    for name, body, launches in (("separate_launches", separate, 6), ("fused_launches", fused, 3 if rows <= 2 else 5)):
         stream_h[0].copy_(x0)
         with torch.cuda.stream(side):
             body()  # first launches configure the kernels and make the long-row workspace; must precede capture
@@ -525,14 +531,14 @@ def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter
     assert status.cpu().tolist() == [0, 0, 0, 0]
     assert torch.equal(finals[0], finals[1]), "the fused block's output differs from the separate operators'"
     wbytes = 3 * (hidden * inter // 2 + hidden * inter // GROUP * 2)
-    abytes = wbytes + rows * (4 * hidden + 3 * inter) * 2 + hidden * 2  # weights and scales; residual in / out, norm weight, gate / up / act
+    abytes = wbytes + rows * (4 * hidden + 4 * inter) * 2 + 2 * hidden * 2  # weights, scales; residual (read 3x, written once), norm weight 2x, gate / up written and read
     gbs = abytes / (results["fused_launches"]["us_per_block"] * 1e-6) / 1e9
     return {"case": f"residual block rows={rows} hidden={hidden} inter={inter}, {layers} blocks per graph ({layers * wbytes >> 20} MiB of weights)",
             **results, "same_bits": True,
             "speedup": round(results["separate_launches"]["us_per_block"] / results["fused_launches"]["us_per_block"], 3),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / peaks["hbm_gbs"], 4), "algorithmic_bytes_per_block": abytes,
-                         "kernel": "int4_gemv_halfsm_kernel (fused and k-block forms) + swiglu_kernel"}}
+                         "kernel": "int4_gemv_halfsm_kernel (fused whole-row and k-block forms)"}}
 
 
 def metric_stats(samples) -> dict:

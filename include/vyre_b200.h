@@ -330,16 +330,18 @@ int32_t vyb_nn_moe_layer_route_and_accumulate(const char* x, const char* w_route
 int32_t vyb_nn_linear_int4_grouped_rowmajor(const char* x, const char* w_packed, const char* scale, const char* out,
                                             uint32_t batch, uint32_t in_dim, uint32_t out_dim, uint32_t group_size,
                                             uint32_t out_dtype, vyb_program** program);
-/* The same projection with its neighbours in the residual block taken into the node (dense_gated_mlp.rs:168-200: `mlp.norm`
- * in front of gate_proj / up_proj, `mlp.residual` behind down_proj): a learned RMSNorm of x (bf16 weight [in_dim],
- * gated_rms_norm.rs:35-247 without gate) when `norm_weight` is named, a residual add (residual_add.rs:8-52; residual bf16
- * [batch, out_dim]) when `residual` is named; at least one of the two. bf16 throughout; every intermediate is rounded as
- * the stand-alone operators round it, so the node's values are those of the operators run in sequence. Slots in order: x,
- * [norm_weight], w, scale, [residual], out. For one or two batch rows of 2048 / 4096 elements the decode GEMV does all of
- * it in one launch (kernel variant 9), for longer rows the residual add joins the launch; other shapes run the stand-alone
- * kernels inside the node. No reference builder: the reference fuses neighbouring nodes in its megakernel scheduler. op id
+/* The same projection with its neighbours in the residual block taken into the node (dense_gated_mlp.rs:168-370: `mlp.norm`
+ * in front of gate_proj / up_proj, `mlp.swiglu` behind up_proj, `mlp.residual` behind down_proj): a learned RMSNorm of x
+ * (bf16 weight [in_dim], gated_rms_norm.rs:35-247 without gate) when `norm_weight` is named; behind the projection either
+ * SwiGLU(gate, projection) (swiglu.rs:51-79; gate bf16 [batch, out_dim], the gate projection's output) when `gate` is
+ * named, or a residual add (residual_add.rs:8-52; residual bf16 [batch, out_dim]) when `residual` is named - not both; at
+ * least one part. bf16 throughout; every intermediate is rounded as the stand-alone operators round it, so the node's
+ * values are those of the operators run in sequence. Slots in order: x, [norm_weight], w, scale, [gate | residual], out.
+ * For one or two batch rows of 2048 / 4096 elements the decode GEMV does all of it in one launch (kernel variant 9); for
+ * longer rows (up to four batch rows) SwiGLU / the residual add join the launch; other shapes run the stand-alone kernels
+ * inside the node. No reference builder: the reference fuses neighbouring nodes in its megakernel scheduler. op id
  * "vyre-b200::nn::linear_int4_block". */
-int32_t vyb_nn_linear_int4_block(const char* x, const char* norm_weight, const char* w_packed, const char* scale,
+int32_t vyb_nn_linear_int4_block(const char* x, const char* norm_weight, const char* w_packed, const char* scale, const char* gate,
                                  const char* residual, const char* out, uint32_t batch, uint32_t in_dim, uint32_t out_dim,
                                  uint32_t group_size, float norm_eps, vyb_program** program);
 /* int8 weight-only linear: W int8 [out_dim, in_dim], per-output-channel f32 scale, x/out f32;
@@ -470,11 +472,12 @@ int32_t vyb_graph_node(const vyb_graph* g, uint32_t id, vyb_graph_node_info* out
 int32_t vyb_graph_node_input(const vyb_graph* g, uint32_t node, uint32_t index, vyb_graph_input* out);
 int32_t vyb_graph_node_output(const vyb_graph* g, uint32_t node, uint32_t index, vyb_graph_output* out, uint32_t* value_id);
 void vyb_graph_digest(const vyb_graph* g, uint8_t out[32]);
-/* A copy of the graph in which bf16 learned-RMSNorm nodes that feed only int4 row-major linears, and bf16 residual adds
- * behind such a linear, are taken into vyb_nn_linear_int4_block nodes wherever the decode kernel does the part in its own
- * launch; all other nodes, names, contracts and the order are kept, the values are unchanged. `n_fused` (nullable): how
- * many nodes were taken in. The reference's counterpart is the fusion step of its megakernel scheduler
- * (vyre-megakernel: schedule search over fusion groups), which is not rebuilt; this pass knows these two patterns only. */
+/* A copy of the graph in which bf16 learned-RMSNorm nodes that feed only int4 row-major linears, a bf16 SwiGLU whose `up`
+ * comes from such a linear, and a bf16 residual add whose `branch` does, are taken into vyb_nn_linear_int4_block nodes
+ * wherever the decode kernel does the part in its own launch; all other nodes, names, contracts and the order are kept,
+ * the values are unchanged. `n_fused` (nullable): how many nodes were taken in. The reference's counterpart is the fusion
+ * step of its megakernel scheduler (vyre-megakernel: schedule search over fusion groups), which is not rebuilt; this pass
+ * knows these three patterns only. */
 int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint32_t* n_fused);
 
 /* ---- safetensors ingestion (vyre-safetensors/src/lib.rs:108-260, 871-907: SafetensorIndex::open) ---------------------
@@ -679,14 +682,15 @@ int32_t vyb_k_int4_gemv_ex(const void* x_bf16, const void* w_packed, const void*
                            uint32_t n, uint32_t k, uint32_t group_size, uint32_t out_dtype, uint32_t flags,
                            void* stream, uint32_t* status);
 /* The decode projection with its neighbours of the residual block in the same launch (the kernel behind
- * vyb_nn_linear_int4_block, kernel variant 9): y = [residual +] W [rmsnorm(x) * norm_weight], bf16 throughout, rounded
- * where the stand-alone operators round. norm_weight_bf16 [k] and residual_bf16 [m, n] are nullable, not both. Shapes:
- * group 128 and either m <= 2 with k 2048 / 4096 (both parts), or the residual alone with m <= 4 and k a larger multiple
- * of 2048 (added where the last k block rounds the sums; under a first-use stream capture a separate add kernel follows).
- * flags as for vyb_k_int4_gemv_ex. Other shapes: UnsupportedFeature. */
+ * vyb_nn_linear_int4_block, kernel variant 9): y = f(W a) with a = rmsnorm(x) * norm_weight or a = x, and f = SwiGLU(gate, .)
+ * or f = residual + . or the identity; bf16 throughout, rounded where the stand-alone operators round. norm_weight_bf16
+ * [k], gate_bf16 [m, n] and residual_bf16 [m, n] are nullable (at least one given, not gate and residual together).
+ * Shapes: group 128 and either m <= 2 with k 2048 / 4096 (every part), or no norm with m <= 4 and k a larger multiple of
+ * 2048 (SwiGLU / the residual where the last k block rounds the sums; on a stream that captures before its first plain use
+ * of the shape, a kernel of its own follows instead). flags as for vyb_k_int4_gemv_ex. Other shapes: UnsupportedFeature. */
 int32_t vyb_k_int4_linear_block(const void* x_bf16, const void* norm_weight_bf16, float norm_eps, const void* w_packed,
-                                const void* scale_bf16, const void* residual_bf16, void* y_bf16, uint32_t m, uint32_t n, uint32_t k,
-                                uint32_t group_size, uint32_t flags, void* stream, uint32_t* status);
+                                const void* scale_bf16, const void* gate_bf16, const void* residual_bf16, void* y_bf16, uint32_t m,
+                                uint32_t n, uint32_t k, uint32_t group_size, uint32_t flags, void* stream, uint32_t* status);
 /* The stand-alone neighbours on raw device pointers (the kernels behind vyb_nn_learned_rms_norm, vyb_nn_residual_add_typed
  * and vyb_nn_swiglu_typed); dtype F16, BF16 or F32. The norm uses the long-row form from 2048 elements on. */
 int32_t vyb_k_rms_norm(const void* input, const void* weight, void* output, uint32_t rows, uint32_t hidden, float eps,

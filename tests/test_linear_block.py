@@ -20,8 +20,13 @@ def test_builder_slots_and_errors():
         ["x", "w", "s", "res", "out"]
     assert [b["name"] for b in vb.linear_int4_block("x", "nw", "w", "s", None, "out", 1, 4096, 64, 128, 1e-5).buffers()] == \
         ["x", "nw", "w", "s", "out"]
-    with pytest.raises(vb.BackendError, match="needs a norm weight, a residual, or both"):
+    assert [(b["name"], b["binding"], b["count"]) for b in
+            vb.linear_int4_block("x", "nw", "w", "s", None, "out", 2, 4096, 64, 128, 1e-6, gate="g").buffers()] == \
+        [("x", 0, 8192), ("nw", 1, 4096), ("w", 2, 64 * 512), ("s", 3, 64 * 32), ("g", 4, 128), ("out", 5, 128)]
+    with pytest.raises(vb.BackendError, match="needs a norm weight, a gate, a residual, or a norm weight with one of the two"):
         vb.linear_int4_block("x", None, "w", "s", None, "out", 1, 4096, 64, 128)
+    with pytest.raises(vb.BackendError, match="a gate or a residual behind the projection, not both"):
+        vb.linear_int4_block("x", "nw", "w", "s", "res", "out", 1, 4096, 64, 128, 1e-6, gate="g")
     with pytest.raises(vb.BackendError, match="requires nonzero batch, in_dim, out_dim and group_size; got batch=0"):
         vb.linear_int4_block("x", "nw", "w", "s", None, "out", 0, 4096, 64, 128)
     with pytest.raises(vb.BackendError, match="in_dim=100 is not divisible by 8"):
@@ -38,7 +43,9 @@ def test_builder_slots_and_errors():
 
 
 @pytest.mark.parametrize("batch,k,norm,resid,want", [
-    (1, 4096, True, True, 9), (2, 2048, True, False, 9), (2, 4096, False, True, 9),
+    (1, 4096, True, True, 9), (2, 2048, True, False, 9), (2, 4096, False, True, 9), (2, 4096, "swiglu", False, 9),
+    (4, 14336, "swiglu", False, 9), (1, 4096, "norm+swiglu", False, 9), (1, 14336, "norm+swiglu", False, 9),
+    (5, 14336, "swiglu", False, 1), (3, 4096, "swiglu", False, 1),
     (3, 4096, True, True, 1),       # three rows take the f16 tensor path: the parts run as their own kernels
     (1, 14336, False, True, 9),     # long rows: the residual add joins the k-block launch ...
     (4, 8192, False, True, 9),
@@ -51,7 +58,8 @@ def test_builder_slots_and_errors():
 ])
 def test_target_compiler_names_the_fused_kernel_only_where_it_exists(batch, k, norm, resid, want):
     group = 128 if k % 128 == 0 else 32
-    p = vb.linear_int4_block("x", "nw" if norm else None, "w", "s", "res" if resid else None, "out", batch, k, 256, group, 1e-6)
+    p = vb.linear_int4_block("x", "nw" if norm in (True, "norm+swiglu") else None, "w", "s", "res" if resid else None, "out", batch,
+                             k, 256, group, 1e-6, gate="g" if str(norm).endswith("swiglu") else None)
     assert variant(p) == want
     bare = vb.linear_int4_grouped_rowmajor("x", "w", "s", "out", batch, k, 256, group)
     if want != 9:
@@ -67,18 +75,19 @@ def names(graph):
 def test_graph_pass_takes_norm_and_residual_into_the_projections():
     g = vb.quantized_gated_mlp_graph(vb.QuantizedGatedMlpSpec(1, 4096, 14336, 128, norm_eps=1e-6))
     f, taken = g.fuse_linear_blocks()
-    assert taken == 2 and len(f.nodes()) == 4
+    assert taken == 3 and len(f.nodes()) == 3
     got = names(f)
     assert got[0] == ("mlp.gate_proj", "linear_int4_block",
                       {"input": "residual", "weight": "mlp.gate_proj.qweight", "scale": "mlp.gate_proj.scales",
                        "norm_weight": "post_attention_layernorm.weight"}, ["mlp.gate"])
-    assert got[1][0:2] == ("mlp.up_proj", "linear_int4_block") and got[1][2]["input"] == "residual"
-    assert got[2] == ("mlp.swiglu", "swiglu", {"gate": "mlp.gate", "up": "mlp.up"}, ["mlp.activated"])
-    assert got[3] == ("mlp.down_proj", "linear_int4_block",
+    assert got[1] == ("mlp.up_proj", "linear_int4_block",
+                      {"input": "residual", "weight": "mlp.up_proj.qweight", "scale": "mlp.up_proj.scales",
+                       "norm_weight": "post_attention_layernorm.weight", "gate": "mlp.gate"}, ["mlp.activated"])
+    assert got[2] == ("mlp.down_proj", "linear_int4_block",
                       {"input": "mlp.activated", "weight": "mlp.down_proj.qweight", "scale": "mlp.down_proj.scales",
                        "residual": "residual"}, ["mlp.block_output"])
     vals = {v["name"]: v for v in f.values()}
-    assert "mlp.normalized" not in vals and "mlp.down" not in vals
+    assert not {"mlp.normalized", "mlp.up", "mlp.down"} & set(vals)
     assert vals["mlp.block_output"]["contract"]["lifetime"] == ffi.LIFETIME_OUTPUT
     assert vals["residual"]["consumers"] == 3
     assert f.digest() != g.digest()
@@ -89,14 +98,17 @@ def test_graph_pass_takes_norm_and_residual_into_the_projections():
 
 
 def test_graph_pass_leaves_what_the_kernel_does_not_take():
-    # four rows: the gate / up projections run on the f16 tensor path (norm stays a node), the long-row down projection
-    # still takes the residual add
+    # four rows: the gate / up projections run on the f16 tensor path (norm and SwiGLU stay nodes), the long-row down
+    # projection still takes the residual add
     f, taken = vb.quantized_gated_mlp_graph(vb.QuantizedGatedMlpSpec(4, 4096, 14336, 128, norm_eps=1e-6)).fuse_linear_blocks()
     assert taken == 1
     assert [n[1] for n in names(f)] == ["learned_rms_norm", "linear_int4_grouped_rowmajor", "linear_int4_grouped_rowmajor",
                                         "swiglu", "linear_int4_block"]
+    # without the norm and the residual add around them, the up projection still takes SwiGLU
+    f, taken = vb.quantized_gated_mlp_graph(vb.QuantizedGatedMlpSpec(1, 4096, 14336, 128)).fuse_linear_blocks()
+    assert taken == 1 and names(f)[1][2]["gate"] == "mlp.gate" and names(f)[1][3] == ["mlp.activated"]
     # prefill rows, and a graph without the two neighbours: unchanged
-    for spec in (vb.QuantizedGatedMlpSpec(64, 4096, 8192, 128, norm_eps=1e-6), vb.QuantizedGatedMlpSpec(1, 4096, 14336, 128)):
+    for spec in (vb.QuantizedGatedMlpSpec(64, 4096, 8192, 128, norm_eps=1e-6), vb.QuantizedGatedMlpSpec(8, 4096, 14336, 128)):
         g = vb.quantized_gated_mlp_graph(spec)
         f, taken = g.fuse_linear_blocks()
         assert taken == 0 and f.digest() == g.digest()

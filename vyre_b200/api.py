@@ -282,11 +282,12 @@ def linear_int4_grouped_rowmajor(x, w_packed, scale, out, batch, in_dim, out_dim
                   out_dtype)
 
 
-def linear_int4_block(x, norm_weight, w_packed, scale, residual, out, batch, in_dim, out_dim, group_size, norm_eps=0.0):
-    """The int4 row-major projection as one node with a learned RMSNorm in front (`norm_weight` named) and / or a residual
-    add behind (`residual` named); pass None for the part that is absent."""
-    return _build("vyb_nn_linear_int4_block", x, None if norm_weight is None else _b(norm_weight), w_packed, scale,
-                  None if residual is None else _b(residual), out, batch, in_dim, out_dim, group_size, C.c_float(norm_eps))
+def linear_int4_block(x, norm_weight, w_packed, scale, residual, out, batch, in_dim, out_dim, group_size, norm_eps=0.0, gate=None):
+    """The int4 row-major projection as one node with a learned RMSNorm in front (`norm_weight` named) and, behind it,
+    SwiGLU(gate, projection) (`gate` named) or a residual add (`residual` named); pass None for the parts that are absent."""
+    opt = lambda name: None if name is None else _b(name)  # noqa: E731
+    return _build("vyb_nn_linear_int4_block", x, opt(norm_weight), w_packed, scale, opt(gate), opt(residual), out, batch, in_dim,
+                  out_dim, group_size, C.c_float(norm_eps))
 
 
 def linear_int8_weight_only(x, w, scale, out, batch, in_dim, out_dim):

@@ -93,7 +93,7 @@ uint32_t select_kernel_variant(const Program& p) {
             // the stand-alone kernels one after the other inside the node
             const uint32_t batch = p.params.u[0], in_dim = p.params.u[1], group = p.params.u[3], parts = p.params.u[5];
             const bool whole_rows = in_dim == 2048 || in_dim == 4096;
-            const bool k_blocks = in_dim > 4096 && in_dim % 2048 == 0 && (parts & 2u);  // only the residual add joins that form
+            const bool k_blocks = in_dim > 4096 && in_dim % 2048 == 0 && (parts & 6u);  // the residual add or SwiGLU joins that form, a norm does not
             if (group == 128 && ((whole_rows && batch <= 2) || (k_blocks && batch <= 4))) return KV_INT4_BLOCK_GEMV;
             Program bare = p;
             bare.kind = OpKind::LinearInt4GroupedRowmajor;

@@ -322,6 +322,8 @@ int32_t vyb_graph_node_output(const vyb_graph* g, uint32_t node, uint32_t index,
 // and up_proj, `mlp.residual` follows down_proj): a copy of the graph in which
 //   * a bf16 learned RMSNorm node whose output is read only as the activation of int4 row-major linears (bf16 outputs) is
 //     dropped, and each of those linears becomes a linear_int4_block node that reads the norm's input and weight itself;
+//   * a bf16 SwiGLU node whose `up` is produced by such a linear, and read by nothing else, is dropped, and the linear becomes
+//     (or stays) a linear_int4_block node that reads the gate and produces the SwiGLU's output value;
 //   * a bf16 residual add whose `branch` is produced by such a linear, and read by nothing else, is dropped, and the linear
 //     becomes (or stays) a linear_int4_block node that reads the residual and produces the add's output value.
 // Every other node and value is carried over with its name, contract and order. Values of the fused graph equal those of
@@ -334,7 +336,7 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
             n.outputs.size() != 1)
             return false;
         for (const BufferDecl& b : n.program.p.buffers)
-            if (b.name == "norm_weight" || b.name == "residual") return false;  // the names of the block node's added ports
+            if (b.name == "norm_weight" || b.name == "residual" || b.name == "gate") return false;  // the block node's added ports
         return true;
     };
     // only where the decode kernel takes the part into its own launch (the target compiler's rule for the block node)
@@ -351,6 +353,7 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
     };
     struct Plan {
         int64_t norm = -1;   // linear: the norm node taken into its prologue
+        int64_t gate = -1;   // linear: the SwiGLU node taken into its stores
         int64_t resid = -1;  // linear: the residual-add node taken into its stores
         bool dropped = false;
     };
@@ -373,6 +376,24 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
                 for (uint32_t c : out.consumers) plan[c].norm = int64_t(i);
             }
         }
+        if (np.kind == OpKind::Swiglu && np.params.u[1] == VYB_DT_BF16 && n.inputs.size() == 2 && n.outputs.size() == 1) {
+            // buffers: gate, up, output (swiglu.rs:51-79)
+            const int64_t gate = port_value(n, np.buffers[0].name), up = port_value(n, np.buffers[1].name);
+            if (gate >= 0 && up >= 0) {
+                const Value& uv = g->values[size_t(up)];
+                const Value& gv = g->values[size_t(gate)];
+                if (uv.producer >= 0 && uv.consumers.size() == 1 && uv.contract.lifetime == VYB_LIFETIME_INVOCATION &&
+                    gv.producer < uv.producer) {  // the gate exists when the up projection runs
+                    const size_t li = size_t(uv.producer);
+                    const Node& lin = g->nodes[li];
+                    if (is_linear(lin) && kernel_takes(lin, 4u) && plan[li].gate < 0 && plan[li].resid < 0 &&
+                        uint64_t(lin.program.p.params.u[0]) * lin.program.p.params.u[2] == np.params.u[0]) {
+                        plan[i].dropped = true;
+                        plan[li].gate = int64_t(i);
+                    }
+                }
+            }
+        }
         if (np.kind == OpKind::ResidualAdd && np.params.u[1] == VYB_DT_BF16 && n.inputs.size() == 2 && n.outputs.size() == 1) {
             // buffers: residual, branch, output (residual_add.rs:8-52)
             const int64_t branch = port_value(n, np.buffers[1].name), residual = port_value(n, np.buffers[0].name);
@@ -380,7 +401,8 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
             const Value& bv = g->values[size_t(branch)];
             if (bv.producer < 0 || bv.consumers.size() != 1 || bv.contract.lifetime != VYB_LIFETIME_INVOCATION) continue;
             const Node& lin = g->nodes[size_t(bv.producer)];
-            if (!is_linear(lin) || !kernel_takes(lin, 2u) || plan[size_t(bv.producer)].resid >= 0) continue;
+            if (!is_linear(lin) || !kernel_takes(lin, 2u) || plan[size_t(bv.producer)].resid >= 0 || plan[size_t(bv.producer)].gate >= 0)
+                continue;
             if (uint64_t(lin.program.p.params.u[0]) * lin.program.p.params.u[2] != np.params.u[0]) continue;
             // the residual must exist when the linear runs
             const Value& rv = g->values[size_t(residual)];
@@ -406,14 +428,16 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
         std::vector<Output> outs = n.outputs;
         vyb_program* built = nullptr;
         const vyb_program* program = &n.program;
-        if (plan[i].norm >= 0 || plan[i].resid >= 0) {
+        if (plan[i].norm >= 0 || plan[i].resid >= 0 || plan[i].gate >= 0) {
             const Program& lp = n.program.p;
+            const Node* swi = plan[i].gate >= 0 ? &g->nodes[size_t(plan[i].gate)] : nullptr;
             const Node* norm = plan[i].norm >= 0 ? &g->nodes[size_t(plan[i].norm)] : nullptr;
             const Node* add = plan[i].resid >= 0 ? &g->nodes[size_t(plan[i].resid)] : nullptr;
             float eps = 0.0f;
             if (norm) std::memcpy(&eps, &norm->program.p.params.u[2], 4);
             if (int32_t rc = vyb_nn_linear_int4_block(lp.buffers[0].name.c_str(), norm ? "norm_weight" : nullptr, lp.buffers[1].name.c_str(),
-                                                      lp.buffers[2].name.c_str(), add ? "residual" : nullptr, lp.buffers[3].name.c_str(),
+                                                      lp.buffers[2].name.c_str(), swi ? "gate" : nullptr, add ? "residual" : nullptr,
+                                                      lp.buffers[3].name.c_str(),
                                                       lp.params.u[0], lp.params.u[1], lp.params.u[2], lp.params.u[3], eps, &built))
                 return rc;
             program = built;
@@ -433,6 +457,19 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
                         w.buffer = "norm_weight";
                         ins.push_back(w);
                     }
+            }
+            if (swi) {
+                // the gate becomes a port of this node, which now produces the SwiGLU's output value
+                const Program& sp = swi->program.p;
+                for (const Input& si : swi->inputs)
+                    if (si.buffer == sp.buffers[0].name) {
+                        Input gi = si;
+                        gi.buffer = "gate";
+                        ins.push_back(gi);
+                    }
+                outs[0].name = swi->outputs[0].name;
+                outs[0].contract = swi->outputs[0].contract;
+                outs[0].retained_successor_of = -1;
             }
             if (add) {
                 const Program& ap = add->program.p;
@@ -468,6 +505,7 @@ int32_t vyb_graph_fuse_linear_blocks(const vyb_graph* g, vyb_graph** fused, uint
         // the values this node produced in the original graph (and, with the add taken in, the add's output) map to the new ones
         for (size_t k = 0; k < n.outputs.size(); ++k) remap[n.outputs[k].value] = ids[k];
         if (plan[i].resid >= 0) remap[g->nodes[size_t(plan[i].resid)].outputs[0].value] = ids[0];
+        if (plan[i].gate >= 0) remap[g->nodes[size_t(plan[i].gate)].outputs[0].value] = ids[0];
         return VYB_OK;
     };
     for (size_t v = 0; v < g->values.size(); ++v) {

@@ -1089,14 +1089,18 @@ int32_t vyb_nn_linear_int4_grouped_rowmajor(const char* x, const char* w_packed,
 
 // The projection of a residual block as ONE node: learned RMSNorm (dense_gated_mlp.rs:168-200 `mlp.norm`, bf16) in front
 // when `norm_weight` is named, residual add (`mlp.residual`) behind when `residual` is named. Values are those of the three
-// operators run one after the other (every intermediate rounded to bf16 as the stand-alone operators round it).
-int32_t vyb_nn_linear_int4_block(const char* x, const char* norm_weight, const char* w_packed, const char* scale,
+// operators run one after the other (every intermediate rounded to bf16 as the stand-alone operators round it). With `gate`
+// named instead of `residual`, the output is SwiGLU(gate, projection) (`mlp.swiglu` behind up_proj, gate = gate_proj's output).
+int32_t vyb_nn_linear_int4_block(const char* x, const char* norm_weight, const char* w_packed, const char* scale, const char* gate,
                                  const char* residual, const char* out, uint32_t batch, uint32_t in_dim, uint32_t out_dim,
                                  uint32_t group_size, float norm_eps, vyb_program** program) {
     VYB_REQUIRE_NAMES(x, w_packed, scale, out);
-    if (!norm_weight && !residual)
+    if (!norm_weight && !residual && !gate)
         return fail_invalid_program(
-            "Fix: linear_int4_block needs a norm weight, a residual, or both; use linear_int4_grouped_rowmajor for the bare projection.");
+            "Fix: linear_int4_block needs a norm weight, a gate, a residual, or a norm weight with one of the two; use "
+            "linear_int4_grouped_rowmajor for the bare projection.");
+    if (gate && residual)
+        return fail_invalid_program("Fix: linear_int4_block takes a gate or a residual behind the projection, not both.");
     if (batch == 0 || in_dim == 0 || out_dim == 0 || group_size == 0)
         return fail_invalid_program("Fix: linear_int4_block requires nonzero batch, in_dim, out_dim and group_size; got batch=" +
                                     std::to_string(batch) + ", in_dim=" + std::to_string(in_dim) + ", out_dim=" +
@@ -1122,13 +1126,14 @@ int32_t vyb_nn_linear_int4_block(const char* x, const char* norm_weight, const c
     p.params.u[2] = out_dim;
     p.params.u[3] = group_size;
     p.params.u[4] = VYB_DT_BF16;
-    p.params.u[5] = (norm_weight ? 1u : 0u) | (residual ? 2u : 0u);
+    p.params.u[5] = (norm_weight ? 1u : 0u) | (residual ? 2u : 0u) | (gate ? 4u : 0u);
     std::memcpy(&p.params.u[6], &norm_eps, 4);
     uint32_t slot = 0;
     p.buffers.push_back(storage(x, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, xc));
     if (norm_weight) p.buffers.push_back(storage(norm_weight, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, in_dim));
     p.buffers.push_back(storage(w_packed, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_U32, wc));
     p.buffers.push_back(storage(scale, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, sc));
+    if (gate) p.buffers.push_back(storage(gate, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, oc));
     if (residual) p.buffers.push_back(storage(residual, slot++, VYB_ACCESS_READ_ONLY, VYB_DT_BF16, oc));
     p.buffers.push_back(output(out, slot++, VYB_DT_BF16, oc));
     return emit(program, std::move(p));

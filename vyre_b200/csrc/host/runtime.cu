@@ -356,7 +356,7 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
                                    u[4] == VYB_DT_F32 ? 1u : 0u, s);
         }
         case OpKind::LinearInt4Block: {
-            // slots: x, [norm weight], packed weights, scales, [residual], out
+            // slots: x, [norm weight], packed weights, scales, [gate | residual], out
             const uint32_t batch = u[0], k = u[1], n = u[2], group = u[3], parts = u[5];
             float eps;
             std::memcpy(&eps, &u[6], 4);
@@ -365,31 +365,33 @@ cudaError_t dispatch(vyb_instance* inst, void* const* b, cudaStream_t s) {
             const void* norm_w = (parts & 1u) ? b[slot++] : nullptr;
             const void* w = b[slot++];
             const void* scale = b[slot++];
+            const void* gate = (parts & 4u) ? b[slot++] : nullptr;
             const void* resid = (parts & 2u) ? b[slot++] : nullptr;
             void* y = b[slot];
             const int sms = inst->dev->prop.multiProcessorCount;
             const bool gemv = inst->variant == KV_INT4_BLOCK_GEMV;
-            // whole rows of 2048 / 4096, one or two batch rows: norm, projection and residual add are ONE launch
+            // whole rows of 2048 / 4096, one or two batch rows: norm, projection and SwiGLU / residual add are ONE launch
             if (gemv && batch <= 2 && int4_gemv_halfsm_supported(batch, n, k, group))
                 return launch_int4_gemv_halfsm(x, w, scale, y, batch, n, k, 0, sms, s, inst->status_dev, false, nullptr, 0, false,
-                                               norm_w, eps, resid);
+                                               norm_w, eps, resid, gate);
             // otherwise the stand-alone kernels in sequence: the norm into scratch (the tree form from 2048 elements on, as
-            // the stand-alone operator chooses), the projection, the residual add in place
+            // the stand-alone operator chooses), the projection, SwiGLU / the residual add in place
             if (norm_w) {
                 cudaError_t e = launch_rms_norm(x, norm_w, nullptr, inst->scratch, batch, k, eps, 1, 1, k >= 2048, s);
                 if (e != cudaSuccess) return e;
                 x = inst->scratch;
             }
-            if (gemv && resid && int4_gemv_kblocks_supported(batch, n, k, group)) {
-                // long rows: the residual is added where the last-arriving k block rounds the sums
-                bool added = false;
-                cudaError_t e = launch_int4_gemv_kblocks(x, w, scale, y, batch, n, k, 0, sms, s, false, resid, &added);
-                if (e != cudaSuccess || added) return e;
+            if (gemv && int4_gemv_kblocks_supported(batch, n, k, group)) {
+                // long rows: SwiGLU / the residual add where the last-arriving k block rounds the sums
+                bool fused = false;
+                cudaError_t e = launch_int4_gemv_kblocks(x, w, scale, y, batch, n, k, 0, sms, s, false, resid, gate, &fused);
+                if (e != cudaSuccess || fused) return e;
             } else {
                 cudaError_t e = run_int4_linear(inst, gemv ? uint32_t(KV_INT4_GEMV_TMA) : inst->variant, x, w, scale, y, batch, k, n,
                                                 group, 0, s);
                 if (e != cudaSuccess) return e;
             }
+            if (gate) return launch_swiglu(gate, y, y, batch * n, 1, s);
             return resid ? launch_residual_add(resid, y, y, batch * n, 1, s) : cudaSuccess;
         }
         case OpKind::LinearInt8Dynamic: {
@@ -1462,17 +1464,18 @@ int32_t vyb_k_int4_gemv(const void* x_bf16, const void* w_packed, const void* sc
 
 // ---- the residual block around a decode projection, on raw device pointers --------------------------------------------
 int32_t vyb_k_int4_linear_block(const void* x_bf16, const void* norm_weight_bf16, float norm_eps, const void* w_packed,
-                                const void* scale_bf16, const void* residual_bf16, void* y_bf16, uint32_t m, uint32_t n, uint32_t k,
-                                uint32_t group_size, uint32_t flags, void* stream, uint32_t* status) {
+                                const void* scale_bf16, const void* gate_bf16, const void* residual_bf16, void* y_bf16, uint32_t m,
+                                uint32_t n, uint32_t k, uint32_t group_size, uint32_t flags, void* stream, uint32_t* status) {
     if (!x_bf16 || !w_packed || !scale_bf16 || !y_bf16) return fail_invalid_program("Fix: pass non-null device pointers.");
-    if (!norm_weight_bf16 && !residual_bf16)
-        return fail_invalid_program("Fix: pass a norm weight, a residual, or both; vyb_k_int4_gemv is the bare projection.");
+    if (!norm_weight_bf16 && !residual_bf16 && !gate_bf16)
+        return fail_invalid_program("Fix: pass a norm weight, a gate, a residual, or a norm weight with one of the two; vyb_k_int4_gemv is the bare projection.");
+    if (gate_bf16 && residual_bf16) return fail_invalid_program("Fix: pass a gate or a residual behind the projection, not both.");
     const bool whole = m <= 2 && vybk::int4_gemv_halfsm_supported(m, n, k, group_size);
     const bool blocks = !norm_weight_bf16 && vybk::int4_gemv_kblocks_supported(m, n, k, group_size);
     if (!whole && !blocks)
         return fail_unsupported("int4 block gemv shape m=" + std::to_string(m) + " n=" + std::to_string(n) + " k=" + std::to_string(k) +
                                 " group=" + std::to_string(group_size) +
-                                " (needs group 128 and m <= 2 with k 2048 or 4096, or the residual alone with m <= 4 and k a larger multiple of 2048)");
+                                " (needs group 128 and m <= 2 with k 2048 or 4096, or no norm with m <= 4 and k a larger multiple of 2048)");
     if ((reinterpret_cast<uintptr_t>(x_bf16) | reinterpret_cast<uintptr_t>(w_packed) | reinterpret_cast<uintptr_t>(scale_bf16) |
          reinterpret_cast<uintptr_t>(norm_weight_bf16)) & 15)
         return fail_invalid_program("Fix: int4 gemv operands must be 16-byte aligned.");
@@ -1487,11 +1490,13 @@ int32_t vyb_k_int4_linear_block(const void* x_bf16, const void* norm_weight_bf16
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (whole)
         return launch_result(vybk::launch_int4_gemv_halfsm(x_bf16, w_packed, scale_bf16, y_bf16, m, n, k, 0, sms, s, status, constant,
-                                                           nullptr, 0, false, norm_weight_bf16, norm_eps, residual_bf16),
+                                                           nullptr, 0, false, norm_weight_bf16, norm_eps, residual_bf16, gate_bf16),
                              "int4 block gemv");
-    bool added = false;
-    e = vybk::launch_int4_gemv_kblocks(x_bf16, w_packed, scale_bf16, y_bf16, m, n, k, 0, sms, s, constant, residual_bf16, &added);
-    if (e == cudaSuccess && !added) e = vybk::launch_residual_add(residual_bf16, y_bf16, y_bf16, m * n, 1, s);
+    bool fused = false;
+    e = vybk::launch_int4_gemv_kblocks(x_bf16, w_packed, scale_bf16, y_bf16, m, n, k, 0, sms, s, constant, residual_bf16, gate_bf16, &fused);
+    if (e == cudaSuccess && !fused)
+        e = gate_bf16 ? vybk::launch_swiglu(gate_bf16, y_bf16, y_bf16, m * n, 1, s)
+                      : vybk::launch_residual_add(residual_bf16, y_bf16, y_bf16, m * n, 1, s);
     return launch_result(e, "int4 block gemv");
 }
 

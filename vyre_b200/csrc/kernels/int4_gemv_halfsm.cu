@@ -119,9 +119,35 @@ struct Params {
     const uint16_t* norm_w;  // [k] bf16 (nullptr: no norm)
     float norm_eps;
     const uint16_t* resid;   // [m][n] bf16 (nullptr: no residual add)
+    // SwiGLU behind an up projection: gate holds the gate projection's outputs ([m][n] bf16); the stores write
+    // gate * (up * sigmoid(gate)) with up = this launch's sums rounded to bf16 (nullptr: none; not together with resid)
+    const uint16_t* gate;
 };
 
 __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(uint32_t(b) << 16); }
+// The stand-alone SwiGLU's arithmetic (vyre-libs/src/nn/activation/unary.rs:79-100: gate * (up * (1 / (1 + exp(-gate)))), every
+// f32 operation rounded to nearest with subnormals flushed, one cast to bf16) on this launch's sum as `up`, rounded to bf16
+// first as the stand-alone projection stores it. Out of line: a handful of outputs per thread, off the main loop's registers.
+__device__ __forceinline__ float mul_ftz(float a, float b) {
+    float r;
+    asm("mul.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float add_ftz(float a, float b) {
+    float r;
+    asm("add.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ float div_ftz(float a, float b) {
+    float r;
+    asm("div.rn.ftz.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __noinline__ __nv_bfloat16 swiglu_of(const uint16_t* gate, size_t at, float sum) {
+    const float g = bf16_bits_to_float(__ldcg(gate + at)), u = __bfloat162float(__float2bfloat16_rn(sum));
+    const float sig = div_ftz(1.0f, add_ftz(1.0f, expf(-g)));
+    return __float2bfloat16_rn(mul_ftz(g, mul_ftz(u, sig)));
+}
 // cast(bf16, f32(residual) + f32(branch)) with the branch already rounded to bf16 (vyre-libs/src/nn/activation/residual_add.rs:40-52)
 __device__ __forceinline__ __nv_bfloat16 add_residual(const uint16_t* resid, size_t at, float sum) {
     return __float2bfloat16_rn(__fadd_rn(bf16_bits_to_float(__ldcg(resid + at)), __bfloat162float(__float2bfloat16_rn(sum))));
@@ -161,7 +187,10 @@ __device__ __noinline__ void ksplit_finish(const Params& p, uint32_t tile0, uint
         for (uint32_t b = 16; b < p.kblocks; ++b) sum += __ldcg(src + b * stride);
         const size_t at = size_t(col) * p.n + row;
         if (OUT_F32) static_cast<float*>(p.y)[at] = sum;
-        else static_cast<__nv_bfloat16*>(p.y)[at] = p.resid ? add_residual(p.resid, at, sum) : __float2bfloat16_rn(sum);
+        else
+            static_cast<__nv_bfloat16*>(p.y)[at] = p.gate    ? swiglu_of(p.gate, at, sum)
+                                                   : p.resid ? add_residual(p.resid, at, sum)
+                                                             : __float2bfloat16_rn(sum);
     }
     __syncthreads();
 }
@@ -598,7 +627,9 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
                     static_cast<float*>(p.y)[size_t(col) * p.n + row] = sum;
                 } else if constexpr (FUSED) {
                     const size_t at = size_t(col) * p.n + row;
-                    static_cast<__nv_bfloat16*>(p.y)[at] = p.resid ? add_residual(p.resid, at, sum) : __float2bfloat16_rn(sum);
+                    static_cast<__nv_bfloat16*>(p.y)[at] = p.gate    ? swiglu_of(p.gate, at, sum)
+                                                           : p.resid ? add_residual(p.resid, at, sum)
+                                                                     : __float2bfloat16_rn(sum);
                 } else {
                     static_cast<__nv_bfloat16*>(p.y)[size_t(col) * p.n + row] = __float2bfloat16_rn(sum);
                 }
@@ -794,7 +825,7 @@ bool int4_gemv_halfsm_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t gro
 cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                     uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
                                     uint32_t* status, bool constant_weights, const PeerGather* gather, uint32_t half, bool pipelined,
-                                    const void* norm_w, float norm_eps, const void* resid) {
+                                    const void* norm_w, float norm_eps, const void* resid, const void* gate) {
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t de = cudaGetDevice(&dev);
@@ -811,8 +842,8 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     // the residual block (norm in front, residual add behind): batch <= 2, bf16 outputs; [k 4096 | 2048]
     static const Kernel fused[2] = {int4_gemv_halfsm_kernel<1, 4, 8, false, false, false, true>,
                                     int4_gemv_halfsm_kernel<1, 2, 8, false, false, false, true>};
-    const bool block = norm_w || resid;
-    if (block && (m > 2 || out_f32 || gather)) return cudaErrorInvalidValue;
+    const bool block = norm_w || resid || gate;
+    if (block && (m > 2 || out_f32 || gather || (resid && gate))) return cudaErrorInvalidValue;
     if (!(configured.load(std::memory_order_acquire) & bit)) {
         for (int i = 0; i < 14; ++i) {
             const void* f = i < 12 ? (const void*)kernels[i / 3][i % 3] : (const void*)fused[i - 12];
@@ -827,6 +858,7 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
     p.norm_w = static_cast<const uint16_t*>(norm_w);
     p.norm_eps = norm_eps;
     p.resid = static_cast<const uint16_t*>(resid);
+    p.gate = static_cast<const uint16_t*>(gate);
     p.x = static_cast<const uint16_t*>(x_bf16);
     p.w = static_cast<const uint8_t*>(w_packed);
     p.scales = static_cast<const uint16_t*>(scale_bf16);
@@ -867,11 +899,46 @@ bool int4_gemv_kblocks_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t gr
     return m >= 1 && m <= 4 && n >= 1 && group == 128 && k > 4096 && k % 2048 == 0;
 }
 
+namespace {
+// The persistent workspace of the one-launch k split (per-tile arrival words, then the partial rows), one per (device,
+// stream); made on first use outside stream capture, nullptr while the stream captures and none exists yet.
+void* kblocks_workspace(int dev, cudaStream_t stream, size_t need) {
+    struct Work {
+        void* ptr;
+        size_t bytes;
+    };
+    static std::mutex ws_mu;
+    static std::map<std::pair<int, cudaStream_t>, Work> ws;
+    std::lock_guard<std::mutex> lock(ws_mu);
+    auto it = ws.find({dev, stream});
+    if (it != ws.end() && it->second.bytes >= need) return it->second.ptr;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone) return nullptr;
+    // a larger workspace replaces a smaller one; the old one may still be in use by launches in flight on this
+    // stream and is kept (a handful of shapes per process)
+    const size_t bytes = need < (size_t(8) << 20) ? (size_t(8) << 20) : need;
+    void* fresh = nullptr;
+    if (cudaMalloc(&fresh, bytes) == cudaSuccess && cudaMemsetAsync(fresh, 0, bytes, stream) == cudaSuccess) {
+        ws[{dev, stream}] = Work{fresh, bytes};
+        return fresh;
+    }
+    cudaGetLastError();
+    if (fresh) cudaFree(fresh);
+    return nullptr;
+}
+size_t kblocks_count_words(uint32_t n) { return (size_t((n + TILE_ROWS - 1) / TILE_ROWS) + 63) & ~size_t(63); }
+size_t kblocks_workspace_bytes(uint32_t m, uint32_t n, uint32_t k) {
+    const uint32_t blk = k % 4096 == 0 ? 4096u : 2048u;
+    return (kblocks_count_words(n) + size_t(k / blk) * m * n) * 4;
+}
+}  // namespace
+
 cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                      uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                                     bool constant_weights, const void* resid, bool* resid_added) {
-    if (resid_added) *resid_added = false;
-    if (resid && out_f32) return cudaErrorInvalidValue;
+                                     bool constant_weights, const void* resid, const void* gate, bool* stores_fused) {
+    if (stores_fused) *stores_fused = false;
+    if ((resid || gate) && (out_f32 || (resid && gate))) return cudaErrorInvalidValue;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -900,37 +967,8 @@ cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, c
     // one block of activations; the per-launch cost is paid once instead of once per block.
     {
         const uint32_t blk = k % 4096 == 0 ? 4096u : 2048u, kblocks = k / blk;
-        const size_t count_words = (size_t(tiles) + 63) & ~size_t(63);  // arrival words first, then the partial rows
-        const size_t need = (count_words + size_t(kblocks) * m * n) * 4;
-        struct Work {
-            void* ptr;
-            size_t bytes;
-        };
-        static std::mutex ws_mu;
-        static std::map<std::pair<int, cudaStream_t>, Work> ws;
-        void* work = nullptr;
-        {
-            std::lock_guard<std::mutex> lock(ws_mu);
-            auto it = ws.find({dev, stream});
-            if (it != ws.end() && it->second.bytes >= need) work = it->second.ptr;
-            if (!work) {
-                cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-                if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
-                if (cap == cudaStreamCaptureStatusNone) {
-                    // a larger workspace replaces a smaller one; the old one may still be in use by launches in flight on this
-                    // stream and is kept (a handful of shapes per process)
-                    const size_t bytes = need < (size_t(8) << 20) ? (size_t(8) << 20) : need;
-                    void* fresh = nullptr;
-                    if (cudaMalloc(&fresh, bytes) == cudaSuccess && cudaMemsetAsync(fresh, 0, bytes, stream) == cudaSuccess) {
-                        ws[{dev, stream}] = Work{fresh, bytes};
-                        work = fresh;
-                    } else {
-                        cudaGetLastError();
-                        if (fresh) cudaFree(fresh);
-                    }
-                }
-            }
-        }
+        const size_t count_words = kblocks_count_words(n);  // arrival words first, then the partial rows
+        void* work = kblocks_workspace(dev, stream, kblocks_workspace_bytes(m, n, k));
         if (work) {
             uint32_t* counts = static_cast<uint32_t*>(work);  // zero between launches: the last arriver of a tile resets its word
             float* part = reinterpret_cast<float*>(counts + count_words);
@@ -949,8 +987,9 @@ cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, c
                 p.kblocks = kblocks;
                 p.part = part;
                 p.tile_count = counts;
-                p.resid = static_cast<const uint16_t*>(resid);  // added where the last arriver rounds the sums
-                if (resid && resid_added) *resid_added = true;
+                p.resid = static_cast<const uint16_t*>(resid);  // applied where the last arriver rounds the sums
+                p.gate = static_cast<const uint16_t*>(gate);
+                if (stores_fused) *stores_fused = true;
                 const uint64_t units = uint64_t(tiles) * kblocks;
                 uint32_t grid = units < uint64_t(sm_count) ? uint32_t(units) : uint32_t(sm_count);
                 if (grid < kblocks) grid = kblocks;

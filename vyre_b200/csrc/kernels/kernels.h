@@ -19,11 +19,13 @@ cudaError_t launch_int4_gemv(const void* x_bf16, const void* w_packed, const voi
 // half-SM form (int4_gemv_halfsm.cu): m <= 4, k 2048 or 4096; launch_int4_gemv routes to it
 // rows longer than 4096 (k a multiple of 2048), m <= 4: one launch of the k-block form per 4096 / 2048 columns, sums carried in f32
 bool int4_gemv_kblocks_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
-// resid (bf16 [m][n], bf16 outputs only): added to the rounded sums in the launch when it runs as ONE launch
-// (*resid_added = true); the launch-per-block fallback leaves the plain projection in y (*resid_added = false)
+// resid / gate (bf16 [m][n], bf16 outputs only, at most one): the residual add or SwiGLU(gate, this projection) applied to the
+// rounded sums in the launch when it runs as ONE launch (*stores_fused = true); the launch-per-block fallback leaves the
+// plain projection in y (*stores_fused = false)
 cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
                                      uint32_t n, uint32_t k, uint32_t out_f32, int sm_count, cudaStream_t stream,
-                                     bool constant_weights, const void* resid = nullptr, bool* resid_added = nullptr);
+                                     bool constant_weights, const void* resid = nullptr, const void* gate = nullptr,
+                                     bool* stores_fused = nullptr);
 // f16 tensor path of the same launch shape (int4_gemv_batch8.cu): up to eight batch rows in one launch, k 2048 or 4096
 bool int4_gemv_batch8_supported(uint32_t m, uint32_t n, uint32_t k, uint32_t group);
 cudaError_t launch_int4_gemv_batch8(const void* x_bf16, const void* w_packed, const void* scale_bf16, void* y, uint32_t m,
@@ -36,7 +38,9 @@ cudaError_t launch_int4_gemv_halfsm(const void* x_bf16, const void* w_packed, co
                                     uint32_t half = 0, bool pipelined = false,
                                     // the residual block around the projection, m <= 2, bf16 outputs: learned RMSNorm of x
                                     // (bf16 weight [k]) in the prologue, residual (bf16 [m][n]) added in the output stores
-                                    const void* norm_w = nullptr, float norm_eps = 0.0f, const void* resid = nullptr);
+                                    // or, instead of the residual, SwiGLU(gate, this projection) with gate bf16 [m][n]
+                                    const void* norm_w = nullptr, float norm_eps = 0.0f, const void* resid = nullptr,
+                                    const void* gate = nullptr);
 // ---- all-gather of column-parallel outputs over peer memory (allgather_push.cu) ------------------------------------
 // gather buffers [2][world][m][n] bf16 per rank; arrival counters and launch counters are 32-bit device words,
 // zero before the first push

@@ -190,7 +190,7 @@ _STATUS_FUNCS = {
     "vyb_nn_expert_mlp": [_S] * 8 + [_U] * 3 + [_PP],
     "vyb_nn_moe_layer_route_and_accumulate": [_S] * 7 + [_U] * 4 + [_PP],
     "vyb_nn_linear_int4_grouped_rowmajor": [_S] * 4 + [_U] * 5 + [_PP],
-    "vyb_nn_linear_int4_block": [_S] * 6 + [_U] * 4 + [C.c_float, _PP],
+    "vyb_nn_linear_int4_block": [_S] * 7 + [_U] * 4 + [C.c_float, _PP],
     "vyb_nn_linear_int8_weight_only": [_S] * 4 + [_U] * 3 + [_PP],
     "vyb_nn_linear_int8_dynamic": [_S] * 4 + [_U] * 3 + [_PP],
     "vyb_nn_moe_ffn_int4": [_S] * 9 + [_U] * 6 + [_PP],
@@ -257,7 +257,7 @@ _STATUS_FUNCS = {
     "vyb_k_colpar_wait": [C.POINTER(AllGatherCtx), _U, _P, _P],
     "vyb_k_int4_gemv": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_int4_gemv_ex": [_P, _P, _P, _P, _U, _U, _U, _U, _U, _U, _P, _P],
-    "vyb_k_int4_linear_block": [_P, _P, C.c_float, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
+    "vyb_k_int4_linear_block": [_P, _P, C.c_float, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P],
     "vyb_k_rms_norm": [_P, _P, _P, _U, _U, C.c_float, _U, _P],
     "vyb_k_residual_add": [_P, _P, _P, _U, _U, _P],
     "vyb_k_swiglu": [_P, _P, _P, _U, _U, _P],
