@@ -344,19 +344,41 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     // stand-alone operator's long-row form (thread t adds elements t, t + 256, ...; a butterfly over the warp; the eight
     // warp sums in warp order), so that the fused launch gives the bits of norm-then-projection
     float inv_rms[2 * NM];
+    uint4 pre_x[2 * NM][2], pre_w[2];  // FUSED with a norm weight: this lane's 16 activations of every row and their weights,
+                                       // loaded ahead so that their round trip overlaps the one of the sum's loads
     if constexpr (FUSED) {
         static_assert(W == 8 && !GATHER && !STRIDED && !OUT_F32, "the fused block is the dense bf16 form of 256 threads");
         __shared__ float warp_sq[2 * NM][W];
 #pragma unroll
         for (int j = 0; j < 2 * NM; ++j) inv_rms[j] = 0.0f;
         if (p.norm_w) {
+            const bool mine = lane < GPW * 8;  // 16 elements per lane cover the warp's slice
+#pragma unroll
+            for (int j = 0; j < 2 * NM; ++j) {
+                pre_x[j][0] = pre_x[j][1] = make_uint4(0, 0, 0, 0);
+                if (uint32_t(j) < p.m && mine) {
+                    const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * K + warp * (GPW * 128) + lane * 16);
+                    pre_x[j][0] = __ldcg(src);
+                    pre_x[j][1] = __ldcg(src + 1);
+                }
+            }
+            pre_w[0] = pre_w[1] = make_uint4(0, 0, 0, 0);
+            if (mine) {
+                const uint4* wsrc = reinterpret_cast<const uint4*>(p.norm_w + warp * (GPW * 128) + lane * 16);
+                pre_w[0] = __ldg(wsrc);
+                pre_w[1] = __ldg(wsrc + 1);
+            }
 #pragma unroll
             for (int j = 0; j < 2 * NM; ++j) {
                 if (uint32_t(j) >= p.m) break;
                 const uint16_t* row = p.x + size_t(j) * K;
+                uint16_t own[K / (W * 32)];  // all loads in flight at once, then the sum in index order
+#pragma unroll
+                for (uint32_t i = 0; i < K / (W * 32); ++i) own[i] = __ldcg(row + threadIdx.x + i * (W * 32));
                 float sum = 0.0f;
-                for (uint32_t c = threadIdx.x; c < K; c += W * 32) {
-                    const float v = bf16_bits_to_float(__ldcg(row + c));
+#pragma unroll
+                for (uint32_t i = 0; i < K / (W * 32); ++i) {
+                    const float v = bf16_bits_to_float(own[i]);
                     sum = __fadd_rn(sum, __fmul_rn(v, v));
                 }
 #pragma unroll
@@ -397,7 +419,15 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
         for (int j = 0; j < 2 * NM; ++j) {
             if (uint32_t(j) >= p.m) break;
             uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0;
-            if (has) {
+            bool preloaded = false;
+            if constexpr (FUSED) {
+                if (p.norm_w) {
+                    x0 = pre_x[j][0];
+                    x1 = pre_x[j][1];
+                    preloaded = true;
+                }
+            }
+            if (has && !preloaded) {
                 const uint4* src = reinterpret_cast<const uint4*>(p.x + size_t(j) * X_STRIDE + kblock * K + warp * (GPW * 128) + lane * 16);
                 x0 = __ldcg(src);
                 x1 = __ldcg(src + 1);
@@ -405,8 +435,7 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
             uint32_t r[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};  // r[i] = elements 2i (low half), 2i+1
             if constexpr (FUSED) {
                 if (p.norm_w && has) {  // x * inv to bf16, times the weight to bf16: the stand-alone operator's two roundings
-                    const uint4* wsrc = reinterpret_cast<const uint4*>(p.norm_w + warp * (GPW * 128) + lane * 16);
-                    const uint4 g0 = __ldg(wsrc), g1 = __ldg(wsrc + 1);
+                    const uint4 g0 = pre_w[0], g1 = pre_w[1];
                     const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
                     auto norm1 = [&](float x, float w) -> uint32_t {
                         const float n = __bfloat162float(__float2bfloat16_rn(__fmul_rn(x, inv_rms[j])));
