@@ -467,14 +467,20 @@ def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter
     bf16 = ffi.DT_BF16
     rng = np.random.default_rng(11)
     dev16 = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int16)).cuda()  # noqa: E731
-    weights = []
+    weights, host0 = [], {}
     for layer in range(layers):
-        ent = {"nw": dev16(synth.f32_to_bf16_bits((1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)))}
+        nw_np = synth.f32_to_bf16_bits((1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32))
+        ent = {"nw": dev16(nw_np)}
+        if layer == 0:
+            host0["post_attention_layernorm.weight"] = nw_np
         for name, (n, k) in {"gate": (inter, hidden), "up": (inter, hidden), "down": (hidden, inter)}.items():
             _, w, sc = synth.int4_linear_inputs(1, n, k, seed=17 * layer + len(name))
             ent[name] = (torch.from_numpy(w).cuda(), dev16(sc))
+            if layer == 0:
+                host0[f"mlp.{name}_proj.qweight"], host0[f"mlp.{name}_proj.scales"] = w.view(np.uint32), sc
         weights.append(ent)
-    x0 = dev16(synth.f32_to_bf16_bits((rng.standard_normal((rows, hidden)) * 2).astype(np.float32)))
+    x0_np = synth.f32_to_bf16_bits((rng.standard_normal((rows, hidden)) * 2).astype(np.float32))
+    x0 = dev16(x0_np)
     stream_h = [dev16(np.zeros((rows, hidden), np.uint16)) for _ in range(layers + 1)]
     normed, act, down = (dev16(np.zeros((rows, d), np.uint16)) for d in (hidden, inter, hidden))
     gate, up = (dev16(np.zeros((rows, inter), np.uint16)) for _ in range(2))
@@ -530,11 +536,44 @@ def measure_residual_block(peaks: dict, rows: int = 1, hidden: int = 4096, inter
         results[name] = {"launches_per_block": launches, "us_per_block": round(us, 2)}
     assert status.cpu().tolist() == [0, 0, 0, 0]
     assert torch.equal(finals[0], finals[1]), "the fused block's output differs from the separate operators'"
+    # the same block through the contract path: the reference's ProgramGraph (six nodes) and the graph the fusion pass makes
+    # of it (three nodes), every node a submission on resident buffers; host time of a run, input uploaded, output read back
+    import time
+
+    import vyre_b200 as vb
+
+    device = vb.Device.acquire(torch.cuda.current_device())
+    graph6 = vb.quantized_gated_mlp_graph(vb.QuantizedGatedMlpSpec(rows, hidden, inter, GROUP, norm_eps=1e-6))
+    graph3, taken = graph6.fuse_linear_blocks()
+    contract, outs = {}, []
+    for name, g in (("program_graph", graph6), ("fused_graph", graph3)):
+        sess = vb.GraphSession(g, device)
+        for cname, data in host0.items():
+            sess.set_constant(cname, data)
+        for _ in range(3):
+            out = sess.run({"residual": x0_np})["mlp.block_output"]
+        t0 = time.perf_counter()
+        for _ in range(20):
+            out = sess.run({"residual": x0_np})["mlp.block_output"]
+        contract[name] = {"nodes": len(g.nodes()), "host_us_per_run": round((time.perf_counter() - t0) / 20 * 1e6, 1)}
+        outs.append(out)
+        # without the host between the nodes: prepared binding sets, each ordered on the device behind the one before
+        for _ in range(3):
+            chained = sess.run_chained({"residual": x0_np})["mlp.block_output"]
+        t0 = time.perf_counter()
+        for _ in range(20):
+            chained = sess.run_chained({"residual": x0_np})["mlp.block_output"]
+        contract[name]["chained_host_us_per_run"] = round((time.perf_counter() - t0) / 20 * 1e6, 1)
+        assert chained == out, "the chained run's block output differs"
+        sess.close()
+    device.release()
+    assert outs[0] == outs[1], "the fused graph's block output differs from the ProgramGraph's"
+    assert outs[0] == stream_h[1].cpu().numpy().tobytes(), "the graph's block output differs from the kernel-level chain's first block"
     wbytes = 3 * (hidden * inter // 2 + hidden * inter // GROUP * 2)
     abytes = wbytes + rows * (4 * hidden + 4 * inter) * 2 + 2 * hidden * 2  # weights, scales; residual (read 3x, written once), norm weight 2x, gate / up written and read
     gbs = abytes / (results["fused_launches"]["us_per_block"] * 1e-6) / 1e9
     return {"case": f"residual block rows={rows} hidden={hidden} inter={inter}, {layers} blocks per graph ({layers * wbytes >> 20} MiB of weights)",
-            **results, "same_bits": True,
+            **results, "same_bits": True, "contract_path": {**contract, "nodes_taken_in": taken},
             "speedup": round(results["separate_launches"]["us_per_block"] / results["fused_launches"]["us_per_block"], 3),
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / peaks["hbm_gbs"], 4), "algorithmic_bytes_per_block": abytes,

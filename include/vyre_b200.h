@@ -567,6 +567,13 @@ int32_t vyb_prepare(vyb_instance* instance, const uint8_t artifact_digest[32], c
                     size_t n_bindings, vyb_prepared** prepared);
 int32_t vyb_prepared_submit(vyb_prepared* prepared, const vyb_binding* host_updates, size_t n_updates,
                             vyb_submission** submission);
+/* The same, ordered on the device behind `after` (a pending submission of any instance of the same device; NULL: as
+ * vyb_prepared_submit): the replay starts when `after` has completed, without the host waiting in between. A chain of
+ * nodes (a ProgramGraph's schedule over resident values) is submitted back to back this way and waited for at the end;
+ * the reference's CUDA Submission is synchronous (vyre-driver-cuda/src/materializer.rs:343-357) and has no such call.
+ * Every submission still has to be waited for and its completion freed. */
+int32_t vyb_prepared_submit_after(vyb_prepared* prepared, const vyb_submission* after, const vyb_binding* host_updates,
+                                  size_t n_updates, vyb_submission** submission);
 int32_t vyb_prepared_free(vyb_prepared* prepared);
 /* Host-side injection for recovery tests, like vyb_device_mark_lost: writes `word` into the instance's kernel
  * status words exactly where a kernel whose bounded wait ran out would raise it; the NEXT submission on the

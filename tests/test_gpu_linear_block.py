@@ -249,6 +249,18 @@ def test_fused_graph_runs_to_the_same_block_output(dev, rows, hidden, inter):
             for _ in range(2):
                 out = sess.run({"residual": x})["mlp.block_output"]
             outs.append(np.frombuffer(out, np.uint16))
+            # the same graph without the host between the nodes: prepared sets, each ordered on the device behind the one before
+            x2 = synth.f32_to_bf16_bits((rng.standard_normal((rows, hidden)) * 2).astype(np.float32))
+            want2 = sess.run({"residual": x2})["mlp.block_output"]
+            for inp, want in ((x, out), (x2, want2), (x, out)):
+                assert sess.run_chained({"residual": inp})["mlp.block_output"] == want
+            # a constant replaced: the prepared sets are made again over the new buffer
+            other = synth.f32_to_bf16_bits(np.ones(hidden, np.float32))
+            sess.set_constant("post_attention_layernorm.weight", other)
+            assert sess.run_chained({"residual": x})["mlp.block_output"] == sess.run({"residual": x})["mlp.block_output"] != out
+            sess.set_constant("post_attention_layernorm.weight", consts["post_attention_layernorm.weight"])
+            with pytest.raises(vb.BackendError, match="bind the graph input"):
+                sess.run_chained({})
             if g is fused:
                 kinds = [s_.kernel_variant() for s_ in sess.sessions]
                 assert kinds[-1] == 9 and (rows > 2 or kinds[0] == kinds[1] == 9)

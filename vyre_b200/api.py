@@ -633,8 +633,9 @@ class PreparedSubmission:
         self._instance = instance
         self._updates: dict[tuple, tuple] = {}
 
-    def submit(self, host_inputs: dict | None = None) -> Submission:
-        """host_inputs: {value_id: array} for the host-bound inputs whose bytes changed (copied in here)."""
+    def submit(self, host_inputs: dict | None = None, after: "Submission | None" = None) -> Submission:
+        """host_inputs: {value_id: array} for the host-bound inputs whose bytes changed (copied in here). `after`: a pending
+        submission (of any instance on the device) behind which this one is ordered on the device."""
         items = sorted((host_inputs or {}).items())
         key = tuple((vid, a.ctypes.data, a.nbytes) for vid, a in items)
         if key not in self._updates:  # same arrays again and again: marshalled once
@@ -646,7 +647,9 @@ class PreparedSubmission:
             self._updates = {key: (arr, [a for _, a in items], len(items))}
         arr, keep, count = self._updates[key]
         out = C.c_void_p()
-        check(ffi.lib().vyb_prepared_submit(self._h, arr, count, C.byref(out)))
+        if after is not None and after._h is None:
+            raise BackendError(ffi.ERR_INVALID_PROGRAM, "Fix: `after` has been waited for already; order behind a pending submission.")
+        check(ffi.lib().vyb_prepared_submit_after(self._h, after._h if after is not None else None, arr, count, C.byref(out)))
         return Submission(out.value, keep)
 
     def free(self) -> None:
@@ -909,6 +912,7 @@ class GraphSession:
         self.sessions = [ArtifactSession.compile(n["program"], device) for n in self.nodes]
         self.handles: dict[int, object] = {}
         self._owned: list = []
+        self._chain = None  # run_chained: one prepared binding set per node
         for v in self.values:
             if v["producer"] is not None or v["contract"]["lifetime"] == ffi.LIFETIME_INVOCATION:
                 self.handles[v["id"]] = self._alloc(v)
@@ -941,6 +945,7 @@ class GraphSession:
                                    f"Fix: constant `{name}` needs {self._bytes(v)} bytes by its contract, got {a.nbytes}.")
             handle = self.device.resident_from(a)
             self._owned.append(handle)
+        self._drop_chain()  # prepared sets have the old buffer's address baked in
         self.handles[v["id"]] = handle
 
     def run(self, inputs: dict) -> dict:
@@ -969,7 +974,74 @@ class GraphSession:
                 out[v["name"]] = self.device.download_resident(self.handles[v["id"]], self._bytes(v)).tobytes()
         return out
 
+    def _is_input(self, v: dict) -> bool:
+        return v["producer"] is None and v["contract"]["lifetime"] == ffi.LIFETIME_INVOCATION
+
+    def _drop_chain(self) -> None:
+        if self._chain:
+            for prep, _, _ in self._chain:
+                prep.free()
+        self._chain = None
+
+    def run_chained(self, inputs: dict) -> dict:
+        """The same as `run`, without the host in between: every node is a prepared binding set (graph inputs bound as host
+        bytes of the nodes that read them, all other values resident, `Output` values that nothing reads handed back by the
+        node's completion), submitted back to back in schedule order, each ordered on the device behind the one before;
+        the host waits once the last node is submitted."""
+        arrays = {}
+        for v in self.values:
+            if self._is_input(v):
+                if v["name"] not in inputs:
+                    raise BackendError(ffi.ERR_INVALID_PROGRAM, f"Fix: bind the graph input `{v['name']}`.")
+                a = np.ascontiguousarray(inputs[v["name"]])
+                if a.nbytes != self._bytes(v):
+                    raise BackendError(ffi.ERR_INVALID_PROGRAM,
+                                       f"Fix: graph input `{v['name']}` needs {self._bytes(v)} bytes by its contract, got {a.nbytes}.")
+                arrays[v["name"]] = a
+            elif v["producer"] is None and v["id"] not in self.handles:
+                raise BackendError(ffi.ERR_INVALID_PROGRAM, f"Fix: set the constant `{v['name']}` before running the graph.")
+        if self._chain is None:
+            chain = []
+            for node, sess in zip(self.nodes, self.sessions):
+                slot = {b["name"]: b["binding"] for b in sess._buffers}
+                bs, host, outs = BindingSet(sess.artifact.digest()), {}, {}
+                for port in node["inputs"]:
+                    v = self.values[port["value"]]
+                    if self._is_input(v):
+                        bs.insert_host(slot[port["buffer"]], arrays[v["name"]])
+                        host[slot[port["buffer"]]] = v["name"]
+                    else:
+                        bs.insert_resident(slot[port["buffer"]], self.handles[port["value"]])
+                for port in node["outputs"]:
+                    v = self.values[port["value"]]
+                    if v["contract"]["lifetime"] == ffi.LIFETIME_OUTPUT and v["consumers"] == 0:
+                        outs[slot[port["buffer"]]] = v["name"]  # allocated by the backend, read from the completion
+                    else:
+                        bs.insert_resident(slot[port["buffer"]], self.handles[port["value"]])
+                chain.append((sess.prepare(bs), host, outs))
+            self._chain = chain
+        subs, prev = [], None
+        for prep, host, _ in self._chain:
+            prev = prep.submit({s: arrays[name] for s, name in host.items()}, after=prev)
+            subs.append(prev)
+        out, failure = {}, None
+        for sub, (_, _, outs) in zip(subs, self._chain):
+            try:
+                done = sub.wait()
+                for s, name in outs.items():
+                    out[name] = done.output(s)
+                del done
+            except BackendError as e:  # every submission is waited for, the first failure is reported
+                failure = failure or e
+        if failure:
+            raise failure
+        for v in self.values:
+            if v["contract"]["lifetime"] == ffi.LIFETIME_OUTPUT and v["name"] not in out:
+                out[v["name"]] = self.device.download_resident(self.handles[v["id"]], self._bytes(v)).tobytes()
+        return out
+
     def close(self) -> None:
+        self._drop_chain()
         for h in self._owned:
             try:
                 self.device.free_resident(h)

@@ -1199,10 +1199,17 @@ int32_t vyb_prepare(vyb_instance* inst, const uint8_t artifact_digest[32], const
 }
 
 int32_t vyb_prepared_submit(vyb_prepared* prep, const vyb_binding* host_updates, size_t n_updates, vyb_submission** submission) {
+    return vyb_prepared_submit_after(prep, nullptr, host_updates, n_updates, submission);
+}
+
+int32_t vyb_prepared_submit_after(vyb_prepared* prep, const vyb_submission* after, const vyb_binding* host_updates, size_t n_updates,
+                                  vyb_submission** submission) {
     if (!prep || !submission || (!host_updates && n_updates))
         return fail_invalid_program("Fix: pass a non-null prepared set, updates and submission out-pointer.");
     vyb_instance* inst = prep->inst;
     vyb_device* d = inst->dev;
+    if (after && (after->consumed || !after->done || after->inst->dev != d))
+        return fail_invalid_program("Fix: `after` must be a pending submission (not yet waited for) on the same device.");
     if (int32_t rc = d->check_alive("submission")) return rc;
     if (inst->generation != d->generation.load())
         return fail_device_lost(d->device_name, inst->generation, "the instance belongs to a previous device generation");
@@ -1226,7 +1233,10 @@ int32_t vyb_prepared_submit(vyb_prepared* prep, const vyb_binding* host_updates,
     }
     cudaSetDevice(d->ordinal);
     std::memset(prep->status_host, 0, 16);
-    cudaError_t e = cudaGraphLaunch(prep->exec, inst->stream);
+    cudaError_t e = cudaSuccess;
+    // ordered behind another submission on the device: this instance's stream waits for that submission's completion event
+    if (after && after->inst->stream != inst->stream) e = cudaStreamWaitEvent(inst->stream, after->done, 0);
+    if (e == cudaSuccess) e = cudaGraphLaunch(prep->exec, inst->stream);
     if (e == cudaSuccess) e = cudaEventRecord(prep->done, inst->stream);
     if (e != cudaSuccess) {
         cudaGetLastError();

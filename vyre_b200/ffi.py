@@ -246,6 +246,7 @@ _STATUS_FUNCS = {
     "vyb_submit": [_P, C.c_char_p, C.POINTER(Binding), C.c_size_t, C.POINTER(DispatchConfig), _PP],
     "vyb_prepare": [_P, C.c_char_p, C.POINTER(Binding), C.c_size_t, _PP],
     "vyb_prepared_submit": [_P, C.POINTER(Binding), C.c_size_t, _PP],
+    "vyb_prepared_submit_after": [_P, _P, C.POINTER(Binding), C.c_size_t, _PP],
     "vyb_prepared_free": [_P],
     "vyb_instance_inject_status": [_P, _U],
     "vyb_submission_is_ready": [_P],
