@@ -250,17 +250,22 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     constexpr uint32_t SSTAGE = TILE_ROWS * GPW * 2; // and of its scales
     constexpr uint32_t MM = 2 * NM;                  // batch rows of a partial
     constexpr uint32_t PART = TILE_ROWS * MM * 4;    // bytes of one warp's partial of one tile
-    // 2048-k rows leave the upper half of the weight stages unused: the partial sums go there, and four times as many tiles
-    // fit between two reductions
-    constexpr uint32_t RED_BYTES = GPW == 4 ? SMEM_RED : SMEM_W / 2;
+    // A warp's tile of a 2048-k row is half as large. Whole rows of 2048: six stages instead of three keep as many bytes in
+    // flight per CTA (6.9 -> 6.2 us at 28672 rows). The k-block form keeps three stages and puts its partial sums into the
+    // unused upper half of the weight stages, so that four times as many tiles fit between two reductions: there every
+    // reduction ends in the arrival protocol of the k split, and six stages with a reduction every 12 tiles measured
+    // slower (4096 x 14336: 12.1 us against 9.3 us).
+    constexpr bool DEEP = GPW == 2 && !STRIDED;
+    constexpr int ST = DEEP ? 2 * STAGES : STAGES;
+    constexpr uint32_t RED_BYTES = (GPW == 4 || DEEP) ? SMEM_RED : SMEM_W / 2;
     constexpr uint32_t PRIV = RED_BYTES / W;         // bytes of partials (and prologue scratch) a warp owns
     constexpr uint32_t FLUSH = PRIV / PART;          // tiles between two reductions
     static_assert(PRIV >= 2 * GPW * 128, "the activation scratch must fit a warp's own area");
     static_assert(GPW == 2 || GPW == 4, "a warp owns 256 or 512 k");
     static_assert(RPI % 2 == 0, "the row parity of a lane must not depend on the copy index");
-    static_assert(W * STAGES * (WSTAGE + SSTAGE) <= SMEM_W + SMEM_S, "stages must fit");
+    static_assert(W * ST * (WSTAGE + SSTAGE) <= SMEM_W + SMEM_S, "stages must fit");
 
-    uint8_t* red = smem + (GPW == 4 ? SMEM_W + SMEM_S : SMEM_W / 2);
+    uint8_t* red = smem + ((GPW == 4 || DEEP) ? SMEM_W + SMEM_S : SMEM_W / 2);
     // whole rows: compile-time strides; a k block of a wider matrix (STRIDED): the strides of that matrix
     const uint32_t ROW_BYTES = STRIDED ? p.row_bytes : ROW_BYTES_DENSE;
     const uint32_t SCALE_STRIDE = STRIDED ? p.scale_stride : K / 128;
@@ -285,8 +290,8 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     const uint32_t r1 = min(p.n, r0 + my_tiles * TILE_ROWS);
     const uint32_t nrows = r1 - r0;
     const uint32_t ntiles = (nrows + TILE_ROWS - 1) / TILE_ROWS;
-    uint8_t* my_w = smem + warp * (STAGES * WSTAGE);             // this warp's private weight stages
-    uint8_t* my_s = smem + SMEM_W + warp * (STAGES * SSTAGE);    // and their scales
+    uint8_t* my_w = smem + warp * (ST * WSTAGE);             // this warp's private weight stages
+    uint8_t* my_s = smem + SMEM_W + warp * (ST * SSTAGE);    // and their scales
 
     // ---- this warp's private weight pipeline: one commit group per tile, STAGES tiles deep ---------------------
     // Lane l of copy i moves chunk l % CPR of row i * RPI + l / CPR. Odd rows are stored with the two 64-byte halves of
@@ -315,7 +320,7 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
             cp_src += TILE_ROWS * ROW_BYTES;
             sc_src += TILE_ROWS * SCALE_STRIDE;
             issue_rows = issue_rows > TILE_ROWS ? issue_rows - TILE_ROWS : 0u;
-            issue_stage = issue_stage == STAGES - 1 ? 0u : issue_stage + 1;
+            issue_stage = issue_stage == ST - 1 ? 0u : issue_stage + 1;
         }
         cp_async_commit();
     };
@@ -324,8 +329,8 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
     // queue, so the prefetch is paced (about PACE_NS between tiles) rather than issued as one 96 KB burst that the
     // predecessor's few activation loads would have to queue behind. This CTA has microseconds to spare here.
 #pragma unroll
-    for (int u = 0; u < STAGES; ++u) {
-        if (u > 0 && p.pace_ns) __nanosleep(p.pace_ns);
+    for (int u = 0; u < ST; ++u) {
+        if (u > 0 && p.pace_ns) __nanosleep(DEEP ? p.pace_ns / 2 : p.pace_ns);  // the same bytes per pause
         issue_tile();
     }
 
@@ -702,11 +707,11 @@ __global__ void __launch_bounds__(W * 32, 2) int4_gemv_halfsm_kernel(const __gri
         ++pending;
     };
     for (uint32_t u = 0; u < ntiles; ++u) {
-        cp_async_wait<STAGES - 1>();  // this thread's copies of tile u have landed ...
+        cp_async_wait<ST - 1>();  // this thread's copies of tile u have landed ...
         __syncwarp();                 // ... and so have the other lanes'
         const uint8_t* ws = my_w + stage * WSTAGE;
         const uint8_t* ss = my_s + stage * SSTAGE + lds_scale;
-        stage = stage == STAGES - 1 ? 0u : stage + 1;
+        stage = stage == ST - 1 ? 0u : stage + 1;
         uint4 wl[GPW], wh[GPW];
 #pragma unroll
         for (int c = 0; c < GPW; ++c) {
