@@ -198,11 +198,12 @@ def test_kernel_level_entry_point_matches_contract_path(dev):
 def test_long_rows_first_use_under_stream_capture_and_workspace_reuse(dev):
     # the one-launch k split needs a per-stream workspace that cannot be allocated while a stream is capturing: a first use
     # under capture runs one launch per k block instead; later, un-captured calls on the stream get the workspace, and
-    # different shapes share it (its arrival words are zero between launches)
+    # different shapes share it (its arrival words, a fixed region at its start, are zero between launches)
     lib = ffi.lib()
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
     cases = []
-    for (m, n, k) in [(2, 520, 8192), (1, 300, 14336), (4, 96, 6144)]:
+    # (the last shape has more 16-row tiles than the others: its arrival words must not lie where theirs kept partial sums)
+    for (m, n, k) in [(2, 520, 8192), (1, 300, 14336), (4, 96, 6144), (1, 2064, 6144)]:
         x, w, s = synth.int4_linear_inputs(m, n, k, seed=n)
         want = oracle.int4_rowmajor_linear(x, w, s, m, n, k)
         t = tuple(torch.from_numpy(a).cuda() for a in (x.view(np.int16), w, s.view(np.int16)))

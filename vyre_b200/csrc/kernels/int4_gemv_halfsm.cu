@@ -961,10 +961,14 @@ void* kblocks_workspace(int dev, cudaStream_t stream, size_t need) {
     if (fresh) cudaFree(fresh);
     return nullptr;
 }
-size_t kblocks_count_words(uint32_t n) { return (size_t((n + TILE_ROWS - 1) / TILE_ROWS) + 63) & ~size_t(63); }
+// The arrival words occupy a region of FIXED size at the start of the workspace and the partial rows follow it, whatever
+// the shape: the words must be zero between launches, so no shape's partial sums may ever land where another shape (more
+// rows, more tiles) keeps its words. 65536 words serve up to a million output rows; beyond that the launch-per-block
+// form runs.
+constexpr size_t KBLOCKS_COUNT_WORDS = size_t(1) << 16;
 size_t kblocks_workspace_bytes(uint32_t m, uint32_t n, uint32_t k) {
     const uint32_t blk = k % 4096 == 0 ? 4096u : 2048u;
-    return (kblocks_count_words(n) + size_t(k / blk) * m * n) * 4;
+    return (KBLOCKS_COUNT_WORDS + size_t(k / blk) * m * n) * 4;
 }
 }  // namespace
 
@@ -1001,8 +1005,8 @@ cudaError_t launch_int4_gemv_kblocks(const void* x_bf16, const void* w_packed, c
     // one block of activations; the per-launch cost is paid once instead of once per block.
     {
         const uint32_t blk = k % 4096 == 0 ? 4096u : 2048u, kblocks = k / blk;
-        const size_t count_words = kblocks_count_words(n);  // arrival words first, then the partial rows
-        void* work = kblocks_workspace(dev, stream, kblocks_workspace_bytes(m, n, k));
+        const size_t count_words = KBLOCKS_COUNT_WORDS;  // arrival words first (fixed region), then the partial rows
+        void* work = tiles <= KBLOCKS_COUNT_WORDS ? kblocks_workspace(dev, stream, kblocks_workspace_bytes(m, n, k)) : nullptr;
         if (work) {
             uint32_t* counts = static_cast<uint32_t*>(work);  // zero between launches: the last arriver of a tile resets its word
             float* part = reinterpret_cast<float*>(counts + count_words);
