@@ -39,7 +39,12 @@
 //    memory; after the last tile (or every few tiles, when a CTA owns many) one barrier, and every thread sums the
 //    warps' partials of one output in fixed order (deterministic).
 //
-// Nothing in the kernel waits on another warp except that barrier, and nothing waits on a flag or an mbarrier: it
+//  * FUSED instantiations take the neighbours of a residual block into the launch: a learned RMSNorm of the activations in
+//    the prologue (one CTA barrier for the row's sum of squares), SwiGLU with another projection's outputs as the gate or a
+//    residual add where a finished sum is rounded and stored; every intermediate is rounded as the stand-alone operators
+//    round it, so the outputs are those of the operators run one after the other.
+//
+// Nothing in the kernel waits on another warp except those barriers, and nothing waits on a flag or an mbarrier: it
 // cannot hang.
 //
 // Replaces the generated scalar kernel of vyre-libs/src/nn/linear/inner/linear_4bit.rs:399-775 (one warp per
@@ -113,7 +118,7 @@ struct Params {
     uint32_t kblocks;
     float* part;            // [kblocks][m][n]
     uint32_t* tile_count;   // [tiles], zero between launches (the last arriver resets its word)
-    // the residual block around the projection (FUSED instantiations; the k-block form honours `resid` as well): a learned
+    // the residual block around the projection (FUSED instantiations; the k-block form honours `resid` and `gate` as well): a learned
     // RMSNorm of the activations in the prologue and a residual add in the output stores, with the roundings of the
     // stand-alone operators (normalised value to bf16, times weight to bf16; sum to bf16, plus residual to bf16)
     const uint16_t* norm_w;  // [k] bf16 (nullptr: no norm)
