@@ -588,6 +588,9 @@ int32_t vyb_upload_at(vyb_device* d, vyb_resident_handle h, size_t offset_bytes,
     }
     cudaSetDevice(d->ordinal);
     cudaError_t e = cudaMemcpy(dst, bytes, len, cudaMemcpyHostToDevice);
+    // a copy from pageable memory may return once the bytes are staged, before the DMA has landed; submissions run on
+    // non-blocking streams that do not order themselves behind it, so the upload ends only when the copy has
+    if (e == cudaSuccess) e = cudaStreamSynchronize(cudaStreamLegacy);
     {
         std::lock_guard<std::mutex> lk(d->mu);
         auto it = d->residents.find(h.id);
