@@ -298,6 +298,11 @@ int32_t vyb_nn_learned_rms_norm(const char* input, const char* weight, const cha
                                 float eps, uint32_t dtype, vyb_program** program);
 int32_t vyb_nn_gated_rms_norm(const char* input, const char* weight, const char* gate, const char* output, uint32_t rows,
                               uint32_t hidden, float eps, uint32_t dtype, vyb_program** program);
+/* gated_rms_norm_with_weight_dtype (gated_rms_norm.rs:67-96): the learned scale stored in a floating type of its own
+ * (bf16 activations with f32 scales, as checkpoints hold them) */
+int32_t vyb_nn_gated_rms_norm_with_weight_dtype(const char* input, const char* weight, const char* gate, const char* output,
+                                                uint32_t rows, uint32_t hidden, float eps, uint32_t dtype, uint32_t weight_dtype,
+                                                vyb_program** program);
 /* GGML K-quants with per-block f32 scale / min sidecars: vyre-libs/src/nn/quant/ggml.rs:28-120 (unpack), 217-400 (fused
  * dequant + linear over the k-major weight stream, out = x @ dequant(w) + b) */
 int32_t vyb_quant_q4_k_unpack(const char* packed, const char* scales, const char* mins, const char* output, uint32_t n,

@@ -679,6 +679,7 @@ VYO_API void vyo_residual_add(const void* residual, const void* branch, void* ou
 // vyre-libs/src/nn/norm/gated_rms_norm.rs:123-247. Per element: sum_squares = sequential f32 sum of x^2 over the row;
 // normalized = x * (1 / sqrt(sum_squares / hidden + eps))  (InverseSqrt = 1.0 / sqrtf, vyre-reference/src/ieee754.rs:60-70);
 // rounded to dtype; times f32(weight[col]); with a gate: times gate / (1 + exp(-gate)); one final cast to dtype.
+// Pinned by the known answers of vyre-libs/tests/gated_rms_norm_contract.rs (f32 fixture, exact F16 / BF16 words, F32 scales).
 VYO_API void vyo_rms_norm(const void* input, const void* weight, const void* gate, void* out, uint32_t rows, uint32_t hidden,
                           float eps, uint32_t dtype, uint32_t weight_dtype) {
     for (uint32_t r = 0; r < rows; ++r) {

@@ -93,6 +93,35 @@ def test_gated_rms_norm_within_the_exp_window(dev):
     assert ulp.max() <= 128
 
 
+def test_gated_rms_norm_contract_vectors_on_the_device(dev):
+    # vyre-libs/tests/gated_rms_norm_contract.rs: the reference's own known answers
+    f = lambda a: np.array(a, np.float32)  # noqa: E731
+    u = lambda a: np.array(a, np.uint16)  # noqa: E731
+    gated = lambda rows, hidden, eps, tag, ins: run(dev, vb.gated_rms_norm("i", "w", "g", "o", rows, hidden, eps, tag), ins)[0]  # noqa: E731
+    got = np.frombuffer(gated(2, 4, 1e-6, ffi.DT_F32, [f([1.0, -2.0, 3.0, -4.0, 0.25, -0.5, 2.0, 1.0]), f([0.5, 1.5, -1.0, 2.0]),
+                                                        f([-3.0, 0.0, 2.0, 8.0, -1.0, 1.0, -8.0, 3.0])]), np.float32)
+    want = f([-0.025976218, 0.0, -1.9297296, -23.361658, -0.029170781, -0.47576645, 0.0046558483, 4.9594145])
+    assert np.abs(got - want).max() <= 3e-6  # :72-101, the reference's tolerance
+    got = np.frombuffer(gated(2, 4, 1e-6, ffi.DT_F32, [np.zeros(8, np.float32), f([1, -2, 3, -4]),
+                                                        f([-100, -1, 0, 100, 1, 2, 3, 4])]), np.float32)
+    assert np.all(got == 0.0)  # :104-116
+    small = np.frombuffer(gated(1, 2, 1e-12, ffi.DT_F32, [f([1e-8, -1e-8]), f([1, 1]), f([1, 1])]), np.float32)
+    large = np.frombuffer(gated(1, 2, 1e-4, ffi.DT_F32, [f([1e-8, -1e-8]), f([1, 1]), f([1, 1])]), np.float32)
+    assert 0.007 < small[0] < 0.008 and 7e-7 < large[0] < 8e-7 and small[0] > large[0] * 9000.0  # :119-129
+    got = np.frombuffer(gated(2, 2, 1e-6, ffi.DT_F32, [f([np.nan, 1.0, 3.0, 4.0]), f([1, 1]), f([1, 1, 1, 1])]), np.float32)
+    assert np.isnan(got[0]) and np.isnan(got[1]) and np.abs(got[2:] - f([0.6203238, 0.8270984])).max() <= 3e-6  # :132-144
+    got = np.frombuffer(gated(1, 2, 1e-6, ffi.DT_F16, [u([0x3C00, 0xC000]), u([0x3C00, 0x3800]), u([0x3C00, 0xBC00])]), np.uint16)
+    assert got.tolist() == [0x3765, 0x3171]  # :170-212, exact words
+    got = np.frombuffer(gated(1, 2, 1e-6, ffi.DT_BF16, [u([0x3F80, 0xC000]), u([0x3F80, 0x3F00]), u([0x3F80, 0xBF80])]), np.uint16)
+    assert got.tolist() == [0x3EED, 0x3E2E]
+    prog = vb.gated_rms_norm_with_weight_dtype("x", "w", "g", "y", 1, 2, 1e-6, ffi.DT_BF16, ffi.DT_F32)  # :214-246
+    assert [b["dtype"] for b in prog.buffers()] == [ffi.DT_BF16, ffi.DT_F32, ffi.DT_BF16, ffi.DT_BF16]
+    got = np.frombuffer(run(dev, prog, [u([0x3F80, 0xC000]), f([1.0, 0.5]), u([0x3F80, 0xBF80])])[0], np.uint16)
+    assert got.tolist() == [0x3EED, 0x3E2E]
+    with pytest.raises(vb.BackendError, match="supports F16, BF16, or F32 source tensors"):  # :248-257
+        vb.gated_rms_norm_with_weight_dtype("x", "w", "g", "y", 1, 2, 1e-6, ffi.DT_BF16, ffi.DT_U32)
+
+
 def test_rms_norm_construction_errors():
     with pytest.raises(vb.BackendError, match="requires nonzero rows and hidden size; got rows=0, hidden=8"):
         vb.learned_rms_norm("i", "w", "o", 0, 8, 1e-6, ffi.DT_F32)

@@ -381,9 +381,39 @@ def test_k_quant_reference_fixtures():
     assert out.tolist() == [2.5, 3.5]
 
 
+# --- vyre-libs/tests/gated_rms_norm_contract.rs -----------------------------------------------------------------------
+def test_gated_rms_norm_contract_vectors():
+    f = lambda a: np.array(a, np.float32)  # noqa: E731
+    u = lambda a: np.array(a, np.uint16)  # noqa: E731
+    # :72-101 exact_two_row_fixture_matches_authoritative_operation_order (the reference's tolerance: 3e-6)
+    got = oracle.rms_norm(f([1.0, -2.0, 3.0, -4.0, 0.25, -0.5, 2.0, 1.0]), f([0.5, 1.5, -1.0, 2.0]), 2, 4, 1e-6,
+                          gate=f([-3.0, 0.0, 2.0, 8.0, -1.0, 1.0, -8.0, 3.0]))
+    want = f([-0.025976218, 0.0, -1.9297296, -23.361658, -0.029170781, -0.47576645, 0.0046558483, 4.9594145])
+    assert np.abs(got - want).max() <= 3e-6
+    # :104-116 zero_rows_produce_exact_signed_zero_independent_of_gate
+    got = oracle.rms_norm(np.zeros(8, np.float32), f([1, -2, 3, -4]), 2, 4, 1e-6, gate=f([-100, -1, 0, 100, 1, 2, 3, 4]))
+    assert np.all(got == 0.0)
+    # :119-129 epsilon_changes_tiny_variance_rows_at_the_expected_boundary
+    small = oracle.rms_norm(f([1e-8, -1e-8]), f([1, 1]), 1, 2, 1e-12, gate=f([1, 1]))
+    large = oracle.rms_norm(f([1e-8, -1e-8]), f([1, 1]), 1, 2, 1e-4, gate=f([1, 1]))
+    assert 0.007 < small[0] < 0.008 and 7e-7 < large[0] < 8e-7 and small[0] > large[0] * 9000.0
+    # :132-144 nan_variance_is_confined_to_its_source_row
+    got = oracle.rms_norm(f([np.nan, 1.0, 3.0, 4.0]), f([1, 1]), 2, 2, 1e-6, gate=f([1, 1, 1, 1]))
+    assert np.isnan(got[0]) and np.isnan(got[1]) and np.abs(got[2:] - f([0.6203238, 0.8270984])).max() <= 3e-6
+    # :170-212 low_precision_programs_execute_with_exact_source_dtype_rounding: exact output words
+    got = oracle.rms_norm(u([0x3C00, 0xC000]), u([0x3C00, 0x3800]), 1, 2, 1e-6, dtype=oracle.DT_F16, gate=u([0x3C00, 0xBC00]))
+    assert got.tolist() == [0x3765, 0x3171]
+    got = oracle.rms_norm(u([0x3F80, 0xC000]), u([0x3F80, 0x3F00]), 1, 2, 1e-6, dtype=oracle.DT_BF16, gate=u([0x3F80, 0xBF80]))
+    assert got.tolist() == [0x3EED, 0x3E2E]
+    # :214-246 bf16_activations_with_f32_weights_execute_exactly
+    got = oracle.rms_norm(u([0x3F80, 0xC000]), f([1.0, 0.5]), 1, 2, 1e-6, dtype=oracle.DT_BF16, gate=u([0x3F80, 0xBF80]),
+                          weight_dtype=oracle.DT_F32)
+    assert got.tolist() == [0x3EED, 0x3E2E]
+
+
 def test_rms_norm_follows_the_stated_order():
-    # no vector of the reference pins this operator (gated_rms_norm.rs has no test module): the restatement is checked
-    # against the formula of its doc comment evaluated step by step in numpy f32
+    # the learned (gate-less) form has no vector of its own in the reference (it shares the gated form's code path, pinned
+    # above): the restatement is also checked against the formula of its doc comment evaluated step by step in numpy f32
     rng = np.random.default_rng(3)
     rows, hidden, eps = 3, 37, np.float32(1e-5)
     x = rng.standard_normal((rows, hidden)).astype(np.float32)

@@ -250,6 +250,11 @@ def gated_rms_norm(input, weight, gate, output, rows, hidden, eps, dtype):  # no
     return _build("vyb_nn_gated_rms_norm", input, weight, gate, output, rows, hidden, C.c_float(eps), dtype)
 
 
+def gated_rms_norm_with_weight_dtype(input, weight, gate, output, rows, hidden, eps, dtype, weight_dtype):  # noqa: A002
+    return _build("vyb_nn_gated_rms_norm_with_weight_dtype", input, weight, gate, output, rows, hidden, C.c_float(eps), dtype,
+                  weight_dtype)
+
+
 def q4_k_unpack(packed, scales, mins, output, n):
     return _build("vyb_quant_q4_k_unpack", packed, scales, mins, output, n)
 

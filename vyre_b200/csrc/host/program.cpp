@@ -920,6 +920,12 @@ int32_t vyb_nn_gated_rms_norm(const char* input, const char* weight, const char*
     VYB_REQUIRE_NAMES(input, weight, gate, output_name);
     return rms_norm_impl(input, weight, gate, output_name, rows, hidden, eps, dtype, dtype, program);
 }
+int32_t vyb_nn_gated_rms_norm_with_weight_dtype(const char* input, const char* weight, const char* gate, const char* output_name,
+                                                uint32_t rows, uint32_t hidden, float eps, uint32_t dtype, uint32_t weight_dtype,
+                                                vyb_program** program) {
+    VYB_REQUIRE_NAMES(input, weight, gate, output_name);
+    return rms_norm_impl(input, weight, gate, output_name, rows, hidden, eps, dtype, weight_dtype, program);
+}
 
 // ---- GGML K-quants (ggml.rs:28-400): Q4_K blocks of 32 weights in 4 words, Q2_K blocks of 16 weights in 1 word ----------
 static int32_t k_quant_unpack_impl(uint32_t bits, const char* packed, const char* scales, const char* mins, const char* out,

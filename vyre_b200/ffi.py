@@ -183,6 +183,7 @@ _STATUS_FUNCS = {
     "vyb_nn_residual_add_typed": [_S] * 3 + [_U, _U, _PP],
     "vyb_nn_learned_rms_norm": [_S] * 3 + [_U, _U, C.c_float, _U, _PP],
     "vyb_nn_gated_rms_norm": [_S] * 4 + [_U, _U, C.c_float, _U, _PP],
+    "vyb_nn_gated_rms_norm_with_weight_dtype": [_S] * 4 + [_U, _U, C.c_float, _U, _U, _PP],
     "vyb_quant_q4_k_unpack": [_S] * 4 + [_U, _PP],
     "vyb_quant_q2_k_unpack": [_S] * 4 + [_U, _PP],
     "vyb_quant_q4_k_linear": [_S] * 6 + [_U, _U, _PP],
