@@ -229,6 +229,13 @@ def test_int8_and_matmul_and_linear_rows(dev):
     bias = rng.standard_normal(6).astype(np.float32)
     got = run(dev, vb.linear_rows("x", "w", "b", "o", 3, 40, 6), [x, w, bias])[0]
     assert got == oracle.linear_rows(x, w, bias, 3, 40, 6).tobytes()
+    # vyre-libs/tests/linear_rows_contract.rs:24-75: the reference's hand-computed projections
+    got = run(dev, vb.linear_rows("x", "w", "b", "o", 2, 3, 2), [f32(1, 2, 3, -1, 0, 2), f32(1, 0, 0, 1, 1, 1), f32(0.5, -0.5)])[0]
+    assert as_f32(got).tolist() == [4.5, 4.5, 1.5, 1.5]
+    got = run(dev, vb.linear_rows("x", "w", "b", "o", 2, 2, 1), [f32(0, 0, 4, -1), f32(2, 3), f32(0.0)])[0]
+    assert as_f32(got).tolist() == [0.0, 5.0]
+    got = run(dev, vb.linear_rows_no_bias_out_in_typed("x", "w", "o", 1, 2, 2, ffi.DT_F32), [f32(2, 3), f32(1, 10, 100, 1000)])[0]
+    assert as_f32(got).tolist() == [32.0, 3200.0]
 
 
 def test_moe_ops(dev):

@@ -21,6 +21,41 @@ def dev():
     d.release()
 
 
+def test_dense_gated_mlp_contract_fixtures_on_the_device(dev):
+    # vyre-libs/tests/dense_gated_mlp_graph_contract.rs: the reference's own fixtures of the connected block
+    f = lambda a: np.array(a, np.float32)  # noqa: E731
+
+    def block(spec, consts, residual):
+        sess = api.GraphSession(api.dense_gated_mlp_graph(spec), dev)
+        try:
+            for name, data in consts.items():
+                sess.set_constant(name, data)
+            out = sess.run({"residual": residual})["mlp.block_output"]
+            assert sess.run_chained({"residual": residual})["mlp.block_output"] == out
+            return out
+        finally:
+            sess.close()
+
+    silu_one = np.float32(1.0) / (np.float32(1.0) + np.exp(np.float32(-1.0)))
+    eye = f([1.0, 0.0, 0.0, 1.0])
+    names = ("post_attention_layernorm.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")
+    # :124-149
+    got = np.frombuffer(block(api.DenseGatedMlpSpec(1, 2, 2, 2, ffi.DT_F32, norm_eps=0.0), dict(zip(names, (f([1.0, 1.0]), eye, eye, eye))),
+                              f([1.0, 1.0, 2.0, 2.0])), np.float32)
+    assert np.abs(got - f([1 + silu_one, 1 + silu_one, 2 + silu_one, 2 + silu_one])).max() < 1e-6
+    # :151-177
+    got = np.frombuffer(block(api.DenseGatedMlpSpec(1, 1, 2, 1, ffi.DT_F32, norm_eps=0.0),
+                              dict(zip(names, (f([1.0, 1.0]), f([1.0, 0.0]), f([0.0, 1.0]), f([2.0, 3.0])))), f([1.0, 1.0])), np.float32)
+    assert abs(got[0] - (1.0 + 2.0 * silu_one)) < 1e-6 and abs(got[1] - (1.0 + 3.0 * silu_one)) < 1e-6
+    # :179-206: the exact BF16 word
+    b = oracle.f32_to_bf16_bits
+    one = b(f([1.0]))
+    got = np.frombuffer(block(api.DenseGatedMlpSpec(1, 1, 1, 1, ffi.DT_BF16, norm_eps=0.0), dict(zip(names, (one, one, one, one))),
+                              b(f([2.0]))), np.uint16)
+    silu_rounded = oracle.bf16_bits_to_f32(b(f([silu_one])))[0]
+    assert got.tolist() == b(f([2.0 + silu_rounded])).tolist()
+
+
 @pytest.mark.parametrize("dtype,odt", [(ffi.DT_F32, oracle.DT_F32), (ffi.DT_BF16, oracle.DT_BF16)])
 def test_dense_gated_mlp_graph_matches_the_oracle_composition(dev, dtype, odt):
     batch, seq, h, inter = 2, 3, 40, 24

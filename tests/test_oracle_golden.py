@@ -308,6 +308,13 @@ def test_linear_rows_layouts_and_bf16_cast():
     assert np.array_equal(out, oracle.f32_to_bf16_bits(f32(201.0, 2010.0, 403.0, 4030.0)))
 
 
+# --- vyre-libs/tests/linear_rows_contract.rs:24-75: the reference's hand-computed projections ---------------
+def test_linear_rows_contract_vectors():
+    assert oracle.linear_rows(f32(1, 2, 3, -1, 0, 2), f32(1, 0, 0, 1, 1, 1), f32(0.5, -0.5), 2, 3, 2).tolist() == [4.5, 4.5, 1.5, 1.5]
+    assert oracle.linear_rows(f32(0, 0, 4, -1), f32(2, 3), f32(0.0), 2, 2, 1).tolist() == [0.0, 5.0]
+    assert oracle.linear_rows(f32(2, 3), f32(1, 10, 100, 1000), None, 1, 2, 2, weight_out_in=True).tolist() == [32.0, 3200.0]
+
+
 # --- vyre-libs/src/math/linalg/matmul.rs:17-60 (wrapping u32) -----------------------------------------------
 def test_matmul_u32_wraps():
     a = u32(0xFFFFFFFF, 2)  # [1,2]
@@ -409,6 +416,33 @@ def test_gated_rms_norm_contract_vectors():
     got = oracle.rms_norm(u([0x3F80, 0xC000]), f([1.0, 0.5]), 1, 2, 1e-6, dtype=oracle.DT_BF16, gate=u([0x3F80, 0xBF80]),
                           weight_dtype=oracle.DT_F32)
     assert got.tolist() == [0x3EED, 0x3E2E]
+
+
+# --- vyre-libs/tests/dense_gated_mlp_graph_contract.rs: the block's operators composed as the graph wires them -----------
+def dense_block(x, wn, wg, wu, wd, rows, hidden, inter, eps, dt):
+    normed = oracle.rms_norm(x, wn, rows, hidden, eps, dtype=dt)
+    gate = oracle.linear_rows(normed, wg, None, rows, hidden, inter, dtype=dt, weight_out_in=True)
+    up = oracle.linear_rows(normed, wu, None, rows, hidden, inter, dtype=dt, weight_out_in=True)
+    down = oracle.linear_rows(oracle.swiglu(gate, up, dtype=dt), wd, None, rows, inter, hidden, dtype=dt, weight_out_in=True)
+    return oracle.residual_add(x, down, dtype=dt)
+
+
+def test_dense_gated_mlp_contract_fixtures():
+    f = lambda a: np.array(a, np.float32)  # noqa: E731
+    silu_one = np.float32(1.0) / (np.float32(1.0) + np.exp(np.float32(-1.0)))
+    eye = f([1.0, 0.0, 0.0, 1.0])
+    # :124-149 f32_prompt_rows_match_direct_formula (norm_eps 0, identity weights, two rows)
+    got = dense_block(f([1.0, 1.0, 2.0, 2.0]), f([1.0, 1.0]), eye, eye, eye, 2, 2, 2, 0.0, oracle.DT_F32)
+    assert np.abs(got - f([1 + silu_one, 1 + silu_one, 2 + silu_one, 2 + silu_one])).max() < 1e-6
+    # :151-177 non_square_cross_model_fixture_uses_output_major_weights
+    got = dense_block(f([1.0, 1.0]), f([1.0, 1.0]), f([1.0, 0.0]), f([0.0, 1.0]), f([2.0, 3.0]), 1, 2, 1, 0.0, oracle.DT_F32)
+    assert abs(got[0] - (1.0 + 2.0 * silu_one)) < 1e-6 and abs(got[1] - (1.0 + 3.0 * silu_one)) < 1e-6
+    # :179-206 bf16_path_matches_exact_rounding_policy: the exact output word
+    b = oracle.f32_to_bf16_bits
+    one = b(f([1.0]))
+    got = dense_block(b(f([2.0])), one, one, one, one, 1, 1, 1, 0.0, oracle.DT_BF16)
+    silu_rounded = oracle.bf16_bits_to_f32(b(f([silu_one])))[0]
+    assert got.tolist() == b(f([2.0 + silu_rounded])).tolist()
 
 
 def test_rms_norm_follows_the_stated_order():

@@ -104,6 +104,16 @@ def test_gated_mlp_templates():
     assert g.digest() == same.digest() != other.digest()
     refuses(lambda: api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(0, 3, 8, 12)), "must be nonzero")
     refuses(lambda: api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(1, 3, 8, 12, ffi.DT_U32)), "dtype must be F16, BF16, or F32")
+    # vyre-libs/tests/dense_gated_mlp_graph_contract.rs:207-235 graph_stage_order_is_canonical
+    canon = api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(1, 1, 2, 3, ffi.DT_F32, norm_eps=1e-6))
+    assert [n["name"] for n in canon.nodes()] == names
+    # :237-262 production_qwen35_dimensions_build_exact_weight_contracts
+    big = {n["name"]: n for n in api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(1, 1, 5120, 17408, ffi.DT_BF16, norm_eps=1e-6)).nodes()}
+    assert big["mlp.gate_proj"]["program"].buffers()[1]["count"] == 17408 * 5120
+    assert big["mlp.down_proj"]["program"].buffers()[1]["count"] == 5120 * 17408
+    # :264-291 invalid_dense_mlp_contracts_are_rejected (the empty batch and the integer dtype are refused above)
+    with pytest.raises(api.BackendError):
+        api.dense_gated_mlp_graph(api.DenseGatedMlpSpec(0xFFFFFFFF, 2, 2, 2, ffi.DT_F32))
     q = api.quantized_gated_mlp_graph(api.QuantizedGatedMlpSpec(rows=4, hidden_dim=256, intermediate_dim=512))
     qv = {v["name"]: v for v in q.values()}
     assert qv["mlp.gate_proj.qweight"]["contract"] == {"dtype": ffi.DT_U32, "access": RO, "lifetime": CONST, "shape": [512, 32]}
