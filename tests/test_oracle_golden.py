@@ -83,6 +83,28 @@ def test_int4_primitive_registry_fixtures():
         204.0, 204.0, 0.0, 0.0]
 
 
+# --- vyre-primitives/tests/quantized_packing_contracts.rs:5-84 -------------------------------------------
+def test_generated_i4_matrix_preserves_packing_and_top1():
+    pattern = [-8, -7, -3, -1, 0, 1, 2, 3, 4, 7]
+    for lane_count in [0, 1, 2, 7, 8, 9, 15, 16, 17, 31, 32, 33, 63, 64, 65]:
+        lanes = [pattern[i % len(pattern)] for i in range(lane_count)]
+        packed = oracle.pack_i4x8(np.array(lanes, np.int32))
+        assert packed.size == (lane_count + 7) // 8
+        assert oracle.unpack_i4x8(packed, lane_count).tolist() == lanes
+        if lane_count:
+            assert oracle.i4x8_dot_i32(packed, packed, lane_count) == sum(v * v for v in lanes)
+    weights = [[7, 6, 5, 4, 3, 2, 1, 0, -1], [-8, -7, -6, -5, -4, -3, -2, -1, 0], [1, -1, 1, -1, 1, -1, 1, -1, 1]]
+    acts = [[1] * 9, [-1] * 9]
+    wp = np.concatenate([oracle.pack_i4x8(np.array(r, np.int32)) for r in weights])
+    ap = np.concatenate([oracle.pack_i4x8(np.array(r, np.int32)) for r in acts])
+    rs, bs = f32(0.5, 0.25, 1.0), f32(1.0, 0.5)
+    logits = oracle.i4x8_batched_matmul_f32_scaled(wp, ap, rs, bs, 2, 3, 9).reshape(2, 3)
+    assert logits.tolist() == [[13.5, -9.0, 1.0], [-6.75, 4.5, -0.5]]
+    top = oracle.i4x8_batched_matmul_top1_f32_scaled(wp, ap, rs, bs, 2, 3, 9)
+    for b in range(2):
+        assert top[2 + b] == float(np.argmax(logits[b])) and np.float32(top[b]).view(np.uint32) == logits[b].max().view(np.uint32)
+
+
 # --- vyre-libs/src/nn/quant/int4.rs:203-243 -----------------------------------------------------------
 def test_int4_lib_registry_fixtures():
     assert oracle.i4x8_dot_i32(u32(0xCDEF4321), u32(0xFEDC1234), 8) == 40

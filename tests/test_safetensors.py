@@ -90,3 +90,44 @@ def test_missing_file_and_adjacent_ranges(tmp_path):
     write_shard(p, {"a": {"dtype": "I8", "shape": [2], "data_offsets": [0, 2]}, "n" * 4096: {"dtype": "I8", "shape": [2], "data_offsets": [2, 4]}},
                 b"\1\2\3\4")
     assert len(api.SafetensorIndex.open(str(p)).tensors()) == 2
+
+
+def test_reference_ingestion_fixtures(tmp_path):
+    """vyre-safetensors/tests/ingestion.rs:49-161: the single-shard fixtures of the reference's own test, byte for byte."""
+    header = (b'{"model.embed_tokens.weight":{"dtype":"BF16","shape":[2,2],"data_offsets":[0,8]},'
+              b'"model.norm.weight":{"dtype":"BF16","shape":[2],"data_offsets":[8,12]}}')
+    p = tmp_path / "model.safetensors"
+    write_shard(p, header, bytes(12))
+    idx = api.SafetensorIndex.open(str(p))  # :49-72 valid_bf16_tensors_have_exact_ranges_and_identity
+    assert len(idx.tensors()) == 2
+    emb = idx.tensor("model.embed_tokens.weight")
+    assert emb["dtype"] == "BF16" and emb["shape"] == [2, 2] and emb["file_range"] == (8 + len(header), 16 + len(header))
+    ident = idx.identity()
+    assert ident["file_len"] == 8 + len(header) + 12 and ident["header_digest"] == vb.blake3(header)
+
+    def refused(name, raw, payload, *needles):
+        q = tmp_path / name
+        if payload is None:
+            q.write_bytes(raw)
+        else:
+            write_shard(q, raw, payload)
+        with pytest.raises(vb.BackendError) as e:
+            api.SafetensorIndex.open(str(q))
+        for needle in needles:
+            assert needle in str(e.value), (name, str(e.value))
+
+    # :75-88 HeaderTooLarge { header_len: 64 MiB + 1, maximum: 64 MiB }
+    refused("oversized.safetensors", struct.pack("<Q", 64 * 1024 * 1024 + 1), None, str(64 * 1024 * 1024 + 1), str(64 * 1024 * 1024))
+    # :91-106 RangeOutOfBounds { name: weight, start: 0, end: 16, data_len: 12 }
+    refused("truncated.safetensors", b'{"weight":{"dtype":"F32","shape":[4],"data_offsets":[0,16]}}', bytes(12), "weight", "16", "12")
+    # :109-122 Overlap { left: a, right: b }
+    refused("overlap.safetensors", b'{"a":{"dtype":"U8","shape":[8],"data_offsets":[0,8]},"b":{"dtype":"U8","shape":[8],"data_offsets":[4,12]}}',
+            bytes(12), "`a`", "`b`")
+    # :125-134 duplicate tensor name `weight`
+    refused("duplicate.safetensors",
+            b'{"weight":{"dtype":"U8","shape":[1],"data_offsets":[0,1]},"weight":{"dtype":"U8","shape":[1],"data_offsets":[1,2]}}', bytes(2),
+            "duplicate tensor name `weight`")
+    # :137-151 ByteLength { name: weight, actual: 6, expected: 8 }
+    refused("wrong-length.safetensors", b'{"weight":{"dtype":"BF16","shape":[2,2],"data_offsets":[0,6]}}', bytes(6), "weight", "6", "8")
+    # :154-161 malformed metadata
+    refused("malformed.safetensors", b'{"weight": ', b"")
